@@ -1,0 +1,361 @@
+"""CudaContext: the reference's ComputeContext interface on the C-ABI library.
+
+Method names, argument meaning and error behaviour follow src/gpu/compute.d.ts:106-255
+(and the two existing implementations, src/gpu/compute.js and src/gpu/wasm-context.js);
+options objects become keyword arguments.  Tensors are opaque handles: engine code uses
+download / stageDownload / rowsView / ensureTensor, never the storage.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Iterable, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+
+ACT = {"none": 0, "gelu": 1, "tanh": 2, "relu": 3, "silu": 4, "gelu_erf": 5}  # src/gpu/kernels/actf.js:24
+
+
+class CudaError(RuntimeError):
+    """Raised for every non-zero status of the C ABI (the reference throws a JS Error)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+class Tensor:
+    """2-D row-major tensor handle {rows, cols}; storage is backend-owned (compute.d.ts:12-15)."""
+
+    __slots__ = ("h", "rows", "cols", "f16", "view")
+
+    def __init__(self, h: int, rows: int, cols: int, f16: bool = False, view: bool = False):
+        self.h, self.rows, self.cols, self.f16, self.view = h, rows, cols, f16, view
+
+    def __repr__(self):
+        return f"Tensor({self.rows}x{self.cols}{', f16' if self.f16 else ''}{', view' if self.view else ''})"
+
+
+class PackedBytes:
+    """Opaque packed-weight handle from uploadBytes (compute.d.ts:34)."""
+
+    __slots__ = ("h", "nbytes")
+
+    def __init__(self, h: int, nbytes: int):
+        self.h, self.nbytes = h, nbytes
+
+
+class StagedRead:
+    """Single-use staged readback (compute.d.ts:39-45)."""
+
+    def __init__(self, ctx: "CudaContext", h: int, rows: int, cols: int):
+        self._ctx, self._h, self._shape = ctx, h, (rows, cols)
+
+    def read(self) -> np.ndarray:
+        out = np.empty(self._shape[0] * self._shape[1], np.float32)
+        self._ctx._check(self._ctx._lib.fa_staged_read(self._ctx._h, self._h, out.ctypes.data))
+        return out
+
+
+def _np_f32(data) -> np.ndarray:
+    return np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+
+
+class CudaContext:
+    """One compute context = one CUDA stream on one B200 (compute.d.ts:106)."""
+
+    backend = "cuda"
+    hasF16 = True
+
+    def __init__(self, device: int = 0):
+        self._lib = _lib.load_library()
+        h = C.c_void_p()
+        rc = self._lib.fa_ctx_create(device, C.byref(h))
+        if rc != 0:
+            raise CudaError(rc, (self._lib.fa_last_error(None) or b"").decode())
+        self._h = h
+        self.device = device
+
+    # -- plumbing -------------------------------------------------------------------------
+    def _check(self, rc: int):
+        if rc != 0:
+            raise CudaError(rc, (self._lib.fa_last_error(self._h) or b"").decode())
+
+    def _wrap(self, h: C.c_void_p, view: bool = False) -> Tensor:
+        r, c, s = C.c_int(), C.c_int(), C.c_int()
+        self._lib.fa_tensor_info(h, C.byref(r), C.byref(c), C.byref(s), None)
+        return Tensor(h.value, r.value, c.value, f16=bool(s.value), view=view)
+
+    @staticmethod
+    def _h_of(t) -> Optional[int]:
+        return None if t is None else t.h
+
+    def _op(self, fn, *args) -> Tensor:
+        out = C.c_void_p()
+        self._check(fn(self._h, *args, C.byref(out)))
+        return self._wrap(out)
+
+    # -- tensors & memory (compute.d.ts:109-133) ------------------------------------------------
+    def upload(self, data, rows: int, cols: int) -> Tensor:
+        a = _np_f32(data)
+        assert a.size >= rows * cols, "upload: data shorter than rows*cols"
+        return self._op(self._lib.fa_upload_f32, a.ctypes.data, rows, cols)
+
+    def uploadF16(self, data, rows: int, cols: int) -> Tensor:
+        a = _np_f32(data)
+        assert a.size >= rows * cols, "uploadF16: data shorter than rows*cols"
+        return self._op(self._lib.fa_upload_f16, a.ctypes.data, rows, cols)
+
+    def alloc(self, rows: int, cols: int) -> Tensor:
+        return self._op(self._lib.fa_alloc, rows, cols)
+
+    def allocF16(self, rows: int, cols: int) -> Tensor:
+        return self._op(self._lib.fa_alloc_f16, rows, cols)
+
+    def ensureTensor(self, t) -> Tensor:
+        """Host {data, rows, cols} literal -> tensor; tensors pass through (compute.d.ts:115-117)."""
+        if isinstance(t, Tensor):
+            return t
+        return self.upload(t["data"], t["rows"], t["cols"])
+
+    def uploadBytes(self, typed) -> PackedBytes:
+        a = np.ascontiguousarray(typed)
+        raw = a.view(np.uint8).reshape(-1)
+        out = C.c_void_p()
+        self._check(self._lib.fa_upload_bytes(self._h, raw.ctypes.data, raw.size, C.byref(out)))
+        return PackedBytes(out.value, raw.size)
+
+    def freeTensor(self, t: Tensor) -> None:
+        if t is not None and t.h:
+            self._check(self._lib.fa_free_tensor(self._h, t.h))
+            t.h = None
+
+    def freeBytes(self, b: PackedBytes) -> None:
+        if b is not None and b.h:
+            self._check(self._lib.fa_free_bytes(self._h, b.h))
+            b.h = None
+
+    def pin(self, t: Tensor, toParent: bool = False) -> Tensor:
+        self._check(self._lib.fa_pin(self._h, t.h, 1 if toParent else 0))
+        return t
+
+    def pushArena(self) -> int:
+        h = C.c_int()
+        self._check(self._lib.fa_push_arena(self._h, C.byref(h)))
+        return h.value
+
+    def popArena(self, handle: Optional[int] = None) -> None:
+        self._check(self._lib.fa_pop_arena(self._h, -1 if handle is None else handle))
+
+    def trimPool(self, budgetBytes: int = 0) -> None:
+        self._check(self._lib.fa_trim_pool(self._h, budgetBytes))
+
+    def destroy(self) -> None:
+        if self._h:
+            self._lib.fa_ctx_destroy(self._h)
+            self._h = None
+
+    # -- readback (compute.d.ts:135-145) ---------------------------------------------------------
+    def download(self, t: Tensor) -> np.ndarray:
+        out = np.empty(t.rows * t.cols, np.float32)
+        self._check(self._lib.fa_download(self._h, t.h, out.ctypes.data))
+        return out
+
+    downloadF16 = download
+
+    def stageDownload(self, t: Tensor) -> StagedRead:
+        out = C.c_void_p()
+        self._check(self._lib.fa_stage_download(self._h, t.h, C.byref(out)))
+        return StagedRead(self, out.value, t.rows, t.cols)
+
+    def rowsView(self, t: Tensor, rows: int) -> Tensor:
+        out = C.c_void_p()
+        self._check(self._lib.fa_rows_view(self._h, t.h, rows, C.byref(out)))
+        return self._wrap(out, view=True)
+
+    # -- batching (compute.d.ts:147-151) ----------------------------------------------------------
+    def beginBatch(self) -> None:
+        self._check(self._lib.fa_begin_batch(self._h))
+
+    def endBatch(self) -> None:
+        self._check(self._lib.fa_end_batch(self._h))
+
+    def withBatchSync(self, fn):
+        self.beginBatch()
+        try:
+            return fn()
+        finally:
+            self.endBatch()
+
+    withBatch = withBatchSync
+
+    # -- linear algebra (compute.d.ts:153-168) -----------------------------------------------------
+    def matmul(self, a: Tensor, b: Tensor, opts: Optional[dict] = None, *, bias=None, act="none", add=None) -> Tensor:
+        if opts:
+            bias, act, add = opts.get("bias", bias), opts.get("act", act), opts.get("add", add)
+        return self._op(self._lib.fa_matmul, a.h, b.h, self._h_of(bias), ACT[act], self._h_of(add))
+
+    def matmulV2(self, a, b, opts: Optional[dict] = None, *, bias=None, act="none") -> Tensor:
+        return self.matmul(a, b, opts, bias=bias, act=act)
+
+    matmulV3 = matmulV4 = matmulF16 = matmulF16C = matmulV2
+
+    def matmulInt8(self, a: Tensor, wq: PackedBytes, scale: Tensor, N: int, K: int, opts: Optional[dict] = None, *,
+                   bias=None, act="none") -> Tensor:
+        if opts:
+            bias, act = opts.get("bias", bias), opts.get("act", act)
+        return self._op(self._lib.fa_matmul_int8, a.h, wq.h, scale.h, N, K, self._h_of(bias), ACT[act])
+
+    def matmulNBits(self, a: Tensor, bq: PackedBytes, scales: Tensor, zp: PackedBytes, N: int, blockSize: int = 32) -> Tensor:
+        return self._op(self._lib.fa_matmul_nbits, a.h, bq.h, scales.h, zp.h, N, blockSize)
+
+    def int8GemmI32(self, aq: np.ndarray, wq: PackedBytes, N: int, K: int) -> np.ndarray:
+        """Integer mode of the int8 tensor-core kernel: exact int32 accumulators [M,N]."""
+        aq = np.ascontiguousarray(aq, dtype=np.int8)
+        M = aq.shape[0]
+        out = np.empty((M, N), np.int32)
+        self._check(self._lib.fa_int8_gemm_i32(self._h, aq.ctypes.data, M, wq.h, N, K, out.ctypes.data))
+        return out
+
+    def layernorm(self, x, gamma, beta, eps: float = 1e-5) -> Tensor:
+        return self._op(self._lib.fa_layernorm, x.h, gamma.h, beta.h, eps)
+
+    def softmax(self, x) -> Tensor:
+        return self._op(self._lib.fa_softmax, x.h)
+
+    # -- convolution (compute.d.ts:170-183) --------------------------------------------------------
+    def conv1d(self, x, w, opts: Optional[dict] = None, *, cout=None, k=None, bias=None, stride=1, pad=0, padLeft=None,
+               padRight=None, dilation=1, groups=1, act="none") -> Tensor:
+        if opts:
+            cout, k = opts.get("cout", cout), opts.get("k", k)
+            bias, stride, pad = opts.get("bias", bias), opts.get("stride", stride), opts.get("pad", pad)
+            padLeft, padRight = opts.get("padLeft", padLeft), opts.get("padRight", padRight)
+            dilation, groups, act = opts.get("dilation", dilation), opts.get("groups", groups), opts.get("act", act)
+        padLeft = pad if padLeft is None else padLeft
+        padRight = pad if padRight is None else padRight
+        return self._op(self._lib.fa_conv1d, x.h, w.h, self._h_of(bias), cout, k, stride, padLeft, padRight, dilation,
+                        groups, ACT[act])
+
+    def conv2d(self, x, w, opts: Optional[dict] = None, **kw) -> Tensor:
+        o = dict(opts or {})
+        o.update(kw)
+        padH, padW = o.get("padH", 0), o.get("padW", 0)
+        pt = o.get("padTop", padH) if o.get("padTop") is not None else padH
+        pb = o.get("padBottom", padH) if o.get("padBottom") is not None else padH
+        pl = o.get("padLeft", padW) if o.get("padLeft") is not None else padW
+        pr = o.get("padRight", padW) if o.get("padRight") is not None else padW
+        return self._op(self._lib.fa_conv2d, x.h, w.h, self._h_of(o.get("bias")), o["cout"], o["cin"], o["h"], o["w"],
+                        o["kh"], o["kw"], o.get("strideH", 1), o.get("strideW", 1), pt, pb, pl, pr, o.get("groups", 1),
+                        ACT[o.get("act", "none")])
+
+    # -- attention (compute.d.ts:189-199) ----------------------------------------------------------
+    def bmmQK(self, q, b, qb, H: int, HD: int, W: int = 1, bShared: bool = False) -> Tensor:
+        return self._op(self._lib.fa_bmm_qk, q.h, b.h, self._h_of(qb), H, HD, W, 1 if bShared else 0)
+
+    def bmmPV(self, p, v, H: int, HD: int, W: int = 1) -> Tensor:
+        return self._op(self._lib.fa_bmm_pv, p.h, v.h, H, HD, W)
+
+    def relShift(self, x) -> Tensor:
+        return self._op(self._lib.fa_rel_shift_b, x.h, 1)
+
+    def relShiftB(self, x, H: int) -> Tensor:
+        return self._op(self._lib.fa_rel_shift_b, x.h, H)
+
+    # -- elementwise & data movement (compute.d.ts:201-224) -----------------------------------------
+    def ewise(self, a, b, op: str) -> Tensor:
+        return self._op(self._lib.fa_ewise, a.h, b.h, 1 if op == "mul" else 0)
+
+    def add(self, a, b) -> Tensor:
+        return self.ewise(a, b, "add")
+
+    def mul(self, a, b) -> Tensor:
+        return self.ewise(a, b, "mul")
+
+    def scale(self, x, s: float) -> Tensor:
+        return self._op(self._lib.fa_scale, x.h, float(s))
+
+    def silu(self, x) -> Tensor:
+        return self._op(self._lib.fa_unary, x.h, ACT["silu"])
+
+    def relu(self, x) -> Tensor:
+        return self._op(self._lib.fa_unary, x.h, ACT["relu"])
+
+    def glu(self, x) -> Tensor:
+        return self._op(self._lib.fa_glu, x.h)
+
+    def transpose(self, x) -> Tensor:
+        return self._op(self._lib.fa_transpose, x.h)
+
+    def sliceCols(self, x, col0: int, width: int) -> Tensor:
+        return self._op(self._lib.fa_slice_cols, x.h, col0, width)
+
+    def setCols(self, dst, src, col0: int) -> Tensor:
+        self._check(self._lib.fa_set_cols(self._h, dst.h, src.h, col0))
+        return dst
+
+    def sliceRows(self, x, row0: int, count: int) -> Tensor:
+        return self._op(self._lib.fa_slice_rows, x.h, row0, count)
+
+    def copyRows(self, dst, src, rowOffset: int) -> Tensor:
+        self._check(self._lib.fa_copy_rows(self._h, dst.h, src.h, rowOffset))
+        return dst
+
+    def concatRows(self, tensors: Sequence[Tensor]) -> Tensor:
+        arr = (C.c_void_p * len(tensors))(*[t.h for t in tensors])
+        return self._op(self._lib.fa_concat_rows, arr, len(tensors))
+
+    def subReshape(self, x, Cc: int, Tsub: int, F: int) -> Tensor:
+        return self._op(self._lib.fa_sub_reshape, x.h, Cc, Tsub, F)
+
+    def argmaxRowsIndex(self, x) -> Tensor:
+        """[rows, 2] = {argmax index, max value} per row (host token pick moved to the device)."""
+        return self._op(self._lib.fa_argmax_rows, x.h)
+
+    # -- profiling / stats (compute.d.ts:250-254) --------------------------------------------------
+    def startProfile(self, maxOps: int = 4096) -> None:
+        self._check(self._lib.fa_profile_start(self._h, maxOps))
+
+    def endProfile(self):
+        cap = 256
+        buf = (_lib.ProfileEntry * cap)()
+        n = C.c_int()
+        self._check(self._lib.fa_profile_end(self._h, buf, cap, C.byref(n)))
+        return [{"label": buf[i].label.decode(), "ms": buf[i].ms, "count": buf[i].count} for i in range(min(n.value, cap))]
+
+    def memStats(self):
+        a, b, c, d = (C.c_ulonglong() for _ in range(4))
+        self._check(self._lib.fa_mem_stats(self._h, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+        return {"created": a.value, "createdBytes": b.value, "reused": c.value, "poolBytes": d.value}
+
+    def poolInfo(self):
+        return {"bytes": self.memStats()["poolBytes"]}
+
+    # -- extras for harnesses ------------------------------------------------------------------
+    def sync(self) -> None:
+        self._check(self._lib.fa_sync(self._h))
+
+    def launchCount(self) -> int:
+        n = C.c_ulonglong()
+        self._check(self._lib.fa_launch_count(self._h, C.byref(n)))
+        return n.value
+
+    def setOption(self, key: str, value: int) -> None:
+        self._check(self._lib.fa_ctx_set_option(self._h, key.encode(), int(value)))
+
+    def stream(self) -> int:
+        s = C.c_void_p()
+        self._check(self._lib.fa_ctx_stream(self._h, C.byref(s)))
+        return s.value or 0
+
+    def devicePtr(self, t: Tensor) -> int:
+        p = C.c_void_p()
+        self._lib.fa_tensor_info(t.h, None, None, None, C.byref(p))
+        return p.value or 0
+
+
+def create_context(backend: str = "cuda", device: int = 0) -> CudaContext:
+    """The "cuda" branch a maintainer adds to createContext() (src/gpu/context.js:23-37)."""
+    if backend != "cuda":
+        raise ValueError(f"this package only provides the 'cuda' backend (asked for {backend!r})")
+    return CudaContext(device)

@@ -1,0 +1,691 @@
+// Glue ops the encoder/decoder forwards call between GEMMs.  Each follows the arithmetic of the
+// reference's CPU twin (src/gpu/wasm-context.js:308-685) and the grid shape idea of its WGSL kernel
+// (src/gpu/kernels/{normalization,attention,convolution,tensor-ops}.js); all are f32.
+#include "fa_internal.cuh"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// One CTA (256 threads) per row; two-pass mean/variance (wasm-context.js:308-326).
+__global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ g,
+                                                   const float *__restrict__ b, float *__restrict__ y, int R, int C,
+                                                   float eps) {
+  __shared__ float red[8];
+  __shared__ float stat;
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const float *row = x + (size_t)r * C;
+    float s = 0.f;
+    for (int j = threadIdx.x; j < C; j += 256) s += row[j];
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; w++) t += red[w];
+      stat = t / (float)C;
+    }
+    __syncthreads();
+    const float mean = stat;
+    float v = 0.f;
+    for (int j = threadIdx.x; j < C; j += 256) {
+      float d = row[j] - mean;
+      v += d * d;
+    }
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; w++) t += red[w];
+      stat = 1.0f / sqrtf(t / (float)C + eps);
+    }
+    __syncthreads();
+    const float inv = stat;
+    for (int j = threadIdx.x; j < C; j += 256) y[(size_t)r * C + j] = (row[j] - mean) * inv * g[j] + b[j];
+    __syncthreads();
+  }
+}
+
+// One warp per row (wasm-context.js:327-343).
+__global__ void k_softmax(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
+  const int warps = (blockDim.x >> 5);
+  const int lane = threadIdx.x & 31;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+    const float *row = x + (size_t)r * C;
+    float mx = -INFINITY;
+    for (int j = lane; j < C; j += 32) mx = fmaxf(mx, row[j]);
+    mx = warp_max(mx);
+    float s = 0.f;
+    for (int j = lane; j < C; j += 32) s += expf(row[j] - mx);
+    s = warp_sum(s);
+    const float inv = 1.0f / s;
+    for (int j = lane; j < C; j += 32) y[(size_t)r * C + j] = expf(row[j] - mx) * inv;
+  }
+}
+
+__global__ void k_ewise(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ y, size_t n, int C,
+                        int bcast, int mul) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float bv = bcast ? b[i % C] : b[i];
+    y[i] = mul ? a[i] * bv : a[i] + bv;
+  }
+}
+__global__ void k_scale(const float *__restrict__ x, float *__restrict__ y, size_t n, float s) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    y[i] = x[i] * s;
+}
+__global__ void k_unary(const float *__restrict__ x, float *__restrict__ y, size_t n, int act) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    y[i] = fa_actf(x[i], act);
+}
+// x[2C,T] -> x[c,t] * sigmoid(x[c+C,t]) (wasm-context.js:428-434)
+__global__ void k_glu(const float *__restrict__ x, float *__restrict__ y, int C, int T) {
+  size_t n = (size_t)C * T;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    y[i] = x[i] * (1.0f / (1.0f + expf(-x[i + n])));
+}
+__global__ void k_transpose(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
+  __shared__ float t[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    int r = r0 + i, c = c0 + threadIdx.x;
+    if (r < R && c < C) t[i][threadIdx.x] = x[(size_t)r * C + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    int c = c0 + i, r = r0 + threadIdx.x;
+    if (r < R && c < C) y[(size_t)c * R + r] = t[threadIdx.x][i];
+  }
+}
+// dst[r, dcol0 + j] = src[r, scol0 + j] for j < width
+__global__ void k_copy_cols(const float *__restrict__ src, int scols, int scol0, float *__restrict__ dst, int dcols,
+                            int dcol0, int rows, int width) {
+  size_t n = (size_t)rows * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    int r = (int)(i / width), j = (int)(i % width);
+    dst[(size_t)r * dcols + dcol0 + j] = src[(size_t)r * scols + scol0 + j];
+  }
+}
+// [C, Tsub*F] -> [Tsub, C*F] (wasm-context.js:552-563)
+__global__ void k_sub_reshape(const float *__restrict__ x, float *__restrict__ y, int C, int Tsub, int F) {
+  size_t n = (size_t)Tsub * C * F;
+  int CF = C * F;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    int ho = (int)(i / CF), rem = (int)(i % CF), c = rem / F, wo = rem % F;
+    y[i] = x[(size_t)c * Tsub * F + (size_t)ho * F + wo];
+  }
+}
+// Batched rel_shift (wasm-context.js:525-538): x[H*t, 2t-1] -> [H*t, t]
+__global__ void k_rel_shift_b(const float *__restrict__ x, float *__restrict__ y, int H, int t) {
+  const int p = 2 * t - 1, twoT = 2 * t;
+  size_t n = (size_t)H * t * t;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    int j = (int)(idx % t), i = (int)((idx / t) % t), h = (int)(idx / ((size_t)t * t));
+    long long f = (long long)t + (long long)i * p + j;
+    int col = (int)(f % twoT);
+    y[idx] = col == 0 ? 0.0f : x[((size_t)h * t + (size_t)(f / twoT)) * p + (col - 1)];
+  }
+}
+
+// Batched QK^T (wasm-context.js:462-482): one (w,h) per blockIdx.z, 32x32 output tile per CTA.
+// out[((w*H+h)*T+i)*Tb + j] = sum_d (q[(w*T+i)*S + h*HD + d] + qb[h*HD+d]) * b[brow(j)*S + h*HD + d]
+__global__ void __launch_bounds__(256) k_bmm_qk(const float *__restrict__ q, const float *__restrict__ b,
+                                                const float *__restrict__ qb, float *__restrict__ out, int T, int Tb,
+                                                int H, int HD, int bShared) {
+  __shared__ float Qs[32][33], Bs[32][33];
+  const int w = blockIdx.z / H, h = blockIdx.z % H, S = H * HD;
+  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 rows of threads
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int d0 = 0; d0 < HD; d0 += 32) {
+    for (int r = ty; r < 32; r += 8) {
+      int d = d0 + tx;
+      int i = i0 + r, j = j0 + r;
+      float qv = 0.f, bv = 0.f;
+      if (d < HD) {
+        if (i < T) qv = q[((size_t)w * T + i) * S + h * HD + d] + (qb ? qb[h * HD + d] : 0.f);
+        if (j < Tb) bv = b[((size_t)(bShared ? 0 : w) * Tb + j) * S + h * HD + d];
+      }
+      Qs[r][tx] = qv;
+      Bs[r][tx] = bv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int d = 0; d < 32; d++) {
+      float bv = Bs[tx][d];
+#pragma unroll
+      for (int u = 0; u < 4; u++) acc[u] = fmaf(Qs[ty + 8 * u][d], bv, acc[u]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    int i = i0 + ty + 8 * u, j = j0 + tx;
+    if (i < T && j < Tb) out[(((size_t)w * H + h) * T + i) * Tb + j] = acc[u];
+  }
+}
+
+// Batched P@V (wasm-context.js:484-500): out[(w*Tq+i)*S + h*HD + d] = sum_j p[((w*H+h)*Tq+i)*Tk + j] * v[(w*Tk+j)*S + h*HD + d]
+__global__ void __launch_bounds__(256) k_bmm_pv(const float *__restrict__ p, const float *__restrict__ v,
+                                                float *__restrict__ out, int Tq, int Tk, int H, int HD) {
+  __shared__ float Ps[32][33], Vs[32][33];
+  const int w = blockIdx.z / H, h = blockIdx.z % H, S = H * HD;
+  const int i0 = blockIdx.y * 32, d0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j0 = 0; j0 < Tk; j0 += 32) {
+    for (int r = ty; r < 32; r += 8) {
+      int i = i0 + r, jc = j0 + tx;
+      Ps[r][tx] = (i < Tq && jc < Tk) ? p[(((size_t)w * H + h) * Tq + i) * Tk + jc] : 0.f;
+      int jr = j0 + r, d = d0 + tx;
+      Vs[r][tx] = (jr < Tk && d < HD) ? v[((size_t)w * Tk + jr) * S + h * HD + d] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+      float vv = Vs[j][tx];
+#pragma unroll
+      for (int u = 0; u < 4; u++) acc[u] = fmaf(Ps[ty + 8 * u][j], vv, acc[u]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    int i = i0 + ty + 8 * u, d = d0 + tx;
+    if (i < Tq && d < HD) out[((size_t)w * Tq + i) * S + h * HD + d] = acc[u];
+  }
+}
+
+// Direct grouped 1-D conv (rust/wasm-kernels/src/lib.rs:99-138): one thread per output sample.
+__global__ void k_conv1d(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+                         float *__restrict__ y, int cout, int cin, int L, int Lout, int k, int stride, int padl,
+                         int dil, int groups, int act) {
+  const int cin_g = cin / groups, cout_g = cout / groups;
+  size_t n = (size_t)cout * Lout;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    int co = (int)(idx / Lout), t = (int)(idx % Lout), g = co / cout_g;
+    float acc = 0.f;
+    for (int cig = 0; cig < cin_g; cig++) {
+      const float *xr = x + (size_t)(g * cin_g + cig) * L;
+      const float *wr = w + ((size_t)co * cin_g + cig) * k;
+      for (int kk = 0; kk < k; kk++) {
+        int xi = t * stride + kk * dil - padl;
+        if (xi >= 0 && xi < L) acc = fmaf(xr[xi], wr[kk], acc);
+      }
+    }
+    if (bias) acc += bias[co];
+    y[idx] = fa_actf(acc, act);
+  }
+}
+
+// Direct 2-D conv, batch 1 (wasm-context.js:632-685): one thread per output element.
+__global__ void k_conv2d(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+                         float *__restrict__ y, int cout, int cin, int h, int W, int kh, int kw, int sh, int sw, int pt,
+                         int pl, int Ho, int Wo, int groups, int act) {
+  const int cinG = cin / groups, coutG = cout / groups;
+  size_t n = (size_t)cout * Ho * Wo;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    int wo = (int)(idx % Wo), ho = (int)((idx / Wo) % Ho), co = (int)(idx / ((size_t)Wo * Ho));
+    int g = co / coutG;
+    float acc = bias ? bias[co] : 0.f;
+    for (int ci = 0; ci < cinG; ci++) {
+      const float *xp = x + (size_t)(g * cinG + ci) * h * W;
+      const float *wp = w + ((size_t)co * cinG + ci) * kh * kw;
+      for (int a = 0; a < kh; a++) {
+        int hi = ho * sh + a - pt;
+        if (hi < 0 || hi >= h) continue;
+        for (int b = 0; b < kw; b++) {
+          int wi = wo * sw + b - pl;
+          if (wi < 0 || wi >= W) continue;
+          acc = fmaf(xp[(size_t)hi * W + wi], wp[a * kw + b], acc);
+        }
+      }
+    }
+    y[idx] = fa_actf(acc, act);
+  }
+}
+
+// Per-row argmax: out[r] = {index, value}; ties resolve to the lowest index like the host loop
+// of src/engines/asr-whisper/index.ts:80-97.
+__global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x, float *__restrict__ out, int R, int C) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const float *row = x + (size_t)r * C;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int j = threadIdx.x; j < C; j += 256) {
+      float v = row[j];
+      if (v > best || (v == best && j < idx)) { best = v; idx = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < 8; w++)
+        if (bv[w] > bv[0] || (bv[w] == bv[0] && bi[w] < bi[0])) { bv[0] = bv[w]; bi[0] = bi[w]; }
+      out[(size_t)r * 2] = (float)bi[0];
+      out[(size_t)r * 2 + 1] = bv[0];
+    }
+    __syncthreads();
+  }
+}
+
+int grid1d(fa_ctx *ctx, size_t n, int block) {
+  size_t g = (n + block - 1) / block, cap = (size_t)ctx->sm_count * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+int need_f32(fa_ctx *ctx, const fa_tensor *t, const char *op) {
+  FA_REQUIRE(ctx, fa_valid(ctx, t), "%s: unknown tensor handle", op);
+  FA_REQUIRE(ctx, t->storage == FA_F32, "%s: operand must be f32 storage", op);
+  return FA_OK;
+}
+
+}  // namespace
+
+#define GLUE_PROLOGUE(name)                                                         \
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, name ": NULL argument");    \
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+
+extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
+                            fa_tensor **out) {
+  GLUE_PROLOGUE("layernorm");
+  FA_TRY(need_f32(ctx, x, "layernorm"));
+  FA_TRY(need_f32(ctx, gamma, "layernorm"));
+  FA_TRY(need_f32(ctx, beta, "layernorm"));
+  FA_REQUIRE(ctx, gamma->rows * gamma->cols >= x->cols && beta->rows * beta->cols >= x->cols,
+             "layernorm: gamma/beta shorter than %d columns", x->cols);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows, x->cols, FA_F32, true, &y));
+  if (x->rows && x->cols) {
+    int grid = x->rows < ctx->sm_count * 8 ? x->rows : ctx->sm_count * 8;
+    {
+      LaunchScope ls(ctx, "layernorm");
+      k_layernorm<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)gamma->dptr,
+                                                 (const float *)beta->dptr, (float *)y->dptr, x->rows, x->cols, eps);
+    }
+    FA_LAUNCH_CHECK(ctx, "layernorm");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
+  GLUE_PROLOGUE("softmax");
+  FA_TRY(need_f32(ctx, x, "softmax"));
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows, x->cols, FA_F32, true, &y));
+  if (x->rows && x->cols) {
+    int grid = ceil_div(x->rows, 8);
+    if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
+    {
+      LaunchScope ls(ctx, "softmax");
+      k_softmax<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+    }
+    FA_LAUNCH_CHECK(ctx, "softmax");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_ewise(fa_ctx *ctx, const fa_tensor *a, const fa_tensor *b, int op_mul, fa_tensor **out) {
+  GLUE_PROLOGUE("ewise");
+  FA_TRY(need_f32(ctx, a, "ewise"));
+  FA_TRY(need_f32(ctx, b, "ewise"));
+  const bool bcast = b->rows == 1 && a->rows != 1;
+  FA_REQUIRE(ctx, b->cols == a->cols && (bcast || b->rows == a->rows), "ewise: a is [%d,%d], b is [%d,%d]", a->rows,
+             a->cols, b->rows, b->cols);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, a->rows, a->cols, FA_F32, true, &y));
+  size_t n = (size_t)a->rows * a->cols;
+  if (n) {
+    {
+      LaunchScope ls(ctx, "ewise");
+      k_ewise<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)a->dptr, (const float *)b->dptr,
+                                                            (float *)y->dptr, n, a->cols, bcast ? 1 : 0, op_mul);
+    }
+    FA_LAUNCH_CHECK(ctx, "ewise");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_scale(fa_ctx *ctx, const fa_tensor *x, float s, fa_tensor **out) {
+  GLUE_PROLOGUE("scale");
+  FA_TRY(need_f32(ctx, x, "scale"));
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows, x->cols, FA_F32, true, &y));
+  size_t n = (size_t)x->rows * x->cols;
+  if (n) {
+    {
+      LaunchScope ls(ctx, "scale");
+      k_scale<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, n, s);
+    }
+    FA_LAUNCH_CHECK(ctx, "scale");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_unary(fa_ctx *ctx, const fa_tensor *x, int act, fa_tensor **out) {
+  GLUE_PROLOGUE("unary");
+  FA_TRY(need_f32(ctx, x, "unary"));
+  FA_REQUIRE(ctx, act >= 0 && act <= 5, "unary: unknown activation code %d", act);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows, x->cols, FA_F32, true, &y));
+  size_t n = (size_t)x->rows * x->cols;
+  if (n) {
+    {
+      LaunchScope ls(ctx, "unary");
+      k_unary<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, n, act);
+    }
+    FA_LAUNCH_CHECK(ctx, "unary");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_glu(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
+  GLUE_PROLOGUE("glu");
+  FA_TRY(need_f32(ctx, x, "glu"));
+  FA_REQUIRE(ctx, x->rows % 2 == 0, "glu: %d rows is not even", x->rows);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows / 2, x->cols, FA_F32, true, &y));
+  size_t n = (size_t)(x->rows / 2) * x->cols;
+  if (n) {
+    {
+      LaunchScope ls(ctx, "glu");
+      k_glu<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows / 2, x->cols);
+    }
+    FA_LAUNCH_CHECK(ctx, "glu");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_transpose(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
+  GLUE_PROLOGUE("transpose");
+  FA_TRY(need_f32(ctx, x, "transpose"));
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->cols, x->rows, FA_F32, true, &y));
+  if (x->rows && x->cols) {
+    dim3 grid(ceil_div(x->cols, 32), ceil_div(x->rows, 32)), block(32, 8);
+    FA_REQUIRE(ctx, grid.y <= 65535, "transpose: %d rows is too many", x->rows);
+    {
+      LaunchScope ls(ctx, "transpose");
+      k_transpose<<<grid, block, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+    }
+    FA_LAUNCH_CHECK(ctx, "transpose");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_slice_cols(fa_ctx *ctx, const fa_tensor *x, int col0, int width, fa_tensor **out) {
+  GLUE_PROLOGUE("sliceCols");
+  FA_TRY(need_f32(ctx, x, "sliceCols"));
+  FA_REQUIRE(ctx, col0 >= 0 && width >= 0 && col0 + width <= x->cols, "sliceCols: [%d,%d) of %d columns", col0,
+             col0 + width, x->cols);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows, width, FA_F32, true, &y));
+  size_t n = (size_t)x->rows * width;
+  if (n) {
+    {
+      LaunchScope ls(ctx, "slice_cols");
+      k_copy_cols<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, x->cols, col0, (float *)y->dptr,
+                                                                width, 0, x->rows, width);
+    }
+    FA_LAUNCH_CHECK(ctx, "slice_cols");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_set_cols(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, int col0) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "setCols: NULL context");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  FA_TRY(need_f32(ctx, dst, "setCols"));
+  FA_TRY(need_f32(ctx, src, "setCols"));
+  FA_REQUIRE(ctx, col0 >= 0 && col0 + src->cols <= dst->cols && src->rows <= dst->rows,
+             "setCols: src [%d,%d] at column %d does not fit dst [%d,%d]", src->rows, src->cols, col0, dst->rows, dst->cols);
+  size_t n = (size_t)src->rows * src->cols;
+  if (n) {
+    {
+      LaunchScope ls(ctx, "set_cols");
+      k_copy_cols<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)src->dptr, src->cols, 0,
+                                                                (float *)dst->dptr, dst->cols, col0, src->rows, src->cols);
+    }
+    FA_LAUNCH_CHECK(ctx, "set_cols");
+  }
+  return FA_OK;
+}
+
+extern "C" int fa_slice_rows(fa_ctx *ctx, const fa_tensor *x, int row0, int count, fa_tensor **out) {
+  GLUE_PROLOGUE("sliceRows");
+  FA_TRY(need_f32(ctx, x, "sliceRows"));
+  FA_REQUIRE(ctx, row0 >= 0 && count >= 0 && row0 + count <= x->rows, "sliceRows: [%d,%d) of %d rows", row0, row0 + count,
+             x->rows);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, count, x->cols, FA_F32, true, &y));
+  size_t bytes = (size_t)count * x->cols * 4;
+  if (bytes)
+    FA_CHECK_CUDA(ctx, cudaMemcpyAsync(y->dptr, (const float *)x->dptr + (size_t)row0 * x->cols, bytes,
+                                       cudaMemcpyDeviceToDevice, ctx->stream));
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_copy_rows(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, int row_offset) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "copyRows: NULL context");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  FA_TRY(need_f32(ctx, dst, "copyRows"));
+  FA_TRY(need_f32(ctx, src, "copyRows"));
+  FA_REQUIRE(ctx, src->cols == dst->cols && row_offset >= 0 && row_offset + src->rows <= dst->rows,
+             "copyRows: src [%d,%d] at row %d does not fit dst [%d,%d]", src->rows, src->cols, row_offset, dst->rows,
+             dst->cols);
+  size_t bytes = (size_t)src->rows * src->cols * 4;
+  if (bytes)
+    FA_CHECK_CUDA(ctx, cudaMemcpyAsync((float *)dst->dptr + (size_t)row_offset * dst->cols, src->dptr, bytes,
+                                       cudaMemcpyDeviceToDevice, ctx->stream));
+  return FA_OK;
+}
+
+extern "C" int fa_concat_rows(fa_ctx *ctx, const fa_tensor *const *tensors, int count, fa_tensor **out) {
+  GLUE_PROLOGUE("concatRows");
+  FA_REQUIRE(ctx, tensors && count > 0, "concatRows: empty list");
+  int rows = 0, cols = 0;
+  for (int i = 0; i < count; i++) {
+    FA_TRY(need_f32(ctx, tensors[i], "concatRows"));
+    if (i == 0) cols = tensors[i]->cols;
+    FA_REQUIRE(ctx, tensors[i]->cols == cols, "concatRows: tensor %d has %d columns, expected %d", i, tensors[i]->cols, cols);
+    rows += tensors[i]->rows;
+  }
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, rows, cols, FA_F32, true, &y));
+  size_t off = 0;
+  for (int i = 0; i < count; i++) {
+    size_t bytes = (size_t)tensors[i]->rows * cols * 4;
+    if (bytes)
+      FA_CHECK_CUDA(ctx, cudaMemcpyAsync((char *)y->dptr + off, tensors[i]->dptr, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    off += bytes;
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_sub_reshape(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, fa_tensor **out) {
+  GLUE_PROLOGUE("subReshape");
+  FA_TRY(need_f32(ctx, x, "subReshape"));
+  FA_REQUIRE(ctx, C > 0 && Tsub > 0 && F > 0 && (long long)x->rows * x->cols >= (long long)C * Tsub * F,
+             "subReshape: x has %d elements, need %d*%d*%d", x->rows * x->cols, C, Tsub, F);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, Tsub, C * F, FA_F32, true, &y));
+  size_t n = (size_t)Tsub * C * F;
+  {
+    LaunchScope ls(ctx, "sub_reshape");
+    k_sub_reshape<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, C, Tsub, F);
+  }
+  FA_LAUNCH_CHECK(ctx, "sub_reshape");
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_rel_shift_b(fa_ctx *ctx, const fa_tensor *x, int H, fa_tensor **out) {
+  GLUE_PROLOGUE("relShiftB");
+  FA_TRY(need_f32(ctx, x, "relShiftB"));
+  FA_REQUIRE(ctx, H > 0 && x->rows % H == 0, "relShiftB: %d rows not divisible by H=%d", x->rows, H);
+  const int t = x->rows / H;
+  FA_REQUIRE(ctx, x->cols == 2 * t - 1, "relShiftB: x is [%d,%d], expected %d columns", x->rows, x->cols, 2 * t - 1);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, H * t, t, FA_F32, true, &y));
+  size_t n = (size_t)H * t * t;
+  if (n) {
+    {
+      LaunchScope ls(ctx, "rel_shift_b");
+      k_rel_shift_b<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, H, t);
+    }
+    FA_LAUNCH_CHECK(ctx, "rel_shift_b");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, const fa_tensor *qb, int H, int HD, int W,
+                         int b_shared, fa_tensor **out) {
+  GLUE_PROLOGUE("bmmQK");
+  FA_TRY(need_f32(ctx, q, "bmmQK"));
+  FA_TRY(need_f32(ctx, b, "bmmQK"));
+  if (qb) FA_TRY(need_f32(ctx, qb, "bmmQK"));
+  FA_REQUIRE(ctx, H > 0 && HD > 0 && W > 0 && q->cols == H * HD && b->cols == H * HD, "bmmQK: q/b need %d columns", H * HD);
+  FA_REQUIRE(ctx, q->rows % W == 0 && (b_shared || b->rows % W == 0), "bmmQK: rows not divisible by W=%d", W);
+  if (qb) FA_REQUIRE(ctx, qb->rows * qb->cols >= H * HD, "bmmQK: qb shorter than %d", H * HD);
+  const int T = q->rows / W, Tb = b_shared ? b->rows : b->rows / W;
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, W * H * T, Tb, FA_F32, true, &y));
+  if (T && Tb) {
+    dim3 grid(ceil_div(Tb, 32), ceil_div(T, 32), W * H);
+    FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmQK: batch too large");
+    {
+      LaunchScope ls(ctx, "bmm_qk");
+      k_bmm_qk<<<grid, 256, 0, ctx->stream>>>((const float *)q->dptr, (const float *)b->dptr,
+                                              qb ? (const float *)qb->dptr : nullptr, (float *)y->dptr, T, Tb, H, HD,
+                                              b_shared);
+    }
+    FA_LAUNCH_CHECK(ctx, "bmm_qk");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, int H, int HD, int W, fa_tensor **out) {
+  GLUE_PROLOGUE("bmmPV");
+  FA_TRY(need_f32(ctx, p, "bmmPV"));
+  FA_TRY(need_f32(ctx, v, "bmmPV"));
+  FA_REQUIRE(ctx, H > 0 && HD > 0 && W > 0 && v->cols == H * HD, "bmmPV: v needs %d columns", H * HD);
+  FA_REQUIRE(ctx, v->rows % W == 0 && p->rows % (W * H) == 0, "bmmPV: rows not divisible by W*H");
+  const int Tk = v->rows / W, Tq = p->rows / (W * H);
+  FA_REQUIRE(ctx, p->cols == Tk, "bmmPV: p has %d columns, v has %d rows per window", p->cols, Tk);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, W * Tq, H * HD, FA_F32, true, &y));
+  if (Tq && Tk) {
+    dim3 grid(ceil_div(HD, 32), ceil_div(Tq, 32), W * H);
+    FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmPV: batch too large");
+    {
+      LaunchScope ls(ctx, "bmm_pv");
+      k_bmm_pv<<<grid, 256, 0, ctx->stream>>>((const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, Tq, Tk, H, HD);
+    }
+    FA_LAUNCH_CHECK(ctx, "bmm_pv");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k,
+                         int stride, int pad_left, int pad_right, int dilation, int groups, int act, fa_tensor **out) {
+  GLUE_PROLOGUE("conv1d");
+  FA_TRY(need_f32(ctx, x, "conv1d"));
+  FA_TRY(need_f32(ctx, w, "conv1d"));
+  if (bias) FA_TRY(need_f32(ctx, bias, "conv1d"));
+  const int cin = x->rows, L = x->cols;
+  FA_REQUIRE(ctx, cout > 0 && k > 0 && stride > 0 && dilation > 0 && groups > 0 && cin % groups == 0 && cout % groups == 0,
+             "conv1d: bad geometry cout=%d k=%d stride=%d dilation=%d groups=%d cin=%d", cout, k, stride, dilation, groups, cin);
+  FA_REQUIRE(ctx, (long long)w->rows * w->cols >= (long long)cout * (cin / groups) * k, "conv1d: weight tensor too small");
+  if (bias) FA_REQUIRE(ctx, bias->rows * bias->cols >= cout, "conv1d: bias shorter than cout");
+  const int Lout = (L + pad_left + pad_right - dilation * (k - 1) - 1) / stride + 1;
+  FA_REQUIRE(ctx, Lout > 0, "conv1d: empty output (L=%d)", L);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, cout, Lout, FA_F32, true, &y));
+  size_t n = (size_t)cout * Lout;
+  {
+    LaunchScope ls(ctx, "conv1d");
+    k_conv1d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
+                                                           bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr,
+                                                           cout, cin, L, Lout, k, stride, pad_left, dilation, groups, act);
+  }
+  FA_LAUNCH_CHECK(ctx, "conv1d");
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin,
+                         int h, int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom,
+                         int pad_left, int pad_right, int groups, int act, fa_tensor **out) {
+  GLUE_PROLOGUE("conv2d");
+  FA_TRY(need_f32(ctx, x, "conv2d"));
+  FA_TRY(need_f32(ctx, w, "conv2d"));
+  if (bias) FA_TRY(need_f32(ctx, bias, "conv2d"));
+  FA_REQUIRE(ctx, cout > 0 && cin > 0 && groups > 0 && cin % groups == 0 && cout % groups == 0 && stride_h > 0 && stride_w > 0,
+             "conv2d: bad geometry");
+  FA_REQUIRE(ctx, (long long)x->rows * x->cols >= (long long)cin * h * w_, "conv2d: input smaller than cin*h*w");
+  FA_REQUIRE(ctx, (long long)w->rows * w->cols >= (long long)cout * (cin / groups) * kh * kw, "conv2d: weight tensor too small");
+  const int Ho = (h + pad_top + pad_bottom - kh) / stride_h + 1, Wo = (w_ + pad_left + pad_right - kw) / stride_w + 1;
+  FA_REQUIRE(ctx, Ho > 0 && Wo > 0, "conv2d: empty output");
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, cout, Ho * Wo, FA_F32, true, &y));
+  size_t n = (size_t)cout * Ho * Wo;
+  {
+    LaunchScope ls(ctx, "conv2d");
+    k_conv2d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
+                                                           bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr,
+                                                           cout, cin, h, w_, kh, kw, stride_h, stride_w, pad_top, pad_left,
+                                                           Ho, Wo, groups, act);
+  }
+  FA_LAUNCH_CHECK(ctx, "conv2d");
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
+  GLUE_PROLOGUE("argmaxRows");
+  FA_TRY(need_f32(ctx, x, "argmaxRows"));
+  FA_REQUIRE(ctx, x->cols > 0, "argmaxRows: no columns");
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows, 2, FA_F32, true, &y));
+  if (x->rows) {
+    int grid = x->rows < ctx->sm_count * 8 ? x->rows : ctx->sm_count * 8;
+    {
+      LaunchScope ls(ctx, "argmax_rows");
+      k_argmax_rows<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+    }
+    FA_LAUNCH_CHECK(ctx, "argmax_rows");
+  }
+  *out = y;
+  return FA_OK;
+}

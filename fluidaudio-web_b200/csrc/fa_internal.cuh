@@ -1,0 +1,223 @@
+// Internal declarations shared by the translation units of libfa_cuda.so.
+// Nothing here crosses the C ABI (include/fa_cuda.h).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/fa_cuda.h"
+
+// ---- handles ---------------------------------------------------------------
+
+struct fa_tensor {
+  int rows = 0, cols = 0;
+  int storage = FA_F32;      // FA_F32 or FA_F16 element storage, row-major [rows][cols]
+  void *dptr = nullptr;      // device pointer of element (0,0)
+  size_t bytes = 0;          // size of the pool block behind dptr (0 for views)
+  bool view = false;         // rowsView alias: owns nothing
+  bool pooled = false;       // block returns to the pool (alloc) vs. plain free (upload)
+  int arena = -1;            // id of the arena that releases it, -1 = persistent
+  // Lazily built operand copy used when this tensor is the B side of a tensor-core GEMM:
+  // f16 [cols][kpad] (row n holds column n of the matrix, K contiguous, zero padded).
+  void *bt_f16 = nullptr;
+  size_t bt_bytes = 0;
+  int bt_kpad = 0;
+};
+
+struct fa_bytes {
+  void *dptr = nullptr;
+  size_t nbytes = 0;
+  size_t block = 0;
+  // Lazily built int8 [N][kpad] copy (K contiguous) of a [K][N] int8 payload.
+  void *nk_i8 = nullptr;
+  size_t nk_bytes = 0;
+  int nk_N = 0, nk_K = 0, nk_kpad = 0;
+  // Lazily built f16 [N][kpad] dequantised copy of an int4 payload (with the scales/zp it was built from).
+  void *nk_f16 = nullptr;
+  size_t nk_f16_bytes = 0;
+  int f16_N = 0, f16_K = 0, f16_kpad = 0;
+  const void *f16_scales = nullptr, *f16_zp = nullptr;
+};
+
+struct fa_staged {
+  float *host = nullptr;     // page-locked snapshot target (f32)
+  void *dev_tmp = nullptr;   // device f32 temp when the source is f16 storage
+  size_t dev_tmp_bytes = 0;
+  size_t count = 0;
+  cudaEvent_t done = nullptr;
+  bool consumed = false;
+};
+
+struct ProfileRec {
+  const char *label;
+  cudaEvent_t e0, e1;
+};
+
+struct fa_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  bool in_batch = false;
+  unsigned long long launches = 0;
+  // options
+  int int8_limbs = 2;
+  size_t pool_cap = 0;
+  // exact-size pool (the reference pools by exact byte size, buffer-pool.js:49-84)
+  std::unordered_map<size_t, std::vector<void *>> pool;
+  size_t pool_bytes = 0;       // idle bytes in the pool
+  size_t live_bytes = 0;       // bytes handed out by cudaMalloc and not yet cudaFree'd
+  unsigned long long created = 0, created_bytes = 0, reused = 0;
+  std::unordered_map<void *, size_t> blocks;   // every device block we own -> size
+  // arenas: id -> tensors allocated while it was the newest open scope
+  int next_arena = 1;
+  std::vector<int> arena_stack;
+  std::unordered_map<int, std::vector<fa_tensor *>> arena_members;
+  std::unordered_set<fa_tensor *> tensors;     // every live handle
+  std::unordered_set<fa_bytes *> byte_handles;
+  std::unordered_set<fa_staged *> staged;
+  // profiling
+  bool profiling = false;
+  int profile_cap = 0;
+  std::vector<ProfileRec> prof;
+  // device-side status word written by kernels whose bounded waits ran out
+  int *dev_status = nullptr;
+  // scratch for tensor-core prepasses (grown on demand, stream-ordered reuse)
+  void *scratch_a = nullptr;
+  size_t scratch_a_bytes = 0;
+  void *scratch_s = nullptr;
+  size_t scratch_s_bytes = 0;
+};
+
+// ---- errors ----------------------------------------------------------------
+
+int fa_fail(fa_ctx *ctx, int code, const char *fmt, ...);
+#define FA_CHECK_CUDA(ctx, expr)                                                                      \
+  do {                                                                                                \
+    cudaError_t e__ = (expr);                                                                         \
+    if (e__ != cudaSuccess)                                                                           \
+      return fa_fail(ctx, e__ == cudaErrorMemoryAllocation ? FA_ERR_OOM : FA_ERR_CUDA, "%s: %s", #expr, \
+                     cudaGetErrorString(e__));                                                        \
+  } while (0)
+#define FA_REQUIRE(ctx, cond, ...)                            \
+  do {                                                        \
+    if (!(cond)) return fa_fail(ctx, FA_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+#define FA_TRY(expr)            \
+  do {                          \
+    int rc__ = (expr);          \
+    if (rc__ != FA_OK) return rc__; \
+  } while (0)
+
+// ---- memory (fa_context.cu) -----------------------------------------------------
+
+int fa_block_acquire(fa_ctx *ctx, size_t bytes, void **out, size_t *block_bytes);
+void fa_block_release(fa_ctx *ctx, void *p);            // back to the pool
+void fa_block_free(fa_ctx *ctx, void *p);               // cudaFree now
+int fa_tensor_new(fa_ctx *ctx, int rows, int cols, int storage, bool pooled, fa_tensor **out);
+int fa_scratch(fa_ctx *ctx, void **slot, size_t *slot_bytes, size_t need);
+bool fa_valid(fa_ctx *ctx, const fa_tensor *t);
+bool fa_valid_bytes(fa_ctx *ctx, const fa_bytes *b);
+// f32 device pointer for `t`: the tensor itself when it is f32 storage, else a converted
+// temporary (arena-scoped like any alloc) returned through *tmp.
+int fa_as_f32(fa_ctx *ctx, const fa_tensor *t, const float **ptr, fa_tensor **tmp);
+
+// ---- launch bookkeeping ------------------------------------------------------------
+
+// Wraps one kernel launch: counts it and, while profiling, brackets it with CUDA events on the
+// context stream (the reference profiler puts each dispatch in its own timestamped pass,
+// scheduler.js:139-180).
+struct LaunchScope {
+  fa_ctx *ctx;
+  bool rec = false;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  const char *label;
+  LaunchScope(fa_ctx *c, const char *lbl) : ctx(c), label(lbl) {
+    ctx->launches++;
+    if (ctx->profiling && (int)ctx->prof.size() < ctx->profile_cap) {
+      if (cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) {
+        rec = true;
+        cudaEventRecord(e0, ctx->stream);
+      }
+    }
+  }
+  ~LaunchScope() {
+    if (rec) {
+      cudaEventRecord(e1, ctx->stream);
+      ctx->prof.push_back({label, e0, e1});
+    }
+  }
+};
+#define FA_LAUNCH_CHECK(ctx, label)                                                          \
+  do {                                                                                       \
+    cudaError_t e__ = cudaGetLastError();                                                    \
+    if (e__ != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch %s: %s", label, cudaGetErrorString(e__)); \
+  } while (0)
+
+// ---- device helpers ----------------------------------------------------------------
+
+// Activation table of src/gpu/kernels/actf.js:5-22 (same clamps), f32.
+__device__ __forceinline__ float fa_actf(float x, int a) {
+  switch (a) {
+    case FA_ACT_GELU: {
+      float t = fminf(fmaxf(0.7978845608028654f * (x + 0.044715f * x * x * x), -20.0f), 20.0f);
+      return 0.5f * x * (1.0f + tanhf(t));
+    }
+    case FA_ACT_TANH: return tanhf(fminf(fmaxf(x, -20.0f), 20.0f));
+    case FA_ACT_RELU: return fmaxf(x, 0.0f);
+    case FA_ACT_SILU: return x / (1.0f + expf(-fminf(fmaxf(x, -30.0f), 30.0f)));
+    case FA_ACT_GELU_ERF: {
+      float z = x * 0.70710678118654752f;
+      float t = 1.0f / (1.0f + 0.3275911f * fabsf(z));
+      float y = 1.0f - (((((1.061405429f * t - 1.453152027f) * t) + 1.421413741f) * t - 0.284496736f) * t +
+                        0.254829592f) * t * expf(-z * z);
+      return 0.5f * x * (1.0f + (z >= 0.0f ? y : -y));
+    }
+    default: return x;
+  }
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline size_t round_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
+
+// ---- kernel entry points implemented in other translation units -------------------------
+
+// fa_gemm_simt.cu: any-shape f32-accumulate kernels (B given as f32/f16 [K][N] or int8 [K][N]).
+int fa_simt_gemm(fa_ctx *ctx, const float *a, const void *b, int b_kind /*0 f32,1 f16,2 int8*/, const float *colscale,
+                 const float *bias, int act, const float *add, float *c, int M, int N, int K);
+int fa_simt_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y,
+                  int M, int N, int K, int nblk, int zpb);
+// fa_gemv.cu: decode-size (M <= 16) bandwidth kernels.
+int fa_gemv_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y,
+                  int M, int N, int K, int nblk, int zpb);
+int fa_gemv_kn(fa_ctx *ctx, const float *a, const void *b, int b_kind, const float *colscale, const float *bias,
+               int act, const float *add, float *c, int M, int N, int K);
+// fa_gemm_tc.cu: tcgen05 kernels and their prepasses.
+struct TcEpilogue {
+  const float *rowscale = nullptr;  // [M] multiplies the accumulator (int8 activation scales)
+  const float *colscale = nullptr;  // [N]
+  const float *bias = nullptr;      // [N]
+  const float *add = nullptr;       // [M][N]
+  int act = 0;
+};
+int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_mk, int lda, const __half *b_nk, int ldb, float *c, int M, int N,
+                   int K, const TcEpilogue &ep);
+int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_lmk, int lda, int limbs, const int8_t *b_nk, int ldb, void *c,
+                  bool raw_i32, int M, int N, int K, const TcEpilogue &ep);
+int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, int kpad, __half *out);
+int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int kpad, int limbs, int8_t *out, float *rowscale);
+int fa_repack_i8_kn_to_nk(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int kpad, int8_t *out_nk);
+int fa_repack_f_kn_to_nk_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, int kpad, __half *out_nk);
+int fa_dequant_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K,
+                         int nblk, int zpb, int kpad, __half *out_nk);
+bool fa_tc_available(fa_ctx *ctx);

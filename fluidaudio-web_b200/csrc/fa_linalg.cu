@@ -1,0 +1,244 @@
+// The hot path's entry points: matmul / matmulInt8 / matmulNBits, routed by shape and storage only
+// (the reference's routers: src/gpu/compute.js:401-436, 593-611, 306-316).
+//
+//   tiny or ragged problems            -> any-shape f32 CUDA-core kernels (fa_gemm_simt.cu)
+//   f16-storage B, int8 B, int4 B      -> tcgen05 kernels (fa_gemm_tc.cu) for every other size,
+//                                         decode sizes (M <= 16) included: at 6.5 TB/s of HBM a CUDA
+//                                         core has fewer than 3 lane-operations per int4 weight, so
+//                                         only the tensor pipe keeps a decode product memory-bound.
+//   f32-storage B                      -> f32 CUDA-core kernel (the reference computes those in f32)
+#include "fa_internal.cuh"
+
+namespace {
+
+// A tensor-core launch pays for two prepasses and TMA descriptor set-up; below this many
+// multiply-adds the any-shape kernel is faster and it is exact f32.
+constexpr long long kTcMinMacs = 1ll << 21;
+
+bool tc_shape_ok(fa_ctx *ctx, int M, int N, int K) {
+  return fa_tc_available(ctx) && N >= 64 && K >= 64 && M >= 1 && (long long)M * N * K >= kTcMinMacs;
+}
+
+int check_vec(fa_ctx *ctx, const fa_tensor *t, int n, const char *what) {
+  FA_REQUIRE(ctx, fa_valid(ctx, t), "%s: unknown tensor handle", what);
+  FA_REQUIRE(ctx, t->storage == FA_F32, "%s must be f32 storage", what);
+  FA_REQUIRE(ctx, (long long)t->rows * t->cols >= n, "%s has %d elements, need %d", what, t->rows * t->cols, n);
+  return FA_OK;
+}
+
+// f16 [N][kpad] copy of a [K][N] weight tensor, built once per handle.
+int ensure_bt_f16(fa_ctx *ctx, fa_tensor *b, int kpad) {
+  if (b->view) return fa_fail(ctx, FA_ERR_INVALID, "matmul: a rowsView cannot be the weight operand of a large product");
+  if (b->bt_f16 && b->bt_kpad == kpad) return FA_OK;
+  if (b->bt_f16) fa_block_release(ctx, b->bt_f16);
+  b->bt_f16 = nullptr;
+  size_t got = 0;
+  FA_TRY(fa_block_acquire(ctx, (size_t)b->cols * kpad * 2, &b->bt_f16, &got));
+  b->bt_bytes = got;
+  b->bt_kpad = kpad;
+  return fa_repack_f_kn_to_nk_f16(ctx, b->dptr, b->storage, b->rows, b->cols, kpad, (__half *)b->bt_f16);
+}
+
+}  // namespace
+
+extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act,
+                         const fa_tensor *add, fa_tensor **out) {
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmul: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, a) && fa_valid(ctx, b), "matmul: unknown tensor handle");
+  const int M = a->rows, K = a->cols, N = b->cols;
+  FA_REQUIRE(ctx, b->rows == K, "matmul: A is [%d,%d] but B is [%d,%d]", M, K, b->rows, N);
+  FA_REQUIRE(ctx, act >= 0 && act <= 5, "matmul: unknown activation code %d", act);
+  if (bias) FA_TRY(check_vec(ctx, bias, N, "matmul: bias"));
+  if (add) {
+    FA_TRY(check_vec(ctx, add, M * N, "matmul: add"));
+    FA_REQUIRE(ctx, add->rows == M && add->cols == N, "matmul: add is [%d,%d], expected [%d,%d]", add->rows, add->cols, M, N);
+  }
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  const float *ap = nullptr;
+  fa_tensor *atmp = nullptr;
+  FA_TRY(fa_as_f32(ctx, a, &ap, &atmp));
+  fa_tensor *c = nullptr;
+  FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
+  int rc;
+  const float *biasp = bias ? (const float *)bias->dptr : nullptr;
+  const float *addp = add ? (const float *)add->dptr : nullptr;
+  if (b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K)) {
+    const int kpad = (int)round_up(K, 64);
+    rc = ensure_bt_f16(ctx, b, kpad);
+    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)M * kpad * 2);
+    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, kpad, (__half *)ctx->scratch_a);
+    if (rc == FA_OK) {
+      TcEpilogue ep;
+      ep.bias = biasp;
+      ep.add = addp;
+      ep.act = act;
+      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, kpad, (const __half *)b->bt_f16, kpad,
+                          (float *)c->dptr, M, N, K, ep);
+    }
+  } else {
+    rc = fa_simt_gemm(ctx, ap, b->dptr, b->storage == FA_F16 ? 1 : 0, nullptr, biasp, act, addp, (float *)c->dptr, M,
+                      N, K);
+  }
+  if (atmp) fa_free_tensor(ctx, atmp);
+  if (rc != FA_OK) {
+    fa_free_tensor(ctx, c);
+    return rc;
+  }
+  *out = c;
+  return FA_OK;
+}
+
+extern "C" int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, const fa_tensor *scale, int N, int K,
+                              const fa_tensor *bias, int act, fa_tensor **out) {
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmulInt8: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, a) && fa_valid_bytes(ctx, wq), "matmulInt8: unknown handle");
+  FA_REQUIRE(ctx, N > 0 && K > 0, "matmulInt8: N=%d K=%d", N, K);
+  const int M = a->rows;
+  FA_REQUIRE(ctx, a->cols == K, "matmulInt8: A is [%d,%d] but K=%d", M, a->cols, K);
+  FA_REQUIRE(ctx, wq->nbytes >= (size_t)N * K, "matmulInt8: packed weights hold %zu bytes, need %zu", wq->nbytes,
+             (size_t)N * K);
+  FA_REQUIRE(ctx, act >= 0 && act <= 5, "matmulInt8: unknown activation code %d", act);
+  FA_TRY(check_vec(ctx, scale, N, "matmulInt8: scale"));
+  if (bias) FA_TRY(check_vec(ctx, bias, N, "matmulInt8: bias"));
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  const float *ap = nullptr;
+  fa_tensor *atmp = nullptr;
+  FA_TRY(fa_as_f32(ctx, a, &ap, &atmp));
+  fa_tensor *c = nullptr;
+  FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
+  int rc = FA_OK;
+  const float *biasp = bias ? (const float *)bias->dptr : nullptr;
+  if (tc_shape_ok(ctx, M, N, K)) {
+    const int kpad = (int)round_up(K, 128);
+    const int limbs = ctx->int8_limbs;
+    if (!(wq->nk_i8 && wq->nk_N == N && wq->nk_K == K)) {  // one-time [K][N] -> [N][K] repack per handle
+      if (wq->nk_i8) fa_block_release(ctx, wq->nk_i8);
+      wq->nk_i8 = nullptr;
+      rc = fa_block_acquire(ctx, (size_t)N * kpad, &wq->nk_i8, &wq->nk_bytes);
+      if (rc == FA_OK) {
+        wq->nk_N = N;
+        wq->nk_K = K;
+        wq->nk_kpad = kpad;
+        rc = fa_repack_i8_kn_to_nk(ctx, (const int8_t *)wq->dptr, K, N, kpad, (int8_t *)wq->nk_i8);
+      }
+    }
+    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)limbs * M * kpad);
+    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_s, &ctx->scratch_s_bytes, (size_t)M * 4);
+    if (rc == FA_OK)
+      rc = fa_prep_a_i8(ctx, ap, M, K, kpad, limbs, (int8_t *)ctx->scratch_a, (float *)ctx->scratch_s);
+    if (rc == FA_OK) {
+      TcEpilogue ep;
+      ep.rowscale = (const float *)ctx->scratch_s;
+      ep.colscale = (const float *)scale->dptr;
+      ep.bias = biasp;
+      ep.act = act;
+      rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, kpad, limbs, (const int8_t *)wq->nk_i8, kpad, c->dptr,
+                         false, M, N, K, ep);
+    }
+  } else {
+    rc = fa_simt_gemm(ctx, ap, wq->dptr, 2, (const float *)scale->dptr, biasp, act, nullptr, (float *)c->dptr, M, N, K);
+  }
+  if (atmp) fa_free_tensor(ctx, atmp);
+  if (rc != FA_OK) {
+    fa_free_tensor(ctx, c);
+    return rc;
+  }
+  *out = c;
+  return FA_OK;
+}
+
+extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, const fa_tensor *scales, fa_bytes *zp,
+                               int N, int block_size, fa_tensor **out) {
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmulNBits: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, a) && fa_valid_bytes(ctx, bq) && fa_valid_bytes(ctx, zp), "matmulNBits: unknown handle");
+  // the reference hard-codes a 16-byte block stride, so 32 is the only block size its layout can hold
+  FA_REQUIRE(ctx, block_size == 32, "matmulNBits: block size %d unsupported (the packed layout fixes it at 32)", block_size);
+  const int M = a->rows, K = a->cols;
+  FA_REQUIRE(ctx, N > 0 && K > 0, "matmulNBits: N=%d K=%d", N, K);
+  const int nblk = ceil_div(K, 32), zpb = ceil_div(nblk, 2);
+  FA_REQUIRE(ctx, bq->nbytes >= (size_t)N * nblk * 16, "matmulNBits: packed weights hold %zu bytes, need %zu", bq->nbytes,
+             (size_t)N * nblk * 16);
+  FA_REQUIRE(ctx, zp->nbytes >= (size_t)N * zpb, "matmulNBits: zero-points hold %zu bytes, need %zu", zp->nbytes,
+             (size_t)N * zpb);
+  FA_TRY(check_vec(ctx, scales, N * nblk, "matmulNBits: scales"));
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  const float *ap = nullptr;
+  fa_tensor *atmp = nullptr;
+  FA_TRY(fa_as_f32(ctx, a, &ap, &atmp));
+  fa_tensor *c = nullptr;
+  FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
+  int rc = FA_OK;
+  if (tc_shape_ok(ctx, M, N, K)) {
+    const int kpad = (int)round_up(K, 64);
+    const bool cached = bq->nk_f16 && bq->f16_N == N && bq->f16_K == K && bq->f16_scales == scales->dptr &&
+                        bq->f16_zp == zp->dptr;
+    if (!cached) {
+      if (bq->nk_f16) fa_block_release(ctx, bq->nk_f16);
+      bq->nk_f16 = nullptr;
+      rc = fa_block_acquire(ctx, (size_t)N * kpad * 2, &bq->nk_f16, &bq->nk_f16_bytes);
+      if (rc == FA_OK) {
+        bq->f16_N = N;
+        bq->f16_K = K;
+        bq->f16_kpad = kpad;
+        bq->f16_scales = scales->dptr;
+        bq->f16_zp = zp->dptr;
+        rc = fa_dequant_nbits_f16(ctx, (const uint8_t *)bq->dptr, (const float *)scales->dptr,
+                                  (const uint8_t *)zp->dptr, N, K, nblk, zpb, kpad, (__half *)bq->nk_f16);
+      }
+    }
+    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)M * kpad * 2);
+    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, kpad, (__half *)ctx->scratch_a);
+    if (rc == FA_OK) {
+      TcEpilogue ep;
+      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, kpad, (const __half *)bq->nk_f16, kpad,
+                          (float *)c->dptr, M, N, K, ep);
+    }
+  } else {
+    rc = fa_simt_nbits(ctx, ap, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr,
+                       (float *)c->dptr, M, N, K, nblk, zpb);
+  }
+  if (atmp) fa_free_tensor(ctx, atmp);
+  if (rc != FA_OK) {
+    fa_free_tensor(ctx, c);
+    return rc;
+  }
+  *out = c;
+  return FA_OK;
+}
+
+extern "C" int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_bytes *wq, int N, int K,
+                                int32_t *acc_out_host) {
+  if (!ctx || !aq_host || !acc_out_host) return fa_fail(ctx, FA_ERR_INVALID, "int8GemmI32: NULL argument");
+  FA_REQUIRE(ctx, fa_valid_bytes(ctx, wq), "int8GemmI32: unknown handle");
+  FA_REQUIRE(ctx, M > 0 && N > 0 && K > 0, "int8GemmI32: M=%d N=%d K=%d", M, N, K);
+  FA_REQUIRE(ctx, wq->nbytes >= (size_t)N * K, "int8GemmI32: packed weights hold %zu bytes, need %zu", wq->nbytes,
+             (size_t)N * K);
+  FA_REQUIRE(ctx, fa_tc_available(ctx), "int8GemmI32: tensor-map encoder unavailable");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int kpad = (int)round_up(K, 128);
+  int rc = FA_OK;
+  if (!(wq->nk_i8 && wq->nk_N == N && wq->nk_K == K)) {
+    if (wq->nk_i8) fa_block_release(ctx, wq->nk_i8);
+    wq->nk_i8 = nullptr;
+    FA_TRY(fa_block_acquire(ctx, (size_t)N * kpad, &wq->nk_i8, &wq->nk_bytes));
+    wq->nk_N = N;
+    wq->nk_K = K;
+    wq->nk_kpad = kpad;
+    FA_TRY(fa_repack_i8_kn_to_nk(ctx, (const int8_t *)wq->dptr, K, N, kpad, (int8_t *)wq->nk_i8));
+  }
+  FA_TRY(fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)M * kpad));
+  FA_CHECK_CUDA(ctx, cudaMemsetAsync(ctx->scratch_a, 0, (size_t)M * kpad, ctx->stream));
+  FA_CHECK_CUDA(ctx, cudaMemcpy2DAsync(ctx->scratch_a, kpad, aq_host, K, K, M, cudaMemcpyHostToDevice, ctx->stream));
+  void *acc = nullptr;
+  size_t got = 0;
+  FA_TRY(fa_block_acquire(ctx, (size_t)M * N * 4, &acc, &got));
+  TcEpilogue ep;
+  rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, kpad, 1, (const int8_t *)wq->nk_i8, kpad, acc, true, M, N, K, ep);
+  if (rc == FA_OK) {
+    cudaError_t e = cudaMemcpyAsync(acc_out_host, acc, (size_t)M * N * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "int8GemmI32 readback: %s", cudaGetErrorString(e));
+  }
+  if (rc == FA_OK) rc = fa_sync(ctx);
+  fa_block_release(ctx, acc);
+  return rc;
+}

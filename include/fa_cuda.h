@@ -1,0 +1,166 @@
+/*
+ * fa_cuda.h — C ABI of the CUDA (sm_100a) compute backend for fluidaudio-web's
+ * quantized matrix-product path.
+ *
+ * Each entry point is what an N-API addon binds to implement one member of the
+ * reference's ComputeContext interface (src/gpu/compute.d.ts:106-255); the member
+ * it replaces is cited beside it.  Plain C types only: opaque handles, pointers,
+ * sizes, ints.  Every function returns 0 on success and a non-zero FA_ERR_* code on
+ * failure; fa_last_error() then holds a message of the same class the reference
+ * throws as a JS Error.  All calls for one fa_ctx come from one host thread
+ * (the reference's contexts are single-threaded, compute.d.ts / README.md:135-138).
+ *
+ * Ops are enqueue-only on the context's CUDA stream (program order = execution
+ * order, which is what the reference's batch/submit model guarantees); only
+ * fa_download, fa_staged_read and fa_sync block.
+ *
+ * There is no CPU fallback: without a CUDA device fa_ctx_create fails.
+ */
+#ifndef FA_CUDA_H
+#define FA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with hidden visibility; these are its exports */
+#endif
+
+typedef struct fa_ctx fa_ctx;       /* one ComputeContext (compute.d.ts:106) */
+typedef struct fa_tensor fa_tensor; /* Tensor {rows, cols}, storage opaque (compute.d.ts:12-15) */
+typedef struct fa_bytes fa_bytes;   /* PackedBytes from uploadBytes (compute.d.ts:34) */
+typedef struct fa_staged fa_staged; /* StagedRead, single use (compute.d.ts:39-45) */
+
+enum {
+  FA_OK = 0,
+  FA_ERR_INVALID = 1,   /* contract violation: bad handle, shape mismatch, nested batch, second read() */
+  FA_ERR_CUDA = 2,      /* a CUDA runtime/driver call failed */
+  FA_ERR_OOM = 3,       /* device allocation failed or the configured cap was exceeded */
+  FA_ERR_NO_DEVICE = 4, /* no CUDA device / unsupported architecture */
+  FA_ERR_TIMEOUT = 5    /* a bounded device-side wait ran out (kernel reported it and returned) */
+};
+
+/* Activation codes: src/gpu/kernels/actf.js:24 */
+enum { FA_ACT_NONE = 0, FA_ACT_GELU = 1, FA_ACT_TANH = 2, FA_ACT_RELU = 3, FA_ACT_SILU = 4, FA_ACT_GELU_ERF = 5 };
+
+/* Tensor storage kinds reported by fa_tensor_info. */
+enum { FA_F32 = 0, FA_F16 = 1 };
+
+/* ---- context ----------------------------------------------------------- */
+/* createContext({backend:"cuda"}) branch of src/gpu/context.js:23-37. */
+int fa_ctx_create(int device, fa_ctx **out);
+/* ComputeContext.destroy (compute.d.ts:133): frees every device allocation of the context. */
+int fa_ctx_destroy(fa_ctx *ctx);
+/* Message of the most recent failure on ctx (ctx may be NULL for fa_ctx_create failures). */
+const char *fa_last_error(fa_ctx *ctx);
+/* Integer options: "int8_limbs" (1..3, see fa_matmul_int8), "pool_cap_bytes" (0 = none; allocation
+ * beyond it fails with FA_ERR_OOM — the reference's poolBudgetBytes, compute.js:128-137). */
+int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
+/* cudaStream_t of the context, for callers that order their own work after it. */
+int fa_ctx_stream(fa_ctx *ctx, void **stream_out);
+/* Block until every enqueued op has finished; surfaces asynchronous kernel errors. */
+int fa_sync(fa_ctx *ctx);
+/* Number of kernels this library has launched on ctx since creation. */
+int fa_launch_count(fa_ctx *ctx, unsigned long long *out);
+
+/* ---- tensors & memory (compute.d.ts:109-133) ----------------------------- */
+int fa_upload_f32(fa_ctx *ctx, const float *host, int rows, int cols, fa_tensor **out);  /* upload :110 */
+int fa_upload_f16(fa_ctx *ctx, const float *host, int rows, int cols, fa_tensor **out);  /* uploadF16 :112 */
+int fa_alloc(fa_ctx *ctx, int rows, int cols, fa_tensor **out);                          /* alloc :113 */
+int fa_alloc_f16(fa_ctx *ctx, int rows, int cols, fa_tensor **out);                      /* allocF16 :114 */
+int fa_upload_bytes(fa_ctx *ctx, const void *host, size_t nbytes, fa_bytes **out);       /* uploadBytes :119 */
+int fa_free_tensor(fa_ctx *ctx, fa_tensor *t);                                           /* freeTensor :122 */
+int fa_free_bytes(fa_ctx *ctx, fa_bytes *b);
+int fa_pin(fa_ctx *ctx, fa_tensor *t, int to_parent);                                    /* pin :125 */
+int fa_push_arena(fa_ctx *ctx, int *handle_out);                                         /* pushArena :128 */
+int fa_pop_arena(fa_ctx *ctx, int handle); /* popArena :129; handle < 0 closes the newest open arena */
+int fa_trim_pool(fa_ctx *ctx, size_t budget_bytes);                                      /* trimPool :131 */
+int fa_tensor_info(const fa_tensor *t, int *rows, int *cols, int *storage, void **device_ptr);
+/* memStats / poolInfo (compute.d.ts:252-254): allocations made, bytes made, pool hits, bytes idle in the pool. */
+int fa_mem_stats(fa_ctx *ctx, unsigned long long *created, unsigned long long *created_bytes,
+                 unsigned long long *reused, unsigned long long *pool_bytes);
+/* Page-locked host memory for callers that want uploads/downloads to be truly asynchronous. */
+int fa_host_alloc(size_t nbytes, void **out);
+int fa_host_free(void *p);
+
+/* ---- readback (compute.d.ts:135-145) -------------------------------------- */
+int fa_download(fa_ctx *ctx, const fa_tensor *t, float *host_out);          /* download / downloadF16 :137-138 */
+int fa_stage_download(fa_ctx *ctx, const fa_tensor *t, fa_staged **out);    /* stageDownload :141 */
+int fa_staged_read(fa_ctx *ctx, fa_staged *s, float *host_out); /* StagedRead.read :44; 2nd call: FA_ERR_INVALID */
+int fa_staged_free(fa_ctx *ctx, fa_staged *s);
+int fa_rows_view(fa_ctx *ctx, fa_tensor *t, int rows, fa_tensor **out);     /* rowsView :145 */
+
+/* ---- batching (compute.d.ts:147-151) --------------------------------------- */
+int fa_begin_batch(fa_ctx *ctx); /* beginBatch :148; nested call fails like scheduler.js:20 */
+int fa_end_batch(fa_ctx *ctx);   /* endBatch :149 */
+
+/* ---- linear algebra: the hot path (compute.d.ts:153-168) ------------------- */
+/* matmul :155, and matmulV2/V3/V4/F16 :158-162 (one shape-routed implementation):
+ * C = act(A[M,K] @ B[K,N] + bias[1,N]) + add[M,N].  bias/add may be NULL.  B may be f32 or
+ * f16 storage (uploadF16); routing is by shape and storage only. */
+int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act, const fa_tensor *add,
+              fa_tensor **out);
+/* matmulInt8 :164.  wq: int8 weights, byte index k*N+n (rust/wasm-kernels/src/lib.rs:141-142);
+ * scale [1,N] per output column; y = act(scale[n]*sum_k a[m,k]*q[k,n] + bias[n]).
+ * Large shapes run on int8 tensor cores: each activation row is split into `int8_limbs` int8
+ * digits of its own row maximum (1 = plain W8A8 quantisation, 2 = default, 3 = f32-grade), the
+ * digit products are exact int32 sums, recombined in the epilogue. */
+int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, const fa_tensor *scale, int N, int K,
+                   const fa_tensor *bias, int act, fa_tensor **out);
+/* matmulNBits :166 (ONNX MatMulNBits, bits=4).  bq [N][nblk][16] bytes, low nibble = even k;
+ * scales f32 [N*nblk]; zp packed nibbles [N][ceil(nblk/2)] (lib.rs:164-203).  block_size must be 32. */
+int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, const fa_tensor *scales, fa_bytes *zp, int N,
+                    int block_size, fa_tensor **out);
+/* Integer mode of the int8 tensor-core kernel, exposed so its accumulators can be checked bit
+ * for bit: aq int8 [M,K] row-major (host), wq as above; acc_out int32 [M,N] (host). */
+int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_bytes *wq, int N, int K, int32_t *acc_out_host);
+
+/* ---- glue ops the encoder/decoder forwards call between GEMMs --------------- */
+int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
+                 fa_tensor **out);                                                        /* layernorm :167 */
+int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);                         /* softmax :168 */
+/* conv1d :172 — grouped/depthwise direct form (lib.rs:99-138); w = Cout*(Cin/groups)*K. */
+int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k, int stride,
+              int pad_left, int pad_right, int dilation, int groups, int act, fa_tensor **out);
+/* conv2d :179 (batch 1). x [Cin, H*W] -> [Cout, Ho*Wo]. */
+int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin, int h,
+              int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left,
+              int pad_right, int groups, int act, fa_tensor **out);
+int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, const fa_tensor *qb, int H, int HD, int W,
+              int b_shared, fa_tensor **out);                                             /* bmmQK :191 */
+int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, int H, int HD, int W, fa_tensor **out); /* bmmPV :193 */
+int fa_rel_shift_b(fa_ctx *ctx, const fa_tensor *x, int H, fa_tensor **out);              /* relShift/relShiftB :195-197 */
+int fa_ewise(fa_ctx *ctx, const fa_tensor *a, const fa_tensor *b, int op_mul, fa_tensor **out); /* ewise/add/mul :202-204 */
+int fa_scale(fa_ctx *ctx, const fa_tensor *x, float s, fa_tensor **out);                  /* scale :205 */
+int fa_unary(fa_ctx *ctx, const fa_tensor *x, int act, fa_tensor **out);                  /* silu :206, relu :207 */
+int fa_glu(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);                             /* glu :212 */
+int fa_transpose(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);                       /* transpose :215 */
+int fa_slice_cols(fa_ctx *ctx, const fa_tensor *x, int col0, int width, fa_tensor **out); /* sliceCols :216 */
+int fa_set_cols(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, int col0);             /* setCols :218 */
+int fa_slice_rows(fa_ctx *ctx, const fa_tensor *x, int row0, int count, fa_tensor **out); /* sliceRows :219 */
+int fa_copy_rows(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, int row_offset);      /* copyRows :221 */
+int fa_concat_rows(fa_ctx *ctx, const fa_tensor *const *tensors, int count, fa_tensor **out); /* concatRows :222 */
+int fa_sub_reshape(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, fa_tensor **out); /* subReshape :228 */
+/* argmax over each row (host picks tokens from it; the reference does this on the host,
+ * src/engines/asr-whisper/index.ts:80-97): out [rows,2] = {index, value}. */
+int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);
+
+/* ---- profiling (compute.d.ts:250-251; scheduler.js:139-180) ----------------- */
+typedef struct fa_profile_entry {
+  char label[48];     /* kernel label (the reference keys by pipeline label) */
+  float ms;           /* summed device time of its launches, CUDA events on the context stream */
+  int count;          /* launches */
+} fa_profile_entry;
+int fa_profile_start(fa_ctx *ctx, int max_ops); /* startProfile */
+int fa_profile_end(fa_ctx *ctx, fa_profile_entry *out, int capacity, int *n_out); /* endProfile */
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_CUDA_H */

@@ -1,0 +1,205 @@
+"""Parity of the CUDA hot path with the CPU oracle, through the C ABI (CudaContext -> libfa_cuda.so).
+
+Tolerances are the reference's own (scripts/backend-conformance.mjs:67-141: 1e-3 for f32/int8/int4
+small cases, 2e-2 for the f16-B route, 5e-2 all-f16) and the stated bars for the large shapes:
+int32 accumulators bit-exact; int8 outputs within 1e-3 relative; f16/int4 within 2e-2 max-abs on
+unit-scale outputs.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle.wasm_oracle import T, WasmOracle, int8_gemm_i32
+
+pytestmark = pytest.mark.gpu
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "conformance_gemm.npz"))
+
+
+def rel_err(got, ref):
+    """max |got-ref| relative to max(|ref|, rms(ref)) elementwise: 'within 1e-3 relative' without
+    blowing up on outputs that happen to be near zero."""
+    ref = ref.astype(np.float64)
+    rms = np.sqrt((ref ** 2).mean()) + 1e-30
+    return float((np.abs(got - ref) / np.maximum(np.abs(ref), rms)).max())
+
+
+def gin(name, key):
+    return GOLD[f"{name}.in.{key}"]
+
+
+# ---- the reference gate's seeded cases (fixtures hold inputs and the oracle's outputs) ----------
+
+@pytest.mark.parametrize("act", ["none", "gelu", "gelu_erf", "tanh", "relu", "silu"])
+def test_conformance_matmul_bias_act(ctx, act):
+    name = f"matmul_bias_{act}"
+    a, b, bias = gin(name, "a"), gin(name, "b"), gin(name, "bias")
+    out = ctx.download(ctx.matmul(ctx.upload(a, 37, 53), ctx.upload(b, 53, 41), bias=ctx.upload(bias, 1, 41), act=act))
+    assert np.abs(out.reshape(37, 41) - GOLD[name]).max() <= 1e-3
+
+
+def test_conformance_matmul_relu_add(ctx):
+    name = "matmul_relu_add"
+    a, b, d = gin(name, "a"), gin(name, "b"), gin(name, "add")
+    out = ctx.download(ctx.matmul(ctx.upload(a, 64, 128), ctx.upload(b, 128, 256), {"act": "relu", "add": ctx.upload(d, 64, 256)}))
+    assert np.abs(out.reshape(64, 256) - GOLD[name]).max() <= 1e-3
+
+
+def test_conformance_variants(ctx):
+    a, b = gin("matmulV2_gelu", "a"), gin("matmulV2_gelu", "b")
+    out = ctx.download(ctx.matmulV2(ctx.upload(a, 33, 48), ctx.upload(b, 48, 52), act="gelu"))
+    assert np.abs(out.reshape(33, 52) - GOLD["matmulV2_gelu"]).max() <= 1e-3
+    a, b = gin("matmulV3", "a"), gin("matmulV3", "b")
+    out = ctx.download(ctx.matmulV3(ctx.upload(a, 33, 64), ctx.upload(b, 64, 48)))
+    assert np.abs(out.reshape(33, 48) - GOLD["matmulV3"]).max() <= 1e-3
+    a, b, bias = (gin("matmulV4_bias_silu", k) for k in ("a", "b", "bias"))
+    out = ctx.download(ctx.matmulV4(ctx.upload(a, 129, 64), ctx.upload(b, 64, 132), bias=ctx.upload(bias, 1, 132), act="silu"))
+    assert np.abs(out.reshape(129, 132) - GOLD["matmulV4_bias_silu"]).max() <= 1e-3
+
+
+def test_conformance_f16_routes(ctx):
+    a, b = gin("matmulF16", "a"), gin("matmulF16", "b")
+    out = ctx.downloadF16(ctx.matmulF16(ctx.uploadF16(a, 40, 64), ctx.uploadF16(b, 64, 64)))
+    assert np.abs(out.reshape(40, 64) - GOLD["matmulF16"]).max() <= 5e-2
+    name = "matmul_f16B_bias_silu"
+    a, b, bias = gin(name, "a"), gin(name, "b"), gin(name, "bias")
+    out = ctx.download(ctx.matmul(ctx.upload(a, 65, 128), ctx.uploadF16(b, 128, 256), bias=ctx.upload(bias, 1, 256), act="silu"))
+    assert np.abs(out.reshape(65, 256) - GOLD[name]).max() <= 2e-2
+
+
+def test_conformance_int8_and_int4(ctx):
+    name = "matmulInt8_bias_relu"
+    a, wq, s, bias = (gin(name, k) for k in ("a", "wq", "scale", "bias"))
+    out = ctx.download(ctx.matmulInt8(ctx.upload(a, 9, 20), ctx.uploadBytes(wq), ctx.upload(s, 1, 16), 16, 20,
+                                      {"bias": ctx.upload(bias, 1, 16), "act": "relu"}))
+    assert np.abs(out.reshape(9, 16) - GOLD[name]).max() <= 1e-3
+    name = "matmulNBits"
+    a, bq, zp, s = (gin(name, k) for k in ("a", "bq", "zp", "scales"))
+    out = ctx.download(ctx.matmulNBits(ctx.upload(a, 7, 64), ctx.uploadBytes(bq), ctx.upload(s, 1, 16), ctx.uploadBytes(zp), 8))
+    assert np.abs(out.reshape(7, 8) - GOLD[name]).max() <= 1e-3
+
+
+# ---- int8: tensor-core route ---------------------------------------------------------------------
+
+def _int8_case(rng, M, K, N):
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    sc = rng.uniform(1e-3, 1e-2, N).astype(np.float32)
+    return a, wq, sc
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 512, 256), (512, 1024, 4096), (200, 328, 136), (16, 1024, 512), (1, 2048, 384)])
+@pytest.mark.parametrize("limbs", [2, 3])
+def test_int8_tensor_core_vs_oracle(ctx, M, K, N, limbs):
+    rng = np.random.default_rng(0)
+    a, wq, sc = _int8_case(rng, M, K, N)
+    bias = rng.standard_normal(N).astype(np.float32)
+    ctx.setOption("int8_limbs", limbs)
+    try:
+        y = ctx.download(ctx.matmulInt8(ctx.upload(a, M, K), ctx.uploadBytes(wq), ctx.upload(sc, 1, N), N, K,
+                                        bias=ctx.upload(bias, 1, N), act="none")).reshape(M, N)
+    finally:
+        ctx.setOption("int8_limbs", 2)
+    ora = WasmOracle(threads=True)
+    ref = ora.matmulInt8(T(a, M, K), ora.uploadBytes(wq), T(sc, 1, N), N, K, bias=T(bias, 1, N), loop_order="ikj").array()
+    assert rel_err(y, ref) <= 1e-3
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 512, 256), (512, 1024, 4096), (77, 200, 136)])
+def test_int8_int32_accumulators_bit_exact(ctx, M, K, N):
+    rng = np.random.default_rng(1)
+    aq = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    got = ctx.int8GemmI32(aq, ctx.uploadBytes(wq), N, K)
+    assert np.array_equal(got, int8_gemm_i32(aq, wq))
+
+
+def test_int8_w8a8_mode_matches_oracle_on_quantised_operands(ctx):
+    """One limb = plain per-row int8 activation quantisation: fp32 outputs equal the oracle run on
+    the same quantised operands (dequantised activations), to f32 rounding."""
+    rng = np.random.default_rng(2)
+    M, K, N = 256, 1024, 512
+    a, wq, sc = _int8_case(rng, M, K, N)
+    ctx.setOption("int8_limbs", 1)
+    try:
+        y = ctx.download(ctx.matmulInt8(ctx.upload(a, M, K), ctx.uploadBytes(wq), ctx.upload(sc, 1, N), N, K)).reshape(M, N)
+    finally:
+        ctx.setOption("int8_limbs", 2)
+    a_scale = (np.abs(a).max(axis=1) / np.float32(127)).astype(np.float32)
+    aq = np.clip(np.rint(a / a_scale[:, None]), -127, 127).astype(np.int8)
+    acc = int8_gemm_i32(aq, wq)
+    ref = acc.astype(np.float32) * a_scale[:, None] * sc[None, :]
+    assert rel_err(y, ref) <= 1e-5
+
+
+# ---- f16-weight GEMM -----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,K,N", [(256, 1024, 1024), (300, 520, 264), (1024, 1024, 3072), (4, 1024, 1024)])
+def test_f16_weight_gemm_vs_oracle(ctx, M, K, N):
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    add = rng.standard_normal((M, N)).astype(np.float32)
+    y = ctx.download(ctx.matmul(ctx.upload(a, M, K), ctx.uploadF16(w, K, N), bias=ctx.upload(bias, 1, N), act="silu",
+                                add=ctx.upload(add, M, N))).reshape(M, N)
+    ora = WasmOracle(threads=True)
+    ref = ora.matmul(T(a, M, K), T(w, K, N), bias=T(bias, 1, N), act="silu", add=T(add, M, N)).array()
+    assert np.abs(y - ref).max() <= 2e-2
+
+
+# ---- int4 ---------------------------------------------------------------------------------------
+
+def _int4_case(rng, M, K, N, signed_zp=True):
+    nblk = -(-K // 32)
+    zpb = -(-nblk // 2)
+    bq = rng.integers(0, 256, N * nblk * 16, dtype=np.uint8)
+    scales = rng.uniform(5e-3, 2e-2, N * nblk).astype(np.float16).astype(np.float32)
+    zp = np.full(N * zpb, 0x88, np.uint8) if signed_zp else rng.integers(0, 256, N * zpb, dtype=np.uint8)
+    a = rng.standard_normal((M, K)).astype(np.float16).astype(np.float32)
+    return a, bq, scales, zp
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+@pytest.mark.parametrize("N", [2048, 8192])
+def test_int4_decode_shapes_vs_oracle(ctx, M, N):
+    K = 2048
+    rng = np.random.default_rng(1)
+    a, bq, scales, zp = _int4_case(rng, M, K, N)
+    y = ctx.download(ctx.matmulNBits(ctx.upload(a, M, K), ctx.uploadBytes(bq), ctx.upload(scales, 1, scales.size),
+                                     ctx.uploadBytes(zp), N)).reshape(M, N)
+    ora = WasmOracle(threads=True)
+    ref = ora.matmulNBits(T(a, M, K), ora.uploadBytes(bq), T(scales, 1, scales.size), ora.uploadBytes(zp), N).array()
+    assert np.abs(y - ref).max() <= 2e-2
+
+
+def test_int4_partial_block_and_random_zero_points(ctx):
+    rng = np.random.default_rng(5)
+    for (M, K, N) in [(8, 100, 64), (40, 1000, 328), (130, 4352, 1024)]:
+        a, bq, scales, zp = _int4_case(rng, M, K, N, signed_zp=False)
+        y = ctx.download(ctx.matmulNBits(ctx.upload(a, M, K), ctx.uploadBytes(bq), ctx.upload(scales, 1, scales.size),
+                                         ctx.uploadBytes(zp), N)).reshape(M, N)
+        ora = WasmOracle(threads=True)
+        ref = ora.matmulNBits(T(a, M, K), ora.uploadBytes(bq), T(scales, 1, scales.size), ora.uploadBytes(zp), N).array()
+        assert np.abs(y - ref).max() <= 2e-2, (M, K, N)
+
+
+# ---- size-independent properties at full size ------------------------------------------------------
+
+def test_int8_full_size_linearity_and_exactness(ctx):
+    """BASELINE config 1 (512x1024x4096): y(a1+a2) = y(a1)+y(a2) holds exactly for the int32
+    accumulators, and zero activations give exactly the bias."""
+    rng = np.random.default_rng(0)
+    M, K, N = 512, 1024, 4096
+    wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    wb = ctx.uploadBytes(wq)
+    a1 = rng.integers(-60, 61, (M, K), dtype=np.int8)
+    a2 = rng.integers(-60, 61, (M, K), dtype=np.int8)
+    y1, y2, y12 = (ctx.int8GemmI32(x, wb, N, K) for x in (a1, a2, (a1 + a2).astype(np.int8)))
+    assert np.array_equal(y1 + y2, y12)
+    sc = rng.uniform(1e-3, 1e-2, N).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    z = ctx.download(ctx.matmulInt8(ctx.upload(np.zeros((M, K), np.float32), M, K), wb, ctx.upload(sc, 1, N), N, K,
+                                    bias=ctx.upload(bias, 1, N))).reshape(M, N)
+    assert np.array_equal(z, np.broadcast_to(bias, (M, N)))
