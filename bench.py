@@ -1,0 +1,457 @@
+"""Benchmark of the quantized matrix-product hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded
+synthetic input; `value` is whole-job throughput with inputs resident in HBM, `e2e` the same metric
+through the public ComputeContext API with host buffers (uploads and the result download inside the
+timed region).  `roofline` describes the dominant kernel, timed per launch with CUDA events on the
+context's own stream; `cpu_baseline` is the CPU port of the reference's wasm kernels on a bounded
+sample.  `--impl reference` times that CPU port alone with every host thread (rank 0 only).
+
+Multi-GPU (torchrun, one process per GPU): the units of work (decode products / encoder windows)
+are independent, so each rank runs its own share with no data-path collective ("weak" scaling);
+the barrier and the max-over-ranks time are the only cross-rank steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+# --------------------------------------------------------------------------------------------
+# helpers
+# --------------------------------------------------------------------------------------------
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# --------------------------------------------------------------------------------------------
+# workloads
+# --------------------------------------------------------------------------------------------
+
+class Int4Decode:
+    """BASELINE config 2: int4 group-quantised decode products (Nemotron-style projection).
+    K=2048, N=8192, M in {1,4,16}; a rotating set of distinct weight matrices larger than L2
+    so every product streams its weights from HBM.  Seed 1."""
+
+    name = "int4_decode_k2048_n8192_m1-4-16"
+    metric = "int4_decode_weight_stream"
+    unit = "GB/s"
+    dtype = "u4 weights x f16 activations, f32 accumulate"
+    dominant = "nbits"
+
+    def __init__(self, quick=False):
+        self.K, self.N, self.Ms = 2048, 8192, (1, 4, 16)
+        self.nblk = self.K // 32
+        self.nsets = 8 if quick else 32  # 32 x 10.3 MB = 330 MB > 2 x L2
+
+    def weight_bytes(self):  # reference format: int4 + f32 scale per block + packed zero-points
+        return self.N * self.K // 2 + self.N * self.nblk * 4 + self.N * (self.nblk // 2)
+
+    def algorithmic_bytes(self, M):  # SURVEY 8(d) reference-format figure
+        return self.weight_bytes() + 4 * M * self.K + 4 * M * self.N
+
+    def host_data(self):
+        rng = np.random.default_rng(1)
+        sets = []
+        for _ in range(self.nsets):
+            s = rng.integers(-8, 8, (self.N, self.K), dtype=np.int8) + 8
+            bq = (s[:, 0::2] | (s[:, 1::2] << 4)).astype(np.uint8).reshape(-1)
+            scales = rng.uniform(5e-3, 2e-2, self.N * self.nblk).astype(np.float16).astype(np.float32)
+            zp = np.full(self.N * (self.nblk // 2), 0x88, np.uint8)
+            sets.append((bq, scales, zp))
+        acts = {M: rng.standard_normal((M, self.K)).astype(np.float16).astype(np.float32) for M in self.Ms}
+        return sets, acts
+
+    def setup(self, ctx):
+        sets, acts = self.host_data()
+        self.host_acts = {}
+        for M, a in acts.items():  # e2e uploads come from page-locked memory
+            buf = ctx.pinnedArray(a.size)
+            buf[:] = a.reshape(-1)
+            self.host_acts[M] = buf
+        self.dev_sets = [(ctx.uploadBytes(bq), ctx.upload(sc, 1, sc.size), ctx.uploadBytes(zp)) for bq, sc, zp in sets]
+        self.dev_acts = {M: ctx.upload(a, M, self.K) for M, a in acts.items()}
+        self.units_per_step = self.nsets * len(self.Ms)  # products
+        self.bytes_per_step = sum(self.algorithmic_bytes(M) for M in self.Ms) * self.nsets
+
+    def step_device(self, ctx):
+        h = ctx.pushArena()
+        for M in self.Ms:
+            a = self.dev_acts[M]
+            for bq, sc, zp in self.dev_sets:
+                ctx.matmulNBits(a, bq, sc, zp, self.N)
+        ctx.popArena(h)
+
+    def step_e2e(self, ctx):
+        h = ctx.pushArena()
+        last = None
+        for M in self.Ms:
+            a = ctx.upload(self.host_acts[M], M, self.K)
+            for bq, sc, zp in self.dev_sets:
+                last = ctx.matmulNBits(a, bq, sc, zp, self.N)
+            out = ctx.download(last)
+            ctx.freeTensor(a)
+        ctx.popArena(h)
+        return out
+
+    def e2e_bytes(self):
+        return sum(4 * M * self.K for M in self.Ms), sum(4 * M * self.N for M in self.Ms)
+
+    def value_from(self, steps, seconds):
+        return self.bytes_per_step * steps / seconds / 1e9
+
+    def roofline(self, prof, peaks):
+        ent = [e for e in prof if e["label"].startswith(("nbits", "tc_gemm_f16"))]
+        if not ent:
+            return None
+        e = max(ent, key=lambda x: x["ms"])
+        per_launch_ms = e["ms"] / e["count"]
+        alg = sum(self.algorithmic_bytes(M) for M in self.Ms) / len(self.Ms)
+        ach = alg / (per_launch_ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": None, "kernel": e["label"],
+                "avg_launch_us": round(per_launch_ms * 1e3, 2), "peak_source": peaks["source"]}
+
+    def cpu_sample(self, threads=True):
+        """One M=4 product at full N,K on the CPU port; returns (value in GB/s, description)."""
+        from oracle.wasm_oracle import T, WasmOracle
+
+        ora = WasmOracle(threads=threads)
+        sets, acts = self.host_data() if not hasattr(self, "_hd") else self._hd
+        self._hd = (sets, acts)
+        bq, sc, zp = sets[0]
+        M = 4
+        a = T(acts[M], M, self.K)
+        bqh, zph, sch = ora.uploadBytes(bq), ora.uploadBytes(zp), T(sc, 1, sc.size)
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            ora.matmulNBits(a, bqh, sch, zph, self.N)
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > 8 or reps >= 200:
+                break
+        return self.algorithmic_bytes(M) * reps / dt / 1e9, f"{reps} x (M=4, N={self.N}, K={self.K}) products, {dt:.1f} s"
+
+
+class Int8Gemm:
+    """BASELINE config 1: int8 GEMM in the reference's layout ([K][N] bytes, per-column f32 scales).
+    A f32 [512,1024] ~ N(0,1), W int8 [1024][4096] uniform in [-127,127], scales U(1e-3,1e-2).  Seed 0.
+    A rotating set of 48 weight matrices (> L2) keeps the weight reads on HBM."""
+
+    name = "int8_gemm_512x1024x4096"
+    metric = "int8_gemm_throughput"
+    unit = "TOP/s"
+    dtype = "s8 x s8 digits -> s32 (f32 activations split in int8 digits), f32 out"
+
+    def __init__(self, quick=False):
+        self.M, self.K, self.N = 512, 1024, 4096
+        self.nsets = 8 if quick else 48
+
+    def ops(self):
+        return 2.0 * self.M * self.N * self.K
+
+    def algorithmic_bytes(self):
+        return self.M * self.K * 4 + self.K * self.N + self.N * 4 + self.M * self.N * 4
+
+    def host_data(self):
+        rng = np.random.default_rng(0)
+        a = rng.standard_normal((self.M, self.K)).astype(np.float32)
+        ws = [rng.integers(-127, 128, (self.K, self.N), dtype=np.int8) for _ in range(self.nsets)]
+        sc = rng.uniform(1e-3, 1e-2, self.N).astype(np.float32)
+        return a, ws, sc
+
+    def setup(self, ctx):
+        a, ws, sc = self.host_data()
+        self.host_a = ctx.pinnedArray(a.size)
+        self.host_a[:] = a.reshape(-1)
+        self.dev_a = ctx.upload(a, self.M, self.K)
+        self.dev_w = [ctx.uploadBytes(w) for w in ws]
+        self.dev_sc = ctx.upload(sc, 1, self.N)
+        self.units_per_step = self.nsets
+        # first use repacks each weight handle once; keep that out of the timed region
+        h = ctx.pushArena()
+        for w in self.dev_w:
+            ctx.matmulInt8(self.dev_a, w, self.dev_sc, self.N, self.K)
+        ctx.popArena(h)
+        ctx.sync()
+
+    def step_device(self, ctx):
+        h = ctx.pushArena()
+        for w in self.dev_w:
+            ctx.matmulInt8(self.dev_a, w, self.dev_sc, self.N, self.K)
+        ctx.popArena(h)
+
+    def step_e2e(self, ctx):
+        h = ctx.pushArena()
+        out = None
+        for w in self.dev_w:
+            a = ctx.upload(self.host_a, self.M, self.K)
+            out = ctx.download(ctx.matmulInt8(a, w, self.dev_sc, self.N, self.K))
+            ctx.freeTensor(a)
+        ctx.popArena(h)
+        return out
+
+    def e2e_bytes(self):
+        return self.nsets * self.M * self.K * 4, self.nsets * self.M * self.N * 4
+
+    def value_from(self, steps, seconds):
+        return self.ops() * self.nsets * steps / seconds / 1e12
+
+    def roofline(self, prof, peaks):
+        ent = [e for e in prof if e["label"] == "tc_gemm_i8"]
+        if not ent:
+            return None
+        e = ent[0]
+        per_launch_ms = e["ms"] / e["count"]
+        ach = self.algorithmic_bytes() / (per_launch_ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": None, "kernel": e["label"],
+                "avg_launch_us": round(per_launch_ms * 1e3, 2), "peak_source": peaks["source"],
+                "tensor_tops": round(self.ops() / (per_launch_ms * 1e-3) / 1e12, 1)}
+
+    def cpu_sample(self, threads=True):
+        from oracle.wasm_oracle import T, WasmOracle
+
+        ora = WasmOracle(threads=threads)
+        a, ws, sc = self.host_data() if not hasattr(self, "_hd") else self._hd
+        self._hd = (a, ws, sc)
+        Ms = 64  # a 64-row slice of the 512 activation rows
+        at, wh, st = T(a[:Ms], Ms, self.K), ora.uploadBytes(ws[0]), T(sc, 1, self.N)
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            ora.matmulInt8(at, wh, st, self.N, self.K)
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > 8 or reps >= 100:
+                break
+        return 2.0 * Ms * self.N * self.K * reps / dt / 1e12, f"{reps} x ({Ms} of 512 rows, N={self.N}, K={self.K}), reference loop order, {dt:.1f} s"
+
+
+WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm}
+DEFAULT_WORKLOAD = "int4_decode"
+
+
+# --------------------------------------------------------------------------------------------
+# arms
+# --------------------------------------------------------------------------------------------
+
+def run_reference(args):
+    rank, _lr, world = dist_env()
+    if rank != 0:
+        return
+    from oracle.wasm_oracle import LIB
+
+    wl = WORKLOADS[args.workload](quick=True)
+    cores = LIB.oracle_num_threads()
+    vals, desc = [], ""
+    for _ in range(args.warmup):
+        wl.cpu_sample(threads=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        v, desc = wl.cpu_sample(threads=True)
+        vals.append(v)
+    dt = time.perf_counter() - t0
+    value = float(np.mean(vals))
+    line = {"impl": "reference", "metric": wl.metric, "value": round(value, 6), "unit": wl.unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU port of the wasm kernels)",
+            "data": "synthetic", "config": {"workload": wl.name, "note": "Node/wasm runtime absent on the box: C port of rust/wasm-kernels timed instead"},
+            "cpu_baseline": {"value": round(value, 6), "unit": wl.unit, "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": round(value, 6), "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_cuda(args):
+    import torch
+    import __graft_entry__ as ge
+
+    rank, local_rank, world = dist_env()
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pkg = ge.load_package()
+    ctx = pkg.CudaContext(local_rank)
+    torch.cuda.set_device(local_rank)
+    stream = torch.cuda.ExternalStream(ctx.stream(), device=local_rank)
+    wl = WORKLOADS[args.workload](quick=args.quick)
+    wl.setup(ctx)
+    ctx.sync()
+
+    def barrier():
+        ctx.sync()
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+
+    def timed(step_fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(steps):
+                step_fn(ctx)
+            e1.record(stream)
+        ctx.sync()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=f"cuda:{local_rank}")
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        wl.step_device(ctx)
+    ctx.sync()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = ctx.launchCount()
+    ms = timed(wl.step_device, args.steps)
+    launches = ctx.launchCount() - l0
+    clocks = sampler.stop() if rank == 0 else None
+    value = wl.value_from(args.steps, ms * 1e-3) * world
+
+    # per-launch durations of the dominant kernel: same steps again with an event pair around each launch
+    ctx.startProfile(200000)
+    for _ in range(args.steps):
+        wl.step_device(ctx)
+    prof = ctx.endProfile()
+    peaks = measured_peaks()
+    roof = wl.roofline(prof, peaks)
+
+    # end to end through the public API with host buffers
+    for _ in range(2):
+        wl.step_e2e(ctx)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        wl.step_e2e(ctx)
+    ctx.sync()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=f"cuda:{local_rank}")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_val = wl.value_from(args.steps, e2e_s) * world
+    h2d, d2h = wl.e2e_bytes()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        from oracle.wasm_oracle import LIB
+
+        v, desc = wl.cpu_sample(threads=False)
+        cpu = {"value": round(v, 6), "unit": wl.unit, "cores": 1, "kind": "port", "sample": desc,
+               "host_threads_available": LIB.oracle_num_threads()}
+
+    if rank == 0:
+        line = {"metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+                "config": {"workload": wl.name, "l2": f"rotating weight set of {wl.nsets} matrices (> 126 MB L2)",
+                           "timing": "CUDA events on the context stream, max over ranks",
+                           "roofline_timing": "per-launch CUDA event pairs, repeat pass of the same steps"},
+                "roofline": roof, "cpu_baseline": cpu,
+                "e2e": {"value": round(e2e_val, 3), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "gpu_launches": int(launches), "clocks": clocks,
+                "kernels": [{"label": e["label"], "launches": e["count"], "ms": round(e["ms"], 3)} for e in prof]}
+        print(json.dumps(line), flush=True)
+    ctx.destroy()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--quick", action="store_true", help="smaller rotating set (for profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()

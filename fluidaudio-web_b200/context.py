@@ -155,6 +155,9 @@ class CudaContext:
         if self._h:
             self._lib.fa_ctx_destroy(self._h)
             self._h = None
+            for p in getattr(self, "_pinned", []):
+                self._lib.fa_host_free(p)
+            self._pinned = []
 
     # -- readback (compute.d.ts:135-145) ---------------------------------------------------------
     def download(self, t: Tensor) -> np.ndarray:
@@ -342,6 +345,15 @@ class CudaContext:
 
     def setOption(self, key: str, value: int) -> None:
         self._check(self._lib.fa_ctx_set_option(self._h, key.encode(), int(value)))
+
+    def pinnedArray(self, n_floats: int) -> np.ndarray:
+        """Page-locked host f32 buffer (uploads from it and downloads into it are asynchronous copies)."""
+        p = C.c_void_p()
+        self._check(self._lib.fa_host_alloc(max(1, n_floats) * 4, C.byref(p)))
+        arr = np.ctypeslib.as_array((C.c_float * max(1, n_floats)).from_address(p.value))
+        self._pinned = getattr(self, "_pinned", [])
+        self._pinned.append(p)
+        return arr[:n_floats]
 
     def stream(self) -> int:
         s = C.c_void_p()

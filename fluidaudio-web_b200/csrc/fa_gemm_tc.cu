@@ -5,47 +5,110 @@
 //
 // One orientation for every shape: the WEIGHTS are the MMA M-side operand (128 output columns
 // n per CTA, one TMEM lane each), the ACTIVATIONS are the MMA N-side operand (MT rows m per CTA,
-// one TMEM column each).  Both operands are K-major in global memory ([rows][K], K contiguous),
-// brought in by TMA (128-byte swizzle, no multicast) through a multi-stage mbarrier ring, multiplied
-// by tcgen05.mma (kind::f16 -> f32, kind::i8 -> s32) into TMEM, and read back with tcgen05.ld by four
-// epilogue warps that apply  acc (*rowscale[m]) (*colscale[n]) + bias[n] -> act -> + add[m,n]  and
-// store out[m][n] so that the 32 lanes of a warp write 32 consecutive n (coalesced 128-byte rows).
+// one TMEM column each).  Operands are brought in by TMA (128-byte swizzle, no multicast) through
+// a multi-stage mbarrier ring, multiplied by tcgen05.mma (kind::f16 -> f32, kind::i8 -> s32) into
+// TMEM, and read back with tcgen05.ld by four epilogue warps that apply
+//   acc (*rowscale[m]) (*colscale[n]) + bias[n] -> act -> + add[m,n]
+// and store out[m][n] so that the 32 lanes of a warp write 32 consecutive n (coalesced rows).
 // Decode sizes (M <= 16) use MT = 16: the kernel then is a pure weight-streaming loop with a deep
 // ring, which is what bounds it (HBM), while padding M to 16 costs nothing on the tensor pipe.
 //
-// int8 activations arrive as `limbs` int8 digit planes [limbs][M][K] (see fa_prep_a_i8): plane l is
-// stacked as MT extra MMA-N rows, so ONE instruction stream produces all digit products, each an exact
-// int32 sum in its own TMEM column range; the epilogue recombines them as sum_l acc_l * 2^(-7 l).
+// Operand layout in HBM ("box-contiguous"): every TMA box is one contiguous run of memory, so a
+// CTA streams its weights as a single linear region instead of 128-byte pieces a row pitch apart
+// (which opens a new DRAM page per piece).  With ck = elements per 128 bytes of K:
+//   weights     Wp[n/128][k/ck][n%128][k%ck]            (one-time repack, cached on the handle)
+//   activations Ap[limb][k/ck][m][k%ck]                  (written by the per-call prepass)
+// The reference itself prepacks weights tile-major for its fastest GEMM (compute.js:224-243).
+//
+// int8 activations arrive as `limbs` int8 digit planes (see fa_prep_a_i8): plane l is stacked as
+// MT extra MMA-N rows, so ONE instruction stream produces all digit products, each an exact int32
+// sum in its own TMEM column range; the epilogue recombines them as sum_l acc_l * 2^(-7 l).
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (TMEM lane quadrant = warp_id % 4).
+#include <cstdlib>
+
 #include "fa_tc_common.cuh"
 
 namespace {
 
 using namespace tc;
 
-constexpr int kThreads = 192;
-constexpr int kRowBytes = 128;             // one swizzle atom of K per stage
-constexpr int kPTileBytes = 128 * kRowBytes;  // weights tile: 128 rows
+constexpr int kEpiWarps = 8;                   // two per TMEM lane quadrant
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
+constexpr int kRowBytes = 128;                 // one swizzle atom of K per stage
+constexpr int kPTileBytes = 128 * kRowBytes;   // weights tile: 128 rows
+constexpr int kSplitMaxMT = 32;                // split-K mode keeps a [MT][128] f32 partial tile in smem
 
 struct TcParams {
   int M, N, K;        // logical sizes; K in elements
-  int MT;             // activation rows per CTA (multiple of 16, MT*limbs <= 256)
+  int MT;             // activation rows per tile (multiple of 16, MT*limbs <= 256)
   int limbs;          // activation digit planes (1 for f16)
   int stages;
-  int num_kb;         // K blocks of 128 bytes
-  int raw_i32;        // store the limb-0 int32 accumulators instead of the float epilogue
+  int num_kb;         // K chunks of 128 bytes
+  int tiles_n, tiles_m;
+  int splitk;         // > 1: cluster of `splitk` CTAs along z shares one tile, each taking kb_per_split chunks
+  int kb_per_split;
+  int raw_i32;        // 1: store the limb-0 int32 accumulators instead of the float epilogue
   float *out;         // [M][N] f32 (or int32 when raw_i32)
   const float *rowscale, *colscale, *bias, *add;
   int act;
   int *status;
+  unsigned long long *trace;  // debugging aid: per-phase %globaltimer stamps of CTA 0, or nullptr
 };
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+  return t;
+}
+#define TC_TRACE(slot)                                                                                   \
+  do {                                                                                                   \
+    if (p.trace && blockIdx.x == 0 && blockIdx.z == 0 && (slot) < 256) p.trace[slot] = gtime();          \
+  } while (0)
 
 __device__ __forceinline__ void report_timeout(int *status, int code, int detail) {
   if (atomicCAS(status, 0, code) == 0) {
-    status[1] = (int)(blockIdx.x + blockIdx.y * gridDim.x);
+    status[1] = (int)blockIdx.x;
     status[2] = detail;
+  }
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
+  uint32_t ra;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra) : "memory");
+  return v;
+}
+
+// Activation applied to 16 values at once with the selector outside the loop, so the 16 chains stay
+// independent (one warp per scheduler has no other work to hide a per-element branch behind).
+__device__ __forceinline__ void act16(float (&v)[16], int act) {
+  switch (act) {
+    case FA_ACT_NONE: break;
+    case FA_ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) v[j] = fmaxf(v[j], 0.0f);
+      break;
+    case FA_ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) v[j] = v[j] / (1.0f + __expf(-fminf(fmaxf(v[j], -30.0f), 30.0f)));
+      break;
+    default:
+#pragma unroll
+      for (int j = 0; j < 16; j++) v[j] = fa_actf(v[j], act);
   }
 }
 
@@ -53,7 +116,7 @@ template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B), then barriers
+  // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B), barriers, split-K partial tile
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int q_rows = p.MT * p.limbs;
   const uint32_t q_bytes = (uint32_t)q_rows * kRowBytes;
@@ -61,21 +124,29 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   const uint32_t bars = smem_base + (uint32_t)p.stages * stage_bytes;  // 8-byte aligned (stage_bytes % 1024 == 0)
   auto full_bar = [&](int s) { return bars + (uint32_t)s * 8u; };
   auto empty_bar = [&](int s) { return bars + (uint32_t)(p.stages + s) * 8u; };
-  const uint32_t acc_bar = bars + (uint32_t)(2 * p.stages) * 8u;
-  const uint32_t tmem_slot = acc_bar + 8u;
+  auto acc_full = [&](int b) { return bars + (uint32_t)(2 * p.stages + b) * 8u; };
+  auto acc_empty = [&](int b) { return bars + (uint32_t)(2 * p.stages + 2 + b) * 8u; };
+  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4) * 8u;
   const uint32_t abort_flag = tmem_slot + 4u;
+  const uint32_t partial = tmem_slot + 16u;  // [MT][128] f32, split-K mode only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * 128, m0 = blockIdx.y * p.MT;
-  uint32_t tmem_cols = 32;
-  while ((int)tmem_cols < q_rows) tmem_cols <<= 1;
+  uint32_t acc_stride = 32;  // TMEM columns per accumulator buffer
+  while ((int)acc_stride < q_rows) acc_stride <<= 1;
+  const uint32_t tmem_cols = 2 * acc_stride;
+  const int num_tiles = p.tiles_n * p.tiles_m;
+  const int kb0 = p.splitk > 1 ? (int)blockIdx.z * p.kb_per_split : 0;
+  const int kb1 = p.splitk > 1 ? min(p.num_kb, kb0 + p.kb_per_split) : p.num_kb;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; b++) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), kEpiWarps);
+    }
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(0u) : "memory");
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -88,6 +159,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+  if (threadIdx.x == 0) TC_TRACE(0);
 
   auto aborted = [&]() {
     uint32_t v;
@@ -99,97 +171,231 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     report_timeout(p.status, code, detail);
   };
 
+  // Role loops are executed by whole warps (lane 0 does the work, the shuffle keeps the other lanes in
+  // step) so that every warp reaches the block-wide barriers converged, as aligned barriers require.
   if (warp == 0) {
-    // ---- TMA producer -----------------------------------------------------------------
-    if (lane == 0) {
-      const int k_per_kb = KIND == 0 ? 64 : 128;
-      for (int kb = 0; kb < p.num_kb; kb++) {
-        const int s = kb % p.stages;
-        const uint32_t round = (uint32_t)(kb / p.stages);
-        if (kb >= p.stages) {
-          if (!mbar_wait(empty_bar(s), (round - 1) & 1)) { set_abort(1, kb); break; }
+    // ---- TMA producer: runs ahead across tiles, bounded only by the ring ----------------------
+    uint32_t it = 0;
+    bool stop = false;
+    for (int tile = blockIdx.x; tile < num_tiles && !stop; tile += gridDim.x) {
+      const int tn = tile % p.tiles_n, tm = tile / p.tiles_n;
+      for (int kb = kb0; kb < kb1; kb++, it++) {
+        if (lane == 0) {
+          const int s = (int)(it % (uint32_t)p.stages);
+          const uint32_t use = it / (uint32_t)p.stages;
+          if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) set_abort(1, kb);
+          if (aborted()) {
+            stop = true;
+          } else {
+            if (it < 64) TC_TRACE(1 + it);
+            mbar_expect_tx(full_bar(s), stage_bytes);
+            const uint32_t dst = smem_base + (uint32_t)s * stage_bytes;
+            tma_load_2d(dst, &map_w, 0, (tn * p.num_kb + kb) * 128, full_bar(s));
+            for (int l = 0; l < p.limbs; l++)
+              tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, tm * p.MT, l * p.num_kb + kb,
+                          full_bar(s));
+          }
         }
-        if (aborted()) break;
-        mbar_expect_tx(full_bar(s), stage_bytes);
-        const uint32_t dst = smem_base + (uint32_t)s * stage_bytes;
-        tma_load_2d(dst, &map_w, kb * k_per_kb, n0, full_bar(s));
-        for (int l = 0; l < p.limbs; l++)
-          tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, kb * k_per_kb, m0, l, full_bar(s));
+        stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
+        if (stop) break;
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer -------------------------------------------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(KIND, 128, q_rows);
-      bool ok = true;
-      for (int kb = 0; kb < p.num_kb; kb++) {
-        const int s = kb % p.stages;
-        const uint32_t round = (uint32_t)(kb / p.stages);
-        if (!mbar_wait(full_bar(s), round & 1)) { set_abort(2, kb); ok = false; break; }
-        tc_fence_after();
-        const uint32_t pa = smem_base + (uint32_t)s * stage_bytes;
-        const uint32_t qa = pa + kPTileBytes;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {  // 4 x 32 bytes of K per stage
-          umma<KIND>(tmem_base, smem_desc_sw128(pa + j * 32), smem_desc_sw128(qa + j * 32), idesc,
-                     (kb > 0 || j > 0) ? 1u : 0u);
-        }
-        umma_commit(empty_bar(s));  // frees the stage when these MMAs have read it
+    // ---- MMA issuer: alternates between the two TMEM accumulator buffers -----------------------
+    const uint32_t idesc = make_idesc(KIND, 128, q_rows);
+    uint32_t it = 0, lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
+      const uint32_t buf = lt & 1, use = lt >> 1;
+      if (lane == 0 && use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1)) {
+        set_abort(4, tile);
+        ok = false;
       }
-      if (ok) umma_commit(acc_bar);  // accumulators complete
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * acc_stride;
+      for (int kb = kb0; kb < kb1; kb++, it++) {
+        if (lane == 0) {
+          const int s = (int)(it % (uint32_t)p.stages);
+          const uint32_t use_s = it / (uint32_t)p.stages;
+          if (!mbar_wait(full_bar(s), use_s & 1)) {
+            set_abort(2, kb);
+            ok = false;
+          } else {
+            tc_fence_after();
+            if (it < 64) TC_TRACE(65 + it);
+            const uint32_t pa = smem_base + (uint32_t)s * stage_bytes;
+            const uint32_t qa = pa + kPTileBytes;
+#pragma unroll
+            for (int j = 0; j < 4; j++)  // 4 x 32 bytes of K per stage
+              umma<KIND>(d_tmem, smem_desc_sw128(pa + j * 32), smem_desc_sw128(qa + j * 32), idesc,
+                         (kb > kb0 || j > 0) ? 1u : 0u);
+            umma_commit(empty_bar(s));  // frees the stage when these MMAs have read it
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+      }
+      if (ok && lane == 0) umma_commit(acc_full(buf));  // this tile's accumulators are complete
+      __syncwarp();
     }
   } else {
-    // ---- epilogue: TMEM -> registers -> global ------------------------------------------
-    const int quad = warp & 3;
-    const int n = n0 + quad * 32 + lane;
-    bool ok = mbar_wait(acc_bar, 0);
-    if (!ok && lane == 0) set_abort(3, quad);
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    if (ok && !aborted()) {
+    // ---- epilogue: TMEM -> registers -> global (or -> smem partial in split-K mode) -------------
+    const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
+      const int tn = tile % p.tiles_n, tm = tile / p.tiles_n;
+      const int n0 = tn * 128, m0 = tm * p.MT;
+      const uint32_t buf = lt & 1, use = lt >> 1;
+      ok = mbar_wait(acc_full(buf), use & 1);
+      if (!ok && lane == 0) set_abort(3, tile);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !aborted();
+      if (!ok) break;
       tc_fence_after();
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      if (threadIdx.x == 64) TC_TRACE(129);
+      const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
+      const int n = n0 + quad * 32 + lane;
       const bool n_ok = n < p.N;
       const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
       const float bs = (p.bias && n_ok) ? p.bias[n] : 0.0f;
-      for (int c = 0; c < p.MT; c += 16) {
+      for (int c = half * 16; c < p.MT; c += 32) {
         if (m0 + c >= p.M) break;  // warp-uniform: no rows left in this tile
         uint32_t v0[16], v1[16], v2[16];
         tmem_ld16(lane_addr + (uint32_t)c, v0);
         if (p.limbs > 1) tmem_ld16(lane_addr + (uint32_t)(p.MT + c), v1);
         if (p.limbs > 2) tmem_ld16(lane_addr + (uint32_t)(2 * p.MT + c), v2);
+        const bool full_rows = m0 + c + 16 <= p.M;
+        // independent loads issued together while the TMEM read is in flight
+        float rs[16], ad[16];
+        if (p.rowscale) {
+          if (full_rows) {
+            const float4 *r4 = (const float4 *)(p.rowscale + m0 + c);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float4 t = __ldg(r4 + j);
+              rs[4 * j] = t.x; rs[4 * j + 1] = t.y; rs[4 * j + 2] = t.z; rs[4 * j + 3] = t.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) rs[j] = __ldg(p.rowscale + min(m0 + c + j, p.M - 1));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; j++) rs[j] = 1.0f;
+        }
+        if (p.add && n_ok && p.splitk <= 1) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) ad[j] = __ldg(p.add + (size_t)min(m0 + c + j, p.M - 1) * p.N + n);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; j++) ad[j] = 0.0f;
+        }
         tmem_ld_wait();
-        if (!n_ok) continue;
+        if (KIND == 1 && p.raw_i32 == 1) {
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+              if (m0 + c + j < p.M) ((int32_t *)p.out)[(size_t)(m0 + c + j) * p.N + n] = (int32_t)v0[j];
+          }
+          continue;
+        }
+        float v[16];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-          const int m = m0 + c + j;
-          if (m >= p.M) break;
-          const size_t o = (size_t)m * p.N + n;
-          if (KIND == 1 && p.raw_i32) {
-            ((int32_t *)p.out)[o] = (int32_t)v0[j];
-            continue;
-          }
-          float v;
           if (KIND == 0) {
-            v = __uint_as_float(v0[j]);
+            v[j] = __uint_as_float(v0[j]);
           } else {
-            v = (float)(int32_t)v0[j];
-            if (p.limbs > 1) v += (float)(int32_t)v1[j] * (1.0f / 128.0f);
-            if (p.limbs > 2) v += (float)(int32_t)v2[j] * (1.0f / 16384.0f);
+            v[j] = (float)(int32_t)v0[j];
+            if (p.limbs > 1) v[j] = fmaf((float)(int32_t)v1[j], 1.0f / 128.0f, v[j]);
+            if (p.limbs > 2) v[j] = fmaf((float)(int32_t)v2[j], 1.0f / 16384.0f, v[j]);
           }
-          if (p.rowscale) v *= p.rowscale[m];
-          v *= cs;
-          v += bs;
-          v = fa_actf(v, p.act);
-          if (p.add) v += p.add[o];
-          p.out[o] = v;
+        }
+        if (p.splitk > 1) {
+          // partial[m_local][n_local]: lanes write consecutive addresses
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(partial + (uint32_t)(((c + j) * 128 + quad * 32 + lane) * 4)), "f"(v[j])
+                         : "memory");
+          continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs);
+        act16(v, p.act);
+        if (n_ok) {
+          float *orow = p.out + (size_t)(m0 + c) * p.N + n;
+          if (full_rows) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) orow[(size_t)j * p.N] = v[j] + ad[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+              if (m0 + c + j < p.M) orow[(size_t)j * p.N] = v[j] + ad[j];
+          }
         }
       }
+      // hand the accumulator buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(buf));
+      if (threadIdx.x == 64) TC_TRACE(130);
     }
   }
 
+  if (p.splitk > 1) {
+    // ---- split-K: the cluster's CTAs hold partial tiles in shared memory; rank 0 sums them over
+    // distributed shared memory in rank order (deterministic), applies the epilogue and stores. ----
+    __syncwarp();
+    cluster_sync_all();
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    if (rank == 0 && warp >= 2 && !aborted()) {
+      const int tile = blockIdx.x, tn = tile % p.tiles_n, tm = tile / p.tiles_n;
+      const int n0 = tn * 128, m0 = tm * p.MT;
+      const int t = threadIdx.x - 64;  // 256 threads, each owns groups of 4 consecutive columns
+      const bool vec_ok = (p.N & 3) == 0;
+      for (int g = t; g < p.MT * 32; g += 256) {
+        const int ml = g >> 5, nl = (g & 31) * 4, m = m0 + ml, n = n0 + nl;
+        if (m >= p.M || n >= p.N) continue;
+        // all remote reads first (independent), then the rank-ordered sum
+        float4 part[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++)
+          if (r < p.splitk) part[r] = ld_dsmem_f32x4(partial + (uint32_t)((ml * 128 + nl) * 4), (uint32_t)r);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < 8; r++)
+          if (r < p.splitk) {
+            acc[0] += part[r].x; acc[1] += part[r].y; acc[2] += part[r].z; acc[3] += part[r].w;
+          }
+        const float rs = p.rowscale ? p.rowscale[m] : 1.0f;
+        float o[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int nn = min(n + q, p.N - 1);
+          float v = fmaf(acc[q] * rs, p.colscale ? p.colscale[nn] : 1.0f, p.bias ? p.bias[nn] : 0.0f);
+          v = fa_actf(v, p.act);
+          if (p.add) v += p.add[(size_t)m * p.N + nn];
+          o[q] = v;
+        }
+        float *dst = p.out + (size_t)m * p.N + n;
+        if (vec_ok && n + 3 < p.N) {
+          *(float4 *)dst = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+          for (int q = 0; q < 4 && n + q < p.N; q++) dst[q] = o[q];
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
+  }
+
   // ---- teardown --------------------------------------------------------------------------------
+  __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TC_TRACE(131);
   if (aborted()) {
     // A wait ran out: give copies still in flight time to land before the CTA's shared memory goes away.
     for (int i = 0; i < 1000; i++) __nanosleep(1000);
@@ -200,13 +406,14 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   }
 }
 
-// ---- prepasses ------------------------------------------------------------------------------------
+// ---- prepasses (write the box-contiguous layouts described at the top) --------------------------
 
-// f32 [M][K] -> f16 [M][kpad], zero padded.
-__global__ void k_prep_a_f16(const float *__restrict__ a, int M, int K, int kpad, __half *__restrict__ out) {
-  const size_t total = (size_t)M * (kpad / 2);
+// f32 [M][K] -> f16 Ap[k/64][m][k%64], K tail zero padded.
+__global__ void k_prep_a_f16(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
+  const size_t total = (size_t)nch * M * 32;  // half2 pairs
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int m = (int)(i / (kpad / 2)), k = (int)(i % (kpad / 2)) * 2;
+    const int pr = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
+    const int k = c * 64 + pr * 2;
     const float *row = a + (size_t)m * K;
     float x = k < K ? row[k] : 0.0f, y = k + 1 < K ? row[k + 1] : 0.0f;
     ((__half2 *)out)[i] = __floats2half2_rn(x, y);
@@ -214,9 +421,9 @@ __global__ void k_prep_a_f16(const float *__restrict__ a, int M, int K, int kpad
 }
 
 // One CTA per activation row: s = max|a|/127 (1 when the row is all zero), r = a/s,
-// q1 = rint(r), q2 = rint((r-q1)*128), q3 = rint(((r-q1)*128-q2)*128); planes [limbs][M][kpad], zero padded.
+// q1 = rint(r), q2 = rint((r-q1)*128), q3 = rint(((r-q1)*128-q2)*128); planes Ap[limb][k/128][m][k%128].
 // With one limb this is the usual symmetric per-row int8 quantiser; each further limb adds 7 bits.
-__global__ void __launch_bounds__(256) k_prep_a_i8(const float *__restrict__ a, int M, int K, int kpad, int limbs,
+__global__ void __launch_bounds__(256) k_prep_a_i8(const float *__restrict__ a, int M, int K, int nch, int limbs,
                                                    int8_t *__restrict__ out, float *__restrict__ rowscale) {
   __shared__ float red[8];
   const int m = blockIdx.x;
@@ -232,26 +439,34 @@ __global__ void __launch_bounds__(256) k_prep_a_i8(const float *__restrict__ a, 
   for (int w = 1; w < 8; w++) mx = fmaxf(mx, red[w]);
   const float s = mx > 0.0f ? mx / 127.0f : 1.0f;
   if (threadIdx.x == 0) rowscale[m] = s;
-  const size_t plane = (size_t)M * kpad;
-  for (int k = threadIdx.x; k < kpad; k += blockDim.x) {
+  const size_t plane = (size_t)nch * M * 128;
+  for (int k = threadIdx.x; k < nch * 128; k += blockDim.x) {
+    const size_t o = ((size_t)(k >> 7) * M + m) * 128 + (k & 127);
     float r = k < K ? row[k] / s : 0.0f;
-    float q1 = rintf(r);
-    q1 = fminf(fmaxf(q1, -127.0f), 127.0f);
-    out[(size_t)m * kpad + k] = (int8_t)q1;
+    float q1 = fminf(fmaxf(rintf(r), -127.0f), 127.0f);
+    out[o] = (int8_t)q1;
     if (limbs > 1) {
       float r1 = (r - q1) * 128.0f;  // exact: |r-q1| <= 0.5, scaling by 2^7
       float q2 = rintf(r1);
-      out[plane + (size_t)m * kpad + k] = (int8_t)q2;
-      if (limbs > 2) {
-        float q3 = rintf((r1 - q2) * 128.0f);
-        out[2 * plane + (size_t)m * kpad + k] = (int8_t)q3;
-      }
+      out[plane + o] = (int8_t)q2;
+      if (limbs > 2) out[2 * plane + o] = (int8_t)rintf((r1 - q2) * 128.0f);
     }
   }
 }
 
-// int8 [K][N] (reference byte order k*N+n) -> int8 [N][kpad], zero padded.  32x32 tiles through smem.
-__global__ void k_repack_i8(const int8_t *__restrict__ w, int K, int N, int kpad, int8_t *__restrict__ out) {
+// int8 [M][K] (already quantised by the caller) -> Ap[0][k/128][m][k%128].
+__global__ void k_pack_a_i8_raw(const int8_t *__restrict__ aq, int M, int K, int nch, int8_t *__restrict__ out) {
+  const size_t total = (size_t)nch * M * 128;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int kk = (int)(i & 127), m = (int)((i >> 7) % M), c = (int)((i >> 7) / M);
+    const int k = c * 128 + kk;
+    out[i] = k < K ? aq[(size_t)m * K + k] : (int8_t)0;
+  }
+}
+
+// int8 [K][N] (reference byte order k*N+n) -> Wp[n/128][k/128][n%128][k%128].  32x32 tiles through smem;
+// the destination was zero-filled, so padding rows/columns stay zero.
+__global__ void k_pack_w_i8(const int8_t *__restrict__ w, int K, int N, int nch, int8_t *__restrict__ out) {
   __shared__ int8_t t[32][33];
   const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -261,13 +476,13 @@ __global__ void k_repack_i8(const int8_t *__restrict__ w, int K, int N, int kpad
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     int n = n0 + r, k = k0 + threadIdx.x;
-    if (n < N && k < kpad) out[(size_t)n * kpad + k] = t[threadIdx.x][r];
+    if (n < N && k < K) out[(((size_t)(n >> 7) * nch + (k >> 7)) * 128 + (n & 127)) * 128 + (k & 127)] = t[threadIdx.x][r];
   }
 }
 
-// f32 or f16 [K][N] -> f16 [N][kpad], zero padded.
+// f32 or f16 [K][N] -> f16 Wp[n/128][k/64][n%128][k%64].
 template <typename SRC>
-__global__ void k_repack_f16(const SRC *__restrict__ w, int K, int N, int kpad, __half *__restrict__ out) {
+__global__ void k_pack_w_f16(const SRC *__restrict__ w, int K, int N, int nch, __half *__restrict__ out) {
   __shared__ __half t[32][33];
   const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -279,41 +494,35 @@ __global__ void k_repack_f16(const SRC *__restrict__ w, int K, int N, int kpad, 
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     int n = n0 + r, k = k0 + threadIdx.x;
-    if (n < N && k < kpad) out[(size_t)n * kpad + k] = t[threadIdx.x][r];
+    if (n < N && k < K) out[(((size_t)(n >> 7) * nch + (k >> 6)) * 128 + (n & 127)) * 64 + (k & 63)] = t[threadIdx.x][r];
   }
 }
 
-// int4 MatMulNBits payload -> f16 [N][kpad]: w = (q - zp) * scale rounded to f16 once.
-// One thread per 16-byte block (32 weights).
-__global__ void k_dequant_nbits(const uint8_t *__restrict__ bq, const float *__restrict__ scales,
-                                const uint8_t *__restrict__ zp, int N, int K, int nblk, int zpb, int kpad,
-                                __half *__restrict__ out) {
-  const int blocks_per_row = kpad / 32;
-  const size_t total = (size_t)N * blocks_per_row;
+// int4 MatMulNBits payload -> f16 Wp: w = (q - zp) * scale rounded to f16 once.
+// One thread per 16-byte block (32 weights = half a 128-byte row of the packed layout).
+__global__ void k_pack_w_nbits(const uint8_t *__restrict__ bq, const float *__restrict__ scales,
+                               const uint8_t *__restrict__ zp, int N, int K, int nblk, int zpb, int nch,
+                               __half *__restrict__ out) {
+  const size_t total = (size_t)N * nblk;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int n = (int)(i / blocks_per_row), blk = (int)(i % blocks_per_row);
+    const int n = (int)(i / nblk), blk = (int)(i % nblk);
     __half2 vals[16];
-    if (blk < nblk) {
-      const uint4 raw = *(const uint4 *)(bq + ((size_t)n * nblk + blk) * 16);
-      const float s = scales[(size_t)n * nblk + blk];
-      const uint8_t zb = zp[(size_t)n * zpb + (blk >> 1)];
-      const float z = (float)((blk & 1) ? (zb >> 4) : (zb & 15));
-      const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+    const uint4 raw = *(const uint4 *)(bq + ((size_t)n * nblk + blk) * 16);
+    const float s = scales[(size_t)n * nblk + blk];
+    const uint8_t zb = zp[(size_t)n * zpb + (blk >> 1)];
+    const float z = (float)((blk & 1) ? (zb >> 4) : (zb & 15));
+    const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int wv = 0; wv < 4; wv++)
+    for (int wv = 0; wv < 4; wv++)
 #pragma unroll
-        for (int b = 0; b < 4; b++) {
-          const uint32_t byte = (wds[wv] >> (8 * b)) & 0xffu;
-          const int k = blk * 32 + wv * 8 + b * 2;
-          float lo = k < K ? ((float)(byte & 15u) - z) * s : 0.0f;
-          float hi = k + 1 < K ? ((float)(byte >> 4) - z) * s : 0.0f;
-          vals[wv * 4 + b] = __floats2half2_rn(lo, hi);
-        }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 16; j++) vals[j] = __floats2half2_rn(0.0f, 0.0f);
-    }
-    uint4 *dst = (uint4 *)(out + (size_t)n * kpad + (size_t)blk * 32);
+      for (int b = 0; b < 4; b++) {
+        const uint32_t byte = (wds[wv] >> (8 * b)) & 0xffu;
+        const int k = blk * 32 + wv * 8 + b * 2;
+        float lo = k < K ? ((float)(byte & 15u) - z) * s : 0.0f;
+        float hi = k + 1 < K ? ((float)(byte >> 4) - z) * s : 0.0f;
+        vals[wv * 4 + b] = __floats2half2_rn(lo, hi);
+      }
+    uint4 *dst = (uint4 *)(out + (((size_t)(n >> 7) * nch + (blk >> 1)) * 128 + (n & 127)) * 64 + (blk & 1) * 32);
 #pragma unroll
     for (int j = 0; j < 4; j++) dst[j] = *(const uint4 *)&vals[j * 4];
   }
@@ -339,25 +548,47 @@ PFN_encodeTiled get_encode() {
   return fn;
 }
 
+int grid_for(fa_ctx *ctx, size_t n, int block, int per_sm) {
+  size_t g = (n + block - 1) / block, cap = (size_t)ctx->sm_count * per_sm;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
 template <int KIND>
-int launch_tc(fa_ctx *ctx, const void *w_nk, int ldw, const void *a_lmk, int lda, int limbs, void *out, bool raw_i32,
-              int M, int N, int K, const TcEpilogue &ep) {
+int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs, void *out, bool raw_i32, int M, int N,
+              int K, const TcEpilogue &ep) {
   const int elem = KIND == 0 ? 2 : 1;
-  const int k_per_kb = kRowBytes / elem;
   TcParams p{};
   p.M = M;
   p.N = N;
   p.K = K;
   p.limbs = limbs;
-  p.num_kb = ceil_div(K, k_per_kb);
-  // activation rows per CTA: as many as fit 256 MMA-N columns, rounded to 16, no more than needed
+  p.num_kb = fa_tc_chunks(K, elem);
+  // activation rows per tile: as many as fit 256 MMA-N columns, rounded to 16, no more than needed
   int mt_max = (256 / limbs) / 16 * 16;
   int mt = ((M + 15) / 16) * 16;
   p.MT = mt < mt_max ? mt : mt_max;
+  p.tiles_n = ceil_div(N, 128);
+  p.tiles_m = ceil_div(M, p.MT);
+  const int num_tiles = p.tiles_n * p.tiles_m;
+  // Decode-size products have fewer tiles than SMs: split K across a cluster (<= 8 CTAs) so that
+  // every SM streams weights.  Each split keeps at least 4 chunks so the ring still pipelines.
+  p.splitk = 1;
+  p.kb_per_split = p.num_kb;
+  if (!raw_i32 && p.tiles_m == 1 && p.MT <= kSplitMaxMT && num_tiles * 2 <= ctx->sm_count) {
+    int s = ctx->sm_count / num_tiles;
+    if (s > 8) s = 8;
+    while (s > 1 && p.num_kb / s < 4) s--;
+    if (s > 1) {
+      p.kb_per_split = ceil_div(p.num_kb, s);
+      p.splitk = ceil_div(p.num_kb, p.kb_per_split);
+    }
+  }
   const size_t stage_bytes = (size_t)kPTileBytes + (size_t)p.MT * limbs * kRowBytes;
-  int stages = (int)((200 * 1024) / stage_bytes);
+  const size_t tail_bytes = (size_t)(2 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + 1024;
+  int stages = (int)((220 * 1024 - tail_bytes) / stage_bytes);
   if (stages > 12) stages = 12;
-  if (stages > p.num_kb) stages = p.num_kb;
+  const int kb_per_cta = p.kb_per_split * ceil_div(num_tiles, p.splitk > 1 ? num_tiles : ctx->sm_count);
+  if (stages > kb_per_cta) stages = kb_per_cta;
   if (stages < 1) stages = 1;
   p.stages = stages;
   p.raw_i32 = raw_i32 ? 1 : 0;
@@ -368,36 +599,74 @@ int launch_tc(fa_ctx *ctx, const void *w_nk, int ldw, const void *a_lmk, int lda
   p.add = ep.add;
   p.act = ep.act;
   p.status = ctx->dev_status;
-  const size_t smem = stage_bytes * stages + (size_t)(2 * stages + 1) * 8 + 16 + 1024;
+  static const bool want_trace = getenv("FA_TC_TRACE") != nullptr;
+  unsigned long long *trace_dev = nullptr;
+  if (want_trace) {
+    cudaMalloc(&trace_dev, 256 * 8);
+    cudaMemsetAsync(trace_dev, 0, 256 * 8, ctx->stream);
+    p.trace = trace_dev;
+  }
+  const size_t smem = stage_bytes * stages + tail_bytes;
 
   CUtensorMap map_w, map_a;
-  FA_TRY(tc::make_tmap_k128(ctx, &map_w, w_nk, elem, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, 0, 0, 128));
-  FA_TRY(tc::make_tmap_k128(ctx, &map_a, a_lmk, elem, (uint64_t)K, (uint64_t)M, (uint64_t)lda, (uint64_t)limbs,
-                            (uint64_t)M * lda, (uint32_t)p.MT));
+  // weights: rows of 128 bytes, (tiles_n * num_kb * 128) of them, boxes of 128 rows
+  FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, (uint64_t)p.tiles_n * p.num_kb * 128, 0, 128));
+  // activations: [limbs * num_kb] slabs of M rows of 128 bytes, boxes of MT rows (rows >= M read as zero)
+  FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M, (uint64_t)limbs * p.num_kb, (uint32_t)p.MT));
   FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-  dim3 grid(ceil_div(N, 128), ceil_div(M, p.MT));
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  if (p.splitk > 1) {
+    cfg.gridDim = dim3(num_tiles, 1, p.splitk);
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = p.splitk;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  } else {
+    cfg.gridDim = dim3(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);  // persistent: one CTA per SM
+  }
   {
     LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : "tc_gemm_i8");
-    k_tc_gemm<KIND><<<grid, kThreads, smem, ctx->stream>>>(map_w, map_a, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, p);
+    if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm: %s", cudaGetErrorString(e));
   }
   FA_LAUNCH_CHECK(ctx, "tc_gemm");
+  if (trace_dev) {  // debugging aid (FA_TC_TRACE=1): timeline of CTA 0 in ns since its start
+    unsigned long long h[256];
+    cudaMemcpyAsync(h, trace_dev, sizeof h, cudaMemcpyDeviceToHost, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(trace_dev);
+    fprintf(stderr, "[tc trace] M=%d N=%d K=%d MT=%d limbs=%d stages=%d num_kb=%d tiles=%dx%d splitk=%d grid=%d\n", M, N, K,
+            p.MT, limbs, stages, p.num_kb, p.tiles_n, p.tiles_m, p.splitk, cfg.gridDim.x);
+    fprintf(stderr, "  tma issue :");
+    for (int i = 0; i < 64 && h[1 + i]; i++) fprintf(stderr, " %lld", (long long)(h[1 + i] - h[0]));
+    fprintf(stderr, "\n  mma ready :");
+    for (int i = 0; i < 64 && h[65 + i]; i++) fprintf(stderr, " %lld", (long long)(h[65 + i] - h[0]));
+    fprintf(stderr, "\n  last acc ready %lld, last epilogue end %lld, all joined %lld\n", (long long)(h[129] - h[0]),
+            (long long)(h[130] - h[0]), (long long)(h[131] - h[0]));
+  }
   return FA_OK;
 }
 
 }  // namespace
 
-int tc::make_tmap_k128(fa_ctx *ctx, CUtensorMap *out, const void *base, int elem_bytes, uint64_t k_elems, uint64_t rows,
-                       uint64_t ld_elems, uint64_t planes, uint64_t plane_stride_elems, uint32_t box_rows) {
+// Tensor of 128-byte rows: `slabs` == 0 gives a 2-d map [rows][128 B]; otherwise a 3-d map
+// [slabs][rows][128 B] with slabs stored back to back.  Boxes are box_rows x 128 bytes, swizzled.
+int tc::make_tmap_rows128(fa_ctx *ctx, CUtensorMap *out, const void *base, int elem_bytes, uint64_t rows, uint64_t slabs,
+                          uint32_t box_rows) {
   PFN_encodeTiled enc = get_encode();
   if (!enc) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable in this driver");
-  FA_REQUIRE(ctx, ((uintptr_t)base & 15) == 0 && (ld_elems * elem_bytes) % 16 == 0,
-             "tensor-core operand is not 16-byte aligned (base %p, row pitch %llu bytes)", base,
-             (unsigned long long)(ld_elems * elem_bytes));
-  // planes == 0: 2-d map [rows][k]; planes >= 1: 3-d map [planes][rows][k]
-  const cuuint32_t rank = planes == 0 ? 2 : 3;
-  cuuint64_t dims[3] = {k_elems, rows, planes ? planes : 1};
-  cuuint64_t strides[2] = {ld_elems * elem_bytes, plane_stride_elems * elem_bytes};
-  cuuint32_t box[3] = {(cuuint32_t)(kRowBytes / elem_bytes), box_rows, 1};
+  FA_REQUIRE(ctx, ((uintptr_t)base & 127) == 0, "tensor-core operand %p is not 128-byte aligned", base);
+  const cuuint32_t rank = slabs == 0 ? 2 : 3;
+  const cuuint32_t inner = (cuuint32_t)(kRowBytes / elem_bytes);
+  cuuint64_t dims[3] = {inner, rows, slabs ? slabs : 1};
+  cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, rows * (cuuint64_t)kRowBytes};
+  cuuint32_t box[3] = {inner, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, rank,
                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -408,73 +677,81 @@ int tc::make_tmap_k128(fa_ctx *ctx, CUtensorMap *out, const void *base, int elem
 
 bool fa_tc_available(fa_ctx *) { return get_encode() != nullptr; }
 
-int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_mk, int lda, const __half *b_nk, int ldb, float *c, int M, int N,
-                   int K, const TcEpilogue &ep) {
-  return launch_tc<0>(ctx, b_nk, ldb, a_mk, lda, 1, c, false, M, N, K, ep);
+int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, float *c, int M, int N, int K,
+                   const TcEpilogue &ep) {
+  return launch_tc<0>(ctx, w_packed, a_packed, 1, c, false, M, N, K, ep);
 }
 
-int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_lmk, int lda, int limbs, const int8_t *b_nk, int ldb, void *c,
-                  bool raw_i32, int M, int N, int K, const TcEpilogue &ep) {
-  return launch_tc<1>(ctx, b_nk, ldb, a_lmk, lda, limbs, c, raw_i32, M, N, K, ep);
+int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *w_packed, void *c, bool raw_i32, int M,
+                  int N, int K, const TcEpilogue &ep) {
+  return launch_tc<1>(ctx, w_packed, a_packed, limbs, c, raw_i32, M, N, K, ep);
 }
 
-int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, int kpad, __half *out) {
+int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out) {
   if (M == 0) return FA_OK;
-  size_t total = (size_t)M * (kpad / 2);
-  int grid = (int)((total + 255) / 256);
-  int cap = ctx->sm_count * 8;
-  if (grid > cap) grid = cap;
+  const int nch = fa_tc_chunks(K, 2);
   {
     LaunchScope ls(ctx, "prep_a_f16");
-    k_prep_a_f16<<<grid, 256, 0, ctx->stream>>>(a, M, K, kpad, out);
+    k_prep_a_f16<<<grid_for(ctx, (size_t)nch * M * 32, 256, 8), 256, 0, ctx->stream>>>(a, M, K, nch, out);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_f16");
   return FA_OK;
 }
 
-int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int kpad, int limbs, int8_t *out, float *rowscale) {
+int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *out, float *rowscale) {
   if (M == 0) return FA_OK;
   {
     LaunchScope ls(ctx, "prep_a_i8");
-    k_prep_a_i8<<<M, 256, 0, ctx->stream>>>(a, M, K, kpad, limbs, out, rowscale);
+    k_prep_a_i8<<<M, 256, 0, ctx->stream>>>(a, M, K, fa_tc_chunks(K, 1), limbs, out, rowscale);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_i8");
   return FA_OK;
 }
 
-int fa_repack_i8_kn_to_nk(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int kpad, int8_t *out_nk) {
-  dim3 grid(ceil_div(kpad, 32), ceil_div(N, 32)), block(32, 8);
+int fa_pack_a_i8_raw(fa_ctx *ctx, const int8_t *aq, int M, int K, int8_t *out) {
+  const int nch = fa_tc_chunks(K, 1);
   {
-    LaunchScope ls(ctx, "repack_i8");
-    k_repack_i8<<<grid, block, 0, ctx->stream>>>(w_kn, K, N, kpad, out_nk);
+    LaunchScope ls(ctx, "pack_a_i8_raw");
+    k_pack_a_i8_raw<<<grid_for(ctx, (size_t)nch * M * 128, 256, 8), 256, 0, ctx->stream>>>(aq, M, K, nch, out);
   }
-  FA_LAUNCH_CHECK(ctx, "repack_i8");
+  FA_LAUNCH_CHECK(ctx, "pack_a_i8_raw");
   return FA_OK;
 }
 
-int fa_repack_f_kn_to_nk_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, int kpad, __half *out_nk) {
-  dim3 grid(ceil_div(kpad, 32), ceil_div(N, 32)), block(32, 8);
+int fa_pack_w_i8(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out) {
+  FA_CHECK_CUDA(ctx, cudaMemsetAsync(out, 0, fa_tc_weight_bytes(N, K, 1), ctx->stream));
+  dim3 grid(ceil_div(K, 32), ceil_div(N, 32)), block(32, 8);
   {
-    LaunchScope ls(ctx, "repack_f16");
+    LaunchScope ls(ctx, "pack_w_i8");
+    k_pack_w_i8<<<grid, block, 0, ctx->stream>>>(w_kn, K, N, fa_tc_chunks(K, 1), out);
+  }
+  FA_LAUNCH_CHECK(ctx, "pack_w_i8");
+  return FA_OK;
+}
+
+int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, __half *out) {
+  FA_CHECK_CUDA(ctx, cudaMemsetAsync(out, 0, fa_tc_weight_bytes(N, K, 2), ctx->stream));
+  dim3 grid(ceil_div(K, 32), ceil_div(N, 32)), block(32, 8);
+  const int nch = fa_tc_chunks(K, 2);
+  {
+    LaunchScope ls(ctx, "pack_w_f16");
     if (src_storage == FA_F16)
-      k_repack_f16<__half><<<grid, block, 0, ctx->stream>>>((const __half *)w_kn, K, N, kpad, out_nk);
+      k_pack_w_f16<__half><<<grid, block, 0, ctx->stream>>>((const __half *)w_kn, K, N, nch, out);
     else
-      k_repack_f16<float><<<grid, block, 0, ctx->stream>>>((const float *)w_kn, K, N, kpad, out_nk);
+      k_pack_w_f16<float><<<grid, block, 0, ctx->stream>>>((const float *)w_kn, K, N, nch, out);
   }
-  FA_LAUNCH_CHECK(ctx, "repack_f16");
+  FA_LAUNCH_CHECK(ctx, "pack_w_f16");
   return FA_OK;
 }
 
-int fa_dequant_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K,
-                         int nblk, int zpb, int kpad, __half *out_nk) {
-  size_t total = (size_t)N * (kpad / 32);
-  int grid = (int)((total + 127) / 128);
-  int cap = ctx->sm_count * 16;
-  if (grid > cap) grid = cap;
+int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk,
+                        int zpb, __half *out) {
+  FA_CHECK_CUDA(ctx, cudaMemsetAsync(out, 0, fa_tc_weight_bytes(N, K, 2), ctx->stream));
   {
-    LaunchScope ls(ctx, "dequant_nbits_f16");
-    k_dequant_nbits<<<grid, 128, 0, ctx->stream>>>(bq, scales, zp, N, K, nblk, zpb, kpad, out_nk);
+    LaunchScope ls(ctx, "pack_w_nbits_f16");
+    k_pack_w_nbits<<<grid_for(ctx, (size_t)N * nblk, 128, 16), 128, 0, ctx->stream>>>(bq, scales, zp, N, K, nblk, zpb,
+                                                                                     fa_tc_chunks(K, 2), out);
   }
-  FA_LAUNCH_CHECK(ctx, "dequant_nbits_f16");
+  FA_LAUNCH_CHECK(ctx, "pack_w_nbits_f16");
   return FA_OK;
 }

@@ -27,25 +27,23 @@ struct fa_tensor {
   bool view = false;         // rowsView alias: owns nothing
   bool pooled = false;       // block returns to the pool (alloc) vs. plain free (upload)
   int arena = -1;            // id of the arena that releases it, -1 = persistent
-  // Lazily built operand copy used when this tensor is the B side of a tensor-core GEMM:
-  // f16 [cols][kpad] (row n holds column n of the matrix, K contiguous, zero padded).
+  // Lazily built packed f16 copy used when this tensor is the weight side of a tensor-core GEMM.
   void *bt_f16 = nullptr;
   size_t bt_bytes = 0;
-  int bt_kpad = 0;
 };
 
 struct fa_bytes {
   void *dptr = nullptr;
   size_t nbytes = 0;
   size_t block = 0;
-  // Lazily built int8 [N][kpad] copy (K contiguous) of a [K][N] int8 payload.
+  // Lazily built packed int8 copy of a [K][N] int8 payload.
   void *nk_i8 = nullptr;
   size_t nk_bytes = 0;
-  int nk_N = 0, nk_K = 0, nk_kpad = 0;
-  // Lazily built f16 [N][kpad] dequantised copy of an int4 payload (with the scales/zp it was built from).
+  int nk_N = 0, nk_K = 0;
+  // Lazily built packed f16 dequantised copy of an int4 payload (with the scales/zp it was built from).
   void *nk_f16 = nullptr;
   size_t nk_f16_bytes = 0;
-  int f16_N = 0, f16_K = 0, f16_kpad = 0;
+  int f16_N = 0, f16_K = 0;
   const void *f16_scales = nullptr, *f16_zp = nullptr;
 };
 
@@ -210,14 +208,23 @@ struct TcEpilogue {
   const float *add = nullptr;       // [M][N]
   int act = 0;
 };
-int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_mk, int lda, const __half *b_nk, int ldb, float *c, int M, int N,
-                   int K, const TcEpilogue &ep);
-int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_lmk, int lda, int limbs, const int8_t *b_nk, int ldb, void *c,
-                  bool raw_i32, int M, int N, int K, const TcEpilogue &ep);
-int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, int kpad, __half *out);
-int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int kpad, int limbs, int8_t *out, float *rowscale);
-int fa_repack_i8_kn_to_nk(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int kpad, int8_t *out_nk);
-int fa_repack_f_kn_to_nk_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, int kpad, __half *out_nk);
-int fa_dequant_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K,
-                         int nblk, int zpb, int kpad, __half *out_nk);
+// Packed ("box-contiguous") operand sizes: K is cut in chunks of 128 bytes.
+static inline int fa_tc_chunks(int K, int elem_bytes) { return ceil_div(K, 128 / elem_bytes); }
+static inline size_t fa_tc_weight_bytes(int N, int K, int elem_bytes) {
+  return (size_t)ceil_div(N, 128) * fa_tc_chunks(K, elem_bytes) * 128 * 128;
+}
+static inline size_t fa_tc_act_bytes(int M, int K, int elem_bytes, int limbs) {
+  return (size_t)limbs * fa_tc_chunks(K, elem_bytes) * M * 128;
+}
+int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, float *c, int M, int N, int K,
+                   const TcEpilogue &ep);
+int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *w_packed, void *c, bool raw_i32, int M,
+                  int N, int K, const TcEpilogue &ep);
+int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out);
+int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *out, float *rowscale);
+int fa_pack_a_i8_raw(fa_ctx *ctx, const int8_t *aq, int M, int K, int8_t *out);
+int fa_pack_w_i8(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out);
+int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, __half *out);
+int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk,
+                        int zpb, __half *out);
 bool fa_tc_available(fa_ctx *ctx);

@@ -26,17 +26,23 @@ int check_vec(fa_ctx *ctx, const fa_tensor *t, int n, const char *what) {
   return FA_OK;
 }
 
-// f16 [N][kpad] copy of a [K][N] weight tensor, built once per handle.
-int ensure_bt_f16(fa_ctx *ctx, fa_tensor *b, int kpad) {
+// Packed f16 copy of a [K][N] weight tensor, built once per handle.
+int ensure_bt_f16(fa_ctx *ctx, fa_tensor *b) {
   if (b->view) return fa_fail(ctx, FA_ERR_INVALID, "matmul: a rowsView cannot be the weight operand of a large product");
-  if (b->bt_f16 && b->bt_kpad == kpad) return FA_OK;
-  if (b->bt_f16) fa_block_release(ctx, b->bt_f16);
-  b->bt_f16 = nullptr;
-  size_t got = 0;
-  FA_TRY(fa_block_acquire(ctx, (size_t)b->cols * kpad * 2, &b->bt_f16, &got));
-  b->bt_bytes = got;
-  b->bt_kpad = kpad;
-  return fa_repack_f_kn_to_nk_f16(ctx, b->dptr, b->storage, b->rows, b->cols, kpad, (__half *)b->bt_f16);
+  if (b->bt_f16) return FA_OK;
+  FA_TRY(fa_block_acquire(ctx, fa_tc_weight_bytes(b->cols, b->rows, 2), &b->bt_f16, &b->bt_bytes));
+  return fa_pack_w_f16(ctx, b->dptr, b->storage, b->rows, b->cols, (__half *)b->bt_f16);
+}
+
+// Packed int8 copy of a [K][N] int8 payload, built once per handle and (N,K).
+int ensure_nk_i8(fa_ctx *ctx, fa_bytes *wq, int N, int K) {
+  if (wq->nk_i8 && wq->nk_N == N && wq->nk_K == K) return FA_OK;
+  if (wq->nk_i8) fa_block_release(ctx, wq->nk_i8);
+  wq->nk_i8 = nullptr;
+  FA_TRY(fa_block_acquire(ctx, fa_tc_weight_bytes(N, K, 1), &wq->nk_i8, &wq->nk_bytes));
+  wq->nk_N = N;
+  wq->nk_K = K;
+  return fa_pack_w_i8(ctx, (const int8_t *)wq->dptr, K, N, (int8_t *)wq->nk_i8);
 }
 
 }  // namespace
@@ -63,17 +69,15 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
   const float *biasp = bias ? (const float *)bias->dptr : nullptr;
   const float *addp = add ? (const float *)add->dptr : nullptr;
   if (b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K)) {
-    const int kpad = (int)round_up(K, 64);
-    rc = ensure_bt_f16(ctx, b, kpad);
-    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)M * kpad * 2);
-    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, kpad, (__half *)ctx->scratch_a);
+    rc = ensure_bt_f16(ctx, b);
+    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 2, 1));
+    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)ctx->scratch_a);
     if (rc == FA_OK) {
       TcEpilogue ep;
       ep.bias = biasp;
       ep.add = addp;
       ep.act = act;
-      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, kpad, (const __half *)b->bt_f16, kpad,
-                          (float *)c->dptr, M, N, K, ep);
+      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {
     rc = fa_simt_gemm(ctx, ap, b->dptr, b->storage == FA_F16 ? 1 : 0, nullptr, biasp, act, addp, (float *)c->dptr, M,
@@ -109,31 +113,19 @@ extern "C" int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, con
   int rc = FA_OK;
   const float *biasp = bias ? (const float *)bias->dptr : nullptr;
   if (tc_shape_ok(ctx, M, N, K)) {
-    const int kpad = (int)round_up(K, 128);
     const int limbs = ctx->int8_limbs;
-    if (!(wq->nk_i8 && wq->nk_N == N && wq->nk_K == K)) {  // one-time [K][N] -> [N][K] repack per handle
-      if (wq->nk_i8) fa_block_release(ctx, wq->nk_i8);
-      wq->nk_i8 = nullptr;
-      rc = fa_block_acquire(ctx, (size_t)N * kpad, &wq->nk_i8, &wq->nk_bytes);
-      if (rc == FA_OK) {
-        wq->nk_N = N;
-        wq->nk_K = K;
-        wq->nk_kpad = kpad;
-        rc = fa_repack_i8_kn_to_nk(ctx, (const int8_t *)wq->dptr, K, N, kpad, (int8_t *)wq->nk_i8);
-      }
-    }
-    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)limbs * M * kpad);
+    rc = ensure_nk_i8(ctx, wq, N, K);  // one-time repack per handle
+    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 1, limbs));
     if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_s, &ctx->scratch_s_bytes, (size_t)M * 4);
     if (rc == FA_OK)
-      rc = fa_prep_a_i8(ctx, ap, M, K, kpad, limbs, (int8_t *)ctx->scratch_a, (float *)ctx->scratch_s);
+      rc = fa_prep_a_i8(ctx, ap, M, K, limbs, (int8_t *)ctx->scratch_a, (float *)ctx->scratch_s);
     if (rc == FA_OK) {
       TcEpilogue ep;
       ep.rowscale = (const float *)ctx->scratch_s;
       ep.colscale = (const float *)scale->dptr;
       ep.bias = biasp;
       ep.act = act;
-      rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, kpad, limbs, (const int8_t *)wq->nk_i8, kpad, c->dptr,
-                         false, M, N, K, ep);
+      rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, limbs, (const int8_t *)wq->nk_i8, c->dptr, false, M, N, K, ep);
     }
   } else {
     rc = fa_simt_gemm(ctx, ap, wq->dptr, 2, (const float *)scale->dptr, biasp, act, nullptr, (float *)c->dptr, M, N, K);
@@ -169,29 +161,26 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
   FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
   int rc = FA_OK;
   if (tc_shape_ok(ctx, M, N, K)) {
-    const int kpad = (int)round_up(K, 64);
     const bool cached = bq->nk_f16 && bq->f16_N == N && bq->f16_K == K && bq->f16_scales == scales->dptr &&
                         bq->f16_zp == zp->dptr;
     if (!cached) {
       if (bq->nk_f16) fa_block_release(ctx, bq->nk_f16);
       bq->nk_f16 = nullptr;
-      rc = fa_block_acquire(ctx, (size_t)N * kpad * 2, &bq->nk_f16, &bq->nk_f16_bytes);
+      rc = fa_block_acquire(ctx, fa_tc_weight_bytes(N, K, 2), &bq->nk_f16, &bq->nk_f16_bytes);
       if (rc == FA_OK) {
         bq->f16_N = N;
         bq->f16_K = K;
-        bq->f16_kpad = kpad;
         bq->f16_scales = scales->dptr;
         bq->f16_zp = zp->dptr;
-        rc = fa_dequant_nbits_f16(ctx, (const uint8_t *)bq->dptr, (const float *)scales->dptr,
-                                  (const uint8_t *)zp->dptr, N, K, nblk, zpb, kpad, (__half *)bq->nk_f16);
+        rc = fa_pack_w_nbits_f16(ctx, (const uint8_t *)bq->dptr, (const float *)scales->dptr,
+                                 (const uint8_t *)zp->dptr, N, K, nblk, zpb, (__half *)bq->nk_f16);
       }
     }
-    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)M * kpad * 2);
-    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, kpad, (__half *)ctx->scratch_a);
+    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 2, 1));
+    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)ctx->scratch_a);
     if (rc == FA_OK) {
       TcEpilogue ep;
-      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, kpad, (const __half *)bq->nk_f16, kpad,
-                          (float *)c->dptr, M, N, K, ep);
+      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, (const __half *)bq->nk_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {
     rc = fa_simt_nbits(ctx, ap, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr,
@@ -215,25 +204,21 @@ extern "C" int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_by
              (size_t)N * K);
   FA_REQUIRE(ctx, fa_tc_available(ctx), "int8GemmI32: tensor-map encoder unavailable");
   FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
-  const int kpad = (int)round_up(K, 128);
   int rc = FA_OK;
-  if (!(wq->nk_i8 && wq->nk_N == N && wq->nk_K == K)) {
-    if (wq->nk_i8) fa_block_release(ctx, wq->nk_i8);
-    wq->nk_i8 = nullptr;
-    FA_TRY(fa_block_acquire(ctx, (size_t)N * kpad, &wq->nk_i8, &wq->nk_bytes));
-    wq->nk_N = N;
-    wq->nk_K = K;
-    wq->nk_kpad = kpad;
-    FA_TRY(fa_repack_i8_kn_to_nk(ctx, (const int8_t *)wq->dptr, K, N, kpad, (int8_t *)wq->nk_i8));
-  }
-  FA_TRY(fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, (size_t)M * kpad));
-  FA_CHECK_CUDA(ctx, cudaMemsetAsync(ctx->scratch_a, 0, (size_t)M * kpad, ctx->stream));
-  FA_CHECK_CUDA(ctx, cudaMemcpy2DAsync(ctx->scratch_a, kpad, aq_host, K, K, M, cudaMemcpyHostToDevice, ctx->stream));
+  FA_TRY(ensure_nk_i8(ctx, wq, N, K));
+  // stage the caller's int8 activations row-major, then pack them into the chunk-major operand layout
+  void *raw = nullptr;
+  size_t raw_bytes = 0;
+  FA_TRY(fa_block_acquire(ctx, (size_t)M * K, &raw, &raw_bytes));
+  FA_CHECK_CUDA(ctx, cudaMemcpyAsync(raw, aq_host, (size_t)M * K, cudaMemcpyHostToDevice, ctx->stream));
+  FA_TRY(fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 1, 1)));
+  FA_TRY(fa_pack_a_i8_raw(ctx, (const int8_t *)raw, M, K, (int8_t *)ctx->scratch_a));
+  fa_block_release(ctx, raw);
   void *acc = nullptr;
   size_t got = 0;
   FA_TRY(fa_block_acquire(ctx, (size_t)M * N * 4, &acc, &got));
   TcEpilogue ep;
-  rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, kpad, 1, (const int8_t *)wq->nk_i8, kpad, acc, true, M, N, K, ep);
+  rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, 1, (const int8_t *)wq->nk_i8, acc, true, M, N, K, ep);
   if (rc == FA_OK) {
     cudaError_t e = cudaMemcpyAsync(acc_out_host, acc, (size_t)M * N * 4, cudaMemcpyDeviceToHost, ctx->stream);
     if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "int8GemmI32 readback: %s", cudaGetErrorString(e));

@@ -131,10 +131,10 @@ __host__ __device__ constexpr uint32_t make_idesc(int kind, int M, int N) {
 
 // ---- host: tensor maps ---------------------------------------------------------------------------
 
-// Row-major [rows][k] global tensor (planes == 0: 2-d map) or [planes][rows][k] (planes >= 1: 3-d map)
-// read in boxes of 128 bytes x box_rows with the 128-byte swizzle.  elem_bytes 1 or 2.  Out-of-range
-// rows/bytes read as zero, so ragged M/N/K tails need no special casing in the kernels.
-int make_tmap_k128(fa_ctx *ctx, CUtensorMap *out, const void *base, int elem_bytes, uint64_t k_elems, uint64_t rows,
-                   uint64_t ld_elems, uint64_t planes, uint64_t plane_stride_elems, uint32_t box_rows);
+// Tensor of 128-byte rows: slabs == 0 gives a 2-d map [rows][128 B], otherwise a 3-d map
+// [slabs][rows][128 B] (slabs back to back).  Boxes are box_rows x 128 bytes with the 128-byte
+// swizzle; rows past the end read as zero, so a ragged M needs no special casing in the kernels.
+int make_tmap_rows128(fa_ctx *ctx, CUtensorMap *out, const void *base, int elem_bytes, uint64_t rows, uint64_t slabs,
+                      uint32_t box_rows);
 
 }  // namespace tc
