@@ -54,6 +54,7 @@ SIGNATURES = {
     "fa_matmul_int8": [P, P, P, P, I, I, P, I, PP],
     "fa_matmul_nbits": [P, P, P, P, P, I, I, PP],
     "fa_int8_gemm_i32": [P, P, I, P, I, I, P],
+    "fa_matmul_int8_static": [P, P, P, P, P, I, P, I, I, I],
     "fa_layernorm": [P, P, P, P, C.c_float, PP],
     "fa_softmax": [P, P, PP],
     "fa_conv1d": [P, P, P, P, I, I, I, I, I, I, I, I, PP],

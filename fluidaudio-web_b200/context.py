@@ -221,6 +221,13 @@ class CudaContext:
         self._check(self._lib.fa_int8_gemm_i32(self._h, aq.ctypes.data, M, wq.h, N, K, out.ctypes.data))
         return out
 
+    def matmulInt8Static(self, a_ptr: int, wq_ptr: int, scale_ptr: int, bias_ptr: Optional[int], act: str, y_ptr: int,
+                         M: int, N: int, K: int) -> None:
+        """Allocation-free int8 product on raw device pointers (see fa_matmul_int8_static in the header):
+        for hosts that cannot allocate device memory when they call.  Scratch is a fixed array inside the
+        library; limits M <= 512, K <= 2048, packed weights <= 8 MiB.  Calls must not overlap on the GPU."""
+        self._check(self._lib.fa_matmul_int8_static(self._h, a_ptr, wq_ptr, scale_ptr, bias_ptr, ACT[act], y_ptr, M, N, K))
+
     def layernorm(self, x, gamma, beta, eps: float = 1e-5) -> Tensor:
         return self._op(self._lib.fa_layernorm, x.h, gamma.h, beta.h, eps)
 

@@ -555,7 +555,7 @@ int grid_for(fa_ctx *ctx, size_t n, int block, int per_sm) {
 
 template <int KIND>
 int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs, void *out, bool raw_i32, int M, int N,
-              int K, const TcEpilogue &ep) {
+              int K, const TcEpilogue &ep, bool allow_trace = true) {
   const int elem = KIND == 0 ? 2 : 1;
   TcParams p{};
   p.M = M;
@@ -601,7 +601,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.status = ctx->dev_status;
   static const bool want_trace = getenv("FA_TC_TRACE") != nullptr;
   unsigned long long *trace_dev = nullptr;
-  if (want_trace) {
+  if (want_trace && allow_trace) {
     cudaMalloc(&trace_dev, 256 * 8);
     cudaMemsetAsync(trace_dev, 0, 256 * 8, ctx->stream);
     p.trace = trace_dev;
@@ -754,4 +754,70 @@ int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, con
   }
   FA_LAUNCH_CHECK(ctx, "pack_w_nbits_f16");
   return FA_OK;
+}
+
+// ---- allocation-free int8 product -------------------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory when they call it: a serving process that
+// has already handed every remaining byte of the GPU to its own pool (so cudaMalloc can fail at any
+// moment), or a real-time audio thread that must never wait on the driver's allocation lock.  For them
+// fa_matmul_int8_static runs the int8 tensor-core product with all of its scratch - the packed copy of
+// the weights, the int8 digit planes of the activations and the per-row scales - inside one fixed array
+// that is part of the library image.  Every GPU that loads the library holds these bytes until exit.
+//
+// Limits (checked, FA_ERR_INVALID beyond them): M <= 512, 64 <= K <= 2048, N >= 64 and the packed weights
+// (N rounded up to 128 times K rounded up to 128 bytes) <= 8 MiB.
+//
+// All calls share the array and it keeps the previous call's contents: this entry point rewrites every
+// byte it later reads (zero padding included), and calls that overlap on the GPU - two streams, two
+// contexts on one device - race on it.  Issue them on one stream.
+constexpr int kStaticMaxM = 512, kStaticMaxK = 2048;
+constexpr size_t kStaticWBytes = 8u << 20;
+constexpr size_t kStaticABytes = (size_t)3 * kStaticMaxM * kStaticMaxK;
+constexpr size_t kStaticSBytes = 4096;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticWBytes + kStaticABytes + kStaticSBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a kernel can use:
+// the device address is looked up once per device, with that device current.
+static unsigned char *g_static_scratch_dev[64] = {nullptr};
+
+extern "C" int fa_matmul_int8_static(fa_ctx *ctx, const float *a_dev, const void *wq_kn_dev, const float *scale_dev,
+                                     const float *bias_dev, int act, float *y_dev, int M, int N, int K) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "matmulInt8Static: NULL context");
+  FA_REQUIRE(ctx, a_dev && wq_kn_dev && scale_dev && y_dev, "matmulInt8Static: NULL device pointer");
+  FA_REQUIRE(ctx, act >= 0 && act <= 5, "matmulInt8Static: unknown activation code %d", act);
+  FA_REQUIRE(ctx, M >= 1 && M <= kStaticMaxM, "matmulInt8Static: M=%d is outside 1..%d", M, kStaticMaxM);
+  FA_REQUIRE(ctx, K >= 64 && K <= kStaticMaxK, "matmulInt8Static: K=%d is outside 64..%d", K, kStaticMaxK);
+  FA_REQUIRE(ctx, N >= 64, "matmulInt8Static: N=%d is below 64", N);
+  FA_REQUIRE(ctx, fa_tc_weight_bytes(N, K, 1) <= kStaticWBytes,
+             "matmulInt8Static: packed weights need %zu bytes, the static scratch holds %zu", fa_tc_weight_bytes(N, K, 1),
+             kStaticWBytes);
+  FA_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "matmulInt8Static: device ordinal %d unsupported", ctx->device);
+  FA_REQUIRE(ctx, get_encode() != nullptr, "matmulInt8Static: tensor-map encoder unavailable");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!g_static_scratch_dev[ctx->device]) {
+    // first call on this device: resolve the array's device address (do this before any stream capture)
+    void *ptr = nullptr;
+    FA_CHECK_CUDA(ctx, cudaGetSymbolAddress(&ptr, g_static_scratch));
+    g_static_scratch_dev[ctx->device] = (unsigned char *)ptr;
+  }
+  unsigned char *base = g_static_scratch_dev[ctx->device];
+  int8_t *w_packed = (int8_t *)base;
+  int8_t *a_planes = (int8_t *)(base + kStaticWBytes);
+  float *rowscale = (float *)(base + kStaticWBytes + kStaticABytes);
+  const int limbs = ctx->int8_limbs;
+  const bool was_profiling = ctx->profiling;  // per-launch event pairs would create events: keep them off here
+  ctx->profiling = false;
+  int rc = fa_pack_w_i8(ctx, (const int8_t *)wq_kn_dev, K, N, w_packed);  // zero-fills the packed region first
+  if (rc == FA_OK) rc = fa_prep_a_i8(ctx, a_dev, M, K, limbs, a_planes, rowscale);
+  if (rc == FA_OK) {
+    TcEpilogue ep;
+    ep.rowscale = rowscale;
+    ep.colscale = scale_dev;
+    ep.bias = bias_dev;
+    ep.act = act;
+    rc = launch_tc<1>(ctx, w_packed, a_planes, limbs, y_dev, false, M, N, K, ep, /*allow_trace=*/false);
+  }
+  ctx->profiling = was_profiling;
+  return rc;
 }

@@ -118,6 +118,19 @@ int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, const fa_tens
  * for bit: aq int8 [M,K] row-major (host), wq as above; acc_out int32 [M,N] (host). */
 int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_bytes *wq, int N, int K, int32_t *acc_out_host);
 
+/* Allocation-free variant of fa_matmul_int8 on raw device pointers.  It has no counterpart in the
+ * reference; it exists for hosts that may not allocate device memory at call time (a process whose own
+ * pool already owns the rest of the GPU, a real-time audio thread that must not wait on the driver's
+ * allocator).  All scratch (packed weights, activation digit planes, row scales) lives in a fixed array
+ * inside the library image, about 11 MiB held by every GPU that loads the library.
+ * a_dev f32 [M,K], wq_kn_dev int8 bytes in k*N+n order, scale_dev f32 [N], bias_dev f32 [N] or NULL,
+ * y_dev f32 [M,N]; all device pointers, work is enqueued on the context's stream.
+ * Limits: M <= 512, 64 <= K <= 2048, N >= 64, ceil(N/128)*ceil(K/128)*16384 <= 8 MiB; otherwise
+ * FA_ERR_INVALID.  The first call on a device resolves the array's device address: make that call
+ * before any stream capture.  Calls share the array and must not overlap on the GPU (same stream). */
+int fa_matmul_int8_static(fa_ctx *ctx, const float *a_dev, const void *wq_kn_dev, const float *scale_dev,
+                          const float *bias_dev, int act, float *y_dev, int M, int N, int K);
+
 /* ---- glue ops the encoder/decoder forwards call between GEMMs --------------- */
 int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
                  fa_tensor **out);                                                        /* layernorm :167 */
