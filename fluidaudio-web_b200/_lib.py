@@ -50,6 +50,10 @@ SIGNATURES = {
     "fa_rows_view": [P, P, I, PP],
     "fa_begin_batch": [P],
     "fa_end_batch": [P],
+    "fa_graph_begin": [P],
+    "fa_graph_end": [P, PP],
+    "fa_graph_launch": [P, P],
+    "fa_graph_free": [P, P],
     "fa_matmul": [P, P, P, P, I, P, PP],
     "fa_matmul_int8": [P, P, P, P, I, I, P, I, PP],
     "fa_matmul_nbits": [P, P, P, P, P, I, I, PP],

@@ -58,6 +58,21 @@ class StagedRead:
         return out
 
 
+class RecordedBatch:
+    """A recorded batch; launch() submits all of its ops with one call."""
+
+    def __init__(self, ctx: "CudaContext", h: int):
+        self._ctx, self._h = ctx, h
+
+    def launch(self) -> None:
+        self._ctx._check(self._ctx._lib.fa_graph_launch(self._ctx._h, self._h))
+
+    def free(self) -> None:
+        if self._h:
+            self._ctx._check(self._ctx._lib.fa_graph_free(self._ctx._h, self._h))
+            self._h = None
+
+
 def _np_f32(data) -> np.ndarray:
     return np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
 
@@ -193,6 +208,24 @@ class CudaContext:
 
     withBatch = withBatchSync
 
+    def recordBatch(self, fn) -> "RecordedBatch":
+        """Record the ops `fn` enqueues into one replayable submission (a CUDA graph) instead of running
+        them: the repeatable form of the reference's one-submit batch (src/gpu/scheduler.js:17-60).  Run
+        the same sequence once eagerly first so weight repacks and pool growth stay out of the recording.
+        Returns (RecordedBatch, whatever fn returned); tensors fn created stay valid across replays."""
+        self._check(self._lib.fa_graph_begin(self._h))
+        try:
+            result = fn()
+        except Exception:
+            g = C.c_void_p()
+            self._lib.fa_graph_end(self._h, C.byref(g))
+            if g.value:
+                self._lib.fa_graph_free(self._h, g)
+            raise
+        g = C.c_void_p()
+        self._check(self._lib.fa_graph_end(self._h, C.byref(g)))
+        return RecordedBatch(self, g.value), result
+
     # -- linear algebra (compute.d.ts:153-168) -----------------------------------------------------
     def matmul(self, a: Tensor, b: Tensor, opts: Optional[dict] = None, *, bias=None, act="none", add=None) -> Tensor:
         if opts:
@@ -247,7 +280,7 @@ class CudaContext:
         return self._op(self._lib.fa_conv1d, x.h, w.h, self._h_of(bias), cout, k, stride, padLeft, padRight, dilation,
                         groups, ACT[act])
 
-    def conv2d(self, x, w, opts: Optional[dict] = None, **kw) -> Tensor:
+    def conv2d(self, x, weight, opts: Optional[dict] = None, **kw) -> Tensor:
         o = dict(opts or {})
         o.update(kw)
         padH, padW = o.get("padH", 0), o.get("padW", 0)
@@ -255,7 +288,7 @@ class CudaContext:
         pb = o.get("padBottom", padH) if o.get("padBottom") is not None else padH
         pl = o.get("padLeft", padW) if o.get("padLeft") is not None else padW
         pr = o.get("padRight", padW) if o.get("padRight") is not None else padW
-        return self._op(self._lib.fa_conv2d, x.h, w.h, self._h_of(o.get("bias")), o["cout"], o["cin"], o["h"], o["w"],
+        return self._op(self._lib.fa_conv2d, x.h, weight.h, self._h_of(o.get("bias")), o["cout"], o["cin"], o["h"], o["w"],
                         o["kh"], o["kw"], o.get("strideH", 1), o.get("strideW", 1), pt, pb, pl, pr, o.get("groups", 1),
                         ACT[o.get("act", "none")])
 

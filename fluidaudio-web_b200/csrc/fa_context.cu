@@ -87,6 +87,11 @@ extern "C" int fa_ctx_destroy(fa_ctx *ctx) {
     if (s->done) cudaEventDestroy(s->done);
     delete s;
   }
+  for (fa_graph *g : ctx->graphs) {
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+  }
   for (fa_tensor *t : ctx->tensors) delete t;
   for (fa_bytes *b : ctx->byte_handles) delete b;
   for (auto &kv : ctx->blocks) cudaFree(kv.first);
@@ -119,6 +124,7 @@ extern "C" int fa_ctx_stream(fa_ctx *ctx, void **stream_out) {
 
 extern "C" int fa_sync(fa_ctx *ctx) {
   if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "fa_sync: NULL context");
+  FA_REQUIRE(ctx, !ctx->capturing, "sync/download/read is not allowed while a graph is being recorded");
   FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
   int st[4] = {0, 0, 0, 0};
   FA_CHECK_CUDA(ctx, cudaMemcpyAsync(st, ctx->dev_status, sizeof st, cudaMemcpyDeviceToHost, ctx->stream));
@@ -141,13 +147,33 @@ extern "C" int fa_launch_count(fa_ctx *ctx, unsigned long long *out) {
 
 int fa_block_acquire(fa_ctx *ctx, size_t bytes, void **out, size_t *block_bytes) {
   size_t sz = round_up(bytes < 256 ? 256 : bytes, 256);
+  if (ctx->capturing) {  // blocks already reserved for the graph being recorded come first
+    auto g = ctx->capturing->free_list.find(sz);
+    if (g != ctx->capturing->free_list.end() && !g->second.empty()) {
+      *out = g->second.back();
+      g->second.pop_back();
+      ctx->reused++;
+      *block_bytes = sz;
+      return FA_OK;
+    }
+  }
+  int rc = fa_block_acquire_global(ctx, sz, out);
+  if (rc != FA_OK) return rc;
+  *block_bytes = sz;
+  if (ctx->capturing) {
+    ctx->capturing->blocks.push_back(*out);
+    ctx->block_owner[*out] = ctx->capturing;
+  }
+  return FA_OK;
+}
+
+int fa_block_acquire_global(fa_ctx *ctx, size_t sz, void **out) {
   auto it = ctx->pool.find(sz);
   if (it != ctx->pool.end() && !it->second.empty()) {
     *out = it->second.back();
     it->second.pop_back();
     ctx->pool_bytes -= sz;
     ctx->reused++;
-    *block_bytes = sz;
     return FA_OK;
   }
   if (ctx->pool_cap && ctx->live_bytes + sz > ctx->pool_cap)
@@ -158,7 +184,7 @@ int fa_block_acquire(fa_ctx *ctx, size_t bytes, void **out, size_t *block_bytes)
   if (e == cudaErrorMemoryAllocation && ctx->pool_bytes) {
     // give idle pool blocks back to the driver and retry once
     cudaGetLastError();
-    cudaStreamSynchronize(ctx->stream);
+    if (!ctx->capturing) cudaStreamSynchronize(ctx->stream);
     for (auto &kv : ctx->pool) {
       for (void *q : kv.second) {
         cudaFree(q);
@@ -180,13 +206,17 @@ int fa_block_acquire(fa_ctx *ctx, size_t bytes, void **out, size_t *block_bytes)
   ctx->created++;
   ctx->created_bytes += sz;
   *out = p;
-  *block_bytes = sz;
   return FA_OK;
 }
 
 void fa_block_release(fa_ctx *ctx, void *p) {
   auto it = ctx->blocks.find(p);
   if (it == ctx->blocks.end()) return;
+  auto ow = ctx->block_owner.find(p);
+  if (ow != ctx->block_owner.end()) {  // reserved for a graph: stays with it
+    ow->second->free_list[it->second].push_back(p);
+    return;
+  }
   ctx->pool[it->second].push_back(p);
   ctx->pool_bytes += it->second;
 }
@@ -199,17 +229,6 @@ void fa_block_free(fa_ctx *ctx, void *p) {
   cudaFree(p);
   ctx->live_bytes -= it->second;
   ctx->blocks.erase(it);
-}
-
-int fa_scratch(fa_ctx *ctx, void **slot, size_t *slot_bytes, size_t need) {
-  if (*slot_bytes >= need) return FA_OK;
-  if (*slot) fa_block_release(ctx, *slot);
-  *slot = nullptr;
-  *slot_bytes = 0;
-  size_t got = 0;
-  FA_TRY(fa_block_acquire(ctx, need, slot, &got));
-  *slot_bytes = got;
-  return FA_OK;
 }
 
 bool fa_valid(fa_ctx *ctx, const fa_tensor *t) { return t && ctx->tensors.count(const_cast<fa_tensor *>(t)); }
@@ -601,5 +620,63 @@ extern "C" int fa_profile_end(fa_ctx *ctx, fa_profile_entry *out, int capacity, 
     n++;
   }
   *n_out = n;
+  return FA_OK;
+}
+
+// ---- recorded batches (CUDA graphs) ---------------------------------------------------------------
+
+extern "C" int fa_graph_begin(fa_ctx *ctx) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "graphBegin: NULL context");
+  FA_REQUIRE(ctx, !ctx->capturing, "graphBegin: a recording is already open");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  fa_graph *g = new fa_graph();
+  // relaxed mode: a pool miss inside the recording may still call cudaMalloc
+  cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed);
+  if (e != cudaSuccess) {
+    delete g;
+    return fa_fail(ctx, FA_ERR_CUDA, "cudaStreamBeginCapture: %s", cudaGetErrorString(e));
+  }
+  ctx->capturing = g;
+  return FA_OK;
+}
+
+extern "C" int fa_graph_end(fa_ctx *ctx, fa_graph **out) {
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "graphEnd: NULL argument");
+  FA_REQUIRE(ctx, ctx->capturing, "graphEnd: no recording is open");
+  fa_graph *g = ctx->capturing;
+  ctx->capturing = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+  ctx->graphs.insert(g);
+  if (e != cudaSuccess) {
+    fa_graph_free(ctx, g);
+    return fa_fail(ctx, FA_ERR_CUDA, "graph capture/instantiate: %s", cudaGetErrorString(e));
+  }
+  *out = g;
+  return FA_OK;
+}
+
+extern "C" int fa_graph_launch(fa_ctx *ctx, fa_graph *g) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "graphLaunch: NULL context");
+  FA_REQUIRE(ctx, g && ctx->graphs.count(g) && g->exec, "graphLaunch: unknown graph handle");
+  FA_REQUIRE(ctx, !ctx->capturing, "graphLaunch: not allowed while recording");
+  FA_CHECK_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+  return FA_OK;
+}
+
+extern "C" int fa_graph_free(fa_ctx *ctx, fa_graph *g) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "graphFree: NULL context");
+  if (!g) return FA_OK;
+  FA_REQUIRE(ctx, ctx->graphs.count(g), "graphFree: unknown graph handle");
+  cudaStreamSynchronize(ctx->stream);
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  // reserved blocks that are idle go back to the shared pool; blocks still held by live tensors just
+  // lose their reservation and return to the pool when those tensors are freed
+  for (void *p : g->blocks) ctx->block_owner.erase(p);
+  for (auto &kv : g->free_list)
+    for (void *p : kv.second) fa_block_release(ctx, p);
+  ctx->graphs.erase(g);
+  delete g;
   return FA_OK;
 }

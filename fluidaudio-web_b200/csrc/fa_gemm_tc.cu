@@ -51,7 +51,7 @@ struct TcParams {
   int kb_per_split;
   int raw_i32;        // 1: store the limb-0 int32 accumulators instead of the float epilogue
   float *out;         // [M][N] f32 (or int32 when raw_i32)
-  const float *rowscale, *colscale, *bias, *add;
+  const float *rowscale, *colscale, *bias, *add, *rowbias;
   int act;
   int *status;
   unsigned long long *trace;  // debugging aid: per-phase %globaltimer stamps of CTA 0, or nullptr
@@ -292,6 +292,14 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
           for (int j = 0; j < 16; j++) ad[j] = 0.0f;
         }
+        float rb[16];  // per-row bias (the output-channel bias of a pointwise convolution run as a GEMM)
+        if (p.rowbias) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) rb[j] = __ldg(p.rowbias + min(m0 + c + j, p.M - 1));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; j++) rb[j] = 0.0f;
+        }
         tmem_ld_wait();
         if (KIND == 1 && p.raw_i32 == 1) {
           if (n_ok) {
@@ -321,7 +329,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           continue;
         }
 #pragma unroll
-        for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs);
+        for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs) + rb[j];
         act16(v, p.act);
         if (n_ok) {
           float *orow = p.out + (size_t)(m0 + c) * p.N + n;
@@ -375,6 +383,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         for (int q = 0; q < 4; q++) {
           const int nn = min(n + q, p.N - 1);
           float v = fmaf(acc[q] * rs, p.colscale ? p.colscale[nn] : 1.0f, p.bias ? p.bias[nn] : 0.0f);
+          if (p.rowbias) v += p.rowbias[m];
           v = fa_actf(v, p.act);
           if (p.add) v += p.add[(size_t)m * p.N + nn];
           o[q] = v;
@@ -597,6 +606,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.colscale = ep.colscale;
   p.bias = ep.bias;
   p.add = ep.add;
+  p.rowbias = ep.rowbias;
   p.act = ep.act;
   p.status = ctx->dev_status;
   static const bool want_trace = getenv("FA_TC_TRACE") != nullptr;

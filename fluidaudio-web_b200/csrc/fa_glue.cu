@@ -660,6 +660,34 @@ extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, cout, Ho * Wo, FA_F32, true, &y));
   size_t n = (size_t)cout * Ho * Wo;
+  // A pointwise convolution is the product W[cout,cin] @ x[cin, H*W] (the reference routes it to its GEMM
+  // plus a per-row bias pass, src/gpu/compute.js:551-555,804-810): run it on the tensor cores with the
+  // feature map as the streamed operand and the output-channel bias applied per row in the epilogue.
+  const int P = h * w_;
+  if (kh == 1 && kw == 1 && stride_h == 1 && stride_w == 1 && groups == 1 && pad_top == 0 && pad_bottom == 0 &&
+      pad_left == 0 && pad_right == 0 && fa_tc_available(ctx) && cin >= 64 && P >= 64 &&
+      (long long)cout * cin * P >= (1ll << 21)) {
+    void *xa = nullptr, *wa = nullptr;
+    size_t xb = 0, wb = 0;
+    int rc = fa_block_acquire(ctx, fa_tc_weight_bytes(P, cin, 2), &xa, &xb);
+    if (rc == FA_OK) rc = fa_block_acquire(ctx, fa_tc_act_bytes(cout, cin, 2, 1), &wa, &wb);
+    if (rc == FA_OK) rc = fa_pack_w_f16(ctx, x->dptr, FA_F32, cin, P, (__half *)xa);
+    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, (const float *)w->dptr, cout, cin, (__half *)wa);
+    if (rc == FA_OK) {
+      TcEpilogue ep;
+      ep.rowbias = bias ? (const float *)bias->dptr : nullptr;
+      ep.act = act;
+      rc = fa_tc_gemm_f16(ctx, (const __half *)wa, (const __half *)xa, (float *)y->dptr, cout, P, cin, ep);
+    }
+    if (xa) fa_block_release(ctx, xa);
+    if (wa) fa_block_release(ctx, wa);
+    if (rc != FA_OK) {
+      fa_free_tensor(ctx, y);
+      return rc;
+    }
+    *out = y;
+    return FA_OK;
+  }
   {
     LaunchScope ls(ctx, "conv2d");
     k_conv2d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,

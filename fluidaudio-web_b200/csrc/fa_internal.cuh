@@ -56,6 +56,13 @@ struct fa_staged {
   bool consumed = false;
 };
 
+struct fa_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  std::vector<void *> blocks;                                 // device blocks reserved for this graph
+  std::unordered_map<size_t, std::vector<void *>> free_list;  // reserved blocks not in use right now
+};
+
 struct ProfileRec {
   const char *label;
   cudaEvent_t e0, e1;
@@ -90,11 +97,10 @@ struct fa_ctx {
   std::vector<ProfileRec> prof;
   // device-side status word written by kernels whose bounded waits ran out
   int *dev_status = nullptr;
-  // scratch for tensor-core prepasses (grown on demand, stream-ordered reuse)
-  void *scratch_a = nullptr;
-  size_t scratch_a_bytes = 0;
-  void *scratch_s = nullptr;
-  size_t scratch_s_bytes = 0;
+  // graph recording: blocks acquired while `capturing` is set belong to that graph
+  fa_graph *capturing = nullptr;
+  std::unordered_map<void *, fa_graph *> block_owner;
+  std::unordered_set<fa_graph *> graphs;
 };
 
 // ---- errors ----------------------------------------------------------------
@@ -120,10 +126,10 @@ int fa_fail(fa_ctx *ctx, int code, const char *fmt, ...);
 // ---- memory (fa_context.cu) -----------------------------------------------------
 
 int fa_block_acquire(fa_ctx *ctx, size_t bytes, void **out, size_t *block_bytes);
+int fa_block_acquire_global(fa_ctx *ctx, size_t rounded_bytes, void **out);
 void fa_block_release(fa_ctx *ctx, void *p);            // back to the pool
 void fa_block_free(fa_ctx *ctx, void *p);               // cudaFree now
 int fa_tensor_new(fa_ctx *ctx, int rows, int cols, int storage, bool pooled, fa_tensor **out);
-int fa_scratch(fa_ctx *ctx, void **slot, size_t *slot_bytes, size_t need);
 bool fa_valid(fa_ctx *ctx, const fa_tensor *t);
 bool fa_valid_bytes(fa_ctx *ctx, const fa_bytes *b);
 // f32 device pointer for `t`: the tensor itself when it is f32 storage, else a converted
@@ -142,7 +148,7 @@ struct LaunchScope {
   const char *label;
   LaunchScope(fa_ctx *c, const char *lbl) : ctx(c), label(lbl) {
     ctx->launches++;
-    if (ctx->profiling && (int)ctx->prof.size() < ctx->profile_cap) {
+    if (ctx->profiling && !ctx->capturing && (int)ctx->prof.size() < ctx->profile_cap) {
       if (cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess) {
         rec = true;
         cudaEventRecord(e0, ctx->stream);
@@ -206,6 +212,7 @@ struct TcEpilogue {
   const float *colscale = nullptr;  // [N]
   const float *bias = nullptr;      // [N]
   const float *add = nullptr;       // [M][N]
+  const float *rowbias = nullptr;   // [M] added before the activation
   int act = 0;
 };
 // Packed ("box-contiguous") operand sizes: K is cut in chunks of 128 bytes.

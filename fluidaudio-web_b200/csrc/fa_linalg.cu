@@ -45,6 +45,19 @@ int ensure_nk_i8(fa_ctx *ctx, fa_bytes *wq, int N, int K) {
   return fa_pack_w_i8(ctx, (const int8_t *)wq->dptr, K, N, (int8_t *)wq->nk_i8);
 }
 
+// Per-call scratch: a pool block that goes back to the pool as soon as the consuming kernel is
+// enqueued (reuse is stream-ordered).
+struct Scratch {
+  fa_ctx *ctx;
+  void *p = nullptr;
+  size_t bytes = 0;
+  explicit Scratch(fa_ctx *c) : ctx(c) {}
+  int get(size_t need) { return fa_block_acquire(ctx, need, &p, &bytes); }
+  ~Scratch() {
+    if (p) fa_block_release(ctx, p);
+  }
+};
+
 }  // namespace
 
 extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act,
@@ -69,15 +82,16 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
   const float *biasp = bias ? (const float *)bias->dptr : nullptr;
   const float *addp = add ? (const float *)add->dptr : nullptr;
   if (b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K)) {
+    Scratch sa(ctx);
     rc = ensure_bt_f16(ctx, b);
-    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 2, 1));
-    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)ctx->scratch_a);
+    if (rc == FA_OK) rc = sa.get(fa_tc_act_bytes(M, K, 2, 1));
+    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)sa.p);
     if (rc == FA_OK) {
       TcEpilogue ep;
       ep.bias = biasp;
       ep.add = addp;
       ep.act = act;
-      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);
+      rc = fa_tc_gemm_f16(ctx, (const __half *)sa.p, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {
     rc = fa_simt_gemm(ctx, ap, b->dptr, b->storage == FA_F16 ? 1 : 0, nullptr, biasp, act, addp, (float *)c->dptr, M,
@@ -114,18 +128,18 @@ extern "C" int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, con
   const float *biasp = bias ? (const float *)bias->dptr : nullptr;
   if (tc_shape_ok(ctx, M, N, K)) {
     const int limbs = ctx->int8_limbs;
+    Scratch sa(ctx), ss(ctx);
     rc = ensure_nk_i8(ctx, wq, N, K);  // one-time repack per handle
-    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 1, limbs));
-    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_s, &ctx->scratch_s_bytes, (size_t)M * 4);
-    if (rc == FA_OK)
-      rc = fa_prep_a_i8(ctx, ap, M, K, limbs, (int8_t *)ctx->scratch_a, (float *)ctx->scratch_s);
+    if (rc == FA_OK) rc = sa.get(fa_tc_act_bytes(M, K, 1, limbs));
+    if (rc == FA_OK) rc = ss.get((size_t)M * 4);
+    if (rc == FA_OK) rc = fa_prep_a_i8(ctx, ap, M, K, limbs, (int8_t *)sa.p, (float *)ss.p);
     if (rc == FA_OK) {
       TcEpilogue ep;
-      ep.rowscale = (const float *)ctx->scratch_s;
+      ep.rowscale = (const float *)ss.p;
       ep.colscale = (const float *)scale->dptr;
       ep.bias = biasp;
       ep.act = act;
-      rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, limbs, (const int8_t *)wq->nk_i8, c->dptr, false, M, N, K, ep);
+      rc = fa_tc_gemm_i8(ctx, (const int8_t *)sa.p, limbs, (const int8_t *)wq->nk_i8, c->dptr, false, M, N, K, ep);
     }
   } else {
     rc = fa_simt_gemm(ctx, ap, wq->dptr, 2, (const float *)scale->dptr, biasp, act, nullptr, (float *)c->dptr, M, N, K);
@@ -176,11 +190,12 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
                                  (const uint8_t *)zp->dptr, N, K, nblk, zpb, (__half *)bq->nk_f16);
       }
     }
-    if (rc == FA_OK) rc = fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 2, 1));
-    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)ctx->scratch_a);
+    Scratch sa(ctx);
+    if (rc == FA_OK) rc = sa.get(fa_tc_act_bytes(M, K, 2, 1));
+    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)sa.p);
     if (rc == FA_OK) {
       TcEpilogue ep;
-      rc = fa_tc_gemm_f16(ctx, (const __half *)ctx->scratch_a, (const __half *)bq->nk_f16, (float *)c->dptr, M, N, K, ep);
+      rc = fa_tc_gemm_f16(ctx, (const __half *)sa.p, (const __half *)bq->nk_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {
     rc = fa_simt_nbits(ctx, ap, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr,
@@ -211,14 +226,15 @@ extern "C" int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_by
   size_t raw_bytes = 0;
   FA_TRY(fa_block_acquire(ctx, (size_t)M * K, &raw, &raw_bytes));
   FA_CHECK_CUDA(ctx, cudaMemcpyAsync(raw, aq_host, (size_t)M * K, cudaMemcpyHostToDevice, ctx->stream));
-  FA_TRY(fa_scratch(ctx, &ctx->scratch_a, &ctx->scratch_a_bytes, fa_tc_act_bytes(M, K, 1, 1)));
-  FA_TRY(fa_pack_a_i8_raw(ctx, (const int8_t *)raw, M, K, (int8_t *)ctx->scratch_a));
+  Scratch sa(ctx);
+  FA_TRY(sa.get(fa_tc_act_bytes(M, K, 1, 1)));
+  FA_TRY(fa_pack_a_i8_raw(ctx, (const int8_t *)raw, M, K, (int8_t *)sa.p));
   fa_block_release(ctx, raw);
   void *acc = nullptr;
   size_t got = 0;
   FA_TRY(fa_block_acquire(ctx, (size_t)M * N * 4, &acc, &got));
   TcEpilogue ep;
-  rc = fa_tc_gemm_i8(ctx, (const int8_t *)ctx->scratch_a, 1, (const int8_t *)wq->nk_i8, acc, true, M, N, K, ep);
+  rc = fa_tc_gemm_i8(ctx, (const int8_t *)sa.p, 1, (const int8_t *)wq->nk_i8, acc, true, M, N, K, ep);
   if (rc == FA_OK) {
     cudaError_t e = cudaMemcpyAsync(acc_out_host, acc, (size_t)M * N * 4, cudaMemcpyDeviceToHost, ctx->stream);
     if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "int8GemmI32 readback: %s", cudaGetErrorString(e));

@@ -1,0 +1,168 @@
+"""FastConformer (Parakeet-TDT-0.6B-shaped) encoder forward, op for op the sequence of
+src/engines/asr-parakeet/raw-encoder.js (loadParakeetEncoder :39-161, posEncoding :163-175,
+preEncode :177-222, parakeetEncodeBatch :235-386), written only against ComputeContext members.
+
+Arch: mel[melBins, T] -> dw-striding 8x subsampling (conv2d x5) -> linear -> N x conformer block
+(macaron FF half, rel-pos MHSA, conv module, FF half, LayerNorm).  Folded into weights at load:
+q * 1/sqrt(HD), pos_bias_u/v * 1/sqrt(HD), FF output projections * 0.5.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import numpy as np
+
+
+def infer_config(man: Dict[str, np.ndarray]) -> dict:
+    """raw-encoder.js:28-35: every size is read off the weight shapes."""
+    layers = sum(1 for k in man if k.endswith("_lnff1_w"))
+    D, DFF = man["L0_ff1w1"].shape
+    H, HD = man["L0_pbu"].shape
+    Csub = man["c0w"].shape[0]
+    Fsub = man["linw"].shape[0] // Csub
+    return dict(D=D, DFF=DFF, H=H, HD=HD, layers=layers, dwK=man["L0_dw"].shape[2], Csub=Csub, Fsub=Fsub,
+                melBins=Fsub * 8)
+
+
+def load_encoder(ctx, weights: Dict[str, np.ndarray], cfg_override: Optional[dict] = None) -> dict:
+    """Upload all encoder weights once (raw-encoder.js:39-161).  `weights` holds f32 arrays (already
+    dequantised when the artifact stores int8, :55-76).  Matrices go up as f16 storage (:92-95)."""
+    cfg = {**infer_config(weights), **(cfg_override or {})}
+    HD, D = cfg["HD"], cfg["D"]
+    INV = 1.0 / math.sqrt(HD)
+    f32 = np.float32
+
+    def mat(k, s=None):
+        a = weights[k].astype(f32)
+        if s is not None:
+            a = (a * f32(s)).astype(f32)
+        return ctx.uploadF16(a, a.shape[0], a.shape[1])
+
+    def vec(k, s=None):
+        a = weights[k].astype(f32).reshape(-1)
+        if s is not None:
+            a = (a * f32(s)).astype(f32)
+        return ctx.upload(a, 1, a.size)
+
+    def vec_opt(k, s=None):
+        return vec(k, s) if k in weights else None
+
+    def pwT(k, cout, cin):
+        # pointwise conv weight [cout, cin, 1] as a transposed matrix [cin, cout] (:112-118)
+        w = weights[k].astype(f32).reshape(cout, cin)
+        return ctx.uploadF16(np.ascontiguousarray(w.T), cin, cout)
+
+    sub = dict(conv=[dict(w=vec(f"c{i}w"), b=vec(f"c{i}b")) for i in range(5)], linw=mat("linw"), linb=vec("linb"))
+    layers = []
+    for L in range(cfg["layers"]):
+        g = lambda s: f"L{L}_{s}"
+        layers.append(dict(
+            lnff1=(vec(g("lnff1_w")), vec(g("lnff1_b"))), ff1w1=mat(g("ff1w1")), ff1w2=mat(g("ff1w2"), 0.5),
+            ff1b1=vec_opt(g("ff1b1")), ff1b2=vec_opt(g("ff1b2"), 0.5),
+            lnatt=(vec(g("lnatt_w")), vec(g("lnatt_b"))), q=mat(g("q"), INV), k=mat(g("k")), v=mat(g("v")),
+            pos=mat(g("pos")), out=mat(g("out")), qb=vec_opt(g("qb"), INV), kb=vec_opt(g("kb")), vb=vec_opt(g("vb")),
+            outb=vec_opt(g("outb")), pbuAll=vec(g("pbu"), INV), pbvAll=vec(g("pbv"), INV),
+            lnconv=(vec(g("lnconv_w")), vec(g("lnconv_b"))), pw1T=pwT(g("pw1"), 2 * D, D), dw=vec(g("dw")),
+            dwb=vec(g("dwb")), pw2T=pwT(g("pw2"), D, D), pw1b=vec_opt(g("pw1b")), pw2b=vec_opt(g("pw2b")),
+            lnff2=(vec(g("lnff2_w")), vec(g("lnff2_b"))), ff2w1=mat(g("ff2w1")), ff2w2=mat(g("ff2w2"), 0.5),
+            ff2b1=vec_opt(g("ff2b1")), ff2b2=vec_opt(g("ff2b2"), 0.5), lnout=(vec(g("lnout_w")), vec(g("lnout_b")))))
+    return dict(sub=sub, layers=layers, cfg=cfg, _pe={}, _posProj={})
+
+
+def pos_encoding(Tsub: int, D: int) -> np.ndarray:
+    """raw-encoder.js:163-175 (computed in doubles, stored f32)."""
+    pos = (Tsub - 1 - np.arange(2 * Tsub - 1, dtype=np.float64))[:, None]
+    i = np.arange(0, D, 2, dtype=np.float64)
+    dv = np.exp(i * -(math.log(10000.0) / D))[None, :]
+    pe = np.empty((2 * Tsub - 1, D), np.float32)
+    pe[:, 0::2] = np.sin(pos * dv)
+    pe[:, 1::2] = np.cos(pos * dv)
+    return pe
+
+
+def pre_encode(ctx, enc, mel: np.ndarray):
+    """Subsampling + linear for ONE window: mel [melBins*T] channel-major -> x [Tsub, D] (:177-222)."""
+    cfg = enc["cfg"]
+    Csub, melBins = cfg["Csub"], cfg["melBins"]
+    Tfull = mel.size // melBins
+    x0 = np.ascontiguousarray(mel.reshape(melBins, Tfull).T, dtype=np.float32)  # [T, melBins]
+    s = ctx.upload(x0, 1, Tfull * melBins)
+    Hh, Wd = Tfull, melBins
+    conv = [(Csub, 1, 3, 2, 1, "relu", True), (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False),
+            (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False)]
+    for i, (cout, cin, k, st, gr, act, s2) in enumerate(conv):
+        p = 1 if s2 else 0
+        s = ctx.conv2d(s, enc["sub"]["conv"][i]["w"], dict(cout=cout, cin=cin, h=Hh, w=Wd, kh=k, kw=k,
+                                                          bias=enc["sub"]["conv"][i]["b"], strideH=st, strideW=st,
+                                                          padTop=p, padBottom=p, padLeft=p, padRight=p, groups=gr, act=act))
+        Hh = (Hh + 2 * p - k) // st + 1
+        Wd = (Wd + 2 * p - k) // st + 1
+    flat = ctx.subReshape(s, Csub, Hh, Wd)
+    return ctx.matmul(flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
+
+
+def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None):
+    """W same-length windows concatenated along rows (:235-386): GEMMs see M = W*Tsub, attention and the
+    depthwise conv stay per window.  Returns (frames [W*Tsub, D], Tsub)."""
+    cfg = enc["cfg"]
+    D, H, HD, LAYERS, dwK = cfg["D"], cfg["H"], cfg["HD"], cfg["layers"], cfg["dwK"]
+    ln = lambda x, lp: ctx.layernorm(x, lp[0], lp[1])
+    W = len(mels)
+    pre = [pre_encode(ctx, enc, m) for m in mels]
+    Tsub = pre[0][1]
+    if any(p[1] != Tsub for p in pre):
+        raise ValueError("encode_batch: windows must have equal Tsub")
+    x = pre[0][0] if W == 1 else ctx.concatRows([p[0] for p in pre])
+    peT = enc["_pe"].get(Tsub)
+    if peT is None:
+        peT = ctx.upload(pos_encoding(Tsub, D), 2 * Tsub - 1, D)
+        enc["_pe"][Tsub] = peT
+    dwPadL = dwPadR = (dwK - 1) >> 1
+
+    def ff(x, lp, w1, w2, b1, b2):
+        return ctx.matmul(ctx.matmul(ln(x, lp), w1, dict(bias=b1, act="silu")), w2, dict(bias=b2, add=x))
+
+    def body():
+        nonlocal x
+        for L in range(LAYERS):
+            layerArena = ctx.pushArena()
+            try:
+                w = enc["layers"][L]
+                x = ff(x, w["lnff1"], w["ff1w1"], w["ff1w2"], w["ff1b1"], w["ff1b2"])
+                xln = ln(x, w["lnatt"])
+                q = ctx.matmul(xln, w["q"], dict(bias=w["qb"]))
+                k = ctx.matmul(xln, w["k"], dict(bias=w["kb"]))
+                v = ctx.matmul(xln, w["v"], dict(bias=w["vb"]))
+                if W > 1:  # pos projection is constant per (layer, Tsub): cached across groups (:307-317)
+                    p = enc["_posProj"].get((L, Tsub))
+                    if p is None:
+                        p = ctx.pin(ctx.matmul(peT, w["pos"]))
+                        enc["_posProj"][(L, Tsub)] = p
+                else:
+                    p = ctx.matmul(peT, w["pos"])
+                ac = ctx.bmmQK(q, k, w["pbuAll"], H, HD, W)
+                bd = ctx.relShiftB(ctx.bmmQK(q, p, w["pbvAll"], H, HD, W, True), W * H)
+                probs = ctx.softmax(ctx.add(ac, bd))
+                outc = ctx.bmmPV(probs, v, H, HD, W)
+                x = ctx.matmul(outc, w["out"], dict(bias=w["outb"], add=x))
+                pre1 = ctx.matmul(ln(x, w["lnconv"]), w["pw1T"], dict(bias=w["pw1b"]))  # [W*T, 2D]
+                glu = ctx.glu(ctx.transpose(pre1))  # [D, W*T]
+                opts = dict(cout=D, k=dwK, groups=D, padLeft=dwPadL, padRight=dwPadR, bias=w["dwb"], act="silu")
+                if W == 1:
+                    dwo = ctx.conv1d(glu, w["dw"], opts)
+                else:  # depthwise conv is over time -> per window (:343-351)
+                    dwo = ctx.alloc(D, W * Tsub)
+                    for wi in range(W):
+                        ctx.setCols(dwo, ctx.conv1d(ctx.sliceCols(glu, wi * Tsub, Tsub), w["dw"], opts), wi * Tsub)
+                x = ctx.matmul(ctx.transpose(dwo), w["pw2T"], dict(bias=w["pw2b"], add=x))
+                x = ff(x, w["lnff2"], w["ff2w1"], w["ff2w2"], w["ff2b1"], w["ff2b2"])
+                x = ln(x, w["lnout"])
+                ctx.pin(x, True)  # x feeds the next layer: promote to the enclosing arena
+                if layer_hook is not None:
+                    layer_hook(L, x)
+            finally:
+                ctx.popArena(layerArena)
+        return x
+
+    return ctx.withBatchSync(body), Tsub

@@ -33,6 +33,7 @@ typedef struct fa_ctx fa_ctx;       /* one ComputeContext (compute.d.ts:106) */
 typedef struct fa_tensor fa_tensor; /* Tensor {rows, cols}, storage opaque (compute.d.ts:12-15) */
 typedef struct fa_bytes fa_bytes;   /* PackedBytes from uploadBytes (compute.d.ts:34) */
 typedef struct fa_staged fa_staged; /* StagedRead, single use (compute.d.ts:39-45) */
+typedef struct fa_graph fa_graph;   /* a recorded batch that can be submitted repeatedly */
 
 enum {
   FA_OK = 0,
@@ -96,6 +97,18 @@ int fa_rows_view(fa_ctx *ctx, fa_tensor *t, int rows, fa_tensor **out);     /* r
 /* ---- batching (compute.d.ts:147-151) --------------------------------------- */
 int fa_begin_batch(fa_ctx *ctx); /* beginBatch :148; nested call fails like scheduler.js:20 */
 int fa_end_batch(fa_ctx *ctx);   /* endBatch :149 */
+
+/* Recorded batches.  The reference records a whole forward into ONE command buffer and submits it once
+ * (withBatchSync, src/gpu/scheduler.js:17-60; src/engines/asr-parakeet/raw-encoder.js:288-291).  The CUDA
+ * form is a graph: ops enqueued between fa_graph_begin and fa_graph_end are captured instead of run, and
+ * fa_graph_launch replays them with one submission.  Rules: no download/sync/staged read while recording;
+ * uploads inside a recording must come from fa_host_alloc memory (replays re-read that memory);
+ * device blocks touched by the recording stay reserved for the graph until fa_graph_free, so tensors made
+ * inside it (its outputs) stay valid across replays. */
+int fa_graph_begin(fa_ctx *ctx);
+int fa_graph_end(fa_ctx *ctx, fa_graph **out);
+int fa_graph_launch(fa_ctx *ctx, fa_graph *g);
+int fa_graph_free(fa_ctx *ctx, fa_graph *g);
 
 /* ---- linear algebra: the hot path (compute.d.ts:153-168) ------------------- */
 /* matmul :155, and matmulV2/V3/V4/F16 :158-162 (one shape-routed implementation):

@@ -161,8 +161,40 @@ class WasmOracle:
     def ensureTensor(self, t):
         return t if isinstance(t, T) else self.upload(t["data"], t["rows"], t["cols"])
 
+    # arenas / batching are GPU-pool concepts: inert on the CPU twin (:104-123)
+    def destroy(self):
+        pass
+
+    def beginBatch(self):
+        pass
+
+    def endBatch(self):
+        pass
+
+    def withBatchSync(self, fn):
+        return fn()
+
+    withBatch = withBatchSync
+
+    def pushArena(self):
+        return []
+
+    def popArena(self, handle=None):
+        pass
+
+    def trimPool(self, budget=0):
+        pass
+
+    def pin(self, t, toParent=False):
+        return t
+
+    def freeTensor(self, t):
+        pass
+
     # -- hot kernels (:135-213) ----------------------------------------------------
-    def matmul(self, a, b, bias=None, act="none", add=None):
+    def matmul(self, a, b, opts=None, bias=None, act="none", add=None):
+        if opts:
+            bias, act, add = opts.get("bias", bias), opts.get("act", act) or "none", opts.get("add", add)
         M, K, N = a.rows, a.cols, b.cols
         assert b.rows == K
         out = np.empty(M * N, np.float32)
@@ -173,8 +205,8 @@ class WasmOracle:
             LIB.js_residual_add(_f(out), _f(add.data), M * N)
         return T(out, M, N)
 
-    def matmulV2(self, a, b, bias=None, act="none"):
-        return self.matmul(a, b, bias=bias, act=act)
+    def matmulV2(self, a, b, opts=None, bias=None, act="none"):
+        return self.matmul(a, b, opts, bias=bias, act=act)
 
     matmulV3 = matmulV4 = matmulF16 = matmulV2
 
@@ -197,8 +229,13 @@ class WasmOracle:
         return T(out, M, N)
 
     # -- conv (:220-264 grouped path, :632-685) --------------------------------------
-    def conv1d(self, x, w, cout, k, bias=None, stride=1, pad=0, padLeft=None, padRight=None, dilation=1, groups=1,
-               act="none"):
+    def conv1d(self, x, w, opts=None, cout=None, k=None, bias=None, stride=1, pad=0, padLeft=None, padRight=None,
+               dilation=1, groups=1, act="none"):
+        if opts:
+            cout, k, bias = opts.get("cout", cout), opts.get("k", k), opts.get("bias", bias)
+            stride, pad, dilation = opts.get("stride", stride), opts.get("pad", pad), opts.get("dilation", dilation)
+            padLeft, padRight = opts.get("padLeft", padLeft), opts.get("padRight", padRight)
+            groups, act = opts.get("groups", groups), opts.get("act", act) or "none"
         padLeft = pad if padLeft is None else padLeft
         padRight = pad if padRight is None else padRight
         Cin, L = x.rows, x.cols
@@ -222,8 +259,17 @@ class WasmOracle:
         LIB.js_bias_act_rows(_f(out), cout, Lout, _f(bias.data) if bias is not None else None, ACT[act])
         return T(out, cout, Lout)
 
-    def conv2d(self, x, w, cout, cin, h, w_, kh, kw, bias=None, strideH=1, strideW=1, padH=0, padW=0, padTop=None,
-               padBottom=None, padLeft=None, padRight=None, groups=1, act="none"):
+    def conv2d(self, x, w, opts=None, cin=None, h=None, w_=None, kh=None, kw=None, bias=None, strideH=1, strideW=1,
+               padH=0, padW=0, padTop=None, padBottom=None, padLeft=None, padRight=None, groups=1, act="none", cout=None):
+        if isinstance(opts, dict):  # JS-style options object (:632-654)
+            o = opts
+            cout, cin, h, w_, kh, kw = o["cout"], o["cin"], o["h"], o["w"], o["kh"], o["kw"]
+            bias, strideH, strideW = o.get("bias"), o.get("strideH", 1), o.get("strideW", 1)
+            padH, padW = o.get("padH", 0), o.get("padW", 0)
+            padTop, padBottom, padLeft, padRight = o.get("padTop"), o.get("padBottom"), o.get("padLeft"), o.get("padRight")
+            groups, act = o.get("groups", 1), o.get("act", "none") or "none"
+        elif opts is not None:
+            cout = opts  # positional form: conv2d(x, w, cout, cin, h, w, kh, kw, ...)
         padTop = padH if padTop is None else padTop
         padBottom = padH if padBottom is None else padBottom
         padLeft = padW if padLeft is None else padLeft

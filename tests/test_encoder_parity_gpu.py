@@ -1,0 +1,60 @@
+"""FastConformer encoder forward on the CUDA backend against the same forward on the CPU oracle
+(the reference gate for this is scripts/backend-parity.mjs:57-67, WebGPU vs WASM maxΔ < 2e-3 on real
+weights).  Random-init stacks amplify rounding differences layer over layer (docs/ORT_REMOVAL.md:121-128),
+so the full-size check is teacher-forced per layer: every layer starts from the oracle's input."""
+import numpy as np
+import pytest
+
+from oracle.wasm_oracle import T, WasmOracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _eng():
+    from fluidaudio_web_b200.engines import fastconformer, synth
+
+    return fastconformer, synth
+
+
+def test_tiny_encoder_end_to_end(ctx, pkg):
+    fc, synth = _eng()
+    w = synth.encoder_weights(synth.TINY, seed=3)
+    mels = [synth.log_mel(a, 32).reshape(-1) for a in synth.synth_audio(3, samples=16000 * 2, seed=3)]
+    ora = WasmOracle(threads=True)
+    ref, Tsub = fc.encode_batch(ora, fc.load_encoder(ora, w), mels)
+    h = ctx.pushArena()
+    got, Tsub2 = fc.encode_batch(ctx, fc.load_encoder(ctx, w), mels)
+    out = ctx.download(got).reshape(ref.rows, ref.cols)
+    ctx.popArena(h)
+    assert Tsub == Tsub2 and (got.rows, got.cols) == (ref.rows, ref.cols)
+    # two layers, f16 weights on the device vs f32 on the oracle; outputs are LayerNorm'ed (unit scale)
+    assert np.abs(out - ref.array()).max() <= 2e-2
+
+
+def test_full_width_layer_teacher_forced(ctx, pkg):
+    """One real-size conformer block (D=1024, DFF=4096, 8 heads of 128) on 2 windows of 188 frames."""
+    fc, synth = _eng()
+    cfg = dict(synth.PARAKEET_06B, layers=1)
+    w = synth.encoder_weights(cfg, seed=3)
+    rng = np.random.default_rng(3)
+    Wn, Tsub, D = 2, 188, 1024
+    x0 = rng.standard_normal((Wn * Tsub, D)).astype(np.float32)
+
+    def run_layer(c):
+        enc = fc.load_encoder(c, w)
+        # drive the block directly from a given residual stream: reuse encode_batch's body through a
+        # stand-in pre-encode (the subsampling front end is covered by the tiny end-to-end case)
+        orig = fc.pre_encode
+        fc.pre_encode = lambda c_, e_, m_: (c_.upload(m_, Tsub, D), Tsub)
+        try:
+            out, _ = fc.encode_batch(c, enc, [x0[i * Tsub:(i + 1) * Tsub] for i in range(Wn)])
+        finally:
+            fc.pre_encode = orig
+        return out
+
+    ora = WasmOracle(threads=True)
+    ref = run_layer(ora).array()
+    h = ctx.pushArena()
+    got = ctx.download(run_layer(ctx)).reshape(ref.shape)
+    ctx.popArena(h)
+    assert np.abs(got - ref).max() <= 2e-2

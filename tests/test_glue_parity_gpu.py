@@ -1,0 +1,114 @@
+"""Glue ops (what the encoder/decoder forwards call between GEMMs) against the CPU oracle, through the
+C ABI.  Tolerances follow scripts/backend-conformance.mjs (1e-4 for normalisation/elementwise, 1e-3 for
+the attention products and convolutions)."""
+import numpy as np
+import pytest
+
+from oracle.wasm_oracle import T, WasmOracle
+
+pytestmark = pytest.mark.gpu
+
+ORA = WasmOracle()
+
+
+def up(ctx, a):
+    a = np.ascontiguousarray(a, np.float32)
+    r, c = (1, a.size) if a.ndim == 1 else a.shape
+    return ctx.upload(a, r, c), T(a, r, c)
+
+
+def close(ctx, got, ref, tol):
+    g = ctx.download(got).reshape(ref.rows, ref.cols)
+    assert (got.rows, got.cols) == (ref.rows, ref.cols)
+    assert np.abs(g - ref.array()).max() <= tol
+
+
+def test_layernorm_softmax(ctx):
+    rng = np.random.default_rng(0)
+    for R, C in [(7, 33), (64, 1024), (3, 1500)]:
+        x, xo = up(ctx, rng.standard_normal((R, C)) * 3)
+        g, go = up(ctx, rng.standard_normal(C))
+        b, bo = up(ctx, rng.standard_normal(C))
+        close(ctx, ctx.layernorm(x, g, b), ORA.layernorm(xo, go, bo), 1e-4)
+        close(ctx, ctx.softmax(x), ORA.softmax(xo), 1e-5)
+
+
+def test_elementwise_and_movement(ctx):
+    rng = np.random.default_rng(1)
+    a, ao = up(ctx, rng.standard_normal((37, 50)))
+    b, bo = up(ctx, rng.standard_normal((37, 50)))
+    r, ro = up(ctx, rng.standard_normal(50))
+    close(ctx, ctx.add(a, b), ORA.add(ao, bo), 0)
+    close(ctx, ctx.mul(a, r), ORA.mul(ao, ro), 0)  # row broadcast
+    close(ctx, ctx.scale(a, 0.37), ORA.scale(ao, 0.37), 1e-6)
+    close(ctx, ctx.silu(a), ORA.silu(ao), 1e-5)
+    close(ctx, ctx.relu(a), ORA.relu(ao), 0)
+    close(ctx, ctx.transpose(a), ORA.transpose(ao), 0)
+    close(ctx, ctx.sliceCols(a, 7, 20), ORA.sliceCols(ao, 7, 20), 0)
+    close(ctx, ctx.sliceRows(a, 5, 9), ORA.sliceRows(ao, 5, 9), 0)
+    g, go = up(ctx, rng.standard_normal((64, 41)))
+    close(ctx, ctx.glu(g), ORA.glu(go), 1e-5)
+    d, do = up(ctx, np.zeros((37, 80)))
+    close(ctx, ctx.setCols(d, a, 11), ORA.setCols(do, ao, 11), 0)
+    c1, c1o = up(ctx, rng.standard_normal((3, 9)))
+    c2, c2o = up(ctx, rng.standard_normal((5, 9)))
+    close(ctx, ctx.concatRows([c1, c2]), ORA.concatRows([c1o, c2o]), 0)
+    dst, dsto = up(ctx, np.zeros((10, 9)))
+    close(ctx, ctx.copyRows(dst, c2, 4), ORA.copyRows(dsto, c2o, 4), 0)
+    s, so = up(ctx, rng.standard_normal((6, 4 * 5)))
+    close(ctx, ctx.subReshape(s, 6, 4, 5), ORA.subReshape(so, 6, 4, 5), 0)
+
+
+def test_attention_products_and_rel_shift(ctx):
+    rng = np.random.default_rng(2)
+    W, H, HD, Tq = 3, 4, 32, 19
+    q, qo = up(ctx, rng.standard_normal((W * Tq, H * HD)))
+    k, ko = up(ctx, rng.standard_normal((W * Tq, H * HD)))
+    pb, pbo = up(ctx, rng.standard_normal(H * HD))
+    pos, poso = up(ctx, rng.standard_normal((2 * Tq - 1, H * HD)))
+    ac, aco = ctx.bmmQK(q, k, pb, H, HD, W), ORA.bmmQK(qo, ko, pbo, H, HD, W)
+    close(ctx, ac, aco, 1e-3)
+    bd, bdo = ctx.bmmQK(q, pos, None, H, HD, W, True), ORA.bmmQK(qo, poso, None, H, HD, W, True)
+    close(ctx, bd, bdo, 1e-3)
+    sh, sho = ctx.relShiftB(bd, W * H), ORA.relShiftB(bdo, W * H)
+    close(ctx, sh, sho, 1e-3)
+    p, po = ctx.softmax(ctx.add(ac, sh)), ORA.softmax(ORA.add(aco, sho))
+    close(ctx, ctx.bmmPV(p, k, H, HD, W), ORA.bmmPV(po, ko, H, HD, W), 1e-3)
+
+
+def test_convolutions(ctx):
+    rng = np.random.default_rng(3)
+    # depthwise conv over time with fused silu (the conformer conv module)
+    Cc, L, k = 48, 77, 9
+    x, xo = up(ctx, rng.standard_normal((Cc, L)))
+    w, wo = up(ctx, rng.standard_normal(Cc * k))
+    b, bo = up(ctx, rng.standard_normal(Cc))
+    close(ctx, ctx.conv1d(x, w, cout=Cc, k=k, groups=Cc, padLeft=4, padRight=4, bias=b, act="silu"),
+          ORA.conv1d(xo, wo, cout=Cc, k=k, groups=Cc, padLeft=4, padRight=4, bias=bo, act="silu"), 1e-4)
+    # subsampling convs: cin=1 3x3 s2, depthwise 3x3 s2, pointwise
+    h, wd, C0 = 41, 24, 16
+    img, imgo = up(ctx, rng.standard_normal((1, h * wd)))
+    w0, w0o = up(ctx, rng.standard_normal(C0 * 9))
+    b0, b0o = up(ctx, rng.standard_normal(C0))
+    o = dict(cout=C0, cin=1, h=h, w=wd, kh=3, kw=3, strideH=2, strideW=2, padTop=1, padBottom=1, padLeft=1, padRight=1, act="relu")
+    y = ctx.conv2d(img, w0, dict(o, bias=b0))
+    yo = ORA.conv2d(imgo, w0o, C0, 1, h, wd, 3, 3, bias=b0o, strideH=2, strideW=2, padTop=1, padBottom=1, padLeft=1, padRight=1, act="relu")
+    close(ctx, y, yo, 1e-4)
+    h2, w2 = (h + 2 - 3) // 2 + 1, (wd + 2 - 3) // 2 + 1
+    wd_, wdo = up(ctx, rng.standard_normal(C0 * 9))
+    y2 = ctx.conv2d(y, wd_, cout=C0, cin=C0, h=h2, w=w2, kh=3, kw=3, strideH=2, strideW=2, padTop=1, padBottom=1, padLeft=1, padRight=1, groups=C0)
+    y2o = ORA.conv2d(yo, wdo, C0, C0, h2, w2, 3, 3, strideH=2, strideW=2, padTop=1, padBottom=1, padLeft=1, padRight=1, groups=C0)
+    close(ctx, y2, y2o, 1e-4)
+    h3, w3 = (h2 + 2 - 3) // 2 + 1, (w2 + 2 - 3) // 2 + 1
+    wp, wpo = up(ctx, rng.standard_normal(C0 * C0))
+    close(ctx, ctx.conv2d(y2, wp, cout=C0, cin=C0, h=h3, w=w3, kh=1, kw=1, act="relu"),
+          ORA.conv2d(y2o, wpo, C0, C0, h3, w3, 1, 1, act="relu"), 1e-4)
+
+
+def test_argmax_rows(ctx):
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((5, 51868)).astype(np.float32)
+    x[2, 100] = x[2, 40000] = 50.0  # tie -> lowest index
+    out = ctx.download(ctx.argmaxRowsIndex(ctx.upload(x, 5, 51868))).reshape(5, 2)
+    assert np.array_equal(out[:, 0].astype(np.int64), x.argmax(axis=1))
+    assert np.array_equal(out[:, 1], x.max(axis=1))
