@@ -392,7 +392,7 @@ class Encoder:
 
 
 WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "encoder": Encoder}
-DEFAULT_WORKLOAD = "int4_decode"
+DEFAULT_WORKLOAD = "encoder"
 
 
 # --------------------------------------------------------------------------------------------

@@ -62,6 +62,7 @@ SIGNATURES = {
     "fa_layernorm": [P, P, P, P, C.c_float, PP],
     "fa_softmax": [P, P, PP],
     "fa_conv1d": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
+    "fa_conv1d_windows": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
     "fa_conv2d": [P, P, P, P] + [I] * 14 + [PP],
     "fa_bmm_qk": [P, P, P, P, I, I, I, I, PP],
     "fa_bmm_pv": [P, P, P, I, I, I, PP],

@@ -280,6 +280,15 @@ class CudaContext:
         return self._op(self._lib.fa_conv1d, x.h, w.h, self._h_of(bias), cout, k, stride, padLeft, padRight, dilation,
                         groups, ACT[act])
 
+    def conv1dWindows(self, x, w, opts: dict, windows: int) -> Tensor:
+        """conv1d over `windows` independent equal-length column blocks of x in one launch (optional fast
+        path for the per-window sliceCols/conv1d/setCols loop of raw-encoder.js:343-351)."""
+        pl = opts.get("padLeft", opts.get("pad", 0))
+        pr = opts.get("padRight", opts.get("pad", 0))
+        assert opts.get("stride", 1) == 1
+        return self._op(self._lib.fa_conv1d_windows, x.h, w.h, self._h_of(opts.get("bias")), opts["cout"], opts["k"], pl, pr,
+                        opts.get("dilation", 1), opts.get("groups", 1), ACT[opts.get("act", "none")], windows)
+
     def conv2d(self, x, weight, opts: Optional[dict] = None, **kw) -> Tensor:
         o = dict(opts or {})
         o.update(kw)

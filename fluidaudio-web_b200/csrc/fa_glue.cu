@@ -138,90 +138,126 @@ __global__ void k_rel_shift_b(const float *__restrict__ x, float *__restrict__ y
   }
 }
 
-// Batched QK^T (wasm-context.js:462-482): one (w,h) per blockIdx.z, 32x32 output tile per CTA.
+// Batched QK^T (wasm-context.js:462-482): one (w,h) per blockIdx.z, 64x64 output tile per CTA,
+// 4x4 outputs per thread, HD consumed in slices of 16 through shared memory.
 // out[((w*H+h)*T+i)*Tb + j] = sum_d (q[(w*T+i)*S + h*HD + d] + qb[h*HD+d]) * b[brow(j)*S + h*HD + d]
 __global__ void __launch_bounds__(256) k_bmm_qk(const float *__restrict__ q, const float *__restrict__ b,
                                                 const float *__restrict__ qb, float *__restrict__ out, int T, int Tb,
                                                 int H, int HD, int bShared) {
-  __shared__ float Qs[32][33], Bs[32][33];
+  __shared__ __align__(16) float Qs[16][68], Bs[16][68];
   const int w = blockIdx.z / H, h = blockIdx.z % H, S = H * HD;
-  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 rows of threads
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int d0 = 0; d0 < HD; d0 += 32) {
-    for (int r = ty; r < 32; r += 8) {
-      int d = d0 + tx;
-      int i = i0 + r, j = j0 + r;
+  const int i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const float *qbase = q + (size_t)w * T * S + h * HD;
+  const float *bbase = b + (size_t)(bShared ? 0 : w) * Tb * S + h * HD;
+  float acc[4][4] = {};
+  for (int d0 = 0; d0 < HD; d0 += 16) {
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+      const int e = threadIdx.x + 256 * s, r = e >> 4, dd = e & 15, d = d0 + dd;
       float qv = 0.f, bv = 0.f;
       if (d < HD) {
-        if (i < T) qv = q[((size_t)w * T + i) * S + h * HD + d] + (qb ? qb[h * HD + d] : 0.f);
-        if (j < Tb) bv = b[((size_t)(bShared ? 0 : w) * Tb + j) * S + h * HD + d];
+        if (i0 + r < T) qv = qbase[(size_t)(i0 + r) * S + d] + (qb ? qb[h * HD + d] : 0.f);
+        if (j0 + r < Tb) bv = bbase[(size_t)(j0 + r) * S + d];
       }
-      Qs[r][tx] = qv;
-      Bs[r][tx] = bv;
+      Qs[dd][r] = qv;
+      Bs[dd][r] = bv;
     }
     __syncthreads();
 #pragma unroll
-    for (int d = 0; d < 32; d++) {
-      float bv = Bs[tx][d];
+    for (int d = 0; d < 16; d++) {
+      const float4 a4 = *(const float4 *)&Qs[d][ty * 4];
+      const float4 b4 = *(const float4 *)&Bs[d][tx * 4];
+      const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-      for (int u = 0; u < 4; u++) acc[u] = fmaf(Qs[ty + 8 * u][d], bv, acc[u]);
+      for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int v = 0; v < 4; v++) acc[u][v] = fmaf(av[u], bv[v], acc[u][v]);
     }
     __syncthreads();
   }
+  float *obase = out + ((size_t)w * H + h) * T * Tb;
 #pragma unroll
   for (int u = 0; u < 4; u++) {
-    int i = i0 + ty + 8 * u, j = j0 + tx;
-    if (i < T && j < Tb) out[(((size_t)w * H + h) * T + i) * Tb + j] = acc[u];
+    const int i = i0 + ty * 4 + u;
+    if (i >= T) continue;
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+      const int j = j0 + tx * 4 + v;
+      if (j < Tb) obase[(size_t)i * Tb + j] = acc[u][v];
+    }
   }
 }
 
-// Batched P@V (wasm-context.js:484-500): out[(w*Tq+i)*S + h*HD + d] = sum_j p[((w*H+h)*Tq+i)*Tk + j] * v[(w*Tk+j)*S + h*HD + d]
+// Batched P@V (wasm-context.js:484-500), 64 (rows i) x 64 (head dims d) per CTA, keys in slices of 16:
+// out[(w*Tq+i)*S + h*HD + d] = sum_j p[((w*H+h)*Tq+i)*Tk + j] * v[(w*Tk+j)*S + h*HD + d]
 __global__ void __launch_bounds__(256) k_bmm_pv(const float *__restrict__ p, const float *__restrict__ v,
                                                 float *__restrict__ out, int Tq, int Tk, int H, int HD) {
-  __shared__ float Ps[32][33], Vs[32][33];
+  __shared__ __align__(16) float Ps[16][68], Vs[16][68];
   const int w = blockIdx.z / H, h = blockIdx.z % H, S = H * HD;
-  const int i0 = blockIdx.y * 32, d0 = blockIdx.x * 32;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int j0 = 0; j0 < Tk; j0 += 32) {
-    for (int r = ty; r < 32; r += 8) {
-      int i = i0 + r, jc = j0 + tx;
-      Ps[r][tx] = (i < Tq && jc < Tk) ? p[(((size_t)w * H + h) * Tq + i) * Tk + jc] : 0.f;
-      int jr = j0 + r, d = d0 + tx;
-      Vs[r][tx] = (jr < Tk && d < HD) ? v[((size_t)w * Tk + jr) * S + h * HD + d] : 0.f;
+  const int i0 = blockIdx.y * 64, d0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const float *pbase = p + ((size_t)w * H + h) * Tq * Tk;
+  const float *vbase = v + (size_t)w * Tk * S + h * HD;
+  float acc[4][4] = {};
+  for (int j0 = 0; j0 < Tk; j0 += 16) {
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+      const int e = threadIdx.x + 256 * s;
+      {  // P tile: 64 rows x 16 keys, keys fastest in memory
+        const int r = e >> 4, jj = e & 15;
+        Ps[jj][r] = (i0 + r < Tq && j0 + jj < Tk) ? pbase[(size_t)(i0 + r) * Tk + j0 + jj] : 0.f;
+      }
+      {  // V tile: 16 keys x 64 dims, dims fastest in memory
+        const int jj = e >> 6, dd = e & 63;
+        Vs[jj][dd] = (j0 + jj < Tk && d0 + dd < HD) ? vbase[(size_t)(j0 + jj) * S + d0 + dd] : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-      float vv = Vs[j][tx];
+    for (int j = 0; j < 16; j++) {
+      const float4 a4 = *(const float4 *)&Ps[j][ty * 4];
+      const float4 b4 = *(const float4 *)&Vs[j][tx * 4];
+      const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-      for (int u = 0; u < 4; u++) acc[u] = fmaf(Ps[ty + 8 * u][j], vv, acc[u]);
+      for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[u][c] = fmaf(av[u], bv[c], acc[u][c]);
     }
     __syncthreads();
   }
 #pragma unroll
   for (int u = 0; u < 4; u++) {
-    int i = i0 + ty + 8 * u, d = d0 + tx;
-    if (i < Tq && d < HD) out[((size_t)w * Tq + i) * S + h * HD + d] = acc[u];
+    const int i = i0 + ty * 4 + u;
+    if (i >= Tq) continue;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      const int d = d0 + tx * 4 + c;
+      if (d < HD) out[((size_t)w * Tq + i) * S + h * HD + d] = acc[u][c];
+    }
   }
 }
 
 // Direct grouped 1-D conv (rust/wasm-kernels/src/lib.rs:99-138): one thread per output sample.
+// With `Lw` < L the columns are independent windows of Lw samples each (stride 1, same-length
+// output): taps never cross a window seam, which is the per-window loop of
+// src/engines/asr-parakeet/raw-encoder.js:343-351 done in one launch.
 __global__ void k_conv1d(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
-                         float *__restrict__ y, int cout, int cin, int L, int Lout, int k, int stride, int padl,
+                         float *__restrict__ y, int cout, int cin, int L, int Lout, int Lw, int k, int stride, int padl,
                          int dil, int groups, int act) {
   const int cin_g = cin / groups, cout_g = cout / groups;
-  size_t n = (size_t)cout * Lout;
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
-    int co = (int)(idx / Lout), t = (int)(idx % Lout), g = co / cout_g;
+  const unsigned n = (unsigned)cout * (unsigned)Lout;
+  for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+    const int co = (int)(idx / (unsigned)Lout), t = (int)(idx % (unsigned)Lout), g = co / cout_g;
+    const int wbase = Lw < L ? (t / Lw) * Lw : 0;   // first column of this sample's window
+    const int tl = t - wbase;
     float acc = 0.f;
     for (int cig = 0; cig < cin_g; cig++) {
-      const float *xr = x + (size_t)(g * cin_g + cig) * L;
+      const float *xr = x + (size_t)(g * cin_g + cig) * L + wbase;
       const float *wr = w + ((size_t)co * cin_g + cig) * k;
       for (int kk = 0; kk < k; kk++) {
-        int xi = t * stride + kk * dil - padl;
-        if (xi >= 0 && xi < L) acc = fmaf(xr[xi], wr[kk], acc);
+        const int xi = tl * stride + kk * dil - padl;
+        if (xi >= 0 && xi < Lw) acc = fmaf(xr[xi], wr[kk], acc);
       }
     }
     if (bias) acc += bias[co];
@@ -234,25 +270,64 @@ __global__ void k_conv2d(const float *__restrict__ x, const float *__restrict__ 
                          float *__restrict__ y, int cout, int cin, int h, int W, int kh, int kw, int sh, int sw, int pt,
                          int pl, int Ho, int Wo, int groups, int act) {
   const int cinG = cin / groups, coutG = cout / groups;
-  size_t n = (size_t)cout * Ho * Wo;
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
-    int wo = (int)(idx % Wo), ho = (int)((idx / Wo) % Ho), co = (int)(idx / ((size_t)Wo * Ho));
-    int g = co / coutG;
+  const unsigned plane = (unsigned)Ho * (unsigned)Wo, n = (unsigned)cout * plane;
+  for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+    const int co = (int)(idx / plane);
+    const unsigned rem = idx - (unsigned)co * plane;
+    const int ho = (int)(rem / (unsigned)Wo), wo = (int)(rem % (unsigned)Wo);
+    const int g = co / coutG;
     float acc = bias ? bias[co] : 0.f;
     for (int ci = 0; ci < cinG; ci++) {
       const float *xp = x + (size_t)(g * cinG + ci) * h * W;
       const float *wp = w + ((size_t)co * cinG + ci) * kh * kw;
       for (int a = 0; a < kh; a++) {
-        int hi = ho * sh + a - pt;
+        const int hi = ho * sh + a - pt;
         if (hi < 0 || hi >= h) continue;
         for (int b = 0; b < kw; b++) {
-          int wi = wo * sw + b - pl;
+          const int wi = wo * sw + b - pl;
           if (wi < 0 || wi >= W) continue;
           acc = fmaf(xp[(size_t)hi * W + wi], wp[a * kw + b], acc);
         }
       }
     }
     y[idx] = fa_actf(acc, act);
+  }
+}
+
+// Single-input-channel 3x3 conv (the first subsampling layer; the reference has the same special
+// case, src/gpu/kernels/convolution.js:112-147): a thread reads its 9 taps once and produces 32
+// output channels, lanes walking consecutive output positions so every channel's store is coalesced.
+__global__ void __launch_bounds__(256) k_conv2d_c1_3x3(const float *__restrict__ x, const float *__restrict__ w,
+                                                       const float *__restrict__ bias, float *__restrict__ y, int cout,
+                                                       int h, int W, int sh, int sw, int pt, int pl, int Ho, int Wo,
+                                                       int act) {
+  __shared__ float ws[32][9], bs[32];
+  const int co0 = blockIdx.y * 32;
+  for (int e = threadIdx.x; e < 32 * 9; e += 256) {
+    const int c = e / 9;
+    ws[c][e % 9] = co0 + c < cout ? w[(size_t)(co0 + c) * 9 + e % 9] : 0.f;
+  }
+  if (threadIdx.x < 32) bs[threadIdx.x] = (bias && co0 + threadIdx.x < cout) ? bias[co0 + threadIdx.x] : 0.f;
+  __syncthreads();
+  const unsigned plane = (unsigned)Ho * (unsigned)Wo;
+  for (unsigned pos = blockIdx.x * 256 + threadIdx.x; pos < plane; pos += gridDim.x * 256) {
+    const int ho = (int)(pos / (unsigned)Wo), wo = (int)(pos % (unsigned)Wo);
+    float in[9];
+#pragma unroll
+    for (int a = 0; a < 3; a++)
+#pragma unroll
+      for (int b = 0; b < 3; b++) {
+        const int hi = ho * sh + a - pt, wi = wo * sw + b - pl;
+        in[a * 3 + b] = (hi >= 0 && hi < h && wi >= 0 && wi < W) ? x[(size_t)hi * W + wi] : 0.f;
+      }
+#pragma unroll 4
+    for (int c = 0; c < 32; c++) {
+      if (co0 + c >= cout) break;
+      float acc = bs[c];
+#pragma unroll
+      for (int t = 0; t < 9; t++) acc = fmaf(in[t], ws[c][t], acc);
+      y[(size_t)(co0 + c) * plane + pos] = fa_actf(acc, act);
+    }
   }
 }
 
@@ -580,7 +655,7 @@ extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, co
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, W * H * T, Tb, FA_F32, true, &y));
   if (T && Tb) {
-    dim3 grid(ceil_div(Tb, 32), ceil_div(T, 32), W * H);
+    dim3 grid(ceil_div(Tb, 64), ceil_div(T, 64), W * H);
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmQK: batch too large");
     {
       LaunchScope ls(ctx, "bmm_qk");
@@ -605,7 +680,7 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, W * Tq, H * HD, FA_F32, true, &y));
   if (Tq && Tk) {
-    dim3 grid(ceil_div(HD, 32), ceil_div(Tq, 32), W * H);
+    dim3 grid(ceil_div(HD, 64), ceil_div(Tq, 64), W * H);
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmPV: batch too large");
     {
       LaunchScope ls(ctx, "bmm_pv");
@@ -617,9 +692,11 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
   return FA_OK;
 }
 
-extern "C" int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k,
-                         int stride, int pad_left, int pad_right, int dilation, int groups, int act, fa_tensor **out) {
-  GLUE_PROLOGUE("conv1d");
+static int conv1d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k,
+                       int stride, int pad_left, int pad_right, int dilation, int groups, int act, int windows,
+                       fa_tensor **out) {
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "conv1d: NULL argument");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
   FA_TRY(need_f32(ctx, x, "conv1d"));
   FA_TRY(need_f32(ctx, w, "conv1d"));
   if (bias) FA_TRY(need_f32(ctx, bias, "conv1d"));
@@ -628,20 +705,37 @@ extern "C" int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
              "conv1d: bad geometry cout=%d k=%d stride=%d dilation=%d groups=%d cin=%d", cout, k, stride, dilation, groups, cin);
   FA_REQUIRE(ctx, (long long)w->rows * w->cols >= (long long)cout * (cin / groups) * k, "conv1d: weight tensor too small");
   if (bias) FA_REQUIRE(ctx, bias->rows * bias->cols >= cout, "conv1d: bias shorter than cout");
-  const int Lout = (L + pad_left + pad_right - dilation * (k - 1) - 1) / stride + 1;
-  FA_REQUIRE(ctx, Lout > 0, "conv1d: empty output (L=%d)", L);
+  FA_REQUIRE(ctx, windows >= 1 && L % windows == 0, "conv1d: %d columns do not split into %d windows", L, windows);
+  const int Lw = L / windows;
+  const int Lout_w = (Lw + pad_left + pad_right - dilation * (k - 1) - 1) / stride + 1;
+  FA_REQUIRE(ctx, Lout_w > 0, "conv1d: empty output (L=%d)", Lw);
+  if (windows > 1)
+    FA_REQUIRE(ctx, stride == 1 && Lout_w == Lw, "conv1d: the windowed form needs stride 1 and same-length output");
+  const int Lout = Lout_w * windows;
+  FA_REQUIRE(ctx, (long long)cout * Lout < (1ll << 31), "conv1d: output too large");
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, cout, Lout, FA_F32, true, &y));
   size_t n = (size_t)cout * Lout;
   {
-    LaunchScope ls(ctx, "conv1d");
+    LaunchScope ls(ctx, windows > 1 ? "conv1d_windows" : "conv1d");
     k_conv1d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
                                                            bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr,
-                                                           cout, cin, L, Lout, k, stride, pad_left, dilation, groups, act);
+                                                           cout, cin, L, Lout, Lw, k, stride, pad_left, dilation, groups, act);
   }
   FA_LAUNCH_CHECK(ctx, "conv1d");
   *out = y;
   return FA_OK;
+}
+
+extern "C" int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k,
+                         int stride, int pad_left, int pad_right, int dilation, int groups, int act, fa_tensor **out) {
+  return conv1d_impl(ctx, x, w, bias, cout, k, stride, pad_left, pad_right, dilation, groups, act, 1, out);
+}
+
+extern "C" int fa_conv1d_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout,
+                                 int k, int pad_left, int pad_right, int dilation, int groups, int act, int windows,
+                                 fa_tensor **out) {
+  return conv1d_impl(ctx, x, w, bias, cout, k, 1, pad_left, pad_right, dilation, groups, act, windows, out);
 }
 
 extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin,
@@ -685,6 +779,20 @@ extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
       fa_free_tensor(ctx, y);
       return rc;
     }
+    *out = y;
+    return FA_OK;
+  }
+  FA_REQUIRE(ctx, n < (1ull << 31), "conv2d: output too large");
+  if (cin == 1 && groups == 1 && kh == 3 && kw == 3) {
+    const unsigned plane = (unsigned)Ho * Wo;
+    dim3 grid((plane + 255) / 256 < (unsigned)ctx->sm_count * 4 ? (plane + 255) / 256 : ctx->sm_count * 4, ceil_div(cout, 32));
+    {
+      LaunchScope ls(ctx, "conv2d_c1_3x3");
+      k_conv2d_c1_3x3<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
+                                                     bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr, cout, h,
+                                                     w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act);
+    }
+    FA_LAUNCH_CHECK(ctx, "conv2d_c1_3x3");
     *out = y;
     return FA_OK;
   }

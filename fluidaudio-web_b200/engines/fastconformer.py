@@ -102,9 +102,11 @@ def pre_encode(ctx, enc, mel: np.ndarray):
     return ctx.matmul(flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
 
 
-def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None):
+def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bool = True):
     """W same-length windows concatenated along rows (:235-386): GEMMs see M = W*Tsub, attention and the
-    depthwise conv stay per window.  Returns (frames [W*Tsub, D], Tsub)."""
+    depthwise conv stay per window.  Optional backend members (feature-tested, like the reference tests
+    `ctx.attnFused`) replace per-window loops when `use_fast`; use_fast=False is the reference's exact op
+    sequence.  Returns (frames [W*Tsub, D], Tsub)."""
     cfg = enc["cfg"]
     D, H, HD, LAYERS, dwK = cfg["D"], cfg["H"], cfg["HD"], cfg["layers"], cfg["dwK"]
     ln = lambda x, lp: ctx.layernorm(x, lp[0], lp[1])
@@ -151,6 +153,8 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None):
                 opts = dict(cout=D, k=dwK, groups=D, padLeft=dwPadL, padRight=dwPadR, bias=w["dwb"], act="silu")
                 if W == 1:
                     dwo = ctx.conv1d(glu, w["dw"], opts)
+                elif use_fast and hasattr(ctx, "conv1dWindows"):  # optional member: all windows in one launch
+                    dwo = ctx.conv1dWindows(glu, w["dw"], opts, W)
                 else:  # depthwise conv is over time -> per window (:343-351)
                     dwo = ctx.alloc(D, W * Tsub)
                     for wi in range(W):

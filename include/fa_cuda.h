@@ -151,6 +151,12 @@ int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);               
 /* conv1d :172 — grouped/depthwise direct form (lib.rs:99-138); w = Cout*(Cin/groups)*K. */
 int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k, int stride,
               int pad_left, int pad_right, int dilation, int groups, int act, fa_tensor **out);
+/* The per-window loop around conv1d in the conformer conv module (sliceCols -> conv1d -> setCols per
+ * window, src/engines/asr-parakeet/raw-encoder.js:343-351) as one call: the columns of x are `windows`
+ * independent windows of equal length; stride 1 and same-length output only.  Optional fast path; the
+ * per-window op sequence gives the same result. */
+int fa_conv1d_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k,
+                      int pad_left, int pad_right, int dilation, int groups, int act, int windows, fa_tensor **out);
 /* conv2d :179 (batch 1). x [Cin, H*W] -> [Cout, Ho*Wo]. */
 int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin, int h,
               int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left,

@@ -26,6 +26,11 @@ def test_tiny_encoder_end_to_end(ctx, pkg):
     got, Tsub2 = fc.encode_batch(ctx, fc.load_encoder(ctx, w), mels)
     out = ctx.download(got).reshape(ref.rows, ref.cols)
     ctx.popArena(h)
+    # the reference's exact op sequence (per-window conv loop) gives the same frames as the one-launch form
+    h = ctx.pushArena()
+    got_ref_seq, _ = fc.encode_batch(ctx, fc.load_encoder(ctx, w), mels, use_fast=False)
+    assert np.array_equal(ctx.download(got_ref_seq).reshape(ref.rows, ref.cols), out)
+    ctx.popArena(h)
     assert Tsub == Tsub2 and (got.rows, got.cols) == (ref.rows, ref.cols)
     # two layers, f16 weights on the device vs f32 on the oracle; outputs are LayerNorm'ed (unit scale)
     assert np.abs(out - ref.array()).max() <= 2e-2
