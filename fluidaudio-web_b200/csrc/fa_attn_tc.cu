@@ -1,0 +1,186 @@
+// Attention products (bmmQK / bmmPV, src/gpu/kernels/attention.js:14-146) on the tensor cores.
+//
+// Each (window, head) pair is one small product; all of them go through ONE launch of the batched
+// tcgen05 GEMM (fa_gemm_tc.cu).  The operands are cut out of the head-strided [T, H*HD] projections and
+// written as f16 in the GEMM's box-contiguous layouts by the pack kernels below:
+//   QK^T : streamed ("weight") side = keys  b[j, h*HD + d]   -> Wp[batch][j/128][d/64][j%128][d%64]
+//          row ("activation") side  = q + qb                  -> Ap[batch][d/64][i][d%64]
+//   P@V  : streamed side = V transposed  v[j, h*HD + d]       -> Wp[batch][d/128][j/64][d%128][j%64]
+//          row side      = probabilities p[(batch*Tq + i), j] -> Ap[batch][j/64][i][j%64]
+// Accumulation is f32 in TMEM; only the operands are rounded to f16.
+#include "fa_internal.cuh"
+
+namespace {
+
+// rows r of src[(row0 + r) * S + col0 + d] (+ addv[col0 + d]) -> Ap[batch][d/64][r][d%64], d zero padded
+__global__ void k_pack_act_heads(const float *__restrict__ src, const float *__restrict__ addv, __half *__restrict__ dst,
+                                 int T, int S, int H, int HD, int nch, unsigned total) {
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    // i indexes half2 pairs of dst: [batch][c][r][32 pairs]
+    const int pr = i & 31;
+    unsigned t = i >> 5;
+    const int r = t % T;
+    t /= T;
+    const int c = t % nch, batch = t / nch;
+    const int w = batch / H, h = batch % H, d = c * 64 + pr * 2;
+    float x = 0.f, y = 0.f;
+    const float *row = src + ((size_t)w * T + r) * S + h * HD;
+    if (d < HD) x = row[d] + (addv ? addv[h * HD + d] : 0.f);
+    if (d + 1 < HD) y = row[d + 1] + (addv ? addv[h * HD + d + 1] : 0.f);
+    ((__half2 *)dst)[i] = __floats2half2_rn(x, y);
+  }
+}
+
+// keys: src[(wsrc*Tb + j) * S + h*HD + d] -> Wp[batch][j/128][d/64][j%128][d%64]; rows j >= Tb and d >= HD zero
+__global__ void k_pack_w_heads(const float *__restrict__ src, __half *__restrict__ dst, int Tb, int S, int H, int HD,
+                               int tiles_n, int nch, unsigned total) {
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int pr = i & 31;
+    unsigned t = i >> 5;
+    const int jr = t & 127;
+    t >>= 7;
+    const int c = t % nch;
+    t /= nch;
+    const int tn = t % tiles_n, batch = t / tiles_n;
+    const int w = batch / H, h = batch % H, j = tn * 128 + jr, d = c * 64 + pr * 2;
+    float x = 0.f, y = 0.f;
+    if (j < Tb) {
+      const float *row = src + ((size_t)w * Tb + j) * S + h * HD;
+      if (d < HD) x = row[d];
+      if (d + 1 < HD) y = row[d + 1];
+    }
+    ((__half2 *)dst)[i] = __floats2half2_rn(x, y);
+  }
+}
+
+// probabilities: p[(batch*Tq + r) * Tk + j] -> Ap[batch][j/64][r][j%64], j zero padded
+__global__ void k_pack_act_probs(const float *__restrict__ p, __half *__restrict__ dst, int Tq, int Tk, int nch,
+                                 unsigned total) {
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int pr = i & 31;
+    unsigned t = i >> 5;
+    const int r = t % Tq;
+    t /= Tq;
+    const int c = t % nch, batch = t / nch;
+    const int j = c * 64 + pr * 2;
+    const float *row = p + ((size_t)batch * Tq + r) * Tk;
+    float x = j < Tk ? row[j] : 0.f, y = j + 1 < Tk ? row[j + 1] : 0.f;
+    ((__half2 *)dst)[i] = __floats2half2_rn(x, y);
+  }
+}
+
+// values transposed: v[(w*Tk + j) * S + h*HD + d] -> Wp[batch][d/128][j/64][d%128][j%64].
+// One CTA per (batch, 64-key chunk): the 64 x HD slab goes through shared memory.
+__global__ void __launch_bounds__(256) k_pack_w_vT(const float *__restrict__ v, __half *__restrict__ dst, int Tk, int S,
+                                                   int H, int HD, int tiles_n, int nch) {
+  extern __shared__ float tile[];  // [64 keys][HD + 1]
+  const int batch = blockIdx.x / nch, c = blockIdx.x % nch;
+  const int w = batch / H, h = batch % H, ldt = HD + 1;
+  for (int e = threadIdx.x; e < 64 * HD; e += 256) {
+    const int jj = e / HD, d = e % HD, j = c * 64 + jj;
+    tile[jj * ldt + d] = j < Tk ? v[((size_t)w * Tk + j) * S + h * HD + d] : 0.f;
+  }
+  __syncthreads();
+  // dst rows: for each d (padded to tiles_n*128), 64 keys = 32 half2
+  for (int e = threadIdx.x; e < tiles_n * 128 * 32; e += 256) {
+    const int pr = e & 31, dr = e >> 5;  // dr = d within [0, tiles_n*128)
+    const int tn = dr >> 7, dl = dr & 127;
+    float x = 0.f, y = 0.f;
+    if (dr < HD) {
+      x = tile[(pr * 2) * ldt + dr];
+      y = tile[(pr * 2 + 1) * ldt + dr];
+    }
+    const size_t o = ((((size_t)batch * tiles_n + tn) * nch + c) * 128 + dl) * 32 + pr;
+    ((__half2 *)dst)[o] = __floats2half2_rn(x, y);
+  }
+}
+
+int grid_for(fa_ctx *ctx, size_t n) {
+  size_t g = (n + 255) / 256, cap = (size_t)ctx->sm_count * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+struct Block {
+  fa_ctx *ctx;
+  void *p = nullptr;
+  size_t bytes = 0;
+  explicit Block(fa_ctx *c) : ctx(c) {}
+  int get(size_t need) { return fa_block_acquire(ctx, need, &p, &bytes); }
+  ~Block() {
+    if (p) fa_block_release(ctx, p);
+  }
+};
+
+}  // namespace
+
+int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, float *out, int T, int Tb, int H, int HD,
+                 int W, int b_shared, bool *done) {
+  *done = false;
+  const long long batches = (long long)W * H;
+  if (!fa_tc_available(ctx) || HD < 64 || T < 32 || Tb < 32 || T > 256 || batches * T * Tb * HD < (1ll << 22)) return FA_OK;
+  const int S = H * HD, nch = ceil_div(HD, 64), tiles_n = ceil_div(Tb, 128);
+  const int wb = b_shared ? H : (int)batches;  // shared keys (the positional table) are packed once per head
+  const size_t a_halves = (size_t)batches * nch * T * 64, w_halves = (size_t)wb * tiles_n * nch * 128 * 64;
+  if (a_halves / 2 >= (1ull << 31) || w_halves / 2 >= (1ull << 31)) return FA_OK;
+  Block ap(ctx), wp(ctx);
+  FA_TRY(ap.get(a_halves * 2));
+  FA_TRY(wp.get(w_halves * 2));
+  {
+    LaunchScope ls(ctx, "attn_pack_q");
+    k_pack_act_heads<<<grid_for(ctx, a_halves / 2), 256, 0, ctx->stream>>>(q, qb, (__half *)ap.p, T, S, H, HD, nch,
+                                                                          (unsigned)(a_halves / 2));
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_pack_q");
+  {
+    LaunchScope ls(ctx, "attn_pack_k");
+    // with shared keys the source has a single "window" (w = 0 for every packed batch h)
+    k_pack_w_heads<<<grid_for(ctx, w_halves / 2), 256, 0, ctx->stream>>>(b, (__half *)wp.p, Tb, S, H, HD, tiles_n, nch,
+                                                                        (unsigned)(w_halves / 2));
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_pack_k");
+  TcEpilogue ep;
+  ep.batches = (int)batches;
+  ep.w_batch_mod = b_shared ? H : 0;
+  ep.o_div = 1;
+  ep.o_hi = (long long)T * Tb;  // out[((w*H+h)*T + i)*Tb + j]
+  ep.o_lo = 0;
+  ep.ldc = Tb;
+  FA_TRY(fa_tc_gemm_f16(ctx, (const __half *)ap.p, (const __half *)wp.p, out, T, Tb, HD, ep));
+  *done = true;
+  return FA_OK;
+}
+
+int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, int Tq, int Tk, int H, int HD, int W, bool *done) {
+  *done = false;
+  const long long batches = (long long)W * H;
+  if (!fa_tc_available(ctx) || HD < 64 || HD > 160 || Tq < 32 || Tk < 32 || Tq > 256 ||
+      batches * Tq * Tk * HD < (1ll << 22))
+    return FA_OK;
+  const int S = H * HD, nch = ceil_div(Tk, 64), tiles_n = ceil_div(HD, 128);
+  const size_t a_halves = (size_t)batches * nch * Tq * 64, w_halves = (size_t)batches * tiles_n * nch * 128 * 64;
+  if (a_halves / 2 >= (1ull << 31) || w_halves / 2 >= (1ull << 31)) return FA_OK;
+  Block ap(ctx), wp(ctx);
+  FA_TRY(ap.get(a_halves * 2));
+  FA_TRY(wp.get(w_halves * 2));
+  {
+    LaunchScope ls(ctx, "attn_pack_p");
+    k_pack_act_probs<<<grid_for(ctx, a_halves / 2), 256, 0, ctx->stream>>>(p, (__half *)ap.p, Tq, Tk, nch,
+                                                                          (unsigned)(a_halves / 2));
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_pack_p");
+  {
+    LaunchScope ls(ctx, "attn_pack_v");
+    k_pack_w_vT<<<(unsigned)(batches * nch), 256, (size_t)64 * (HD + 1) * 4, ctx->stream>>>(v, (__half *)wp.p, Tk, S, H, HD,
+                                                                                          tiles_n, nch);
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_pack_v");
+  TcEpilogue ep;
+  ep.batches = (int)batches;
+  ep.o_div = H;  // out[(w*Tq + i)*S + h*HD + d]
+  ep.o_hi = (long long)Tq * S;
+  ep.o_lo = HD;
+  ep.ldc = S;
+  FA_TRY(fa_tc_gemm_f16(ctx, (const __half *)ap.p, (const __half *)wp.p, out, Tq, HD, Tk, ep));
+  *done = true;
+  return FA_OK;
+}

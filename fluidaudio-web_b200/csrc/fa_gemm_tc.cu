@@ -50,6 +50,11 @@ struct TcParams {
   int splitk;         // > 1: cluster of `splitk` CTAs along z shares one tile, each taking kb_per_split chunks
   int kb_per_split;
   int raw_i32;        // 1: store the limb-0 int32 accumulators instead of the float epilogue
+  // batched mode (attention products): `batches` independent [M][N] problems share one launch.  Batch b
+  // reads weight slab (w_batch_mod ? b % w_batch_mod : b) and activation slabs of batch b, and writes at
+  // out + (b / o_div) * o_hi + (b % o_div) * o_lo with row pitch ldc.
+  int batches, w_batch_mod, o_div, ldc;
+  long long o_hi, o_lo;
   float *out;         // [M][N] f32 (or int32 when raw_i32)
   const float *rowscale, *colscale, *bias, *add, *rowbias;
   int act;
@@ -134,7 +139,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   uint32_t acc_stride = 32;  // TMEM columns per accumulator buffer
   while ((int)acc_stride < q_rows) acc_stride <<= 1;
   const uint32_t tmem_cols = 2 * acc_stride;
-  const int num_tiles = p.tiles_n * p.tiles_m;
+  const int num_tiles = p.tiles_n * p.tiles_m * p.batches;
   const int kb0 = p.splitk > 1 ? (int)blockIdx.z * p.kb_per_split : 0;
   const int kb1 = p.splitk > 1 ? min(p.num_kb, kb0 + p.kb_per_split) : p.num_kb;
 
@@ -178,7 +183,9 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     uint32_t it = 0;
     bool stop = false;
     for (int tile = blockIdx.x; tile < num_tiles && !stop; tile += gridDim.x) {
-      const int tn = tile % p.tiles_n, tm = tile / p.tiles_n;
+      const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
+      const int tn = tin % p.tiles_n, tm = tin / p.tiles_n;
+      const int wb = p.w_batch_mod ? batch % p.w_batch_mod : batch;
       for (int kb = kb0; kb < kb1; kb++, it++) {
         if (lane == 0) {
           const int s = (int)(it % (uint32_t)p.stages);
@@ -190,10 +197,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (it < 64) TC_TRACE(1 + it);
             mbar_expect_tx(full_bar(s), stage_bytes);
             const uint32_t dst = smem_base + (uint32_t)s * stage_bytes;
-            tma_load_2d(dst, &map_w, 0, (tn * p.num_kb + kb) * 128, full_bar(s));
+            tma_load_2d(dst, &map_w, 0, ((wb * p.tiles_n + tn) * p.num_kb + kb) * 128, full_bar(s));
             for (int l = 0; l < p.limbs; l++)
-              tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, tm * p.MT, l * p.num_kb + kb,
-                          full_bar(s));
+              tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, tm * p.MT,
+                          (batch * p.limbs + l) * p.num_kb + kb, full_bar(s));
           }
         }
         stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
@@ -246,8 +253,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     uint32_t lt = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
-      const int tn = tile % p.tiles_n, tm = tile / p.tiles_n;
+      const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
+      const int tn = tin % p.tiles_n, tm = tin / p.tiles_n;
       const int n0 = tn * 128, m0 = tm * p.MT;
+      float *const outb = p.out + (size_t)(batch / p.o_div) * p.o_hi + (size_t)(batch % p.o_div) * p.o_lo;
       const uint32_t buf = lt & 1, use = lt >> 1;
       ok = mbar_wait(acc_full(buf), use & 1);
       if (!ok && lane == 0) set_abort(3, tile);
@@ -305,7 +314,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           if (n_ok) {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (m0 + c + j < p.M) ((int32_t *)p.out)[(size_t)(m0 + c + j) * p.N + n] = (int32_t)v0[j];
+              if (m0 + c + j < p.M) ((int32_t *)outb)[(size_t)(m0 + c + j) * p.ldc + n] = (int32_t)v0[j];
           }
           continue;
         }
@@ -332,14 +341,14 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs) + rb[j];
         act16(v, p.act);
         if (n_ok) {
-          float *orow = p.out + (size_t)(m0 + c) * p.N + n;
+          float *orow = outb + (size_t)(m0 + c) * p.ldc + n;
           if (full_rows) {
 #pragma unroll
-            for (int j = 0; j < 16; j++) orow[(size_t)j * p.N] = v[j] + ad[j];
+            for (int j = 0; j < 16; j++) orow[(size_t)j * p.ldc] = v[j] + ad[j];
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j++)
-              if (m0 + c + j < p.M) orow[(size_t)j * p.N] = v[j] + ad[j];
+              if (m0 + c + j < p.M) orow[(size_t)j * p.ldc] = v[j] + ad[j];
           }
         }
       }
@@ -578,12 +587,18 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.MT = mt < mt_max ? mt : mt_max;
   p.tiles_n = ceil_div(N, 128);
   p.tiles_m = ceil_div(M, p.MT);
-  const int num_tiles = p.tiles_n * p.tiles_m;
+  p.batches = ep.batches;
+  p.w_batch_mod = ep.w_batch_mod;
+  p.o_div = ep.o_div > 0 ? ep.o_div : 1;
+  p.ldc = ep.ldc > 0 ? ep.ldc : N;
+  p.o_hi = ep.o_hi;
+  p.o_lo = ep.o_lo;
+  const int num_tiles = p.tiles_n * p.tiles_m * p.batches;
   // Decode-size products have fewer tiles than SMs: split K across a cluster (<= 8 CTAs) so that
   // every SM streams weights.  Each split keeps at least 4 chunks so the ring still pipelines.
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
-  if (!raw_i32 && p.tiles_m == 1 && p.MT <= kSplitMaxMT && num_tiles * 2 <= ctx->sm_count) {
+  if (!raw_i32 && p.batches == 1 && p.tiles_m == 1 && p.MT <= kSplitMaxMT && num_tiles * 2 <= ctx->sm_count) {
     int s = ctx->sm_count / num_tiles;
     if (s > 8) s = 8;
     while (s > 1 && p.num_kb / s < 4) s--;
@@ -620,9 +635,11 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
 
   CUtensorMap map_w, map_a;
   // weights: rows of 128 bytes, (tiles_n * num_kb * 128) of them, boxes of 128 rows
-  FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, (uint64_t)p.tiles_n * p.num_kb * 128, 0, 128));
+  const uint64_t w_batches = p.w_batch_mod ? p.w_batch_mod : p.batches;
+  FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, w_batches * p.tiles_n * p.num_kb * 128, 0, 128));
   // activations: [limbs * num_kb] slabs of M rows of 128 bytes, boxes of MT rows (rows >= M read as zero)
-  FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M, (uint64_t)limbs * p.num_kb, (uint32_t)p.MT));
+  FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M, (uint64_t)p.batches * limbs * p.num_kb,
+                               (uint32_t)p.MT));
   FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];

@@ -654,7 +654,11 @@ extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, co
   const int T = q->rows / W, Tb = b_shared ? b->rows : b->rows / W;
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, W * H * T, Tb, FA_F32, true, &y));
-  if (T && Tb) {
+  bool on_tc = false;
+  if (T && Tb)
+    FA_TRY(fa_tc_bmm_qk(ctx, (const float *)q->dptr, (const float *)b->dptr, qb ? (const float *)qb->dptr : nullptr,
+                        (float *)y->dptr, T, Tb, H, HD, W, b_shared, &on_tc));
+  if (T && Tb && !on_tc) {
     dim3 grid(ceil_div(Tb, 64), ceil_div(T, 64), W * H);
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmQK: batch too large");
     {
@@ -679,7 +683,10 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
   FA_REQUIRE(ctx, p->cols == Tk, "bmmPV: p has %d columns, v has %d rows per window", p->cols, Tk);
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, W * Tq, H * HD, FA_F32, true, &y));
-  if (Tq && Tk) {
+  bool on_tc = false;
+  if (Tq && Tk)
+    FA_TRY(fa_tc_bmm_pv(ctx, (const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, Tq, Tk, H, HD, W, &on_tc));
+  if (Tq && Tk && !on_tc) {
     dim3 grid(ceil_div(HD, 64), ceil_div(Tq, 64), W * H);
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmPV: batch too large");
     {

@@ -214,6 +214,9 @@ struct TcEpilogue {
   const float *add = nullptr;       // [M][N]
   const float *rowbias = nullptr;   // [M] added before the activation
   int act = 0;
+  // batched launch: `batches` independent [M][N] products (see TcParams in fa_gemm_tc.cu)
+  int batches = 1, w_batch_mod = 0, o_div = 1, ldc = 0;
+  long long o_hi = 0, o_lo = 0;
 };
 // Packed ("box-contiguous") operand sizes: K is cut in chunks of 128 bytes.
 static inline int fa_tc_chunks(int K, int elem_bytes) { return ceil_div(K, 128 / elem_bytes); }
@@ -235,3 +238,8 @@ int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, 
 int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk,
                         int zpb, __half *out);
 bool fa_tc_available(fa_ctx *ctx);
+// Batched attention products on the tensor cores (fa_attn_tc.cu); return FA_OK and *done=false when the
+// shape does not fit the packed layouts (the caller then uses the any-shape kernels).
+int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, float *out, int T, int Tb, int H, int HD,
+                 int W, int b_shared, bool *done);
+int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, int Tq, int Tk, int H, int HD, int W, bool *done);

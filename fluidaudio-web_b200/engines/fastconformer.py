@@ -81,13 +81,23 @@ def pos_encoding(Tsub: int, D: int) -> np.ndarray:
     return pe
 
 
-def pre_encode(ctx, enc, mel: np.ndarray):
-    """Subsampling + linear for ONE window: mel [melBins*T] channel-major -> x [Tsub, D] (:177-222)."""
+def mel_time_major(mel: np.ndarray, melBins: int) -> np.ndarray:
+    """The host-side transpose of preEncode (:181-183): mel [melBins*T] channel-major -> [T*melBins]."""
+    Tfull = mel.size // melBins
+    return np.ascontiguousarray(mel.reshape(melBins, Tfull).T, dtype=np.float32).reshape(-1)
+
+
+def pre_encode(ctx, enc, mel):
+    """Subsampling + linear for ONE window -> x [Tsub, D] (:177-222).  `mel` is the reference's
+    channel-major array [melBins*T], or a backend tensor [1, T*melBins] that already holds the
+    time-major image (so a caller can keep windows resident on the device)."""
     cfg = enc["cfg"]
     Csub, melBins = cfg["Csub"], cfg["melBins"]
-    Tfull = mel.size // melBins
-    x0 = np.ascontiguousarray(mel.reshape(melBins, Tfull).T, dtype=np.float32)  # [T, melBins]
-    s = ctx.upload(x0, 1, Tfull * melBins)
+    if isinstance(mel, np.ndarray):
+        s = ctx.upload(mel_time_major(mel, melBins), 1, mel.size)
+    else:
+        s = mel
+    Tfull = (s.rows * s.cols) // melBins
     Hh, Wd = Tfull, melBins
     conv = [(Csub, 1, 3, 2, 1, "relu", True), (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False),
             (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False)]

@@ -76,6 +76,23 @@ def test_attention_products_and_rel_shift(ctx):
     close(ctx, ctx.bmmPV(p, k, H, HD, W), ORA.bmmPV(po, ko, H, HD, W), 1e-3)
 
 
+def test_attention_products_full_head_size_tensor_core_route(ctx):
+    """Parakeet head geometry (8 heads of 128, 188 frames): the batched tcgen05 route, f16 operands."""
+    rng = np.random.default_rng(5)
+    W, H, HD, Tq = 3, 8, 128, 188
+    q, qo = up(ctx, rng.standard_normal((W * Tq, H * HD)) * 0.3)
+    k, ko = up(ctx, rng.standard_normal((W * Tq, H * HD)) * 0.3)
+    pb, pbo = up(ctx, rng.standard_normal(H * HD) * 0.02)
+    pos, poso = up(ctx, rng.standard_normal((2 * Tq - 1, H * HD)) * 0.3)
+    ac, aco = ctx.bmmQK(q, k, pb, H, HD, W), ORA.bmmQK(qo, ko, pbo, H, HD, W)
+    close(ctx, ac, aco, 2e-2)
+    bd, bdo = ctx.bmmQK(q, pos, None, H, HD, W, True), ORA.bmmQK(qo, poso, None, H, HD, W, True)
+    close(ctx, bd, bdo, 2e-2)
+    po = ORA.softmax(ORA.add(aco, ORA.relShiftB(bdo, W * H)))
+    p = ctx.upload(po.array(), po.rows, po.cols)
+    close(ctx, ctx.bmmPV(p, k, H, HD, W), ORA.bmmPV(po, ko, H, HD, W), 2e-3)
+
+
 def test_convolutions(ctx):
     rng = np.random.default_rng(3)
     # depthwise conv over time with fused silu (the conformer conv module)
