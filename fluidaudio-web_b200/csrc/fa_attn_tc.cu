@@ -150,7 +150,8 @@ int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, f
   return FA_OK;
 }
 
-int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, int Tq, int Tk, int H, int HD, int W, bool *done) {
+int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half *out16, int Tq, int Tk, int H, int HD,
+                 int W, bool *done) {
   *done = false;
   const long long batches = (long long)W * H;
   if (!fa_tc_available(ctx) || HD < 64 || HD > 160 || Tq < 32 || Tk < 32 || Tq > 256 ||
@@ -180,6 +181,10 @@ int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, int Tq
   ep.o_hi = (long long)Tq * S;
   ep.o_lo = HD;
   ep.ldc = S;
+  ep.out16 = out16;  // the context feeds the output projection: hand it over already packed
+  ep.o16_rows = W * Tq;
+  ep.o16_row_hi = Tq;
+  ep.o16_col_lo = HD;
   FA_TRY(fa_tc_gemm_f16(ctx, (const __half *)ap.p, (const __half *)wp.p, out, Tq, HD, Tk, ep));
   *done = true;
   return FA_OK;

@@ -260,8 +260,10 @@ int fa_tensor_new(fa_ctx *ctx, int rows, int cols, int storage, bool pooled, fa_
 static void tensor_drop_storage(fa_ctx *ctx, fa_tensor *t) {
   if (t->view) return;
   if (t->bt_f16) fa_block_release(ctx, t->bt_f16);
+  if (t->a16) fa_block_release(ctx, t->a16);
   if (t->dptr) fa_block_release(ctx, t->dptr);
-  t->dptr = t->bt_f16 = nullptr;
+  t->dptr = t->bt_f16 = t->a16 = nullptr;
+  t->a16_valid = false;
 }
 
 // ---- uploads ----------------------------------------------------------------------------

@@ -55,6 +55,8 @@ struct TcParams {
   // out + (b / o_div) * o_hi + (b % o_div) * o_lo with row pitch ldc.
   int batches, w_batch_mod, o_div, ldc;
   long long o_hi, o_lo;
+  __half *out16;      // optional packed f16 shadow of the result (see TcEpilogue), or nullptr
+  int o16_rows, o16_row_hi, o16_col_lo;
   float *out;         // [M][N] f32 (or int32 when raw_i32)
   const float *rowscale, *colscale, *bias, *add, *rowbias;
   int act;
@@ -257,6 +259,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       const int tn = tin % p.tiles_n, tm = tin / p.tiles_n;
       const int n0 = tn * 128, m0 = tm * p.MT;
       float *const outb = p.out + (size_t)(batch / p.o_div) * p.o_hi + (size_t)(batch % p.o_div) * p.o_lo;
+      const int r16 = (batch / p.o_div) * p.o16_row_hi, c16 = (batch % p.o_div) * p.o16_col_lo;
       const uint32_t buf = lt & 1, use = lt >> 1;
       ok = mbar_wait(acc_full(buf), use & 1);
       if (!ok && lane == 0) set_abort(3, tile);
@@ -341,6 +344,13 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs) + rb[j];
         act16(v, p.act);
         if (n_ok) {
+          if (p.out16) {  // shadow: Ap[k/64][row][k%64] of the output tensor, 32 lanes = 64 contiguous bytes
+            const int gn = n + c16;
+            __half *h16 = p.out16 + ((size_t)(gn >> 6) * p.o16_rows + (r16 + m0 + c)) * 64 + (gn & 63);
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+              if (full_rows || m0 + c + j < p.M) h16[(size_t)j * 64] = __float2half_rn(v[j] + ad[j]);
+          }
           float *orow = outb + (size_t)(m0 + c) * p.ldc + n;
           if (full_rows) {
 #pragma unroll
@@ -586,6 +596,20 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   int mt = ((M + 15) / 16) * 16;
   p.MT = mt < mt_max ? mt : mt_max;
   p.tiles_n = ceil_div(N, 128);
+  if (M > mt_max) {
+    // Several row tiles: pick the tile height that minimises (rounds over the SMs) x (bytes a tile pulls per
+    // K chunk, 128 weight rows + MT activation rows) - a full last wave matters more than the tallest tile.
+    const long long batches = ep.batches > 0 ? ep.batches : 1;
+    long long best = -1;
+    for (int cand = mt_max; cand >= 64; cand -= 16) {
+      const long long tiles = (long long)p.tiles_n * ceil_div(M, cand) * batches;
+      const long long cost = ((tiles + ctx->sm_count - 1) / ctx->sm_count) * (128 + cand * limbs);
+      if (best < 0 || cost < best) {
+        best = cost;
+        p.MT = cand;
+      }
+    }
+  }
   p.tiles_m = ceil_div(M, p.MT);
   p.batches = ep.batches;
   p.w_batch_mod = ep.w_batch_mod;
@@ -593,12 +617,16 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.ldc = ep.ldc > 0 ? ep.ldc : N;
   p.o_hi = ep.o_hi;
   p.o_lo = ep.o_lo;
+  p.out16 = ep.out16;
+  p.o16_rows = ep.o16_rows > 0 ? ep.o16_rows : M;
+  p.o16_row_hi = ep.o16_row_hi;
+  p.o16_col_lo = ep.o16_col_lo;
   const int num_tiles = p.tiles_n * p.tiles_m * p.batches;
   // Decode-size products have fewer tiles than SMs: split K across a cluster (<= 8 CTAs) so that
   // every SM streams weights.  Each split keeps at least 4 chunks so the ring still pipelines.
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
-  if (!raw_i32 && p.batches == 1 && p.tiles_m == 1 && p.MT <= kSplitMaxMT && num_tiles * 2 <= ctx->sm_count) {
+  if (!raw_i32 && !ep.out16 && p.batches == 1 && p.tiles_m == 1 && p.MT <= kSplitMaxMT && num_tiles * 2 <= ctx->sm_count) {
     int s = ctx->sm_count / num_tiles;
     if (s > 8) s = 8;
     while (s > 1 && p.num_kb / s < 4) s--;

@@ -18,8 +18,8 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // One CTA (256 threads) per row; two-pass mean/variance (wasm-context.js:308-326).
 __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ g,
-                                                   const float *__restrict__ b, float *__restrict__ y, int R, int C,
-                                                   float eps) {
+                                                   const float *__restrict__ b, float *__restrict__ y,
+                                                   __half *__restrict__ y16, int R, int C, float eps) {
   __shared__ float red[8];
   __shared__ float stat;
   for (int r = blockIdx.x; r < R; r += gridDim.x) {
@@ -52,7 +52,12 @@ __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, 
     }
     __syncthreads();
     const float inv = stat;
-    for (int j = threadIdx.x; j < C; j += 256) y[(size_t)r * C + j] = (row[j] - mean) * inv * g[j] + b[j];
+    for (int j = threadIdx.x; j < C; j += 256) {
+      const float o = (row[j] - mean) * inv * g[j] + b[j];
+      y[(size_t)r * C + j] = o;
+      // normalised rows feed linear layers: also emit them as the packed f16 row operand Ap[j/64][r][j%64]
+      if (y16) y16[((size_t)(j >> 6) * R + r) * 64 + (j & 63)] = __float2half_rn(o);
+    }
     __syncthreads();
   }
 }
@@ -393,8 +398,11 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
     int grid = x->rows < ctx->sm_count * 8 ? x->rows : ctx->sm_count * 8;
     {
       LaunchScope ls(ctx, "layernorm");
+      __half *y16 = nullptr;
+      if ((x->cols & 63) == 0 && x->rows >= 16 && fa_tc_available(ctx) && (y16 = fa_shadow_block(ctx, y)) != nullptr)
+        y->a16_valid = true;
       k_layernorm<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)gamma->dptr,
-                                                 (const float *)beta->dptr, (float *)y->dptr, x->rows, x->cols, eps);
+                                                 (const float *)beta->dptr, (float *)y->dptr, y16, x->rows, x->cols, eps);
     }
     FA_LAUNCH_CHECK(ctx, "layernorm");
   }
@@ -540,6 +548,7 @@ extern "C" int fa_set_cols(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, in
   FA_TRY(need_f32(ctx, src, "setCols"));
   FA_REQUIRE(ctx, col0 >= 0 && col0 + src->cols <= dst->cols && src->rows <= dst->rows,
              "setCols: src [%d,%d] at column %d does not fit dst [%d,%d]", src->rows, src->cols, col0, dst->rows, dst->cols);
+  fa_shadow_drop(dst);
   size_t n = (size_t)src->rows * src->cols;
   if (n) {
     {
@@ -575,6 +584,7 @@ extern "C" int fa_copy_rows(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, i
   FA_REQUIRE(ctx, src->cols == dst->cols && row_offset >= 0 && row_offset + src->rows <= dst->rows,
              "copyRows: src [%d,%d] at row %d does not fit dst [%d,%d]", src->rows, src->cols, row_offset, dst->rows,
              dst->cols);
+  fa_shadow_drop(dst);
   size_t bytes = (size_t)src->rows * src->cols * 4;
   if (bytes)
     FA_CHECK_CUDA(ctx, cudaMemcpyAsync((float *)dst->dptr + (size_t)row_offset * dst->cols, src->dptr, bytes,
@@ -685,7 +695,11 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
   FA_TRY(fa_tensor_new(ctx, W * Tq, H * HD, FA_F32, true, &y));
   bool on_tc = false;
   if (Tq && Tk)
-    FA_TRY(fa_tc_bmm_pv(ctx, (const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, Tq, Tk, H, HD, W, &on_tc));
+  {
+    __half *y16 = ((H * HD) & 63) == 0 && (HD & 31) == 0 ? fa_shadow_block(ctx, y) : nullptr;
+    FA_TRY(fa_tc_bmm_pv(ctx, (const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, y16, Tq, Tk, H, HD, W, &on_tc));
+    if (on_tc && y16) y->a16_valid = true;
+  }
   if (Tq && Tk && !on_tc) {
     dim3 grid(ceil_div(HD, 64), ceil_div(Tq, 64), W * H);
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmPV: batch too large");

@@ -30,6 +30,12 @@ struct fa_tensor {
   // Lazily built packed f16 copy used when this tensor is the weight side of a tensor-core GEMM.
   void *bt_f16 = nullptr;
   size_t bt_bytes = 0;
+  // Packed f16 shadow Ap[k/64][row][k%64] used when this tensor is the row (activation) side of a
+  // tensor-core GEMM.  Written by the producing kernel (layernorm, GEMM epilogue) or on first use;
+  // dropped whenever the tensor is written in place.  Storage stays opaque to callers (compute.d.ts:10-15).
+  void *a16 = nullptr;
+  size_t a16_bytes = 0;
+  bool a16_valid = false;
 };
 
 struct fa_bytes {
@@ -214,6 +220,10 @@ struct TcEpilogue {
   const float *add = nullptr;       // [M][N]
   const float *rowbias = nullptr;   // [M] added before the activation
   int act = 0;
+  // optional second output: the epilogue result as a packed f16 activation shadow of a tensor with
+  // o16_rows rows; this launch's rows/cols sit at (+o16_row_hi per batch/o_div, +o16_col_lo per batch%o_div)
+  __half *out16 = nullptr;
+  int o16_rows = 0, o16_row_hi = 0, o16_col_lo = 0;
   // batched launch: `batches` independent [M][N] products (see TcParams in fa_gemm_tc.cu)
   int batches = 1, w_batch_mod = 0, o_div = 1, ldc = 0;
   long long o_hi = 0, o_lo = 0;
@@ -242,4 +252,10 @@ bool fa_tc_available(fa_ctx *ctx);
 // shape does not fit the packed layouts (the caller then uses the any-shape kernels).
 int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, float *out, int T, int Tb, int H, int HD,
                  int W, int b_shared, bool *done);
-int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, int Tq, int Tk, int H, int HD, int W, bool *done);
+int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half *out16, int Tq, int Tk, int H, int HD,
+                 int W, bool *done);
+// Shadow management (fa_linalg.cu): block for t's packed f16 shadow (nullptr when t cannot carry one),
+// and the shadow itself, built by the prepass when no producer wrote it.
+__half *fa_shadow_block(fa_ctx *ctx, fa_tensor *t);
+int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out);
+static inline void fa_shadow_drop(fa_tensor *t) { t->a16_valid = false; }

@@ -60,6 +60,35 @@ struct Scratch {
 
 }  // namespace
 
+__half *fa_shadow_block(fa_ctx *ctx, fa_tensor *t) {
+  if (!t || t->view || t->storage != FA_F32 || t->rows <= 0 || t->cols <= 0) return nullptr;
+  if (!t->a16) {
+    if (fa_block_acquire(ctx, fa_tc_act_bytes(t->rows, t->cols, 2, 1), &t->a16, &t->a16_bytes) != FA_OK) return nullptr;
+    t->a16_valid = false;
+  }
+  return (__half *)t->a16;
+}
+
+int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out) {
+  __half *blk = fa_shadow_block(ctx, t);
+  if (!blk) return fa_fail(ctx, FA_ERR_OOM, "no block for the f16 shadow of a %dx%d tensor", t->rows, t->cols);
+  if (!t->a16_valid) {
+    FA_TRY(fa_prep_a_f16(ctx, (const float *)t->dptr, t->rows, t->cols, blk));
+    t->a16_valid = true;
+  }
+  *out = blk;
+  return FA_OK;
+}
+
+// Packed f16 row operand for `a`: its cached shadow when it can carry one, else a per-call scratch block.
+static int row_operand_f16(fa_ctx *ctx, const fa_tensor *a, const float *ap, Scratch &sa, const __half **out) {
+  if (a->storage == FA_F32 && !a->view) return fa_shadow_ensure(ctx, const_cast<fa_tensor *>(a), out);
+  FA_TRY(sa.get(fa_tc_act_bytes(a->rows, a->cols, 2, 1)));
+  FA_TRY(fa_prep_a_f16(ctx, ap, a->rows, a->cols, (__half *)sa.p));
+  *out = (const __half *)sa.p;
+  return FA_OK;
+}
+
 extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act,
                          const fa_tensor *add, fa_tensor **out) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmul: NULL argument");
@@ -83,15 +112,18 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
   const float *addp = add ? (const float *)add->dptr : nullptr;
   if (b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K)) {
     Scratch sa(ctx);
+    const __half *a16 = nullptr;
     rc = ensure_bt_f16(ctx, b);
-    if (rc == FA_OK) rc = sa.get(fa_tc_act_bytes(M, K, 2, 1));
-    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)sa.p);
+    if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16);
     if (rc == FA_OK) {
       TcEpilogue ep;
       ep.bias = biasp;
       ep.add = addp;
       ep.act = act;
-      rc = fa_tc_gemm_f16(ctx, (const __half *)sa.p, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);
+      // A product with a fused activation is a hidden layer: its result goes straight into the next
+      // product, so the epilogue also emits it as that product's packed f16 row operand.
+      if (act != FA_ACT_NONE && (N & 63) == 0 && (ep.out16 = fa_shadow_block(ctx, c)) != nullptr) c->a16_valid = true;
+      rc = fa_tc_gemm_f16(ctx, a16, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {
     rc = fa_simt_gemm(ctx, ap, b->dptr, b->storage == FA_F16 ? 1 : 0, nullptr, biasp, act, addp, (float *)c->dptr, M,
@@ -191,11 +223,11 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
       }
     }
     Scratch sa(ctx);
-    if (rc == FA_OK) rc = sa.get(fa_tc_act_bytes(M, K, 2, 1));
-    if (rc == FA_OK) rc = fa_prep_a_f16(ctx, ap, M, K, (__half *)sa.p);
+    const __half *a16 = nullptr;
+    if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16);
     if (rc == FA_OK) {
       TcEpilogue ep;
-      rc = fa_tc_gemm_f16(ctx, (const __half *)sa.p, (const __half *)bq->nk_f16, (float *)c->dptr, M, N, K, ep);
+      rc = fa_tc_gemm_f16(ctx, a16, (const __half *)bq->nk_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {
     rc = fa_simt_nbits(ctx, ap, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr,
