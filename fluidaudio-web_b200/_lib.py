@@ -66,6 +66,7 @@ SIGNATURES = {
     "fa_conv2d": [P, P, P, P] + [I] * 14 + [PP],
     "fa_bmm_qk": [P, P, P, P, I, I, I, I, PP],
     "fa_bmm_pv": [P, P, P, I, I, I, PP],
+    "fa_attn_fused": [P, P, P, P, P, P, P, I, I, I, PP],
     "fa_rel_shift_b": [P, P, I, PP],
     "fa_ewise": [P, P, P, I, PP],
     "fa_scale": [P, P, C.c_float, PP],

@@ -308,6 +308,13 @@ class CudaContext:
     def bmmPV(self, p, v, H: int, HD: int, W: int = 1) -> Tensor:
         return self._op(self._lib.fa_bmm_pv, p.h, v.h, H, HD, W)
 
+    def attnFused(self, q, k, v, pos, pbu, pbv, H: int, HD: int, W: int) -> Optional[Tensor]:
+        """Fused rel-pos self-attention (optional member, compute.d.ts:247-248).  Returns None when the
+        shape is outside the fused kernel's range - the caller then runs the separate ops."""
+        out = C.c_void_p()
+        self._check(self._lib.fa_attn_fused(self._h, q.h, k.h, v.h, pos.h, pbu.h, pbv.h, H, HD, W, C.byref(out)))
+        return self._wrap(out) if out.value else None
+
     def relShift(self, x) -> Tensor:
         return self._op(self._lib.fa_rel_shift_b, x.h, 1)
 

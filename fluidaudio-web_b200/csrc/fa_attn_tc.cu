@@ -95,6 +95,43 @@ __global__ void __launch_bounds__(256) k_pack_w_vT(const float *__restrict__ v, 
   }
 }
 
+// softmax over j of ac[i][j] + bd[i][T-1-i+j] (the rel-shifted positional scores, see k_rel_shift_b),
+// written straight into the packed f16 row operand of the P@V product: Ap[batch][j/64][i][j%64], the
+// K tail zero filled.  One warp per score row, the row held in registers (T <= 256).
+__global__ void k_softmax_shift_pack(const float *__restrict__ ac, const float *__restrict__ bd, __half *__restrict__ dst,
+                                     int rows, int T, int nch) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31, P = 2 * T - 1;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps) {
+    const int batch = r / T, i = r - batch * T;
+    const float *a = ac + (size_t)r * T;
+    const float *b = bd + (size_t)r * P + (T - 1 - i);
+    float v[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int j = lane + 32 * u;
+      v[u] = j < T ? a[j] + b[j] : -INFINITY;
+      mx = fmaxf(mx, v[u]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      v[u] = lane + 32 * u < T ? expf(v[u] - mx) : 0.f;
+      s += v[u];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.0f / s;
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int j = lane + 32 * u;
+      if (j < nch * 64) dst[(((size_t)batch * nch + (j >> 6)) * T + i) * 64 + (j & 63)] = __float2half_rn(v[u] * inv);
+    }
+  }
+}
+
 int grid_for(fa_ctx *ctx, size_t n) {
   size_t g = (n + 255) / 256, cap = (size_t)ctx->sm_count * 16;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
@@ -150,25 +187,33 @@ int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, f
   return FA_OK;
 }
 
-int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half *out16, int Tq, int Tk, int H, int HD,
-                 int W, bool *done) {
-  *done = false;
+static bool pv_shape_ok(fa_ctx *ctx, int Tq, int Tk, int H, int HD, int W) {
   const long long batches = (long long)W * H;
-  if (!fa_tc_available(ctx) || HD < 64 || HD > 160 || Tq < 32 || Tk < 32 || Tq > 256 ||
-      batches * Tq * Tk * HD < (1ll << 22))
-    return FA_OK;
+  if (!fa_tc_available(ctx) || HD < 64 || HD > 160 || Tq < 32 || Tk < 32 || Tq > 256 || batches * Tq * Tk * HD < (1ll << 22))
+    return false;
+  const int nch = ceil_div(Tk, 64), tiles_n = ceil_div(HD, 128);
+  const size_t a_halves = (size_t)batches * nch * Tq * 64, w_halves = (size_t)batches * tiles_n * nch * 128 * 64;
+  return a_halves / 2 < (1ull << 31) && w_halves / 2 < (1ull << 31);
+}
+
+// P@V with the probabilities already in packed f16 form (p16 == nullptr: pack them from the f32 tensor p).
+static int pv_core(fa_ctx *ctx, const float *p, const __half *p16, const float *v, float *out, __half *out16, int Tq, int Tk,
+                   int H, int HD, int W) {
+  const long long batches = (long long)W * H;
   const int S = H * HD, nch = ceil_div(Tk, 64), tiles_n = ceil_div(HD, 128);
   const size_t a_halves = (size_t)batches * nch * Tq * 64, w_halves = (size_t)batches * tiles_n * nch * 128 * 64;
-  if (a_halves / 2 >= (1ull << 31) || w_halves / 2 >= (1ull << 31)) return FA_OK;
   Block ap(ctx), wp(ctx);
-  FA_TRY(ap.get(a_halves * 2));
   FA_TRY(wp.get(w_halves * 2));
-  {
-    LaunchScope ls(ctx, "attn_pack_p");
-    k_pack_act_probs<<<grid_for(ctx, a_halves / 2), 256, 0, ctx->stream>>>(p, (__half *)ap.p, Tq, Tk, nch,
-                                                                          (unsigned)(a_halves / 2));
+  if (!p16) {
+    FA_TRY(ap.get(a_halves * 2));
+    {
+      LaunchScope ls(ctx, "attn_pack_p");
+      k_pack_act_probs<<<grid_for(ctx, a_halves / 2), 256, 0, ctx->stream>>>(p, (__half *)ap.p, Tq, Tk, nch,
+                                                                            (unsigned)(a_halves / 2));
+    }
+    FA_LAUNCH_CHECK(ctx, "attn_pack_p");
+    p16 = (const __half *)ap.p;
   }
-  FA_LAUNCH_CHECK(ctx, "attn_pack_p");
   {
     LaunchScope ls(ctx, "attn_pack_v");
     k_pack_w_vT<<<(unsigned)(batches * nch), 256, (size_t)64 * (HD + 1) * 4, ctx->stream>>>(v, (__half *)wp.p, Tk, S, H, HD,
@@ -185,7 +230,47 @@ int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half
   ep.o16_rows = W * Tq;
   ep.o16_row_hi = Tq;
   ep.o16_col_lo = HD;
-  FA_TRY(fa_tc_gemm_f16(ctx, (const __half *)ap.p, (const __half *)wp.p, out, Tq, HD, Tk, ep));
+  return fa_tc_gemm_f16(ctx, p16, (const __half *)wp.p, out, Tq, HD, Tk, ep);
+}
+
+int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half *out16, int Tq, int Tk, int H, int HD,
+                 int W, bool *done) {
+  *done = false;
+  if (!pv_shape_ok(ctx, Tq, Tk, H, HD, W)) return FA_OK;
+  FA_TRY(pv_core(ctx, p, nullptr, v, out, out16, Tq, Tk, H, HD, W));
+  *done = true;
+  return FA_OK;
+}
+
+// Fused rel-pos self-attention (the optional attnFused member, src/gpu/compute.d.ts:247-248; op sequence
+// of src/engines/asr-parakeet/raw-encoder.js:335-341): content scores and positional scores on the
+// batched tensor-core GEMM, then ONE pass that shifts, adds, normalises and emits the probabilities as
+// the packed f16 operand of the P@V product - the [W*H*T, T] probability tensor is never stored in f32.
+int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
+                     const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done) {
+  *done = false;
+  const int P = 2 * T - 1;
+  const long long batches = (long long)W * H;
+  if (!pv_shape_ok(ctx, T, T, H, HD, W) || batches * T * P >= (1ll << 31)) return FA_OK;
+  Block ac(ctx), bd(ctx), pr(ctx);
+  FA_TRY(ac.get((size_t)batches * T * T * 4));
+  FA_TRY(bd.get((size_t)batches * T * P * 4));
+  bool ok1 = false, ok2 = false;
+  FA_TRY(fa_tc_bmm_qk(ctx, q, k, pbu, (float *)ac.p, T, T, H, HD, W, 0, &ok1));
+  if (!ok1) return FA_OK;
+  FA_TRY(fa_tc_bmm_qk(ctx, q, pos, pbv, (float *)bd.p, T, P, H, HD, W, 1, &ok2));
+  if (!ok2) return FA_OK;
+  const int nch = ceil_div(T, 64);
+  FA_TRY(pr.get((size_t)batches * nch * T * 64 * 2));
+  {
+    LaunchScope ls(ctx, "attn_softmax_shift_pack");
+    const int rows = (int)(batches * T);
+    int grid = ceil_div(rows, 8);
+    if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
+    k_softmax_shift_pack<<<grid, 256, 0, ctx->stream>>>((const float *)ac.p, (const float *)bd.p, (__half *)pr.p, rows, T, nch);
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_softmax_shift_pack");
+  FA_TRY(pv_core(ctx, nullptr, (const __half *)pr.p, v, out, out16, T, T, H, HD, W));
   *done = true;
   return FA_OK;
 }

@@ -62,6 +62,75 @@ __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, 
   }
 }
 
+// Row held in registers (C % 4 == 0, C <= 4096): one global read, one write.  Same two-pass
+// mean / variance arithmetic as above.
+template <int V4>  // float4 per thread
+__global__ void __launch_bounds__(256) k_layernorm_reg(const float *__restrict__ x, const float *__restrict__ g,
+                                                       const float *__restrict__ b, float *__restrict__ y,
+                                                       __half *__restrict__ y16, int R, int C, float eps) {
+  __shared__ float red[8];
+  __shared__ float stat;
+  const int r = blockIdx.x, c4 = C >> 2;
+  const float4 *row = (const float4 *)(x + (size_t)r * C);
+  float4 v[V4];
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < V4; u++) {
+    const int q = threadIdx.x + u * 256;
+    v[u] = q < c4 ? row[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; w++) t += red[w];
+    stat = t / (float)C;
+  }
+  __syncthreads();
+  const float mean = stat;
+  float vs = 0.f;
+#pragma unroll
+  for (int u = 0; u < V4; u++) {
+    const int q = threadIdx.x + u * 256;
+    if (q < c4) {
+      const float a = v[u].x - mean, bb = v[u].y - mean, c = v[u].z - mean, d = v[u].w - mean;
+      vs += (a * a + bb * bb) + (c * c + d * d);
+    }
+  }
+  vs = warp_sum(vs);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = vs;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; w++) t += red[w];
+    stat = 1.0f / sqrtf(t / (float)C + eps);
+  }
+  __syncthreads();
+  const float inv = stat;
+#pragma unroll
+  for (int u = 0; u < V4; u++) {
+    const int q = threadIdx.x + u * 256;
+    if (q < c4) {
+      const float4 gg = ((const float4 *)g)[q], bb = ((const float4 *)b)[q];
+      float4 o;
+      o.x = (v[u].x - mean) * inv * gg.x + bb.x;
+      o.y = (v[u].y - mean) * inv * gg.y + bb.y;
+      o.z = (v[u].z - mean) * inv * gg.z + bb.z;
+      o.w = (v[u].w - mean) * inv * gg.w + bb.w;
+      ((float4 *)(y + (size_t)r * C))[q] = o;
+      if (y16) {
+        const int j = q * 4;
+        __half2 *d16 = (__half2 *)(y16 + ((size_t)(j >> 6) * R + r) * 64 + (j & 63));
+        d16[0] = __floats2half2_rn(o.x, o.y);
+        d16[1] = __floats2half2_rn(o.z, o.w);
+      }
+    }
+  }
+}
+
 // One warp per row (wasm-context.js:327-343).
 __global__ void k_softmax(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
   const int warps = (blockDim.x >> 5);
@@ -76,6 +145,50 @@ __global__ void k_softmax(const float *__restrict__ x, float *__restrict__ y, in
     s = warp_sum(s);
     const float inv = 1.0f / s;
     for (int j = lane; j < C; j += 32) y[(size_t)r * C + j] = expf(row[j] - mx) * inv;
+  }
+}
+
+// Rows of up to 256 columns: the row lives in registers (8 values per lane), one read and one write.
+__global__ void k_softmax_reg(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+    const float *row = x + (size_t)r * C;
+    float v[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int j = lane + 32 * u;
+      v[u] = j < C ? row[j] : -INFINITY;
+      mx = fmaxf(mx, v[u]);
+    }
+    mx = warp_max(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      v[u] = lane + 32 * u < C ? expf(v[u] - mx) : 0.f;
+      s += v[u];
+    }
+    s = warp_sum(s);
+    const float inv = 1.0f / s;
+#pragma unroll
+    for (int u = 0; u < 8; u++)
+      if (lane + 32 * u < C) y[(size_t)r * C + lane + 32 * u] = v[u] * inv;
+  }
+}
+
+// float4 forms of the elementwise family (n % 4 == 0, 16-byte aligned operands)
+__global__ void k_ewise4(const float4 *__restrict__ a, const float4 *__restrict__ b, float4 *__restrict__ y, unsigned n4,
+                         int mul) {
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    const float4 p = a[i], q = b[i];
+    y[i] = mul ? make_float4(p.x * q.x, p.y * q.y, p.z * q.z, p.w * q.w) : make_float4(p.x + q.x, p.y + q.y, p.z + q.z, p.w + q.w);
+  }
+}
+__global__ void k_glu4(const float4 *__restrict__ x, float4 *__restrict__ y, unsigned n4) {
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    const float4 p = x[i], q = x[i + n4];
+    y[i] = make_float4(p.x * (1.0f / (1.0f + expf(-q.x))), p.y * (1.0f / (1.0f + expf(-q.y))),
+                       p.z * (1.0f / (1.0f + expf(-q.z))), p.w * (1.0f / (1.0f + expf(-q.w))));
   }
 }
 
@@ -131,15 +244,16 @@ __global__ void k_sub_reshape(const float *__restrict__ x, float *__restrict__ y
     y[i] = x[(size_t)c * Tsub * F + (size_t)ho * F + wo];
   }
 }
-// Batched rel_shift (wasm-context.js:525-538): x[H*t, 2t-1] -> [H*t, t]
-__global__ void k_rel_shift_b(const float *__restrict__ x, float *__restrict__ y, int H, int t) {
-  const int p = 2 * t - 1, twoT = 2 * t;
-  size_t n = (size_t)H * t * t;
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
-    int j = (int)(idx % t), i = (int)((idx / t) % t), h = (int)(idx / ((size_t)t * t));
-    long long f = (long long)t + (long long)i * p + j;
-    int col = (int)(f % twoT);
-    y[idx] = col == 0 ? 0.0f : x[((size_t)h * t + (size_t)(f / twoT)) * p + (col - 1)];
+// Batched rel_shift (wasm-context.js:525-538): x[H*t, 2t-1] -> [H*t, t].  With f = t + i*(2t-1) + j the
+// reference reads row f / 2t, column f % 2t - 1; for 0 <= i, j < t that is row i, column t-1-i+j (never
+// the zero column), so every output row is one contiguous run of its input row.
+__global__ void k_rel_shift_b(const float *__restrict__ x, float *__restrict__ y, int rows, int t) {
+  const int p = 2 * t - 1;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int i = r % t;
+    const float *src = x + (size_t)r * p + (t - 1 - i);
+    float *dst = y + (size_t)r * t;
+    for (int j = threadIdx.x; j < t; j += blockDim.x) dst[j] = src[j];
   }
 }
 
@@ -268,6 +382,48 @@ __global__ void k_conv1d(const float *__restrict__ x, const float *__restrict__ 
     if (bias) acc += bias[co];
     y[idx] = fa_actf(acc, act);
   }
+}
+
+// Depthwise forms (one filter per channel): channel = blockIdx.y, threads walk the output row/plane, so
+// the only integer division left is the window / row split.
+__global__ void __launch_bounds__(256) k_dwconv1d(const float *__restrict__ x, const float *__restrict__ w,
+                                                  const float *__restrict__ bias, float *__restrict__ y, int L, int Lw,
+                                                  int k, int padl, int dil, int act) {
+  const int c = blockIdx.y, t = blockIdx.x * 256 + threadIdx.x;
+  if (t >= L) return;
+  const int wbase = (t / Lw) * Lw, tl = t - wbase;
+  const float *xr = x + (size_t)c * L + wbase;
+  const float *wr = w + (size_t)c * k;
+  float acc = 0.f;
+  for (int kk = 0; kk < k; kk++) {
+    const int xi = tl + kk * dil - padl;
+    if (xi >= 0 && xi < Lw) acc = fmaf(xr[xi], __ldg(wr + kk), acc);
+  }
+  if (bias) acc += bias[c];
+  y[(size_t)c * L + t] = fa_actf(acc, act);
+}
+
+__global__ void __launch_bounds__(256) k_dwconv2d_3x3(const float *__restrict__ x, const float *__restrict__ w,
+                                                      const float *__restrict__ bias, float *__restrict__ y, int h, int W,
+                                                      int sh, int sw, int pt, int pl, int Ho, int Wo, int act) {
+  const int c = blockIdx.y;
+  const unsigned plane = (unsigned)Ho * Wo, pos = blockIdx.x * 256 + threadIdx.x;
+  if (pos >= plane) return;
+  const int ho = (int)(pos / (unsigned)Wo), wo = (int)(pos % (unsigned)Wo);
+  const float *xp = x + (size_t)c * h * W;
+  const float *wp = w + (size_t)c * 9;
+  float acc = bias ? bias[c] : 0.f;
+#pragma unroll
+  for (int a = 0; a < 3; a++) {
+    const int hi = ho * sh + a - pt;
+    if (hi < 0 || hi >= h) continue;
+#pragma unroll
+    for (int b = 0; b < 3; b++) {
+      const int wi = wo * sw + b - pl;
+      if (wi >= 0 && wi < W) acc = fmaf(xp[(size_t)hi * W + wi], __ldg(wp + a * 3 + b), acc);
+    }
+  }
+  y[(size_t)c * plane + pos] = fa_actf(acc, act);
 }
 
 // Direct 2-D conv, batch 1 (wasm-context.js:632-685): one thread per output element.
@@ -401,8 +557,14 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
       __half *y16 = nullptr;
       if ((x->cols & 63) == 0 && x->rows >= 16 && fa_tc_available(ctx) && (y16 = fa_shadow_block(ctx, y)) != nullptr)
         y->a16_valid = true;
-      k_layernorm<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)gamma->dptr,
-                                                 (const float *)beta->dptr, (float *)y->dptr, y16, x->rows, x->cols, eps);
+      const float *xp = (const float *)x->dptr, *gp = (const float *)gamma->dptr, *bp = (const float *)beta->dptr;
+      const bool al = (((uintptr_t)xp | (uintptr_t)gp | (uintptr_t)bp | (uintptr_t)y->dptr) & 15) == 0;
+      if ((x->cols & 3) == 0 && x->cols <= 1024 && al)
+        k_layernorm_reg<1><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
+      else if ((x->cols & 3) == 0 && x->cols <= 4096 && al)
+        k_layernorm_reg<4><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
+      else
+        k_layernorm<<<grid, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
     }
     FA_LAUNCH_CHECK(ctx, "layernorm");
   }
@@ -420,7 +582,10 @@ extern "C" int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
     if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
     {
       LaunchScope ls(ctx, "softmax");
-      k_softmax<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+      if (x->cols <= 256)
+        k_softmax_reg<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+      else
+        k_softmax<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
     }
     FA_LAUNCH_CHECK(ctx, "softmax");
   }
@@ -441,8 +606,12 @@ extern "C" int fa_ewise(fa_ctx *ctx, const fa_tensor *a, const fa_tensor *b, int
   if (n) {
     {
       LaunchScope ls(ctx, "ewise");
-      k_ewise<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)a->dptr, (const float *)b->dptr,
-                                                            (float *)y->dptr, n, a->cols, bcast ? 1 : 0, op_mul);
+      if (!bcast && (n & 3) == 0 && n / 4 < (1ull << 32))
+        k_ewise4<<<grid1d(ctx, n / 4, 256), 256, 0, ctx->stream>>>((const float4 *)a->dptr, (const float4 *)b->dptr,
+                                                                   (float4 *)y->dptr, (unsigned)(n / 4), op_mul);
+      else
+        k_ewise<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)a->dptr, (const float *)b->dptr,
+                                                              (float *)y->dptr, n, a->cols, bcast ? 1 : 0, op_mul);
     }
     FA_LAUNCH_CHECK(ctx, "ewise");
   }
@@ -495,7 +664,10 @@ extern "C" int fa_glu(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
   if (n) {
     {
       LaunchScope ls(ctx, "glu");
-      k_glu<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows / 2, x->cols);
+      if ((n & 3) == 0 && n / 4 < (1ull << 31))
+        k_glu4<<<grid1d(ctx, n / 4, 256), 256, 0, ctx->stream>>>((const float4 *)x->dptr, (float4 *)y->dptr, (unsigned)(n / 4));
+      else
+        k_glu<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows / 2, x->cols);
     }
     FA_LAUNCH_CHECK(ctx, "glu");
   }
@@ -644,7 +816,8 @@ extern "C" int fa_rel_shift_b(fa_ctx *ctx, const fa_tensor *x, int H, fa_tensor 
   if (n) {
     {
       LaunchScope ls(ctx, "rel_shift_b");
-      k_rel_shift_b<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, H, t);
+      const int rows = H * t, rgrid = rows < ctx->sm_count * 32 ? rows : ctx->sm_count * 32;
+      k_rel_shift_b<<<rgrid, t >= 128 ? 128 : 64, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, rows, t);
     }
     FA_LAUNCH_CHECK(ctx, "rel_shift_b");
   }
@@ -737,6 +910,17 @@ static int conv1d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, cout, Lout, FA_F32, true, &y));
   size_t n = (size_t)cout * Lout;
+  if (groups == cin && cout == cin && stride == 1 && Lout == L && cout <= 65535) {
+    {
+      LaunchScope ls(ctx, "dwconv1d");
+      k_dwconv1d<<<dim3(ceil_div(L, 256), cout), 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
+                                                                       bias ? (const float *)bias->dptr : nullptr,
+                                                                       (float *)y->dptr, L, Lw, k, pad_left, dilation, act);
+    }
+    FA_LAUNCH_CHECK(ctx, "dwconv1d");
+    *out = y;
+    return FA_OK;
+  }
   {
     LaunchScope ls(ctx, windows > 1 ? "conv1d_windows" : "conv1d");
     k_conv1d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
@@ -744,6 +928,33 @@ static int conv1d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
                                                            cout, cin, L, Lout, Lw, k, stride, pad_left, dilation, groups, act);
   }
   FA_LAUNCH_CHECK(ctx, "conv1d");
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k, const fa_tensor *v, const fa_tensor *pos,
+                             const fa_tensor *pbu, const fa_tensor *pbv, int H, int HD, int W, fa_tensor **out) {
+  GLUE_PROLOGUE("attnFused");
+  *out = nullptr;
+  const fa_tensor *ts[6] = {q, k, v, pos, pbu, pbv};
+  for (int i = 0; i < 6; i++) FA_TRY(need_f32(ctx, ts[i], "attnFused"));
+  FA_REQUIRE(ctx, H > 0 && HD > 0 && W > 0 && q->rows % W == 0, "attnFused: bad geometry");
+  const int T = q->rows / W, S = H * HD;
+  FA_REQUIRE(ctx, q->cols == S && k->cols == S && v->cols == S && pos->cols == S && k->rows == q->rows && v->rows == q->rows &&
+                      pos->rows == 2 * T - 1 && pbu->rows * pbu->cols >= S && pbv->rows * pbv->cols >= S,
+             "attnFused: operand shapes do not match T=%d H=%d HD=%d W=%d", T, H, HD, W);
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, W * T, S, FA_F32, true, &y));
+  __half *y16 = (S & 63) == 0 && (HD & 31) == 0 ? fa_shadow_block(ctx, y) : nullptr;
+  bool done = false;
+  int rc = fa_tc_attn_fused(ctx, (const float *)q->dptr, (const float *)k->dptr, (const float *)v->dptr,
+                            (const float *)pos->dptr, (const float *)pbu->dptr, (const float *)pbv->dptr, (float *)y->dptr,
+                            y16, T, H, HD, W, &done);
+  if (rc != FA_OK || !done) {  // not this shape: the caller falls back to the separate ops (may return null)
+    fa_free_tensor(ctx, y);
+    return rc;
+  }
+  if (y16) y->a16_valid = true;
   *out = y;
   return FA_OK;
 }
@@ -814,6 +1025,17 @@ extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
                                                      w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act);
     }
     FA_LAUNCH_CHECK(ctx, "conv2d_c1_3x3");
+    *out = y;
+    return FA_OK;
+  }
+  if (groups == cin && cout == cin && kh == 3 && kw == 3 && cout <= 65535) {
+    {
+      LaunchScope ls(ctx, "dwconv2d_3x3");
+      k_dwconv2d_3x3<<<dim3(ceil_div(Ho * Wo, 256), cout), 256, 0, ctx->stream>>>(
+          (const float *)x->dptr, (const float *)w->dptr, bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr, h,
+          w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act);
+    }
+    FA_LAUNCH_CHECK(ctx, "dwconv2d_3x3");
     *out = y;
     return FA_OK;
   }

@@ -254,6 +254,8 @@ int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, f
                  int W, int b_shared, bool *done);
 int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half *out16, int Tq, int Tk, int H, int HD,
                  int W, bool *done);
+int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
+                     const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done);
 // Shadow management (fa_linalg.cu): block for t's packed f16 shadow (nullptr when t cannot carry one),
 // and the shadow itself, built by the prepass when no producer wrote it.
 __half *fa_shadow_block(fa_ctx *ctx, fa_tensor *t);

@@ -153,10 +153,14 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                         enc["_posProj"][(L, Tsub)] = p
                 else:
                     p = ctx.matmul(peT, w["pos"])
-                ac = ctx.bmmQK(q, k, w["pbuAll"], H, HD, W)
-                bd = ctx.relShiftB(ctx.bmmQK(q, p, w["pbvAll"], H, HD, W, True), W * H)
-                probs = ctx.softmax(ctx.add(ac, bd))
-                outc = ctx.bmmPV(probs, v, H, HD, W)
+                outc = None
+                if use_fast and getattr(ctx, "attnFused", None):  # optional member, may decline (:333-336)
+                    outc = ctx.attnFused(q, k, v, p, w["pbuAll"], w["pbvAll"], H, HD, W)
+                if outc is None:
+                    ac = ctx.bmmQK(q, k, w["pbuAll"], H, HD, W)
+                    bd = ctx.relShiftB(ctx.bmmQK(q, p, w["pbvAll"], H, HD, W, True), W * H)
+                    probs = ctx.softmax(ctx.add(ac, bd))
+                    outc = ctx.bmmPV(probs, v, H, HD, W)
                 x = ctx.matmul(outc, w["out"], dict(bias=w["outb"], add=x))
                 pre1 = ctx.matmul(ln(x, w["lnconv"]), w["pw1T"], dict(bias=w["pw1b"]))  # [W*T, 2D]
                 glu = ctx.glu(ctx.transpose(pre1))  # [D, W*T]

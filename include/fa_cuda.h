@@ -164,6 +164,11 @@ int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tens
 int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, const fa_tensor *qb, int H, int HD, int W,
               int b_shared, fa_tensor **out);                                             /* bmmQK :191 */
 int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, int H, int HD, int W, fa_tensor **out); /* bmmPV :193 */
+/* attnFused :247-248 (optional member; may yield no tensor, the caller then uses the separate ops):
+ * rel-pos self-attention for W windows of T = q.rows/W frames; pos [2T-1, H*HD] is the projected
+ * positional table, pbu/pbv [1, H*HD].  *out == NULL with status 0 means "not this shape". */
+int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k, const fa_tensor *v, const fa_tensor *pos,
+                  const fa_tensor *pbu, const fa_tensor *pbv, int H, int HD, int W, fa_tensor **out);
 int fa_rel_shift_b(fa_ctx *ctx, const fa_tensor *x, int H, fa_tensor **out);              /* relShift/relShiftB :195-197 */
 int fa_ewise(fa_ctx *ctx, const fa_tensor *a, const fa_tensor *b, int op_mul, fa_tensor **out); /* ewise/add/mul :202-204 */
 int fa_scale(fa_ctx *ctx, const fa_tensor *x, float s, fa_tensor **out);                  /* scale :205 */

@@ -45,14 +45,14 @@ def test_full_width_layer_teacher_forced(ctx, pkg):
     Wn, Tsub, D = 2, 188, 1024
     x0 = rng.standard_normal((Wn * Tsub, D)).astype(np.float32)
 
-    def run_layer(c):
+    def run_layer(c, use_fast=True):
         enc = fc.load_encoder(c, w)
         # drive the block directly from a given residual stream: reuse encode_batch's body through a
         # stand-in pre-encode (the subsampling front end is covered by the tiny end-to-end case)
         orig = fc.pre_encode
         fc.pre_encode = lambda c_, e_, m_: (c_.upload(m_, Tsub, D), Tsub)
         try:
-            out, _ = fc.encode_batch(c, enc, [x0[i * Tsub:(i + 1) * Tsub] for i in range(Wn)])
+            out, _ = fc.encode_batch(c, enc, [x0[i * Tsub:(i + 1) * Tsub] for i in range(Wn)], use_fast=use_fast)
         finally:
             fc.pre_encode = orig
         return out
@@ -60,6 +60,8 @@ def test_full_width_layer_teacher_forced(ctx, pkg):
     ora = WasmOracle(threads=True)
     ref = run_layer(ora).array()
     h = ctx.pushArena()
-    got = ctx.download(run_layer(ctx)).reshape(ref.shape)
+    got = ctx.download(run_layer(ctx)).reshape(ref.shape)            # optional fast members (fused attention, ...)
+    got_seq = ctx.download(run_layer(ctx, False)).reshape(ref.shape)  # the reference's exact op sequence
     ctx.popArena(h)
     assert np.abs(got - ref).max() <= 2e-2
+    assert np.abs(got_seq - ref).max() <= 2e-2
