@@ -380,6 +380,41 @@ class Encoder:
                 "frac": None, "traffic": None, "kernel": "tc_gemm_f16", "launches": e["count"],
                 "avg_launch_us": round(e["ms"] / e["count"] * 1e3, 2), "peak_source": peaks["source"] + " (sustained bf16)"}
 
+    def roofline_live(self, ctx, peaks, timer):
+        """The dominant kernel on its own: the ten weight products of one conformer block at this batch's
+        M (2x FF up, 2x FF down, q/k/v/out/pw2 at D x D, pw1 at D x 2D), recorded back to back and replayed;
+        achieved = their algorithmic FLOPs / CUDA-event time.  The row operands are already packed, as they
+        are inside the forward (producers hand them over as f16)."""
+        D, DFF, M = 1024, 4096, self.W * 188
+        rng = np.random.default_rng(5)
+        x1 = ctx.upload(rng.standard_normal((M, D)).astype(np.float32), M, D)
+        x4 = ctx.upload(rng.standard_normal((M, DFF)).astype(np.float32), M, DFF)
+        L0 = self.enc["layers"][0]
+        seq = [(x1, L0["ff1w1"]), (x4, L0["ff1w2"]), (x1, L0["q"]), (x1, L0["k"]), (x1, L0["v"]), (x1, L0["out"]),
+               (x1, L0["pw1T"]), (x1, L0["pw2T"]), (x1, L0["ff2w1"]), (x4, L0["ff2w2"])]
+        flops = sum(2.0 * a.rows * a.cols * b.cols for a, b in seq)
+
+        def body():
+            h = ctx.pushArena()
+            for a, b in seq:
+                ctx.matmul(a, b)
+            ctx.popArena(h)
+
+        body()
+        batch, _ = ctx.recordBatch(body)
+        reps = 5
+        ms = timer(lambda _c: batch.launch(), reps)
+        batch.free()
+        ctx.freeTensor(x1)
+        ctx.freeTensor(x4)
+        ach = flops * reps / (ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"]
+        return {"bound": "tensor", "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
+                "traffic": None, "kernel": "k_tc_gemm<f16> (label tc_gemm_f16)", "launches_timed": len(seq) * reps,
+                "avg_launch_us": round(ms * 1e3 / (len(seq) * reps), 2),
+                "what": "the 10 weight products of one conformer block at M=%d, back to back (recorded batch)" % M,
+                "peak_source": peaks["source"] + " (burst bf16: kernel timed alone)"}
+
     def cpu_sample(self, threads=True):
         """One conformer block on one 15 s window on the CPU port, scaled to the full stack."""
         from oracle.wasm_oracle import WasmOracle
@@ -504,7 +539,13 @@ def run_cuda(args):
     prof = ctx.endProfile()
     peaks = measured_peaks()
     roof = wl.roofline(prof, peaks)
-    if roof is not None and roof.get("frac") is None:  # per-step figure over a profile of `steps` steps
+    if hasattr(wl, "roofline_live"):
+        in_step = roof
+        roof = wl.roofline_live(ctx, peaks, timed)
+        if in_step is not None:
+            roof["in_step_profile"] = {"launches": in_step.get("launches"), "avg_launch_us": in_step.get("avg_launch_us"),
+                                       "note": "per-launch event pairs inside the eager forward; includes launch gaps"}
+    elif roof is not None and roof.get("frac") is None:  # per-step figure over a profile of `steps` steps
         roof["achieved"] = round(roof["achieved"] * args.steps, 1)
         roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
 

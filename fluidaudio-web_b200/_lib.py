@@ -63,6 +63,7 @@ SIGNATURES = {
     "fa_softmax": [P, P, PP],
     "fa_conv1d": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
     "fa_conv1d_windows": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
+    "fa_glu_dwconv_tm": [P, P, P, P, I, I, I, I, I, PP],
     "fa_conv2d": [P, P, P, P] + [I] * 14 + [PP],
     "fa_bmm_qk": [P, P, P, P, I, I, I, I, PP],
     "fa_bmm_pv": [P, P, P, I, I, I, PP],

@@ -289,6 +289,14 @@ class CudaContext:
         return self._op(self._lib.fa_conv1d_windows, x.h, w.h, self._h_of(opts.get("bias")), opts["cout"], opts["k"], pl, pr,
                         opts.get("dilation", 1), opts.get("groups", 1), ACT[opts.get("act", "none")], windows)
 
+    def gluDwConvTimeMajor(self, x, w, opts: dict, windows: int) -> Tensor:
+        """transpose -> glu -> per-window depthwise conv1d(+act) -> transpose of the conformer conv module
+        (raw-encoder.js:340-362) in one launch, time-major in and out: x [W*T, 2D] -> [W*T, D]."""
+        pl = opts.get("padLeft", opts.get("pad", 0))
+        pr = opts.get("padRight", opts.get("pad", 0))
+        return self._op(self._lib.fa_glu_dwconv_tm, x.h, w.h, self._h_of(opts.get("bias")), opts["k"], pl, pr,
+                        ACT[opts.get("act", "none")], windows)
+
     def conv2d(self, x, weight, opts: Optional[dict] = None, **kw) -> Tensor:
         o = dict(opts or {})
         o.update(kw)

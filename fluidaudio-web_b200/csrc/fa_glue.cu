@@ -426,6 +426,84 @@ __global__ void __launch_bounds__(256) k_dwconv2d_3x3(const float *__restrict__ 
   y[(size_t)c * plane + pos] = fa_actf(acc, act);
 }
 
+// The conformer conv module between its two pointwise projections, in the time-major layout the
+// projections use (src/engines/asr-parakeet/raw-encoder.js:340-362 does it as transpose -> glu ->
+// per-window depthwise conv1d(+act) -> transpose): x [W*T, 2D] -> y [W*T, D],
+//   y[t][c] = act( bias[c] + sum_k w[c][k] * g[t + k - padl][c] ),  g[t][c] = x[t][c] * sigmoid(x[t][c + D]),
+// taps outside the window of t read zero.  Lanes walk channels, so every access is coalesced; the result is
+// also emitted as the packed f16 row operand of the projection that follows.
+__global__ void __launch_bounds__(256) k_glu_dwconv_tm(const float *__restrict__ x, const float *__restrict__ w,
+                                                       const float *__restrict__ bias, float *__restrict__ y,
+                                                       __half *__restrict__ y16, int rows, int Tw, int D, int k, int padl,
+                                                       int act) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= D) return;
+  float wk[16];
+#pragma unroll
+  for (int kk = 0; kk < 16; kk++) wk[kk] = kk < k ? w[(size_t)c * k + kk] : 0.f;
+  const float b = bias ? bias[c] : 0.f;
+  const int t0 = blockIdx.y * 16;  // 16 consecutive frames per CTA row block
+  for (int t = t0; t < t0 + 16 && t < rows; t++) {
+    const int wbase = (t / Tw) * Tw, tl = t - wbase;
+    float acc = b;
+#pragma unroll
+    for (int kk = 0; kk < 16; kk++) {
+      if (kk >= k) break;
+      const int tt = tl + kk - padl;
+      if (tt >= 0 && tt < Tw) {
+        const float *xr = x + (size_t)(wbase + tt) * (2 * D);
+        acc = fmaf(wk[kk], xr[c] * (1.0f / (1.0f + expf(-xr[c + D]))), acc);
+      }
+    }
+    const float o = fa_actf(acc, act);
+    y[(size_t)t * D + c] = o;
+    if (y16) y16[((size_t)(c >> 6) * rows + t) * 64 + (c & 63)] = __float2half_rn(o);
+  }
+}
+
+// Same operation with the tap count known at compile time: a thread owns one channel and 16 consecutive
+// frames, evaluates the gated values of the 16+K-1 frames it needs once (one exp each) and slides the
+// filter over them in registers.
+template <int K>
+__global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict__ x, const float *__restrict__ w,
+                                                         const float *__restrict__ bias, float *__restrict__ y,
+                                                         __half *__restrict__ y16, int rows, int Tw, int D, int padl,
+                                                         int act) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= D) return;
+  float wk[K];
+#pragma unroll
+  for (int kk = 0; kk < K; kk++) wk[kk] = w[(size_t)c * K + kk];
+  const float b = bias ? bias[c] : 0.f;
+  const int t0 = blockIdx.y * 16;
+  float g[16 + K - 1];
+  int win[16 + K - 1];
+#pragma unroll
+  for (int j = 0; j < 16 + K - 1; j++) {
+    const int tg = t0 - padl + j;
+    g[j] = 0.f;
+    win[j] = -1;
+    if (tg >= 0 && tg < rows) {
+      const float *xr = x + (size_t)tg * (2 * D);
+      g[j] = xr[c] * (1.0f / (1.0f + expf(-xr[c + D])));
+      win[j] = tg / Tw;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; i++) {
+    const int t = t0 + i;
+    if (t >= rows) break;
+    const int wt = t / Tw;  // window of frame t itself
+    float acc = b;
+#pragma unroll
+    for (int kk = 0; kk < K; kk++)
+      if (win[i + kk] == wt) acc = fmaf(wk[kk], g[i + kk], acc);
+    const float o = fa_actf(acc, act);
+    y[(size_t)t * D + c] = o;
+    if (y16) y16[((size_t)(c >> 6) * rows + t) * 64 + (c & 63)] = __float2half_rn(o);
+  }
+}
+
 // Direct 2-D conv, batch 1 (wasm-context.js:632-685): one thread per output element.
 __global__ void k_conv2d(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                          float *__restrict__ y, int cout, int cin, int h, int W, int kh, int kw, int sh, int sw, int pt,
@@ -955,6 +1033,42 @@ extern "C" int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k
     return rc;
   }
   if (y16) y->a16_valid = true;
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_glu_dwconv_tm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int k,
+                                int pad_left, int pad_right, int act, int windows, fa_tensor **out) {
+  GLUE_PROLOGUE("gluDwConvTimeMajor");
+  FA_TRY(need_f32(ctx, x, "gluDwConvTimeMajor"));
+  FA_TRY(need_f32(ctx, w, "gluDwConvTimeMajor"));
+  if (bias) FA_TRY(need_f32(ctx, bias, "gluDwConvTimeMajor"));
+  FA_REQUIRE(ctx, x->cols % 2 == 0 && windows >= 1 && x->rows % windows == 0, "gluDwConvTimeMajor: x is [%d,%d], %d windows",
+             x->rows, x->cols, windows);
+  const int D = x->cols / 2, rows = x->rows, Tw = rows / windows;
+  FA_REQUIRE(ctx, k >= 1 && k <= 16 && pad_left + pad_right == k - 1, "gluDwConvTimeMajor: k=%d pads %d+%d (same-length only)", k,
+             pad_left, pad_right);
+  FA_REQUIRE(ctx, (long long)w->rows * w->cols >= (long long)D * k, "gluDwConvTimeMajor: weight tensor too small");
+  if (bias) FA_REQUIRE(ctx, bias->rows * bias->cols >= D, "gluDwConvTimeMajor: bias shorter than D");
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, rows, D, FA_F32, true, &y));
+  if (rows && D) {
+    __half *y16 = nullptr;
+    if ((D & 63) == 0 && rows >= 16 && fa_tc_available(ctx) && (y16 = fa_shadow_block(ctx, y)) != nullptr) y->a16_valid = true;
+    dim3 grid(ceil_div(D, 256), ceil_div(rows, 16));
+    FA_REQUIRE(ctx, grid.y <= 65535, "gluDwConvTimeMajor: too many rows");
+    {
+      LaunchScope ls(ctx, "glu_dwconv_tm");
+      const float *bp = bias ? (const float *)bias->dptr : nullptr;
+      if (k == 9)
+        k_glu_dwconv_tm_k<9><<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr, bp,
+                                                            (float *)y->dptr, y16, rows, Tw, D, pad_left, act);
+      else
+        k_glu_dwconv_tm<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr,
+                                                       y16, rows, Tw, D, k, pad_left, act);
+    }
+    FA_LAUNCH_CHECK(ctx, "glu_dwconv_tm");
+  }
   *out = y;
   return FA_OK;
 }

@@ -163,17 +163,21 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                     outc = ctx.bmmPV(probs, v, H, HD, W)
                 x = ctx.matmul(outc, w["out"], dict(bias=w["outb"], add=x))
                 pre1 = ctx.matmul(ln(x, w["lnconv"]), w["pw1T"], dict(bias=w["pw1b"]))  # [W*T, 2D]
-                glu = ctx.glu(ctx.transpose(pre1))  # [D, W*T]
                 opts = dict(cout=D, k=dwK, groups=D, padLeft=dwPadL, padRight=dwPadR, bias=w["dwb"], act="silu")
-                if W == 1:
-                    dwo = ctx.conv1d(glu, w["dw"], opts)
-                elif use_fast and hasattr(ctx, "conv1dWindows"):  # optional member: all windows in one launch
-                    dwo = ctx.conv1dWindows(glu, w["dw"], opts, W)
-                else:  # depthwise conv is over time -> per window (:343-351)
-                    dwo = ctx.alloc(D, W * Tsub)
-                    for wi in range(W):
-                        ctx.setCols(dwo, ctx.conv1d(ctx.sliceCols(glu, wi * Tsub, Tsub), w["dw"], opts), wi * Tsub)
-                x = ctx.matmul(ctx.transpose(dwo), w["pw2T"], dict(bias=w["pw2b"], add=x))
+                if use_fast and hasattr(ctx, "gluDwConvTimeMajor"):  # optional member: the module's middle in one launch
+                    dwoT = ctx.gluDwConvTimeMajor(pre1, w["dw"], opts, W)  # [W*T, D]
+                else:
+                    glu = ctx.glu(ctx.transpose(pre1))  # [D, W*T]
+                    if W == 1:
+                        dwo = ctx.conv1d(glu, w["dw"], opts)
+                    elif use_fast and hasattr(ctx, "conv1dWindows"):  # optional member: all windows in one launch
+                        dwo = ctx.conv1dWindows(glu, w["dw"], opts, W)
+                    else:  # depthwise conv is over time -> per window (:343-351)
+                        dwo = ctx.alloc(D, W * Tsub)
+                        for wi in range(W):
+                            ctx.setCols(dwo, ctx.conv1d(ctx.sliceCols(glu, wi * Tsub, Tsub), w["dw"], opts), wi * Tsub)
+                    dwoT = ctx.transpose(dwo)
+                x = ctx.matmul(dwoT, w["pw2T"], dict(bias=w["pw2b"], add=x))
                 x = ff(x, w["lnff2"], w["ff2w1"], w["ff2w2"], w["ff2b1"], w["ff2b2"])
                 x = ln(x, w["lnout"])
                 ctx.pin(x, True)  # x feeds the next layer: promote to the enclosing arena

@@ -157,6 +157,11 @@ int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tens
  * per-window op sequence gives the same result. */
 int fa_conv1d_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k,
                       int pad_left, int pad_right, int dilation, int groups, int act, int windows, fa_tensor **out);
+/* The conv module's middle (transpose -> glu -> per-window depthwise conv1d + act -> transpose,
+ * raw-encoder.js:340-362) as one call in time-major layout: x [W*T, 2D] -> [W*T, D]; w = D*k depthwise
+ * taps, same-length output (pad_left + pad_right == k-1, k <= 16).  Optional fast path. */
+int fa_glu_dwconv_tm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int k, int pad_left,
+                     int pad_right, int act, int windows, fa_tensor **out);
 /* conv2d :179 (batch 1). x [Cin, H*W] -> [Cout, Ho*Wo]. */
 int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin, int h,
               int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left,

@@ -129,3 +129,21 @@ def test_argmax_rows(ctx):
     out = ctx.download(ctx.argmaxRowsIndex(ctx.upload(x, 5, 51868))).reshape(5, 2)
     assert np.array_equal(out[:, 0].astype(np.int64), x.argmax(axis=1))
     assert np.array_equal(out[:, 1], x.max(axis=1))
+
+
+def test_conv_module_fast_members_match_the_op_sequence(ctx):
+    """conv1dWindows and gluDwConvTimeMajor (optional members) against the reference's per-window sequence
+    transpose -> glu -> sliceCols/conv1d/setCols -> transpose run on the oracle."""
+    rng = np.random.default_rng(6)
+    W, T, D, k = 3, 37, 128, 9
+    pre1, pre1o = up(ctx, rng.standard_normal((W * T, 2 * D)))
+    dw, dwo_ = up(ctx, rng.standard_normal(D * k) * 0.3)
+    b, bo = up(ctx, rng.standard_normal(D) * 0.1)
+    opts = dict(cout=D, k=k, groups=D, padLeft=4, padRight=4, act="silu")
+    gluo = ORA.glu(ORA.transpose(pre1o))
+    ref = ORA.alloc(D, W * T)
+    for wi in range(W):
+        ORA.setCols(ref, ORA.conv1d(ORA.sliceCols(gluo, wi * T, T), dwo_, dict(opts, bias=bo)), wi * T)
+    glu = ctx.glu(ctx.transpose(pre1))
+    close(ctx, ctx.conv1dWindows(glu, dw, dict(opts, bias=b), W), ref, 1e-4)
+    close(ctx, ctx.gluDwConvTimeMajor(pre1, dw, dict(opts, bias=b), W), ORA.transpose(ref), 1e-4)
