@@ -119,6 +119,107 @@ __device__ __forceinline__ void act16(float (&v)[16], int act) {
   }
 }
 
+// One tile's epilogue for one warp: TMEM lanes [32*quad, 32*quad+32) = output columns n0 + 32*quad + lane,
+// column chunks c = 16*half, 16*half + 32, ... = output rows m0 + c .. m0 + c + 15.
+template <int KIND>
+__device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_addr, int n0, int m0, int quad, int lane,
+                                              int half, float *outb, int r16, int c16, uint32_t partial) {
+  const int n = n0 + quad * 32 + lane;
+  const bool n_ok = n < p.N;
+  const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
+  const float bs = (p.bias && n_ok) ? p.bias[n] : 0.0f;
+  for (int c = half * 16; c < p.MT; c += 32) {
+    if (m0 + c >= p.M) break;  // warp-uniform: no rows left in this tile
+    uint32_t v0[16], v1[16], v2[16];
+    tmem_ld16(lane_addr + (uint32_t)c, v0);
+    if (p.limbs > 1) tmem_ld16(lane_addr + (uint32_t)(p.MT + c), v1);
+    if (p.limbs > 2) tmem_ld16(lane_addr + (uint32_t)(2 * p.MT + c), v2);
+    const bool full_rows = m0 + c + 16 <= p.M;
+    // independent loads issued together while the TMEM read is in flight
+    float rs[16], ad[16];
+    if (p.rowscale) {
+      if (full_rows) {
+        const float4 *r4 = (const float4 *)(p.rowscale + m0 + c);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          float4 t = __ldg(r4 + j);
+          rs[4 * j] = t.x; rs[4 * j + 1] = t.y; rs[4 * j + 2] = t.z; rs[4 * j + 3] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) rs[j] = __ldg(p.rowscale + min(m0 + c + j, p.M - 1));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j++) rs[j] = 1.0f;
+    }
+    if (p.add && n_ok && p.splitk <= 1) {
+#pragma unroll
+      for (int j = 0; j < 16; j++) ad[j] = __ldg(p.add + (size_t)min(m0 + c + j, p.M - 1) * p.N + n);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j++) ad[j] = 0.0f;
+    }
+    float rb[16];  // per-row bias (the output-channel bias of a pointwise convolution run as a GEMM)
+    if (p.rowbias) {
+#pragma unroll
+      for (int j = 0; j < 16; j++) rb[j] = __ldg(p.rowbias + min(m0 + c + j, p.M - 1));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j++) rb[j] = 0.0f;
+    }
+    tmem_ld_wait();
+    if (KIND == 1 && p.raw_i32 == 1) {
+      if (n_ok) {
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if (m0 + c + j < p.M) ((int32_t *)outb)[(size_t)(m0 + c + j) * p.ldc + n] = (int32_t)v0[j];
+      }
+      continue;
+    }
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      if (KIND == 0) {
+        v[j] = __uint_as_float(v0[j]);
+      } else {
+        v[j] = (float)(int32_t)v0[j];
+        if (p.limbs > 1) v[j] = fmaf((float)(int32_t)v1[j], 1.0f / 128.0f, v[j]);
+        if (p.limbs > 2) v[j] = fmaf((float)(int32_t)v2[j], 1.0f / 16384.0f, v[j]);
+      }
+    }
+    if (p.splitk > 1) {
+      // partial[m_local][n_local]: lanes write consecutive addresses
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(partial + (uint32_t)(((c + j) * 128 + quad * 32 + lane) * 4)), "f"(v[j])
+                     : "memory");
+      continue;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs) + rb[j];
+    act16(v, p.act);
+    if (n_ok) {
+      if (p.out16) {  // shadow: Ap[k/64][row][k%64] of the output tensor, 32 lanes = 64 contiguous bytes
+        const int gn = n + c16;
+        __half *h16 = p.out16 + ((size_t)(gn >> 6) * p.o16_rows + (r16 + m0 + c)) * 64 + (gn & 63);
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if (full_rows || m0 + c + j < p.M) h16[(size_t)j * 64] = __float2half_rn(v[j] + ad[j]);
+      }
+      float *orow = outb + (size_t)(m0 + c) * p.ldc + n;
+      if (full_rows) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) orow[(size_t)j * p.ldc] = v[j] + ad[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if (m0 + c + j < p.M) orow[(size_t)j * p.ldc] = v[j] + ad[j];
+      }
+    }
+  }
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
@@ -180,75 +281,86 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 
   // Role loops are executed by whole warps (lane 0 does the work, the shuffle keeps the other lanes in
   // step) so that every warp reaches the block-wide barriers converged, as aligned barriers require.
+  // The two single-lane role loops below are latency-critical: one thread issues every TMA load / every
+  // MMA of the CTA, and with no other warp on its scheduler to hide behind, each extra instruction costs its
+  // full dependent-issue latency per K chunk.  So: no division, no per-chunk warp shuffle, ring position and
+  // barrier addresses kept as running values.  Lanes 1..31 wait at the __syncwarp that closes the role, which
+  // also reconverges the warp before the block-wide barriers (aligned barriers need converged warps).
   if (warp == 0) {
     // ---- TMA producer: runs ahead across tiles, bounded only by the ring ----------------------
-    uint32_t it = 0;
-    bool stop = false;
-    for (int tile = blockIdx.x; tile < num_tiles && !stop; tile += gridDim.x) {
-      const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
-      const int tn = tin % p.tiles_n, tm = tin / p.tiles_n;
-      const int wb = p.w_batch_mod ? batch % p.w_batch_mod : batch;
-      for (int kb = kb0; kb < kb1; kb++, it++) {
-        if (lane == 0) {
-          const int s = (int)(it % (uint32_t)p.stages);
-          const uint32_t use = it / (uint32_t)p.stages;
-          if (use > 0 && !mbar_wait(empty_bar(s), (use - 1) & 1)) set_abort(1, kb);
-          if (aborted()) {
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0, it = 0;  // ring slot, parity of the slot's current use, chunks issued
+      const uint32_t nst = (uint32_t)p.stages;
+      bool stop = false;
+      for (int tile = blockIdx.x; tile < num_tiles && !stop; tile += gridDim.x) {
+        const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
+        const int tn = tin % p.tiles_n, tm = tin / p.tiles_n;
+        const int wb = p.w_batch_mod ? batch % p.w_batch_mod : batch;
+        int wrow = ((wb * p.tiles_n + tn) * p.num_kb + kb0) * 128;
+        int aslab = batch * p.limbs * p.num_kb + kb0;
+        const int m0 = tm * p.MT;
+        for (int kb = kb0; kb < kb1; kb++, it++, wrow += 128, aslab++) {
+          const uint32_t fb = bars + s * 8u, dst = smem_base + s * stage_bytes;
+          if (it >= nst && !mbar_wait(fb + nst * 8u, ph ^ 1u)) {  // empty barrier of slot s, previous use
+            set_abort(1, kb);
             stop = true;
-          } else {
-            if (it < 64) TC_TRACE(1 + it);
-            mbar_expect_tx(full_bar(s), stage_bytes);
-            const uint32_t dst = smem_base + (uint32_t)s * stage_bytes;
-            tma_load_2d(dst, &map_w, 0, ((wb * p.tiles_n + tn) * p.num_kb + kb) * 128, full_bar(s));
-            for (int l = 0; l < p.limbs; l++)
-              tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, tm * p.MT,
-                          (batch * p.limbs + l) * p.num_kb + kb, full_bar(s));
+            break;
+          }
+          if (it < 64) TC_TRACE(1 + it);
+          mbar_expect_tx(fb, stage_bytes);
+          tma_load_2d(dst, &map_w, 0, wrow, fb);
+          tma_load_3d(dst + kPTileBytes, &map_a, 0, m0, aslab, fb);
+          for (int l = 1; l < p.limbs; l++)
+            tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
+          if (++s == nst) {
+            s = 0;
+            ph ^= 1u;
           }
         }
-        stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
-        if (stop) break;
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ---- MMA issuer: alternates between the two TMEM accumulator buffers -----------------------
-    const uint32_t idesc = make_idesc(KIND, 128, q_rows);
-    uint32_t it = 0, lt = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
-      const uint32_t buf = lt & 1, use = lt >> 1;
-      if (lane == 0 && use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1)) {
-        set_abort(4, tile);
-        ok = false;
-      }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * acc_stride;
-      for (int kb = kb0; kb < kb1; kb++, it++) {
-        if (lane == 0) {
-          const int s = (int)(it % (uint32_t)p.stages);
-          const uint32_t use_s = it / (uint32_t)p.stages;
-          if (!mbar_wait(full_bar(s), use_s & 1)) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(KIND, 128, q_rows);
+      const uint32_t nst = (uint32_t)p.stages;
+      const uint64_t desc0 = smem_desc_sw128(smem_base);  // slot 0 weights tile; other tiles are address offsets
+      const uint64_t q_off = (uint64_t)(kPTileBytes >> 4), st_off = (uint64_t)(stage_bytes >> 4);
+      uint32_t s = 0, ph = 0, it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
+        const uint32_t buf = lt & 1, use = lt >> 1;
+        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1)) {
+          set_abort(4, tile);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * acc_stride;
+        for (int kb = kb0; kb < kb1; kb++, it++) {
+          const uint32_t fb = bars + s * 8u;
+          if (!mbar_wait(fb, ph)) {
             set_abort(2, kb);
             ok = false;
-          } else {
-            tc_fence_after();
-            if (it < 64) TC_TRACE(65 + it);
-            const uint32_t pa = smem_base + (uint32_t)s * stage_bytes;
-            const uint32_t qa = pa + kPTileBytes;
-#pragma unroll
-            for (int j = 0; j < 4; j++)  // 4 x 32 bytes of K per stage
-              umma<KIND>(d_tmem, smem_desc_sw128(pa + j * 32), smem_desc_sw128(qa + j * 32), idesc,
-                         (kb > kb0 || j > 0) ? 1u : 0u);
-            umma_commit(empty_bar(s));  // frees the stage when these MMAs have read it
+            break;
+          }
+          tc_fence_after();
+          if (it < 64) TC_TRACE(65 + it);
+          const uint64_t da = desc0 + (uint64_t)s * st_off, db = da + q_off;
+          umma<KIND>(d_tmem, da, db, idesc, kb > kb0 ? 1u : 0u);  // 4 x 32 bytes of K per slot
+          umma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
+          umma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
+          umma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
+          umma_commit(fb + nst * 8u);  // frees the slot when these MMAs have read it
+          if (++s == nst) {
+            s = 0;
+            ph ^= 1u;
           }
         }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
+        if (ok) umma_commit(acc_full(buf));  // this tile's accumulators are complete
       }
-      if (ok && lane == 0) umma_commit(acc_full(buf));  // this tile's accumulators are complete
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ---- epilogue: TMEM -> registers -> global (or -> smem partial in split-K mode) -------------
     const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
@@ -268,100 +380,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       tc_fence_after();
       if (threadIdx.x == 64) TC_TRACE(129);
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      const int n = n0 + quad * 32 + lane;
-      const bool n_ok = n < p.N;
-      const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
-      const float bs = (p.bias && n_ok) ? p.bias[n] : 0.0f;
-      for (int c = half * 16; c < p.MT; c += 32) {
-        if (m0 + c >= p.M) break;  // warp-uniform: no rows left in this tile
-        uint32_t v0[16], v1[16], v2[16];
-        tmem_ld16(lane_addr + (uint32_t)c, v0);
-        if (p.limbs > 1) tmem_ld16(lane_addr + (uint32_t)(p.MT + c), v1);
-        if (p.limbs > 2) tmem_ld16(lane_addr + (uint32_t)(2 * p.MT + c), v2);
-        const bool full_rows = m0 + c + 16 <= p.M;
-        // independent loads issued together while the TMEM read is in flight
-        float rs[16], ad[16];
-        if (p.rowscale) {
-          if (full_rows) {
-            const float4 *r4 = (const float4 *)(p.rowscale + m0 + c);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              float4 t = __ldg(r4 + j);
-              rs[4 * j] = t.x; rs[4 * j + 1] = t.y; rs[4 * j + 2] = t.z; rs[4 * j + 3] = t.w;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; j++) rs[j] = __ldg(p.rowscale + min(m0 + c + j, p.M - 1));
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; j++) rs[j] = 1.0f;
-        }
-        if (p.add && n_ok && p.splitk <= 1) {
-#pragma unroll
-          for (int j = 0; j < 16; j++) ad[j] = __ldg(p.add + (size_t)min(m0 + c + j, p.M - 1) * p.N + n);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; j++) ad[j] = 0.0f;
-        }
-        float rb[16];  // per-row bias (the output-channel bias of a pointwise convolution run as a GEMM)
-        if (p.rowbias) {
-#pragma unroll
-          for (int j = 0; j < 16; j++) rb[j] = __ldg(p.rowbias + min(m0 + c + j, p.M - 1));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; j++) rb[j] = 0.0f;
-        }
-        tmem_ld_wait();
-        if (KIND == 1 && p.raw_i32 == 1) {
-          if (n_ok) {
-#pragma unroll
-            for (int j = 0; j < 16; j++)
-              if (m0 + c + j < p.M) ((int32_t *)outb)[(size_t)(m0 + c + j) * p.ldc + n] = (int32_t)v0[j];
-          }
-          continue;
-        }
-        float v[16];
-#pragma unroll
-        for (int j = 0; j < 16; j++) {
-          if (KIND == 0) {
-            v[j] = __uint_as_float(v0[j]);
-          } else {
-            v[j] = (float)(int32_t)v0[j];
-            if (p.limbs > 1) v[j] = fmaf((float)(int32_t)v1[j], 1.0f / 128.0f, v[j]);
-            if (p.limbs > 2) v[j] = fmaf((float)(int32_t)v2[j], 1.0f / 16384.0f, v[j]);
-          }
-        }
-        if (p.splitk > 1) {
-          // partial[m_local][n_local]: lanes write consecutive addresses
-#pragma unroll
-          for (int j = 0; j < 16; j++)
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(partial + (uint32_t)(((c + j) * 128 + quad * 32 + lane) * 4)), "f"(v[j])
-                         : "memory");
-          continue;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs) + rb[j];
-        act16(v, p.act);
-        if (n_ok) {
-          if (p.out16) {  // shadow: Ap[k/64][row][k%64] of the output tensor, 32 lanes = 64 contiguous bytes
-            const int gn = n + c16;
-            __half *h16 = p.out16 + ((size_t)(gn >> 6) * p.o16_rows + (r16 + m0 + c)) * 64 + (gn & 63);
-#pragma unroll
-            for (int j = 0; j < 16; j++)
-              if (full_rows || m0 + c + j < p.M) h16[(size_t)j * 64] = __float2half_rn(v[j] + ad[j]);
-          }
-          float *orow = outb + (size_t)(m0 + c) * p.ldc + n;
-          if (full_rows) {
-#pragma unroll
-            for (int j = 0; j < 16; j++) orow[(size_t)j * p.ldc] = v[j] + ad[j];
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; j++)
-              if (m0 + c + j < p.M) orow[(size_t)j * p.ldc] = v[j] + ad[j];
-          }
-        }
-      }
+      epilogue_tile<KIND>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial);
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -431,6 +450,179 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ---- CTA-pair variant (f16, one limb) --------------------------------------------------------------
+// Two CTAs of a cluster work on one 256 (weights) x MT (activations) tile with tcgen05.mma.cta_group::2:
+// each CTA stages its own 128 weight rows and HALF of the activation rows, so per CTA and K chunk the
+// operand traffic is 16 KB + MT*64 B instead of 16 KB + MT*128 B - the main loop of the single-CTA kernel
+// is bound by exactly that traffic (shared-memory fill rate), not by the tensor pipe.  No TMA multicast:
+// every CTA loads only what it alone needs.  The leader (rank 0) issues the MMAs for the pair; loads of
+// both CTAs count on the leader's "full" barriers, MMA completion is signalled to both CTAs' "empty" and
+// "accumulator full" barriers, and both CTAs' epilogue warps release the accumulator on the leader's barrier.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int half_rows = p.MT / 2;  // activation rows this CTA stages
+  const uint32_t stage_bytes = kPTileBytes + (uint32_t)half_rows * kRowBytes;
+  const uint32_t bars = smem_base + (uint32_t)p.stages * stage_bytes;
+  auto full_bar = [&](int s) { return bars + (uint32_t)s * 8u; };
+  auto empty_bar = [&](int s) { return bars + (uint32_t)(p.stages + s) * 8u; };
+  auto acc_full = [&](int b) { return bars + (uint32_t)(2 * p.stages + b) * 8u; };
+  auto acc_empty = [&](int b) { return bars + (uint32_t)(2 * p.stages + 2 + b) * 8u; };
+  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4) * 8u;
+  const uint32_t abort_flag = tmem_slot + 4u;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  uint32_t acc_stride = 32;
+  while ((int)acc_stride < p.MT) acc_stride <<= 1;
+  const uint32_t tmem_cols = 2 * acc_stride;
+  const int tiles_n2 = (p.tiles_n + 1) / 2;
+  const int num_tiles = tiles_n2 * p.tiles_m;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 2 * kEpiWarps);  // both CTAs' epilogue warps arrive on the leader's barrier
+    }
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(0u) : "memory");
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_a);
+  }
+  if (warp == 1) tmem_alloc2(tmem_slot, tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+  if (threadIdx.x == 0) TC_TRACE(0);
+
+  auto aborted = [&]() {
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(abort_flag) : "memory");
+    return v != 0;
+  };
+  auto set_abort = [&](int code, int detail) {
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(1u) : "memory");
+    report_timeout(p.status, code, detail);
+  };
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs), single lane, lean loop ------------------------------------------
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0, it = 0;
+      const uint32_t nst = (uint32_t)p.stages;
+      bool stop = false;
+      for (int tile = pair; tile < num_tiles && !stop; tile += npairs) {
+        const int tn2 = tile % tiles_n2, tm = tile / tiles_n2;
+        const int tn = tn2 * 2 + (int)rank;  // this CTA's 128-row weight tile (may lie past N: reads as zero)
+        int wrow = tn * p.num_kb * 128;
+        const int arow = tm * p.MT + (int)rank * half_rows;
+        for (int kb = 0; kb < p.num_kb; kb++, it++, wrow += 128) {
+          const uint32_t fb = bars + s * 8u, dst = smem_base + s * stage_bytes;
+          if (it >= nst && !mbar_wait(fb + nst * 8u, ph ^ 1u)) {
+            set_abort(11, kb);
+            stop = true;
+            break;
+          }
+          if (it < 64) TC_TRACE(1 + it);
+          if (rank == 0) mbar_expect_tx(fb, 2 * stage_bytes);  // bytes of both CTAs land on this barrier
+          tma_load_2d_pair(dst, &map_w, 0, wrow, fb);
+          tma_load_3d_pair(dst + kPTileBytes, &map_a, 0, arow, kb, fb);
+          if (++s == nst) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---- MMA issuer (leader only), single lane, lean loop ------------------------------------------
+    if (rank == 0 && lane == 0) {
+      const uint32_t idesc = make_idesc(KIND, 256, p.MT);
+      const uint32_t nst = (uint32_t)p.stages;
+      const uint64_t desc0 = smem_desc_sw128(smem_base);
+      const uint64_t q_off = (uint64_t)(kPTileBytes >> 4), st_off = (uint64_t)(stage_bytes >> 4);
+      uint32_t s = 0, ph = 0, it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
+        const uint32_t buf = lt & 1, use = lt >> 1;
+        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1)) {
+          set_abort(14, tile);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * acc_stride;
+        for (int kb = 0; kb < p.num_kb; kb++, it++) {
+          const uint32_t fb = bars + s * 8u;
+          if (!mbar_wait(fb, ph)) {
+            set_abort(12, kb);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (it < 64) TC_TRACE(65 + it);
+          const uint64_t da = desc0 + (uint64_t)s * st_off, db = da + q_off;
+          umma2_f16(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
+          umma2_f16(d_tmem, da + 2, db + 2, idesc, 1u);
+          umma2_f16(d_tmem, da + 4, db + 4, idesc, 1u);
+          umma2_f16(d_tmem, da + 6, db + 6, idesc, 1u);
+          umma_commit_pair(fb + nst * 8u);
+          if (++s == nst) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) umma_commit_pair(acc_full(buf));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---- epilogue (both CTAs): this CTA's 128 output columns x all MT rows -----------------------------
+    const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
+      const int tn2 = tile % tiles_n2, tm = tile / tiles_n2;
+      const int n0 = (tn2 * 2 + (int)rank) * 128, m0 = tm * p.MT;
+      const uint32_t buf = lt & 1, use = lt >> 1;
+      ok = mbar_wait(acc_full(buf), use & 1);
+      if (!ok && lane == 0) set_abort(13, tile);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !aborted();
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
+      epilogue_tile<KIND>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, 0u);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(acc_empty(buf), 0);
+    }
+  }
+
+  // ---- teardown: neither CTA leaves while the other may still read its shared memory or TMEM -----------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();
+  if (aborted()) {
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, tmem_cols);
   }
 }
 
@@ -610,6 +802,22 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
       }
     }
   }
+  // CTA pairs (cta_group::2) for large single-limb f16 products: halves the activation bytes each CTA stages.
+  static const bool pair_enabled = getenv("FA_TC_PAIR") != nullptr;
+  const bool use_pair = pair_enabled && KIND == 0 && limbs == 1 && !raw_i32 && ep.batches <= 1 && p.tiles_n >= 2 &&
+                        M >= 256 && (ctx->sm_count & 1) == 0;
+  if (use_pair) {
+    const int npairs = ctx->sm_count / 2, tiles_n2 = (p.tiles_n + 1) / 2;
+    long long best = -1;
+    for (int cand = 256; cand >= 64; cand -= 32) {
+      const long long tiles = (long long)tiles_n2 * ceil_div(M, cand);
+      const long long cost = ((tiles + npairs - 1) / npairs) * (256 + cand);
+      if (best < 0 || cost < best) {
+        best = cost;
+        p.MT = cand;
+      }
+    }
+  }
   p.tiles_m = ceil_div(M, p.MT);
   p.batches = ep.batches;
   p.w_batch_mod = ep.w_batch_mod;
@@ -634,6 +842,70 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
       p.kb_per_split = ceil_div(p.num_kb, s);
       p.splitk = ceil_div(p.num_kb, p.kb_per_split);
     }
+  }
+  if (use_pair) {
+    p.splitk = 1;
+    p.kb_per_split = p.num_kb;
+    const size_t stage_b = (size_t)kPTileBytes + (size_t)(p.MT / 2) * kRowBytes;
+    const size_t tail_b = (size_t)(2 * 12 + 4) * 8 + 16 + 1024;
+    const int npairs = ctx->sm_count / 2, ptiles = ((p.tiles_n + 1) / 2) * p.tiles_m;
+    int st = (int)((220 * 1024 - tail_b) / stage_b);
+    if (st > 12) st = 12;
+    const int kb_per_cta = p.num_kb * ceil_div(ptiles, npairs);
+    if (st > kb_per_cta) st = kb_per_cta;
+    p.stages = st < 1 ? 1 : st;
+    p.raw_i32 = 0;
+    p.out = (float *)out;
+    p.rowscale = ep.rowscale;
+    p.colscale = ep.colscale;
+    p.bias = ep.bias;
+    p.add = ep.add;
+    p.rowbias = ep.rowbias;
+    p.act = ep.act;
+    p.status = ctx->dev_status;
+    p.trace = nullptr;
+    static const bool want_trace2 = getenv("FA_TC_TRACE") != nullptr;
+    unsigned long long *trace_dev = nullptr;
+    if (want_trace2 && allow_trace) {
+      cudaMalloc(&trace_dev, 256 * 8);
+      cudaMemsetAsync(trace_dev, 0, 256 * 8, ctx->stream);
+      p.trace = trace_dev;
+    }
+    CUtensorMap map_w, map_a;
+    FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, (uint64_t)p.tiles_n * p.num_kb * 128, 0, 128));
+    FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M, (uint64_t)p.num_kb, (uint32_t)(p.MT / 2)));
+    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm_pair<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = stage_b * p.stages + tail_b;
+    cfg.stream = ctx->stream;
+    cfg.gridDim = dim3(2 * (ptiles < npairs ? ptiles : npairs));
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    {
+      LaunchScope ls(ctx, "tc_gemm_f16_pair");
+      cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm_pair<KIND>, map_w, map_a, p);
+      if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm_pair: %s", cudaGetErrorString(e));
+    }
+    FA_LAUNCH_CHECK(ctx, "tc_gemm_pair");
+    if (trace_dev) {
+      unsigned long long h[256];
+      cudaMemcpyAsync(h, trace_dev, sizeof h, cudaMemcpyDeviceToHost, ctx->stream);
+      cudaStreamSynchronize(ctx->stream);
+      cudaFree(trace_dev);
+      fprintf(stderr, "[tc pair trace] M=%d N=%d K=%d MT=%d stages=%d num_kb=%d grid=%d\n  tma issue :", M, N, K, p.MT, p.stages,
+              p.num_kb, cfg.gridDim.x);
+      for (int i = 0; i < 64 && h[1 + i]; i++) fprintf(stderr, " %lld", (long long)(h[1 + i] - h[0]));
+      fprintf(stderr, "\n  mma ready :");
+      for (int i = 0; i < 64 && h[65 + i]; i++) fprintf(stderr, " %lld", (long long)(h[65 + i] - h[0]));
+      fprintf(stderr, "\n");
+    }
+    return FA_OK;
   }
   const size_t stage_bytes = (size_t)kPTileBytes + (size_t)p.MT * limbs * kRowBytes;
   const size_t tail_bytes = (size_t)(2 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + 1024;

@@ -476,19 +476,19 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
   for (int kk = 0; kk < K; kk++) wk[kk] = w[(size_t)c * K + kk];
   const float b = bias ? bias[c] : 0.f;
   const int t0 = blockIdx.y * 16;
-  float g[16 + K - 1];
+  float g[16 + K - 1], gate[16 + K - 1];
   int win[16 + K - 1];
+  // all loads first (addresses clamped into the tensor so none is conditional), then the gating math
 #pragma unroll
   for (int j = 0; j < 16 + K - 1; j++) {
-    const int tg = t0 - padl + j;
-    g[j] = 0.f;
-    win[j] = -1;
-    if (tg >= 0 && tg < rows) {
-      const float *xr = x + (size_t)tg * (2 * D);
-      g[j] = xr[c] * (1.0f / (1.0f + expf(-xr[c + D])));
-      win[j] = tg / Tw;
-    }
+    const int tg = t0 - padl + j, tc = min(max(tg, 0), rows - 1);
+    const float *xr = x + (size_t)tc * (2 * D);
+    g[j] = __ldg(xr + c);
+    gate[j] = __ldg(xr + c + D);
+    win[j] = (tg >= 0 && tg < rows) ? tg / Tw : -1;
   }
+#pragma unroll
+  for (int j = 0; j < 16 + K - 1; j++) g[j] = g[j] * (1.0f / (1.0f + __expf(-gate[j])));
 #pragma unroll
   for (int i = 0; i < 16; i++) {
     const int t = t0 + i;
