@@ -299,6 +299,87 @@ class Int8Gemm:
         return 2.0 * Ms * self.N * self.K * reps / dt / 1e12, f"{reps} x ({Ms} of 512 rows, N={self.N}, K={self.K}), reference loop order, {dt:.1f} s"
 
 
+class F16Gemm:
+    """BASELINE config 3: f16-weight GEMM sweep over FastConformer encoder shapes.
+    M in {256, 1024, 4096, 16384} x (K,N) in {(1024,3072), (1024,1024), (1024,4096), (4096,1024)};
+    activations ~N(0,1) f32, weights ~N(0,1/K) rounded to f16, f32 accumulate.  Seed 2.
+    One step = the 16 products once.  The M >= 4096 products move more than the 126 MB L2 per launch;
+    the small ones are L2-resident by nature (8 MB of weights) and are reported as such."""
+
+    name = "f16_gemm_sweep_fastconformer_shapes"
+    metric = "f16_gemm_throughput"
+    unit = "TFLOP/s"
+    dtype = "f16 x f16 -> f32 accumulate, f32 out"
+    nsets = 1
+
+    def __init__(self, quick=False):
+        self.Ms = (4096,) if quick else (256, 1024, 4096, 16384)
+        self.KNs = ((1024, 4096),) if quick else ((1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024))
+
+    def setup(self, ctx):
+        rng = np.random.default_rng(2)
+        self.W = {kn: ctx.uploadF16((rng.standard_normal(kn) / np.sqrt(kn[0])).astype(np.float32), kn[0], kn[1]) for kn in self.KNs}
+        self.host_A, self.A = {}, {}
+        for M in self.Ms:
+            for K in sorted({k for k, _ in self.KNs}):
+                buf = ctx.pinnedArray(M * K)
+                buf[:] = rng.standard_normal(M * K).astype(np.float32)
+                self.host_A[(M, K)] = buf
+                self.A[(M, K)] = ctx.upload(buf, M, K)
+        self.units_per_step = len(self.Ms) * len(self.KNs)
+        self.flops_per_step = sum(2.0 * M * K * N for M in self.Ms for K, N in self.KNs)
+
+    def step_device(self, ctx):
+        h = ctx.pushArena()
+        for M in self.Ms:
+            for K, N in self.KNs:
+                ctx.matmul(self.A[(M, K)], self.W[(K, N)])
+        ctx.popArena(h)
+
+    def step_e2e(self, ctx):
+        h = ctx.pushArena()
+        out = None
+        for M in self.Ms:
+            for K, N in self.KNs:
+                a = ctx.upload(self.host_A[(M, K)], M, K)
+                out = ctx.download(ctx.matmul(a, self.W[(K, N)]))
+                ctx.freeTensor(a)
+        ctx.popArena(h)
+        return out
+
+    def e2e_bytes(self):
+        return (sum(4 * M * K for M in self.Ms for K, _ in self.KNs), sum(4 * M * N for M in self.Ms for _, N in self.KNs))
+
+    def value_from(self, steps, seconds):
+        return self.flops_per_step * steps / seconds / 1e12
+
+    def roofline(self, prof, peaks):
+        ent = [e for e in prof if e["label"].startswith("tc_gemm_f16")]
+        if not ent:
+            return None
+        ms = sum(e["ms"] for e in ent)
+        n = sum(e["count"] for e in ent)
+        return {"bound": "tensor", "achieved": self.flops_per_step / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": None, "traffic": None, "kernel": "k_tc_gemm<f16>", "launches": n,
+                "avg_launch_us": round(ms / n * 1e3, 2), "peak_source": peaks["source"] + " (burst bf16)"}
+
+    def cpu_sample(self, threads=True):
+        from oracle.wasm_oracle import T, WasmOracle
+
+        ora = WasmOracle(threads=threads)
+        rng = np.random.default_rng(2)
+        M, K, N = 64, 1024, 1024
+        a, b = T(rng.standard_normal((M, K)).astype(np.float32), M, K), T(rng.standard_normal((K, N)).astype(np.float32), K, N)
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            ora.matmul(a, b)
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > 8 or reps >= 400:
+                break
+        return 2.0 * M * K * N * reps / dt / 1e12, f"{reps} x (64 rows of the 1024x1024 product), {dt:.1f} s"
+
+
 class Encoder:
     """BASELINE config 4: Parakeet-TDT-0.6B-shaped FastConformer encoder (24 blocks, d_model 1024, 8 heads,
     FFN 4096, dw-conv 9, 8x conv subsampling, 128 mel bins), random-init weights stored int8 per output
@@ -436,7 +517,7 @@ class Encoder:
         return self.window_s / (dt * 24), f"1 conformer block on one 15 s window ({dt:.2f} s), x24 blocks"
 
 
-WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "encoder": Encoder}
+WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "f16_gemm": F16Gemm, "encoder": Encoder}
 DEFAULT_WORKLOAD = "encoder"
 
 
