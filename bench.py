@@ -517,7 +517,128 @@ class Encoder:
         return self.window_s / (dt * 24), f"1 conformer block on one 15 s window ({dt:.2f} s), x24 blocks"
 
 
-WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "f16_gemm": F16Gemm, "encoder": Encoder}
+class Decoder:
+    """BASELINE config 5: Whisper-large-v3-turbo-shaped decoder (4 layers, d_model 1280, 20 heads, FFN 5120,
+    vocab 51866 padded to 51868), random-init weights, KV-cached greedy decoding of 64 concurrent streams of
+    224 tokens after a 4-token forced prefix, cross-attention over 1500 x 1280 encoder states per stream.
+    One step = the whole decode of the 64 streams (cross K/V products included).  Seed 5."""
+
+    metric = "decode_tokens_per_second"
+    unit = "tokens/s"
+    nsets = 1
+    quant = None
+    profile_steps = 2  # a decode is ~30k launches: two of them are enough for per-launch statistics
+
+    def __init__(self, quick=False):
+        self.S = 8 if quick else 64
+        self.n_tok = 16 if quick else 224
+        self.Tenc = 1500
+        self.prefix = [1, 2, 3, 4]
+        v = "int8" if self.quant else "f16"
+        self.name = f"whisper_large_v3_turbo_decoder_{v}_{self.S}streams_{self.n_tok}tok_greedy"
+        self.dtype = ("int8 weights x 3 int8 activation digits, int32 accumulate" if self.quant else
+                      "f16 weights x f16 value+residue activations, f32 accumulate")
+
+    def setup(self, ctx):
+        import __graft_entry__ as ge
+
+        ge.load_package()
+        from fluidaudio_web_b200.engines import synth, whisper_decoder
+
+        self.dm = whisper_decoder
+        self.cfg = dict(synth.WHISPER_TURBO_DEC, Tenc=self.Tenc)
+        ctx.setOption("int8_limbs", 3)  # f32-grade activations on both weight variants, so that
+        ctx.setOption("f16_hilo_rows", 1 << 30)  # greedy token picks follow the f32 reference arithmetic
+        self.dec = whisper_decoder.load_decoder(ctx, synth.decoder_weights(self.cfg, seed=5), self.cfg["NH"], quant=self.quant)
+        whisper_decoder.resident_tables(ctx, self.dec)
+        D = self.cfg["D"]
+        base = synth.encoder_states(self.cfg, 4, seed=7)  # 4 distinct clips, cycled over the streams
+        self.host_enc = ctx.pinnedArray(self.S * self.Tenc * D)
+        self.host_enc.reshape(self.S, self.Tenc, D)[:] = base[np.arange(self.S) % 4]
+        self.enc_all = ctx.upload(self.host_enc, self.S * self.Tenc, D)
+        self.prefix_idx = [ctx.upload(np.full(self.S, t, np.float32), self.S, 1) for t in self.prefix]
+        self.st = whisper_decoder.decode_init_streams(ctx, self.dec, self.S, len(self.prefix) + self.n_tok)
+        self.units_per_step = self.S * self.n_tok
+        self.e2e_batch = None
+
+    def _decode(self, ctx, enc_all):
+        return self.dm.greedy_decode_streams_resident(ctx, self.dec, enc_all, self.S, self.prefix_idx, self.n_tok, st=self.st)
+
+    def step_device(self, ctx):
+        ctx.freeTensor(self._decode(ctx, self.enc_all))  # encoder states resident in HBM
+
+    def _e2e_body(self, ctx):
+        h = ctx.pushArena()
+        enc = ctx.upload(self.host_enc, self.S * self.Tenc, self.cfg["D"])  # H2D from page-locked memory
+        hist = ctx.pin(self._decode(ctx, enc), True)
+        ctx.popArena(h)
+        return hist
+
+    def step_e2e(self, ctx):
+        if self.e2e_batch is None:
+            ctx.freeTensor(self._e2e_body(ctx))
+            self.e2e_batch, self.e2e_out = ctx.recordBatch(lambda: self._e2e_body(ctx))
+        self.e2e_batch.launch()
+        return ctx.download(self.e2e_out)  # token ids [n_tok, S]
+
+    def e2e_bytes(self):
+        return self.S * self.Tenc * self.cfg["D"] * 4, self.n_tok * self.S * 4
+
+    def value_from(self, steps, seconds):
+        return self.S * self.n_tok * steps / seconds
+
+    def attn_bytes_per_step(self):
+        """Algorithmic bytes of the single-query attention kernels over one whole decode: each launch
+        streams its key (or value) cache once, f32, plus the query/probability and result rows."""
+        D, L, S = self.cfg["D"], self.cfg["layers"], self.S
+        steps = len(self.prefix) + self.n_tok - 1
+        cross = steps * L * S * self.Tenc * D * 4
+        selfb = sum(L * S * (n + 1) * D * 4 for n in range(steps))
+        return cross + selfb  # per kernel (qk reads K, pv reads V)
+
+    def roofline(self, prof, peaks):
+        ent = {e["label"]: e for e in prof}
+        if "bmm_qk_t1" not in ent or "bmm_pv_t1" not in ent:
+            return None
+        ms = ent["bmm_qk_t1"]["ms"] + ent["bmm_pv_t1"]["ms"]
+        launches = ent["bmm_qk_t1"]["count"] + ent["bmm_pv_t1"]["count"]
+        ach = 2 * self.attn_bytes_per_step() / (ms * 1e-3) / 1e9  # per step; the caller scales by `steps`
+        return {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None,
+                "kernel": "k_bmm_qk_t1 + k_bmm_pv_t1 (single-query attention over the f32 K/V caches)",
+                "launches": launches, "avg_launch_us": round(ms / launches * 1e3, 2),
+                "share_of_step": None, "peak_source": peaks["source"]}
+
+    def cpu_sample(self, threads=True):
+        """One stream, 8 tokens through the reference-form one-token step on the CPU port, full widths;
+        the cross K/V of the clip are random stand-ins (their one-off products are left out of the sample)."""
+        from oracle.wasm_oracle import WasmOracle
+        from fluidaudio_web_b200.engines import synth, whisper_decoder
+
+        if not hasattr(Decoder, "_cpu_dec") or Decoder._cpu_dec[0] != (self.quant, threads):
+            ora = WasmOracle(threads=threads)
+            cfg = dict(synth.WHISPER_TURBO_DEC)
+            dec = whisper_decoder.load_decoder(ora, synth.decoder_weights(cfg, seed=5), cfg["NH"], quant=self.quant)
+            rng = np.random.default_rng(9)
+            kv = [dict(k=ora.upload(rng.standard_normal((1500, 1280), dtype=np.float32), 1500, 1280),
+                       v=ora.upload(rng.standard_normal((1500, 1280), dtype=np.float32), 1500, 1280)) for _ in range(cfg["layers"])]
+            Decoder._cpu_dec = ((self.quant, threads), ora, dec, kv)
+        _, ora, dec, kv = Decoder._cpu_dec
+        st = whisper_decoder.decode_init(ora, dec, 16)
+        n = 8
+        tok = 1
+        t0 = time.perf_counter()
+        for _ in range(n):
+            tok = int(np.argmax(whisper_decoder.decode_next(ora, dec, kv, st, tok)))
+        dt = time.perf_counter() - t0
+        return n / dt, f"1 stream x {n} tokens, one-token reference-form step, Tenc 1500 ({dt:.2f} s)"
+
+
+class DecoderInt8(Decoder):
+    quant = "int8"
+
+
+WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "f16_gemm": F16Gemm, "encoder": Encoder,
+             "decoder": Decoder, "decoder_int8": DecoderInt8}
 DEFAULT_WORKLOAD = "encoder"
 
 
@@ -614,8 +735,9 @@ def run_cuda(args):
     value = wl.value_from(args.steps, ms * 1e-3) * world
 
     # per-launch durations of the dominant kernel: same steps again with an event pair around each launch
+    psteps = min(args.steps, getattr(wl, "profile_steps", args.steps))
     ctx.startProfile(200000)
-    for _ in range(args.steps):
+    for _ in range(psteps):
         wl.step_device(ctx)
     prof = ctx.endProfile()
     peaks = measured_peaks()
@@ -627,7 +749,7 @@ def run_cuda(args):
             roof["in_step_profile"] = {"launches": in_step.get("launches"), "avg_launch_us": in_step.get("avg_launch_us"),
                                        "note": "per-launch event pairs inside the eager forward; includes launch gaps"}
     elif roof is not None and roof.get("frac") is None:  # per-step figure over a profile of `steps` steps
-        roof["achieved"] = round(roof["achieved"] * args.steps, 1)
+        roof["achieved"] = round(roof["achieved"] * psteps, 1)
         roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
 
     # end to end through the public API with host buffers

@@ -48,6 +48,7 @@ SIGNATURES = {
     "fa_staged_read": [P, P, P],
     "fa_staged_free": [P, P],
     "fa_rows_view": [P, P, I, PP],
+    "fa_reshape_view": [P, P, I, I, PP],
     "fa_begin_batch": [P],
     "fa_end_batch": [P],
     "fa_graph_begin": [P],
@@ -80,7 +81,8 @@ SIGNATURES = {
     "fa_copy_rows": [P, P, P, I],
     "fa_concat_rows": [P, PP, I, PP],
     "fa_sub_reshape": [P, P, I, I, I, PP],
-    "fa_argmax_rows": [P, P, PP],
+    "fa_argmax_rows": [P, P, I, PP],
+    "fa_embed_rows": [P, P, P, P, I, PP],
     "fa_profile_start": [P, I],
     "fa_profile_end": [P, C.POINTER(ProfileEntry), I, IP],
 }

@@ -192,6 +192,12 @@ class CudaContext:
         self._check(self._lib.fa_rows_view(self._h, t.h, rows, C.byref(out)))
         return self._wrap(out, view=True)
 
+    def reshapeView(self, t: Tensor, rows: int, cols: int) -> Tensor:
+        """Same storage, other [rows, cols] (a JS engine re-labels the tensor object for this)."""
+        out = C.c_void_p()
+        self._check(self._lib.fa_reshape_view(self._h, t.h, rows, cols, C.byref(out)))
+        return self._wrap(out, view=True)
+
     # -- batching (compute.d.ts:147-151) ----------------------------------------------------------
     def beginBatch(self) -> None:
         self._check(self._lib.fa_begin_batch(self._h))
@@ -375,9 +381,15 @@ class CudaContext:
     def subReshape(self, x, Cc: int, Tsub: int, F: int) -> Tensor:
         return self._op(self._lib.fa_sub_reshape, x.h, Cc, Tsub, F)
 
-    def argmaxRowsIndex(self, x) -> Tensor:
-        """[rows, 2] = {argmax index, max value} per row (host token pick moved to the device)."""
-        return self._op(self._lib.fa_argmax_rows, x.h)
+    def argmaxRowsIndex(self, x, ncols: int = 0) -> Tensor:
+        """[rows, 2] = {argmax index, max value} per row over the first `ncols` columns (0 = all); the
+        host token pick moved to the device."""
+        return self._op(self._lib.fa_argmax_rows, x.h, ncols)
+
+    def embedRows(self, table: Tensor, pos: Tensor, idx: Tensor, n: int) -> Tensor:
+        """[S, D] = table[id_s] + pos[n], ids read from column 0 of `idx` on the device (so a greedy
+        decode needs no host round trip between tokens)."""
+        return self._op(self._lib.fa_embed_rows, table.h, pos.h, idx.h, n)
 
     # -- profiling / stats (compute.d.ts:250-254) --------------------------------------------------
     def startProfile(self, maxOps: int = 4096) -> None:

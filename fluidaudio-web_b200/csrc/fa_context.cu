@@ -103,6 +103,11 @@ extern "C" int fa_ctx_destroy(fa_ctx *ctx) {
 
 extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) {
   if (!ctx || !key) return fa_fail(ctx, FA_ERR_INVALID, "fa_ctx_set_option: NULL argument");
+  if (!strcmp(key, "f16_hilo_rows")) {
+    FA_REQUIRE(ctx, value >= 0, "f16_hilo_rows must be >= 0 (got %lld)", value);
+    ctx->f16_hilo_rows = value > 0x7fffffffLL ? 0x7fffffff : (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "int8_limbs")) {
     FA_REQUIRE(ctx, value >= 1 && value <= 3, "int8_limbs must be 1..3 (got %lld)", value);
     ctx->int8_limbs = (int)value;
@@ -133,6 +138,10 @@ extern "C" int fa_sync(fa_ctx *ctx) {
     cudaMemsetAsync(ctx->dev_status, 0, sizeof st, ctx->stream);
     return fa_fail(ctx, FA_ERR_TIMEOUT, "device-side bounded wait ran out (code %d, block %d, detail %d)", st[0], st[1],
                    st[2]);
+  }
+  if (st[3] != 0) {
+    cudaMemsetAsync(ctx->dev_status, 0, sizeof st, ctx->stream);
+    return fa_fail(ctx, FA_ERR_INVALID, "embedRows: a token id was outside the embedding table");
   }
   return FA_OK;
 }
@@ -554,6 +563,22 @@ extern "C" int fa_rows_view(fa_ctx *ctx, fa_tensor *t, int rows, fa_tensor **out
   v->rows = rows;
   v->cols = t->cols;
   v->storage = t->storage;  // routing metadata is preserved (compute.d.ts:142-145)
+  v->dptr = t->dptr;
+  v->view = true;
+  ctx->tensors.insert(v);
+  *out = v;
+  return FA_OK;
+}
+
+extern "C" int fa_reshape_view(fa_ctx *ctx, fa_tensor *t, int rows, int cols, fa_tensor **out) {
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "reshapeView: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, t), "reshapeView: unknown tensor handle");
+  FA_REQUIRE(ctx, rows >= 0 && cols >= 0 && (long long)rows * cols <= (long long)t->rows * t->cols,
+             "reshapeView: [%d,%d] does not fit a [%d,%d] tensor", rows, cols, t->rows, t->cols);
+  fa_tensor *v = new fa_tensor();
+  v->rows = rows;
+  v->cols = cols;
+  v->storage = t->storage;
   v->dptr = t->dptr;
   v->view = true;
   ctx->tensors.insert(v);

@@ -38,12 +38,14 @@ constexpr int kEpiWarps = 8;                   // two per TMEM lane quadrant
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
 constexpr int kRowBytes = 128;                 // one swizzle atom of K per stage
 constexpr int kPTileBytes = 128 * kRowBytes;   // weights tile: 128 rows
-constexpr int kSplitMaxMT = 32;                // split-K mode keeps a [MT][128] f32 partial tile in smem
+constexpr int kSplitMaxMT = 128;               // split-K mode keeps a [MT][128] f32 partial tile in smem
 
 struct TcParams {
   int M, N, K;        // logical sizes; K in elements
   int MT;             // activation rows per tile (multiple of 16, MT*limbs <= 256)
   int limbs;          // activation digit planes (1 for f16)
+  int limb_sum;       // f16 kind, limbs == 2: plane 1 holds the f16 rounding residue of plane 0 and both are
+                      // accumulated into the SAME TMEM columns (f32-grade activations for decode-size products)
   int stages;
   int num_kb;         // K chunks of 128 bytes
   int tiles_n, tiles_m;
@@ -132,8 +134,8 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
     if (m0 + c >= p.M) break;  // warp-uniform: no rows left in this tile
     uint32_t v0[16], v1[16], v2[16];
     tmem_ld16(lane_addr + (uint32_t)c, v0);
-    if (p.limbs > 1) tmem_ld16(lane_addr + (uint32_t)(p.MT + c), v1);
-    if (p.limbs > 2) tmem_ld16(lane_addr + (uint32_t)(2 * p.MT + c), v2);
+    if (KIND == 1 && p.limbs > 1) tmem_ld16(lane_addr + (uint32_t)(p.MT + c), v1);
+    if (KIND == 1 && p.limbs > 2) tmem_ld16(lane_addr + (uint32_t)(2 * p.MT + c), v2);
     const bool full_rows = m0 + c + 16 <= p.M;
     // independent loads issued together while the TMEM read is in flight
     float rs[16], ad[16];
@@ -239,8 +241,9 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   const uint32_t partial = tmem_slot + 16u;  // [MT][128] f32, split-K mode only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int acc_cols = p.limb_sum ? p.MT : q_rows;
   uint32_t acc_stride = 32;  // TMEM columns per accumulator buffer
-  while ((int)acc_stride < q_rows) acc_stride <<= 1;
+  while ((int)acc_stride < acc_cols) acc_stride <<= 1;
   const uint32_t tmem_cols = 2 * acc_stride;
   const int num_tiles = p.tiles_n * p.tiles_m * p.batches;
   const int kb0 = p.splitk > 1 ? (int)blockIdx.z * p.kb_per_split : 0;
@@ -323,10 +326,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ---- MMA issuer: alternates between the two TMEM accumulator buffers -----------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(KIND, 128, q_rows);
+      const uint32_t idesc = make_idesc(KIND, 128, acc_cols);
       const uint32_t nst = (uint32_t)p.stages;
       const uint64_t desc0 = smem_desc_sw128(smem_base);  // slot 0 weights tile; other tiles are address offsets
       const uint64_t q_off = (uint64_t)(kPTileBytes >> 4), st_off = (uint64_t)(stage_bytes >> 4);
+      const uint64_t lo_off = (uint64_t)((p.MT * kRowBytes) >> 4);  // residue plane of the activations
       uint32_t s = 0, ph = 0, it = 0, lt = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
@@ -351,6 +355,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           umma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
           umma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
           umma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
+          if (p.limb_sum) {
+            umma<KIND>(d_tmem, da, db + lo_off, idesc, 1u);
+            umma<KIND>(d_tmem, da + 2, db + lo_off + 2, idesc, 1u);
+            umma<KIND>(d_tmem, da + 4, db + lo_off + 4, idesc, 1u);
+            umma<KIND>(d_tmem, da + 6, db + lo_off + 6, idesc, 1u);
+          }
           umma_commit(fb + nst * 8u);  // frees the slot when these MMAs have read it
           if (++s == nst) {
             s = 0;
@@ -390,18 +400,20 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   }
 
   if (p.splitk > 1) {
-    // ---- split-K: the cluster's CTAs hold partial tiles in shared memory; rank 0 sums them over
-    // distributed shared memory in rank order (deterministic), applies the epilogue and stores. ----
+    // ---- split-K: the cluster's CTAs hold partial tiles in shared memory; each CTA sums its share of
+    // the tile over distributed shared memory in rank order (deterministic), applies the epilogue and
+    // stores. ----
     __syncwarp();
     cluster_sync_all();
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-    if (rank == 0 && warp >= 2 && !aborted()) {
+    if (warp >= 2 && !aborted()) {
       const int tile = blockIdx.x, tn = tile % p.tiles_n, tm = tile / p.tiles_n;
       const int n0 = tn * 128, m0 = tm * p.MT;
       const int t = threadIdx.x - 64;  // 256 threads, each owns groups of 4 consecutive columns
       const bool vec_ok = (p.N & 3) == 0;
-      for (int g = t; g < p.MT * 32; g += 256) {
+      // every CTA of the cluster finishes an interleaved share of the tile (remote reads are the cost)
+      for (int g = t + 256 * (int)rank; g < p.MT * 32; g += 256 * p.splitk) {
         const int ml = g >> 5, nl = (g & 31) * 4, m = m0 + ml, n = n0 + nl;
         if (m >= p.M || n >= p.N) continue;
         // all remote reads first (independent), then the rank-ordered sum
@@ -435,7 +447,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       }
     }
     __syncwarp();
-    cluster_sync_all();  // peers keep their shared memory alive until rank 0 has read it
+    cluster_sync_all();  // every CTA keeps its shared memory alive until its peers have read it
   }
 
   // ---- teardown --------------------------------------------------------------------------------
@@ -640,6 +652,22 @@ __global__ void k_prep_a_f16(const float *__restrict__ a, int M, int K, int nch,
   }
 }
 
+// f32 [M][K] -> two f16 planes Ap[2][k/64][m][k%64]: hi = f16(a), lo = f16(a - hi).  hi + lo carries about
+// 22 bits of a, so a product that accumulates both planes in f32 is as accurate as an f32-activation one.
+__global__ void k_prep_a_f16_hilo(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
+  const size_t total = (size_t)nch * M * 32;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int pr = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
+    const int k = c * 64 + pr * 2;
+    const float *row = a + (size_t)m * K;
+    const float x = k < K ? row[k] : 0.0f, y = k + 1 < K ? row[k + 1] : 0.0f;
+    const __half2 hi = __floats2half2_rn(x, y);
+    const float2 hf = __half22float2(hi);
+    ((__half2 *)out)[i] = hi;
+    ((__half2 *)out)[total + i] = __floats2half2_rn(x - hf.x, y - hf.y);
+  }
+}
+
 // One CTA per activation row: s = max|a|/127 (1 when the row is all zero), r = a/s,
 // q1 = rint(r), q2 = rint((r-q1)*128), q3 = rint(((r-q1)*128-q2)*128); planes Ap[limb][k/128][m][k%128].
 // With one limb this is the usual symmetric per-row int8 quantiser; each further limb adds 7 bits.
@@ -782,6 +810,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.N = N;
   p.K = K;
   p.limbs = limbs;
+  p.limb_sum = (KIND == 0 && limbs == 2) ? 1 : 0;
   p.num_kb = fa_tc_chunks(K, elem);
   // activation rows per tile: as many as fit 256 MMA-N columns, rounded to 16, no more than needed
   int mt_max = (256 / limbs) / 16 * 16;
@@ -831,13 +860,13 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.o16_col_lo = ep.o16_col_lo;
   const int num_tiles = p.tiles_n * p.tiles_m * p.batches;
   // Decode-size products have fewer tiles than SMs: split K across a cluster (<= 8 CTAs) so that
-  // every SM streams weights.  Each split keeps at least 4 chunks so the ring still pipelines.
+  // every SM streams weights.  Each split keeps at least 2 chunks.
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
   if (!raw_i32 && !ep.out16 && p.batches == 1 && p.tiles_m == 1 && p.MT <= kSplitMaxMT && num_tiles * 2 <= ctx->sm_count) {
     int s = ctx->sm_count / num_tiles;
     if (s > 8) s = 8;
-    while (s > 1 && p.num_kb / s < 4) s--;
+    while (s > 1 && p.num_kb / s < 2) s--;
     if (s > 1) {
       p.kb_per_split = ceil_div(p.num_kb, s);
       p.splitk = ceil_div(p.num_kb, p.kb_per_split);
@@ -1006,7 +1035,7 @@ bool fa_tc_available(fa_ctx *) { return get_encode() != nullptr; }
 
 int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, float *c, int M, int N, int K,
                    const TcEpilogue &ep) {
-  return launch_tc<0>(ctx, w_packed, a_packed, 1, c, false, M, N, K, ep);
+  return launch_tc<0>(ctx, w_packed, a_packed, ep.a_hilo ? 2 : 1, c, false, M, N, K, ep);
 }
 
 int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *w_packed, void *c, bool raw_i32, int M,
@@ -1022,6 +1051,17 @@ int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out) {
     k_prep_a_f16<<<grid_for(ctx, (size_t)nch * M * 32, 256, 8), 256, 0, ctx->stream>>>(a, M, K, nch, out);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_f16");
+  return FA_OK;
+}
+
+int fa_prep_a_f16_hilo(fa_ctx *ctx, const float *a, int M, int K, __half *out) {
+  if (M == 0) return FA_OK;
+  const int nch = fa_tc_chunks(K, 2);
+  {
+    LaunchScope ls(ctx, "prep_a_f16_hilo");
+    k_prep_a_f16_hilo<<<grid_for(ctx, (size_t)nch * M * 32, 256, 8), 256, 0, ctx->stream>>>(a, M, K, nch, out);
+  }
+  FA_LAUNCH_CHECK(ctx, "prep_a_f16_hilo");
   return FA_OK;
 }
 

@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, 
 template <int V4>  // float4 per thread
 __global__ void __launch_bounds__(256) k_layernorm_reg(const float *__restrict__ x, const float *__restrict__ g,
                                                        const float *__restrict__ b, float *__restrict__ y,
-                                                       __half *__restrict__ y16, int R, int C, float eps) {
+                                                       __half *__restrict__ y16, size_t lo_off, int R, int C,
+                                                       float eps) {
   __shared__ float red[8];
   __shared__ float stat;
   const int r = blockIdx.x, c4 = C >> 2;
@@ -124,8 +125,15 @@ __global__ void __launch_bounds__(256) k_layernorm_reg(const float *__restrict__
       if (y16) {
         const int j = q * 4;
         __half2 *d16 = (__half2 *)(y16 + ((size_t)(j >> 6) * R + r) * 64 + (j & 63));
-        d16[0] = __floats2half2_rn(o.x, o.y);
-        d16[1] = __floats2half2_rn(o.z, o.w);
+        const __half2 h0 = __floats2half2_rn(o.x, o.y), h1 = __floats2half2_rn(o.z, o.w);
+        d16[0] = h0;
+        d16[1] = h1;
+        if (lo_off) {  // second plane: what the f16 rounding dropped
+          const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+          __half2 *l16 = (__half2 *)((__half *)d16 + lo_off);
+          l16[0] = __floats2half2_rn(o.x - f0.x, o.y - f0.y);
+          l16[1] = __floats2half2_rn(o.z - f1.x, o.w - f1.y);
+        }
       }
     }
   }
@@ -304,6 +312,98 @@ __global__ void __launch_bounds__(256) k_bmm_qk(const float *__restrict__ q, con
     for (int v = 0; v < 4; v++) {
       const int j = j0 + tx * 4 + v;
       if (j < Tb) obase[(size_t)i * Tb + j] = acc[u][v];
+    }
+  }
+}
+
+// Single-query forms of the two attention products (token-by-token decoding: T = 1 per window).  Both are
+// streams over the key / value cache, so they are laid out for full-line loads: a warp owns 128 consecutive
+// columns (32 lanes x float4) of one cache row at a time, 8 warps take rows round-robin, 4 rows in flight each.
+// LPH = lanes per head = HD / 4 (a power of two <= 32).
+__global__ void __launch_bounds__(256) k_bmm_qk_t1(const float *__restrict__ q, const float *__restrict__ b,
+                                                    const float *__restrict__ qb, float *__restrict__ out, int Tb, int H,
+                                                    int HD, int bShared, int lph) {
+  const int S = H * HD, w = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 128 + lane * 4;
+  const bool live = c < S;
+  float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (live) {
+    qv = *(const float4 *)(q + (size_t)w * S + c);
+    if (qb) {
+      const float4 t = *(const float4 *)(qb + c);
+      qv.x += t.x, qv.y += t.y, qv.z += t.z, qv.w += t.w;
+    }
+  }
+  const float *bbase = b + (size_t)(bShared ? 0 : w) * Tb * S + (live ? c : 0);
+  const int h = (live ? c : 0) / HD;
+  float *orow = out + ((size_t)w * H + h) * Tb;
+  const bool writer = live && (lane & (lph - 1)) == 0;
+  const int jstep = gridDim.y * 8 * 4;
+  for (int j0 = (blockIdx.y * 8 + warp) * 4; j0 < Tb; j0 += jstep) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int j = j0 + u < Tb ? j0 + u : Tb - 1;
+      v[u] = *(const float4 *)(bbase + (size_t)j * S);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      float d = live ? fmaf(qv.x, v[u].x, fmaf(qv.y, v[u].y, fmaf(qv.z, v[u].z, qv.w * v[u].w))) : 0.f;
+      for (int o = lph >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (writer && j0 + u < Tb) orow[j0 + u] = d;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) k_bmm_pv_t1(const float *__restrict__ p, const float *__restrict__ v,
+                                                    float *__restrict__ out, __half *__restrict__ y16, size_t lo_off,
+                                                    int Tk, int H, int HD) {
+  __shared__ float4 part[8][32];
+  const int S = H * HD, w = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 128 + lane * 4;
+  const bool live = c < S;
+  const int cc = live ? c : 0, h = cc / HD;
+  const float *prow = p + ((size_t)w * H + h) * Tk;
+  const float *vbase = v + (size_t)w * Tk * S + cc;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j0 = warp * 4; j0 < Tk; j0 += 32) {
+    float4 x[4];
+    float pr[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int j = j0 + u < Tk ? j0 + u : Tk - 1;
+      x[u] = *(const float4 *)(vbase + (size_t)j * S);
+      pr[u] = j0 + u < Tk ? prow[j] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      acc.x = fmaf(pr[u], x[u].x, acc.x);
+      acc.y = fmaf(pr[u], x[u].y, acc.y);
+      acc.z = fmaf(pr[u], x[u].z, acc.z);
+      acc.w = fmaf(pr[u], x[u].w, acc.w);
+    }
+  }
+  part[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0 && live) {
+    float4 t = part[0][lane];
+#pragma unroll
+    for (int i = 1; i < 8; i++) {
+      const float4 o = part[i][lane];
+      t.x += o.x, t.y += o.y, t.z += o.z, t.w += o.w;
+    }
+    *(float4 *)(out + (size_t)w * S + c) = t;
+    if (y16) {  // packed f16 row operand of the product that follows (value plane, then residue plane)
+      __half2 *d16 = (__half2 *)(y16 + ((size_t)(c >> 6) * gridDim.z + w) * 64 + (c & 63));
+      const __half2 h0 = __floats2half2_rn(t.x, t.y), h1 = __floats2half2_rn(t.z, t.w);
+      d16[0] = h0;
+      d16[1] = h1;
+      if (lo_off) {
+        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+        __half2 *l16 = (__half2 *)((__half *)d16 + lo_off);
+        l16[0] = __floats2half2_rn(t.x - f0.x, t.y - f0.y);
+        l16[1] = __floats2half2_rn(t.z - f1.x, t.w - f1.y);
+      }
     }
   }
 }
@@ -572,11 +672,12 @@ __global__ void __launch_bounds__(256) k_conv2d_c1_3x3(const float *__restrict__
 
 // Per-row argmax: out[r] = {index, value}; ties resolve to the lowest index like the host loop
 // of src/engines/asr-whisper/index.ts:80-97.
-__global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x, float *__restrict__ out, int R, int C) {
+__global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x, float *__restrict__ out, int R, int ld,
+                                                     int C) {
   __shared__ float bv[8];
   __shared__ int bi[8];
   for (int r = blockIdx.x; r < R; r += gridDim.x) {
-    const float *row = x + (size_t)r * C;
+    const float *row = x + (size_t)r * ld;
     float best = -INFINITY;
     int idx = 0x7fffffff;
     for (int j = threadIdx.x; j < C; j += 256) {
@@ -599,6 +700,22 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x
     }
     __syncthreads();
   }
+}
+
+// Token embedding + position for one decoding step, on the device: out[s][:] = table[idx[s*stride]][:] + pos[n][:].
+// idx holds token ids as floats (an argmax_rows result, stride 2, or a [S,1] tensor, stride 1); ids outside
+// [0, V) select row 0 and set word 3 of the context's status block (reported by the next sync) instead of reading out of bounds.
+__global__ void __launch_bounds__(256) k_embed_rows(const float *__restrict__ table, const float *__restrict__ pos,
+                                                     const float *__restrict__ idx, int stride, int V, int D, int n,
+                                                     float *__restrict__ out, int *status) {
+  const int s = blockIdx.x;
+  int t = (int)idx[(size_t)s * stride];
+  if (t < 0 || t >= V) {
+    if (threadIdx.x == 0) atomicOr(status + 3, 1);
+    t = 0;
+  }
+  const float *row = table + (size_t)t * D, *pr = pos + (size_t)n * D;
+  for (int d = threadIdx.x; d < D; d += 256) out[(size_t)s * D + d] = row[d] + pr[d];
 }
 
 int grid1d(fa_ctx *ctx, size_t n, int block) {
@@ -633,14 +750,24 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
     {
       LaunchScope ls(ctx, "layernorm");
       __half *y16 = nullptr;
-      if ((x->cols & 63) == 0 && x->rows >= 16 && fa_tc_available(ctx) && (y16 = fa_shadow_block(ctx, y)) != nullptr)
-        y->a16_valid = true;
+      size_t lo_off = 0;
       const float *xp = (const float *)x->dptr, *gp = (const float *)gamma->dptr, *bp = (const float *)beta->dptr;
       const bool al = (((uintptr_t)xp | (uintptr_t)gp | (uintptr_t)bp | (uintptr_t)y->dptr) & 15) == 0;
+      const bool reg = (x->cols & 3) == 0 && x->cols <= 4096 && al;
+      if ((x->cols & 63) == 0 && fa_tc_available(ctx)) {
+        if (x->rows <= ctx->f16_hilo_rows) {  // few rows: the consumer wants value + residue planes
+          if (reg && (y16 = fa_shadow_hilo_block(ctx, y)) != nullptr) {
+            y->a16_valid = true;
+            lo_off = (size_t)(x->cols >> 6) * x->rows * 64;
+          }
+        } else if (x->rows >= 16 && (y16 = fa_shadow_block(ctx, y)) != nullptr) {
+          y->a16_valid = true;
+        }
+      }
       if ((x->cols & 3) == 0 && x->cols <= 1024 && al)
-        k_layernorm_reg<1><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
-      else if ((x->cols & 3) == 0 && x->cols <= 4096 && al)
-        k_layernorm_reg<4><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
+        k_layernorm_reg<1><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows, x->cols, eps);
+      else if (reg)
+        k_layernorm_reg<4><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows, x->cols, eps);
       else
         k_layernorm<<<grid, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
     }
@@ -916,6 +1043,23 @@ extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, co
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, W * H * T, Tb, FA_F32, true, &y));
   bool on_tc = false;
+  const int lph = HD / 4;
+  if (T == 1 && Tb && (HD & 3) == 0 && lph <= 32 && (lph & (lph - 1)) == 0 && W <= 65535) {
+    const int strips = ceil_div(H * HD, 128);
+    int gy = ceil_div(ctx->sm_count * 8, strips * W);
+    const int gy_max = ceil_div(Tb, 32);
+    if (gy > gy_max) gy = gy_max;
+    if (gy < 1) gy = 1;
+    {
+      LaunchScope ls(ctx, "bmm_qk_t1");
+      k_bmm_qk_t1<<<dim3(strips, gy, W), 256, 0, ctx->stream>>>((const float *)q->dptr, (const float *)b->dptr,
+                                                               qb ? (const float *)qb->dptr : nullptr,
+                                                               (float *)y->dptr, Tb, H, HD, b_shared, lph);
+    }
+    FA_LAUNCH_CHECK(ctx, "bmm_qk_t1");
+    *out = y;
+    return FA_OK;
+  }
   if (T && Tb)
     FA_TRY(fa_tc_bmm_qk(ctx, (const float *)q->dptr, (const float *)b->dptr, qb ? (const float *)qb->dptr : nullptr,
                         (float *)y->dptr, T, Tb, H, HD, W, b_shared, &on_tc));
@@ -945,6 +1089,26 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, W * Tq, H * HD, FA_F32, true, &y));
   bool on_tc = false;
+  if (Tq == 1 && Tk && (HD & 3) == 0 && W <= 65535) {
+    {
+      LaunchScope ls(ctx, "bmm_pv_t1");
+      __half *y16 = nullptr;
+      size_t lo_off = 0;
+      if (((H * HD) & 63) == 0 && fa_tc_available(ctx)) {
+        if (W <= ctx->f16_hilo_rows) {
+          if ((y16 = fa_shadow_hilo_block(ctx, y)) != nullptr) lo_off = (size_t)((H * HD) >> 6) * W * 64;
+        } else {
+          y16 = fa_shadow_block(ctx, y);
+        }
+        if (y16) y->a16_valid = true;
+      }
+      k_bmm_pv_t1<<<dim3(ceil_div(H * HD, 128), 1, W), 256, 0, ctx->stream>>>(
+          (const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, y16, lo_off, Tk, H, HD);
+    }
+    FA_LAUNCH_CHECK(ctx, "bmm_pv_t1");
+    *out = y;
+    return FA_OK;
+  }
   if (Tq && Tk)
   {
     __half *y16 = ((H * HD) & 63) == 0 && (HD & 31) == 0 ? fa_shadow_block(ctx, y) : nullptr;
@@ -1165,17 +1329,43 @@ extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
   return FA_OK;
 }
 
-extern "C" int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
+extern "C" int fa_embed_rows(fa_ctx *ctx, const fa_tensor *table, const fa_tensor *pos, const fa_tensor *idx, int n,
+                             fa_tensor **out) {
+  GLUE_PROLOGUE("embedRows");
+  FA_TRY(need_f32(ctx, table, "embedRows"));
+  FA_TRY(need_f32(ctx, pos, "embedRows"));
+  FA_TRY(need_f32(ctx, idx, "embedRows"));
+  FA_REQUIRE(ctx, pos->cols == table->cols, "embedRows: table has %d columns, pos has %d", table->cols, pos->cols);
+  FA_REQUIRE(ctx, n >= 0 && n < pos->rows, "embedRows: position %d outside [0,%d)", n, pos->rows);
+  FA_REQUIRE(ctx, idx->cols >= 1, "embedRows: empty index tensor");
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, idx->rows, table->cols, FA_F32, true, &y));
+  if (idx->rows) {
+    {
+      LaunchScope ls(ctx, "embed_rows");
+      k_embed_rows<<<idx->rows, 256, 0, ctx->stream>>>((const float *)table->dptr, (const float *)pos->dptr,
+                                                       (const float *)idx->dptr, idx->cols, table->rows, table->cols, n,
+                                                       (float *)y->dptr, ctx->dev_status);
+    }
+    FA_LAUNCH_CHECK(ctx, "embed_rows");
+  }
+  *out = y;
+  return FA_OK;
+}
+
+extern "C" int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, int ncols, fa_tensor **out) {
   GLUE_PROLOGUE("argmaxRows");
   FA_TRY(need_f32(ctx, x, "argmaxRows"));
   FA_REQUIRE(ctx, x->cols > 0, "argmaxRows: no columns");
+  FA_REQUIRE(ctx, ncols <= x->cols, "argmaxRows: %d of %d columns", ncols, x->cols);
+  if (ncols <= 0) ncols = x->cols;
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, x->rows, 2, FA_F32, true, &y));
   if (x->rows) {
     int grid = x->rows < ctx->sm_count * 8 ? x->rows : ctx->sm_count * 8;
     {
       LaunchScope ls(ctx, "argmax_rows");
-      k_argmax_rows<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+      k_argmax_rows<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols, ncols);
     }
     FA_LAUNCH_CHECK(ctx, "argmax_rows");
   }

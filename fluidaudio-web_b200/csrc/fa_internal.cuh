@@ -36,6 +36,7 @@ struct fa_tensor {
   void *a16 = nullptr;
   size_t a16_bytes = 0;
   bool a16_valid = false;
+  bool a16_hilo = false;  // the shadow holds two planes (value, rounding residue)
 };
 
 struct fa_bytes {
@@ -83,6 +84,7 @@ struct fa_ctx {
   unsigned long long launches = 0;
   // options
   int int8_limbs = 2;
+  int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
   size_t pool_cap = 0;
   // exact-size pool (the reference pools by exact byte size, buffer-pool.js:49-84)
   std::unordered_map<size_t, std::vector<void *>> pool;
@@ -220,6 +222,7 @@ struct TcEpilogue {
   const float *add = nullptr;       // [M][N]
   const float *rowbias = nullptr;   // [M] added before the activation
   int act = 0;
+  bool a_hilo = false;              // f16 kind: the row operand is two planes (value, rounding residue)
   // optional second output: the epilogue result as a packed f16 activation shadow of a tensor with
   // o16_rows rows; this launch's rows/cols sit at (+o16_row_hi per batch/o_div, +o16_col_lo per batch%o_div)
   __half *out16 = nullptr;
@@ -241,6 +244,7 @@ int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, 
 int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *w_packed, void *c, bool raw_i32, int M,
                   int N, int K, const TcEpilogue &ep);
 int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out);
+int fa_prep_a_f16_hilo(fa_ctx *ctx, const float *a, int M, int K, __half *out);
 int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *out, float *rowscale);
 int fa_pack_a_i8_raw(fa_ctx *ctx, const int8_t *aq, int M, int K, int8_t *out);
 int fa_pack_w_i8(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out);
@@ -259,5 +263,6 @@ int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v
 // Shadow management (fa_linalg.cu): block for t's packed f16 shadow (nullptr when t cannot carry one),
 // and the shadow itself, built by the prepass when no producer wrote it.
 __half *fa_shadow_block(fa_ctx *ctx, fa_tensor *t);
+__half *fa_shadow_hilo_block(fa_ctx *ctx, fa_tensor *t);
 int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out);
 static inline void fa_shadow_drop(fa_tensor *t) { t->a16_valid = false; }

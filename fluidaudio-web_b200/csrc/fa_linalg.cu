@@ -16,7 +16,10 @@ namespace {
 constexpr long long kTcMinMacs = 1ll << 21;
 
 bool tc_shape_ok(fa_ctx *ctx, int M, int N, int K) {
-  return fa_tc_available(ctx) && N >= 64 && K >= 64 && M >= 1 && (long long)M * N * K >= kTcMinMacs;
+  // big enough to amortise the packing of the row operand, or a weight matrix big enough that the
+  // product is a stream over it whatever M is (token-by-token decoding, M = 1)
+  return fa_tc_available(ctx) && N >= 64 && K >= 64 && M >= 1 &&
+         ((long long)M * N * K >= kTcMinMacs || (long long)N * K >= (1ll << 18));
 }
 
 int check_vec(fa_ctx *ctx, const fa_tensor *t, int n, const char *what) {
@@ -60,11 +63,20 @@ struct Scratch {
 
 }  // namespace
 
+// Single-plane f16 shadow block of a tensor, for producers that write it alongside their f32 result.
+// Tensors in the value+residue regime (few rows) carry a two-plane shadow instead, which only
+// fa_shadow_hilo_ensure fills: producers get nullptr for them and write no shadow.
 __half *fa_shadow_block(fa_ctx *ctx, fa_tensor *t) {
   if (!t || t->view || t->storage != FA_F32 || t->rows <= 0 || t->cols <= 0) return nullptr;
+  if (t->rows <= ctx->f16_hilo_rows) return nullptr;
+  if (t->a16 && t->a16_hilo) {
+    fa_block_release(ctx, t->a16);
+    t->a16 = nullptr;
+  }
   if (!t->a16) {
     if (fa_block_acquire(ctx, fa_tc_act_bytes(t->rows, t->cols, 2, 1), &t->a16, &t->a16_bytes) != FA_OK) return nullptr;
     t->a16_valid = false;
+    t->a16_hilo = false;
   }
   return (__half *)t->a16;
 }
@@ -80,9 +92,48 @@ int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out) {
   return FA_OK;
 }
 
+// Two-plane (value, residue) shadow block of a few-row tensor, for a producer that fills both planes.
+__half *fa_shadow_hilo_block(fa_ctx *ctx, fa_tensor *t) {
+  if (!t || t->view || t->storage != FA_F32 || t->rows <= 0 || t->cols <= 0) return nullptr;
+  if (t->a16 && !t->a16_hilo) {
+    fa_block_release(ctx, t->a16);
+    t->a16 = nullptr;
+  }
+  if (!t->a16) {
+    if (fa_block_acquire(ctx, fa_tc_act_bytes(t->rows, t->cols, 2, 2), &t->a16, &t->a16_bytes) != FA_OK) return nullptr;
+    t->a16_valid = false;
+    t->a16_hilo = true;
+  }
+  return (__half *)t->a16;
+}
+
+static int fa_shadow_hilo_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out) {
+  if (!fa_shadow_hilo_block(ctx, t))
+    return fa_fail(ctx, FA_ERR_OOM, "no block for the f16 shadow of a %dx%d tensor", t->rows, t->cols);
+  if (!t->a16_valid) {
+    FA_TRY(fa_prep_a_f16_hilo(ctx, (const float *)t->dptr, t->rows, t->cols, (__half *)t->a16));
+    t->a16_valid = true;
+  }
+  *out = (const __half *)t->a16;
+  return FA_OK;
+}
+
 // Packed f16 row operand for `a`: its cached shadow when it can carry one, else a per-call scratch block.
-static int row_operand_f16(fa_ctx *ctx, const fa_tensor *a, const float *ap, Scratch &sa, const __half **out) {
-  if (a->storage == FA_F32 && !a->view) return fa_shadow_ensure(ctx, const_cast<fa_tensor *>(a), out);
+// Products with few rows (token-by-token decoding) are bound by the weight stream, so their row operand is
+// packed as two planes, value and rounding residue, which the kernel accumulates together: the result then
+// matches an f32-activation product to a few ulps and greedy token choices follow the f32 path.
+static int row_operand_f16(fa_ctx *ctx, const fa_tensor *a, const float *ap, Scratch &sa, const __half **out,
+                           bool *hilo) {
+  *hilo = a->rows <= ctx->f16_hilo_rows;
+  const bool can_shadow = a->storage == FA_F32 && !a->view;
+  if (*hilo) {
+    if (can_shadow) return fa_shadow_hilo_ensure(ctx, const_cast<fa_tensor *>(a), out);
+    FA_TRY(sa.get(fa_tc_act_bytes(a->rows, a->cols, 2, 2)));
+    FA_TRY(fa_prep_a_f16_hilo(ctx, ap, a->rows, a->cols, (__half *)sa.p));
+    *out = (const __half *)sa.p;
+    return FA_OK;
+  }
+  if (can_shadow) return fa_shadow_ensure(ctx, const_cast<fa_tensor *>(a), out);
   FA_TRY(sa.get(fa_tc_act_bytes(a->rows, a->cols, 2, 1)));
   FA_TRY(fa_prep_a_f16(ctx, ap, a->rows, a->cols, (__half *)sa.p));
   *out = (const __half *)sa.p;
@@ -114,9 +165,11 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
     Scratch sa(ctx);
     const __half *a16 = nullptr;
     rc = ensure_bt_f16(ctx, b);
-    if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16);
+    bool hilo = false;
+    if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16, &hilo);
     if (rc == FA_OK) {
       TcEpilogue ep;
+      ep.a_hilo = hilo;
       ep.bias = biasp;
       ep.add = addp;
       ep.act = act;
@@ -224,9 +277,11 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
     }
     Scratch sa(ctx);
     const __half *a16 = nullptr;
-    if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16);
+    bool hilo = false;
+    if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16, &hilo);
     if (rc == FA_OK) {
       TcEpilogue ep;
+      ep.a_hilo = hilo;
       rc = fa_tc_gemm_f16(ctx, a16, (const __half *)bq->nk_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {

@@ -67,6 +67,45 @@ def encoder_weights(cfg: dict, seed: int = 3) -> Dict[str, np.ndarray]:
     return w
 
 
+WHISPER_TURBO_DEC = dict(D=1280, NH=20, FFN=5120, layers=4, VOCAB=51866, maxPos=448, Tenc=1500)
+TINY_DEC = dict(D=64, NH=4, FFN=128, layers=2, VOCAB=203, maxPos=40, Tenc=24)
+
+
+def decoder_weights(cfg: dict, seed: int = 5) -> Dict[str, np.ndarray]:
+    """Random-init weights in the naming and shapes of the Whisper decoder manifest
+    (src/engines/asr-whisper/raw-whisper-decoder.js:33-56, embed/pos/lnf :66-71).  Matrix values are
+    f16-representable (the artifact's f16 variant), so f16 storage loses nothing against f32 storage."""
+    rng = np.random.default_rng(seed)
+    D, FFN = cfg["D"], cfg["FFN"]
+    h16 = lambda a: a.astype(np.float16).astype(np.float32)
+    n = lambda shape, fan_in: h16(rng.standard_normal(shape, dtype=np.float32) / np.float32(math.sqrt(fan_in)))
+    small = lambda m: (rng.standard_normal(m) * 0.02).astype(np.float32)
+    w: Dict[str, np.ndarray] = {}
+    for L in range(cfg["layers"]):
+        g = lambda s: f"L{L}_{s}"
+        for nm in ("sqw", "skw", "svw", "sow", "cqw", "ckw", "cvw", "cow"):
+            w[g(nm)] = n((D, D), D)
+        for nm in ("sqb", "svb", "sob", "cqb", "cvb", "cob", "f2b"):
+            w[g(nm)] = small(D)
+        w[g("f1w")] = n((D, FFN), D)
+        w[g("f1b")] = small(FFN)
+        w[g("f2w")] = n((FFN, D), FFN)
+        for nm in ("ln1", "ln2", "ln3"):
+            w[g(nm + "w")] = (1.0 + rng.standard_normal(D) * 0.05).astype(np.float32)
+            w[g(nm + "b")] = small(D)
+    w["embed"] = h16(rng.standard_normal((cfg["VOCAB"], D), dtype=np.float32) * np.float32(0.05))
+    w["pos"] = (rng.standard_normal((cfg["maxPos"], D)) * 0.05).astype(np.float32)
+    w["lnf_w"] = (1.0 + rng.standard_normal(D) * 0.05).astype(np.float32)
+    w["lnf_b"] = small(D)
+    return w
+
+
+def encoder_states(cfg: dict, n_clips: int, seed: int = 7) -> np.ndarray:
+    """Stand-in encoder outputs [n_clips, Tenc, D]: unit-variance rows like a final-LayerNorm output."""
+    rng = np.random.default_rng(seed)
+    return rng.standard_normal((n_clips, cfg["Tenc"], cfg["D"]), dtype=np.float32)
+
+
 def synth_audio(n_windows: int, samples: int = 240000, sr: int = 16000, seed: int = 3) -> np.ndarray:
     """Pink noise (white noise shaped by 1/sqrt(f), unit RMS) x amp~U(0.05,0.5) plus 1-4 tones of
     100-4000 Hz, amp~U(0.05,0.5).  [n_windows, samples] f32."""

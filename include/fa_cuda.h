@@ -58,7 +58,11 @@ int fa_ctx_destroy(fa_ctx *ctx);
 /* Message of the most recent failure on ctx (ctx may be NULL for fa_ctx_create failures). */
 const char *fa_last_error(fa_ctx *ctx);
 /* Integer options: "int8_limbs" (1..3, see fa_matmul_int8), "pool_cap_bytes" (0 = none; allocation
- * beyond it fails with FA_ERR_OOM — the reference's poolBudgetBytes, compute.js:128-137). */
+ * beyond it fails with FA_ERR_OOM — the reference's poolBudgetBytes, compute.js:128-137),
+ * "f16_hilo_rows" (>= 0, default 64: tensor-core products against f16 weights whose row operand has
+ * at most this many rows feed it as two f16 planes, value and rounding residue, summed in the f32
+ * accumulator, so token-by-token decoding keeps f32-grade activations at twice the MMA work; 0 turns
+ * it off, a huge value applies it to every product). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);
@@ -93,6 +97,10 @@ int fa_stage_download(fa_ctx *ctx, const fa_tensor *t, fa_staged **out);    /* s
 int fa_staged_read(fa_ctx *ctx, fa_staged *s, float *host_out); /* StagedRead.read :44; 2nd call: FA_ERR_INVALID */
 int fa_staged_free(fa_ctx *ctx, fa_staged *s);
 int fa_rows_view(fa_ctx *ctx, fa_tensor *t, int rows, fa_tensor **out);     /* rowsView :145 */
+/* The same storage seen as [rows, cols] with rows*cols <= the tensor's element count (row-major order
+ * unchanged).  No counterpart in compute.d.ts, where a JS engine re-labels {rows, cols} on the tensor
+ * object itself; the batched multi-stream decoder uses it to see [streams, D] as [1, streams*D]. */
+int fa_reshape_view(fa_ctx *ctx, fa_tensor *t, int rows, int cols, fa_tensor **out);
 
 /* ---- batching (compute.d.ts:147-151) --------------------------------------- */
 int fa_begin_batch(fa_ctx *ctx); /* beginBatch :148; nested call fails like scheduler.js:20 */
@@ -187,8 +195,17 @@ int fa_copy_rows(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, int row_offs
 int fa_concat_rows(fa_ctx *ctx, const fa_tensor *const *tensors, int count, fa_tensor **out); /* concatRows :222 */
 int fa_sub_reshape(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, fa_tensor **out); /* subReshape :228 */
 /* argmax over each row (host picks tokens from it; the reference does this on the host,
- * src/engines/asr-whisper/index.ts:80-97): out [rows,2] = {index, value}. */
-int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);
+ * src/engines/asr-whisper/index.ts:80-97): out [rows,2] = {index, value}.  Only the first `ncols`
+ * columns of each row take part (ncols <= 0: all of them) - the tied vocabulary projection is padded
+ * with zero columns that must never win (raw-whisper-decoder.js:62-66). */
+int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, int ncols, fa_tensor **out);
+/* Token embedding + position on the device (the reference gathers on the host and uploads,
+ * src/engines/asr-whisper/raw-whisper-decoder.js:106-108): out[s,:] = table[id_s,:] + pos[n,:], where id_s
+ * is column 0 of row s of idx (token ids as floats: an fa_argmax_rows result or a [S,1] tensor).  With it
+ * a greedy decode never leaves the device between tokens.  An id outside the table reads row 0 and makes
+ * the next fa_sync fail with FA_ERR_INVALID. */
+int fa_embed_rows(fa_ctx *ctx, const fa_tensor *table, const fa_tensor *pos, const fa_tensor *idx, int n,
+                  fa_tensor **out);
 
 /* ---- profiling (compute.d.ts:250-251; scheduler.js:139-180) ----------------- */
 typedef struct fa_profile_entry {

@@ -153,9 +153,23 @@ class WasmOracle:
 
     downloadF16 = download
 
+    def stageDownload(self, t):  # :141, StagedRead.read :44 (single use)
+        data = t.data[: t.rows * t.cols].copy()
+
+        class _Staged:
+            def read(self_inner):
+                return data
+
+        return _Staged()
+
     def rowsView(self, t, rows):
         v = T.__new__(T)
         v.data, v.rows, v.cols = t.data[: rows * t.cols], rows, t.cols
+        return v
+
+    def reshapeView(self, t, rows, cols):
+        v = T.__new__(T)
+        v.data, v.rows, v.cols = t.data[: rows * cols], rows, cols
         return v
 
     def ensureTensor(self, t):

@@ -129,6 +129,9 @@ def test_argmax_rows(ctx):
     out = ctx.download(ctx.argmaxRowsIndex(ctx.upload(x, 5, 51868))).reshape(5, 2)
     assert np.array_equal(out[:, 0].astype(np.int64), x.argmax(axis=1))
     assert np.array_equal(out[:, 1], x.max(axis=1))
+    x[:, 51866:] = 99.0  # pad columns beyond the limit never win
+    out = ctx.download(ctx.argmaxRowsIndex(ctx.upload(x, 5, 51868), 51866)).reshape(5, 2)
+    assert np.array_equal(out[:, 0].astype(np.int64), x[:, :51866].argmax(axis=1))
 
 
 def test_conv_module_fast_members_match_the_op_sequence(ctx):
