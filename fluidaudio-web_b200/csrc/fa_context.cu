@@ -70,6 +70,14 @@ extern "C" int fa_ctx_create(int device, fa_ctx **out) {
     delete ctx;
     return fa_fail(nullptr, FA_ERR_CUDA, "fa_ctx_create: status word allocation failed");
   }
+  ctx->gemv_ticket_count = 8192;
+  if (cudaMalloc(&ctx->gemv_tickets, sizeof(int) * ctx->gemv_ticket_count) != cudaSuccess ||
+      cudaMemsetAsync(ctx->gemv_tickets, 0, sizeof(int) * ctx->gemv_ticket_count, ctx->stream) != cudaSuccess) {
+    cudaFree(ctx->dev_status);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return fa_fail(nullptr, FA_ERR_CUDA, "fa_ctx_create: ticket array allocation failed");
+  }
   *out = ctx;
   return FA_OK;
 }
@@ -96,6 +104,7 @@ extern "C" int fa_ctx_destroy(fa_ctx *ctx) {
   for (fa_bytes *b : ctx->byte_handles) delete b;
   for (auto &kv : ctx->blocks) cudaFree(kv.first);
   cudaFree(ctx->dev_status);
+  cudaFree(ctx->gemv_tickets);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return FA_OK;
@@ -106,6 +115,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
   if (!strcmp(key, "f16_hilo_rows")) {
     FA_REQUIRE(ctx, value >= 0, "f16_hilo_rows must be >= 0 (got %lld)", value);
     ctx->f16_hilo_rows = value > 0x7fffffffLL ? 0x7fffffff : (int)value;
+    return FA_OK;
+  }
+  if (!strcmp(key, "gemv_rows")) {
+    FA_REQUIRE(ctx, value >= 0 && value <= kGemvMaxRows, "gemv_rows must be 0..%d (got %lld)", kGemvMaxRows, value);
+    ctx->gemv_rows = (int)value;
     return FA_OK;
   }
   if (!strcmp(key, "int8_limbs")) {

@@ -1,0 +1,387 @@
+// Decode-size products (M <= 4 activation rows) on the CUDA cores: pure streams over the weights in the
+// layouts the reference uploads them in (no repack, no packing prepass, no TMEM or cluster set-up), with
+// 128-bit coalesced loads, in-register dequantisation and f32 / exact-integer accumulation.
+//
+//   k_gemv_nbits  matmulNBits (rust/wasm-kernels/src/lib.rs:169-203): bq [N][nblk][16] nibbles, K-contiguous.
+//                 One warp per output column; a lane takes whole 32-weight blocks (one 16-byte load each).
+//                 The activation row is split, inside the kernel, into two int8 digits of its own maximum,
+//                 stored in the even/odd order the nibbles unpack to, so a block is 16 dp4a per digit pair
+//                 and its sum is an exact integer; zero-point and scale are applied once per block:
+//                 y = s_m * sum_blk scale[n,blk] * ((S1 - zp*A1) + (S2 - zp*A2) / 128).
+//                 Arithmetic budget: ~1 lane-op per weight at M = 1 (an f32 unpack-and-FMA needs 4).
+//   k_gemv_kn     matmul with f16-storage B [K][N] (lib.rs:59-94) and matmulInt8 with wq [K][N]
+//                 (lib.rs:143-162): N-contiguous rows.  A warp owns 32*VEC consecutive columns, the 8 warps of
+//                 a CTA take rows k round-robin, K is split over gridDim.y; activations stay f32 (exact).
+//                 Partial sums meet in a scratch buffer and the last CTA to arrive (an atomic ticket, no
+//                 waiting) adds them in slice order, so the result does not depend on scheduling.
+#include <cuda_fp16.h>
+
+#include "fa_internal.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- int4 ---------------------------------------------------------------------------------------
+
+template <int M, int R>
+__global__ void __launch_bounds__(kThreads) k_gemv_nbits(const float *__restrict__ a, const uint8_t *__restrict__ bq,
+                                                         const float *__restrict__ scales, const uint8_t *__restrict__ zp,
+                                                         float *__restrict__ y, int N, int K, int nblk, int zpb) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  int8_t *dig = (int8_t *)smem;                     // [M][2] planes of K bytes: even-k words of every block (16 B
+                                                    // each, so 8 lanes read 128 consecutive bytes), then odd-k words
+  int *SA = (int *)(smem + (size_t)M * 2 * K);      // [M][2][nblk] digit sums per block
+  float *red = (float *)(SA + M * 2 * nblk);        // [8][M] per-warp row maxima
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // Activation digits, all M rows at once so the loads of a pass overlap: row maxima, then q1 = rint(a/s),
+  // q2 = rint((a/s - q1) * 128) with s = max/127, stored in the order the nibbles unpack to.
+  float mx[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) mx[m] = 0.f;
+#pragma unroll 4
+  for (int k = tid; k < K; k += kThreads) {
+#pragma unroll
+    for (int m = 0; m < M; m++) mx[m] = fmaxf(mx[m], fabsf(a[(size_t)m * K + k]));
+  }
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    mx[m] = warp_max_f(mx[m]);
+    if (lane == 0) red[warp * M + m] = mx[m];
+  }
+  __syncthreads();
+  float rs[M], inv[M];
+#pragma unroll
+  for (int m = 0; m < M; m++) {
+    float t = red[m];
+#pragma unroll
+    for (int w = 1; w < 8; w++) t = fmaxf(t, red[w * M + m]);
+    rs[m] = t > 0.f ? t / 127.0f : 1.0f;
+    inv[m] = 1.0f / rs[m];
+  }
+#pragma unroll 4
+  for (int k = tid; k < K; k += kThreads) {
+    const int b = k >> 5, j = k & 31;
+    const int off = (j & 1) * (K >> 1) + b * 16 + (j >> 3) * 4 + ((j & 7) >> 1);
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+      const float t = a[(size_t)m * K + k] * inv[m];
+      const float q1 = rintf(t);
+      dig[(size_t)(m * 2 + 0) * K + off] = (int8_t)q1;
+      dig[(size_t)(m * 2 + 1) * K + off] = (int8_t)rintf((t - q1) * 128.0f);
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < M * 2 * nblk; idx += kThreads) {
+    const int p = idx / nblk, b = idx - p * nblk;
+    const int4 w0 = *(const int4 *)(dig + (size_t)p * K + b * 16);
+    const int4 w1 = *(const int4 *)(dig + (size_t)p * K + (K >> 1) + b * 16);
+    int s = __dp4a(w0.x, 0x01010101, 0);
+    s = __dp4a(w0.y, 0x01010101, s), s = __dp4a(w0.z, 0x01010101, s), s = __dp4a(w0.w, 0x01010101, s);
+    s = __dp4a(w1.x, 0x01010101, s), s = __dp4a(w1.y, 0x01010101, s);
+    s = __dp4a(w1.z, 0x01010101, s), s = __dp4a(w1.w, 0x01010101, s);
+    SA[idx] = s;
+  }
+  __syncthreads();
+
+  const uint4 *bq4 = (const uint4 *)bq;
+  for (int n0 = (blockIdx.x * 8 + warp) * R; n0 < N; n0 += gridDim.x * 8 * R) {
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+      for (int m = 0; m < M; m++) acc[r][m] = 0.f;
+    for (int b = lane; b < nblk; b += 32) {
+      int lo[R][4], hi[R][4], z[R];
+      float sc[R];
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        const int n = n0 + r < N ? n0 + r : N - 1;
+        const uint4 wv = __ldcs(bq4 + (size_t)n * nblk + b);
+        sc[r] = scales[(size_t)n * nblk + b];
+        const unsigned zb = zp[(size_t)n * zpb + (b >> 1)];
+        z[r] = (b & 1) ? (int)(zb >> 4) : (int)(zb & 15u);
+        lo[r][0] = (int)(wv.x & 0x0F0F0F0Fu), hi[r][0] = (int)((wv.x >> 4) & 0x0F0F0F0Fu);
+        lo[r][1] = (int)(wv.y & 0x0F0F0F0Fu), hi[r][1] = (int)((wv.y >> 4) & 0x0F0F0F0Fu);
+        lo[r][2] = (int)(wv.z & 0x0F0F0F0Fu), hi[r][2] = (int)((wv.z >> 4) & 0x0F0F0F0Fu);
+        lo[r][3] = (int)(wv.w & 0x0F0F0F0Fu), hi[r][3] = (int)((wv.w >> 4) & 0x0F0F0F0Fu);
+      }
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        const int4 e1 = *(const int4 *)(dig + (size_t)(m * 2 + 0) * K + b * 16);
+        const int4 o1 = *(const int4 *)(dig + (size_t)(m * 2 + 0) * K + (K >> 1) + b * 16);
+        const int4 e2 = *(const int4 *)(dig + (size_t)(m * 2 + 1) * K + b * 16);
+        const int4 o2 = *(const int4 *)(dig + (size_t)(m * 2 + 1) * K + (K >> 1) + b * 16);
+        const int a1 = SA[(m * 2 + 0) * nblk + b], a2 = SA[(m * 2 + 1) * nblk + b];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          int s1 = 0, s2 = 0;
+          s1 = __dp4a(lo[r][0], e1.x, s1), s1 = __dp4a(hi[r][0], o1.x, s1);
+          s1 = __dp4a(lo[r][1], e1.y, s1), s1 = __dp4a(hi[r][1], o1.y, s1);
+          s1 = __dp4a(lo[r][2], e1.z, s1), s1 = __dp4a(hi[r][2], o1.z, s1);
+          s1 = __dp4a(lo[r][3], e1.w, s1), s1 = __dp4a(hi[r][3], o1.w, s1);
+          s2 = __dp4a(lo[r][0], e2.x, s2), s2 = __dp4a(hi[r][0], o2.x, s2);
+          s2 = __dp4a(lo[r][1], e2.y, s2), s2 = __dp4a(hi[r][1], o2.y, s2);
+          s2 = __dp4a(lo[r][2], e2.z, s2), s2 = __dp4a(hi[r][2], o2.z, s2);
+          s2 = __dp4a(lo[r][3], e2.w, s2), s2 = __dp4a(hi[r][3], o2.w, s2);
+          const float f = fmaf((float)(s2 - z[r] * a2), 1.0f / 128.0f, (float)(s1 - z[r] * a1));
+          acc[r][m] = fmaf(sc[r], f, acc[r][m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        const float t = warp_sum_f(acc[r][m]);
+        if (lane == 0 && n0 + r < N) y[(size_t)m * N + n0 + r] = t * rs[m];
+      }
+  }
+}
+
+// ---- f16 / int8 weights, N-contiguous ---------------------------------------------------------------
+
+struct GemvEp {
+  const float *colscale, *bias, *add;
+  int act;
+};
+
+__device__ __forceinline__ float gemv_finish(float acc, int m, int n, int N, const GemvEp &ep) {
+  float v = acc;
+  if (ep.colscale) v *= ep.colscale[n];
+  if (ep.bias) v += ep.bias[n];
+  v = fa_actf(v, ep.act);
+  if (ep.add) v += ep.add[(size_t)m * N + n];
+  return v;
+}
+
+// VEC weights per lane and row: 8 (f16, 16-byte loads) or 4 (f16, 8-byte loads, for N % 8 != 0) or 16 (int8).
+template <int VEC, bool I8>
+__device__ __forceinline__ void load_row(const void *w, size_t off, float (&f)[VEC]) {
+  if constexpr (I8) {
+    static_assert(VEC == 16, "int8 rows are read 16 bytes at a time");
+    const uint4 v = __ldcs((const uint4 *)((const int8_t *)w + off));
+    const unsigned wd[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      // byte b of (q + 128) into the mantissa of 2^23: the float 8388608 + q + 128, then back to q
+      f[i * 4 + 0] = __uint_as_float(__byte_perm(wd[i], 0x4B000000u, 0x7650)) - 8388736.0f;
+      f[i * 4 + 1] = __uint_as_float(__byte_perm(wd[i], 0x4B000000u, 0x7651)) - 8388736.0f;
+      f[i * 4 + 2] = __uint_as_float(__byte_perm(wd[i], 0x4B000000u, 0x7652)) - 8388736.0f;
+      f[i * 4 + 3] = __uint_as_float(__byte_perm(wd[i], 0x4B000000u, 0x7653)) - 8388736.0f;
+    }
+  } else if constexpr (VEC == 8) {
+    const uint4 v = __ldcs((const uint4 *)((const __half *)w + off));
+    const __half2 *h = (const __half2 *)&v;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x, f[2 * i + 1] = t.y;
+    }
+  } else {
+    static_assert(VEC == 4, "f16 rows are read 16 or 8 bytes at a time");
+    const uint2 v = __ldcs((const uint2 *)((const __half *)w + off));
+    const __half2 *h = (const __half2 *)&v;
+    const float2 t0 = __half22float2(h[0]), t1 = __half22float2(h[1]);
+    f[0] = t0.x, f[1] = t0.y, f[2] = t1.x, f[3] = t1.y;
+  }
+}
+
+template <int M, int VEC, bool I8>
+__global__ void __launch_bounds__(kThreads) k_gemv_kn(const float *__restrict__ a, const void *__restrict__ w,
+                                                      float *__restrict__ y, float *__restrict__ partials,
+                                                      int *__restrict__ tickets, int K, int N, int kslice, GemvEp ep) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  float *as = (float *)smem;                 // [M][kslice] activations of this K slice
+  float *red = as + (size_t)M * kslice;      // [8][32*VEC]
+  __shared__ int last_flag;
+  constexpr int U = I8 ? 2 : 4;              // rows in flight per warp
+  constexpr int CW = 32 * VEC;               // columns per CTA
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int k0 = blockIdx.y * kslice, k1 = min(K, k0 + kslice), ks = gridDim.y;
+  const int c0 = blockIdx.x * CW + lane * VEC;
+  const bool live = c0 < N;  // N % VEC == 0, so a live lane owns VEC whole columns
+  for (int i = tid; i < M * kslice; i += kThreads) {
+    const int m = i / kslice, kk = i - m * kslice;
+    as[i] = k0 + kk < k1 ? a[(size_t)m * K + k0 + kk] : 0.f;
+  }
+  __syncthreads();
+  float acc[M][VEC];
+#pragma unroll
+  for (int m = 0; m < M; m++)
+#pragma unroll
+    for (int v = 0; v < VEC; v++) acc[m][v] = 0.f;
+  if (live) {
+    for (int kk = k0 + warp * U; kk < k1; kk += 8 * U) {
+      float f[U][VEC];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int k = kk + u < k1 ? kk + u : k1 - 1;
+        load_row<VEC, I8>(w, (size_t)k * N + c0, f[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        if (kk + u < k1) {
+#pragma unroll
+          for (int m = 0; m < M; m++) {
+            const float av = as[m * kslice + (kk + u - k0)];
+#pragma unroll
+            for (int v = 0; v < VEC; v++) acc[m][v] = fmaf(av, f[u][v], acc[m][v]);
+          }
+        }
+      }
+    }
+  }
+  // the 8 warps' partial sums, one activation row at a time, added in warp order
+  for (int m = 0; m < M; m++) {
+#pragma unroll
+    for (int v = 0; v < VEC; v++) red[warp * CW + lane * VEC + v] = acc[m][v];
+    __syncthreads();
+    for (int c = tid; c < CW; c += kThreads) {
+      const int n = blockIdx.x * CW + c;
+      if (n < N) {
+        float s = red[c];
+#pragma unroll
+        for (int wv = 1; wv < 8; wv++) s += red[wv * CW + c];
+        if (ks == 1)
+          y[(size_t)m * N + n] = gemv_finish(s, m, n, N, ep);
+        else
+          partials[((size_t)blockIdx.y * M + m) * N + n] = s;
+      }
+    }
+    __syncthreads();
+  }
+  if (ks == 1) return;
+  __threadfence();
+  if (tid == 0) {
+    const int old = atomicAdd(&tickets[blockIdx.x], 1);
+    last_flag = old == ks - 1;
+    if (last_flag) tickets[blockIdx.x] = 0;  // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  for (int i = tid; i < M * CW; i += kThreads) {
+    const int m = i / CW, n = blockIdx.x * CW + (i - m * CW);
+    if (n < N) {
+      float s = 0.f;
+#pragma unroll 8
+      for (int q = 0; q < ks; q++) s += __ldcg(&partials[((size_t)q * M + m) * N + n]);
+      y[(size_t)m * N + n] = gemv_finish(s, m, n, N, ep);
+    }
+  }
+}
+
+template <int M, int VEC, bool I8>
+int launch_kn(fa_ctx *ctx, const float *a, const void *w, float *y, float *partials, int K, int N, int kslice, int ksplit,
+              const GemvEp &ep) {
+  const size_t smem = ((size_t)M * kslice + 8 * 32 * VEC) * sizeof(float);
+  auto kern = k_gemv_kn<M, VEC, I8>;
+  if (smem > 48 * 1024) FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  {
+    LaunchScope ls(ctx, I8 ? "gemv_i8" : "gemv_f16");
+    kern<<<dim3(ceil_div(N, 32 * VEC), ksplit), kThreads, smem, ctx->stream>>>(a, w, y, partials, ctx->gemv_tickets, K, N,
+                                                                               kslice, ep);
+  }
+  FA_LAUNCH_CHECK(ctx, "gemv_kn");
+  return FA_OK;
+}
+
+template <int VEC, bool I8>
+int dispatch_kn(fa_ctx *ctx, int M, const float *a, const void *w, float *y, float *partials, int K, int N, int kslice,
+                int ksplit, const GemvEp &ep) {
+  switch (M) {
+    case 1: return launch_kn<1, VEC, I8>(ctx, a, w, y, partials, K, N, kslice, ksplit, ep);
+    case 2: return launch_kn<2, VEC, I8>(ctx, a, w, y, partials, K, N, kslice, ksplit, ep);
+    case 3: return launch_kn<3, VEC, I8>(ctx, a, w, y, partials, K, N, kslice, ksplit, ep);
+    default: return launch_kn<4, VEC, I8>(ctx, a, w, y, partials, K, N, kslice, ksplit, ep);
+  }
+}
+
+template <int M>
+int launch_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y, int N,
+                 int K, int nblk, int zpb) {
+  const size_t smem = (size_t)M * 2 * K + (size_t)M * 2 * nblk * 4 + 8 * M * 4;
+  constexpr int R = M >= 3 ? 4 : 2;  // output columns per warp pass: shares each digit load between R rows of weights
+  auto kern = k_gemv_nbits<M, R>;
+  if (smem > 48 * 1024) FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  // one resident wave: every CTA pays the digit prologue once and a second wave would pay it twice
+  int per_sm = 0;
+  FA_CHECK_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem));
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 4) per_sm = 4;
+  int grid = ceil_div(N, 8 * R);
+  if (grid > ctx->sm_count * per_sm) grid = ctx->sm_count * per_sm;
+  {
+    LaunchScope ls(ctx, "gemv_nbits");
+    kern<<<grid, kThreads, smem, ctx->stream>>>(a, bq, scales, zp, y, N, K, nblk, zpb);
+  }
+  FA_LAUNCH_CHECK(ctx, "gemv_nbits");
+  return FA_OK;
+}
+
+}  // namespace
+
+bool fa_gemv_nbits_ok(int M, int N, int K, int block_size) {
+  return M >= 1 && M <= kGemvMaxRows && block_size == 32 && (K & 31) == 0 && K >= 32 && N >= 1 &&
+         (size_t)M * 2 * K + (size_t)M * (K / 32) * 8 + 64 <= 96 * 1024;
+}
+
+int fa_gemv_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y, int M,
+                  int N, int K, int nblk, int zpb) {
+  switch (M) {
+    case 1: return launch_nbits<1>(ctx, a, bq, scales, zp, y, N, K, nblk, zpb);
+    case 2: return launch_nbits<2>(ctx, a, bq, scales, zp, y, N, K, nblk, zpb);
+    case 3: return launch_nbits<3>(ctx, a, bq, scales, zp, y, N, K, nblk, zpb);
+    default: return launch_nbits<4>(ctx, a, bq, scales, zp, y, N, K, nblk, zpb);
+  }
+}
+
+// N-contiguous weights: one activation row only.  From two rows on, the tensor-core kernel (which shares each
+// weight tile between all rows for free) is at least as fast as this one; measured on 1280 x 1280 f16 at
+// M = 4: 10.6 us here against 7.3 us there.
+bool fa_gemv_kn_ok(int M, int N, int K, bool i8) { return M == 1 && K >= 1 && N >= 1 && (N % (i8 ? 16 : 4)) == 0; }
+
+// w: f16 [K][N] (i8 = false) or int8 [K][N]; y = act(acc * colscale[n] + bias[n]) + add[m][n].
+int fa_gemv_kn(fa_ctx *ctx, const float *a, const void *w, bool i8, const float *colscale, const float *bias, int act,
+               const float *add, float *y, int M, int N, int K) {
+  const int vec = i8 ? 16 : ((N & 7) == 0 ? 8 : 4);
+  const int strips = ceil_div(N, 32 * vec);
+  // enough CTAs to put ~4 on every SM; a K slice of at most 2048 rows so its activations fit shared memory
+  const int target = 2, cap = 40;
+  int ksplit = ceil_div(ctx->sm_count * target, strips);
+  int max_split = ceil_div(K, 32);
+  if (max_split > cap) max_split = cap;
+  if (ksplit > max_split) ksplit = max_split;
+  if (ksplit < ceil_div(K, 2048)) ksplit = ceil_div(K, 2048);
+  if (ksplit < 1) ksplit = 1;
+  int kslice = ceil_div(K, ksplit);
+  kslice = (kslice + 7) / 8 * 8;
+  ksplit = ceil_div(K, kslice);
+  FA_REQUIRE(ctx, strips <= ctx->gemv_ticket_count, "gemv: %d column strips exceed the ticket array", strips);
+  void *partials = nullptr;
+  size_t pbytes = 0;
+  if (ksplit > 1) FA_TRY(fa_block_acquire(ctx, (size_t)ksplit * M * N * sizeof(float), &partials, &pbytes));
+  GemvEp ep{colscale, bias, add, act};
+  int rc;
+  if (i8)
+    rc = dispatch_kn<16, true>(ctx, M, a, w, y, (float *)partials, K, N, kslice, ksplit, ep);
+  else if (vec == 8)
+    rc = dispatch_kn<8, false>(ctx, M, a, w, y, (float *)partials, K, N, kslice, ksplit, ep);
+  else
+    rc = dispatch_kn<4, false>(ctx, M, a, w, y, (float *)partials, K, N, kslice, ksplit, ep);
+  if (partials) fa_block_release(ctx, partials);
+  return rc;
+}

@@ -318,8 +318,9 @@ __global__ void __launch_bounds__(256) k_bmm_qk(const float *__restrict__ q, con
 
 // Single-query forms of the two attention products (token-by-token decoding: T = 1 per window).  Both are
 // streams over the key / value cache, so they are laid out for full-line loads: a warp owns 128 consecutive
-// columns (32 lanes x float4) of one cache row at a time, 8 warps take rows round-robin, 4 rows in flight each.
+// columns (32 lanes x float4) of one cache row at a time, 8 warps take rows round-robin, U rows in flight each.
 // LPH = lanes per head = HD / 4 (a power of two <= 32).
+template <int U>
 __global__ void __launch_bounds__(256) k_bmm_qk_t1(const float *__restrict__ q, const float *__restrict__ b,
                                                     const float *__restrict__ qb, float *__restrict__ out, int Tb, int H,
                                                     int HD, int bShared, int lph) {
@@ -338,23 +339,36 @@ __global__ void __launch_bounds__(256) k_bmm_qk_t1(const float *__restrict__ q, 
   const int h = (live ? c : 0) / HD;
   float *orow = out + ((size_t)w * H + h) * Tb;
   const bool writer = live && (lane & (lph - 1)) == 0;
-  const int jstep = gridDim.y * 8 * 4;
-  for (int j0 = (blockIdx.y * 8 + warp) * 4; j0 < Tb; j0 += jstep) {
-    float4 v[4];
+  const bool vec = (Tb & 3) == 0 && (((uintptr_t)out) & 15) == 0;
+  const int jstep = gridDim.y * 8 * U;
+  for (int j0 = (blockIdx.y * 8 + warp) * U; j0 < Tb; j0 += jstep) {
+    float4 v[U];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < U; u++) {
       const int j = j0 + u < Tb ? j0 + u : Tb - 1;
-      v[u] = *(const float4 *)(bbase + (size_t)j * S);
+      v[u] = __ldcs((const float4 *)(bbase + (size_t)j * S));
     }
+    float d[U];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
-      float d = live ? fmaf(qv.x, v[u].x, fmaf(qv.y, v[u].y, fmaf(qv.z, v[u].z, qv.w * v[u].w))) : 0.f;
-      for (int o = lph >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-      if (writer && j0 + u < Tb) orow[j0 + u] = d;
+    for (int u = 0; u < U; u++) d[u] = fmaf(qv.x, v[u].x, fmaf(qv.y, v[u].y, fmaf(qv.z, v[u].z, qv.w * v[u].w)));
+    for (int o = lph >> 1; o > 0; o >>= 1) {
+#pragma unroll
+      for (int u = 0; u < U; u++) d[u] += __shfl_xor_sync(0xffffffffu, d[u], o);
+    }
+    if (writer) {
+      if (vec && j0 + U <= Tb) {  // U consecutive scores of one head: whole 16-byte stores
+#pragma unroll
+        for (int u = 0; u < U; u += 4) *(float4 *)(orow + j0 + u) = make_float4(d[u], d[u + 1], d[u + 2], d[u + 3]);
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; u++)
+          if (j0 + u < Tb) orow[j0 + u] = d[u];
+      }
     }
   }
 }
 
+template <int U>
 __global__ void __launch_bounds__(256) k_bmm_pv_t1(const float *__restrict__ p, const float *__restrict__ v,
                                                     float *__restrict__ out, __half *__restrict__ y16, size_t lo_off,
                                                     int Tk, int H, int HD) {
@@ -366,17 +380,17 @@ __global__ void __launch_bounds__(256) k_bmm_pv_t1(const float *__restrict__ p, 
   const float *prow = p + ((size_t)w * H + h) * Tk;
   const float *vbase = v + (size_t)w * Tk * S + cc;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int j0 = warp * 4; j0 < Tk; j0 += 32) {
-    float4 x[4];
-    float pr[4];
+  for (int j0 = warp * U; j0 < Tk; j0 += 8 * U) {
+    float4 x[U];
+    float pr[U];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < U; u++) {
       const int j = j0 + u < Tk ? j0 + u : Tk - 1;
-      x[u] = *(const float4 *)(vbase + (size_t)j * S);
+      x[u] = __ldcs((const float4 *)(vbase + (size_t)j * S));
       pr[u] = j0 + u < Tk ? prow[j] : 0.f;
     }
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < U; u++) {
       acc.x = fmaf(pr[u], x[u].x, acc.x);
       acc.y = fmaf(pr[u], x[u].y, acc.y);
       acc.z = fmaf(pr[u], x[u].z, acc.z);
@@ -1046,15 +1060,18 @@ extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, co
   const int lph = HD / 4;
   if (T == 1 && Tb && (HD & 3) == 0 && lph <= 32 && (lph & (lph - 1)) == 0 && W <= 65535) {
     const int strips = ceil_div(H * HD, 128);
+    static const int unroll = getenv("FA_T1_UNROLL") ? atoi(getenv("FA_T1_UNROLL")) : 8;
+    const int U = Tb >= 256 ? unroll : 4;
     int gy = ceil_div(ctx->sm_count * 8, strips * W);
-    const int gy_max = ceil_div(Tb, 32);
+    const int gy_max = ceil_div(Tb, 8 * U);
     if (gy > gy_max) gy = gy_max;
     if (gy < 1) gy = 1;
     {
       LaunchScope ls(ctx, "bmm_qk_t1");
-      k_bmm_qk_t1<<<dim3(strips, gy, W), 256, 0, ctx->stream>>>((const float *)q->dptr, (const float *)b->dptr,
-                                                               qb ? (const float *)qb->dptr : nullptr,
-                                                               (float *)y->dptr, Tb, H, HD, b_shared, lph);
+      auto kern = U == 8 ? k_bmm_qk_t1<8> : k_bmm_qk_t1<4>;
+      kern<<<dim3(strips, gy, W), 256, 0, ctx->stream>>>((const float *)q->dptr, (const float *)b->dptr,
+                                                        qb ? (const float *)qb->dptr : nullptr, (float *)y->dptr, Tb, H,
+                                                        HD, b_shared, lph);
     }
     FA_LAUNCH_CHECK(ctx, "bmm_qk_t1");
     *out = y;
@@ -1102,8 +1119,10 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
         }
         if (y16) y->a16_valid = true;
       }
-      k_bmm_pv_t1<<<dim3(ceil_div(H * HD, 128), 1, W), 256, 0, ctx->stream>>>(
-          (const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, y16, lo_off, Tk, H, HD);
+      static const int unroll = getenv("FA_T1_UNROLL") ? atoi(getenv("FA_T1_UNROLL")) : 8;
+      auto kern = (Tk >= 256 && unroll == 8) ? k_bmm_pv_t1<8> : k_bmm_pv_t1<4>;
+      kern<<<dim3(ceil_div(H * HD, 128), 1, W), 256, 0, ctx->stream>>>((const float *)p->dptr, (const float *)v->dptr,
+                                                                      (float *)y->dptr, y16, lo_off, Tk, H, HD);
     }
     FA_LAUNCH_CHECK(ctx, "bmm_pv_t1");
     *out = y;

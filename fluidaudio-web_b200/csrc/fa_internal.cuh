@@ -84,6 +84,7 @@ struct fa_ctx {
   unsigned long long launches = 0;
   // options
   int int8_limbs = 2;
+  int gemv_rows = 4;       // products with at most this many rows run on the CUDA-core GEMV kernels (0 = never)
   int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
   size_t pool_cap = 0;
   // exact-size pool (the reference pools by exact byte size, buffer-pool.js:49-84)
@@ -105,6 +106,8 @@ struct fa_ctx {
   std::vector<ProfileRec> prof;
   // device-side status word written by kernels whose bounded waits ran out
   int *dev_status = nullptr;
+  int *gemv_tickets = nullptr;  // zeroed arrival counters of the split-K GEMV (self-resetting)
+  int gemv_ticket_count = 0;
   // graph recording: blocks acquired while `capturing` is set belong to that graph
   fa_graph *capturing = nullptr;
   std::unordered_map<void *, fa_graph *> block_owner;
@@ -243,6 +246,14 @@ int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, 
                    const TcEpilogue &ep);
 int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *w_packed, void *c, bool raw_i32, int M,
                   int N, int K, const TcEpilogue &ep);
+// CUDA-core products for M <= kGemvMaxRows activation rows, on the weights as uploaded (fa_gemv.cu)
+constexpr int kGemvMaxRows = 4;
+bool fa_gemv_nbits_ok(int M, int N, int K, int block_size);
+int fa_gemv_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y, int M,
+                  int N, int K, int nblk, int zpb);
+bool fa_gemv_kn_ok(int M, int N, int K, bool i8);
+int fa_gemv_kn(fa_ctx *ctx, const float *a, const void *w, bool i8, const float *colscale, const float *bias, int act,
+               const float *add, float *y, int M, int N, int K);
 int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out);
 int fa_prep_a_f16_hilo(fa_ctx *ctx, const float *a, int M, int K, __half *out);
 int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *out, float *rowscale);

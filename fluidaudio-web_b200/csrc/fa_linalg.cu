@@ -22,6 +22,12 @@ bool tc_shape_ok(fa_ctx *ctx, int M, int N, int K) {
          ((long long)M * N * K >= kTcMinMacs || (long long)N * K >= (1ll << 18));
 }
 
+// Few activation rows against a weight matrix worth streaming: the CUDA-core GEMV kernels (no packing,
+// f32 or exact-integer activations).  "gemv_rows" = 0 sends these shapes to the tensor-core kernel instead.
+bool gemv_shape_ok(fa_ctx *ctx, int M, int N, int K) {
+  return M >= 1 && M <= ctx->gemv_rows && (long long)N * K >= (1ll << 14);
+}
+
 int check_vec(fa_ctx *ctx, const fa_tensor *t, int n, const char *what) {
   FA_REQUIRE(ctx, fa_valid(ctx, t), "%s: unknown tensor handle", what);
   FA_REQUIRE(ctx, t->storage == FA_F32, "%s must be f32 storage", what);
@@ -161,7 +167,9 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
   int rc;
   const float *biasp = bias ? (const float *)bias->dptr : nullptr;
   const float *addp = add ? (const float *)add->dptr : nullptr;
-  if (b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K)) {
+  if (b->storage == FA_F16 && gemv_shape_ok(ctx, M, N, K) && fa_gemv_kn_ok(M, N, K, false)) {
+    rc = fa_gemv_kn(ctx, ap, b->dptr, false, nullptr, biasp, act, addp, (float *)c->dptr, M, N, K);
+  } else if (b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K)) {
     Scratch sa(ctx);
     const __half *a16 = nullptr;
     rc = ensure_bt_f16(ctx, b);
@@ -211,7 +219,9 @@ extern "C" int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, con
   FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
   int rc = FA_OK;
   const float *biasp = bias ? (const float *)bias->dptr : nullptr;
-  if (tc_shape_ok(ctx, M, N, K)) {
+  if (gemv_shape_ok(ctx, M, N, K) && fa_gemv_kn_ok(M, N, K, true)) {
+    rc = fa_gemv_kn(ctx, ap, wq->dptr, true, (const float *)scale->dptr, biasp, act, nullptr, (float *)c->dptr, M, N, K);
+  } else if (tc_shape_ok(ctx, M, N, K)) {
     const int limbs = ctx->int8_limbs;
     Scratch sa(ctx), ss(ctx);
     rc = ensure_nk_i8(ctx, wq, N, K);  // one-time repack per handle
@@ -259,7 +269,10 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
   fa_tensor *c = nullptr;
   FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
   int rc = FA_OK;
-  if (tc_shape_ok(ctx, M, N, K)) {
+  if (gemv_shape_ok(ctx, M, N, K) && fa_gemv_nbits_ok(M, N, K, block_size)) {
+    rc = fa_gemv_nbits(ctx, ap, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr,
+                       (float *)c->dptr, M, N, K, nblk, zpb);
+  } else if (tc_shape_ok(ctx, M, N, K)) {
     const bool cached = bq->nk_f16 && bq->f16_N == N && bq->f16_K == K && bq->f16_scales == scales->dptr &&
                         bq->f16_zp == zp->dptr;
     if (!cached) {

@@ -62,7 +62,9 @@ const char *fa_last_error(fa_ctx *ctx);
  * "f16_hilo_rows" (>= 0, default 64: tensor-core products against f16 weights whose row operand has
  * at most this many rows feed it as two f16 planes, value and rounding residue, summed in the f32
  * accumulator, so token-by-token decoding keeps f32-grade activations at twice the MMA work; 0 turns
- * it off, a huge value applies it to every product). */
+ * it off, a huge value applies it to every product), "gemv_rows" (0..4, default 4: products with at
+ * most this many activation rows stream the weights through the CUDA-core GEMV kernels - no packing,
+ * f32 / exact-integer activations; 0 sends them to the tensor-core kernel). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);

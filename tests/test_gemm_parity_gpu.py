@@ -203,3 +203,79 @@ def test_int8_full_size_linearity_and_exactness(ctx):
     z = ctx.download(ctx.matmulInt8(ctx.upload(np.zeros((M, K), np.float32), M, K), wb, ctx.upload(sc, 1, N), N, K,
                                     bias=ctx.upload(bias, 1, N))).reshape(M, N)
     assert np.array_equal(z, np.broadcast_to(bias, (M, N)))
+
+
+# ---- decode-size products on the CUDA-core GEMV kernels (M <= 4) ---------------------------------------
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("K,N", [(2048, 8192), (2048, 2048), (96, 200), (4096, 333)])
+def test_gemv_nbits_matches_oracle(ctx, oracle, M, K, N):
+    rng = np.random.default_rng(M * 7 + N)
+    nblk = K // 32
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    bq = rng.integers(0, 256, N * nblk * 16, dtype=np.uint8)
+    scales = rng.uniform(5e-3, 2e-2, N * nblk).astype(np.float32)
+    zp = rng.integers(0, 256, N * ((nblk + 1) // 2), dtype=np.uint8)
+    ref = oracle.matmulNBits(oracle.upload(a, M, K), oracle.uploadBytes(bq), oracle.upload(scales, 1, scales.size),
+                             oracle.uploadBytes(zp), N).array()
+    ctx.startProfile(64)
+    got = ctx.download(ctx.matmulNBits(ctx.upload(a, M, K), ctx.uploadBytes(bq), ctx.upload(scales, 1, scales.size),
+                                       ctx.uploadBytes(zp), N)).reshape(M, N)
+    labels = [e["label"] for e in ctx.endProfile()]
+    assert "gemv_nbits" in labels and not any(l.startswith(("tc_gemm", "gemm_simt", "nbits_simt")) for l in labels), labels
+    # two int8 digits of the row maximum: error bound 2^-15 * max|a| * sum|w| per output; outputs are O(sqrt(K)*0.06)
+    assert np.abs(got - ref).max() <= 2e-3 * max(1.0, float(np.abs(ref).max()) / 3.0)
+    assert np.abs(got - ref).max() <= 2e-2
+
+
+@pytest.mark.parametrize("M", [1])
+@pytest.mark.parametrize("K,N", [(1280, 1280), (1280, 5120), (5120, 1280), (1280, 51868), (77, 260), (4100, 64)])
+def test_gemv_f16_weights_matches_oracle(ctx, oracle, M, K, N):
+    rng = np.random.default_rng(M + K + N)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    add = rng.standard_normal((M, N)).astype(np.float32)
+    ref = oracle.matmul(oracle.upload(a, M, K), oracle.upload(b, K, N),
+                        dict(bias=oracle.upload(bias, 1, N), act="gelu_erf", add=oracle.upload(add, M, N))).array()
+    ctx.startProfile(64)
+    got = ctx.download(ctx.matmul(ctx.upload(a, M, K), ctx.uploadF16(b, K, N),
+                                  dict(bias=ctx.upload(bias, 1, N), act="gelu_erf", add=ctx.upload(add, M, N))))
+    labels = [e["label"] for e in ctx.endProfile()]
+    assert "gemv_f16" in labels and not any(l.startswith(("tc_gemm", "gemm_simt", "nbits_simt")) for l in labels), labels
+    assert np.abs(got.reshape(M, N) - ref).max() <= 2e-5  # f32 activations, f32 accumulation: only summation order differs
+
+
+@pytest.mark.parametrize("M", [1])
+@pytest.mark.parametrize("K,N", [(1024, 4096), (1280, 51872), (333, 64), (5120, 1280)])
+def test_gemv_int8_weights_matches_oracle(ctx, oracle, M, K, N):
+    rng = np.random.default_rng(M + K + N)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    sc = rng.uniform(1e-3, 1e-2, N).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    ref = oracle.matmulInt8(oracle.upload(a, M, K), oracle.uploadBytes(wq.view(np.uint8).reshape(-1)), oracle.upload(sc, 1, N),
+                            N, K, bias=oracle.upload(bias, 1, N), act="relu").array()
+    ctx.startProfile(64)
+    got = ctx.download(ctx.matmulInt8(ctx.upload(a, M, K), ctx.uploadBytes(wq.view(np.uint8).reshape(-1)), ctx.upload(sc, 1, N),
+                                      N, K, bias=ctx.upload(bias, 1, N), act="relu"))
+    labels = [e["label"] for e in ctx.endProfile()]
+    assert "gemv_i8" in labels and not any(l.startswith(("tc_gemm", "gemm_simt", "nbits_simt")) for l in labels), labels
+    assert np.abs(got.reshape(M, N) - ref).max() <= 1e-3 * max(1.0, float(np.abs(ref).max()))
+    assert np.abs(got.reshape(M, N) - ref).max() <= 5e-5 * max(1.0, float(np.abs(ref).max()))
+
+
+def test_gemv_option_off_uses_tensor_cores(ctx, oracle):
+    rng = np.random.default_rng(1)
+    M, K, N = 1, 1280, 1280
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    ref = oracle.matmul(oracle.upload(a, M, K), oracle.upload(b, K, N)).array()
+    ctx.setOption("gemv_rows", 0)
+    try:
+        ctx.startProfile(64)
+        got = ctx.download(ctx.matmul(ctx.upload(a, M, K), ctx.uploadF16(b, K, N)))
+        assert "tc_gemm_f16" in [e["label"] for e in ctx.endProfile()]
+    finally:
+        ctx.setOption("gemv_rows", 4)
+    assert np.abs(got.reshape(M, N) - ref).max() <= 2e-5
