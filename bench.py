@@ -609,7 +609,7 @@ class Decoder:
                 "share_of_step": None, "peak_source": peaks["source"]}
 
     def cpu_sample(self, threads=True):
-        """One stream, 8 tokens through the reference-form one-token step on the CPU port, full widths;
+        """One stream, 128 tokens through the reference-form one-token step on the CPU port, full widths;
         the cross K/V of the clip are random stand-ins (their one-off products are left out of the sample)."""
         from oracle.wasm_oracle import WasmOracle
         from fluidaudio_web_b200.engines import synth, whisper_decoder
@@ -623,8 +623,8 @@ class Decoder:
                        v=ora.upload(rng.standard_normal((1500, 1280), dtype=np.float32), 1500, 1280)) for _ in range(cfg["layers"])]
             Decoder._cpu_dec = ((self.quant, threads), ora, dec, kv)
         _, ora, dec, kv = Decoder._cpu_dec
-        st = whisper_decoder.decode_init(ora, dec, 16)
-        n = 8
+        n = 128
+        st = whisper_decoder.decode_init(ora, dec, n)
         tok = 1
         t0 = time.perf_counter()
         for _ in range(n):
@@ -637,8 +637,93 @@ class DecoderInt8(Decoder):
     quant = "int8"
 
 
+class F16GemmNSharded:
+    """BASELINE config 3, its multi-GPU leg: the M = 16384 row of the f16 GEMM sweep with the output columns
+    sharded over the ranks (each GPU holds N/world columns of every weight matrix) and an NCCL all-gather of
+    the column blocks, so every rank ends with the whole row-major [M, N] product.  Total work is fixed as
+    the number of GPUs grows ("strong" scaling); value = whole-product FLOPs / max-over-ranks time.  Seed 2."""
+
+    name = "f16_gemm_m16384_n_sharded_allgather"
+    metric = "f16_gemm_throughput"
+    unit = "TFLOP/s"
+    dtype = "f16 x f16 -> f32 accumulate, f32 out"
+    nsets = 1
+    scaling = "strong"
+    graph = False  # the collective is enqueued by torch.distributed between the products: eager steps
+
+    def __init__(self, quick=False):
+        self.M = 4096 if quick else 16384
+        self.KNs = ((1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024))
+
+    def setup(self, ctx):
+        import __graft_entry__ as ge
+
+        ge.load_package()
+        from fluidaudio_web_b200 import sharding
+
+        self.sh = sharding
+        rank, _lr, world = dist_env()
+        self.world = world
+        rng = np.random.default_rng(2)
+        self.W = {}
+        for kn in self.KNs:
+            w = (rng.standard_normal(kn) / np.sqrt(kn[0])).astype(np.float32)
+            ws = sharding.column_shard(w, world, rank)
+            self.W[kn] = ctx.uploadF16(ws, ws.shape[0], ws.shape[1])
+        self.host_A, self.A = {}, {}
+        for K in sorted({k for k, _ in self.KNs}):
+            buf = ctx.pinnedArray(self.M * K)
+            buf[:] = rng.standard_normal(self.M * K).astype(np.float32)
+            self.host_A[K] = buf
+            self.A[K] = ctx.upload(buf, self.M, K)
+        self.units_per_step = len(self.KNs)
+        self.flops_per_step = sum(2.0 * self.M * K * N for K, N in self.KNs)
+
+    def _product(self, ctx, a, kn):
+        if self.world == 1:
+            return ctx.matmul(a, self.W[kn])
+        return self.sh.matmul_n_sharded(ctx, a, self.W[kn])
+
+    def step_device(self, ctx):
+        h = ctx.pushArena()
+        self.sh.matmul_n_sharded_many(ctx, [(self.A[kn[0]], self.W[kn]) for kn in self.KNs])
+        ctx.popArena(h)
+
+    def step_e2e(self, ctx):
+        h = ctx.pushArena()
+        outs = self.sh.matmul_n_sharded_many(ctx, [(ctx.upload(self.host_A[kn[0]], self.M, kn[0]), self.W[kn]) for kn in self.KNs])
+        out = [ctx.download(o) for o in outs][-1]
+        ctx.popArena(h)
+        return out
+
+    def nvlink_bytes_per_step(self):
+        """Bytes every rank must receive over NVLink per step: (world-1)/world of each f32 product."""
+        return sum(4 * self.M * N for _, N in self.KNs) * (self.world - 1) // self.world
+
+    def e2e_bytes(self):
+        return sum(4 * self.M * K for K, _ in self.KNs), sum(4 * self.M * N for _, N in self.KNs)
+
+    def value_from(self, steps, seconds):
+        return self.flops_per_step * steps / seconds / 1e12
+
+    def roofline(self, prof, peaks):
+        ent = [e for e in prof if e["label"].startswith("tc_gemm_f16")]
+        if not ent:
+            return None
+        ms = sum(e["ms"] for e in ent)
+        n = sum(e["count"] for e in ent)
+        return {"bound": "tensor", "achieved": self.flops_per_step / self.world / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": None, "traffic": None, "kernel": "k_tc_gemm<f16> (this rank's column block)",
+                "launches": n, "avg_launch_us": round(ms / n * 1e3, 2), "peak_source": peaks["source"] + " (burst bf16)",
+                "nvlink_bytes_per_step_per_rank": self.nvlink_bytes_per_step(),
+                "note": "with world > 1 the step is bound by the all-gather: f32 outputs leave a GPU faster than NVLink takes them "
+                        "(K=1024 products make 1 output byte per 512 FLOP); step floor = nvlink bytes / 770 GB/s measured peer copy"}
+
+    cpu_sample = F16Gemm.cpu_sample
+
+
 WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "f16_gemm": F16Gemm, "encoder": Encoder,
-             "decoder": Decoder, "decoder_int8": DecoderInt8}
+             "decoder": Decoder, "decoder_int8": DecoderInt8, "f16_gemm_nsharded": F16GemmNSharded}
 DEFAULT_WORKLOAD = "encoder"
 
 
@@ -720,19 +805,27 @@ def run_cuda(args):
     ctx.sync()
     # the step is recorded once (one CUDA graph = the reference's one-submit batch) and replayed
     l0 = ctx.launchCount()
-    batch, _ = ctx.recordBatch(lambda: wl.step_device(ctx))
+    use_graph = getattr(wl, "graph", True)
+    if use_graph:
+        batch, _ = ctx.recordBatch(lambda: wl.step_device(ctx))
+    else:
+        wl.step_device(ctx)
+        batch = None
     launches_per_step = ctx.launchCount() - l0
     for _ in range(3):
-        batch.launch()
+        batch.launch() if use_graph else wl.step_device(ctx)
     ctx.sync()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = timed(lambda _ctx: batch.launch(), args.steps)
+    ms = timed((lambda _ctx: batch.launch()) if use_graph else wl.step_device, args.steps)
     launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
-    batch.free()
-    value = wl.value_from(args.steps, ms * 1e-3) * world
+    if use_graph:
+        batch.free()
+    scaling = getattr(wl, "scaling", "weak")
+    units = world if scaling == "weak" else 1  # weak: every rank ran a whole step; strong: the ranks shared one
+    value = wl.value_from(args.steps, ms * 1e-3) * units
 
     # per-launch durations of the dominant kernel: same steps again with an event pair around each launch
     psteps = min(args.steps, getattr(wl, "profile_steps", args.steps))
@@ -765,7 +858,7 @@ def run_cuda(args):
         t = torch.tensor([e2e_s], device=f"cuda:{local_rank}")
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         e2e_s = float(t.item())
-    e2e_val = wl.value_from(args.steps, e2e_s) * world
+    e2e_val = wl.value_from(args.steps, e2e_s) * units
     h2d, d2h = wl.e2e_bytes()
 
     cpu = None
@@ -779,9 +872,10 @@ def run_cuda(args):
     if rank == 0:
         line = {"metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+                "scaling": scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
                 "config": {"workload": wl.name, "l2": f"rotating weight set of {wl.nsets} matrices (> 126 MB L2)",
-                           "timing": "CUDA events on the context stream around K replays of the recorded step (CUDA graph), max over ranks",
+                           "timing": ("CUDA events on the context stream around K replays of the recorded step (CUDA graph), max over ranks"
+                                      if use_graph else "CUDA events on the context stream around K eager steps, max over ranks"),
                            "roofline_timing": "per-launch CUDA event pairs, repeat pass of the same steps"},
                 "roofline": roof, "cpu_baseline": cpu,
                 "e2e": {"value": round(e2e_val, 3), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

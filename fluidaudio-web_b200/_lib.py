@@ -83,6 +83,7 @@ SIGNATURES = {
     "fa_sub_reshape": [P, P, I, I, I, PP],
     "fa_argmax_rows": [P, P, I, PP],
     "fa_embed_rows": [P, P, P, P, I, PP],
+    "fa_unshard_cols": [P, P, I, PP],
     "fa_profile_start": [P, I],
     "fa_profile_end": [P, C.POINTER(ProfileEntry), I, IP],
 }

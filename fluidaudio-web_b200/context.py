@@ -386,6 +386,10 @@ class CudaContext:
         host token pick moved to the device."""
         return self._op(self._lib.fa_argmax_rows, x.h, ncols)
 
+    def unshardCols(self, gathered: Tensor, world: int) -> Tensor:
+        """[world*M, Ns] column shards stacked along rows -> the row-major [M, world*Ns] product."""
+        return self._op(self._lib.fa_unshard_cols, gathered.h, world)
+
     def embedRows(self, table: Tensor, pos: Tensor, idx: Tensor, n: int) -> Tensor:
         """[S, D] = table[id_s] + pos[n], ids read from column 0 of `idx` on the device (so a greedy
         decode needs no host round trip between tokens)."""

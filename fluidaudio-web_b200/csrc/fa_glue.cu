@@ -952,6 +952,41 @@ extern "C" int fa_set_cols(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, in
   return FA_OK;
 }
 
+// Column shards stacked along rows, g [world*M][Ns] (what an all-gather of per-rank [M][Ns] results
+// leaves), into the row-major product out [M][world*Ns]: out[m][r*Ns + j] = g[r*M + m][j].
+__global__ void __launch_bounds__(256) k_unshard_cols(const float4 *__restrict__ g, float4 *__restrict__ out, int M,
+                                                      int ns4, int world) {
+  const size_t total = (size_t)world * M * ns4;
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
+    const int j = (int)(i % ns4);
+    const size_t rm = i / ns4;
+    const int m = (int)(rm % M), r = (int)(rm / M);
+    out[((size_t)m * world + r) * ns4 + j] = g[i];
+  }
+}
+
+extern "C" int fa_unshard_cols(fa_ctx *ctx, const fa_tensor *gathered, int world, fa_tensor **out) {
+  GLUE_PROLOGUE("unshardCols");
+  FA_TRY(need_f32(ctx, gathered, "unshardCols"));
+  FA_REQUIRE(ctx, world >= 1 && gathered->rows % world == 0, "unshardCols: %d rows do not split into %d shards",
+             gathered->rows, world);
+  FA_REQUIRE(ctx, (gathered->cols & 3) == 0, "unshardCols: shard width %d is not a multiple of 4", gathered->cols);
+  const int M = gathered->rows / world, ns = gathered->cols;
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, M, world * ns, FA_F32, true, &y));
+  const size_t n4 = (size_t)gathered->rows * (ns / 4);
+  if (n4) {
+    {
+      LaunchScope ls(ctx, "unshard_cols");
+      k_unshard_cols<<<grid1d(ctx, n4, 256), 256, 0, ctx->stream>>>((const float4 *)gathered->dptr, (float4 *)y->dptr, M,
+                                                                    ns / 4, world);
+    }
+    FA_LAUNCH_CHECK(ctx, "unshard_cols");
+  }
+  *out = y;
+  return FA_OK;
+}
+
 extern "C" int fa_slice_rows(fa_ctx *ctx, const fa_tensor *x, int row0, int count, fa_tensor **out) {
   GLUE_PROLOGUE("sliceRows");
   FA_TRY(need_f32(ctx, x, "sliceRows"));

@@ -40,6 +40,92 @@ def gather_rows(local: np.ndarray, world: int, rank: int, group=None) -> Optiona
     return np.concatenate([p.reshape(-1, cols) for p in parts], axis=0)
 
 
+def column_shard(w: np.ndarray, world: int, rank: int) -> np.ndarray:
+    """This rank's block of output columns of a [K, N] weight matrix (N divisible by world)."""
+    N = w.shape[1]
+    if N % world:
+        raise ValueError(f"N={N} does not split evenly over {world} ranks")
+    ns = N // world
+    return np.ascontiguousarray(w[:, rank * ns:(rank + 1) * ns])
+
+
+def unshard_cols_host(gathered: np.ndarray, world: int) -> np.ndarray:
+    """Host statement of the device unshardCols: [world*M, Ns] -> [M, world*Ns]."""
+    M = gathered.shape[0] // world
+    return np.ascontiguousarray(gathered.reshape(world, M, -1).transpose(1, 0, 2).reshape(M, -1))
+
+
+class _DeviceArray:
+    """A device buffer of the context seen through __cuda_array_interface__, so torch.distributed can
+    send and receive it in place (no staging copy)."""
+
+    def __init__(self, ptr: int, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+
+
+def as_torch(ctx, t):
+    import torch
+
+    return torch.as_tensor(_DeviceArray(ctx.devicePtr(t), (t.rows, t.cols)), device=f"cuda:{ctx.device}")
+
+
+def matmul_n_sharded(ctx, a, w_shard, opts=None, group=None):
+    """The one exchange step of the path: every rank multiplies the same activations [M, K] by its block of
+    output columns [K, N/world] on its own GPU, then an NCCL all-gather over NVLink brings all blocks to
+    every rank and unshardCols lays them out as the row-major [M, N] product.  The collective runs on the
+    context's stream (ordered after the product, before the unshard)."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    c_local = ctx.matmul(a, w_shard, opts)
+    if world == 1:
+        return c_local
+    gathered = ctx.alloc(world * c_local.rows, c_local.cols)
+    stream = torch.cuda.ExternalStream(ctx.stream(), device=ctx.device)
+    with torch.cuda.stream(stream):
+        dist.all_gather_into_tensor(as_torch(ctx, gathered), as_torch(ctx, c_local), group=group)
+    out = ctx.unshardCols(gathered, world)
+    ctx.freeTensor(gathered)
+    ctx.freeTensor(c_local)
+    return out
+
+
+def matmul_n_sharded_many(ctx, pairs, group=None):
+    """Several N-sharded products back to back, pipelined: the all-gather of product i runs on a side
+    stream while product i+1 is computed; the unshard of each result waits only for its own gather.
+    `pairs` = [(a, w_shard), ...]; returns the row-major [M, N] products in order."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    if world == 1:
+        return [ctx.matmul(a, w) for a, w in pairs]
+    ext = torch.cuda.ExternalStream(ctx.stream(), device=ctx.device)
+    comm = getattr(ctx, "_comm_stream", None)
+    if comm is None:
+        comm = ctx._comm_stream = torch.cuda.Stream(device=ctx.device)
+    pending = []
+    for a, w in pairs:
+        c = ctx.matmul(a, w)
+        g = ctx.alloc(world * c.rows, c.cols)
+        ready = torch.cuda.Event()
+        ready.record(ext)
+        comm.wait_event(ready)
+        with torch.cuda.stream(comm):
+            dist.all_gather_into_tensor(as_torch(ctx, g), as_torch(ctx, c), group=group)
+            done = torch.cuda.Event()
+            done.record(comm)
+        pending.append((c, g, done))
+    outs = []
+    for c, g, done in pending:
+        ext.wait_event(done)
+        outs.append(ctx.unshardCols(g, world))
+        ctx.freeTensor(g)
+        ctx.freeTensor(c)
+    return outs
+
+
 def encode_windows_sharded(ctx, enc, mels: Sequence[np.ndarray], world: int, rank: int, batch: int = 32, group=None):
     """Encode this rank's block of windows in batches of `batch` and gather the frames on rank 0.
     Returns ([n_windows * Tsub, D] on rank 0 else None, Tsub)."""

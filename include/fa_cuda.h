@@ -201,6 +201,11 @@ int fa_sub_reshape(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, fa_t
  * columns of each row take part (ncols <= 0: all of them) - the tied vocabulary projection is padded
  * with zero columns that must never win (raw-whisper-decoder.js:62-66). */
 int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, int ncols, fa_tensor **out);
+/* N-sharded products (one process per GPU, each holding a block of output columns): `gathered`
+ * [world*M, Ns] is what an all-gather of the ranks' [M, Ns] results leaves; out [M, world*Ns] is the
+ * row-major product, out[m, r*Ns + j] = gathered[r*M + m, j].  Ns must be a multiple of 4.  The
+ * reference has no multi-device path (one GPUDevice, src/gpu/device.js). */
+int fa_unshard_cols(fa_ctx *ctx, const fa_tensor *gathered, int world, fa_tensor **out);
 /* Token embedding + position on the device (the reference gathers on the host and uploads,
  * src/engines/asr-whisper/raw-whisper-decoder.js:106-108): out[s,:] = table[id_s,:] + pos[n,:], where id_s
  * is column 0 of row s of idx (token ids as floats: an fa_argmax_rows result or a [S,1] tensor).  With it

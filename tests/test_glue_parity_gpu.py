@@ -150,3 +150,13 @@ def test_conv_module_fast_members_match_the_op_sequence(ctx):
     glu = ctx.glu(ctx.transpose(pre1))
     close(ctx, ctx.conv1dWindows(glu, dw, dict(opts, bias=b), W), ref, 1e-4)
     close(ctx, ctx.gluDwConvTimeMajor(pre1, dw, dict(opts, bias=b), W), ORA.transpose(ref), 1e-4)
+
+
+def test_unshard_cols_matches_host_statement(ctx, pkg):
+    from fluidaudio_web_b200 import sharding
+
+    rng = np.random.default_rng(8)
+    for world, M, ns in ((2, 5, 8), (4, 33, 12), (8, 16, 128), (1, 3, 4)):
+        g = rng.standard_normal((world * M, ns)).astype(np.float32)
+        got = ctx.download(ctx.unshardCols(ctx.upload(g, world * M, ns), world)).reshape(M, world * ns)
+        assert np.array_equal(got, sharding.unshard_cols_host(g, world))

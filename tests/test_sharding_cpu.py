@@ -64,3 +64,55 @@ def test_shard_ranges_cover_and_order(pkg):
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         sharding.shard_range(4, 2, 2)
+
+
+def _nshard_worker(rank, world, port, out_path):
+    """N-sharded product on two gloo ranks: each multiplies by its column block on the CPU oracle backend,
+    the blocks are all-gathered along rows and unsharded into the row-major product."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+
+    ge.load_package()
+    from fluidaudio_web_b200 import sharding
+    from oracle.wasm_oracle import WasmOracle
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(2)
+        a = rng.standard_normal((6, 40)).astype(np.float32)
+        w = rng.standard_normal((40, 24)).astype(np.float32)
+        ora = WasmOracle()
+        ws = sharding.column_shard(w, world, rank)
+        local = ora.matmul(ora.upload(a, 6, 40), ora.upload(ws, 40, ws.shape[1])).array()
+        gathered = torch.empty((world * 6, ws.shape[1]), dtype=torch.float32)
+        dist.all_gather_into_tensor(gathered, torch.from_numpy(np.ascontiguousarray(local)))
+        full = sharding.unshard_cols_host(gathered.numpy(), world)
+        np.save(out_path + f".{rank}.npy", full)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_n_sharded_product_two_gloo_ranks(pkg, tmp_path):
+    from oracle.wasm_oracle import WasmOracle
+
+    out = str(tmp_path / "ns")
+    port = 29850 + os.getpid() % 100
+    mp.spawn(_nshard_worker, args=(2, port, out), nprocs=2, join=True)
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((6, 40)).astype(np.float32)
+    w = rng.standard_normal((40, 24)).astype(np.float32)
+    ora = WasmOracle()
+    ref = ora.matmul(ora.upload(a, 6, 40), ora.upload(w, 40, 24)).array()
+    for r in range(2):  # every rank ends with the whole product, bit for bit (same per-column arithmetic)
+        assert np.array_equal(np.load(out + f".{r}.npy"), ref)
+
+
+def test_column_shard_rejects_uneven(pkg):
+    from fluidaudio_web_b200 import sharding
+
+    with pytest.raises(ValueError):
+        sharding.column_shard(np.zeros((4, 10), np.float32), 4, 0)
+    parts = [sharding.column_shard(np.arange(24, dtype=np.float32).reshape(2, 12), 3, r) for r in range(3)]
+    assert np.array_equal(np.concatenate(parts, axis=1), np.arange(24, dtype=np.float32).reshape(2, 12))
