@@ -117,6 +117,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->f16_hilo_rows = value > 0x7fffffffLL ? 0x7fffffff : (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "nbits_fused")) {
+    FA_REQUIRE(ctx, value == 0 || value == 1, "nbits_fused must be 0 or 1 (got %lld)", value);
+    ctx->nbits_fused = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "gemv_rows")) {
     FA_REQUIRE(ctx, value >= 0 && value <= kGemvMaxRows, "gemv_rows must be 0..%d (got %lld)", kGemvMaxRows, value);
     ctx->gemv_rows = (int)value;
@@ -374,6 +379,7 @@ extern "C" int fa_free_bytes(fa_ctx *ctx, fa_bytes *b) {
   FA_REQUIRE(ctx, fa_valid_bytes(ctx, b), "freeBytes: unknown or already freed handle");
   if (b->nk_i8) fa_block_release(ctx, b->nk_i8);
   if (b->nk_f16) fa_block_release(ctx, b->nk_f16);
+  if (b->nb_side) fa_block_release(ctx, b->nb_side);
   fa_block_release(ctx, b->dptr);
   ctx->byte_handles.erase(b);
   delete b;

@@ -38,6 +38,13 @@ constexpr int kEpiWarps = 8;                   // two per TMEM lane quadrant
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
 constexpr int kRowBytes = 128;                 // one swizzle atom of K per stage
 constexpr int kPTileBytes = 128 * kRowBytes;   // weights tile: 128 rows
+// int4 variant: 8 more warps unpack nibbles into the f16 weights tile.  They sit on warp ids 10,11,14,15,18,19,22,23
+// (ids 12,13,16,17,20,21 have no role and park at the closing barrier): with warps dealt to the four schedulers round-robin, that keeps the busy
+// unpack warps off the schedulers of warp 0 (TMA producer) and warp 1 (MMA issuer), whose single-lane loops
+// otherwise get every third issue slot and set the pace of the whole pipeline (measured: ~550 ns per K chunk).
+constexpr int kDeqWarps = 8;
+constexpr int kThreadsNbits = 32 * 24;
+constexpr int kRawTileBytes = 128 * 32;        // int4 variant: 128 rows x 64 nibbles of one K chunk, as uploaded
 constexpr int kSplitMaxMT = 128;               // split-K mode keeps a [MT][128] f32 partial tile in smem
 
 struct TcParams {
@@ -62,6 +69,10 @@ struct TcParams {
   float *out;         // [M][N] f32 (or int32 when raw_i32)
   const float *rowscale, *colscale, *bias, *add, *rowbias;
   int act;
+  // int4 variant (KIND 2): block-major scales [nblk][N] and zero-points [nblk][N] (one per byte)
+  const float *nb_scales;
+  const uint8_t *nb_zp;
+  int nblk;
   int *status;
   unsigned long long *trace;  // debugging aid: per-phase %globaltimer stamps of CTA 0, or nullptr
 };
@@ -222,23 +233,34 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
   }
 }
 
+// KIND 0: f16 weights, 1: int8 weights, 2: int4 (MatMulNBits) weights.  KIND 2 is the f16 pipeline with one more
+// stage in front of the MMA: TMA brings the RAW nibbles of a K chunk (128 rows x 32 bytes, the reference's
+// layout as uploaded) next to the activation tile, eight extra warps unpack them in shared memory into the
+// swizzled f16 weights tile - (q - zp) * scale per 32-weight block, two f16 lanes per instruction - and hand the
+// slot to the MMA warp through a third barrier.  HBM sees 0.5 byte per weight instead of a 2-byte f16 copy.
+// Within every group of 8 weights the unpack leaves k in the order 0,4,1,5,2,6,3,7 (the pairs one mask
+// extracts); the activation tile is packed in the same order, and a sum over k does not care.
 template <int KIND>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(KIND == 2 ? kThreadsNbits : kThreads, 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
+  constexpr int MK = KIND == 2 ? 0 : KIND;  // MMA kind and epilogue arithmetic
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B), barriers, split-K partial tile
+  // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B | raw nibble tile 4 KB for KIND 2), barriers,
+  // split-K partial tile
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int q_rows = p.MT * p.limbs;
   const uint32_t q_bytes = (uint32_t)q_rows * kRowBytes;
-  const uint32_t stage_bytes = kPTileBytes + q_bytes;
+  const uint32_t stage_bytes = kPTileBytes + q_bytes + (KIND == 2 ? kRawTileBytes : 0);
   const uint32_t bars = smem_base + (uint32_t)p.stages * stage_bytes;  // 8-byte aligned (stage_bytes % 1024 == 0)
   auto full_bar = [&](int s) { return bars + (uint32_t)s * 8u; };
   auto empty_bar = [&](int s) { return bars + (uint32_t)(p.stages + s) * 8u; };
   auto acc_full = [&](int b) { return bars + (uint32_t)(2 * p.stages + b) * 8u; };
   auto acc_empty = [&](int b) { return bars + (uint32_t)(2 * p.stages + 2 + b) * 8u; };
-  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4) * 8u;
+  auto deq_bar = [&](int s) { return bars + (uint32_t)(2 * p.stages + 4 + s) * 8u; };  // KIND 2 only
+  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4 + (KIND == 2 ? p.stages : 0)) * 8u;
   const uint32_t abort_flag = tmem_slot + 4u;
-  const uint32_t partial = tmem_slot + 16u;  // [MT][128] f32, split-K mode only
+  const uint32_t partial = (tmem_slot + 16u + 15u) & ~15u;  // [MT][128] f32, split-K mode only; 16-byte aligned for
+                                                            // the vector loads of the reduction (3*stages+4 may be odd)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int acc_cols = p.limb_sum ? p.MT : q_rows;
@@ -253,6 +275,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     for (int s = 0; s < p.stages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
+      if (KIND == 2) mbar_init(deq_bar(s), kDeqWarps / 2);  // the four warps of the group that owns the chunk
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(acc_full(b), 1);
@@ -310,8 +333,13 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             break;
           }
           if (it < 64) TC_TRACE(1 + it);
-          mbar_expect_tx(fb, stage_bytes);
-          tma_load_2d(dst, &map_w, 0, wrow, fb);
+          if (KIND == 2) {
+            mbar_expect_tx(fb, q_bytes + kRawTileBytes);
+            tma_load_2d(dst + kPTileBytes + q_bytes, &map_w, 0, (tn * p.num_kb + kb) * 16, fb);  // 4 KB nibble tile
+          } else {
+            mbar_expect_tx(fb, stage_bytes);
+            tma_load_2d(dst, &map_w, 0, wrow, fb);
+          }
           tma_load_3d(dst + kPTileBytes, &map_a, 0, m0, aslab, fb);
           for (int l = 1; l < p.limbs; l++)
             tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
@@ -326,7 +354,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ---- MMA issuer: alternates between the two TMEM accumulator buffers -----------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(KIND, 128, acc_cols);
+      const uint32_t idesc = make_idesc(MK, 128, acc_cols);
       const uint32_t nst = (uint32_t)p.stages;
       const uint64_t desc0 = smem_desc_sw128(smem_base);  // slot 0 weights tile; other tiles are address offsets
       const uint64_t q_off = (uint64_t)(kPTileBytes >> 4), st_off = (uint64_t)(stage_bytes >> 4);
@@ -348,18 +376,23 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             ok = false;
             break;
           }
+          if (KIND == 2 && !mbar_wait(fb + (2u * nst + 4u) * 8u, ph)) {  // weights tile unpacked
+            set_abort(6, kb);
+            ok = false;
+            break;
+          }
           tc_fence_after();
           if (it < 64) TC_TRACE(65 + it);
           const uint64_t da = desc0 + (uint64_t)s * st_off, db = da + q_off;
-          umma<KIND>(d_tmem, da, db, idesc, kb > kb0 ? 1u : 0u);  // 4 x 32 bytes of K per slot
-          umma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
-          umma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
-          umma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
+          umma<MK>(d_tmem, da, db, idesc, kb > kb0 ? 1u : 0u);  // 4 x 32 bytes of K per slot
+          umma<MK>(d_tmem, da + 2, db + 2, idesc, 1u);
+          umma<MK>(d_tmem, da + 4, db + 4, idesc, 1u);
+          umma<MK>(d_tmem, da + 6, db + 6, idesc, 1u);
           if (p.limb_sum) {
-            umma<KIND>(d_tmem, da, db + lo_off, idesc, 1u);
-            umma<KIND>(d_tmem, da + 2, db + lo_off + 2, idesc, 1u);
-            umma<KIND>(d_tmem, da + 4, db + lo_off + 4, idesc, 1u);
-            umma<KIND>(d_tmem, da + 6, db + lo_off + 6, idesc, 1u);
+            umma<MK>(d_tmem, da, db + lo_off, idesc, 1u);
+            umma<MK>(d_tmem, da + 2, db + lo_off + 2, idesc, 1u);
+            umma<MK>(d_tmem, da + 4, db + lo_off + 4, idesc, 1u);
+            umma<MK>(d_tmem, da + 6, db + lo_off + 6, idesc, 1u);
           }
           umma_commit(fb + nst * 8u);  // frees the slot when these MMAs have read it
           if (++s == nst) {
@@ -368,6 +401,103 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           }
         }
         if (ok) umma_commit(acc_full(buf));  // this tile's accumulators are complete
+      }
+    }
+    __syncwarp();
+  } else if (KIND == 2 && warp >= 2 + kEpiWarps && (warp & 2) == 0) {
+    // spare warp ids (see kDeqWarps): no role; they wait at the barriers below with everyone else
+  } else if (KIND == 2 && warp >= 2 + kEpiWarps) {
+    // ---- int4 unpack: two groups of four warps take alternate K chunks, so one group's load-unpack-store
+    // chain overlaps the other's; a thread owns weight row r of the tile for both 32-weight blocks of a chunk
+    // warps 10,11,14,15 -> unpack index 0..3 (group 0), warps 18,19,22,23 -> 4..7 (group 1)
+    const int dw = ((warp - 10) >> 2) * 2 + (warp & 1);
+    const int dq = dw * 32 + lane, r = dq & 127, grp = dq >> 7;
+    const uint32_t nst = (uint32_t)p.stages;
+    const int chunks = kb1 - kb0;
+    uint32_t tiles_done = 0;
+    bool ok = true;
+    const __half2 sixteenth = __float2half2_rn(0.0625f);
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tiles_done++) {
+      const int tn = (tile % (p.tiles_n * p.tiles_m)) % p.tiles_n;
+      const int n = min(tn * 128 + r, p.N - 1);
+      // Scale and zero-point of (block, row) from the block-major side copy: a warp's 32 rows are one
+      // 128-byte (scales) and one 32-byte (zero-points) request.  (Read in the uploaded [N][nblk] order, every
+      // lane touched its own sector and the load/store unit, not DRAM, set the pace of the unpack.)  Fetched
+      // for 4 of this group's chunks at a time, one batch ahead.
+      const float *srow = p.nb_scales + n;
+      const uint8_t *zrow = p.nb_zp + n;
+      constexpr int G = 4;
+      float scg[2 * G], scn[2 * G];
+      unsigned long long zbg = 0, zbn = 0;  // (chunk i, block hb) in bits [8(2i+hb), 8(2i+hb)+8)
+      const uint32_t it_base = tiles_done * (uint32_t)chunks;   // ring index of this tile's first chunk
+      const int first = (int)((grp - (it_base & 1u)) & 1u);     // this group's first chunk within the tile
+      auto fetch = [&](int c0, float *sc, unsigned long long &zb) {
+        zb = 0;
+#pragma unroll
+        for (int i = 0; i < G; i++)
+#pragma unroll
+          for (int hb = 0; hb < 2; hb++) {
+            const size_t blk = (size_t)min(2 * (kb0 + c0 + 2 * i) + hb, p.nblk - 1);
+            sc[2 * i + hb] = __ldg(srow + blk * p.N);
+            zb |= (unsigned long long)__ldg(zrow + blk * p.N) << (8 * (2 * i + hb));
+          }
+      };
+      fetch(first, scg, zbg);
+      for (int cg = first; cg < chunks && ok; cg += 2 * G) {
+        if (cg + 2 * G < chunks) fetch(cg + 2 * G, scn, zbn);
+#pragma unroll
+        for (int i = 0; i < G; i++) {
+          const int c = cg + 2 * i;
+          if (c >= chunks) break;
+          const uint32_t it = it_base + (uint32_t)c, slot_i = it % nst, ph = (it / nst) & 1u;
+          const bool tr = dq == 0 && c < 32;
+          if (tr) TC_TRACE(140 + 4 * (c >> 1));
+          int okw = 1;
+          if (lane == 0 && !mbar_wait(full_bar((int)slot_i), ph)) {
+            set_abort(5, c);
+            okw = 0;
+          }
+          ok = __shfl_sync(0xffffffffu, okw, 0) != 0 && !aborted();
+          if (!ok) break;
+          if (tr) TC_TRACE(141 + 4 * (c >> 1));
+          const uint32_t slot = smem_base + slot_i * stage_bytes;
+#pragma unroll
+          for (int hb = 0; hb < 2; hb++) {
+            uint32_t wd[4];
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(wd[0]), "=r"(wd[1]), "=r"(wd[2]), "=r"(wd[3])
+                         : "r"(slot + kPTileBytes + q_bytes + (uint32_t)(r * 32 + hb * 16))
+                         : "memory");
+            const int z = (int)((unsigned)(zbg >> (8 * (2 * i + hb))) & 0xFFu);
+            const __half2 s2 = __float2half2_rn(scg[2 * i + hb]);
+            const __half2 zsub = __half2half2(__int2half_rn(1024 + z));   // (1024 + q) - (1024 + zp)
+            const __half2 zneg = __half2half2(__int2half_rn(-(64 + z)));  // (1024 + 16 q) / 16 - (64 + zp)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const uint32_t w0 = wd[j], w8 = wd[j] >> 8;
+              uint32_t a0 = (w0 & 0x000F000Fu) | 0x64006400u;  // nibbles 0,4 as 1024 + q
+              uint32_t a1 = (w0 & 0x00F000F0u) | 0x64006400u;  // nibbles 1,5 as 1024 + 16 q
+              uint32_t a2 = (w8 & 0x000F000Fu) | 0x64006400u;  // nibbles 2,6
+              uint32_t a3 = (w8 & 0x00F000F0u) | 0x64006400u;  // nibbles 3,7
+              __half2 h0 = __hmul2(__hsub2(*(__half2 *)&a0, zsub), s2);
+              __half2 h1 = __hmul2(__hfma2(*(__half2 *)&a1, sixteenth, zneg), s2);
+              __half2 h2 = __hmul2(__hsub2(*(__half2 *)&a2, zsub), s2);
+              __half2 h3 = __hmul2(__hfma2(*(__half2 *)&a3, sixteenth, zneg), s2);
+              const uint32_t cc = (uint32_t)(hb * 4 + j);
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(slot + (uint32_t)(r * 128) + ((cc ^ (uint32_t)(r & 7)) << 4)),
+                           "r"(*(uint32_t *)&h0), "r"(*(uint32_t *)&h1), "r"(*(uint32_t *)&h2), "r"(*(uint32_t *)&h3)
+                           : "memory");
+            }
+          }
+          if (tr) TC_TRACE(142 + 4 * (c >> 1));
+          fence_proxy_async_smem();  // the tile is read by the tensor core through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(deq_bar((int)slot_i));
+          if (tr) TC_TRACE(143 + 4 * (c >> 1));
+        }
+#pragma unroll
+        for (int i = 0; i < 2 * G; i++) scg[i] = scn[i];
+        zbg = zbn;
       }
     }
     __syncwarp();
@@ -383,14 +513,22 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       float *const outb = p.out + (size_t)(batch / p.o_div) * p.o_hi + (size_t)(batch % p.o_div) * p.o_lo;
       const int r16 = (batch / p.o_div) * p.o16_row_hi, c16 = (batch % p.o_div) * p.o16_col_lo;
       const uint32_t buf = lt & 1, use = lt >> 1;
-      ok = mbar_wait(acc_full(buf), use & 1);
+      if (KIND == 2) {  // leave the issue slots to the unpack warps while the tile is being accumulated
+        ok = false;
+        for (uint32_t i = 0; i < (kWaitLimit >> 4) && !ok; i++) {
+          ok = mbar_try_wait(acc_full(buf), use & 1) != 0;
+          if (!ok) __nanosleep(256);
+        }
+      } else {
+        ok = mbar_wait(acc_full(buf), use & 1);
+      }
       if (!ok && lane == 0) set_abort(3, tile);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !aborted();
       if (!ok) break;
       tc_fence_after();
       if (threadIdx.x == 64) TC_TRACE(129);
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<KIND>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial);
+      epilogue_tile<MK>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial);
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -407,7 +545,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     cluster_sync_all();
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-    if (warp >= 2 && !aborted()) {
+    if (warp >= 2 && warp < 2 + kEpiWarps && !aborted()) {
       const int tile = blockIdx.x, tn = tile % p.tiles_n, tm = tile / p.tiles_n;
       const int n0 = tn * 128, m0 = tm * p.MT;
       const int t = threadIdx.x - 64;  // 256 threads, each owns groups of 4 consecutive columns
@@ -652,6 +790,43 @@ __global__ void k_prep_a_f16(const float *__restrict__ a, int M, int K, int nch,
   }
 }
 
+// bq [N][nblk][16] -> nibble tiles [n/128][k/64][n%128][32 B] (same 4-bit payload, tile-contiguous: a K chunk of
+// a 128-row tile read from the uploaded layout is 128 separate 32-byte pieces, one DRAM access each).
+__global__ void k_nbits_tiles(const uint4 *__restrict__ bq, int N, int nblk, int tiles_n, int num_kb, uint4 *__restrict__ out) {
+  const size_t total = (size_t)tiles_n * num_kb * 128 * 2;  // 16-byte pieces = one 32-weight block each
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int hb = (int)(i & 1), r = (int)((i >> 1) & 127);
+    const size_t tk = i >> 8;
+    const int kb = (int)(tk % num_kb), tn = (int)(tk / num_kb);
+    const int n = tn * 128 + r, blk = kb * 2 + hb;
+    out[i] = (n < N && blk < nblk) ? bq[(size_t)n * nblk + blk] : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+__global__ void k_nbits_side(const float *__restrict__ scales, const uint8_t *__restrict__ zp, int N, int nblk, int zpb,
+                             float *__restrict__ scales_t, uint8_t *__restrict__ zp_t) {
+  const size_t total = (size_t)N * nblk;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int n = (int)(i % N), blk = (int)(i / N);
+    scales_t[i] = scales[(size_t)n * nblk + blk];
+    const unsigned zb = zp[(size_t)n * zpb + (blk >> 1)];
+    zp_t[i] = (uint8_t)((blk & 1) ? (zb >> 4) : (zb & 15u));
+  }
+}
+
+// f32 [M][K] -> f16 Ap[k/64][m][64] for the int4 variant: inside every group of 8 the order of k is
+// 0,4,1,5,2,6,3,7, the order its in-kernel nibble unpack produces.
+__global__ void k_prep_a_f16_perm8(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
+  const size_t total = (size_t)nch * M * 32;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int pr = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
+    const int k = c * 64 + (pr >> 2) * 8 + (pr & 3);  // pair j of group g holds k = 8g + j and 8g + j + 4
+    const float *row = a + (size_t)m * K;
+    const float x = k < K ? row[k] : 0.0f, y = k + 4 < K ? row[k + 4] : 0.0f;
+    ((__half2 *)out)[i] = __floats2half2_rn(x, y);
+  }
+}
+
 // f32 [M][K] -> two f16 planes Ap[2][k/64][m][k%64]: hi = f16(a), lo = f16(a - hi).  hi + lo carries about
 // 22 bits of a, so a product that accumulates both planes in f32 is as accurate as an f32-activation one.
 __global__ void k_prep_a_f16_hilo(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
@@ -804,13 +979,16 @@ int grid_for(fa_ctx *ctx, size_t n, int block, int per_sm) {
 template <int KIND>
 int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs, void *out, bool raw_i32, int M, int N,
               int K, const TcEpilogue &ep, bool allow_trace = true) {
-  const int elem = KIND == 0 ? 2 : 1;
+  const int elem = KIND == 1 ? 1 : 2;
   TcParams p{};
   p.M = M;
   p.N = N;
   p.K = K;
   p.limbs = limbs;
-  p.limb_sum = (KIND == 0 && limbs == 2) ? 1 : 0;
+  p.limb_sum = (KIND != 1 && limbs == 2) ? 1 : 0;
+  p.nb_scales = ep.nb_scales;
+  p.nb_zp = ep.nb_zp;
+  p.nblk = ep.nblk;
   p.num_kb = fa_tc_chunks(K, elem);
   // activation rows per tile: as many as fit 256 MMA-N columns, rounded to 16, no more than needed
   int mt_max = (256 / limbs) / 16 * 16;
@@ -936,8 +1114,8 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     }
     return FA_OK;
   }
-  const size_t stage_bytes = (size_t)kPTileBytes + (size_t)p.MT * limbs * kRowBytes;
-  const size_t tail_bytes = (size_t)(2 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + 1024;
+  const size_t stage_bytes = (size_t)kPTileBytes + (size_t)p.MT * limbs * kRowBytes + (KIND == 2 ? kRawTileBytes : 0);
+  const size_t tail_bytes = (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + 1024;
   int stages = (int)((220 * 1024 - tail_bytes) / stage_bytes);
   if (stages > 12) stages = 12;
   const int kb_per_cta = p.kb_per_split * ceil_div(num_tiles, p.splitk > 1 ? num_tiles : ctx->sm_count);
@@ -965,14 +1143,18 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   CUtensorMap map_w, map_a;
   // weights: rows of 128 bytes, (tiles_n * num_kb * 128) of them, boxes of 128 rows
   const uint64_t w_batches = p.w_batch_mod ? p.w_batch_mod : p.batches;
-  FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, w_batches * p.tiles_n * p.num_kb * 128, 0, 128));
+  if (KIND == 2)  // nibble tiles [n/128][k/64][n%128][32 B]: a tile is one contiguous 4 KB run, described to the copy
+                  // engine as 16 rows of 256 bytes (as 128 rows of 32 bytes it cost the engine ~0.5 us per tile)
+    FA_TRY(tc::make_tmap_bytes2d(ctx, &map_w, w_packed, 256, (uint64_t)p.tiles_n * p.num_kb * 16, 256, 16));
+  else
+    FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, w_batches * p.tiles_n * p.num_kb * 128, 0, 128));
   // activations: [limbs * num_kb] slabs of M rows of 128 bytes, boxes of MT rows (rows >= M read as zero)
   FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M, (uint64_t)p.batches * limbs * p.num_kb,
                                (uint32_t)p.MT));
   FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(KIND == 2 ? kThreadsNbits : kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
   if (p.splitk > 1) {
@@ -987,7 +1169,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     cfg.gridDim = dim3(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);  // persistent: one CTA per SM
   }
   {
-    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : "tc_gemm_i8");
+    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : "tc_gemm_nbits"));
     cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, p);
     if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm: %s", cudaGetErrorString(e));
   }
@@ -1005,6 +1187,13 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     for (int i = 0; i < 64 && h[65 + i]; i++) fprintf(stderr, " %lld", (long long)(h[65 + i] - h[0]));
     fprintf(stderr, "\n  last acc ready %lld, last epilogue end %lld, all joined %lld\n", (long long)(h[129] - h[0]),
             (long long)(h[130] - h[0]), (long long)(h[131] - h[0]));
+    if (KIND == 2) {
+      fprintf(stderr, "  unpack warp 0 (loop top / tile landed / stored / arrived):");
+      for (int i = 0; i < 16 && h[140 + 4 * i]; i++)
+        fprintf(stderr, " [%lld %lld %lld %lld]", (long long)(h[140 + 4 * i] - h[0]), (long long)(h[141 + 4 * i] - h[0]),
+                (long long)(h[142 + 4 * i] - h[0]), (long long)(h[143 + 4 * i] - h[0]));
+      fprintf(stderr, "\n");
+    }
   }
   return FA_OK;
 }
@@ -1031,7 +1220,69 @@ int tc::make_tmap_rows128(fa_ctx *ctx, CUtensorMap *out, const void *base, int e
   return FA_OK;
 }
 
+// Plain byte matrix [rows][row_bytes] (row_bytes a multiple of 16), boxes of box_rows x box_bytes, no swizzle;
+// bytes past either end read as zero.
+int tc::make_tmap_bytes2d(fa_ctx *ctx, CUtensorMap *out, const void *base, uint64_t row_bytes, uint64_t rows,
+                          uint32_t box_bytes, uint32_t box_rows) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable in this driver");
+  FA_REQUIRE(ctx, ((uintptr_t)base & 15) == 0 && (row_bytes & 15) == 0 && (box_bytes & 15) == 0,
+             "byte tensor %p with rows of %llu bytes is not 16-byte aligned", base, (unsigned long long)row_bytes);
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled (bytes) failed with CUresult %d", (int)r);
+  return FA_OK;
+}
+
 bool fa_tc_available(fa_ctx *) { return get_encode() != nullptr; }
+
+// int4 weights as tile-contiguous nibbles with block-major scales and zero-points (fa_nbits_side) against
+// activations packed by fa_prep_a_f16_perm8: the nibbles are unpacked in shared memory inside the kernel.
+int fa_tc_gemm_nbits(fa_ctx *ctx, const __half *a_packed, const uint8_t *bq, const float *scales_t, const uint8_t *zp_t,
+                     float *c, int M, int N, int K, int nblk) {
+  TcEpilogue ep;
+  ep.nb_scales = scales_t;
+  ep.nb_zp = zp_t;
+  ep.nblk = nblk;
+  return launch_tc<2>(ctx, bq, a_packed, 1, c, false, M, N, K, ep);
+}
+
+size_t fa_nbits_tiles_bytes(int N, int K) { return (size_t)ceil_div(N, 128) * fa_tc_chunks(K, 2) * kRawTileBytes; }
+
+// scales [N][nblk], zp nibbles [N][zpb] (even block = low nibble) -> scales_t [nblk][N], zp_t [nblk][N] bytes;
+// bq -> tile-contiguous nibbles (see k_nbits_tiles).
+int fa_nbits_side(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk, int zpb,
+                  uint8_t *tiles, float *scales_t, uint8_t *zp_t) {
+  {
+    LaunchScope ls(ctx, "nbits_tiles");
+    const int tiles_n = ceil_div(N, 128), num_kb = fa_tc_chunks(K, 2);
+    k_nbits_tiles<<<grid_for(ctx, (size_t)tiles_n * num_kb * 256, 256, 8), 256, 0, ctx->stream>>>(
+        (const uint4 *)bq, N, nblk, tiles_n, num_kb, (uint4 *)tiles);
+  }
+  FA_LAUNCH_CHECK(ctx, "nbits_tiles");
+  {
+    LaunchScope ls(ctx, "nbits_side");
+    k_nbits_side<<<grid_for(ctx, (size_t)N * nblk, 256, 8), 256, 0, ctx->stream>>>(scales, zp, N, nblk, zpb, scales_t, zp_t);
+  }
+  FA_LAUNCH_CHECK(ctx, "nbits_side");
+  return FA_OK;
+}
+
+int fa_prep_a_f16_perm8(fa_ctx *ctx, const float *a, int M, int K, __half *out) {
+  if (M == 0) return FA_OK;
+  const int nch = fa_tc_chunks(K, 2);
+  {
+    LaunchScope ls(ctx, "prep_a_f16_perm8");
+    k_prep_a_f16_perm8<<<grid_for(ctx, (size_t)nch * M * 32, 256, 8), 256, 0, ctx->stream>>>(a, M, K, nch, out);
+  }
+  FA_LAUNCH_CHECK(ctx, "prep_a_f16_perm8");
+  return FA_OK;
+}
 
 int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, float *c, int M, int N, int K,
                    const TcEpilogue &ep) {

@@ -52,6 +52,13 @@ struct fa_bytes {
   size_t nk_f16_bytes = 0;
   int f16_N = 0, f16_K = 0;
   const void *f16_scales = nullptr, *f16_zp = nullptr;
+  // Lazily built tensor-core form of an int4 payload, still 4 bits per weight: nibble tiles
+  // [n/128][k/64][n%128][32 B], then block-major scales sT f32 [nblk][N], then zero-points zT u8 [nblk][N] (one
+  // unpacked nibble per byte) - what the in-kernel unpack reads, a contiguous 4 KB per tile and 32 rows per request.
+  void *nb_side = nullptr;
+  size_t nb_side_bytes = 0;
+  int side_N = 0, side_K = 0;
+  const void *side_scales = nullptr, *side_zp = nullptr;
 };
 
 struct fa_staged {
@@ -84,6 +91,7 @@ struct fa_ctx {
   unsigned long long launches = 0;
   // options
   int int8_limbs = 2;
+  int nbits_fused = 0;     // 1: int4 products on the tensor cores unpack nibbles in shared memory (0: f16 copy, faster today)
   int gemv_rows = 4;       // products with at most this many rows run on the CUDA-core GEMV kernels (0 = never)
   int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
   size_t pool_cap = 0;
@@ -225,7 +233,10 @@ struct TcEpilogue {
   const float *add = nullptr;       // [M][N]
   const float *rowbias = nullptr;   // [M] added before the activation
   int act = 0;
-  bool a_hilo = false;              // f16 kind: the row operand is two planes (value, rounding residue)
+  bool a_hilo = false;
+  const float *nb_scales = nullptr;  // int4 variant: per-block scales, packed zero-points, blocks per row
+  const uint8_t *nb_zp = nullptr;
+  int nblk = 0;              // f16 kind: the row operand is two planes (value, rounding residue)
   // optional second output: the epilogue result as a packed f16 activation shadow of a tensor with
   // o16_rows rows; this launch's rows/cols sit at (+o16_row_hi per batch/o_div, +o16_col_lo per batch%o_div)
   __half *out16 = nullptr;
@@ -256,6 +267,12 @@ int fa_gemv_kn(fa_ctx *ctx, const float *a, const void *w, bool i8, const float 
                const float *add, float *y, int M, int N, int K);
 int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out);
 int fa_prep_a_f16_hilo(fa_ctx *ctx, const float *a, int M, int K, __half *out);
+int fa_prep_a_f16_perm8(fa_ctx *ctx, const float *a, int M, int K, __half *out);
+int fa_tc_gemm_nbits(fa_ctx *ctx, const __half *a_packed, const uint8_t *bq, const float *scales_t, const uint8_t *zp_t,
+                     float *c, int M, int N, int K, int nblk);
+size_t fa_nbits_tiles_bytes(int N, int K);
+int fa_nbits_side(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk, int zpb,
+                  uint8_t *tiles, float *scales_t, uint8_t *zp_t);
 int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *out, float *rowscale);
 int fa_pack_a_i8_raw(fa_ctx *ctx, const int8_t *aq, int M, int K, int8_t *out);
 int fa_pack_w_i8(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out);

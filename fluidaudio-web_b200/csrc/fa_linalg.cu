@@ -272,6 +272,32 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
   if (gemv_shape_ok(ctx, M, N, K) && fa_gemv_nbits_ok(M, N, K, block_size)) {
     rc = fa_gemv_nbits(ctx, ap, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr,
                        (float *)c->dptr, M, N, K, nblk, zpb);
+  } else if (tc_shape_ok(ctx, M, N, K) && ctx->nbits_fused && (K & 31) == 0) {
+    const bool cached = bq->nb_side && bq->side_N == N && bq->side_K == K && bq->side_scales == scales->dptr &&
+                        bq->side_zp == zp->dptr;
+    const size_t tb = fa_nbits_tiles_bytes(N, K), sb = (size_t)N * nblk * 4;
+    if (!cached) {  // one-time tensor-core form of this handle: nibble tiles, block-major scales and zero-points
+      if (bq->nb_side) fa_block_release(ctx, bq->nb_side);
+      bq->nb_side = nullptr;
+      rc = fa_block_acquire(ctx, tb + sb + (size_t)N * nblk, &bq->nb_side, &bq->nb_side_bytes);
+      if (rc == FA_OK) {
+        bq->side_N = N;
+        bq->side_K = K;
+        bq->side_scales = scales->dptr;
+        bq->side_zp = zp->dptr;
+        uint8_t *side = (uint8_t *)bq->nb_side;
+        rc = fa_nbits_side(ctx, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr, N, K, nblk,
+                           zpb, side, (float *)(side + tb), side + tb + sb);
+      }
+    }
+    Scratch sa(ctx);
+    if (rc == FA_OK) rc = sa.get(fa_tc_act_bytes(M, K, 2, 1));
+    if (rc == FA_OK) rc = fa_prep_a_f16_perm8(ctx, ap, M, K, (__half *)sa.p);
+    if (rc == FA_OK) {
+      const uint8_t *side = (const uint8_t *)bq->nb_side;
+      rc = fa_tc_gemm_nbits(ctx, (const __half *)sa.p, side, (const float *)(side + tb), side + tb + sb, (float *)c->dptr, M,
+                            N, K, nblk);
+    }
   } else if (tc_shape_ok(ctx, M, N, K)) {
     const bool cached = bq->nk_f16 && bq->f16_N == N && bq->f16_K == K && bq->f16_scales == scales->dptr &&
                         bq->f16_zp == zp->dptr;

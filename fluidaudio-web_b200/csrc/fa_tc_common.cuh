@@ -193,5 +193,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int kind, int M, int N) {
 // swizzle; rows past the end read as zero, so a ragged M needs no special casing in the kernels.
 int make_tmap_rows128(fa_ctx *ctx, CUtensorMap *out, const void *base, int elem_bytes, uint64_t rows, uint64_t slabs,
                       uint32_t box_rows);
+int make_tmap_bytes2d(fa_ctx *ctx, CUtensorMap *out, const void *base, uint64_t row_bytes, uint64_t rows,
+                      uint32_t box_bytes, uint32_t box_rows);
 
 }  // namespace tc

@@ -64,7 +64,10 @@ const char *fa_last_error(fa_ctx *ctx);
  * accumulator, so token-by-token decoding keeps f32-grade activations at twice the MMA work; 0 turns
  * it off, a huge value applies it to every product), "gemv_rows" (0..4, default 4: products with at
  * most this many activation rows stream the weights through the CUDA-core GEMV kernels - no packing,
- * f32 / exact-integer activations; 0 sends them to the tensor-core kernel). */
+ * f32 / exact-integer activations; 0 sends them to the tensor-core kernel), "nbits_fused" (0/1, default 0:
+ * 1 = int4 products on the tensor cores stream 4-bit tiles and unpack them in shared memory inside the
+ * kernel; 0 = through a one-time dequantised f16 copy of the weights, which is the faster of the two
+ * today). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);

@@ -279,3 +279,27 @@ def test_gemv_option_off_uses_tensor_cores(ctx, oracle):
     finally:
         ctx.setOption("gemv_rows", 4)
     assert np.abs(got.reshape(M, N) - ref).max() <= 2e-5
+
+
+@pytest.mark.parametrize("M,K,N", [(16, 2048, 8192), (8, 2048, 2048), (130, 1056, 300), (5, 96, 4100)])
+def test_int4_unpack_in_shared_memory_variant(ctx, oracle, M, K, N):
+    """The tensor-core int4 kernel that streams 4-bit tiles and unpacks them in shared memory (option
+    nbits_fused): same product as the oracle within the int4 tolerance, ragged N and odd block counts too."""
+    rng = np.random.default_rng(M + K + N)
+    nblk = K // 32
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    bq = rng.integers(0, 256, N * nblk * 16, dtype=np.uint8)
+    scales = rng.uniform(5e-3, 2e-2, N * nblk).astype(np.float32)
+    zp = rng.integers(0, 256, N * ((nblk + 1) // 2), dtype=np.uint8)
+    ref = oracle.matmulNBits(oracle.upload(a, M, K), oracle.uploadBytes(bq), oracle.upload(scales, 1, scales.size),
+                             oracle.uploadBytes(zp), N).array()
+    ctx.setOption("nbits_fused", 1)
+    try:
+        ctx.startProfile(64)
+        got = ctx.download(ctx.matmulNBits(ctx.upload(a, M, K), ctx.uploadBytes(bq), ctx.upload(scales, 1, scales.size),
+                                           ctx.uploadBytes(zp), N)).reshape(M, N)
+        labels = [e["label"] for e in ctx.endProfile()]
+    finally:
+        ctx.setOption("nbits_fused", 0)
+    assert "tc_gemm_nbits" in labels, labels
+    assert np.abs(got - ref).max() <= 2e-2 * max(1.0, float(np.abs(ref).max()) / 3.0)
