@@ -66,6 +66,7 @@ SIGNATURES = {
     "fa_conv1d_windows": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
     "fa_glu_dwconv_tm": [P, P, P, P, I, I, I, I, I, PP],
     "fa_conv2d": [P, P, P, P] + [I] * 14 + [PP],
+    "fa_conv2d_windows": [P, P, P, P] + [I] * 15 + [PP],
     "fa_bmm_qk": [P, P, P, P, I, I, I, I, PP],
     "fa_bmm_pv": [P, P, P, I, I, I, PP],
     "fa_attn_fused": [P, P, P, P, P, P, P, I, I, I, PP],
@@ -81,6 +82,7 @@ SIGNATURES = {
     "fa_copy_rows": [P, P, P, I],
     "fa_concat_rows": [P, PP, I, PP],
     "fa_sub_reshape": [P, P, I, I, I, PP],
+    "fa_sub_reshape_windows": [P, P, I, I, I, I, PP],
     "fa_argmax_rows": [P, P, I, PP],
     "fa_embed_rows": [P, P, P, P, I, PP],
     "fa_unshard_cols": [P, P, I, PP],

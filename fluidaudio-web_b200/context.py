@@ -315,6 +315,22 @@ class CudaContext:
                         o["kh"], o["kw"], o.get("strideH", 1), o.get("strideW", 1), pt, pb, pl, pr, o.get("groups", 1),
                         ACT[o.get("act", "none")])
 
+    def conv2dWindows(self, x, weight, opts: dict, W: int) -> Tensor:
+        """conv2d over W images at once: x [W, cin*h*w] -> [W, cout*Ho*Wo] (optional member)."""
+        o = dict(opts)
+        padH, padW = o.get("padH", 0), o.get("padW", 0)
+        pt = o.get("padTop", padH) if o.get("padTop") is not None else padH
+        pb = o.get("padBottom", padH) if o.get("padBottom") is not None else padH
+        pl = o.get("padLeft", padW) if o.get("padLeft") is not None else padW
+        pr = o.get("padRight", padW) if o.get("padRight") is not None else padW
+        return self._op(self._lib.fa_conv2d_windows, x.h, weight.h, self._h_of(o.get("bias")), o["cout"], o["cin"], o["h"],
+                        o["w"], o["kh"], o["kw"], o.get("strideH", 1), o.get("strideW", 1), pt, pb, pl, pr, o.get("groups", 1),
+                        ACT[o.get("act", "none")], W)
+
+    def subReshapeWindows(self, x, Cc: int, Tsub: int, F: int, W: int) -> Tensor:
+        """subReshape over W windows at once: x [W, C*Tsub*F] -> [W*Tsub, C*F] (optional member)."""
+        return self._op(self._lib.fa_sub_reshape_windows, x.h, Cc, Tsub, F, W)
+
     # -- attention (compute.d.ts:189-199) ----------------------------------------------------------
     def bmmQK(self, q, b, qb, H: int, HD: int, W: int = 1, bShared: bool = False) -> Tensor:
         return self._op(self._lib.fa_bmm_qk, q.h, b.h, self._h_of(qb), H, HD, W, 1 if bShared else 0)

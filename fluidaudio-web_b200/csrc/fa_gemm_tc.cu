@@ -63,6 +63,7 @@ struct TcParams {
   // reads weight slab (w_batch_mod ? b % w_batch_mod : b) and activation slabs of batch b, and writes at
   // out + (b / o_div) * o_hi + (b % o_div) * o_lo with row pitch ldc.
   int batches, w_batch_mod, o_div, ldc;
+  int a_shared;       // batched mode: every batch multiplies the same activation slabs
   long long o_hi, o_lo;
   __half *out16;      // optional packed f16 shadow of the result (see TcEpilogue), or nullptr
   int o16_rows, o16_row_hi, o16_col_lo;
@@ -323,7 +324,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const int tn = tin % p.tiles_n, tm = tin / p.tiles_n;
         const int wb = p.w_batch_mod ? batch % p.w_batch_mod : batch;
         int wrow = ((wb * p.tiles_n + tn) * p.num_kb + kb0) * 128;
-        int aslab = batch * p.limbs * p.num_kb + kb0;
+        int aslab = (p.a_shared ? 0 : batch) * p.limbs * p.num_kb + kb0;
         const int m0 = tm * p.MT;
         for (int kb = kb0; kb < kb1; kb++, it++, wrow += 128, aslab++) {
           const uint32_t fb = bars + s * 8u, dst = smem_base + s * stage_bytes;
@@ -905,9 +906,12 @@ __global__ void k_pack_w_i8(const int8_t *__restrict__ w, int K, int N, int nch,
 
 // f32 or f16 [K][N] -> f16 Wp[n/128][k/64][n%128][k%64].
 template <typename SRC>
-__global__ void k_pack_w_f16(const SRC *__restrict__ w, int K, int N, int nch, __half *__restrict__ out) {
+__global__ void k_pack_w_f16(const SRC *__restrict__ w, int K, int N, int nch, __half *__restrict__ out,
+                             size_t src_stride = 0, size_t dst_stride = 0) {
   __shared__ __half t[32][33];
   const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
+  w += (size_t)blockIdx.z * src_stride;  // blockIdx.z = matrix of a batch
+  out += (size_t)blockIdx.z * dst_stride;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     int k = k0 + r, n = n0 + threadIdx.x;
     float v = 0.0f;
@@ -1028,6 +1032,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.tiles_m = ceil_div(M, p.MT);
   p.batches = ep.batches;
   p.w_batch_mod = ep.w_batch_mod;
+  p.a_shared = ep.a_shared ? 1 : 0;
   p.o_div = ep.o_div > 0 ? ep.o_div : 1;
   p.ldc = ep.ldc > 0 ? ep.ldc : N;
   p.o_hi = ep.o_hi;
@@ -1149,8 +1154,8 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   else
     FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, w_batches * p.tiles_n * p.num_kb * 128, 0, 128));
   // activations: [limbs * num_kb] slabs of M rows of 128 bytes, boxes of MT rows (rows >= M read as zero)
-  FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M, (uint64_t)p.batches * limbs * p.num_kb,
-                               (uint32_t)p.MT));
+  FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M,
+                               (uint64_t)(p.a_shared ? 1 : p.batches) * limbs * p.num_kb, (uint32_t)p.MT));
   FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
@@ -1357,6 +1362,21 @@ int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, 
       k_pack_w_f16<__half><<<grid, block, 0, ctx->stream>>>((const __half *)w_kn, K, N, nch, out);
     else
       k_pack_w_f16<float><<<grid, block, 0, ctx->stream>>>((const float *)w_kn, K, N, nch, out);
+  }
+  FA_LAUNCH_CHECK(ctx, "pack_w_f16");
+  return FA_OK;
+}
+
+// `batch` f32 matrices [K][N], matrix b at w + b*src_stride -> packed slabs back to back.
+int fa_pack_w_f16_batched(fa_ctx *ctx, const void *w_kn, int K, int N, int batch, size_t src_stride, __half *out) {
+  const size_t slab = fa_tc_weight_bytes(N, K, 2);
+  FA_CHECK_CUDA(ctx, cudaMemsetAsync(out, 0, slab * batch, ctx->stream));
+  dim3 grid(ceil_div(K, 32), ceil_div(N, 32), batch), block(32, 8);
+  FA_REQUIRE(ctx, batch <= 65535 && grid.y <= 65535, "pack_w_f16: batch or N too large");
+  {
+    LaunchScope ls(ctx, "pack_w_f16");
+    k_pack_w_f16<float><<<grid, block, 0, ctx->stream>>>((const float *)w_kn, K, N, fa_tc_chunks(K, 2), out, src_stride,
+                                                         slab / sizeof(__half));
   }
   FA_LAUNCH_CHECK(ctx, "pack_w_f16");
   return FA_OK;

@@ -244,9 +244,12 @@ __global__ void k_copy_cols(const float *__restrict__ src, int scols, int scol0,
   }
 }
 // [C, Tsub*F] -> [Tsub, C*F] (wasm-context.js:552-563)
-__global__ void k_sub_reshape(const float *__restrict__ x, float *__restrict__ y, int C, int Tsub, int F) {
+// blockIdx.y = window: window b reads x + b*xstride and writes rows [b*Tsub, (b+1)*Tsub).
+__global__ void k_sub_reshape(const float *__restrict__ x, float *__restrict__ y, int C, int Tsub, int F, size_t xstride) {
   size_t n = (size_t)Tsub * C * F;
   int CF = C * F;
+  x += (size_t)blockIdx.y * xstride;
+  y += (size_t)blockIdx.y * n;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     int ho = (int)(i / CF), rem = (int)(i % CF), c = rem / F, wo = rem % F;
     y[i] = x[(size_t)c * Tsub * F + (size_t)ho * F + wo];
@@ -519,10 +522,13 @@ __global__ void __launch_bounds__(256) k_dwconv1d(const float *__restrict__ x, c
 
 __global__ void __launch_bounds__(256) k_dwconv2d_3x3(const float *__restrict__ x, const float *__restrict__ w,
                                                       const float *__restrict__ bias, float *__restrict__ y, int h, int W,
-                                                      int sh, int sw, int pt, int pl, int Ho, int Wo, int act) {
+                                                      int sh, int sw, int pt, int pl, int Ho, int Wo, int act,
+                                                      size_t xstride, size_t ystride) {
   const int c = blockIdx.y;
   const unsigned plane = (unsigned)Ho * Wo, pos = blockIdx.x * 256 + threadIdx.x;
   if (pos >= plane) return;
+  x += (size_t)blockIdx.z * xstride;  // blockIdx.z = window
+  y += (size_t)blockIdx.z * ystride;
   const int ho = (int)(pos / (unsigned)Wo), wo = (int)(pos % (unsigned)Wo);
   const float *xp = x + (size_t)c * h * W;
   const float *wp = w + (size_t)c * 9;
@@ -653,9 +659,11 @@ __global__ void k_conv2d(const float *__restrict__ x, const float *__restrict__ 
 __global__ void __launch_bounds__(256) k_conv2d_c1_3x3(const float *__restrict__ x, const float *__restrict__ w,
                                                        const float *__restrict__ bias, float *__restrict__ y, int cout,
                                                        int h, int W, int sh, int sw, int pt, int pl, int Ho, int Wo,
-                                                       int act) {
+                                                       int act, size_t xstride, size_t ystride) {
   __shared__ float ws[32][9], bs[32];
   const int co0 = blockIdx.y * 32;
+  x += (size_t)blockIdx.z * xstride;  // blockIdx.z = window
+  y += (size_t)blockIdx.z * ystride;
   for (int e = threadIdx.x; e < 32 * 9; e += 256) {
     const int c = e / 9;
     ws[c][e % 9] = co0 + c < cout ? w[(size_t)(co0 + c) * 9 + e % 9] : 0.f;
@@ -1041,21 +1049,35 @@ extern "C" int fa_concat_rows(fa_ctx *ctx, const fa_tensor *const *tensors, int 
   return FA_OK;
 }
 
-extern "C" int fa_sub_reshape(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, fa_tensor **out) {
+static int sub_reshape_impl(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, int windows, fa_tensor **out) {
   GLUE_PROLOGUE("subReshape");
   FA_TRY(need_f32(ctx, x, "subReshape"));
-  FA_REQUIRE(ctx, C > 0 && Tsub > 0 && F > 0 && (long long)x->rows * x->cols >= (long long)C * Tsub * F,
-             "subReshape: x has %d elements, need %d*%d*%d", x->rows * x->cols, C, Tsub, F);
+  FA_REQUIRE(ctx, C > 0 && Tsub > 0 && F > 0 && windows > 0 && windows <= 65535, "subReshape: bad geometry");
+  if (windows == 1)
+    FA_REQUIRE(ctx, (long long)x->rows * x->cols >= (long long)C * Tsub * F,
+               "subReshape: x has %d elements, need %d*%d*%d", x->rows * x->cols, C, Tsub, F);
+  else
+    FA_REQUIRE(ctx, x->rows == windows && (long long)x->cols >= (long long)C * Tsub * F,
+               "subReshapeWindows: x is [%d,%d], need [%d, >= %d*%d*%d]", x->rows, x->cols, windows, C, Tsub, F);
   fa_tensor *y = nullptr;
-  FA_TRY(fa_tensor_new(ctx, Tsub, C * F, FA_F32, true, &y));
+  FA_TRY(fa_tensor_new(ctx, windows * Tsub, C * F, FA_F32, true, &y));
   size_t n = (size_t)Tsub * C * F;
   {
     LaunchScope ls(ctx, "sub_reshape");
-    k_sub_reshape<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, C, Tsub, F);
+    k_sub_reshape<<<dim3(grid1d(ctx, n, 256), windows), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, C,
+                                                                              Tsub, F, (size_t)x->cols);
   }
   FA_LAUNCH_CHECK(ctx, "sub_reshape");
   *out = y;
   return FA_OK;
+}
+
+extern "C" int fa_sub_reshape(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, fa_tensor **out) {
+  return sub_reshape_impl(ctx, x, C, Tsub, F, 1, out);
+}
+extern "C" int fa_sub_reshape_windows(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, int windows,
+                                      fa_tensor **out) {
+  return sub_reshape_impl(ctx, x, C, Tsub, F, windows, out);
 }
 
 extern "C" int fa_rel_shift_b(fa_ctx *ctx, const fa_tensor *x, int H, fa_tensor **out) {
@@ -1302,22 +1324,34 @@ extern "C" int fa_conv1d_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tenso
   return conv1d_impl(ctx, x, w, bias, cout, k, 1, pad_left, pad_right, dilation, groups, act, windows, out);
 }
 
-extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin,
-                         int h, int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom,
-                         int pad_left, int pad_right, int groups, int act, fa_tensor **out) {
+// windows == 1: x holds one image [cin*h*w] (any [rows, cols] with that many elements), out [cout, Ho*Wo].
+// windows > 1: x [windows, cin*h*w], one image per row; out [windows, cout*Ho*Wo]; one launch for all of them.
+static int conv2d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin,
+                       int h, int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom,
+                       int pad_left, int pad_right, int groups, int act, int windows, fa_tensor **out) {
   GLUE_PROLOGUE("conv2d");
   FA_TRY(need_f32(ctx, x, "conv2d"));
   FA_TRY(need_f32(ctx, w, "conv2d"));
   if (bias) FA_TRY(need_f32(ctx, bias, "conv2d"));
   FA_REQUIRE(ctx, cout > 0 && cin > 0 && groups > 0 && cin % groups == 0 && cout % groups == 0 && stride_h > 0 && stride_w > 0,
              "conv2d: bad geometry");
-  FA_REQUIRE(ctx, (long long)x->rows * x->cols >= (long long)cin * h * w_, "conv2d: input smaller than cin*h*w");
+  FA_REQUIRE(ctx, windows >= 1 && windows <= 65535, "conv2d: %d windows", windows);
+  if (windows == 1)
+    FA_REQUIRE(ctx, (long long)x->rows * x->cols >= (long long)cin * h * w_, "conv2d: input smaller than cin*h*w");
+  else
+    FA_REQUIRE(ctx, x->rows == windows && (long long)x->cols >= (long long)cin * h * w_,
+               "conv2dWindows: x is [%d,%d], need [%d, >= %d]", x->rows, x->cols, windows, cin * h * w_);
+  const size_t xstride = windows == 1 ? 0 : (size_t)x->cols;
   FA_REQUIRE(ctx, (long long)w->rows * w->cols >= (long long)cout * (cin / groups) * kh * kw, "conv2d: weight tensor too small");
   const int Ho = (h + pad_top + pad_bottom - kh) / stride_h + 1, Wo = (w_ + pad_left + pad_right - kw) / stride_w + 1;
   FA_REQUIRE(ctx, Ho > 0 && Wo > 0, "conv2d: empty output");
   fa_tensor *y = nullptr;
-  FA_TRY(fa_tensor_new(ctx, cout, Ho * Wo, FA_F32, true, &y));
+  if (windows == 1)
+    FA_TRY(fa_tensor_new(ctx, cout, Ho * Wo, FA_F32, true, &y));
+  else
+    FA_TRY(fa_tensor_new(ctx, windows, cout * Ho * Wo, FA_F32, true, &y));
   size_t n = (size_t)cout * Ho * Wo;
+  const size_t ystride = n;
   // A pointwise convolution is the product W[cout,cin] @ x[cin, H*W] (the reference routes it to its GEMM
   // plus a per-row bias pass, src/gpu/compute.js:551-555,804-810): run it on the tensor cores with the
   // feature map as the streamed operand and the output-channel bias applied per row in the epilogue.
@@ -1327,14 +1361,22 @@ extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
       (long long)cout * cin * P >= (1ll << 21)) {
     void *xa = nullptr, *wa = nullptr;
     size_t xb = 0, wb = 0;
-    int rc = fa_block_acquire(ctx, fa_tc_weight_bytes(P, cin, 2), &xa, &xb);
+    const size_t slab = fa_tc_weight_bytes(P, cin, 2);
+    int rc = fa_block_acquire(ctx, slab * windows, &xa, &xb);
     if (rc == FA_OK) rc = fa_block_acquire(ctx, fa_tc_act_bytes(cout, cin, 2, 1), &wa, &wb);
-    if (rc == FA_OK) rc = fa_pack_w_f16(ctx, x->dptr, FA_F32, cin, P, (__half *)xa);
+    if (rc == FA_OK) rc = fa_pack_w_f16_batched(ctx, x->dptr, cin, P, windows, xstride, (__half *)xa);
     if (rc == FA_OK) rc = fa_prep_a_f16(ctx, (const float *)w->dptr, cout, cin, (__half *)wa);
     if (rc == FA_OK) {
       TcEpilogue ep;
       ep.rowbias = bias ? (const float *)bias->dptr : nullptr;
       ep.act = act;
+      if (windows > 1) {  // one feature map per window against the shared filter bank
+        ep.batches = windows;
+        ep.a_shared = true;
+        ep.o_div = 1;
+        ep.o_hi = (long long)ystride;
+        ep.ldc = P;
+      }
       rc = fa_tc_gemm_f16(ctx, (const __half *)wa, (const __half *)xa, (float *)y->dptr, cout, P, cin, ep);
     }
     if (xa) fa_block_release(ctx, xa);
@@ -1349,12 +1391,13 @@ extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
   FA_REQUIRE(ctx, n < (1ull << 31), "conv2d: output too large");
   if (cin == 1 && groups == 1 && kh == 3 && kw == 3) {
     const unsigned plane = (unsigned)Ho * Wo;
-    dim3 grid((plane + 255) / 256 < (unsigned)ctx->sm_count * 4 ? (plane + 255) / 256 : ctx->sm_count * 4, ceil_div(cout, 32));
+    dim3 grid((plane + 255) / 256 < (unsigned)ctx->sm_count * 4 ? (plane + 255) / 256 : ctx->sm_count * 4, ceil_div(cout, 32),
+              windows);
     {
       LaunchScope ls(ctx, "conv2d_c1_3x3");
       k_conv2d_c1_3x3<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
                                                      bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr, cout, h,
-                                                     w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act);
+                                                     w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act, xstride, ystride);
     }
     FA_LAUNCH_CHECK(ctx, "conv2d_c1_3x3");
     *out = y;
@@ -1363,24 +1406,38 @@ extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, co
   if (groups == cin && cout == cin && kh == 3 && kw == 3 && cout <= 65535) {
     {
       LaunchScope ls(ctx, "dwconv2d_3x3");
-      k_dwconv2d_3x3<<<dim3(ceil_div(Ho * Wo, 256), cout), 256, 0, ctx->stream>>>(
+      k_dwconv2d_3x3<<<dim3(ceil_div(Ho * Wo, 256), cout, windows), 256, 0, ctx->stream>>>(
           (const float *)x->dptr, (const float *)w->dptr, bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr, h,
-          w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act);
+          w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act, xstride, ystride);
     }
     FA_LAUNCH_CHECK(ctx, "dwconv2d_3x3");
     *out = y;
     return FA_OK;
   }
-  {
+  for (int b = 0; b < windows; b++) {  // general geometry: one launch per window
     LaunchScope ls(ctx, "conv2d");
-    k_conv2d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
-                                                           bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr,
-                                                           cout, cin, h, w_, kh, kw, stride_h, stride_w, pad_top, pad_left,
-                                                           Ho, Wo, groups, act);
+    k_conv2d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr + b * xstride, (const float *)w->dptr,
+                                                           bias ? (const float *)bias->dptr : nullptr,
+                                                           (float *)y->dptr + b * ystride, cout, cin, h, w_, kh, kw, stride_h,
+                                                           stride_w, pad_top, pad_left, Ho, Wo, groups, act);
   }
   FA_LAUNCH_CHECK(ctx, "conv2d");
   *out = y;
   return FA_OK;
+}
+
+extern "C" int fa_conv2d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin,
+                         int h, int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom,
+                         int pad_left, int pad_right, int groups, int act, fa_tensor **out) {
+  return conv2d_impl(ctx, x, w, bias, cout, cin, h, w_, kh, kw, stride_h, stride_w, pad_top, pad_bottom, pad_left,
+                     pad_right, groups, act, 1, out);
+}
+extern "C" int fa_conv2d_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout,
+                                 int cin, int h, int w_, int kh, int kw, int stride_h, int stride_w, int pad_top,
+                                 int pad_bottom, int pad_left, int pad_right, int groups, int act, int windows,
+                                 fa_tensor **out) {
+  return conv2d_impl(ctx, x, w, bias, cout, cin, h, w_, kh, kw, stride_h, stride_w, pad_top, pad_bottom, pad_left,
+                     pad_right, groups, act, windows, out);
 }
 
 extern "C" int fa_embed_rows(fa_ctx *ctx, const fa_tensor *table, const fa_tensor *pos, const fa_tensor *idx, int n,

@@ -234,6 +234,7 @@ struct TcEpilogue {
   const float *rowbias = nullptr;   // [M] added before the activation
   int act = 0;
   bool a_hilo = false;
+  bool a_shared = false;            // batched mode: all batches share the row operand
   const float *nb_scales = nullptr;  // int4 variant: per-block scales, packed zero-points, blocks per row
   const uint8_t *nb_zp = nullptr;
   int nblk = 0;              // f16 kind: the row operand is two planes (value, rounding residue)
@@ -277,6 +278,7 @@ int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *o
 int fa_pack_a_i8_raw(fa_ctx *ctx, const int8_t *aq, int M, int K, int8_t *out);
 int fa_pack_w_i8(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out);
 int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, __half *out);
+int fa_pack_w_f16_batched(fa_ctx *ctx, const void *w_kn, int K, int N, int batch, size_t src_stride, __half *out);
 int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk,
                         int zpb, __half *out);
 bool fa_tc_available(fa_ctx *ctx);

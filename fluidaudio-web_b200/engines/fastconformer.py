@@ -112,6 +112,32 @@ def pre_encode(ctx, enc, mel):
     return ctx.matmul(flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
 
 
+def pre_encode_windows(ctx, enc, mels):
+    """pre_encode for W equal-length windows in one pass of window-batched launches (optional members
+    conv2dWindows / subReshapeWindows): same per-window arithmetic, x [W*Tsub, D] directly."""
+    cfg = enc["cfg"]
+    Csub, melBins = cfg["Csub"], cfg["melBins"]
+    W = len(mels)
+    if isinstance(mels[0], np.ndarray):
+        stacked = np.stack([mel_time_major(m, melBins) for m in mels])
+        s = ctx.upload(stacked, W, stacked.shape[1])
+    else:
+        s = ctx.concatRows(list(mels))  # [W, T*melBins]
+    Hh, Wd = s.cols // melBins, melBins
+    conv = [(Csub, 1, 3, 2, 1, "relu", True), (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False),
+            (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False)]
+    for i, (cout, cin, k, st, gr, act, s2) in enumerate(conv):
+        p = 1 if s2 else 0
+        s = ctx.conv2dWindows(s, enc["sub"]["conv"][i]["w"], dict(cout=cout, cin=cin, h=Hh, w=Wd, kh=k, kw=k,
+                                                                 bias=enc["sub"]["conv"][i]["b"], strideH=st, strideW=st,
+                                                                 padTop=p, padBottom=p, padLeft=p, padRight=p, groups=gr,
+                                                                 act=act), W)
+        Hh = (Hh + 2 * p - k) // st + 1
+        Wd = (Wd + 2 * p - k) // st + 1
+    flat = ctx.subReshapeWindows(s, Csub, Hh, Wd, W)
+    return ctx.matmul(flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
+
+
 def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bool = True):
     """W same-length windows concatenated along rows (:235-386): GEMMs see M = W*Tsub, attention and the
     depthwise conv stay per window.  Optional backend members (feature-tested, like the reference tests
@@ -121,11 +147,15 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
     D, H, HD, LAYERS, dwK = cfg["D"], cfg["H"], cfg["HD"], cfg["layers"], cfg["dwK"]
     ln = lambda x, lp: ctx.layernorm(x, lp[0], lp[1])
     W = len(mels)
-    pre = [pre_encode(ctx, enc, m) for m in mels]
-    Tsub = pre[0][1]
-    if any(p[1] != Tsub for p in pre):
-        raise ValueError("encode_batch: windows must have equal Tsub")
-    x = pre[0][0] if W == 1 else ctx.concatRows([p[0] for p in pre])
+    sizes = {(m.size if isinstance(m, np.ndarray) else m.rows * m.cols) for m in mels}
+    if use_fast and W > 1 and len(sizes) == 1 and hasattr(ctx, "conv2dWindows") and hasattr(ctx, "subReshapeWindows"):
+        x, Tsub = pre_encode_windows(ctx, enc, mels)  # optional members: the whole front end in 7 launches
+    else:
+        pre = [pre_encode(ctx, enc, m) for m in mels]
+        Tsub = pre[0][1]
+        if any(p[1] != Tsub for p in pre):
+            raise ValueError("encode_batch: windows must have equal Tsub")
+        x = pre[0][0] if W == 1 else ctx.concatRows([p[0] for p in pre])
     peT = enc["_pe"].get(Tsub)
     if peT is None:
         peT = ctx.upload(pos_encoding(Tsub, D), 2 * Tsub - 1, D)

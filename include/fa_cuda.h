@@ -199,6 +199,15 @@ int fa_slice_rows(fa_ctx *ctx, const fa_tensor *x, int row0, int count, fa_tenso
 int fa_copy_rows(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, int row_offset);      /* copyRows :221 */
 int fa_concat_rows(fa_ctx *ctx, const fa_tensor *const *tensors, int count, fa_tensor **out); /* concatRows :222 */
 int fa_sub_reshape(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, fa_tensor **out); /* subReshape :228 */
+/* Window-batched forms of conv2d and subReshape (optional members conv2dWindows / subReshapeWindows): x is
+ * [windows, cin*h*w], one image per row; conv2d_windows returns [windows, cout*Ho*Wo], sub_reshape_windows
+ * returns [windows*Tsub, C*F] (window b in rows [b*Tsub, (b+1)*Tsub)).  Same arithmetic per window as the
+ * single-image members; one launch for all windows instead of the reference's per-window preEncode loop
+ * (src/engines/asr-parakeet/raw-encoder.js:177-222, 246-252). */
+int fa_conv2d_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int cin, int h,
+                      int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left,
+                      int pad_right, int groups, int act, int windows, fa_tensor **out);
+int fa_sub_reshape_windows(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, int windows, fa_tensor **out);
 /* argmax over each row (host picks tokens from it; the reference does this on the host,
  * src/engines/asr-whisper/index.ts:80-97): out [rows,2] = {index, value}.  Only the first `ncols`
  * columns of each row take part (ncols <= 0: all of them) - the tied vocabulary projection is padded

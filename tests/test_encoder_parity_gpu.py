@@ -49,12 +49,13 @@ def test_full_width_layer_teacher_forced(ctx, pkg):
         enc = fc.load_encoder(c, w)
         # drive the block directly from a given residual stream: reuse encode_batch's body through a
         # stand-in pre-encode (the subsampling front end is covered by the tiny end-to-end case)
-        orig = fc.pre_encode
+        orig, orig_w = fc.pre_encode, fc.pre_encode_windows
         fc.pre_encode = lambda c_, e_, m_: (c_.upload(m_, Tsub, D), Tsub)
+        fc.pre_encode_windows = lambda c_, e_, ms: (c_.upload(np.concatenate(ms), len(ms) * Tsub, D), Tsub)
         try:
             out, _ = fc.encode_batch(c, enc, [x0[i * Tsub:(i + 1) * Tsub] for i in range(Wn)], use_fast=use_fast)
         finally:
-            fc.pre_encode = orig
+            fc.pre_encode, fc.pre_encode_windows = orig, orig_w
         return out
 
     ora = WasmOracle(threads=True)

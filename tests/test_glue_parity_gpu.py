@@ -160,3 +160,36 @@ def test_unshard_cols_matches_host_statement(ctx, pkg):
         g = rng.standard_normal((world * M, ns)).astype(np.float32)
         got = ctx.download(ctx.unshardCols(ctx.upload(g, world * M, ns), world)).reshape(M, world * ns)
         assert np.array_equal(got, sharding.unshard_cols_host(g, world))
+
+
+@pytest.mark.parametrize("geom", [
+    dict(cout=16, cin=1, kh=3, kw=3, strideH=2, strideW=2, padTop=1, padBottom=1, padLeft=1, padRight=1, groups=1, act="relu"),
+    dict(cout=16, cin=16, kh=3, kw=3, strideH=2, strideW=2, padTop=1, padBottom=1, padLeft=1, padRight=1, groups=16, act="none"),
+    dict(cout=64, cin=64, kh=1, kw=1, groups=1, act="relu"),   # pointwise -> tensor cores, batched over windows
+    dict(cout=8, cin=4, kh=3, kw=2, strideH=1, strideW=2, padTop=0, padBottom=1, padLeft=1, padRight=0, groups=2, act="silu"),
+])
+def test_conv2d_windows_equals_per_window_conv2d(ctx, geom):
+    """The window-batched front-end members against the per-window members they replace (bit for bit: same
+    kernels, one more grid dimension)."""
+    rng = np.random.default_rng(geom["cout"] + geom["cin"])
+    W, h, w = 3, 37, 50
+    cin, cout, g = geom["cin"], geom["cout"], geom["groups"]
+    x = rng.standard_normal((W, cin * h * w)).astype(np.float32)
+    wt = rng.standard_normal((cout, (cin // g) * geom["kh"] * geom["kw"])).astype(np.float32)
+    b = rng.standard_normal(cout).astype(np.float32)
+    wt_t, b_t = ctx.upload(wt, wt.shape[0], wt.shape[1]), ctx.upload(b, 1, cout)
+    opts = dict(geom, h=h, w=w, bias=b_t)
+    got = ctx.download(ctx.conv2dWindows(ctx.upload(x, W, x.shape[1]), wt_t, opts, W)).reshape(W, -1)
+    for i in range(W):
+        one = ctx.download(ctx.conv2d(ctx.upload(x[i], 1, x.shape[1]), wt_t, opts))
+        assert np.array_equal(got[i], one.reshape(-1)), (geom, i)
+
+
+def test_sub_reshape_windows(ctx):
+    rng = np.random.default_rng(1)
+    W, C, Tsub, F = 4, 6, 9, 5
+    x = rng.standard_normal((W, C * Tsub * F)).astype(np.float32)
+    got = ctx.download(ctx.subReshapeWindows(ctx.upload(x, W, x.shape[1]), C, Tsub, F, W)).reshape(W, Tsub, C * F)
+    for i in range(W):
+        one = ctx.download(ctx.subReshape(ctx.upload(x[i], C, Tsub * F), C, Tsub, F)).reshape(Tsub, C * F)
+        assert np.array_equal(got[i], one)
