@@ -12,45 +12,47 @@
 
 namespace {
 
-// rows r of src[(row0 + r) * S + col0 + d] (+ addv[col0 + d]) -> Ap[batch][d/64][r][d%64], d zero padded
-__global__ void k_pack_act_heads(const float *__restrict__ src, const float *__restrict__ addv, __half *__restrict__ dst,
-                                 int T, int S, int H, int HD, int nch, unsigned total) {
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    // i indexes half2 pairs of dst: [batch][c][r][32 pairs]
-    const int pr = i & 31;
-    unsigned t = i >> 5;
-    const int r = t % T;
-    t /= T;
-    const int c = t % nch, batch = t / nch;
-    const int w = batch / H, h = batch % H, d = c * 64 + pr * 2;
-    float x = 0.f, y = 0.f;
-    const float *row = src + ((size_t)w * T + r) * S + h * HD;
-    if (d < HD) x = row[d] + (addv ? addv[h * HD + d] : 0.f);
-    if (d + 1 < HD) y = row[d + 1] + (addv ? addv[h * HD + d + 1] : 0.f);
-    ((__half2 *)dst)[i] = __floats2half2_rn(x, y);
+// rows r of src[(w*T + r) * S + h*HD + d] (+ addv[h*HD + d]) -> Ap[batch][d/64][r][d%64], d zero padded.
+// Grid (row groups of 8, K chunks, batch = w*H + h): a warp packs one 64-wide chunk of one row, so the only
+// division left is the one per thread that splits the batch index.
+__global__ void __launch_bounds__(256) k_pack_act_heads(const float *__restrict__ src, const float *__restrict__ addv,
+                                                        __half *__restrict__ dst, int T, int S, int H, int HD, int nch) {
+  const int pr = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= T) return;
+  const int c = blockIdx.y, batch = blockIdx.z, w = batch / H, h = batch - w * H, d = c * 64 + pr * 2;
+  float x = 0.f, y = 0.f;
+  const float *row = src + ((size_t)w * T + r) * S + h * HD;
+  if (d + 1 < HD) {
+    const float2 v = *(const float2 *)(row + d);
+    x = v.x, y = v.y;
+    if (addv) {
+      const float2 a = *(const float2 *)(addv + h * HD + d);
+      x += a.x, y += a.y;
+    }
+  } else if (d < HD) {
+    x = row[d] + (addv ? addv[h * HD + d] : 0.f);
   }
+  ((__half2 *)dst)[(((size_t)batch * nch + c) * T + r) * 32 + pr] = __floats2half2_rn(x, y);
 }
 
-// keys: src[(wsrc*Tb + j) * S + h*HD + d] -> Wp[batch][j/128][d/64][j%128][d%64]; rows j >= Tb and d >= HD zero
-__global__ void k_pack_w_heads(const float *__restrict__ src, __half *__restrict__ dst, int Tb, int S, int H, int HD,
-                               int tiles_n, int nch, unsigned total) {
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const int pr = i & 31;
-    unsigned t = i >> 5;
-    const int jr = t & 127;
-    t >>= 7;
-    const int c = t % nch;
-    t /= nch;
-    const int tn = t % tiles_n, batch = t / tiles_n;
-    const int w = batch / H, h = batch % H, j = tn * 128 + jr, d = c * 64 + pr * 2;
-    float x = 0.f, y = 0.f;
-    if (j < Tb) {
-      const float *row = src + ((size_t)w * Tb + j) * S + h * HD;
-      if (d < HD) x = row[d];
-      if (d + 1 < HD) y = row[d + 1];
+// keys: src[(wsrc*Tb + j) * S + h*HD + d] -> Wp[batch][j/128][d/64][j%128][d%64]; rows j >= Tb and d >= HD zero.
+// Grid (16 row groups of 8 per 128-row tile, tiles_n * nch, batch).
+__global__ void __launch_bounds__(256) k_pack_w_heads(const float *__restrict__ src, __half *__restrict__ dst, int Tb, int S,
+                                                      int H, int HD, int tiles_n, int nch, int w_shared) {
+  const int pr = threadIdx.x & 31, jr = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int tn = blockIdx.y / nch, c = blockIdx.y - tn * nch, batch = blockIdx.z;
+  const int w = w_shared ? 0 : batch / H, h = batch % H, j = tn * 128 + jr, d = c * 64 + pr * 2;
+  float x = 0.f, y = 0.f;
+  if (j < Tb) {
+    const float *row = src + ((size_t)w * Tb + j) * S + h * HD;
+    if (d + 1 < HD) {
+      const float2 v = *(const float2 *)(row + d);
+      x = v.x, y = v.y;
+    } else if (d < HD) {
+      x = row[d];
     }
-    ((__half2 *)dst)[i] = __floats2half2_rn(x, y);
   }
+  ((__half2 *)dst)[((((size_t)batch * tiles_n + tn) * nch + c) * 128 + jr) * 32 + pr] = __floats2half2_rn(x, y);
 }
 
 // probabilities: p[(batch*Tq + r) * Tk + j] -> Ap[batch][j/64][r][j%64], j zero padded
@@ -76,9 +78,10 @@ __global__ void __launch_bounds__(256) k_pack_w_vT(const float *__restrict__ v, 
   extern __shared__ float tile[];  // [64 keys][HD + 1]
   const int batch = blockIdx.x / nch, c = blockIdx.x % nch;
   const int w = batch / H, h = batch % H, ldt = HD + 1;
-  for (int e = threadIdx.x; e < 64 * HD; e += 256) {
-    const int jj = e / HD, d = e % HD, j = c * 64 + jj;
-    tile[jj * ldt + d] = j < Tk ? v[((size_t)w * Tk + j) * S + h * HD + d] : 0.f;
+  for (int jj = threadIdx.x >> 5; jj < 64; jj += 8) {  // a warp per key row, lanes along the head dimension
+    const int j = c * 64 + jj;
+    const float *row = v + ((size_t)w * Tk + (j < Tk ? j : Tk - 1)) * S + h * HD;
+    for (int d = threadIdx.x & 31; d < HD; d += 32) tile[jj * ldt + d] = j < Tk ? row[d] : 0.f;
   }
   __syncthreads();
   // dst rows: for each d (padded to tiles_n*128), 64 keys = 32 half2
@@ -158,21 +161,21 @@ int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, f
   const int S = H * HD, nch = ceil_div(HD, 64), tiles_n = ceil_div(Tb, 128);
   const int wb = b_shared ? H : (int)batches;  // shared keys (the positional table) are packed once per head
   const size_t a_halves = (size_t)batches * nch * T * 64, w_halves = (size_t)wb * tiles_n * nch * 128 * 64;
-  if (a_halves / 2 >= (1ull << 31) || w_halves / 2 >= (1ull << 31)) return FA_OK;
+  if (a_halves / 2 >= (1ull << 31) || w_halves / 2 >= (1ull << 31) || batches > 65535 || tiles_n * nch > 65535) return FA_OK;
   Block ap(ctx), wp(ctx);
   FA_TRY(ap.get(a_halves * 2));
   FA_TRY(wp.get(w_halves * 2));
   {
     LaunchScope ls(ctx, "attn_pack_q");
-    k_pack_act_heads<<<grid_for(ctx, a_halves / 2), 256, 0, ctx->stream>>>(q, qb, (__half *)ap.p, T, S, H, HD, nch,
-                                                                          (unsigned)(a_halves / 2));
+    k_pack_act_heads<<<dim3(ceil_div(T, 8), nch, (unsigned)batches), 256, 0, ctx->stream>>>(q, qb, (__half *)ap.p, T, S, H,
+                                                                                           HD, nch);
   }
   FA_LAUNCH_CHECK(ctx, "attn_pack_q");
   {
     LaunchScope ls(ctx, "attn_pack_k");
     // with shared keys the source has a single "window" (w = 0 for every packed batch h)
-    k_pack_w_heads<<<grid_for(ctx, w_halves / 2), 256, 0, ctx->stream>>>(b, (__half *)wp.p, Tb, S, H, HD, tiles_n, nch,
-                                                                        (unsigned)(w_halves / 2));
+    k_pack_w_heads<<<dim3(16, tiles_n * nch, (unsigned)wb), 256, 0, ctx->stream>>>(b, (__half *)wp.p, Tb, S, H, HD, tiles_n,
+                                                                                  nch, 0);
   }
   FA_LAUNCH_CHECK(ctx, "attn_pack_k");
   TcEpilogue ep;

@@ -34,16 +34,18 @@ namespace {
 
 using namespace tc;
 
-constexpr int kEpiWarps = 8;                   // two per TMEM lane quadrant
+constexpr int kEpiWarps = 8;                   // two per TMEM lane quadrant (one per quadrant leaves the MMA and
+                                               // producer warps more issue slots - later tiles ran ~15 % faster - but
+                                               // doubles the epilogue's own time, and the encoder step got 20 % slower)
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
 constexpr int kRowBytes = 128;                 // one swizzle atom of K per stage
 constexpr int kPTileBytes = 128 * kRowBytes;   // weights tile: 128 rows
-// int4 variant: 8 more warps unpack nibbles into the f16 weights tile.  They sit on warp ids 10,11,14,15,18,19,22,23
-// (ids 12,13,16,17,20,21 have no role and park at the closing barrier): with warps dealt to the four schedulers round-robin, that keeps the busy
+// int4 variant: 8 more warps unpack nibbles into the f16 weights tile.  They sit on the warp ids above the epilogue
+// warps whose id has bit 1 set (10,11,14,15,18,19,22,23; the ids between have no role and park at the closing barrier): with warps dealt to the four schedulers round-robin, that keeps the busy
 // unpack warps off the schedulers of warp 0 (TMA producer) and warp 1 (MMA issuer), whose single-lane loops
 // otherwise get every third issue slot and set the pace of the whole pipeline (measured: ~550 ns per K chunk).
 constexpr int kDeqWarps = 8;
-constexpr int kThreadsNbits = 32 * 24;
+constexpr int kThreadsNbits = 32 * (2 + kEpiWarps + 2 * kDeqWarps - 2);
 constexpr int kRawTileBytes = 128 * 32;        // int4 variant: 128 rows x 64 nibbles of one K chunk, as uploaded
 constexpr int kSplitMaxMT = 128;               // split-K mode keeps a [MT][128] f32 partial tile in smem
 
@@ -142,7 +144,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
   const bool n_ok = n < p.N;
   const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
   const float bs = (p.bias && n_ok) ? p.bias[n] : 0.0f;
-  for (int c = half * 16; c < p.MT; c += 32) {
+  for (int c = half * 16; c < p.MT; c += 4 * kEpiWarps) {
     if (m0 + c >= p.M) break;  // warp-uniform: no rows left in this tile
     uint32_t v0[16], v1[16], v2[16];
     tmem_ld16(lane_addr + (uint32_t)c, v0);
@@ -410,8 +412,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   } else if (KIND == 2 && warp >= 2 + kEpiWarps) {
     // ---- int4 unpack: two groups of four warps take alternate K chunks, so one group's load-unpack-store
     // chain overlaps the other's; a thread owns weight row r of the tile for both 32-weight blocks of a chunk
-    // warps 10,11,14,15 -> unpack index 0..3 (group 0), warps 18,19,22,23 -> 4..7 (group 1)
-    const int dw = ((warp - 10) >> 2) * 2 + (warp & 1);
+    // the first four unpack warps (by id) form group 0, the last four group 1
+    const int dw = ((warp - (2 + kEpiWarps)) >> 2) * 2 + (warp & 1);
     const int dq = dw * 32 + lane, r = dq & 127, grp = dq >> 7;
     const uint32_t nst = (uint32_t)p.stages;
     const int chunks = kb1 - kb0;
@@ -549,10 +551,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     if (warp >= 2 && warp < 2 + kEpiWarps && !aborted()) {
       const int tile = blockIdx.x, tn = tile % p.tiles_n, tm = tile / p.tiles_n;
       const int n0 = tn * 128, m0 = tm * p.MT;
-      const int t = threadIdx.x - 64;  // 256 threads, each owns groups of 4 consecutive columns
+      const int t = threadIdx.x - 64;  // the epilogue threads, each owns groups of 4 consecutive columns
       const bool vec_ok = (p.N & 3) == 0;
       // every CTA of the cluster finishes an interleaved share of the tile (remote reads are the cost)
-      for (int g = t + 256 * (int)rank; g < p.MT * 32; g += 256 * p.splitk) {
+      constexpr int ET = 32 * kEpiWarps;
+      for (int g = t + ET * (int)rank; g < p.MT * 32; g += ET * p.splitk) {
         const int ml = g >> 5, nl = (g & 31) * 4, m = m0 + ml, n = n0 + nl;
         if (m >= p.M || n >= p.N) continue;
         // all remote reads first (independent), then the rank-ordered sum

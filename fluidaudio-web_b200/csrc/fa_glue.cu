@@ -139,6 +139,61 @@ __global__ void __launch_bounds__(256) k_layernorm_reg(const float *__restrict__
   }
 }
 
+// One warp per row (C % 4 == 0, C <= 1024): the row lives in the warp's registers, both reductions are
+// shuffles, no block barrier; 8 rows per CTA.  Same two-pass mean / variance arithmetic as above.
+template <int V4>  // float4 per lane: C <= 128 * V4
+__global__ void __launch_bounds__(256) k_layernorm_warp(const float *__restrict__ x, const float *__restrict__ g,
+                                                        const float *__restrict__ b, float *__restrict__ y,
+                                                        __half *__restrict__ y16, size_t lo_off, int R, int C, float eps) {
+  const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5), c4 = C >> 2;
+  if (r >= R) return;
+  const float4 *row = (const float4 *)(x + (size_t)r * C);
+  float4 v[V4];
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < V4; u++) {
+    const int q = lane + u * 32;
+    v[u] = q < c4 ? row[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+  }
+  const float mean = warp_sum(s) / (float)C;
+  float vs = 0.f;
+#pragma unroll
+  for (int u = 0; u < V4; u++) {
+    if (lane + u * 32 < c4) {
+      const float a = v[u].x - mean, bb = v[u].y - mean, c = v[u].z - mean, d = v[u].w - mean;
+      vs += (a * a + bb * bb) + (c * c + d * d);
+    }
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(vs) / (float)C + eps);
+#pragma unroll
+  for (int u = 0; u < V4; u++) {
+    const int q = lane + u * 32;
+    if (q < c4) {
+      const float4 gg = ((const float4 *)g)[q], bb = ((const float4 *)b)[q];
+      float4 o;
+      o.x = (v[u].x - mean) * inv * gg.x + bb.x;
+      o.y = (v[u].y - mean) * inv * gg.y + bb.y;
+      o.z = (v[u].z - mean) * inv * gg.z + bb.z;
+      o.w = (v[u].w - mean) * inv * gg.w + bb.w;
+      ((float4 *)(y + (size_t)r * C))[q] = o;
+      if (y16) {
+        const int j = q * 4;
+        __half2 *d16 = (__half2 *)(y16 + ((size_t)(j >> 6) * R + r) * 64 + (j & 63));
+        const __half2 h0 = __floats2half2_rn(o.x, o.y), h1 = __floats2half2_rn(o.z, o.w);
+        d16[0] = h0;
+        d16[1] = h1;
+        if (lo_off) {
+          const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+          __half2 *l16 = (__half2 *)((__half *)d16 + lo_off);
+          l16[0] = __floats2half2_rn(o.x - f0.x, o.y - f0.y);
+          l16[1] = __floats2half2_rn(o.z - f1.x, o.w - f1.y);
+        }
+      }
+    }
+  }
+}
+
 // One warp per row (wasm-context.js:327-343).
 __global__ void k_softmax(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
   const int warps = (blockDim.x >> 5);
@@ -588,37 +643,40 @@ template <int K>
 __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict__ x, const float *__restrict__ w,
                                                          const float *__restrict__ bias, float *__restrict__ y,
                                                          __half *__restrict__ y16, int rows, int Tw, int D, int padl,
-                                                         int act) {
+                                                         int act, int chunks) {
+  // blockIdx.y = (window, chunk of 16 frames inside it): every frame a CTA touches that belongs to its window
+  // takes part, everything else is a zero tap, so the filter loop needs no per-tap window test.
   const int c = blockIdx.x * 256 + threadIdx.x;
   if (c >= D) return;
+  const int wdw = blockIdx.y / chunks, ch = blockIdx.y - wdw * chunks;
+  const int lo = wdw * Tw, hi = lo + Tw;          // frames of this window
+  const int t0 = lo + ch * 16, nt = min(16, hi - t0);
   float wk[K];
 #pragma unroll
   for (int kk = 0; kk < K; kk++) wk[kk] = w[(size_t)c * K + kk];
   const float b = bias ? bias[c] : 0.f;
-  const int t0 = blockIdx.y * 16;
   float g[16 + K - 1], gate[16 + K - 1];
-  int win[16 + K - 1];
-  // all loads first (addresses clamped into the tensor so none is conditional), then the gating math
+  // all loads first (addresses clamped into the window so none is conditional), then the gating math
 #pragma unroll
   for (int j = 0; j < 16 + K - 1; j++) {
-    const int tg = t0 - padl + j, tc = min(max(tg, 0), rows - 1);
+    const int tg = t0 - padl + j, tc = min(max(tg, lo), hi - 1);
     const float *xr = x + (size_t)tc * (2 * D);
     g[j] = __ldg(xr + c);
     gate[j] = __ldg(xr + c + D);
-    win[j] = (tg >= 0 && tg < rows) ? tg / Tw : -1;
   }
 #pragma unroll
-  for (int j = 0; j < 16 + K - 1; j++) g[j] = g[j] * (1.0f / (1.0f + __expf(-gate[j])));
+  for (int j = 0; j < 16 + K - 1; j++) {
+    const int tg = t0 - padl + j;
+    g[j] = (tg >= lo && tg < hi) ? g[j] * (1.0f / (1.0f + __expf(-gate[j]))) : 0.f;
+  }
 #pragma unroll
   for (int i = 0; i < 16; i++) {
-    const int t = t0 + i;
-    if (t >= rows) break;
-    const int wt = t / Tw;  // window of frame t itself
+    if (i >= nt) break;
     float acc = b;
 #pragma unroll
-    for (int kk = 0; kk < K; kk++)
-      if (win[i + kk] == wt) acc = fmaf(wk[kk], g[i + kk], acc);
+    for (int kk = 0; kk < K; kk++) acc = fmaf(wk[kk], g[i + kk], acc);
     const float o = fa_actf(acc, act);
+    const int t = t0 + i;
     y[(size_t)t * D + c] = o;
     if (y16) y16[((size_t)(c >> 6) * rows + t) * 64 + (c & 63)] = __float2half_rn(o);
   }
@@ -786,8 +844,12 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
           y->a16_valid = true;
         }
       }
-      if ((x->cols & 3) == 0 && x->cols <= 1024 && al)
-        k_layernorm_reg<1><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows, x->cols, eps);
+      if ((x->cols & 3) == 0 && x->cols <= 512 && al)
+        k_layernorm_warp<4><<<ceil_div(x->rows, 8), 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
+                                                                          x->cols, eps);
+      else if ((x->cols & 3) == 0 && x->cols <= 1024 && al)
+        k_layernorm_warp<8><<<ceil_div(x->rows, 8), 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
+                                                                          x->cols, eps);
       else if (reg)
         k_layernorm_reg<4><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows, x->cols, eps);
       else
@@ -1300,9 +1362,10 @@ extern "C" int fa_glu_dwconv_tm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor
     {
       LaunchScope ls(ctx, "glu_dwconv_tm");
       const float *bp = bias ? (const float *)bias->dptr : nullptr;
-      if (k == 9)
-        k_glu_dwconv_tm_k<9><<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr, bp,
-                                                            (float *)y->dptr, y16, rows, Tw, D, pad_left, act);
+      const int chunks = ceil_div(Tw, 16);
+      if (k == 9 && (long long)windows * chunks <= 65535)
+        k_glu_dwconv_tm_k<9><<<dim3(ceil_div(D, 256), windows * chunks), 256, 0, ctx->stream>>>(
+            (const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr, y16, rows, Tw, D, pad_left, act, chunks);
       else
         k_glu_dwconv_tm<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr,
                                                        y16, rows, Tw, D, k, pad_left, act);
