@@ -173,7 +173,7 @@ class Int4Decode:
         return self.bytes_per_step * steps / seconds / 1e9
 
     def roofline(self, prof, peaks):
-        ent = [e for e in prof if e["label"].startswith(("nbits", "tc_gemm_f16"))]
+        ent = [e for e in prof if e["label"].startswith(("gemv_nbits", "nbits", "tc_gemm"))]
         if not ent:
             return None
         e = max(ent, key=lambda x: x["ms"])
@@ -183,6 +183,32 @@ class Int4Decode:
         return {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": None, "kernel": e["label"],
                 "avg_launch_us": round(per_launch_ms * 1e3, 2), "peak_source": peaks["source"]}
+
+    def roofline_live(self, ctx, peaks, timer):
+        """The dominant kernel on its own: the M = 1 and M = 4 products (k_gemv_nbits) over the rotating weight
+        sets, recorded back to back and replayed; achieved = their algorithmic bytes / CUDA-event time."""
+        Ms = [M for M in self.Ms if M <= 4]
+
+        def body():
+            h = ctx.pushArena()
+            for M in Ms:
+                for bq, sc, zp in self.dev_sets:
+                    ctx.matmulNBits(self.dev_acts[M], bq, sc, zp, self.N)
+            ctx.popArena(h)
+
+        body()
+        batch, _ = ctx.recordBatch(body)
+        reps = 20
+        ms = timer(lambda _c: batch.launch(), reps)
+        batch.free()
+        n = len(Ms) * self.nsets * reps
+        ach = sum(self.algorithmic_bytes(M) for M in Ms) * self.nsets * reps / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(ach / peaks["hbm_gbs"], 4),
+                "traffic": 10.8e6, "traffic_note": "per launch, ncu memory throughput x duration of the M=4 launches "
+                "(profiles/gemv_nbits_int4_decode.md); algorithmic bytes per launch 10.6e6",
+                "kernel": "k_gemv_nbits (label gemv_nbits), the M = 1 and M = 4 products", "launches_timed": n,
+                "avg_launch_us": round(ms * 1e3 / n, 2), "peak_source": peaks["source"]}
 
     def cpu_sample(self, threads=True):
         """One M=4 product at full N,K on the CPU port; returns (value in GB/s, description)."""
@@ -491,7 +517,10 @@ class Encoder:
         ach = flops * reps / (ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"]
         return {"bound": "tensor", "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
-                "traffic": None, "kernel": "k_tc_gemm<f16> (label tc_gemm_f16)", "launches_timed": len(seq) * reps,
+                "traffic": 26.3e6, "traffic_note": "ncu dram read+write of ONE launch at M=4096, K=1024, N=4096 "
+                "(profiles/tc_gemm_f16_M4096_K1024_N4096.md): 16.9 MB read = the two f16 operands once, 9.4 MB written "
+                "(the rest of the 67 MB f32 result was still in the 126 MB L2 at kernel end); algorithmic 84 MB",
+                "kernel": "k_tc_gemm<f16> (label tc_gemm_f16)", "launches_timed": len(seq) * reps,
                 "avg_launch_us": round(ms * 1e3 / (len(seq) * reps), 2),
                 "what": "the 10 weight products of one conformer block at M=%d, back to back (recorded batch)" % M,
                 "peak_source": peaks["source"] + " (burst bf16: kernel timed alone)"}
@@ -603,7 +632,10 @@ class Decoder:
         ms = ent["bmm_qk_t1"]["ms"] + ent["bmm_pv_t1"]["ms"]
         launches = ent["bmm_qk_t1"]["count"] + ent["bmm_pv_t1"]["count"]
         ach = 2 * self.attn_bytes_per_step() / (ms * 1e-3) / 1e9  # per step; the caller scales by `steps`
-        return {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None,
+        return {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
+                "traffic": float(self.S * self.Tenc * self.cfg["D"] * 4),
+                "traffic_note": "per cross-attention launch = its algorithmic bytes: ncu shows 1-2 % L2 hits on these "
+                "launches (profiles/bmm_t1_cross_attention.md), i.e. the cache is streamed from DRAM once",
                 "kernel": "k_bmm_qk_t1 + k_bmm_pv_t1 (single-query attention over the f32 K/V caches)",
                 "launches": launches, "avg_launch_us": round(ms / launches * 1e3, 2),
                 "share_of_step": None, "peak_source": peaks["source"]}

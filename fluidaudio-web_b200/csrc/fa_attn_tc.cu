@@ -17,6 +17,7 @@ namespace {
 // division left is the one per thread that splits the batch index.
 __global__ void __launch_bounds__(256) k_pack_act_heads(const float *__restrict__ src, const float *__restrict__ addv,
                                                         __half *__restrict__ dst, int T, int S, int H, int HD, int nch) {
+  fa_grid_dep_sync();
   const int pr = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= T) return;
   const int c = blockIdx.y, batch = blockIdx.z, w = batch / H, h = batch - w * H, d = c * 64 + pr * 2;
@@ -39,6 +40,7 @@ __global__ void __launch_bounds__(256) k_pack_act_heads(const float *__restrict_
 // Grid (16 row groups of 8 per 128-row tile, tiles_n * nch, batch).
 __global__ void __launch_bounds__(256) k_pack_w_heads(const float *__restrict__ src, __half *__restrict__ dst, int Tb, int S,
                                                       int H, int HD, int tiles_n, int nch, int w_shared) {
+  fa_grid_dep_sync();
   const int pr = threadIdx.x & 31, jr = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int tn = blockIdx.y / nch, c = blockIdx.y - tn * nch, batch = blockIdx.z;
   const int w = w_shared ? 0 : batch / H, h = batch % H, j = tn * 128 + jr, d = c * 64 + pr * 2;
@@ -58,6 +60,7 @@ __global__ void __launch_bounds__(256) k_pack_w_heads(const float *__restrict__ 
 // probabilities: p[(batch*Tq + r) * Tk + j] -> Ap[batch][j/64][r][j%64], j zero padded
 __global__ void k_pack_act_probs(const float *__restrict__ p, __half *__restrict__ dst, int Tq, int Tk, int nch,
                                  unsigned total) {
+  fa_grid_dep_sync();
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const int pr = i & 31;
     unsigned t = i >> 5;
@@ -75,6 +78,7 @@ __global__ void k_pack_act_probs(const float *__restrict__ p, __half *__restrict
 // One CTA per (batch, 64-key chunk): the 64 x HD slab goes through shared memory.
 __global__ void __launch_bounds__(256) k_pack_w_vT(const float *__restrict__ v, __half *__restrict__ dst, int Tk, int S,
                                                    int H, int HD, int tiles_n, int nch) {
+  fa_grid_dep_sync();
   extern __shared__ float tile[];  // [64 keys][HD + 1]
   const int batch = blockIdx.x / nch, c = blockIdx.x % nch;
   const int w = batch / H, h = batch % H, ldt = HD + 1;
@@ -103,6 +107,7 @@ __global__ void __launch_bounds__(256) k_pack_w_vT(const float *__restrict__ v, 
 // K tail zero filled.  One warp per score row, the row held in registers (T <= 256).
 __global__ void k_softmax_shift_pack(const float *__restrict__ ac, const float *__restrict__ bd, __half *__restrict__ dst,
                                      int rows, int T, int nch) {
+  fa_grid_dep_sync();
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31, P = 2 * T - 1;
   for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps) {
     const int batch = r / T, i = r - batch * T;
@@ -167,14 +172,14 @@ int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, f
   FA_TRY(wp.get(w_halves * 2));
   {
     LaunchScope ls(ctx, "attn_pack_q");
-    k_pack_act_heads<<<dim3(ceil_div(T, 8), nch, (unsigned)batches), 256, 0, ctx->stream>>>(q, qb, (__half *)ap.p, T, S, H,
+    fa_launch_dep(ctx, k_pack_act_heads, dim3(dim3(ceil_div(T, 8), nch, (unsigned)batches)), dim3(256), 0, q, qb, (__half *)ap.p, T, S, H,
                                                                                            HD, nch);
   }
   FA_LAUNCH_CHECK(ctx, "attn_pack_q");
   {
     LaunchScope ls(ctx, "attn_pack_k");
     // with shared keys the source has a single "window" (w = 0 for every packed batch h)
-    k_pack_w_heads<<<dim3(16, tiles_n * nch, (unsigned)wb), 256, 0, ctx->stream>>>(b, (__half *)wp.p, Tb, S, H, HD, tiles_n,
+    fa_launch_dep(ctx, k_pack_w_heads, dim3(dim3(16, tiles_n * nch, (unsigned)wb)), dim3(256), 0, b, (__half *)wp.p, Tb, S, H, HD, tiles_n,
                                                                                   nch, 0);
   }
   FA_LAUNCH_CHECK(ctx, "attn_pack_k");
@@ -211,7 +216,7 @@ static int pv_core(fa_ctx *ctx, const float *p, const __half *p16, const float *
     FA_TRY(ap.get(a_halves * 2));
     {
       LaunchScope ls(ctx, "attn_pack_p");
-      k_pack_act_probs<<<grid_for(ctx, a_halves / 2), 256, 0, ctx->stream>>>(p, (__half *)ap.p, Tq, Tk, nch,
+      fa_launch_dep(ctx, k_pack_act_probs, dim3(grid_for(ctx, a_halves / 2)), dim3(256), 0, p, (__half *)ap.p, Tq, Tk, nch,
                                                                             (unsigned)(a_halves / 2));
     }
     FA_LAUNCH_CHECK(ctx, "attn_pack_p");
@@ -219,7 +224,7 @@ static int pv_core(fa_ctx *ctx, const float *p, const __half *p16, const float *
   }
   {
     LaunchScope ls(ctx, "attn_pack_v");
-    k_pack_w_vT<<<(unsigned)(batches * nch), 256, (size_t)64 * (HD + 1) * 4, ctx->stream>>>(v, (__half *)wp.p, Tk, S, H, HD,
+    fa_launch_dep(ctx, k_pack_w_vT, dim3((unsigned)(batches * nch)), dim3(256), (size_t)64 * (HD + 1) * 4, v, (__half *)wp.p, Tk, S, H, HD,
                                                                                           tiles_n, nch);
   }
   FA_LAUNCH_CHECK(ctx, "attn_pack_v");
@@ -270,7 +275,7 @@ int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v
     const int rows = (int)(batches * T);
     int grid = ceil_div(rows, 8);
     if (grid > ctx->sm_count * 16) grid = ctx->sm_count * 16;
-    k_softmax_shift_pack<<<grid, 256, 0, ctx->stream>>>((const float *)ac.p, (const float *)bd.p, (__half *)pr.p, rows, T, nch);
+    fa_launch_dep(ctx, k_softmax_shift_pack, dim3(grid), dim3(256), 0, (const float *)ac.p, (const float *)bd.p, (__half *)pr.p, rows, T, nch);
   }
   FA_LAUNCH_CHECK(ctx, "attn_softmax_shift_pack");
   FA_TRY(pv_core(ctx, nullptr, (const __half *)pr.p, v, out, out16, T, T, H, HD, W));

@@ -70,6 +70,7 @@ extern "C" int fa_ctx_create(int device, fa_ctx **out) {
     delete ctx;
     return fa_fail(nullptr, FA_ERR_CUDA, "fa_ctx_create: status word allocation failed");
   }
+  if (const char *e = getenv("FA_PDL")) ctx->pdl = atoi(e) != 0;  // A/B switch for measurements
   ctx->gemv_ticket_count = 8192;
   if (cudaMalloc(&ctx->gemv_tickets, sizeof(int) * ctx->gemv_ticket_count) != cudaSuccess ||
       cudaMemsetAsync(ctx->gemv_tickets, 0, sizeof(int) * ctx->gemv_ticket_count, ctx->stream) != cudaSuccess) {
@@ -115,6 +116,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
   if (!strcmp(key, "f16_hilo_rows")) {
     FA_REQUIRE(ctx, value >= 0, "f16_hilo_rows must be >= 0 (got %lld)", value);
     ctx->f16_hilo_rows = value > 0x7fffffffLL ? 0x7fffffff : (int)value;
+    return FA_OK;
+  }
+  if (!strcmp(key, "pdl")) {
+    FA_REQUIRE(ctx, value == 0 || value == 1, "pdl must be 0 or 1 (got %lld)", value);
+    ctx->pdl = (int)value;
     return FA_OK;
   }
   if (!strcmp(key, "nbits_fused")) {

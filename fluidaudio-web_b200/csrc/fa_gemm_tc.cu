@@ -296,6 +296,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+  fa_grid_dep_sync();  // barriers, TMEM and descriptors were set up while the previous kernel drained
   if (threadIdx.x == 0) TC_TRACE(0);
 
   auto aborted = [&]() {
@@ -784,6 +785,7 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // f32 [M][K] -> f16 Ap[k/64][m][k%64], K tail zero padded.
 __global__ void k_prep_a_f16(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
+  fa_grid_dep_sync();
   const size_t total = (size_t)nch * M * 32;  // half2 pairs
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int pr = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
@@ -821,6 +823,7 @@ __global__ void k_nbits_side(const float *__restrict__ scales, const uint8_t *__
 // f32 [M][K] -> f16 Ap[k/64][m][64] for the int4 variant: inside every group of 8 the order of k is
 // 0,4,1,5,2,6,3,7, the order its in-kernel nibble unpack produces.
 __global__ void k_prep_a_f16_perm8(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
+  fa_grid_dep_sync();
   const size_t total = (size_t)nch * M * 32;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int pr = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
@@ -834,6 +837,7 @@ __global__ void k_prep_a_f16_perm8(const float *__restrict__ a, int M, int K, in
 // f32 [M][K] -> two f16 planes Ap[2][k/64][m][k%64]: hi = f16(a), lo = f16(a - hi).  hi + lo carries about
 // 22 bits of a, so a product that accumulates both planes in f32 is as accurate as an f32-activation one.
 __global__ void k_prep_a_f16_hilo(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
+  fa_grid_dep_sync();
   const size_t total = (size_t)nch * M * 32;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int pr = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
@@ -853,6 +857,7 @@ __global__ void k_prep_a_f16_hilo(const float *__restrict__ a, int M, int K, int
 __global__ void __launch_bounds__(256) k_prep_a_i8(const float *__restrict__ a, int M, int K, int nch, int limbs,
                                                    int8_t *__restrict__ out, float *__restrict__ rowscale) {
   __shared__ float red[8];
+  fa_grid_dep_sync();
   const int m = blockIdx.x;
   const float *row = a + (size_t)m * K;
   float mx = 0.0f;
@@ -1161,18 +1166,21 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
                                (uint64_t)(p.a_shared ? 1 : p.batches) * limbs * p.num_kb, (uint32_t)p.MT));
   FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   cfg.blockDim = dim3(KIND == 2 ? kThreadsNbits : kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see fa_launch_dep
+  attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   if (p.splitk > 1) {
     cfg.gridDim = dim3(num_tiles, 1, p.splitk);
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = p.splitk;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = p.splitk;
+    cfg.numAttrs = 2;
   } else {
     cfg.gridDim = dim3(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);  // persistent: one CTA per SM
   }
@@ -1286,7 +1294,7 @@ int fa_prep_a_f16_perm8(fa_ctx *ctx, const float *a, int M, int K, __half *out) 
   const int nch = fa_tc_chunks(K, 2);
   {
     LaunchScope ls(ctx, "prep_a_f16_perm8");
-    k_prep_a_f16_perm8<<<grid_for(ctx, (size_t)nch * M * 32, 256, 8), 256, 0, ctx->stream>>>(a, M, K, nch, out);
+    fa_launch_dep(ctx, k_prep_a_f16_perm8, dim3(grid_for(ctx, (size_t)nch * M * 32, 256, 8)), dim3(256), 0, a, M, K, nch, out);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_f16_perm8");
   return FA_OK;
@@ -1307,7 +1315,7 @@ int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out) {
   const int nch = fa_tc_chunks(K, 2);
   {
     LaunchScope ls(ctx, "prep_a_f16");
-    k_prep_a_f16<<<grid_for(ctx, (size_t)nch * M * 32, 256, 8), 256, 0, ctx->stream>>>(a, M, K, nch, out);
+    fa_launch_dep(ctx, k_prep_a_f16, dim3(grid_for(ctx, (size_t)nch * M * 32, 256, 8)), dim3(256), 0, a, M, K, nch, out);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_f16");
   return FA_OK;
@@ -1318,7 +1326,7 @@ int fa_prep_a_f16_hilo(fa_ctx *ctx, const float *a, int M, int K, __half *out) {
   const int nch = fa_tc_chunks(K, 2);
   {
     LaunchScope ls(ctx, "prep_a_f16_hilo");
-    k_prep_a_f16_hilo<<<grid_for(ctx, (size_t)nch * M * 32, 256, 8), 256, 0, ctx->stream>>>(a, M, K, nch, out);
+    fa_launch_dep(ctx, k_prep_a_f16_hilo, dim3(grid_for(ctx, (size_t)nch * M * 32, 256, 8)), dim3(256), 0, a, M, K, nch, out);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_f16_hilo");
   return FA_OK;
@@ -1328,7 +1336,7 @@ int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *o
   if (M == 0) return FA_OK;
   {
     LaunchScope ls(ctx, "prep_a_i8");
-    k_prep_a_i8<<<M, 256, 0, ctx->stream>>>(a, M, K, fa_tc_chunks(K, 1), limbs, out, rowscale);
+    fa_launch_dep(ctx, k_prep_a_i8, dim3(M), dim3(256), 0, a, M, K, fa_tc_chunks(K, 1), limbs, out, rowscale);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_i8");
   return FA_OK;

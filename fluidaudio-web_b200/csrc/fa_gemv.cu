@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(kThreads) k_gemv_nbits(const float *__restrict
   int *SA = (int *)(smem + (size_t)M * 2 * K);      // [M][2][nblk] digit sums per block
   float *red = (float *)(SA + M * 2 * nblk);        // [8][M] per-warp row maxima
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  fa_grid_dep_sync();
 
   // Activation digits, all M rows at once so the loads of a pass overlap: row maxima, then q1 = rint(a/s),
   // q2 = rint((a/s - q1) * 128) with s = max/127, stored in the order the nibbles unpack to.
@@ -213,6 +214,7 @@ __global__ void __launch_bounds__(kThreads) k_gemv_kn(const float *__restrict__ 
   const int k0 = blockIdx.y * kslice, k1 = min(K, k0 + kslice), ks = gridDim.y;
   const int c0 = blockIdx.x * CW + lane * VEC;
   const bool live = c0 < N;  // N % VEC == 0, so a live lane owns VEC whole columns
+  fa_grid_dep_sync();
   for (int i = tid; i < M * kslice; i += kThreads) {
     const int m = i / kslice, kk = i - m * kslice;
     as[i] = k0 + kk < k1 ? a[(size_t)m * K + k0 + kk] : 0.f;
@@ -292,8 +294,8 @@ int launch_kn(fa_ctx *ctx, const float *a, const void *w, float *y, float *parti
   if (smem > 48 * 1024) FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
     LaunchScope ls(ctx, I8 ? "gemv_i8" : "gemv_f16");
-    kern<<<dim3(ceil_div(N, 32 * VEC), ksplit), kThreads, smem, ctx->stream>>>(a, w, y, partials, ctx->gemv_tickets, K, N,
-                                                                               kslice, ep);
+    fa_launch_dep(ctx, kern, dim3(ceil_div(N, 32 * VEC), ksplit), dim3(kThreads), smem, a, w, y, partials, ctx->gemv_tickets, K,
+                  N, kslice, ep);
   }
   FA_LAUNCH_CHECK(ctx, "gemv_kn");
   return FA_OK;
@@ -326,7 +328,7 @@ int launch_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *sc
   if (grid > ctx->sm_count * per_sm) grid = ctx->sm_count * per_sm;
   {
     LaunchScope ls(ctx, "gemv_nbits");
-    kern<<<grid, kThreads, smem, ctx->stream>>>(a, bq, scales, zp, y, N, K, nblk, zpb);
+    fa_launch_dep(ctx, kern, dim3(grid), dim3(kThreads), smem, a, bq, scales, zp, y, N, K, nblk, zpb);
   }
   FA_LAUNCH_CHECK(ctx, "gemv_nbits");
   return FA_OK;

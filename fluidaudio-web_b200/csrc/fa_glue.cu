@@ -20,6 +20,7 @@ __device__ __forceinline__ float warp_max(float v) {
 __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ g,
                                                    const float *__restrict__ b, float *__restrict__ y,
                                                    __half *__restrict__ y16, int R, int C, float eps) {
+  fa_grid_dep_sync();
   __shared__ float red[8];
   __shared__ float stat;
   for (int r = blockIdx.x; r < R; r += gridDim.x) {
@@ -69,6 +70,7 @@ __global__ void __launch_bounds__(256) k_layernorm_reg(const float *__restrict__
                                                        const float *__restrict__ b, float *__restrict__ y,
                                                        __half *__restrict__ y16, size_t lo_off, int R, int C,
                                                        float eps) {
+  fa_grid_dep_sync();
   __shared__ float red[8];
   __shared__ float stat;
   const int r = blockIdx.x, c4 = C >> 2;
@@ -145,6 +147,7 @@ template <int V4>  // float4 per lane: C <= 128 * V4
 __global__ void __launch_bounds__(256) k_layernorm_warp(const float *__restrict__ x, const float *__restrict__ g,
                                                         const float *__restrict__ b, float *__restrict__ y,
                                                         __half *__restrict__ y16, size_t lo_off, int R, int C, float eps) {
+  fa_grid_dep_sync();
   const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5), c4 = C >> 2;
   if (r >= R) return;
   const float4 *row = (const float4 *)(x + (size_t)r * C);
@@ -196,6 +199,7 @@ __global__ void __launch_bounds__(256) k_layernorm_warp(const float *__restrict_
 
 // One warp per row (wasm-context.js:327-343).
 __global__ void k_softmax(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
+  fa_grid_dep_sync();
   const int warps = (blockDim.x >> 5);
   const int lane = threadIdx.x & 31;
   for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
@@ -213,6 +217,7 @@ __global__ void k_softmax(const float *__restrict__ x, float *__restrict__ y, in
 
 // Rows of up to 256 columns: the row lives in registers (8 values per lane), one read and one write.
 __global__ void k_softmax_reg(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
+  fa_grid_dep_sync();
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
     const float *row = x + (size_t)r * C;
@@ -242,12 +247,14 @@ __global__ void k_softmax_reg(const float *__restrict__ x, float *__restrict__ y
 // float4 forms of the elementwise family (n % 4 == 0, 16-byte aligned operands)
 __global__ void k_ewise4(const float4 *__restrict__ a, const float4 *__restrict__ b, float4 *__restrict__ y, unsigned n4,
                          int mul) {
+  fa_grid_dep_sync();
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
     const float4 p = a[i], q = b[i];
     y[i] = mul ? make_float4(p.x * q.x, p.y * q.y, p.z * q.z, p.w * q.w) : make_float4(p.x + q.x, p.y + q.y, p.z + q.z, p.w + q.w);
   }
 }
 __global__ void k_glu4(const float4 *__restrict__ x, float4 *__restrict__ y, unsigned n4) {
+  fa_grid_dep_sync();
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
     const float4 p = x[i], q = x[i + n4];
     y[i] = make_float4(p.x * (1.0f / (1.0f + expf(-q.x))), p.y * (1.0f / (1.0f + expf(-q.y))),
@@ -257,26 +264,31 @@ __global__ void k_glu4(const float4 *__restrict__ x, float4 *__restrict__ y, uns
 
 __global__ void k_ewise(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ y, size_t n, int C,
                         int bcast, int mul) {
+  fa_grid_dep_sync();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     float bv = bcast ? b[i % C] : b[i];
     y[i] = mul ? a[i] * bv : a[i] + bv;
   }
 }
 __global__ void k_scale(const float *__restrict__ x, float *__restrict__ y, size_t n, float s) {
+  fa_grid_dep_sync();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     y[i] = x[i] * s;
 }
 __global__ void k_unary(const float *__restrict__ x, float *__restrict__ y, size_t n, int act) {
+  fa_grid_dep_sync();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     y[i] = fa_actf(x[i], act);
 }
 // x[2C,T] -> x[c,t] * sigmoid(x[c+C,t]) (wasm-context.js:428-434)
 __global__ void k_glu(const float *__restrict__ x, float *__restrict__ y, int C, int T) {
+  fa_grid_dep_sync();
   size_t n = (size_t)C * T;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     y[i] = x[i] * (1.0f / (1.0f + expf(-x[i + n])));
 }
 __global__ void k_transpose(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
+  fa_grid_dep_sync();
   __shared__ float t[32][33];
   const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -292,6 +304,7 @@ __global__ void k_transpose(const float *__restrict__ x, float *__restrict__ y, 
 // dst[r, dcol0 + j] = src[r, scol0 + j] for j < width
 __global__ void k_copy_cols(const float *__restrict__ src, int scols, int scol0, float *__restrict__ dst, int dcols,
                             int dcol0, int rows, int width) {
+  fa_grid_dep_sync();
   size_t n = (size_t)rows * width;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     int r = (int)(i / width), j = (int)(i % width);
@@ -301,6 +314,7 @@ __global__ void k_copy_cols(const float *__restrict__ src, int scols, int scol0,
 // [C, Tsub*F] -> [Tsub, C*F] (wasm-context.js:552-563)
 // blockIdx.y = window: window b reads x + b*xstride and writes rows [b*Tsub, (b+1)*Tsub).
 __global__ void k_sub_reshape(const float *__restrict__ x, float *__restrict__ y, int C, int Tsub, int F, size_t xstride) {
+  fa_grid_dep_sync();
   size_t n = (size_t)Tsub * C * F;
   int CF = C * F;
   x += (size_t)blockIdx.y * xstride;
@@ -314,6 +328,7 @@ __global__ void k_sub_reshape(const float *__restrict__ x, float *__restrict__ y
 // reference reads row f / 2t, column f % 2t - 1; for 0 <= i, j < t that is row i, column t-1-i+j (never
 // the zero column), so every output row is one contiguous run of its input row.
 __global__ void k_rel_shift_b(const float *__restrict__ x, float *__restrict__ y, int rows, int t) {
+  fa_grid_dep_sync();
   const int p = 2 * t - 1;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const int i = r % t;
@@ -329,6 +344,7 @@ __global__ void k_rel_shift_b(const float *__restrict__ x, float *__restrict__ y
 __global__ void __launch_bounds__(256) k_bmm_qk(const float *__restrict__ q, const float *__restrict__ b,
                                                 const float *__restrict__ qb, float *__restrict__ out, int T, int Tb,
                                                 int H, int HD, int bShared) {
+  fa_grid_dep_sync();
   __shared__ __align__(16) float Qs[16][68], Bs[16][68];
   const int w = blockIdx.z / H, h = blockIdx.z % H, S = H * HD;
   const int i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
@@ -382,6 +398,7 @@ template <int U>
 __global__ void __launch_bounds__(256) k_bmm_qk_t1(const float *__restrict__ q, const float *__restrict__ b,
                                                     const float *__restrict__ qb, float *__restrict__ out, int Tb, int H,
                                                     int HD, int bShared, int lph) {
+  fa_grid_dep_sync();
   const int S = H * HD, w = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = blockIdx.x * 128 + lane * 4;
   const bool live = c < S;
@@ -430,6 +447,7 @@ template <int U>
 __global__ void __launch_bounds__(256) k_bmm_pv_t1(const float *__restrict__ p, const float *__restrict__ v,
                                                     float *__restrict__ out, __half *__restrict__ y16, size_t lo_off,
                                                     int Tk, int H, int HD) {
+  fa_grid_dep_sync();
   __shared__ float4 part[8][32];
   const int S = H * HD, w = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = blockIdx.x * 128 + lane * 4;
@@ -484,6 +502,7 @@ __global__ void __launch_bounds__(256) k_bmm_pv_t1(const float *__restrict__ p, 
 // out[(w*Tq+i)*S + h*HD + d] = sum_j p[((w*H+h)*Tq+i)*Tk + j] * v[(w*Tk+j)*S + h*HD + d]
 __global__ void __launch_bounds__(256) k_bmm_pv(const float *__restrict__ p, const float *__restrict__ v,
                                                 float *__restrict__ out, int Tq, int Tk, int H, int HD) {
+  fa_grid_dep_sync();
   __shared__ __align__(16) float Ps[16][68], Vs[16][68];
   const int w = blockIdx.z / H, h = blockIdx.z % H, S = H * HD;
   const int i0 = blockIdx.y * 64, d0 = blockIdx.x * 64;
@@ -536,6 +555,7 @@ __global__ void __launch_bounds__(256) k_bmm_pv(const float *__restrict__ p, con
 __global__ void k_conv1d(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                          float *__restrict__ y, int cout, int cin, int L, int Lout, int Lw, int k, int stride, int padl,
                          int dil, int groups, int act) {
+  fa_grid_dep_sync();
   const int cin_g = cin / groups, cout_g = cout / groups;
   const unsigned n = (unsigned)cout * (unsigned)Lout;
   for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
@@ -561,6 +581,7 @@ __global__ void k_conv1d(const float *__restrict__ x, const float *__restrict__ 
 __global__ void __launch_bounds__(256) k_dwconv1d(const float *__restrict__ x, const float *__restrict__ w,
                                                   const float *__restrict__ bias, float *__restrict__ y, int L, int Lw,
                                                   int k, int padl, int dil, int act) {
+  fa_grid_dep_sync();
   const int c = blockIdx.y, t = blockIdx.x * 256 + threadIdx.x;
   if (t >= L) return;
   const int wbase = (t / Lw) * Lw, tl = t - wbase;
@@ -579,6 +600,7 @@ __global__ void __launch_bounds__(256) k_dwconv2d_3x3(const float *__restrict__ 
                                                       const float *__restrict__ bias, float *__restrict__ y, int h, int W,
                                                       int sh, int sw, int pt, int pl, int Ho, int Wo, int act,
                                                       size_t xstride, size_t ystride) {
+  fa_grid_dep_sync();
   const int c = blockIdx.y;
   const unsigned plane = (unsigned)Ho * Wo, pos = blockIdx.x * 256 + threadIdx.x;
   if (pos >= plane) return;
@@ -611,6 +633,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm(const float *__restrict__
                                                        const float *__restrict__ bias, float *__restrict__ y,
                                                        __half *__restrict__ y16, int rows, int Tw, int D, int k, int padl,
                                                        int act) {
+  fa_grid_dep_sync();
   const int c = blockIdx.x * 256 + threadIdx.x;
   if (c >= D) return;
   float wk[16];
@@ -644,6 +667,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
                                                          const float *__restrict__ bias, float *__restrict__ y,
                                                          __half *__restrict__ y16, int rows, int Tw, int D, int padl,
                                                          int act, int chunks) {
+  fa_grid_dep_sync();
   // blockIdx.y = (window, chunk of 16 frames inside it): every frame a CTA touches that belongs to its window
   // takes part, everything else is a zero tap, so the filter loop needs no per-tap window test.
   const int c = blockIdx.x * 256 + threadIdx.x;
@@ -686,6 +710,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
 __global__ void k_conv2d(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                          float *__restrict__ y, int cout, int cin, int h, int W, int kh, int kw, int sh, int sw, int pt,
                          int pl, int Ho, int Wo, int groups, int act) {
+  fa_grid_dep_sync();
   const int cinG = cin / groups, coutG = cout / groups;
   const unsigned plane = (unsigned)Ho * (unsigned)Wo, n = (unsigned)cout * plane;
   for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
@@ -718,6 +743,7 @@ __global__ void __launch_bounds__(256) k_conv2d_c1_3x3(const float *__restrict__
                                                        const float *__restrict__ bias, float *__restrict__ y, int cout,
                                                        int h, int W, int sh, int sw, int pt, int pl, int Ho, int Wo,
                                                        int act, size_t xstride, size_t ystride) {
+  fa_grid_dep_sync();
   __shared__ float ws[32][9], bs[32];
   const int co0 = blockIdx.y * 32;
   x += (size_t)blockIdx.z * xstride;  // blockIdx.z = window
@@ -754,6 +780,7 @@ __global__ void __launch_bounds__(256) k_conv2d_c1_3x3(const float *__restrict__
 // of src/engines/asr-whisper/index.ts:80-97.
 __global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x, float *__restrict__ out, int R, int ld,
                                                      int C) {
+  fa_grid_dep_sync();
   __shared__ float bv[8];
   __shared__ int bi[8];
   for (int r = blockIdx.x; r < R; r += gridDim.x) {
@@ -788,6 +815,7 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x
 __global__ void __launch_bounds__(256) k_embed_rows(const float *__restrict__ table, const float *__restrict__ pos,
                                                      const float *__restrict__ idx, int stride, int V, int D, int n,
                                                      float *__restrict__ out, int *status) {
+  fa_grid_dep_sync();
   const int s = blockIdx.x;
   int t = (int)idx[(size_t)s * stride];
   if (t < 0 || t >= V) {
@@ -845,15 +873,15 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
         }
       }
       if ((x->cols & 3) == 0 && x->cols <= 512 && al)
-        k_layernorm_warp<4><<<ceil_div(x->rows, 8), 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
+        fa_launch_dep(ctx, k_layernorm_warp<4>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
                                                                           x->cols, eps);
       else if ((x->cols & 3) == 0 && x->cols <= 1024 && al)
-        k_layernorm_warp<8><<<ceil_div(x->rows, 8), 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
+        fa_launch_dep(ctx, k_layernorm_warp<8>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
                                                                           x->cols, eps);
       else if (reg)
-        k_layernorm_reg<4><<<x->rows, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows, x->cols, eps);
+        fa_launch_dep(ctx, k_layernorm_reg<4>, dim3(x->rows), dim3(256), 0, xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows, x->cols, eps);
       else
-        k_layernorm<<<grid, 256, 0, ctx->stream>>>(xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
+        fa_launch_dep(ctx, k_layernorm, dim3(grid), dim3(256), 0, xp, gp, bp, (float *)y->dptr, y16, x->rows, x->cols, eps);
     }
     FA_LAUNCH_CHECK(ctx, "layernorm");
   }
@@ -872,9 +900,9 @@ extern "C" int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
     {
       LaunchScope ls(ctx, "softmax");
       if (x->cols <= 256)
-        k_softmax_reg<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+        fa_launch_dep(ctx, k_softmax_reg, dim3(grid), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
       else
-        k_softmax<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+        fa_launch_dep(ctx, k_softmax, dim3(grid), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
     }
     FA_LAUNCH_CHECK(ctx, "softmax");
   }
@@ -896,10 +924,10 @@ extern "C" int fa_ewise(fa_ctx *ctx, const fa_tensor *a, const fa_tensor *b, int
     {
       LaunchScope ls(ctx, "ewise");
       if (!bcast && (n & 3) == 0 && n / 4 < (1ull << 32))
-        k_ewise4<<<grid1d(ctx, n / 4, 256), 256, 0, ctx->stream>>>((const float4 *)a->dptr, (const float4 *)b->dptr,
+        fa_launch_dep(ctx, k_ewise4, dim3(grid1d(ctx, n / 4, 256)), dim3(256), 0, (const float4 *)a->dptr, (const float4 *)b->dptr,
                                                                    (float4 *)y->dptr, (unsigned)(n / 4), op_mul);
       else
-        k_ewise<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)a->dptr, (const float *)b->dptr,
+        fa_launch_dep(ctx, k_ewise, dim3(grid1d(ctx, n, 256)), dim3(256), 0, (const float *)a->dptr, (const float *)b->dptr,
                                                               (float *)y->dptr, n, a->cols, bcast ? 1 : 0, op_mul);
     }
     FA_LAUNCH_CHECK(ctx, "ewise");
@@ -917,7 +945,7 @@ extern "C" int fa_scale(fa_ctx *ctx, const fa_tensor *x, float s, fa_tensor **ou
   if (n) {
     {
       LaunchScope ls(ctx, "scale");
-      k_scale<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, n, s);
+      fa_launch_dep(ctx, k_scale, dim3(grid1d(ctx, n, 256)), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, n, s);
     }
     FA_LAUNCH_CHECK(ctx, "scale");
   }
@@ -935,7 +963,7 @@ extern "C" int fa_unary(fa_ctx *ctx, const fa_tensor *x, int act, fa_tensor **ou
   if (n) {
     {
       LaunchScope ls(ctx, "unary");
-      k_unary<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, n, act);
+      fa_launch_dep(ctx, k_unary, dim3(grid1d(ctx, n, 256)), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, n, act);
     }
     FA_LAUNCH_CHECK(ctx, "unary");
   }
@@ -954,9 +982,9 @@ extern "C" int fa_glu(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
     {
       LaunchScope ls(ctx, "glu");
       if ((n & 3) == 0 && n / 4 < (1ull << 31))
-        k_glu4<<<grid1d(ctx, n / 4, 256), 256, 0, ctx->stream>>>((const float4 *)x->dptr, (float4 *)y->dptr, (unsigned)(n / 4));
+        fa_launch_dep(ctx, k_glu4, dim3(grid1d(ctx, n / 4, 256)), dim3(256), 0, (const float4 *)x->dptr, (float4 *)y->dptr, (unsigned)(n / 4));
       else
-        k_glu<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows / 2, x->cols);
+        fa_launch_dep(ctx, k_glu, dim3(grid1d(ctx, n, 256)), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, x->rows / 2, x->cols);
     }
     FA_LAUNCH_CHECK(ctx, "glu");
   }
@@ -974,7 +1002,7 @@ extern "C" int fa_transpose(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
     FA_REQUIRE(ctx, grid.y <= 65535, "transpose: %d rows is too many", x->rows);
     {
       LaunchScope ls(ctx, "transpose");
-      k_transpose<<<grid, block, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
+      fa_launch_dep(ctx, k_transpose, dim3(grid), dim3(block), 0, (const float *)x->dptr, (float *)y->dptr, x->rows, x->cols);
     }
     FA_LAUNCH_CHECK(ctx, "transpose");
   }
@@ -993,7 +1021,7 @@ extern "C" int fa_slice_cols(fa_ctx *ctx, const fa_tensor *x, int col0, int widt
   if (n) {
     {
       LaunchScope ls(ctx, "slice_cols");
-      k_copy_cols<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)x->dptr, x->cols, col0, (float *)y->dptr,
+      fa_launch_dep(ctx, k_copy_cols, dim3(grid1d(ctx, n, 256)), dim3(256), 0, (const float *)x->dptr, x->cols, col0, (float *)y->dptr,
                                                                 width, 0, x->rows, width);
     }
     FA_LAUNCH_CHECK(ctx, "slice_cols");
@@ -1014,7 +1042,7 @@ extern "C" int fa_set_cols(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, in
   if (n) {
     {
       LaunchScope ls(ctx, "set_cols");
-      k_copy_cols<<<grid1d(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)src->dptr, src->cols, 0,
+      fa_launch_dep(ctx, k_copy_cols, dim3(grid1d(ctx, n, 256)), dim3(256), 0, (const float *)src->dptr, src->cols, 0,
                                                                 (float *)dst->dptr, dst->cols, col0, src->rows, src->cols);
     }
     FA_LAUNCH_CHECK(ctx, "set_cols");
@@ -1026,6 +1054,7 @@ extern "C" int fa_set_cols(fa_ctx *ctx, fa_tensor *dst, const fa_tensor *src, in
 // leaves), into the row-major product out [M][world*Ns]: out[m][r*Ns + j] = g[r*M + m][j].
 __global__ void __launch_bounds__(256) k_unshard_cols(const float4 *__restrict__ g, float4 *__restrict__ out, int M,
                                                       int ns4, int world) {
+  fa_grid_dep_sync();
   const size_t total = (size_t)world * M * ns4;
   for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
     const int j = (int)(i % ns4);
@@ -1048,7 +1077,7 @@ extern "C" int fa_unshard_cols(fa_ctx *ctx, const fa_tensor *gathered, int world
   if (n4) {
     {
       LaunchScope ls(ctx, "unshard_cols");
-      k_unshard_cols<<<grid1d(ctx, n4, 256), 256, 0, ctx->stream>>>((const float4 *)gathered->dptr, (float4 *)y->dptr, M,
+      fa_launch_dep(ctx, k_unshard_cols, dim3(grid1d(ctx, n4, 256)), dim3(256), 0, (const float4 *)gathered->dptr, (float4 *)y->dptr, M,
                                                                     ns / 4, world);
     }
     FA_LAUNCH_CHECK(ctx, "unshard_cols");
@@ -1126,7 +1155,7 @@ static int sub_reshape_impl(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, in
   size_t n = (size_t)Tsub * C * F;
   {
     LaunchScope ls(ctx, "sub_reshape");
-    k_sub_reshape<<<dim3(grid1d(ctx, n, 256), windows), 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, C,
+    fa_launch_dep(ctx, k_sub_reshape, dim3(dim3(grid1d(ctx, n, 256), windows)), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, C,
                                                                               Tsub, F, (size_t)x->cols);
   }
   FA_LAUNCH_CHECK(ctx, "sub_reshape");
@@ -1155,7 +1184,7 @@ extern "C" int fa_rel_shift_b(fa_ctx *ctx, const fa_tensor *x, int H, fa_tensor 
     {
       LaunchScope ls(ctx, "rel_shift_b");
       const int rows = H * t, rgrid = rows < ctx->sm_count * 32 ? rows : ctx->sm_count * 32;
-      k_rel_shift_b<<<rgrid, t >= 128 ? 128 : 64, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, rows, t);
+      fa_launch_dep(ctx, k_rel_shift_b, dim3(rgrid), dim3(t >= 128 ? 128 : 64), 0, (const float *)x->dptr, (float *)y->dptr, rows, t);
     }
     FA_LAUNCH_CHECK(ctx, "rel_shift_b");
   }
@@ -1188,7 +1217,7 @@ extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, co
     {
       LaunchScope ls(ctx, "bmm_qk_t1");
       auto kern = U == 8 ? k_bmm_qk_t1<8> : k_bmm_qk_t1<4>;
-      kern<<<dim3(strips, gy, W), 256, 0, ctx->stream>>>((const float *)q->dptr, (const float *)b->dptr,
+      fa_launch_dep(ctx, kern, dim3(dim3(strips, gy, W)), dim3(256), 0, (const float *)q->dptr, (const float *)b->dptr,
                                                         qb ? (const float *)qb->dptr : nullptr, (float *)y->dptr, Tb, H,
                                                         HD, b_shared, lph);
     }
@@ -1204,7 +1233,7 @@ extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, co
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmQK: batch too large");
     {
       LaunchScope ls(ctx, "bmm_qk");
-      k_bmm_qk<<<grid, 256, 0, ctx->stream>>>((const float *)q->dptr, (const float *)b->dptr,
+      fa_launch_dep(ctx, k_bmm_qk, dim3(grid), dim3(256), 0, (const float *)q->dptr, (const float *)b->dptr,
                                               qb ? (const float *)qb->dptr : nullptr, (float *)y->dptr, T, Tb, H, HD,
                                               b_shared);
     }
@@ -1240,7 +1269,7 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
       }
       static const int unroll = getenv("FA_T1_UNROLL") ? atoi(getenv("FA_T1_UNROLL")) : 8;
       auto kern = (Tk >= 256 && unroll == 8) ? k_bmm_pv_t1<8> : k_bmm_pv_t1<4>;
-      kern<<<dim3(ceil_div(H * HD, 128), 1, W), 256, 0, ctx->stream>>>((const float *)p->dptr, (const float *)v->dptr,
+      fa_launch_dep(ctx, kern, dim3(dim3(ceil_div(H * HD, 128), 1, W)), dim3(256), 0, (const float *)p->dptr, (const float *)v->dptr,
                                                                       (float *)y->dptr, y16, lo_off, Tk, H, HD);
     }
     FA_LAUNCH_CHECK(ctx, "bmm_pv_t1");
@@ -1258,7 +1287,7 @@ extern "C" int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, in
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmPV: batch too large");
     {
       LaunchScope ls(ctx, "bmm_pv");
-      k_bmm_pv<<<grid, 256, 0, ctx->stream>>>((const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, Tq, Tk, H, HD);
+      fa_launch_dep(ctx, k_bmm_pv, dim3(grid), dim3(256), 0, (const float *)p->dptr, (const float *)v->dptr, (float *)y->dptr, Tq, Tk, H, HD);
     }
     FA_LAUNCH_CHECK(ctx, "bmm_pv");
   }
@@ -1293,7 +1322,7 @@ static int conv1d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
   if (groups == cin && cout == cin && stride == 1 && Lout == L && cout <= 65535) {
     {
       LaunchScope ls(ctx, "dwconv1d");
-      k_dwconv1d<<<dim3(ceil_div(L, 256), cout), 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
+      fa_launch_dep(ctx, k_dwconv1d, dim3(dim3(ceil_div(L, 256), cout)), dim3(256), 0, (const float *)x->dptr, (const float *)w->dptr,
                                                                        bias ? (const float *)bias->dptr : nullptr,
                                                                        (float *)y->dptr, L, Lw, k, pad_left, dilation, act);
     }
@@ -1303,7 +1332,7 @@ static int conv1d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
   }
   {
     LaunchScope ls(ctx, windows > 1 ? "conv1d_windows" : "conv1d");
-    k_conv1d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
+    fa_launch_dep(ctx, k_conv1d, dim3(grid1d(ctx, n, 128)), dim3(128), 0, (const float *)x->dptr, (const float *)w->dptr,
                                                            bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr,
                                                            cout, cin, L, Lout, Lw, k, stride, pad_left, dilation, groups, act);
   }
@@ -1364,10 +1393,10 @@ extern "C" int fa_glu_dwconv_tm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor
       const float *bp = bias ? (const float *)bias->dptr : nullptr;
       const int chunks = ceil_div(Tw, 16);
       if (k == 9 && (long long)windows * chunks <= 65535)
-        k_glu_dwconv_tm_k<9><<<dim3(ceil_div(D, 256), windows * chunks), 256, 0, ctx->stream>>>(
+        fa_launch_dep(ctx, k_glu_dwconv_tm_k<9>, dim3(dim3(ceil_div(D, 256), windows * chunks)), dim3(256), 0, 
             (const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr, y16, rows, Tw, D, pad_left, act, chunks);
       else
-        k_glu_dwconv_tm<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr,
+        fa_launch_dep(ctx, k_glu_dwconv_tm, dim3(grid), dim3(256), 0, (const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr,
                                                        y16, rows, Tw, D, k, pad_left, act);
     }
     FA_LAUNCH_CHECK(ctx, "glu_dwconv_tm");
@@ -1458,7 +1487,7 @@ static int conv2d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
               windows);
     {
       LaunchScope ls(ctx, "conv2d_c1_3x3");
-      k_conv2d_c1_3x3<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (const float *)w->dptr,
+      fa_launch_dep(ctx, k_conv2d_c1_3x3, dim3(grid), dim3(256), 0, (const float *)x->dptr, (const float *)w->dptr,
                                                      bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr, cout, h,
                                                      w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act, xstride, ystride);
     }
@@ -1469,7 +1498,7 @@ static int conv2d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
   if (groups == cin && cout == cin && kh == 3 && kw == 3 && cout <= 65535) {
     {
       LaunchScope ls(ctx, "dwconv2d_3x3");
-      k_dwconv2d_3x3<<<dim3(ceil_div(Ho * Wo, 256), cout, windows), 256, 0, ctx->stream>>>(
+      fa_launch_dep(ctx, k_dwconv2d_3x3, dim3(dim3(ceil_div(Ho * Wo, 256), cout, windows)), dim3(256), 0, 
           (const float *)x->dptr, (const float *)w->dptr, bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr, h,
           w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act, xstride, ystride);
     }
@@ -1479,7 +1508,7 @@ static int conv2d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
   }
   for (int b = 0; b < windows; b++) {  // general geometry: one launch per window
     LaunchScope ls(ctx, "conv2d");
-    k_conv2d<<<grid1d(ctx, n, 128), 128, 0, ctx->stream>>>((const float *)x->dptr + b * xstride, (const float *)w->dptr,
+    fa_launch_dep(ctx, k_conv2d, dim3(grid1d(ctx, n, 128)), dim3(128), 0, (const float *)x->dptr + b * xstride, (const float *)w->dptr,
                                                            bias ? (const float *)bias->dptr : nullptr,
                                                            (float *)y->dptr + b * ystride, cout, cin, h, w_, kh, kw, stride_h,
                                                            stride_w, pad_top, pad_left, Ho, Wo, groups, act);
@@ -1517,7 +1546,7 @@ extern "C" int fa_embed_rows(fa_ctx *ctx, const fa_tensor *table, const fa_tenso
   if (idx->rows) {
     {
       LaunchScope ls(ctx, "embed_rows");
-      k_embed_rows<<<idx->rows, 256, 0, ctx->stream>>>((const float *)table->dptr, (const float *)pos->dptr,
+      fa_launch_dep(ctx, k_embed_rows, dim3(idx->rows), dim3(256), 0, (const float *)table->dptr, (const float *)pos->dptr,
                                                        (const float *)idx->dptr, idx->cols, table->rows, table->cols, n,
                                                        (float *)y->dptr, ctx->dev_status);
     }
@@ -1539,7 +1568,7 @@ extern "C" int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, int ncols, fa_ten
     int grid = x->rows < ctx->sm_count * 8 ? x->rows : ctx->sm_count * 8;
     {
       LaunchScope ls(ctx, "argmax_rows");
-      k_argmax_rows<<<grid, 256, 0, ctx->stream>>>((const float *)x->dptr, (float *)y->dptr, x->rows, x->cols, ncols);
+      fa_launch_dep(ctx, k_argmax_rows, dim3(grid), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, x->rows, x->cols, ncols);
     }
     FA_LAUNCH_CHECK(ctx, "argmax_rows");
   }

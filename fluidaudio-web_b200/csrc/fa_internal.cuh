@@ -91,6 +91,7 @@ struct fa_ctx {
   unsigned long long launches = 0;
   // options
   int int8_limbs = 2;
+  int pdl = 1;             // programmatic dependent launch between the library's kernels (see fa_launch_dep)
   int nbits_fused = 0;     // 1: int4 products on the tensor cores unpack nibbles in shared memory (0: f16 copy, faster today)
   int gemv_rows = 4;       // products with at most this many rows run on the CUDA-core GEMV kernels (0 = never)
   int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
@@ -186,6 +187,33 @@ struct LaunchScope {
     cudaError_t e__ = cudaGetLastError();                                                    \
     if (e__ != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch %s: %s", label, cudaGetErrorString(e__)); \
   } while (0)
+
+// ---- programmatic dependent launch -----------------------------------------------------
+// Chains of short kernels (a decode step is ~120 of them) lose 1.5-2.5 us per boundary to launch latency and
+// kernel prologues.  Kernels launched through fa_launch_dep carry the programmatic-stream-serialization
+// attribute: the grid may be scheduled while its predecessor is still running.  Such a kernel MUST execute
+// fa_grid_dep_sync() before it reads or writes anything its predecessors touch: the call first lets the NEXT
+// grid in the stream be scheduled early in turn, then waits until every earlier grid has completed and its
+// writes are visible.  Without the attribute (option "pdl" = 0, or a plain <<<>>> launch) the call is a no-op.
+__device__ __forceinline__ void fa_grid_dep_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t fa_launch_dep(fa_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args &&...args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---- device helpers ----------------------------------------------------------------
 

@@ -67,7 +67,9 @@ const char *fa_last_error(fa_ctx *ctx);
  * f32 / exact-integer activations; 0 sends them to the tensor-core kernel), "nbits_fused" (0/1, default 0:
  * 1 = int4 products on the tensor cores stream 4-bit tiles and unpack them in shared memory inside the
  * kernel; 0 = through a one-time dequantised f16 copy of the weights, which is the faster of the two
- * today). */
+ * today), "pdl" (0/1, default 1: the library's kernels are chained with programmatic dependent launch, so a
+ * kernel's scheduling and prologue overlap its predecessor's tail; every such kernel waits for its
+ * predecessors before touching their data; 0 = plain stream order). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);
