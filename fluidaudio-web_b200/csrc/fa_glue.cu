@@ -601,26 +601,75 @@ __global__ void __launch_bounds__(256) k_dwconv2d_3x3(const float *__restrict__ 
                                                       int sh, int sw, int pt, int pl, int Ho, int Wo, int act,
                                                       size_t xstride, size_t ystride) {
   fa_grid_dep_sync();
-  const int c = blockIdx.y;
-  const unsigned plane = (unsigned)Ho * Wo, pos = blockIdx.x * 256 + threadIdx.x;
-  if (pos >= plane) return;
+  // One thread = 4 consecutive outputs of one row of one channel (Wo4 = ceil(Wo/4) groups per row): the three input
+  // rows it needs are loaded once, all loads issued before any arithmetic (addresses clamped, taps outside the image
+  // zeroed afterwards), and the four results leave as one 16-byte store when the row allows it.
+  const int c = blockIdx.y, Wo4 = (Wo + 3) >> 2;
+  const unsigned grp = blockIdx.x * 256 + threadIdx.x;
+  if (grp >= (unsigned)(Ho * Wo4)) return;
   x += (size_t)blockIdx.z * xstride;  // blockIdx.z = window
   y += (size_t)blockIdx.z * ystride;
-  const int ho = (int)(pos / (unsigned)Wo), wo = (int)(pos % (unsigned)Wo);
+  const int ho = (int)(grp / (unsigned)Wo4), wo0 = (int)(grp % (unsigned)Wo4) * 4;
   const float *xp = x + (size_t)c * h * W;
-  const float *wp = w + (size_t)c * 9;
-  float acc = bias ? bias[c] : 0.f;
+  float wk[9];
 #pragma unroll
-  for (int a = 0; a < 3; a++) {
-    const int hi = ho * sh + a - pt;
-    if (hi < 0 || hi >= h) continue;
+  for (int t = 0; t < 9; t++) wk[t] = __ldg(w + (size_t)c * 9 + t);
+  const float b = bias ? bias[c] : 0.f;
+  if (sw == 2) {
+    float in[3][9];  // input columns 2*wo0 - pl .. + 8
 #pragma unroll
-    for (int b = 0; b < 3; b++) {
-      const int wi = wo * sw + b - pl;
-      if (wi >= 0 && wi < W) acc = fmaf(xp[(size_t)hi * W + wi], __ldg(wp + a * 3 + b), acc);
+    for (int a = 0; a < 3; a++) {
+      const int hi = ho * sh + a - pt, hc = min(max(hi, 0), h - 1);
+#pragma unroll
+      for (int j = 0; j < 9; j++) {
+        const int wi = wo0 * 2 + j - pl, wc = min(max(wi, 0), W - 1);
+        in[a][j] = xp[(size_t)hc * W + wc];
+      }
     }
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+      const int hi = ho * sh + a - pt;
+#pragma unroll
+      for (int j = 0; j < 9; j++) {
+        const int wi = wo0 * 2 + j - pl;
+        if (hi < 0 || hi >= h || wi < 0 || wi >= W) in[a][j] = 0.f;
+      }
+    }
+    float o[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      float acc = b;
+#pragma unroll
+      for (int a = 0; a < 3; a++)
+#pragma unroll
+        for (int bb = 0; bb < 3; bb++) acc = fmaf(in[a][2 * q + bb], wk[a * 3 + bb], acc);
+      o[q] = fa_actf(acc, act);
+    }
+    float *dst = y + (size_t)c * Ho * Wo + (size_t)ho * Wo + wo0;
+    if ((Wo & 3) == 0 && ((ystride | ((size_t)Ho * Wo)) & 3) == 0 && (((uintptr_t)y) & 15) == 0) {
+      *(float4 *)dst = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; q++)
+        if (wo0 + q < Wo) dst[q] = o[q];
+    }
+    return;
   }
-  y[(size_t)c * plane + pos] = fa_actf(acc, act);
+  for (int q = 0; q < 4 && wo0 + q < Wo; q++) {  // other strides: one output at a time
+    const int wo = wo0 + q;
+    float acc = b;
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+      const int hi = ho * sh + a - pt;
+      if (hi < 0 || hi >= h) continue;
+#pragma unroll
+      for (int bb = 0; bb < 3; bb++) {
+        const int wi = wo * sw + bb - pl;
+        if (wi >= 0 && wi < W) acc = fmaf(xp[(size_t)hi * W + wi], wk[a * 3 + bb], acc);
+      }
+    }
+    y[(size_t)c * Ho * Wo + (size_t)ho * Wo + wo] = fa_actf(acc, act);
+  }
 }
 
 // The conformer conv module between its two pointwise projections, in the time-major layout the
@@ -744,6 +793,9 @@ __global__ void __launch_bounds__(256) k_conv2d_c1_3x3(const float *__restrict__
                                                        int h, int W, int sh, int sw, int pt, int pl, int Ho, int Wo,
                                                        int act, size_t xstride, size_t ystride) {
   fa_grid_dep_sync();
+  // One thread = 4 consecutive output positions of one row, all 32 channels of its channel group: the 3 x 9 input
+  // patch is loaded once, each channel's 9 weights are read from shared memory once per 4 outputs (read per output
+  // they made the kernel load/store-unit bound), and every channel's 4 results leave as one 16-byte store.
   __shared__ float ws[32][9], bs[32];
   const int co0 = blockIdx.y * 32;
   x += (size_t)blockIdx.z * xstride;  // blockIdx.z = window
@@ -755,23 +807,50 @@ __global__ void __launch_bounds__(256) k_conv2d_c1_3x3(const float *__restrict__
   if (threadIdx.x < 32) bs[threadIdx.x] = (bias && co0 + threadIdx.x < cout) ? bias[co0 + threadIdx.x] : 0.f;
   __syncthreads();
   const unsigned plane = (unsigned)Ho * (unsigned)Wo;
-  for (unsigned pos = blockIdx.x * 256 + threadIdx.x; pos < plane; pos += gridDim.x * 256) {
-    const int ho = (int)(pos / (unsigned)Wo), wo = (int)(pos % (unsigned)Wo);
-    float in[9];
+  const int Wo4 = (Wo + 3) >> 2;
+  const unsigned groups = (unsigned)Ho * (unsigned)Wo4;
+  const bool vec = (Wo & 3) == 0 && ((ystride | plane) & 3) == 0 && (((uintptr_t)y) & 15) == 0;
+  for (unsigned grp = blockIdx.x * 256 + threadIdx.x; grp < groups; grp += gridDim.x * 256) {
+    const int ho = (int)(grp / (unsigned)Wo4), wo0 = (int)(grp % (unsigned)Wo4) * 4;
+    float in[3][4 * 2 + 1 + 6];  // columns wo0*sw - pl .. for 4 outputs; sized for sw <= 3
+    const int ncol = 3 * sw + 3;
 #pragma unroll
-    for (int a = 0; a < 3; a++)
+    for (int a = 0; a < 3; a++) {
+      const int hi = ho * sh + a - pt;
 #pragma unroll
-      for (int b = 0; b < 3; b++) {
-        const int hi = ho * sh + a - pt, wi = wo * sw + b - pl;
-        in[a * 3 + b] = (hi >= 0 && hi < h && wi >= 0 && wi < W) ? x[(size_t)hi * W + wi] : 0.f;
+      for (int j = 0; j < 15; j++) {
+        const int wi = wo0 * sw + j - pl;
+        in[a][j] = (j < ncol && hi >= 0 && hi < h && wi >= 0 && wi < W) ? x[(size_t)hi * W + wi] : 0.f;
       }
-#pragma unroll 4
+    }
+#pragma unroll 2
     for (int c = 0; c < 32; c++) {
       if (co0 + c >= cout) break;
-      float acc = bs[c];
+      float wk[9];
 #pragma unroll
-      for (int t = 0; t < 9; t++) acc = fmaf(in[t], ws[c][t], acc);
-      y[(size_t)(co0 + c) * plane + pos] = fa_actf(acc, act);
+      for (int t = 0; t < 9; t++) wk[t] = ws[c][t];
+      float o[4];
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        float acc = bs[c];
+#pragma unroll
+        for (int a = 0; a < 3; a++)
+#pragma unroll
+          for (int bb = 0; bb < 3; bb++) {
+            // column of tap bb of output q: q*sw + bb (sw is 1, 2 or 3 for the specialised path)
+            const float v = sw == 2 ? in[a][2 * q + bb] : (sw == 1 ? in[a][q + bb] : in[a][3 * q + bb]);
+            acc = fmaf(v, wk[a * 3 + bb], acc);
+          }
+        o[q] = fa_actf(acc, act);
+      }
+      float *dst = y + (size_t)(co0 + c) * plane + (size_t)ho * Wo + wo0;
+      if (vec) {
+        *(float4 *)dst = make_float4(o[0], o[1], o[2], o[3]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+          if (wo0 + q < Wo) dst[q] = o[q];
+      }
     }
   }
 }
@@ -1481,10 +1560,10 @@ static int conv2d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
     return FA_OK;
   }
   FA_REQUIRE(ctx, n < (1ull << 31), "conv2d: output too large");
-  if (cin == 1 && groups == 1 && kh == 3 && kw == 3) {
-    const unsigned plane = (unsigned)Ho * Wo;
-    dim3 grid((plane + 255) / 256 < (unsigned)ctx->sm_count * 4 ? (plane + 255) / 256 : ctx->sm_count * 4, ceil_div(cout, 32),
-              windows);
+  if (cin == 1 && groups == 1 && kh == 3 && kw == 3 && stride_w <= 3) {
+    const unsigned groups4 = (unsigned)Ho * ((Wo + 3) / 4);  // threads: 4 output positions each
+    dim3 grid((groups4 + 255) / 256 < (unsigned)ctx->sm_count * 4 ? (groups4 + 255) / 256 : ctx->sm_count * 4,
+              ceil_div(cout, 32), windows);
     {
       LaunchScope ls(ctx, "conv2d_c1_3x3");
       fa_launch_dep(ctx, k_conv2d_c1_3x3, dim3(grid), dim3(256), 0, (const float *)x->dptr, (const float *)w->dptr,
@@ -1498,7 +1577,7 @@ static int conv2d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
   if (groups == cin && cout == cin && kh == 3 && kw == 3 && cout <= 65535) {
     {
       LaunchScope ls(ctx, "dwconv2d_3x3");
-      fa_launch_dep(ctx, k_dwconv2d_3x3, dim3(dim3(ceil_div(Ho * Wo, 256), cout, windows)), dim3(256), 0, 
+      fa_launch_dep(ctx, k_dwconv2d_3x3, dim3(ceil_div(Ho * ((Wo + 3) / 4), 256), cout, windows), dim3(256), 0,
           (const float *)x->dptr, (const float *)w->dptr, bias ? (const float *)bias->dptr : nullptr, (float *)y->dptr, h,
           w_, stride_h, stride_w, pad_top, pad_left, Ho, Wo, act, xstride, ystride);
     }

@@ -1,8 +1,15 @@
 /*
  * CPU oracle for the quantized matrix-product path of fluidaudio-web.
  *
- * TEST INFRASTRUCTURE ONLY. This file is the checker the CUDA backend is judged
+ * TEST INFRASTRUCTURE ONLY. This file is the checker the CUDA backend is compared
  * against; nothing in the shipped package links, imports or calls it.
+ *
+ * Pinning status: the reference holds no golden output vectors for this path and
+ * cannot be executed here (no Node / wasm runtime / Rust toolchain), so this port is
+ * pinned to what the reference's own gates contain - the closed-form expectations of
+ * scripts/wasm-verify.mjs and the seeded cases of scripts/backend-conformance.mjs,
+ * both restated in tests/test_oracle.py - and NOT to outputs produced by the
+ * reference: to that extent, parity unpinned.
  *
  * It restates, operation by operation and in the same order, the reference's own
  * CPU implementation of the path:

@@ -188,7 +188,7 @@ def test_int4_partial_block_and_random_zero_points(ctx):
 # ---- size-independent properties at full size ------------------------------------------------------
 
 def test_int8_full_size_linearity_and_exactness(ctx):
-    """BASELINE config 1 (512x1024x4096): y(a1+a2) = y(a1)+y(a2) holds exactly for the int32
+    """The int8 benchmark shape (512x1024x4096): y(a1+a2) = y(a1)+y(a2) holds exactly for the int32
     accumulators, and zero activations give exactly the bias."""
     rng = np.random.default_rng(0)
     M, K, N = 512, 1024, 4096
