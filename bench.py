@@ -714,6 +714,12 @@ class F16GemmNSharded:
             self.A[K] = ctx.upload(buf, self.M, K)
         self.units_per_step = len(self.KNs)
         self.flops_per_step = sum(2.0 * self.M * K * N for K, N in self.KNs)
+        # FA_NSHARD_FUSED=0 selects the NCCL all-gather + unshard form instead of the fused peer-store epilogue
+        self.fused = os.environ.get("FA_NSHARD_FUSED", "1") != "0"
+        self.res = {}
+        if world > 1 and self.fused:
+            self.res = {kn: sharding.ScatterResult(ctx, self.M, kn[1]) for kn in self.KNs}
+            self.name = "f16_gemm_m16384_n_sharded_fused_peer_store_allgather"
 
     def _product(self, ctx, a, kn):
         if self.world == 1:
@@ -721,6 +727,12 @@ class F16GemmNSharded:
         return self.sh.matmul_n_sharded(ctx, a, self.W[kn])
 
     def step_device(self, ctx):
+        if self.world > 1 and self.fused:
+            # the all-gather rides the epilogue: peer stores into every rank's result, then one barrier
+            for kn in self.KNs:
+                self.sh.matmul_n_sharded_scatter(ctx, self.A[kn[0]], self.W[kn], self.res[kn])
+            self.sh.stream_barrier(ctx)
+            return
         h = ctx.pushArena()
         self.sh.matmul_n_sharded_many(ctx, [(self.A[kn[0]], self.W[kn]) for kn in self.KNs])
         ctx.popArena(h)

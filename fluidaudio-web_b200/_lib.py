@@ -86,6 +86,10 @@ SIGNATURES = {
     "fa_argmax_rows": [P, P, I, PP],
     "fa_embed_rows": [P, P, P, P, I, PP],
     "fa_unshard_cols": [P, P, I, PP],
+    "fa_ipc_export": [P, P, P],
+    "fa_ipc_open": [P, P, PP],
+    "fa_ipc_close": [P, P],
+    "fa_matmul_scatter": [P, P, P, P, I, P, I, I, I],
     "fa_profile_start": [P, I],
     "fa_profile_end": [P, C.POINTER(ProfileEntry), I, IP],
 }

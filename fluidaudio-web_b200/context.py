@@ -406,6 +406,27 @@ class CudaContext:
         """[world*M, Ns] column shards stacked along rows -> the row-major [M, world*Ns] product."""
         return self._op(self._lib.fa_unshard_cols, gathered.h, world)
 
+    # -- peer mappings and the product with a fused all-gather (one process per GPU) ----------------------
+    def ipcExport(self, t: Tensor) -> bytes:
+        buf = (C.c_ubyte * 64)()
+        self._check(self._lib.fa_ipc_export(self._h, t.h, buf))
+        return bytes(buf)
+
+    def ipcOpen(self, handle: bytes) -> int:
+        buf = (C.c_ubyte * 64).from_buffer_copy(handle)
+        out = C.c_void_p()
+        self._check(self._lib.fa_ipc_open(self._h, buf, C.byref(out)))
+        return out.value
+
+    def ipcClose(self, ptr: int) -> None:
+        self._check(self._lib.fa_ipc_close(self._h, C.c_void_p(ptr)))
+
+    def matmulScatter(self, a: Tensor, b_shard: Tensor, out_ptrs, ldc: int, col0: int, *, bias=None, act="none") -> None:
+        """This rank's block of output columns written into every buffer of `out_ptrs` (own first, then the
+        peers' IPC mappings) by the product's own epilogue."""
+        arr = (C.c_void_p * len(out_ptrs))(*[C.c_void_p(int(p)) for p in out_ptrs])
+        self._check(self._lib.fa_matmul_scatter(self._h, a.h, b_shard.h, self._h_of(bias), ACT[act], arr, len(out_ptrs), ldc, col0))
+
     def embedRows(self, table: Tensor, pos: Tensor, idx: Tensor, n: int) -> Tensor:
         """[S, D] = table[id_s] + pos[n], ids read from column 0 of `idx` on the device (so a greedy
         decode needs no host round trip between tokens)."""

@@ -612,6 +612,37 @@ extern "C" int fa_reshape_view(fa_ctx *ctx, fa_tensor *t, int rows, int cols, fa
   return FA_OK;
 }
 
+// ---- peer mappings (one process per GPU) --------------------------------------------------------
+// Every pool block is its own device allocation, so a tensor's storage can be exported as a CUDA IPC handle.
+
+extern "C" int fa_ipc_export(fa_ctx *ctx, const fa_tensor *t, unsigned char handle_out[64]) {
+  if (!ctx || !handle_out) return fa_fail(ctx, FA_ERR_INVALID, "ipcExport: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, t) && !t->view, "ipcExport: unknown tensor handle or a view");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  FA_CHECK_CUDA(ctx, cudaIpcGetMemHandle(&h, t->dptr));
+  memcpy(handle_out, &h, 64);
+  return FA_OK;
+}
+
+extern "C" int fa_ipc_open(fa_ctx *ctx, const unsigned char handle[64], void **dev_ptr_out) {
+  if (!ctx || !handle || !dev_ptr_out) return fa_fail(ctx, FA_ERR_INVALID, "ipcOpen: NULL argument");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  FA_CHECK_CUDA(ctx, cudaIpcOpenMemHandle(dev_ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+  return FA_OK;
+}
+
+extern "C" int fa_ipc_close(fa_ctx *ctx, void *dev_ptr) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "ipcClose: NULL context");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  FA_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  FA_CHECK_CUDA(ctx, cudaIpcCloseMemHandle(dev_ptr));
+  return FA_OK;
+}
+
 // ---- batching -------------------------------------------------------------------------------
 
 extern "C" int fa_begin_batch(fa_ctx *ctx) {

@@ -70,6 +70,11 @@ struct TcParams {
   __half *out16;      // optional packed f16 shadow of the result (see TcEpilogue), or nullptr
   int o16_rows, o16_row_hi, o16_col_lo;
   float *out;         // [M][N] f32 (or int32 when raw_i32)
+  // N-sharded products: besides `out`, every finished tile is also stored at the same [row][column] of up to 7
+  // more result buffers - the other GPUs' copies of the full product, reached by plain stores over NVLink
+  // (peer pointers), so the all-gather of output columns happens inside the epilogue, tile by tile.
+  float *peer_out[7];
+  int n_peers;
   const float *rowscale, *colscale, *bias, *add, *rowbias;
   int act;
   // int4 variant (KIND 2): block-major scales [nblk][N] and zero-points [nblk][N] (one per byte)
@@ -137,7 +142,7 @@ __device__ __forceinline__ void act16(float (&v)[16], int act) {
 
 // One tile's epilogue for one warp: TMEM lanes [32*quad, 32*quad+32) = output columns n0 + 32*quad + lane,
 // column chunks c = 16*half, 16*half + 32, ... = output rows m0 + c .. m0 + c + 15.
-template <int KIND>
+template <int KIND, bool PEERS = false>
 __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_addr, int n0, int m0, int quad, int lane,
                                               int half, float *outb, int r16, int c16, uint32_t partial) {
   const int n = n0 + quad * 32 + lane;
@@ -232,11 +237,20 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
         for (int j = 0; j < 16; j++)
           if (m0 + c + j < p.M) orow[(size_t)j * p.ldc] = v[j] + ad[j];
       }
+      if (PEERS)
+      for (int pi = 0; pi < p.n_peers; pi++) {  // the same tile into the peers' result buffers (batches == 1)
+        float *prow = p.peer_out[pi] + (size_t)(m0 + c) * p.ldc + n;
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if (full_rows || m0 + c + j < p.M) prow[(size_t)j * p.ldc] = v[j] + ad[j];
+      }
     }
   }
 }
 
-// KIND 0: f16 weights, 1: int8 weights, 2: int4 (MatMulNBits) weights.  KIND 2 is the f16 pipeline with one more
+// KIND 0: f16 weights, 1: int8 weights, 2: int4 (MatMulNBits) weights, 3: f16 weights with the epilogue also storing
+// into peer GPUs' result buffers (TcParams::peer_out; a separate instantiation so the common epilogue stays lean -
+// as a run-time loop it cost the plain f16 product 5 %).  KIND 2 is the f16 pipeline with one more
 // stage in front of the MMA: TMA brings the RAW nibbles of a K chunk (128 rows x 32 bytes, the reference's
 // layout as uploaded) next to the activation tile, eight extra warps unpack them in shared memory into the
 // swizzled f16 weights tile - (q - zp) * scale per 32-weight block, two f16 lanes per instruction - and hand the
@@ -246,7 +260,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
 template <int KIND>
 __global__ void __launch_bounds__(KIND == 2 ? kThreadsNbits : kThreads, 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
-  constexpr int MK = KIND == 2 ? 0 : KIND;  // MMA kind and epilogue arithmetic
+  constexpr int MK = KIND >= 2 ? 0 : KIND;  // MMA kind and epilogue arithmetic (KIND 3: f16 with peer stores)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B | raw nibble tile 4 KB for KIND 2), barriers,
   // split-K partial tile
@@ -532,7 +546,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       tc_fence_after();
       if (threadIdx.x == 64) TC_TRACE(129);
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<MK>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial);
+      epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial);
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -1041,6 +1055,8 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.batches = ep.batches;
   p.w_batch_mod = ep.w_batch_mod;
   p.a_shared = ep.a_shared ? 1 : 0;
+  p.n_peers = ep.n_peers;
+  for (int i = 0; i < 7; i++) p.peer_out[i] = i < ep.n_peers ? ep.peer_out[i] : nullptr;
   p.o_div = ep.o_div > 0 ? ep.o_div : 1;
   p.ldc = ep.ldc > 0 ? ep.ldc : N;
   p.o_hi = ep.o_hi;
@@ -1054,7 +1070,8 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   // every SM streams weights.  Each split keeps at least 2 chunks.
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
-  if (!raw_i32 && !ep.out16 && p.batches == 1 && p.tiles_m == 1 && p.MT <= kSplitMaxMT && num_tiles * 2 <= ctx->sm_count) {
+  if (!raw_i32 && !ep.out16 && ep.n_peers == 0 && p.batches == 1 && p.tiles_m == 1 && p.MT <= kSplitMaxMT &&
+      num_tiles * 2 <= ctx->sm_count) {
     int s = ctx->sm_count / num_tiles;
     if (s > 8) s = 8;
     while (s > 1 && p.num_kb / s < 2) s--;
@@ -1185,7 +1202,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     cfg.gridDim = dim3(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);  // persistent: one CTA per SM
   }
   {
-    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : "tc_gemm_nbits"));
+    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : (KIND == 2 ? "tc_gemm_nbits" : "tc_gemm_f16_scatter")));
     cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, p);
     if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm: %s", cudaGetErrorString(e));
   }
@@ -1302,6 +1319,7 @@ int fa_prep_a_f16_perm8(fa_ctx *ctx, const float *a, int M, int K, __half *out) 
 
 int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, float *c, int M, int N, int K,
                    const TcEpilogue &ep) {
+  if (ep.n_peers > 0) return launch_tc<3>(ctx, w_packed, a_packed, ep.a_hilo ? 2 : 1, c, false, M, N, K, ep);
   return launch_tc<0>(ctx, w_packed, a_packed, ep.a_hilo ? 2 : 1, c, false, M, N, K, ep);
 }
 

@@ -263,6 +263,8 @@ struct TcEpilogue {
   int act = 0;
   bool a_hilo = false;
   bool a_shared = false;            // batched mode: all batches share the row operand
+  float *peer_out[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // see TcParams::peer_out
+  int n_peers = 0;
   const float *nb_scales = nullptr;  // int4 variant: per-block scales, packed zero-points, blocks per row
   const uint8_t *nb_zp = nullptr;
   int nblk = 0;              // f16 kind: the row operand is two planes (value, rounding residue)

@@ -199,6 +199,47 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
   return FA_OK;
 }
 
+// N-sharded product with the all-gather fused into the epilogue: this rank's block of output columns
+// C[:, col0 : col0 + Ns] = act(A @ B_shard + bias_shard) is written at its place in EVERY buffer of `outs`
+// (n_outs <= 8 device pointers to [M][ldc] f32 results: this GPU's own and, through IPC mappings, the other
+// ranks'), tile by tile as the accumulators finish.  The caller orders the ranks afterwards (a stream-ordered
+// barrier) before anyone reads a result.
+extern "C" int fa_matmul_scatter(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act,
+                                 void *const *outs, int n_outs, int ldc, int col0) {
+  if (!ctx || !outs) return fa_fail(ctx, FA_ERR_INVALID, "matmulScatter: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, a) && fa_valid(ctx, b), "matmulScatter: unknown tensor handle");
+  const int M = a->rows, K = a->cols, N = b->cols;
+  FA_REQUIRE(ctx, b->rows == K, "matmulScatter: A is [%d,%d] but B is [%d,%d]", M, K, b->rows, N);
+  FA_REQUIRE(ctx, n_outs >= 1 && n_outs <= 8, "matmulScatter: %d result buffers (1..8)", n_outs);
+  FA_REQUIRE(ctx, col0 >= 0 && col0 + N <= ldc, "matmulScatter: columns [%d,%d) do not fit a row of %d", col0, col0 + N, ldc);
+  FA_REQUIRE(ctx, act >= 0 && act <= 5, "matmulScatter: unknown activation code %d", act);
+  FA_REQUIRE(ctx, b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K) && M > ctx->f16_hilo_rows,
+             "matmulScatter: needs f16-storage weights and a tensor-core sized product with more than %d rows",
+             ctx->f16_hilo_rows);
+  for (int i = 0; i < n_outs; i++) FA_REQUIRE(ctx, outs[i] != nullptr, "matmulScatter: result buffer %d is NULL", i);
+  if (bias) FA_TRY(check_vec(ctx, bias, N, "matmulScatter: bias"));
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  const float *ap = nullptr;
+  fa_tensor *atmp = nullptr;
+  FA_TRY(fa_as_f32(ctx, a, &ap, &atmp));
+  Scratch sa(ctx);
+  const __half *a16 = nullptr;
+  bool hilo = false;
+  int rc = ensure_bt_f16(ctx, b);
+  if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16, &hilo);
+  if (rc == FA_OK) {
+    TcEpilogue ep;
+    ep.bias = bias ? (const float *)bias->dptr : nullptr;
+    ep.act = act;
+    ep.ldc = ldc;
+    ep.n_peers = n_outs - 1;
+    for (int i = 1; i < n_outs; i++) ep.peer_out[i - 1] = (float *)outs[i] + col0;
+    rc = fa_tc_gemm_f16(ctx, a16, (const __half *)b->bt_f16, (float *)outs[0] + col0, M, N, K, ep);
+  }
+  if (atmp) fa_free_tensor(ctx, atmp);
+  return rc;
+}
+
 extern "C" int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, const fa_tensor *scale, int N, int K,
                               const fa_tensor *bias, int act, fa_tensor **out) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmulInt8: NULL argument");

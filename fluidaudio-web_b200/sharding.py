@@ -126,6 +126,57 @@ def matmul_n_sharded_many(ctx, pairs, group=None):
     return outs
 
 
+class ScatterResult:
+    """A full [M, N] f32 result buffer on every rank, each mapped into every other rank (CUDA IPC), for
+    products whose epilogue stores its tiles straight into all of them (matmul_n_sharded_scatter)."""
+
+    def __init__(self, ctx, M: int, N: int, group=None):
+        import torch.distributed as dist
+
+        self.ctx, self.M, self.N, self.group = ctx, M, N, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.local = ctx.pin(ctx.alloc(M, N))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, ctx.ipcExport(self.local), group=group)
+        own = ctx.devicePtr(self.local)
+        self._peers = {r: ctx.ipcOpen(h) for r, h in enumerate(handles) if r != self.rank}
+        self.ptrs = [own] + [self._peers[r] for r in sorted(self._peers)]  # own buffer first
+
+    def close(self):
+        import torch.distributed as dist
+
+        self.ctx.sync()
+        dist.barrier(group=self.group)  # nobody unmaps while a peer may still be writing
+        for p in self._peers.values():
+            self.ctx.ipcClose(p)
+        self._peers = {}
+        dist.barrier(group=self.group)
+        self.ctx.freeTensor(self.local)
+
+
+def stream_barrier(ctx, group=None):
+    """Orders the ranks on the context's stream: work enqueued after it starts only when every rank's work
+    enqueued before it has finished (a one-element NCCL all-reduce on that stream)."""
+    import torch
+    import torch.distributed as dist
+
+    flag = getattr(ctx, "_barrier_flag", None)
+    if flag is None:
+        flag = ctx._barrier_flag = torch.zeros(1, device=f"cuda:{ctx.device}")
+    with torch.cuda.stream(torch.cuda.ExternalStream(ctx.stream(), device=ctx.device)):
+        dist.all_reduce(flag, group=group)
+
+
+def matmul_n_sharded_scatter(ctx, a, w_shard, res: ScatterResult, opts=None):
+    """N-sharded product with the all-gather inside the GEMM: the epilogue of this rank's column block stores
+    each finished tile into every rank's result buffer over NVLink (plain peer stores).  Call stream_barrier
+    afterwards, before any rank reads `res.local`, and again before the next product reuses `res`."""
+    o = opts or {}
+    ns = w_shard.cols
+    ctx.matmulScatter(a, w_shard, res.ptrs, res.N, res.rank * ns, bias=o.get("bias"), act=o.get("act", "none"))
+    return res.local
+
+
 def encode_windows_sharded(ctx, enc, mels: Sequence[np.ndarray], world: int, rank: int, batch: int = 32, group=None):
     """Encode this rank's block of windows in batches of `batch` and gather the frames on rank 0.
     Returns ([n_windows * Tsub, D] on rank 0 else None, Tsub)."""

@@ -220,6 +220,18 @@ int fa_argmax_rows(fa_ctx *ctx, const fa_tensor *x, int ncols, fa_tensor **out);
  * row-major product, out[m, r*Ns + j] = gathered[r*M + m, j].  Ns must be a multiple of 4.  The
  * reference has no multi-device path (one GPUDevice, src/gpu/device.js). */
 int fa_unshard_cols(fa_ctx *ctx, const fa_tensor *gathered, int world, fa_tensor **out);
+/* The same exchange fused into the product (one process per GPU, buffers shared through CUDA IPC): fa_ipc_export
+ * gives a 64-byte handle of a tensor's storage, fa_ipc_open maps a peer's handle into this process (a device
+ * pointer usable by kernels of this GPU over NVLink), fa_ipc_close unmaps it.  fa_matmul_scatter computes this
+ * rank's block of output columns, act(A @ B_shard + bias_shard), and its epilogue stores every finished tile at
+ * columns [col0, col0 + Ns) of ALL `n_outs` result buffers ([M][ldc] f32 each: outs[0] this GPU's own, the rest
+ * peers'), so no separate all-gather or re-layout pass runs.  The caller must order the ranks (a stream-ordered
+ * barrier) between this call and any read of a result, and again before the buffers are overwritten. */
+int fa_ipc_export(fa_ctx *ctx, const fa_tensor *t, unsigned char handle_out[64]);
+int fa_ipc_open(fa_ctx *ctx, const unsigned char handle[64], void **dev_ptr_out);
+int fa_ipc_close(fa_ctx *ctx, void *dev_ptr);
+int fa_matmul_scatter(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b_shard, const fa_tensor *bias_shard, int act,
+                      void *const *outs, int n_outs, int ldc, int col0);
 /* Token embedding + position on the device (the reference gathers on the host and uploads,
  * src/engines/asr-whisper/raw-whisper-decoder.js:106-108): out[s,:] = table[id_s,:] + pos[n,:], where id_s
  * is column 0 of row s of idx (token ids as floats: an fa_argmax_rows result or a [S,1] tensor).  With it

@@ -303,3 +303,25 @@ def test_int4_unpack_in_shared_memory_variant(ctx, oracle, M, K, N):
         ctx.setOption("nbits_fused", 0)
     assert "tc_gemm_nbits" in labels, labels
     assert np.abs(got - ref).max() <= 2e-2 * max(1.0, float(np.abs(ref).max()) / 3.0)
+
+
+def test_matmul_scatter_writes_every_result_buffer(ctx, oracle):
+    """The product whose epilogue stores its column block into several [M, ldc] result buffers (the fused
+    all-gather of the N-sharded sweep), here with three buffers on one GPU."""
+    rng = np.random.default_rng(12)
+    M, K, Ns, ldc, col0 = 300, 256, 192, 640, 256
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, Ns)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    bias = rng.standard_normal(Ns).astype(np.float32)
+    ref = oracle.matmul(oracle.upload(a, M, K), oracle.upload(b, K, Ns), dict(bias=oracle.upload(bias, 1, Ns), act="relu")).array()
+    fill = np.full((M, ldc), -7.0, np.float32)
+    bufs = [ctx.upload(fill, M, ldc) for _ in range(3)]
+    ctx.matmulScatter(ctx.upload(a, M, K), ctx.uploadF16(b, K, Ns), [ctx.devicePtr(t) for t in bufs], ldc, col0,
+                      bias=ctx.upload(bias, 1, Ns), act="relu")
+    first = None
+    for t in bufs:
+        got = ctx.download(t).reshape(M, ldc)
+        assert np.all(got[:, :col0] == -7.0) and np.all(got[:, col0 + Ns:] == -7.0)  # only the block is written
+        assert np.abs(got[:, col0:col0 + Ns] - ref).max() <= 2e-2
+        first = got if first is None else first
+        assert np.array_equal(got, first)  # every buffer holds the same bits
