@@ -526,11 +526,11 @@ class Encoder:
                 "peak_source": peaks["source"] + " (burst bf16: kernel timed alone)"}
 
     def cpu_sample(self, threads=True):
-        """Four conformer blocks on one 15 s window on the CPU port, scaled to the full stack."""
+        """Twelve conformer blocks on one 15 s window on the CPU port, scaled to the full stack."""
         from oracle.wasm_oracle import WasmOracle
         from fluidaudio_web_b200.engines import fastconformer, synth
 
-        nl = 4
+        nl = 12 if not threads else 4
         key = (threads,)
         if getattr(Encoder, "_cpu_enc", (None,))[0] != key:
             ora = WasmOracle(threads=threads)
@@ -720,11 +720,6 @@ class F16GemmNSharded:
         if world > 1 and self.fused:
             self.res = {kn: sharding.ScatterResult(ctx, self.M, kn[1]) for kn in self.KNs}
             self.name = "f16_gemm_m16384_n_sharded_fused_peer_store_allgather"
-
-    def _product(self, ctx, a, kn):
-        if self.world == 1:
-            return ctx.matmul(a, self.W[kn])
-        return self.sh.matmul_n_sharded(ctx, a, self.W[kn])
 
     def step_device(self, ctx):
         if self.world > 1 and self.fused:
