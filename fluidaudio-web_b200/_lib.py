@@ -47,6 +47,7 @@ SIGNATURES = {
     "fa_stage_download": [P, P, PP],
     "fa_staged_read": [P, P, P],
     "fa_staged_free": [P, P],
+    "fa_tensor_ptr": [P, P, PP],
     "fa_rows_view": [P, P, I, PP],
     "fa_reshape_view": [P, P, I, I, PP],
     "fa_begin_batch": [P],

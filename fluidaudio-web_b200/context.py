@@ -479,7 +479,7 @@ class CudaContext:
 
     def devicePtr(self, t: Tensor) -> int:
         p = C.c_void_p()
-        self._lib.fa_tensor_info(t.h, None, None, None, C.byref(p))
+        self._check(self._lib.fa_tensor_ptr(self._h, t.h, C.byref(p)))
         return p.value or 0
 
 

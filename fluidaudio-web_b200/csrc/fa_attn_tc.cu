@@ -16,24 +16,35 @@ namespace {
 // Grid (row groups of 8, K chunks, batch = w*H + h): a warp packs one 64-wide chunk of one row, so the only
 // division left is the one per thread that splits the batch index.
 __global__ void __launch_bounds__(256) k_pack_act_heads(const float *__restrict__ src, const float *__restrict__ addv,
-                                                        __half *__restrict__ dst, int T, int S, int H, int HD, int nch) {
+                                                        const float *__restrict__ addv2, __half *__restrict__ dst,
+                                                        __half *__restrict__ dst2, int T, int S, int H, int HD, int nch) {
   fa_grid_dep_sync();
+  // dst2 (optional): the same rows with a second bias vector - the content and the positional query of
+  // relative-position attention (q + u, q + v) from one read of q
   const int pr = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= T) return;
   const int c = blockIdx.y, batch = blockIdx.z, w = batch / H, h = batch - w * H, d = c * 64 + pr * 2;
-  float x = 0.f, y = 0.f;
+  float x = 0.f, y = 0.f, x2 = 0.f, y2 = 0.f;
   const float *row = src + ((size_t)w * T + r) * S + h * HD;
   if (d + 1 < HD) {
     const float2 v = *(const float2 *)(row + d);
-    x = v.x, y = v.y;
+    x = x2 = v.x, y = y2 = v.y;
     if (addv) {
       const float2 a = *(const float2 *)(addv + h * HD + d);
       x += a.x, y += a.y;
     }
+    if (dst2 && addv2) {
+      const float2 a = *(const float2 *)(addv2 + h * HD + d);
+      x2 += a.x, y2 += a.y;
+    }
   } else if (d < HD) {
-    x = row[d] + (addv ? addv[h * HD + d] : 0.f);
+    x = x2 = row[d];
+    if (addv) x += addv[h * HD + d];
+    if (dst2 && addv2) x2 += addv2[h * HD + d];
   }
-  ((__half2 *)dst)[(((size_t)batch * nch + c) * T + r) * 32 + pr] = __floats2half2_rn(x, y);
+  const size_t o = (((size_t)batch * nch + c) * T + r) * 32 + pr;
+  ((__half2 *)dst)[o] = __floats2half2_rn(x, y);
+  if (dst2) ((__half2 *)dst2)[o] = __floats2half2_rn(x2, y2);
 }
 
 // keys: src[(wsrc*Tb + j) * S + h*HD + d] -> Wp[batch][j/128][d/64][j%128][d%64]; rows j >= Tb and d >= HD zero.
@@ -158,39 +169,82 @@ struct Block {
 
 }  // namespace
 
-int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, float *out, int T, int Tb, int H, int HD,
-                 int W, int b_shared, bool *done) {
-  *done = false;
+static bool qk_shape_ok(fa_ctx *ctx, int T, int Tb, int H, int HD, int W, size_t *a_halves, size_t *w_halves, int b_shared) {
   const long long batches = (long long)W * H;
-  if (!fa_tc_available(ctx) || HD < 64 || T < 32 || Tb < 32 || T > 256 || batches * T * Tb * HD < (1ll << 22)) return FA_OK;
-  const int S = H * HD, nch = ceil_div(HD, 64), tiles_n = ceil_div(Tb, 128);
+  if (!fa_tc_available(ctx) || HD < 64 || T < 32 || Tb < 32 || T > 256 || batches * T * Tb * HD < (1ll << 22)) return false;
+  const int nch = ceil_div(HD, 64), tiles_n = ceil_div(Tb, 128);
   const int wb = b_shared ? H : (int)batches;  // shared keys (the positional table) are packed once per head
-  const size_t a_halves = (size_t)batches * nch * T * 64, w_halves = (size_t)wb * tiles_n * nch * 128 * 64;
-  if (a_halves / 2 >= (1ull << 31) || w_halves / 2 >= (1ull << 31) || batches > 65535 || tiles_n * nch > 65535) return FA_OK;
-  Block ap(ctx), wp(ctx);
-  FA_TRY(ap.get(a_halves * 2));
-  FA_TRY(wp.get(w_halves * 2));
-  {
-    LaunchScope ls(ctx, "attn_pack_q");
-    fa_launch_dep(ctx, k_pack_act_heads, dim3(dim3(ceil_div(T, 8), nch, (unsigned)batches)), dim3(256), 0, q, qb, (__half *)ap.p, T, S, H,
-                                                                                           HD, nch);
+  *a_halves = (size_t)batches * nch * T * 64;
+  *w_halves = (size_t)wb * tiles_n * nch * 128 * 64;
+  return !(*a_halves / 2 >= (1ull << 31) || *w_halves / 2 >= (1ull << 31) || batches > 65535 || tiles_n * nch > 65535);
+}
+
+// Packed per-head keys of `b`.  b_cache (may be NULL): the tensor behind `b` when the keys are shared; its packed
+// copy is kept on the tensor across calls (the projected positional table of a layer never changes between steps).
+static int pack_keys(fa_ctx *ctx, const float *b, fa_tensor *b_cache, int Tb, int H, int HD, int W, int b_shared,
+                     size_t w_halves, Block &wp, const __half **wpk) {
+  const long long batches = (long long)W * H;
+  const int S = H * HD, nch = ceil_div(HD, 64), tiles_n = ceil_div(Tb, 128);
+  const int wb = b_shared ? H : (int)batches;
+  const bool cacheable = b_shared && b_cache && !b_cache->view;
+  const bool cached = cacheable && b_cache->hk16_valid && b_cache->hk_Tb == Tb && b_cache->hk_H == H && b_cache->hk_HD == HD;
+  if (cached) {
+    *wpk = (const __half *)b_cache->hk16;
+    return FA_OK;
   }
-  FA_LAUNCH_CHECK(ctx, "attn_pack_q");
+  if (cacheable && !ctx->capturing) {  // (a block taken while recording belongs to the recording)
+    if (b_cache->hk16 && b_cache->hk16_bytes < w_halves * 2) {
+      fa_block_release(ctx, b_cache->hk16);
+      b_cache->hk16 = nullptr;
+    }
+    if (!b_cache->hk16) FA_TRY(fa_block_acquire(ctx, w_halves * 2, &b_cache->hk16, &b_cache->hk16_bytes));
+    b_cache->hk_Tb = Tb, b_cache->hk_H = H, b_cache->hk_HD = HD;
+    b_cache->hk16_valid = true;
+    *wpk = (const __half *)b_cache->hk16;
+  } else {
+    FA_TRY(wp.get(w_halves * 2));
+    *wpk = (const __half *)wp.p;
+  }
   {
     LaunchScope ls(ctx, "attn_pack_k");
     // with shared keys the source has a single "window" (w = 0 for every packed batch h)
-    fa_launch_dep(ctx, k_pack_w_heads, dim3(dim3(16, tiles_n * nch, (unsigned)wb)), dim3(256), 0, b, (__half *)wp.p, Tb, S, H, HD, tiles_n,
-                                                                                  nch, 0);
+    fa_launch_dep(ctx, k_pack_w_heads, dim3(16, tiles_n * nch, (unsigned)wb), dim3(256), 0, b, (__half *)*wpk, Tb, S, H, HD,
+                  tiles_n, nch, 0);
   }
   FA_LAUNCH_CHECK(ctx, "attn_pack_k");
+  return FA_OK;
+}
+
+// out[((w*H+h)*T + i)*Tb + j] = packed queries x packed keys, one (w, h) per batch
+static int qk_gemm(fa_ctx *ctx, const __half *ap, const __half *wpk, float *out, int T, int Tb, int H, int HD, int W,
+                   int b_shared) {
   TcEpilogue ep;
-  ep.batches = (int)batches;
+  ep.batches = W * H;
   ep.w_batch_mod = b_shared ? H : 0;
   ep.o_div = 1;
-  ep.o_hi = (long long)T * Tb;  // out[((w*H+h)*T + i)*Tb + j]
+  ep.o_hi = (long long)T * Tb;
   ep.o_lo = 0;
   ep.ldc = Tb;
-  FA_TRY(fa_tc_gemm_f16(ctx, (const __half *)ap.p, (const __half *)wp.p, out, T, Tb, HD, ep));
+  return fa_tc_gemm_f16(ctx, ap, wpk, out, T, Tb, HD, ep);
+}
+
+int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, fa_tensor *b_cache, const float *qb, float *out, int T, int Tb,
+                 int H, int HD, int W, int b_shared, bool *done) {
+  *done = false;
+  size_t a_halves = 0, w_halves = 0;
+  if (!qk_shape_ok(ctx, T, Tb, H, HD, W, &a_halves, &w_halves, b_shared)) return FA_OK;
+  const int S = H * HD, nch = ceil_div(HD, 64);
+  Block ap(ctx), wp(ctx);
+  FA_TRY(ap.get(a_halves * 2));
+  {
+    LaunchScope ls(ctx, "attn_pack_q");
+    fa_launch_dep(ctx, k_pack_act_heads, dim3(ceil_div(T, 8), nch, (unsigned)(W * H)), dim3(256), 0, q, qb, (const float *)nullptr,
+                  (__half *)ap.p, (__half *)nullptr, T, S, H, HD, nch);
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_pack_q");
+  const __half *wpk = nullptr;
+  FA_TRY(pack_keys(ctx, b, b_cache, Tb, H, HD, W, b_shared, w_halves, wp, &wpk));
+  FA_TRY(qk_gemm(ctx, (const __half *)ap.p, wpk, out, T, Tb, H, HD, W, b_shared));
   *done = true;
   return FA_OK;
 }
@@ -254,8 +308,8 @@ int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half
 // of src/engines/asr-parakeet/raw-encoder.js:335-341): content scores and positional scores on the
 // batched tensor-core GEMM, then ONE pass that shifts, adds, normalises and emits the probabilities as
 // the packed f16 operand of the P@V product - the [W*H*T, T] probability tensor is never stored in f32.
-int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
-                     const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done) {
+int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache,
+                     const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done) {
   *done = false;
   const int P = 2 * T - 1;
   const long long batches = (long long)W * H;
@@ -263,11 +317,25 @@ int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v
   Block ac(ctx), bd(ctx), pr(ctx);
   FA_TRY(ac.get((size_t)batches * T * T * 4));
   FA_TRY(bd.get((size_t)batches * T * P * 4));
-  bool ok1 = false, ok2 = false;
-  FA_TRY(fa_tc_bmm_qk(ctx, q, k, pbu, (float *)ac.p, T, T, H, HD, W, 0, &ok1));
-  if (!ok1) return FA_OK;
-  FA_TRY(fa_tc_bmm_qk(ctx, q, pos, pbv, (float *)bd.p, T, P, H, HD, W, 1, &ok2));
-  if (!ok2) return FA_OK;
+  // one read of q gives both packed queries; the layer's own keys are packed per call, the positional keys once
+  size_t a_halves = 0, wk_halves = 0, wp_halves = 0, a2 = 0;
+  if (!qk_shape_ok(ctx, T, T, H, HD, W, &a_halves, &wk_halves, 0) || !qk_shape_ok(ctx, T, P, H, HD, W, &a2, &wp_halves, 1))
+    return FA_OK;
+  const int S = H * HD, nchq = ceil_div(HD, 64);
+  Block qu(ctx), qv(ctx), wk(ctx), wpos(ctx);
+  FA_TRY(qu.get(a_halves * 2));
+  FA_TRY(qv.get(a_halves * 2));
+  {
+    LaunchScope ls(ctx, "attn_pack_q");
+    fa_launch_dep(ctx, k_pack_act_heads, dim3(ceil_div(T, 8), nchq, (unsigned)batches), dim3(256), 0, q, pbu, pbv, (__half *)qu.p,
+                  (__half *)qv.p, T, S, H, HD, nchq);
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_pack_q");
+  const __half *kk = nullptr, *kp = nullptr;
+  FA_TRY(pack_keys(ctx, k, nullptr, T, H, HD, W, 0, wk_halves, wk, &kk));
+  FA_TRY(qk_gemm(ctx, (const __half *)qu.p, kk, (float *)ac.p, T, T, H, HD, W, 0));
+  FA_TRY(pack_keys(ctx, pos, pos_cache, P, H, HD, W, 1, wp_halves, wpos, &kp));
+  FA_TRY(qk_gemm(ctx, (const __half *)qv.p, kp, (float *)bd.p, T, P, H, HD, W, 1));
   const int nch = ceil_div(T, 64);
   FA_TRY(pr.get((size_t)batches * nch * T * 64 * 2));
   {

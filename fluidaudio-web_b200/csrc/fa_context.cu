@@ -118,6 +118,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->f16_hilo_rows = value > 0x7fffffffLL ? 0x7fffffff : (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "lazy_f32")) {
+    FA_REQUIRE(ctx, value == 0 || value == 1, "lazy_f32 must be 0 or 1 (got %lld)", value);
+    ctx->lazy_f32 = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "pdl")) {
     FA_REQUIRE(ctx, value == 0 || value == 1, "pdl must be 0 or 1 (got %lld)", value);
     ctx->pdl = (int)value;
@@ -266,6 +271,13 @@ void fa_block_free(fa_ctx *ctx, void *p) {
 }
 
 bool fa_valid(fa_ctx *ctx, const fa_tensor *t) { return t && ctx->tensors.count(const_cast<fa_tensor *>(t)); }
+int fa_touch_f32(fa_ctx *ctx, const fa_tensor *t) {
+  fa_tensor *m = const_cast<fa_tensor *>(t);
+  if (!m || !m->f32_lazy) return FA_OK;
+  m->f32_lazy = false;
+  return fa_unpack_a_f16(ctx, (const __half *)m->a16, m->rows, m->cols, (float *)m->dptr);
+}
+
 bool fa_valid_bytes(fa_ctx *ctx, const fa_bytes *b) { return b && ctx->byte_handles.count(const_cast<fa_bytes *>(b)); }
 
 int fa_tensor_new(fa_ctx *ctx, int rows, int cols, int storage, bool pooled, fa_tensor **out) {
@@ -295,6 +307,9 @@ static void tensor_drop_storage(fa_ctx *ctx, fa_tensor *t) {
   if (t->view) return;
   if (t->bt_f16) fa_block_release(ctx, t->bt_f16);
   if (t->a16) fa_block_release(ctx, t->a16);
+  if (t->hk16) fa_block_release(ctx, t->hk16);
+  t->hk16 = nullptr;
+  t->hk16_valid = false;
   if (t->dptr) fa_block_release(ctx, t->dptr);
   t->dptr = t->bt_f16 = t->a16 = nullptr;
   t->a16_valid = false;
@@ -461,6 +476,15 @@ extern "C" int fa_trim_pool(fa_ctx *ctx, size_t budget_bytes) {
   return FA_OK;
 }
 
+extern "C" int fa_tensor_ptr(fa_ctx *ctx, const fa_tensor *t, void **device_ptr) {
+  if (!ctx || !device_ptr) return fa_fail(ctx, FA_ERR_INVALID, "tensorPtr: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, t), "tensorPtr: unknown tensor handle");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  FA_TRY(fa_touch_f32(ctx, t));
+  *device_ptr = t->dptr;
+  return FA_OK;
+}
+
 extern "C" int fa_tensor_info(const fa_tensor *t, int *rows, int *cols, int *storage, void **device_ptr) {
   if (!t) return FA_ERR_INVALID;
   if (rows) *rows = t->rows;
@@ -495,6 +519,7 @@ extern "C" int fa_host_free(void *p) {
 
 int fa_as_f32(fa_ctx *ctx, const fa_tensor *t, const float **ptr, fa_tensor **tmp) {
   *tmp = nullptr;
+  FA_TRY(fa_touch_f32(ctx, t));
   if (t->storage == FA_F32) {
     *ptr = (const float *)t->dptr;
     return FA_OK;
@@ -584,6 +609,7 @@ extern "C" int fa_staged_free(fa_ctx *ctx, fa_staged *s) {
 extern "C" int fa_rows_view(fa_ctx *ctx, fa_tensor *t, int rows, fa_tensor **out) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "rowsView: NULL argument");
   FA_REQUIRE(ctx, fa_valid(ctx, t), "rowsView: unknown tensor handle");
+  FA_TRY(fa_touch_f32(ctx, t));
   FA_REQUIRE(ctx, rows >= 0 && rows <= t->rows, "rowsView: %d rows of a %d-row tensor", rows, t->rows);
   fa_tensor *v = new fa_tensor();
   v->rows = rows;
@@ -599,6 +625,7 @@ extern "C" int fa_rows_view(fa_ctx *ctx, fa_tensor *t, int rows, fa_tensor **out
 extern "C" int fa_reshape_view(fa_ctx *ctx, fa_tensor *t, int rows, int cols, fa_tensor **out) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "reshapeView: NULL argument");
   FA_REQUIRE(ctx, fa_valid(ctx, t), "reshapeView: unknown tensor handle");
+  FA_TRY(fa_touch_f32(ctx, t));
   FA_REQUIRE(ctx, rows >= 0 && cols >= 0 && (long long)rows * cols <= (long long)t->rows * t->cols,
              "reshapeView: [%d,%d] does not fit a [%d,%d] tensor", rows, cols, t->rows, t->cols);
   fa_tensor *v = new fa_tensor();
@@ -618,6 +645,7 @@ extern "C" int fa_reshape_view(fa_ctx *ctx, fa_tensor *t, int rows, int cols, fa
 extern "C" int fa_ipc_export(fa_ctx *ctx, const fa_tensor *t, unsigned char handle_out[64]) {
   if (!ctx || !handle_out) return fa_fail(ctx, FA_ERR_INVALID, "ipcExport: NULL argument");
   FA_REQUIRE(ctx, fa_valid(ctx, t) && !t->view, "ipcExport: unknown tensor handle or a view");
+  FA_TRY(fa_touch_f32(ctx, t));
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
   cudaIpcMemHandle_t h;

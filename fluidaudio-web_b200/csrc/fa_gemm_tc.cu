@@ -68,6 +68,7 @@ struct TcParams {
   int a_shared;       // batched mode: every batch multiplies the same activation slabs
   long long o_hi, o_lo;
   __half *out16;      // optional packed f16 shadow of the result (see TcEpilogue), or nullptr
+  int skip_f32;       // with out16: the f32 result is not stored at all (fa_tensor::f32_lazy)
   int o16_rows, o16_row_hi, o16_col_lo;
   float *out;         // [M][N] f32 (or int32 when raw_i32)
   // N-sharded products: besides `out`, every finished tile is also stored at the same [row][column] of up to 7
@@ -229,7 +230,9 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
           if (full_rows || m0 + c + j < p.M) h16[(size_t)j * 64] = __float2half_rn(v[j] + ad[j]);
       }
       float *orow = outb + (size_t)(m0 + c) * p.ldc + n;
-      if (full_rows) {
+      if (p.skip_f32) {
+        // hidden-layer result: the shadow above is all the next product reads
+      } else if (full_rows) {
 #pragma unroll
         for (int j = 0; j < 16; j++) orow[(size_t)j * p.ldc] = v[j] + ad[j];
       } else {
@@ -834,6 +837,20 @@ __global__ void k_nbits_side(const float *__restrict__ scales, const uint8_t *__
   }
 }
 
+// The reverse of k_prep_a_f16: packed f16 Ap[k/64][m][k%64] -> f32 [M][K] (fills a lazy tensor's f32 storage).
+__global__ void k_unpack_a_f16(const __half *__restrict__ packed, int M, int K, int nch, float *__restrict__ out) {
+  fa_grid_dep_sync();
+  const size_t total = (size_t)nch * M * 32;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int pr = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
+    const int k = c * 64 + pr * 2;
+    const float2 v = __half22float2(((const __half2 *)packed)[i]);
+    float *row = out + (size_t)m * K;
+    if (k < K) row[k] = v.x;
+    if (k + 1 < K) row[k + 1] = v.y;
+  }
+}
+
 // f32 [M][K] -> f16 Ap[k/64][m][64] for the int4 variant: inside every group of 8 the order of k is
 // 0,4,1,5,2,6,3,7, the order its in-kernel nibble unpack produces.
 __global__ void k_prep_a_f16_perm8(const float *__restrict__ a, int M, int K, int nch, __half *__restrict__ out) {
@@ -1062,6 +1079,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.o_hi = ep.o_hi;
   p.o_lo = ep.o_lo;
   p.out16 = ep.out16;
+  p.skip_f32 = (ep.skip_f32 && ep.out16) ? 1 : 0;
   p.o16_rows = ep.o16_rows > 0 ? ep.o16_rows : M;
   p.o16_row_hi = ep.o16_row_hi;
   p.o16_col_lo = ep.o16_col_lo;
@@ -1336,6 +1354,17 @@ int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out) {
     fa_launch_dep(ctx, k_prep_a_f16, dim3(grid_for(ctx, (size_t)nch * M * 32, 256, 8)), dim3(256), 0, a, M, K, nch, out);
   }
   FA_LAUNCH_CHECK(ctx, "prep_a_f16");
+  return FA_OK;
+}
+
+int fa_unpack_a_f16(fa_ctx *ctx, const __half *packed, int M, int K, float *out) {
+  if (M == 0 || K == 0) return FA_OK;
+  const int nch = fa_tc_chunks(K, 2);
+  {
+    LaunchScope ls(ctx, "unpack_a_f16");
+    fa_launch_dep(ctx, k_unpack_a_f16, dim3(grid_for(ctx, (size_t)nch * M * 32, 256, 8)), dim3(256), 0, packed, M, K, nch, out);
+  }
+  FA_LAUNCH_CHECK(ctx, "unpack_a_f16");
   return FA_OK;
 }
 

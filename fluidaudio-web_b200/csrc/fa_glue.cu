@@ -913,7 +913,7 @@ int grid1d(fa_ctx *ctx, size_t n, int block) {
 int need_f32(fa_ctx *ctx, const fa_tensor *t, const char *op) {
   FA_REQUIRE(ctx, fa_valid(ctx, t), "%s: unknown tensor handle", op);
   FA_REQUIRE(ctx, t->storage == FA_F32, "%s: operand must be f32 storage", op);
-  return FA_OK;
+  return fa_touch_f32(ctx, t);
 }
 
 }  // namespace
@@ -1304,8 +1304,8 @@ extern "C" int fa_bmm_qk(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *b, co
     return FA_OK;
   }
   if (T && Tb)
-    FA_TRY(fa_tc_bmm_qk(ctx, (const float *)q->dptr, (const float *)b->dptr, qb ? (const float *)qb->dptr : nullptr,
-                        (float *)y->dptr, T, Tb, H, HD, W, b_shared, &on_tc));
+    FA_TRY(fa_tc_bmm_qk(ctx, (const float *)q->dptr, (const float *)b->dptr, b_shared ? const_cast<fa_tensor *>(b) : nullptr,
+                        qb ? (const float *)qb->dptr : nullptr, (float *)y->dptr, T, Tb, H, HD, W, b_shared, &on_tc));
   if (T && Tb && !on_tc) {
     dim3 grid(ceil_div(Tb, 64), ceil_div(T, 64), W * H);
     FA_REQUIRE(ctx, grid.z <= 65535 && grid.y <= 65535, "bmmQK: batch too large");
@@ -1434,8 +1434,8 @@ extern "C" int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k
   __half *y16 = (S & 63) == 0 && (HD & 31) == 0 ? fa_shadow_block(ctx, y) : nullptr;
   bool done = false;
   int rc = fa_tc_attn_fused(ctx, (const float *)q->dptr, (const float *)k->dptr, (const float *)v->dptr,
-                            (const float *)pos->dptr, (const float *)pbu->dptr, (const float *)pbv->dptr, (float *)y->dptr,
-                            y16, T, H, HD, W, &done);
+                            (const float *)pos->dptr, const_cast<fa_tensor *>(pos), (const float *)pbu->dptr,
+                            (const float *)pbv->dptr, (float *)y->dptr, y16, T, H, HD, W, &done);
   if (rc != FA_OK || !done) {  // not this shape: the caller falls back to the separate ops (may return null)
     fa_free_tensor(ctx, y);
     return rc;

@@ -37,6 +37,16 @@ struct fa_tensor {
   size_t a16_bytes = 0;
   bool a16_valid = false;
   bool a16_hilo = false;  // the shadow holds two planes (value, rounding residue)
+  // Hidden-layer results (a product with a fused activation) are consumed by the next product through their
+  // packed f16 shadow only, so their f32 storage is left unwritten until somebody else asks for it
+  // (fa_touch_f32 then fills it from the shadow: the f16-rounded values the next product sees anyway).
+  bool f32_lazy = false;
+  // Packed per-head f16 copy of this tensor as the shared KEYS of a batched attention product (the projected
+  // positional table of a conformer layer is the same every step): built on first use, dropped with the shadow.
+  void *hk16 = nullptr;
+  size_t hk16_bytes = 0;
+  bool hk16_valid = false;
+  int hk_Tb = 0, hk_H = 0, hk_HD = 0;
 };
 
 struct fa_bytes {
@@ -91,6 +101,7 @@ struct fa_ctx {
   unsigned long long launches = 0;
   // options
   int int8_limbs = 2;
+  int lazy_f32 = 1;        // hidden-layer products leave their f32 result unwritten until it is asked for
   int pdl = 1;             // programmatic dependent launch between the library's kernels (see fa_launch_dep)
   int nbits_fused = 0;     // 1: int4 products on the tensor cores unpack nibbles in shared memory (0: f16 copy, faster today)
   int gemv_rows = 4;       // products with at most this many rows run on the CUDA-core GEMV kernels (0 = never)
@@ -152,6 +163,10 @@ void fa_block_free(fa_ctx *ctx, void *p);               // cudaFree now
 int fa_tensor_new(fa_ctx *ctx, int rows, int cols, int storage, bool pooled, fa_tensor **out);
 bool fa_valid(fa_ctx *ctx, const fa_tensor *t);
 bool fa_valid_bytes(fa_ctx *ctx, const fa_bytes *b);
+// Makes the f32 storage of `t` current (see fa_tensor::f32_lazy); a no-op for every other tensor.  Every path
+// that reads or aliases a tensor's f32 storage calls it first.
+int fa_touch_f32(fa_ctx *ctx, const fa_tensor *t);
+int fa_unpack_a_f16(fa_ctx *ctx, const __half *packed, int M, int K, float *out);
 // f32 device pointer for `t`: the tensor itself when it is f32 storage, else a converted
 // temporary (arena-scoped like any alloc) returned through *tmp.
 int fa_as_f32(fa_ctx *ctx, const fa_tensor *t, const float **ptr, fa_tensor **tmp);
@@ -263,6 +278,7 @@ struct TcEpilogue {
   int act = 0;
   bool a_hilo = false;
   bool a_shared = false;            // batched mode: all batches share the row operand
+  bool skip_f32 = false;            // write only the packed f16 shadow (out16); the f32 result stays lazy
   float *peer_out[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // see TcParams::peer_out
   int n_peers = 0;
   const float *nb_scales = nullptr;  // int4 variant: per-block scales, packed zero-points, blocks per row
@@ -314,15 +330,18 @@ int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, con
 bool fa_tc_available(fa_ctx *ctx);
 // Batched attention products on the tensor cores (fa_attn_tc.cu); return FA_OK and *done=false when the
 // shape does not fit the packed layouts (the caller then uses the any-shape kernels).
-int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, const float *qb, float *out, int T, int Tb, int H, int HD,
+int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, fa_tensor *b_cache, const float *qb, float *out, int T, int Tb, int H, int HD,
                  int W, int b_shared, bool *done);
 int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half *out16, int Tq, int Tk, int H, int HD,
                  int W, bool *done);
-int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
+int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache, const float *pbu,
                      const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done);
 // Shadow management (fa_linalg.cu): block for t's packed f16 shadow (nullptr when t cannot carry one),
 // and the shadow itself, built by the prepass when no producer wrote it.
 __half *fa_shadow_block(fa_ctx *ctx, fa_tensor *t);
 __half *fa_shadow_hilo_block(fa_ctx *ctx, fa_tensor *t);
 int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out);
-static inline void fa_shadow_drop(fa_tensor *t) { t->a16_valid = false; }
+static inline void fa_shadow_drop(fa_tensor *t) {
+  t->a16_valid = false;
+  t->hk16_valid = false;
+}

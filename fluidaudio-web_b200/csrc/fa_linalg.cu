@@ -32,7 +32,7 @@ int check_vec(fa_ctx *ctx, const fa_tensor *t, int n, const char *what) {
   FA_REQUIRE(ctx, fa_valid(ctx, t), "%s: unknown tensor handle", what);
   FA_REQUIRE(ctx, t->storage == FA_F32, "%s must be f32 storage", what);
   FA_REQUIRE(ctx, (long long)t->rows * t->cols >= n, "%s has %d elements, need %d", what, t->rows * t->cols, n);
-  return FA_OK;
+  return fa_touch_f32(ctx, t);
 }
 
 // Packed f16 copy of a [K][N] weight tensor, built once per handle.
@@ -91,6 +91,7 @@ int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out) {
   __half *blk = fa_shadow_block(ctx, t);
   if (!blk) return fa_fail(ctx, FA_ERR_OOM, "no block for the f16 shadow of a %dx%d tensor", t->rows, t->cols);
   if (!t->a16_valid) {
+    FA_TRY(fa_touch_f32(ctx, t));
     FA_TRY(fa_prep_a_f16(ctx, (const float *)t->dptr, t->rows, t->cols, blk));
     t->a16_valid = true;
   }
@@ -101,6 +102,7 @@ int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out) {
 // Two-plane (value, residue) shadow block of a few-row tensor, for a producer that fills both planes.
 __half *fa_shadow_hilo_block(fa_ctx *ctx, fa_tensor *t) {
   if (!t || t->view || t->storage != FA_F32 || t->rows <= 0 || t->cols <= 0) return nullptr;
+  if (fa_touch_f32(ctx, t) != FA_OK) return nullptr;  // a lazy result lives only in the shadow released below
   if (t->a16 && !t->a16_hilo) {
     fa_block_release(ctx, t->a16);
     t->a16 = nullptr;
@@ -161,7 +163,13 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
   FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
   const float *ap = nullptr;
   fa_tensor *atmp = nullptr;
-  FA_TRY(fa_as_f32(ctx, a, &ap, &atmp));
+  // A row operand that already carries a valid packed shadow and is headed for the tensor cores is not read as
+  // f32 at all (and, if it is a lazy hidden-layer result, must not be: that would fill its f32 storage for nothing).
+  const bool tc_route = b->storage == FA_F16 && !b->view && tc_shape_ok(ctx, M, N, K) &&
+                        !(gemv_shape_ok(ctx, M, N, K) && fa_gemv_kn_ok(M, N, K, false));
+  const bool shadow_only = tc_route && a->storage == FA_F32 && !a->view && a->a16_valid && !a->a16_hilo &&
+                           a->rows > ctx->f16_hilo_rows;
+  if (!shadow_only) FA_TRY(fa_as_f32(ctx, a, &ap, &atmp));
   fa_tensor *c = nullptr;
   FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
   int rc;
@@ -183,7 +191,13 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
       ep.act = act;
       // A product with a fused activation is a hidden layer: its result goes straight into the next
       // product, so the epilogue also emits it as that product's packed f16 row operand.
-      if (act != FA_ACT_NONE && (N & 63) == 0 && (ep.out16 = fa_shadow_block(ctx, c)) != nullptr) c->a16_valid = true;
+      if (act != FA_ACT_NONE && (N & 63) == 0 && (ep.out16 = fa_shadow_block(ctx, c)) != nullptr) {
+        c->a16_valid = true;
+        if (ctx->lazy_f32 && !add) {  // ... and only as that: the f32 copy is made if and when something else reads it
+          ep.skip_f32 = true;
+          c->f32_lazy = true;
+        }
+      }
       rc = fa_tc_gemm_f16(ctx, a16, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);
     }
   } else {

@@ -69,7 +69,9 @@ const char *fa_last_error(fa_ctx *ctx);
  * kernel; 0 = through a one-time dequantised f16 copy of the weights, which is the faster of the two
  * today), "pdl" (0/1, default 1: the library's kernels are chained with programmatic dependent launch, so a
  * kernel's scheduling and prologue overlap its predecessor's tail; every such kernel waits for its
- * predecessors before touching their data; 0 = plain stream order). */
+ * predecessors before touching their data; 0 = plain stream order), "lazy_f32" (0/1, default 1: the result of
+ * a tensor-core product with a fused activation is written only as the packed f16 operand of the next product;
+ * its f32 storage is filled from that, f16-rounded, the first time anything else reads it). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);
@@ -91,6 +93,10 @@ int fa_push_arena(fa_ctx *ctx, int *handle_out);                                
 int fa_pop_arena(fa_ctx *ctx, int handle); /* popArena :129; handle < 0 closes the newest open arena */
 int fa_trim_pool(fa_ctx *ctx, size_t budget_bytes);                                      /* trimPool :131 */
 int fa_tensor_info(const fa_tensor *t, int *rows, int *cols, int *storage, void **device_ptr);
+/* Device pointer of a tensor's storage for callers that hand it to other libraries (NCCL, their own kernels).
+ * Use this rather than fa_tensor_info's device_ptr: a hidden-layer result (a product with a fused activation)
+ * keeps its f32 storage unwritten until something asks for it, and this call is such an ask. */
+int fa_tensor_ptr(fa_ctx *ctx, const fa_tensor *t, void **device_ptr);
 /* memStats / poolInfo (compute.d.ts:252-254): allocations made, bytes made, pool hits, bytes idle in the pool. */
 int fa_mem_stats(fa_ctx *ctx, unsigned long long *created, unsigned long long *created_bytes,
                  unsigned long long *reused, unsigned long long *pool_bytes);

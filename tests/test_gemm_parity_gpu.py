@@ -325,3 +325,45 @@ def test_matmul_scatter_writes_every_result_buffer(ctx, oracle):
         assert np.abs(got[:, col0:col0 + Ns] - ref).max() <= 2e-2
         first = got if first is None else first
         assert np.array_equal(got, first)  # every buffer holds the same bits
+
+
+def test_hidden_layer_result_is_lazy_and_consistent(ctx, oracle):
+    """A product with a fused activation writes only the packed f16 operand of the next product; its f32
+    storage is filled (f16-rounded) when something else reads it.  The chained product is bit-identical with
+    the option off, and a direct read stays within the f16-route tolerance of the oracle."""
+    rng = np.random.default_rng(21)
+    M, K, N, N2 = 300, 256, 512, 192
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w1 = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    w2 = (rng.standard_normal((N, N2)) / np.sqrt(N)).astype(np.float16).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    ref_h = oracle.matmul(oracle.upload(a, M, K), oracle.upload(w1, K, N), dict(bias=oracle.upload(bias, 1, N), act="silu")).array()
+    outs = {}
+    for lazy in (1, 0):
+        ctx.setOption("lazy_f32", lazy)
+        try:
+            A, W1, W2, B = ctx.upload(a, M, K), ctx.uploadF16(w1, K, N), ctx.uploadF16(w2, N, N2), ctx.upload(bias, 1, N)
+            ctx.startProfile(64)
+            h = ctx.matmul(A, W1, dict(bias=B, act="silu"))
+            y = ctx.download(ctx.matmul(h, W2)).reshape(M, N2)
+            labels_chain = [e["label"] for e in ctx.endProfile()]
+            ctx.startProfile(64)
+            hd = ctx.download(h).reshape(M, N)
+            labels_read = [e["label"] for e in ctx.endProfile()]
+            outs[lazy] = (y, hd, labels_chain, labels_read)
+        finally:
+            ctx.setOption("lazy_f32", 1)
+    y1, h1, chain1, read1 = outs[1]
+    y0, h0, chain0, read0 = outs[0]
+    assert np.array_equal(y1, y0)                      # the next product sees the same f16 operand either way
+    assert "unpack_a_f16" not in chain1 and "unpack_a_f16" in read1 and "unpack_a_f16" not in read0
+    assert np.array_equal(h1, h0.astype(np.float16).astype(np.float32))  # the lazy copy is the f16 rounding of the f32 one
+    assert np.abs(h1 - ref_h).max() <= 2e-2
+    # reading through other members works too: a view and an elementwise op on a fresh lazy result
+    A, W1, B = ctx.upload(a, M, K), ctx.uploadF16(w1, K, N), ctx.upload(bias, 1, N)
+    h = ctx.matmul(A, W1, dict(bias=B, act="silu"))
+    v = ctx.download(ctx.rowsView(h, 7)).reshape(7, N)
+    assert np.array_equal(v, h1[:7])
+    h = ctx.matmul(A, W1, dict(bias=B, act="silu"))
+    s2 = ctx.download(ctx.scale(h, 2.0)).reshape(M, N)
+    assert np.array_equal(s2, h1 * 2.0)
