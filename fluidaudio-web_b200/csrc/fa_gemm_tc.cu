@@ -1,31 +1,34 @@
-// tcgen05 GEMM for the f16-weight and int8-weight products (sm_100a).
+// tcgen05 GEMM for the f16-weight, int8-weight and int4-weight products (sm_100a).
 //
 // Replaces the reference's WGSL GEMM family for large shapes: f16-storage B
-// (src/gpu/kernels/gemm.js:336-419, 420-503) and int8 B (gemm.js:679-885).
+// (src/gpu/kernels/gemm.js:336-419, 420-503), int8 B (gemm.js:679-885) and int4 B (gemm.js:893-919).
 //
 // One orientation for every shape: the WEIGHTS are the MMA M-side operand (128 output columns
 // n per CTA, one TMEM lane each), the ACTIVATIONS are the MMA N-side operand (MT rows m per CTA,
 // one TMEM column each).  Operands are brought in by TMA (128-byte swizzle, no multicast) through
 // a multi-stage mbarrier ring, multiplied by tcgen05.mma (kind::f16 -> f32, kind::i8 -> s32) into
-// TMEM, and read back with tcgen05.ld by four epilogue warps that apply
+// TMEM, and read back with tcgen05.ld by eight epilogue warps that apply
 //   acc (*rowscale[m]) (*colscale[n]) + bias[n] -> act -> + add[m,n]
 // and store out[m][n] so that the 32 lanes of a warp write 32 consecutive n (coalesced rows).
-// Decode sizes (M <= 16) use MT = 16: the kernel then is a pure weight-streaming loop with a deep
-// ring, which is what bounds it (HBM), while padding M to 16 costs nothing on the tensor pipe.
+// The kernel is persistent (one CTA per SM walks the tiles) with two TMEM accumulator buffers, so a
+// tile's epilogue overlaps the next tile's main loop.  Products with fewer tiles than SMs and at most
+// 128 rows split K over a cluster of up to 8 CTAs and reduce over distributed shared memory.
 //
 // Operand layout in HBM ("box-contiguous"): every TMA box is one contiguous run of memory, so a
 // CTA streams its weights as a single linear region instead of 128-byte pieces a row pitch apart
 // (which opens a new DRAM page per piece).  With ck = elements per 128 bytes of K:
 //   weights     Wp[n/128][k/ck][n%128][k%ck]            (one-time repack, cached on the handle)
-//   activations Ap[limb][k/ck][m][k%ck]                  (written by the per-call prepass)
+//   activations Ap[plane][k/ck][m][k%ck]                 (prepass, or written by the producing kernel)
 // The reference itself prepacks weights tile-major for its fastest GEMM (compute.js:224-243).
 //
 // int8 activations arrive as `limbs` int8 digit planes (see fa_prep_a_i8): plane l is stacked as
 // MT extra MMA-N rows, so ONE instruction stream produces all digit products, each an exact int32
 // sum in its own TMEM column range; the epilogue recombines them as sum_l acc_l * 2^(-7 l).
+// f16 activations of few-row products arrive as two planes, value and rounding residue, accumulated
+// into the SAME TMEM columns (f32-grade activations where the weight stream is the cost anyway).
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (TMEM lane quadrant = warp_id % 4).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (TMEM lane quadrant = warp_id % 4, two warps per quadrant).
 #include <cstdlib>
 
 #include "fa_tc_common.cuh"
