@@ -783,6 +783,8 @@ def run_reference(args):
 
     ge.load_package()  # the engines' host logic (backend-agnostic) drives the CPU port for the model workloads
     wl = WORKLOADS[args.workload](quick=True)
+    # all host threads, also under torchrun (which exports OMP_NUM_THREADS=1 to its workers)
+    LIB.oracle_set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cores = LIB.oracle_num_threads()
     vals, desc = [], ""
     for _ in range(args.warmup):

@@ -449,6 +449,15 @@ ORACLE_API void mulberry32_fill_u8(uint32_t *seed, uint8_t *out, size_t n) {
   for (size_t i = 0; i < n; i++) out[i] = (uint8_t)floor(mulberry32_next(seed) * 256.0);
 }
 
+/* Thread count of the OpenMP variants (the timed CPU baseline); n <= 0 leaves it unchanged. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORACLE_API int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -68,6 +68,8 @@ def _load() -> C.CDLL:
     lib.js_apply_act.argtypes = [C.c_double, C.c_int]
     lib.js_apply_act.restype = C.c_double
     lib.oracle_num_threads.restype = C.c_int
+    lib.oracle_set_num_threads.argtypes = [C.c_int]
+    lib.oracle_set_num_threads.restype = None
     return lib
 
 
