@@ -274,7 +274,7 @@ bool fa_valid(fa_ctx *ctx, const fa_tensor *t) { return t && ctx->tensors.count(
 int fa_touch_f32(fa_ctx *ctx, const fa_tensor *t) {
   fa_tensor *m = const_cast<fa_tensor *>(t);
   if (!m || !m->f32_lazy) return FA_OK;
-  m->f32_lazy = false;
+  if (!m->lazy_sticky) m->f32_lazy = false;
   return fa_unpack_a_f16(ctx, (const __half *)m->a16, m->rows, m->cols, (float *)m->dptr);
 }
 

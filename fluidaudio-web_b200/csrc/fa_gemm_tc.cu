@@ -136,7 +136,9 @@ __device__ __forceinline__ void act16(float (&v)[16], int act) {
       break;
     case FA_ACT_SILU:
 #pragma unroll
-      for (int j = 0; j < 16; j++) v[j] = v[j] / (1.0f + __expf(-fminf(fmaxf(v[j], -30.0f), 30.0f)));
+      // ex2.approx + rcp.approx (a few ulp): the IEEE division here made the SiLU products epilogue-bound
+      // (84 us against 53 us for the same product without activation)
+      for (int j = 0; j < 16; j++) v[j] = __fdividef(v[j], 1.0f + __expf(-fminf(fmaxf(v[j], -30.0f), 30.0f)));
       break;
     default:
 #pragma unroll

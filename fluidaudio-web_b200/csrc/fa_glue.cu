@@ -755,7 +755,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
 #pragma unroll
   for (int j = 0; j < 16 + K - 1; j++) {
     const int tg = t0 - padl + j;
-    g[j] = (tg >= lo && tg < hi) ? g[j] * (1.0f / (1.0f + __expf(-gate[j]))) : 0.f;
+    g[j] = (tg >= lo && tg < hi) ? __fdividef(g[j], 1.0f + __expf(-gate[j])) : 0.f;
   }
 #pragma unroll
   for (int i = 0; i < 16; i++) {
@@ -763,7 +763,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
     float acc = b;
 #pragma unroll
     for (int kk = 0; kk < K; kk++) acc = fmaf(wk[kk], g[i + kk], acc);
-    const float o = fa_actf(acc, act);
+    const float o = act == FA_ACT_SILU ? __fdividef(acc, 1.0f + __expf(-fminf(fmaxf(acc, -30.0f), 30.0f))) : fa_actf(acc, act);
     const int t = t0 + i;
     y[(size_t)t * D + c] = o;
     if (y16) y16[((size_t)(c >> 6) * rows + t) * 64 + (c & 63)] = __float2half_rn(o);

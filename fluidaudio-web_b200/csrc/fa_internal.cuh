@@ -41,6 +41,8 @@ struct fa_tensor {
   // packed f16 shadow only, so their f32 storage is left unwritten until somebody else asks for it
   // (fa_touch_f32 then fills it from the shadow: the f16-rounded values the next product sees anyway).
   bool f32_lazy = false;
+  bool lazy_sticky = false;  // produced inside a recording: every replay rewrites the shadow only, so the f32
+                             // copy is refreshed on EVERY outside read, not just the first
   // Packed per-head f16 copy of this tensor as the shared KEYS of a batched attention product (the projected
   // positional table of a conformer layer is the same every step): built on first use, dropped with the shadow.
   void *hk16 = nullptr;
@@ -341,7 +343,11 @@ int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v
 __half *fa_shadow_block(fa_ctx *ctx, fa_tensor *t);
 __half *fa_shadow_hilo_block(fa_ctx *ctx, fa_tensor *t);
 int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out);
+// Called by in-place writers AFTER they made the f32 storage current (need_f32): from here on the f32 storage
+// is the truth again.
 static inline void fa_shadow_drop(fa_tensor *t) {
   t->a16_valid = false;
   t->hk16_valid = false;
+  t->f32_lazy = false;
+  t->lazy_sticky = false;
 }

@@ -196,6 +196,7 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
         if (ctx->lazy_f32 && !add) {  // ... and only as that: the f32 copy is made if and when something else reads it
           ep.skip_f32 = true;
           c->f32_lazy = true;
+          c->lazy_sticky = ctx->capturing != nullptr;
         }
       }
       rc = fa_tc_gemm_f16(ctx, a16, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);

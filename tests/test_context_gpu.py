@@ -121,3 +121,28 @@ def test_profiler_reports_labels_and_counts(ctx):
     prof = {e["label"]: e for e in ctx.endProfile()}
     assert prof["ewise"]["count"] == 2 and prof["transpose"]["count"] == 1
     assert all(e["ms"] >= 0 for e in prof.values())
+
+
+def test_recorded_hidden_layer_result_is_fresh_after_every_replay(ctx):
+    """A product with a fused activation recorded in a batch writes only its packed f16 form on replay; reading
+    its f32 values after each replay must see that replay's result, not the first one's."""
+    rng = np.random.default_rng(5)
+    M, K, N = 300, 256, 512
+    w = (rng.standard_normal((K, N)) / 16).astype(np.float16).astype(np.float32)
+    W = ctx.uploadF16(w, K, N)
+    host = ctx.pinnedArray(M * K)
+    a0 = rng.standard_normal((M, K)).astype(np.float32)
+    host[:] = a0.reshape(-1)
+
+    def body():
+        return ctx.matmul(ctx.upload(host, M, K), W, dict(act="relu"))
+
+    ctx.freeTensor(body())
+    batch, out = ctx.recordBatch(body)
+    for scale in (1.0, -2.0, 0.5):
+        host[:] = (a0 * scale).reshape(-1)
+        batch.launch()
+        got = ctx.download(out).reshape(M, N)
+        ref = np.maximum((a0 * scale).astype(np.float16).astype(np.float32) @ w, 0)
+        assert np.abs(got - ref).max() <= 2e-2 * max(1.0, float(np.abs(ref).max())), scale
+    batch.free()
