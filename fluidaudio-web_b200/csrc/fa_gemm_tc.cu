@@ -181,8 +181,14 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
       for (int j = 0; j < 16; j++) rs[j] = 1.0f;
     }
     if (p.add && n_ok && p.splitk <= 1) {
+      const float *arow = p.add + (size_t)(m0 + c) * p.N + n;
+      if (full_rows) {  // one base address, constant row stride: no per-row clamp and 64-bit multiply
 #pragma unroll
-      for (int j = 0; j < 16; j++) ad[j] = __ldg(p.add + (size_t)min(m0 + c + j, p.M - 1) * p.N + n);
+        for (int j = 0; j < 16; j++) ad[j] = __ldg(arow + (size_t)j * p.N);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) ad[j] = m0 + c + j < p.M ? __ldg(arow + (size_t)j * p.N) : 0.0f;
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 16; j++) ad[j] = 0.0f;
