@@ -62,6 +62,7 @@ SIGNATURES = {
     "fa_int8_gemm_i32": [P, P, I, P, I, I, P],
     "fa_matmul_int8_static": [P, P, P, P, P, I, P, I, I, I],
     "fa_layernorm": [P, P, P, P, C.c_float, PP],
+    "fa_layernorm_operand": [P, P, P, P, C.c_float, PP],
     "fa_softmax": [P, P, PP],
     "fa_conv1d": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
     "fa_conv1d_windows": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
@@ -84,6 +85,7 @@ SIGNATURES = {
     "fa_concat_rows": [P, PP, I, PP],
     "fa_sub_reshape": [P, P, I, I, I, PP],
     "fa_sub_reshape_windows": [P, P, I, I, I, I, PP],
+    "fa_conv_stem_windows": [P, P, P, P, P, P, P, P, I, I, I, I, PP],
     "fa_argmax_rows": [P, P, I, PP],
     "fa_embed_rows": [P, P, P, P, I, PP],
     "fa_unshard_cols": [P, P, I, PP],

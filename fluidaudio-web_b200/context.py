@@ -270,6 +270,12 @@ class CudaContext:
     def layernorm(self, x, gamma, beta, eps: float = 1e-5) -> Tensor:
         return self._op(self._lib.fa_layernorm, x.h, gamma.h, beta.h, eps)
 
+    def layernormOperand(self, x, gamma, beta, eps: float = 1e-5) -> Tensor:
+        """Optional member: layernorm whose result the caller only feeds to matmul as the row operand.  For
+        many-row inputs it is kept as the packed f16 operand alone; reading it any other way first fills its
+        f32 storage from that operand (values rounded to f16)."""
+        return self._op(self._lib.fa_layernorm_operand, x.h, gamma.h, beta.h, eps)
+
     def softmax(self, x) -> Tensor:
         return self._op(self._lib.fa_softmax, x.h)
 
@@ -330,6 +336,18 @@ class CudaContext:
     def subReshapeWindows(self, x, Cc: int, Tsub: int, F: int, W: int) -> Tensor:
         """subReshape over W windows at once: x [W, C*Tsub*F] -> [W*Tsub, C*F] (optional member)."""
         return self._op(self._lib.fa_sub_reshape_windows, x.h, Cc, Tsub, F, W)
+
+    def convStemWindows(self, x, layers, Cc: int, h: int, w: int, W: int) -> Optional[Tensor]:
+        """Optional member: the stem's first three layers (3x3 stride-2 conv from one channel + relu, 3x3 stride-2
+        depthwise, pointwise + relu) over W images x [W, h*w] in one call; `layers` = three dicts {"w", "b"}.
+        Returns [W, C*H2*W2], bit-identical to the three conv2dWindows calls, or None when the geometry is
+        outside the fused kernel's range (the caller then makes those calls)."""
+        out = C.c_void_p()
+        hs = []
+        for l in layers:
+            hs += [l["w"].h, self._h_of(l.get("b"))]
+        self._check(self._lib.fa_conv_stem_windows(self._h, x.h, *hs, Cc, h, w, W, C.byref(out)))
+        return self._wrap(out) if out.value else None
 
     # -- attention (compute.d.ts:189-199) ----------------------------------------------------------
     def bmmQK(self, q, b, qb, H: int, HD: int, W: int = 1, bShared: bool = False) -> Tensor:

@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(256) k_layernorm_warp(const float *__restrict_
       o.y = (v[u].y - mean) * inv * gg.y + bb.y;
       o.z = (v[u].z - mean) * inv * gg.z + bb.z;
       o.w = (v[u].w - mean) * inv * gg.w + bb.w;
-      ((float4 *)(y + (size_t)r * C))[q] = o;
+      if (y) ((float4 *)(y + (size_t)r * C))[q] = o;  // y == nullptr: the result exists only as the packed operand
       if (y16) {
         const int j = q * 4;
         __half2 *d16 = (__half2 *)(y16 + ((size_t)(j >> 6) * R + r) * 64 + (j & 63));
@@ -687,6 +687,118 @@ __global__ void __launch_bounds__(256) k_dwconv2d_3x3(const float *__restrict__ 
   }
 }
 
+// First two layers of the 8x subsampling stem in one pass, for 128-column images (128 mel bins):
+//   c1 = relu(conv 1->C, 3x3, stride 2, pad 1)   [C][H1][64]      (never stored)
+//   d  = depthwise 3x3, stride 2, pad 1 of c1     [C][H2][32]
+// written straight into the packed f16 layout Wp[n/128][k/64][n%128][k%64] (n = pixel y*32 + x, k = channel)
+// that the pointwise product after it streams as its [cin, H2*W2] operand.  Same accumulation order as
+// k_conv2d_c1_3x3 and k_dwconv2d_3x3 and the same f16 rounding as k_pack_w_f16, so the result is bit-identical
+// to running the three kernels; what disappears is the store and re-load of c1 (the largest tensor of the
+// forward) and of d.
+// CTA = 8 rows of d (two 128-pixel blocks) x 64 channels x one window.  The 35 input rows those need sit in shared
+// memory, zero padded; a lane owns a channel (its 20 weights stay in registers), a warp walks a 4-pixel-wide
+// column strip downwards, so every input read is a 16-byte shared-memory broadcast and each c1 row is evaluated
+// once per strip (the row shared by consecutive d rows is kept in registers).
+constexpr int kStemRows = 8, kStemInRows = 4 * kStemRows + 3, kStemLd = 132;
+__global__ void __launch_bounds__(256, 3) k_stem_c1_dw_pack(const float *__restrict__ x, const float *__restrict__ w0,
+                                                            const float *__restrict__ b0, const float *__restrict__ w1,
+                                                            const float *__restrict__ b1, __half *__restrict__ out, int H,
+                                                            int H1, int H2, int nblocks, int nch, size_t xstride,
+                                                            size_t slab) {
+  fa_grid_dep_sync();
+  extern __shared__ __align__(16) unsigned char stem_smem[];
+  float(*in_s)[kStemLd] = (float(*)[kStemLd])stem_smem;                                 // [35][4 zeros + 128]
+  __half *o_s = (__half *)(stem_smem + sizeof(float) * kStemInRows * kStemLd);          // [2][128][64]
+  const int y0 = blockIdx.x * kStemRows, cq = blockIdx.y, win = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  x += (size_t)win * xstride;
+  const int in_row0 = 4 * y0 - 3;
+  for (int e = threadIdx.x; e < kStemInRows * (kStemLd / 4); e += 256) {
+    const int r = e / (kStemLd / 4), q = e - r * (kStemLd / 4), hi = in_row0 + r;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (q > 0 && hi >= 0 && hi < H) v = __ldg((const float4 *)(x + (size_t)hi * 128) + (q - 1));
+    *(float4 *)&in_s[r][q * 4] = v;
+  }
+  const int cl = (warp & 1) * 32 + lane, c = cq * 64 + cl;
+  float wa[9], wb[9];
+#pragma unroll
+  for (int t = 0; t < 9; t++) {
+    wa[t] = __ldg(w0 + (size_t)c * 9 + t);
+    wb[t] = __ldg(w1 + (size_t)c * 9 + t);
+  }
+  const float ba = b0 ? __ldg(b0 + c) : 0.f, bb = b1 ? __ldg(b1 + c) : 0.f;
+  __syncthreads();
+
+  // one c1 row (9 columns 2*x0-1 .. 2*x0+7) of this lane's channel; rows outside the c1 image are the zero
+  // padding of the depthwise layer, and so is column -1
+  auto c1_row = [&](int r, int x0, float(&o)[9]) {
+    if (r < 0 || r >= H1) {
+#pragma unroll
+      for (int j = 0; j < 9; j++) o[j] = 0.f;
+      return;
+    }
+#pragma unroll
+    for (int j = 0; j < 9; j++) o[j] = ba;
+    const int sr = 2 * r - 1 - in_row0;
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+      float v[20];  // input columns 4*x0-4 .. 4*x0+15
+      const float4 *src = (const float4 *)&in_s[sr + a][4 * x0];
+#pragma unroll
+      for (int q = 0; q < 5; q++) {
+        const float4 t = src[q];
+        v[4 * q] = t.x, v[4 * q + 1] = t.y, v[4 * q + 2] = t.z, v[4 * q + 3] = t.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 9; j++)
+#pragma unroll
+        for (int t = 0; t < 3; t++) o[j] = fmaf(v[1 + 2 * j + t], wa[a * 3 + t], o[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 9; j++) o[j] = fmaxf(o[j], 0.0f);
+    if (x0 == 0) o[0] = 0.f;
+  };
+
+  for (int task = 0; task < 2; task++) {
+    const int x0 = ((warp >> 1) + task * 4) * 4;  // first d column of the strip
+    float prev[9], ra[9], rb[9];
+    c1_row(2 * y0 - 1, x0, prev);
+    for (int yl = 0; yl < kStemRows; yl++) {
+      const int y2 = y0 + yl;
+      __half *dst = o_s + ((size_t)(yl >> 2) * 128 + (yl & 3) * 32 + x0) * 64 + cl;
+      if (y2 >= H2) {  // rows past the image: the zero fill of the packed block
+#pragma unroll
+        for (int q = 0; q < 4; q++) dst[q * 64] = __float2half_rn(0.f);
+        continue;
+      }
+      c1_row(2 * y2, x0, ra);
+      c1_row(2 * y2 + 1, x0, rb);
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        float acc = bb;
+#pragma unroll
+        for (int t = 0; t < 3; t++) acc = fmaf(prev[2 * q + t], wb[t], acc);
+#pragma unroll
+        for (int t = 0; t < 3; t++) acc = fmaf(ra[2 * q + t], wb[3 + t], acc);
+#pragma unroll
+        for (int t = 0; t < 3; t++) acc = fmaf(rb[2 * q + t], wb[6 + t], acc);
+        dst[q * 64] = __float2half_rn(acc);
+      }
+#pragma unroll
+      for (int j = 0; j < 9; j++) prev[j] = rb[j];
+    }
+  }
+  __syncthreads();
+  out += (size_t)win * slab;
+  for (int half = 0; half < 2; half++) {
+    const int nb = (y0 >> 2) + half;
+    if (nb >= nblocks) break;
+    uint4 *dst = (uint4 *)(out + ((size_t)nb * nch + cq) * 128 * 64);
+    const uint4 *src = (const uint4 *)(o_s + (size_t)half * 128 * 64);
+    for (int e = threadIdx.x; e < 128 * 64 / 8; e += 256) dst[e] = src[e];
+  }
+}
+
 // The conformer conv module between its two pointwise projections, in the time-major layout the
 // projections use (src/engines/asr-parakeet/raw-encoder.js:340-362 does it as transpose -> glu ->
 // per-window depthwise conv1d(+act) -> transpose): x [W*T, 2D] -> y [W*T, D],
@@ -765,7 +877,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
     for (int kk = 0; kk < K; kk++) acc = fmaf(wk[kk], g[i + kk], acc);
     const float o = act == FA_ACT_SILU ? __fdividef(acc, 1.0f + __expf(-fminf(fmaxf(acc, -30.0f), 30.0f))) : fa_actf(acc, act);
     const int t = t0 + i;
-    y[(size_t)t * D + c] = o;
+    if (y) y[(size_t)t * D + c] = o;  // y == nullptr: the result exists only as the packed operand
     if (y16) y16[((size_t)(c >> 6) * rows + t) * 64 + (c & 63)] = __float2half_rn(o);
   }
 }
@@ -936,8 +1048,11 @@ int need_f32(fa_ctx *ctx, const fa_tensor *t, const char *op) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, name ": NULL argument");    \
   FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
 
-extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
-                            fa_tensor **out) {
+// operand_only: the caller promises the result is read as a matmul row operand.  When the packed f16 shadow can
+// carry it (single plane, warp-per-row kernel), the f32 store is skipped and the tensor is marked lazy: anything
+// else that reads it gets the f32 storage filled from the shadow first (values rounded to f16).
+static int layernorm_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
+                          bool operand_only, fa_tensor **out) {
   GLUE_PROLOGUE("layernorm");
   FA_TRY(need_f32(ctx, x, "layernorm"));
   FA_TRY(need_f32(ctx, gamma, "layernorm"));
@@ -965,11 +1080,17 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
           y->a16_valid = true;
         }
       }
+      float *yp = (float *)y->dptr;
+      if (operand_only && ctx->lazy_f32 && y16 && !lo_off && (x->cols & 3) == 0 && x->cols <= 1024 && al) {
+        yp = nullptr;
+        y->f32_lazy = true;
+        y->lazy_sticky = ctx->capturing != nullptr;
+      }
       if ((x->cols & 3) == 0 && x->cols <= 512 && al)
-        fa_launch_dep(ctx, k_layernorm_warp<4>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
+        fa_launch_dep(ctx, k_layernorm_warp<4>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, gp, bp, yp, y16, lo_off, x->rows,
                                                                           x->cols, eps);
       else if ((x->cols & 3) == 0 && x->cols <= 1024 && al)
-        fa_launch_dep(ctx, k_layernorm_warp<8>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows,
+        fa_launch_dep(ctx, k_layernorm_warp<8>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, gp, bp, yp, y16, lo_off, x->rows,
                                                                           x->cols, eps);
       else if (reg)
         fa_launch_dep(ctx, k_layernorm_reg<4>, dim3(x->rows), dim3(256), 0, xp, gp, bp, (float *)y->dptr, y16, lo_off, x->rows, x->cols, eps);
@@ -980,6 +1101,15 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
   }
   *out = y;
   return FA_OK;
+}
+
+extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
+                            fa_tensor **out) {
+  return layernorm_impl(ctx, x, gamma, beta, eps, false, out);
+}
+extern "C" int fa_layernorm_operand(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta,
+                                    float eps, fa_tensor **out) {
+  return layernorm_impl(ctx, x, gamma, beta, eps, true, out);
 }
 
 extern "C" int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {
@@ -1483,9 +1613,18 @@ extern "C" int fa_glu_dwconv_tm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor
       LaunchScope ls(ctx, "glu_dwconv_tm");
       const float *bp = bias ? (const float *)bias->dptr : nullptr;
       const int chunks = ceil_div(Tw, 16);
-      if (k == 9 && (long long)windows * chunks <= 65535)
-        fa_launch_dep(ctx, k_glu_dwconv_tm_k<9>, dim3(dim3(ceil_div(D, 256), windows * chunks)), dim3(256), 0, 
-            (const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr, y16, rows, Tw, D, pad_left, act, chunks);
+      if (k == 9 && (long long)windows * chunks <= 65535) {
+        // the module's next step is a product: above the hi/lo row limit the packed operand is all it reads, so
+        // the f32 result stays unwritten until something else asks for it
+        float *yp = (float *)y->dptr;
+        if (y16 && ctx->lazy_f32 && rows > ctx->f16_hilo_rows) {
+          yp = nullptr;
+          y->f32_lazy = true;
+          y->lazy_sticky = ctx->capturing != nullptr;
+        }
+        fa_launch_dep(ctx, k_glu_dwconv_tm_k<9>, dim3(dim3(ceil_div(D, 256), windows * chunks)), dim3(256), 0,
+            (const float *)x->dptr, (const float *)w->dptr, bp, yp, y16, rows, Tw, D, pad_left, act, chunks);
+      }
       else
         fa_launch_dep(ctx, k_glu_dwconv_tm, dim3(grid), dim3(256), 0, (const float *)x->dptr, (const float *)w->dptr, bp, (float *)y->dptr,
                                                        y16, rows, Tw, D, k, pad_left, act);
@@ -1606,6 +1745,81 @@ static int conv2d_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, cons
                                                            stride_w, pad_top, pad_left, Ho, Wo, groups, act);
   }
   FA_LAUNCH_CHECK(ctx, "conv2d");
+  *out = y;
+  return FA_OK;
+}
+
+// conv(1->C, 3x3, s2, p1, relu) -> depthwise(3x3, s2, p1) -> pointwise(C->C, relu): the head of the subsampling
+// stem as one member.  The first two layers run fused into the packed operand of the third (k_stem_c1_dw_pack),
+// which is the same tensor-core product conv2d_impl makes of a pointwise layer.  *out stays NULL when the
+// geometry is not the fused kernel's (image width 128, C a multiple of 64): the caller runs the three members.
+extern "C" int fa_conv_stem_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w0, const fa_tensor *b0,
+                                    const fa_tensor *w1, const fa_tensor *b1, const fa_tensor *w2, const fa_tensor *b2,
+                                    int C, int h, int w_, int windows, fa_tensor **out) {
+  GLUE_PROLOGUE("convStemWindows");
+  *out = nullptr;
+  FA_TRY(need_f32(ctx, x, "convStemWindows"));
+  FA_TRY(need_f32(ctx, w0, "convStemWindows"));
+  FA_TRY(need_f32(ctx, w1, "convStemWindows"));
+  FA_TRY(need_f32(ctx, w2, "convStemWindows"));
+  if (b0) FA_TRY(need_f32(ctx, b0, "convStemWindows"));
+  if (b1) FA_TRY(need_f32(ctx, b1, "convStemWindows"));
+  if (b2) FA_TRY(need_f32(ctx, b2, "convStemWindows"));
+  FA_REQUIRE(ctx, C > 0 && h > 0 && w_ > 0 && windows >= 1 && windows <= 65535, "convStemWindows: bad geometry");
+  FA_REQUIRE(ctx, x->rows == windows && (long long)x->cols >= (long long)h * w_, "convStemWindows: x is [%d,%d], need [%d, >= %d]",
+             x->rows, x->cols, windows, h * w_);
+  FA_REQUIRE(ctx, (long long)w0->rows * w0->cols >= (long long)C * 9 && (long long)w1->rows * w1->cols >= (long long)C * 9 &&
+                      (long long)w2->rows * w2->cols >= (long long)C * C,
+             "convStemWindows: weight tensor too small");
+  FA_REQUIRE(ctx, (!b0 || b0->rows * b0->cols >= C) && (!b1 || b1->rows * b1->cols >= C) && (!b2 || b2->rows * b2->cols >= C),
+             "convStemWindows: bias shorter than %d", C);
+  const int H1 = (h - 1) / 2 + 1, H2 = (H1 - 1) / 2 + 1, W2 = 32, P = H2 * W2;
+  const bool al = ((((uintptr_t)x->dptr) & 15) == 0) && (x->cols & 3) == 0;
+  // declined unless conv2d would also run the pointwise layer as the tensor-core product (same size rule)
+  if (w_ != 128 || (C & 63) || !fa_tc_available(ctx) || !al || ceil_div(H2, kStemRows) > 65535 || (C >> 6) > 65535 ||
+      P < 64 || (long long)C * C * P < (1ll << 21))
+    return FA_OK;
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, windows, C * P, FA_F32, true, &y));
+  void *xa = nullptr, *wa = nullptr;
+  size_t xb = 0, wb = 0;
+  const size_t slab = fa_tc_weight_bytes(P, C, 2);
+  int rc = fa_block_acquire(ctx, slab * windows, &xa, &xb);
+  if (rc == FA_OK) rc = fa_block_acquire(ctx, fa_tc_act_bytes(C, C, 2, 1), &wa, &wb);
+  if (rc == FA_OK) {
+    static bool attr_set[64] = {false};
+    const size_t smem = sizeof(float) * kStemInRows * kStemLd + sizeof(__half) * 2 * 128 * 64;
+    if (!attr_set[ctx->device & 63]) {
+      cudaFuncSetAttribute(k_stem_c1_dw_pack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      attr_set[ctx->device & 63] = true;
+    }
+    {
+      LaunchScope ls(ctx, "stem_c1_dw_pack");
+      fa_launch_dep(ctx, k_stem_c1_dw_pack, dim3(ceil_div(H2, kStemRows), C >> 6, windows), dim3(256), smem,
+                    (const float *)x->dptr, (const float *)w0->dptr, b0 ? (const float *)b0->dptr : nullptr,
+                    (const float *)w1->dptr, b1 ? (const float *)b1->dptr : nullptr, (__half *)xa, h, H1, H2,
+                    ceil_div(P, 128), fa_tc_chunks(C, 2), (size_t)x->cols, slab / sizeof(__half));
+    }
+    if (cudaGetLastError() != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "stem_c1_dw_pack: launch failed");
+  }
+  if (rc == FA_OK) rc = fa_prep_a_f16(ctx, (const float *)w2->dptr, C, C, (__half *)wa);
+  if (rc == FA_OK) {
+    TcEpilogue ep;
+    ep.rowbias = b2 ? (const float *)b2->dptr : nullptr;
+    ep.act = FA_ACT_RELU;
+    ep.batches = windows;
+    ep.a_shared = true;
+    ep.o_div = 1;
+    ep.o_hi = (long long)C * P;
+    ep.ldc = P;
+    rc = fa_tc_gemm_f16(ctx, (const __half *)wa, (const __half *)xa, (float *)y->dptr, C, P, C, ep);
+  }
+  if (xa) fa_block_release(ctx, xa);
+  if (wa) fa_block_release(ctx, wa);
+  if (rc != FA_OK) {
+    fa_free_tensor(ctx, y);
+    return rc;
+  }
   *out = y;
   return FA_OK;
 }

@@ -126,7 +126,15 @@ def pre_encode_windows(ctx, enc, mels):
     Hh, Wd = s.cols // melBins, melBins
     conv = [(Csub, 1, 3, 2, 1, "relu", True), (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False),
             (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False)]
+    first = 0
+    if hasattr(ctx, "convStemWindows"):  # optional member: layers 0-2 without storing the two largest feature maps
+        head = ctx.convStemWindows(s, enc["sub"]["conv"][:3], Csub, Hh, Wd, W)
+        if head is not None:
+            s, first = head, 3
+            Hh, Wd = ((Hh - 1) // 2 + 1 - 1) // 2 + 1, ((Wd - 1) // 2 + 1 - 1) // 2 + 1
     for i, (cout, cin, k, st, gr, act, s2) in enumerate(conv):
+        if i < first:
+            continue
         p = 1 if s2 else 0
         s = ctx.conv2dWindows(s, enc["sub"]["conv"][i]["w"], dict(cout=cout, cin=cin, h=Hh, w=Wd, kh=k, kw=k,
                                                                  bias=enc["sub"]["conv"][i]["b"], strideH=st, strideW=st,
@@ -162,8 +170,11 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
         enc["_pe"][Tsub] = peT
     dwPadL = dwPadR = (dwK - 1) >> 1
 
+    # a layernorm that only feeds products: optional member, keeps the result as the product's operand alone
+    ln_op = (lambda x, lp: ctx.layernormOperand(x, lp[0], lp[1])) if use_fast and hasattr(ctx, "layernormOperand") else ln
+
     def ff(x, lp, w1, w2, b1, b2):
-        return ctx.matmul(ctx.matmul(ln(x, lp), w1, dict(bias=b1, act="silu")), w2, dict(bias=b2, add=x))
+        return ctx.matmul(ctx.matmul(ln_op(x, lp), w1, dict(bias=b1, act="silu")), w2, dict(bias=b2, add=x))
 
     def body():
         nonlocal x
@@ -172,7 +183,7 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
             try:
                 w = enc["layers"][L]
                 x = ff(x, w["lnff1"], w["ff1w1"], w["ff1w2"], w["ff1b1"], w["ff1b2"])
-                xln = ln(x, w["lnatt"])
+                xln = ln_op(x, w["lnatt"])
                 q = ctx.matmul(xln, w["q"], dict(bias=w["qb"]))
                 k = ctx.matmul(xln, w["k"], dict(bias=w["kb"]))
                 v = ctx.matmul(xln, w["v"], dict(bias=w["vb"]))
@@ -192,7 +203,7 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                     probs = ctx.softmax(ctx.add(ac, bd))
                     outc = ctx.bmmPV(probs, v, H, HD, W)
                 x = ctx.matmul(outc, w["out"], dict(bias=w["outb"], add=x))
-                pre1 = ctx.matmul(ln(x, w["lnconv"]), w["pw1T"], dict(bias=w["pw1b"]))  # [W*T, 2D]
+                pre1 = ctx.matmul(ln_op(x, w["lnconv"]), w["pw1T"], dict(bias=w["pw1b"]))  # [W*T, 2D]
                 opts = dict(cout=D, k=dwK, groups=D, padLeft=dwPadL, padRight=dwPadR, bias=w["dwb"], act="silu")
                 if use_fast and hasattr(ctx, "gluDwConvTimeMajor"):  # optional member: the module's middle in one launch
                     dwoT = ctx.gluDwConvTimeMajor(pre1, w["dw"], opts, W)  # [W*T, D]

@@ -168,6 +168,11 @@ int fa_matmul_int8_static(fa_ctx *ctx, const float *a_dev, const void *wq_kn_dev
 /* ---- glue ops the encoder/decoder forwards call between GEMMs --------------- */
 int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
                  fa_tensor **out);                                                        /* layernorm :167 */
+/* Optional member layernormOperand: same arithmetic; the caller states that the result is only read as the row
+ * operand of matmul.  Above the f16_hilo_rows limit the result is then kept as the packed f16 operand alone and
+ * its f32 storage is filled from that (values rounded to f16) only if something else reads the tensor. */
+int fa_layernorm_operand(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
+                         fa_tensor **out);
 int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);                         /* softmax :168 */
 /* conv1d :172 — grouped/depthwise direct form (lib.rs:99-138); w = Cout*(Cin/groups)*K. */
 int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k, int stride,
@@ -216,6 +221,14 @@ int fa_conv2d_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const
                       int w_, int kh, int kw, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left,
                       int pad_right, int groups, int act, int windows, fa_tensor **out);
 int fa_sub_reshape_windows(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int F, int windows, fa_tensor **out);
+/* Optional member convStemWindows: the first three layers of the subsampling stem (raw-encoder.js:177-222) as one
+ * call: conv(1->C, 3x3, stride 2, pad 1, relu) -> depthwise(3x3, stride 2, pad 1) -> pointwise(C->C, relu) over
+ * x [windows, h*w]; returns [windows, C*H2*W2] with H2 = ceil(ceil(h/2)/2), W2 = w/4, bit-identical to the three
+ * conv2d_windows calls.  Biases may be NULL.  *out is NULL (and the call succeeds) when the geometry is outside
+ * the fused kernel's range (w == 128, C a multiple of 64): run the three members instead. */
+int fa_conv_stem_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w0, const fa_tensor *b0, const fa_tensor *w1,
+                         const fa_tensor *b1, const fa_tensor *w2, const fa_tensor *b2, int C, int h, int w_, int windows,
+                         fa_tensor **out);
 /* argmax over each row (host picks tokens from it; the reference does this on the host,
  * src/engines/asr-whisper/index.ts:80-97): out [rows,2] = {index, value}.  Only the first `ncols`
  * columns of each row take part (ncols <= 0: all of them) - the tied vocabulary projection is padded

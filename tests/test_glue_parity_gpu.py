@@ -33,6 +33,47 @@ def test_layernorm_softmax(ctx):
         close(ctx, ctx.softmax(x), ORA.softmax(xo), 1e-5)
 
 
+def test_layernorm_operand_is_the_f16_operand_of_the_same_layernorm(ctx):
+    """layernormOperand (optional member): identical to layernorm for few rows; for many rows the tensor is the
+    product's packed f16 operand (read-back = f16 rounding of layernorm's result) and a product of it equals the
+    product of the plain layernorm bit for bit, eagerly and when replayed from a recording."""
+    rng = np.random.default_rng(12)
+    for R, C in [(7, 64), (200, 1024), (130, 320), (90, 1500)]:
+        x, xo = up(ctx, rng.standard_normal((R, C)) * 3)
+        g, go = up(ctx, rng.standard_normal(C))
+        b, bo = up(ctx, rng.standard_normal(C))
+        plain = ctx.download(ctx.layernorm(x, g, b))
+        got = ctx.download(ctx.layernormOperand(x, g, b))
+        if R <= 64 or C > 1024 or C % 64:
+            assert np.array_equal(got, plain)
+        else:
+            assert np.array_equal(got, plain.astype(np.float16).astype(np.float32))
+    R, C, N = 200, 1024, 256
+    x, _ = up(ctx, rng.standard_normal((R, C)))
+    g, _ = up(ctx, rng.standard_normal(C))
+    b, _ = up(ctx, rng.standard_normal(C))
+    w = ctx.uploadF16((rng.standard_normal((C, N)) * 0.05).astype(np.float32), C, N)
+    want = ctx.download(ctx.matmul(ctx.layernorm(x, g, b), w))
+    assert np.array_equal(ctx.download(ctx.matmul(ctx.layernormOperand(x, g, b), w)), want)
+
+    host = ctx.pinnedArray(R * C)
+    host[:] = rng.standard_normal(R * C).astype(np.float32)
+
+    def body():
+        h = ctx.layernormOperand(ctx.upload(host, R, C), g, b)
+        return ctx.matmul(h, w), h
+
+    body()
+    batch, (y, h) = ctx.recordBatch(body)
+    for _ in range(2):
+        host[:] = rng.standard_normal(R * C).astype(np.float32)
+        batch.launch()
+        ln = ctx.layernorm(ctx.upload(host, R, C), g, b)
+        assert np.array_equal(ctx.download(y), ctx.download(ctx.matmul(ln, w)))
+        assert np.array_equal(ctx.download(h), ctx.download(ln).astype(np.float16).astype(np.float32))
+    batch.free()
+
+
 def test_elementwise_and_movement(ctx):
     rng = np.random.default_rng(1)
     a, ao = up(ctx, rng.standard_normal((37, 50)))
@@ -149,7 +190,17 @@ def test_conv_module_fast_members_match_the_op_sequence(ctx):
         ORA.setCols(ref, ORA.conv1d(ORA.sliceCols(gluo, wi * T, T), dwo_, dict(opts, bias=bo)), wi * T)
     glu = ctx.glu(ctx.transpose(pre1))
     close(ctx, ctx.conv1dWindows(glu, dw, dict(opts, bias=b), W), ref, 1e-4)
-    close(ctx, ctx.gluDwConvTimeMajor(pre1, dw, dict(opts, bias=b), W), ORA.transpose(ref), 1e-4)
+    # above the hi/lo row limit the fused member keeps its result as the next product's f16 operand alone: the f32
+    # read-back is that operand (f16 rounding of the exact result); with lazy_f32 off it stores the f32 result
+    lazy = ctx.gluDwConvTimeMajor(pre1, dw, dict(opts, bias=b), W)
+    ctx.setOption("lazy_f32", 0)
+    try:
+        exact = ctx.gluDwConvTimeMajor(pre1, dw, dict(opts, bias=b), W)
+    finally:
+        ctx.setOption("lazy_f32", 1)
+    close(ctx, exact, ORA.transpose(ref), 1e-4)
+    e = ctx.download(exact)
+    assert np.array_equal(ctx.download(lazy), e.astype(np.float16).astype(np.float32))
 
 
 def test_unshard_cols_matches_host_statement(ctx, pkg):
@@ -193,3 +244,27 @@ def test_sub_reshape_windows(ctx):
     for i in range(W):
         one = ctx.download(ctx.subReshape(ctx.upload(x[i], C, Tsub * F), C, Tsub, F)).reshape(Tsub, C * F)
         assert np.array_equal(got[i], one)
+
+
+@pytest.mark.parametrize("h,Cc,W,bias", [(70, 64, 3, True), (37, 128, 2, True), (131, 64, 1, False), (7, 256, 2, True)])
+def test_conv_stem_windows_equals_the_three_layer_sequence(ctx, h, Cc, W, bias):
+    """convStemWindows (optional member) against the conv2dWindows calls it replaces, bit for bit, over image
+    heights that leave ragged last row groups; and it declines geometries outside its kernel's range."""
+    rng = np.random.default_rng(h + Cc)
+    w = 128
+    x = ctx.upload(rng.standard_normal((W, h * w)).astype(np.float32), W, h * w)
+    mk = lambda n, s: ctx.upload((rng.standard_normal(n) * s).astype(np.float32), 1, n)
+    layers = [dict(w=mk(Cc * 9, 0.3), b=mk(Cc, 0.1) if bias else None), dict(w=mk(Cc * 9, 0.3), b=mk(Cc, 0.1) if bias else None),
+              dict(w=mk(Cc * Cc, 0.1), b=mk(Cc, 0.1) if bias else None)]
+    got = ctx.convStemWindows(x, layers, Cc, h, w, W)
+    assert got is not None
+    geo = [(1, 3, 2, 1, "relu", 1), (Cc, 3, 2, Cc, "none", 1), (Cc, 1, 1, 1, "relu", 0)]
+    s, Hh, Wd = x, h, w
+    for l, (cin, k, st, gr, act, p) in zip(layers, geo):
+        s = ctx.conv2dWindows(s, l["w"], dict(cout=Cc, cin=cin, h=Hh, w=Wd, kh=k, kw=k, bias=l["b"], strideH=st, strideW=st,
+                                              padTop=p, padBottom=p, padLeft=p, padRight=p, groups=gr, act=act), W)
+        Hh, Wd = (Hh + 2 * p - k) // st + 1, (Wd + 2 * p - k) // st + 1
+    assert (got.rows, got.cols) == (W, Cc * Hh * Wd)  # (conv2dWindows of one window is shaped [C, H*W] like conv2d)
+    assert np.array_equal(ctx.download(got).reshape(-1), ctx.download(s).reshape(-1))
+    x64 = ctx.upload(rng.standard_normal((W, h * 64)).astype(np.float32), W, h * 64)
+    assert ctx.convStemWindows(x64, layers, Cc, h, 64, W) is None  # not a 128-column image: declined
