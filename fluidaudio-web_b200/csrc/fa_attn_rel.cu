@@ -1,0 +1,281 @@
+// Relative-position self-attention of one conformer block in ONE kernel (the optional attnFused member,
+// src/gpu/compute.d.ts:247-248; op sequence of src/engines/asr-parakeet/raw-encoder.js:335-341):
+//   ac[i][j] = (q[i] + u) . k[j]          bd[i][p] = (q[i] + v) . pos[p]
+//   prob[i]  = softmax_j( ac[i][j] + bd[i][T-1-i+j] )          out[i] = sum_j prob[i][j] * v[j]
+// per (window, head), T <= 192 frames, head width 128.  The separate-op form stores ac and bd (36 + 72 MB per
+// block for 32 windows), reads them back for the shifted softmax and packs q, k, v and the probabilities into
+// GEMM operand layouts with four more kernels: seven launches that are all memory traffic around 9 GFLOP.
+// Here one CTA owns one (window, head): keys and the head's slice of the positional projection are converted to
+// f16 into shared memory once, each of the 12 warps owns 16 query rows and keeps their whole score row block
+// (16 x 192, f32) in registers, the positional scores of a 64-key block are computed for the 80 positions those
+// rows can reach, shifted through a per-warp staging tile (row r of the tile is read 15 - r columns to the
+// right) and added, the softmax runs on the registers, and the probabilities - rounded to f16 exactly as the
+// packed operand of the separate-op form is - multiply V from the same shared memory.  Operands f16,
+// accumulation f32 (mma.sync m16n8k16: the problem is 0.04 GFLOP per CTA and latency bound, a tcgen05 pipeline
+// with TMEM accumulators cannot shift rows by a per-row amount without the same round trip through shared memory).
+#include "fa_internal.cuh"
+
+namespace {
+
+constexpr int kAT = 192;          // keys / queries per (window, head), padded
+constexpr int kAHD = 128;         // head width
+constexpr int kALd = 136;         // shared-memory row pitch in halves: 272 B, conflict-free for ldmatrix
+constexpr int kAPosPad = 16;      // zero rows in front of positional row 0
+constexpr int kAPosRows = 400;    // 16 + (2*192 - 1) rounded up to whole 8-row matrices past the last read
+constexpr int kAStLd = 84;        // staging tile pitch in floats
+constexpr int kAWarps = 12;
+constexpr size_t kAKBytes = (size_t)kAT * kALd * 2, kAPBytes = (size_t)kAPosRows * kALd * 2,
+                 kAStBytes = (size_t)kAWarps * 16 * kAStLd * 4, kASmem = kAKBytes + kAPBytes + kAStBytes;
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const __half *p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], const __half *p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ uint32_t pack_h2(float x, float y) {
+  const __half2 h = __floats2half2_rn(x, y);
+  return *(const uint32_t *)&h;
+}
+
+// rows [0, nvalid) of src (row stride S floats, 128 columns) -> f16 rows [row0, row0 + nvalid) of dst; rows
+// [row0 + nvalid, row_end) and [0, row0) of the destination range are zero filled by the caller's ranges.
+__device__ __forceinline__ void fill_rows_f16(__half *dst, const float *__restrict__ src, int S, int nvalid, int nrows) {
+  for (int e = threadIdx.x; e < nrows * 32; e += kAWarps * 32) {
+    const int r = e >> 5, c = (e & 31) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nvalid) v = __ldg((const float4 *)(src + (size_t)r * S + c));
+    uint2 o;
+    o.x = pack_h2(v.x, v.y);
+    o.y = pack_h2(v.z, v.w);
+    *(uint2 *)(dst + (size_t)r * kALd + c) = o;
+  }
+}
+
+// A fragment (16 query rows x 16 head columns at k0) of q + bias, straight from the f32 projection.
+__device__ __forceinline__ void load_q_frag(uint32_t (&a)[4], const float *__restrict__ q0, const float *__restrict__ q1,
+                                            const float *__restrict__ bias, int k0, int t, bool ok0, bool ok1) {
+  const int c = k0 + 2 * t;
+  const float2 b0 = *(const float2 *)(bias + c), b1 = *(const float2 *)(bias + c + 8);
+  float2 x0 = make_float2(0.f, 0.f), x1 = x0, x2 = x0, x3 = x0;
+  if (ok0) {
+    x0 = *(const float2 *)(q0 + c);
+    x2 = *(const float2 *)(q0 + c + 8);
+  }
+  if (ok1) {
+    x1 = *(const float2 *)(q1 + c);
+    x3 = *(const float2 *)(q1 + c + 8);
+  }
+  a[0] = pack_h2(x0.x + b0.x, x0.y + b0.y);
+  a[1] = pack_h2(x1.x + b0.x, x1.y + b0.y);
+  a[2] = pack_h2(x2.x + b1.x, x2.y + b1.y);
+  a[3] = pack_h2(x3.x + b1.x, x3.y + b1.y);
+}
+
+__global__ void __launch_bounds__(kAWarps * 32, 1)
+    k_attn_rel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+               const float *__restrict__ pos, const float *__restrict__ pbu, const float *__restrict__ pbv,
+               float *__restrict__ out, __half *__restrict__ out16, int T, int H, int Mrows) {
+  fa_grid_dep_sync();
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  __half *Ks = (__half *)attn_smem;                              // [192][136]; V after the scores are done
+  __half *Ps = (__half *)(attn_smem + kAKBytes);                 // [400][136], positional row p at row p + 16
+  float *stage = (float *)(attn_smem + kAKBytes + kAPBytes);     // [12][16][84]
+  const int S = H * kAHD, w = blockIdx.x / H, h = blockIdx.x - w * H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int NP = 2 * T - 1;
+
+  fill_rows_f16(Ks, k + (size_t)w * T * S + h * kAHD, S, T, kAT);
+  for (int e = threadIdx.x; e < kAPosPad * 32; e += kAWarps * 32)
+    *(uint2 *)(Ps + (size_t)(e >> 5) * kALd + (e & 31) * 4) = make_uint2(0u, 0u);
+  fill_rows_f16(Ps + (size_t)kAPosPad * kALd, pos + h * kAHD, S, NP, kAPosRows - kAPosPad);
+  __syncthreads();
+
+  const int i0 = warp * 16, r0 = i0 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < T, ok1 = r1 < T;
+  const bool active = i0 < T;  // warps whose 16 rows all lie past T only help with the fills and the barriers
+  const float *q0 = q + ((size_t)w * T + (ok0 ? r0 : 0)) * S + h * kAHD;
+  const float *q1 = q + ((size_t)w * T + (ok1 ? r1 : 0)) * S + h * kAHD;
+  // ldmatrix row addresses: lane l names row l%8 of matrix l/8; matrices = (n tile 0|1) x (k half 0|1)
+  const int lm_row = (lane & 7) + ((lane >> 4) << 3), lm_col = ((lane >> 3) & 1) << 3;
+
+  float s[24][4];
+#pragma unroll
+  for (int n = 0; n < 24; n++) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+
+  // content scores: S = (q + u) K^T, 16 x 192 per warp
+  if (active) {
+    const float *bu = pbu + h * kAHD;
+    uint32_t a[4], an[4];
+    load_q_frag(a, q0, q1, bu, 0, t, ok0, ok1);
+#pragma unroll 1
+    for (int ks = 0; ks < 8; ks++) {
+      if (ks < 7) load_q_frag(an, q0, q1, bu, (ks + 1) * 16, t, ok0, ok1);
+      const __half *kb = Ks + (size_t)lm_row * kALd + ks * 16 + lm_col;
+#pragma unroll
+      for (int np = 0; np < 12; np++) {
+        uint32_t b[4];
+        ldsm4(b, kb + (size_t)np * 16 * kALd);
+        mma16816(s[2 * np], a, b[0], b[1]);
+        mma16816(s[2 * np + 1], a, b[2], b[3]);
+      }
+#pragma unroll
+      for (int x = 0; x < 4; x++) a[x] = an[x];
+    }
+  }
+  __syncthreads();  // every warp is done with the keys: their rows become V
+  fill_rows_f16(Ks, v + (size_t)w * T * S + h * kAHD, S, T, kAT);
+
+  // positional scores, one 64-key block at a time: the 80 positions p_lo .. p_lo+79 with
+  // p_lo = T - 16 - i0 + j0 cover bd[i][T-1-i+j] for the warp's 16 rows and the block's 64 keys
+  if (active) {
+    const float *bv = pbv + h * kAHD;
+    float *st = stage + (size_t)warp * 16 * kAStLd;
+#pragma unroll  // (unrolled so that s[] is indexed statically and stays in registers)
+    for (int jb = 0; jb < 3; jb++) {
+      float c[10][4];
+#pragma unroll
+      for (int n = 0; n < 10; n++) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+      const __half *pb = Ps + (size_t)(T - i0 + jb * 64 + lm_row) * kALd + lm_col;  // row (p_lo + 16) + ...
+      uint32_t a[4], an[4];
+      load_q_frag(a, q0, q1, bv, 0, t, ok0, ok1);
+#pragma unroll 1
+      for (int ks = 0; ks < 8; ks++) {
+        if (ks < 7) load_q_frag(an, q0, q1, bv, (ks + 1) * 16, t, ok0, ok1);
+#pragma unroll
+        for (int np = 0; np < 5; np++) {
+          uint32_t b[4];
+          ldsm4(b, pb + (size_t)np * 16 * kALd + ks * 16);
+          mma16816(c[2 * np], a, b[0], b[1]);
+          mma16816(c[2 * np + 1], a, b[2], b[3]);
+        }
+#pragma unroll
+        for (int x = 0; x < 4; x++) a[x] = an[x];
+      }
+#pragma unroll
+      for (int n = 0; n < 10; n++) {
+        *(float2 *)(st + g * kAStLd + 8 * n + 2 * t) = make_float2(c[n][0], c[n][1]);
+        *(float2 *)(st + (g + 8) * kAStLd + 8 * n + 2 * t) = make_float2(c[n][2], c[n][3]);
+      }
+      __syncwarp();
+      const float *s0 = st + g * kAStLd + 15 - g + 2 * t, *s1 = st + (g + 8) * kAStLd + 7 - g + 2 * t;
+#pragma unroll
+      for (int n = 0; n < 8; n++) {
+        float(&d)[4] = s[jb * 8 + n];
+        d[0] += s0[8 * n];
+        d[1] += s0[8 * n + 1];
+        d[2] += s1[8 * n];
+        d[3] += s1[8 * n + 1];
+      }
+      __syncwarp();
+    }
+  }
+
+  // softmax over the keys (columns j >= T masked), rows r0 and r1 of this thread's quad
+  uint32_t pf[12][4];
+  if (active) {
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 24; n++) {
+      const int j = 8 * n + 2 * t;
+      if (j >= T) s[n][0] = s[n][2] = -INFINITY;
+      if (j + 1 >= T) s[n][1] = s[n][3] = -INFINITY;
+      m0 = fmaxf(m0, fmaxf(s[n][0], s[n][1]));
+      m1 = fmaxf(m1, fmaxf(s[n][2], s[n][3]));
+    }
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+    float z0 = 0.f, z1 = 0.f;
+#pragma unroll
+    for (int n = 0; n < 24; n++) {
+      s[n][0] = __expf(s[n][0] - m0);
+      s[n][1] = __expf(s[n][1] - m0);
+      s[n][2] = __expf(s[n][2] - m1);
+      s[n][3] = __expf(s[n][3] - m1);
+      z0 += s[n][0] + s[n][1];
+      z1 += s[n][2] + s[n][3];
+    }
+    z0 += __shfl_xor_sync(0xffffffffu, z0, 1);
+    z0 += __shfl_xor_sync(0xffffffffu, z0, 2);
+    z1 += __shfl_xor_sync(0xffffffffu, z1, 1);
+    z1 += __shfl_xor_sync(0xffffffffu, z1, 2);
+    const float inv0 = 1.0f / z0, inv1 = 1.0f / z1;
+#pragma unroll
+    for (int kk = 0; kk < 12; kk++) {
+      pf[kk][0] = pack_h2(s[2 * kk][0] * inv0, s[2 * kk][1] * inv0);
+      pf[kk][1] = pack_h2(s[2 * kk][2] * inv1, s[2 * kk][3] * inv1);
+      pf[kk][2] = pack_h2(s[2 * kk + 1][0] * inv0, s[2 * kk + 1][1] * inv0);
+      pf[kk][3] = pack_h2(s[2 * kk + 1][2] * inv1, s[2 * kk + 1][3] * inv1);
+    }
+  }
+  __syncthreads();  // V is in place
+  if (!active) return;
+
+  // out = P V: 16 x 128 per warp
+  float o[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  {
+    // transposed loads: matrices = (key half 0|1) x (n tile 0|1)
+    const __half *vb = Ks + (size_t)((lane & 7) + (((lane >> 3) & 1) << 3)) * kALd + ((lane >> 4) << 3);
+#pragma unroll
+    for (int kk = 0; kk < 12; kk++) {
+#pragma unroll
+      for (int np = 0; np < 8; np++) {
+        uint32_t b[4];
+        ldsm4t(b, vb + (size_t)kk * 16 * kALd + np * 16);
+        mma16816(o[2 * np], pf[kk], b[0], b[1]);
+        mma16816(o[2 * np + 1], pf[kk], b[2], b[3]);
+      }
+    }
+  }
+  const size_t m0 = (size_t)w * T + r0, m1 = (size_t)w * T + r1;
+#pragma unroll
+  for (int n = 0; n < 16; n++) {
+    const int col = h * kAHD + 8 * n + 2 * t;
+    if (out) {
+      if (ok0) *(float2 *)(out + m0 * S + col) = make_float2(o[n][0], o[n][1]);
+      if (ok1) *(float2 *)(out + m1 * S + col) = make_float2(o[n][2], o[n][3]);
+    }
+    if (out16) {
+      __half *d = out16 + (size_t)(col >> 6) * Mrows * 64 + (col & 63);
+      if (ok0) *(__half2 *)(d + m0 * 64) = __floats2half2_rn(o[n][0], o[n][1]);
+      if (ok1) *(__half2 *)(d + m1 * 64) = __floats2half2_rn(o[n][2], o[n][3]);
+    }
+  }
+}
+
+}  // namespace
+
+bool fa_attn_rel_shape_ok(int T, int H, int HD, int W) {
+  return HD == kAHD && T >= 16 && T <= kAT && H >= 1 && W >= 1 && (long long)W * H <= 0x7fffffffll;
+}
+
+// out (f32 [W*T, H*HD]) may be NULL when out16 (the packed f16 row operand of the projection that follows) is given.
+int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
+                const float *pbv, float *out, __half *out16, int T, int H, int HD, int W) {
+  FA_REQUIRE(ctx, fa_attn_rel_shape_ok(T, H, HD, W) && (out || out16), "attnFused: shape outside the one-kernel form");
+  static bool attr_set[64] = {false};
+  if (!attr_set[ctx->device & 63]) {
+    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_attn_rel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kASmem));
+    attr_set[ctx->device & 63] = true;
+  }
+  {
+    LaunchScope ls(ctx, "attn_rel");
+    fa_launch_dep(ctx, k_attn_rel, dim3((unsigned)(W * H)), dim3(kAWarps * 32), kASmem, q, k, v, pos, pbu, pbv, out, out16, T, H,
+                  W * T);
+  }
+  FA_LAUNCH_CHECK(ctx, "attn_rel");
+  return FA_OK;
+}

@@ -123,6 +123,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->lazy_f32 = (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "attn_one_kernel")) {
+    FA_REQUIRE(ctx, value == 0 || value == 1, "attn_one_kernel must be 0 or 1 (got %lld)", value);
+    ctx->attn_one_kernel = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "pdl")) {
     FA_REQUIRE(ctx, value == 0 || value == 1, "pdl must be 0 or 1 (got %lld)", value);
     ctx->pdl = (int)value;

@@ -1081,7 +1081,7 @@ static int layernorm_impl(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamm
         }
       }
       float *yp = (float *)y->dptr;
-      if (operand_only && ctx->lazy_f32 && y16 && !lo_off && (x->cols & 3) == 0 && x->cols <= 1024 && al) {
+      if (operand_only && fa_operand_only_ok(ctx, x->rows, x->cols) && y16 && !lo_off && (x->cols & 3) == 0 && x->cols <= 1024 && al) {
         yp = nullptr;
         y->f32_lazy = true;
         y->lazy_sticky = ctx->capturing != nullptr;
@@ -1576,6 +1576,24 @@ extern "C" int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, W * T, S, FA_F32, true, &y));
   __half *y16 = (S & 63) == 0 && (HD & 31) == 0 ? fa_shadow_block(ctx, y) : nullptr;
+  if (ctx->attn_one_kernel && fa_attn_rel_shape_ok(T, H, HD, W)) {
+    // the result feeds the output projection: above the hi/lo row limit its packed operand is all that is written
+    float *yp = (float *)y->dptr;
+    if (y16 && fa_operand_only_ok(ctx, W * T, S)) {
+      yp = nullptr;
+      y->f32_lazy = true;
+      y->lazy_sticky = ctx->capturing != nullptr;
+    }
+    int rc1 = fa_attn_rel(ctx, (const float *)q->dptr, (const float *)k->dptr, (const float *)v->dptr, (const float *)pos->dptr,
+                          (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W);
+    if (rc1 != FA_OK) {
+      fa_free_tensor(ctx, y);
+      return rc1;
+    }
+    if (y16) y->a16_valid = true;
+    *out = y;
+    return FA_OK;
+  }
   bool done = false;
   int rc = fa_tc_attn_fused(ctx, (const float *)q->dptr, (const float *)k->dptr, (const float *)v->dptr,
                             (const float *)pos->dptr, const_cast<fa_tensor *>(pos), (const float *)pbu->dptr,
@@ -1617,7 +1635,7 @@ extern "C" int fa_glu_dwconv_tm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor
         // the module's next step is a product: above the hi/lo row limit the packed operand is all it reads, so
         // the f32 result stays unwritten until something else asks for it
         float *yp = (float *)y->dptr;
-        if (y16 && ctx->lazy_f32 && rows > ctx->f16_hilo_rows) {
+        if (y16 && fa_operand_only_ok(ctx, rows, D)) {
           yp = nullptr;
           y->f32_lazy = true;
           y->lazy_sticky = ctx->capturing != nullptr;

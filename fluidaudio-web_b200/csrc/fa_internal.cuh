@@ -103,6 +103,7 @@ struct fa_ctx {
   unsigned long long launches = 0;
   // options
   int int8_limbs = 2;
+  int attn_one_kernel = 1; // attnFused as the single mma kernel (fa_attn_rel.cu) when the shape allows, else the GEMM form
   int lazy_f32 = 1;        // hidden-layer products leave their f32 result unwritten until it is asked for
   int pdl = 1;             // programmatic dependent launch between the library's kernels (see fa_launch_dep)
   int nbits_fused = 0;     // 1: int4 products on the tensor cores unpack nibbles in shared memory (0: f16 copy, faster today)
@@ -336,6 +337,15 @@ int fa_tc_bmm_qk(fa_ctx *ctx, const float *q, const float *b, fa_tensor *b_cache
                  int W, int b_shared, bool *done);
 int fa_tc_bmm_pv(fa_ctx *ctx, const float *p, const float *v, float *out, __half *out16, int Tq, int Tk, int H, int HD,
                  int W, bool *done);
+// A producer whose result only feeds products may leave the f32 storage unwritten (fa_tensor::f32_lazy) when every
+// such product is sure to take the tensor-core route and read the packed f16 operand: more rows than the hi/lo
+// limit and rows x cols large enough that even a 64-column weight matrix passes the size rule of the router.
+static inline bool fa_operand_only_ok(const fa_ctx *ctx, int rows, int cols) {
+  return ctx->lazy_f32 && rows > ctx->f16_hilo_rows && cols >= 64 && (long long)rows * cols * 64 >= (1ll << 21);
+}
+bool fa_attn_rel_shape_ok(int T, int H, int HD, int W);
+int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
+                const float *pbv, float *out, __half *out16, int T, int H, int HD, int W);
 int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache, const float *pbu,
                      const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done);
 // Shadow management (fa_linalg.cu): block for t's packed f16 shadow (nullptr when t cannot carry one),

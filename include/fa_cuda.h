@@ -71,7 +71,9 @@ const char *fa_last_error(fa_ctx *ctx);
  * kernel's scheduling and prologue overlap its predecessor's tail; every such kernel waits for its
  * predecessors before touching their data; 0 = plain stream order), "lazy_f32" (0/1, default 1: the result of
  * a tensor-core product with a fused activation is written only as the packed f16 operand of the next product;
- * its f32 storage is filled from that, f16-rounded, the first time anything else reads it). */
+ * its f32 storage is filled from that, f16-rounded, the first time anything else reads it; the same holds for
+ * the results of layernormOperand, gluDwConvTimeMajor and attnFused), "attn_one_kernel" (0/1, default 1:
+ * attnFused runs as one kernel per call when head width is 128 and T <= 192; 0 = the batched-GEMM form). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);

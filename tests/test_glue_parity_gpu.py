@@ -38,13 +38,13 @@ def test_layernorm_operand_is_the_f16_operand_of_the_same_layernorm(ctx):
     product's packed f16 operand (read-back = f16 rounding of layernorm's result) and a product of it equals the
     product of the plain layernorm bit for bit, eagerly and when replayed from a recording."""
     rng = np.random.default_rng(12)
-    for R, C in [(7, 64), (200, 1024), (130, 320), (90, 1500)]:
+    for R, C in [(7, 64), (200, 1024), (130, 320), (90, 1500), (100, 64)]:
         x, xo = up(ctx, rng.standard_normal((R, C)) * 3)
         g, go = up(ctx, rng.standard_normal(C))
         b, bo = up(ctx, rng.standard_normal(C))
         plain = ctx.download(ctx.layernorm(x, g, b))
         got = ctx.download(ctx.layernormOperand(x, g, b))
-        if R <= 64 or C > 1024 or C % 64:
+        if R <= 64 or C > 1024 or C % 64 or R * C < 32768:  # too small for a sure tensor-core consumer: plain layernorm
             assert np.array_equal(got, plain)
         else:
             assert np.array_equal(got, plain.astype(np.float16).astype(np.float32))
@@ -179,7 +179,7 @@ def test_conv_module_fast_members_match_the_op_sequence(ctx):
     """conv1dWindows and gluDwConvTimeMajor (optional members) against the reference's per-window sequence
     transpose -> glu -> sliceCols/conv1d/setCols -> transpose run on the oracle."""
     rng = np.random.default_rng(6)
-    W, T, D, k = 3, 37, 128, 9
+    W, T, D, k = 3, 37, 512, 9
     pre1, pre1o = up(ctx, rng.standard_normal((W * T, 2 * D)))
     dw, dwo_ = up(ctx, rng.standard_normal(D * k) * 0.3)
     b, bo = up(ctx, rng.standard_normal(D) * 0.1)
@@ -190,7 +190,7 @@ def test_conv_module_fast_members_match_the_op_sequence(ctx):
         ORA.setCols(ref, ORA.conv1d(ORA.sliceCols(gluo, wi * T, T), dwo_, dict(opts, bias=bo)), wi * T)
     glu = ctx.glu(ctx.transpose(pre1))
     close(ctx, ctx.conv1dWindows(glu, dw, dict(opts, bias=b), W), ref, 1e-4)
-    # above the hi/lo row limit the fused member keeps its result as the next product's f16 operand alone: the f32
+    # when large enough that its consumer is a tensor-core product, the fused member keeps its result as that product's f16 operand alone: the f32
     # read-back is that operand (f16 rounding of the exact result); with lazy_f32 off it stores the f32 result
     lazy = ctx.gluDwConvTimeMajor(pre1, dw, dict(opts, bias=b), W)
     ctx.setOption("lazy_f32", 0)
@@ -268,3 +268,34 @@ def test_conv_stem_windows_equals_the_three_layer_sequence(ctx, h, Cc, W, bias):
     assert np.array_equal(ctx.download(got).reshape(-1), ctx.download(s).reshape(-1))
     x64 = ctx.upload(rng.standard_normal((W, h * 64)).astype(np.float32), W, h * 64)
     assert ctx.convStemWindows(x64, layers, Cc, h, 64, W) is None  # not a 128-column image: declined
+
+
+@pytest.mark.parametrize("W,H,T", [(3, 8, 188), (2, 2, 100), (1, 3, 192), (2, 1, 16), (1, 2, 57)])
+def test_attn_fused_matches_the_op_sequence(ctx, W, H, T):
+    """attnFused (optional member) in both of its forms - the one-kernel form and the batched-GEMM form - against
+    the reference's op sequence bmmQK x2 -> relShiftB -> add -> softmax -> bmmPV on the oracle; the result must also
+    work as the row operand of the projection that follows (it is stored as that operand alone by default)."""
+    rng = np.random.default_rng(W * 1000 + T)
+    HD, S = 128, H * 128
+    q, qo = up(ctx, rng.standard_normal((W * T, S)) * 0.3)
+    k, ko = up(ctx, rng.standard_normal((W * T, S)) * 0.3)
+    v, vo = up(ctx, rng.standard_normal((W * T, S)) * 0.5)
+    pos, poso = up(ctx, rng.standard_normal((2 * T - 1, S)) * 0.3)
+    pbu, pbuo = up(ctx, rng.standard_normal(S) * 0.1)
+    pbv, pbvo = up(ctx, rng.standard_normal(S) * 0.1)
+    aco = ORA.bmmQK(qo, ko, pbuo, H, HD, W)
+    bdo = ORA.relShiftB(ORA.bmmQK(qo, poso, pbvo, H, HD, W, True), W * H)
+    ref = ORA.bmmPV(ORA.softmax(ORA.add(aco, bdo)), vo, H, HD, W)
+    wout = (rng.standard_normal((S, 64)) * 0.05).astype(np.float32)
+    for one_kernel in (1, 0):
+        ctx.setOption("attn_one_kernel", one_kernel)
+        try:
+            got = ctx.attnFused(q, k, v, pos, pbu, pbv, H, HD, W)
+            if got is None:
+                assert one_kernel == 0  # the GEMM form may decline small shapes; the one-kernel form covers T in 16..192
+                continue
+            y = ctx.download(ctx.matmul(got, ctx.uploadF16(wout, S, 64))).reshape(W * T, 64)
+            close(ctx, got, ref, 3e-3)
+            assert np.abs(y - ref.array() @ wout.astype(np.float16).astype(np.float32)).max() <= 5e-3
+        finally:
+            ctx.setOption("attn_one_kernel", 1)
