@@ -22,7 +22,7 @@ constexpr int kAHD = 128;         // head width
 constexpr int kALd = 136;         // shared-memory row pitch in halves: 272 B, conflict-free for ldmatrix
 constexpr int kAPosPad = 16;      // zero rows in front of positional row 0
 constexpr int kAPosRows = 400;    // 16 + (2*192 - 1) rounded up to whole 8-row matrices past the last read
-constexpr int kAStLd = 84;        // staging tile pitch in floats
+constexpr int kAStLd = 88;        // staging tile pitch in floats (rows 0..3 / 4..7 of a 64-bit store land in distinct banks)
 constexpr int kAWarps = 12;
 constexpr size_t kAKBytes = (size_t)kAT * kALd * 2, kAPBytes = (size_t)kAPosRows * kALd * 2,
                  kAStBytes = (size_t)kAWarps * 16 * kAStLd * 4, kASmem = kAKBytes + kAPBytes + kAStBytes;
@@ -47,38 +47,53 @@ __device__ __forceinline__ uint32_t pack_h2(float x, float y) {
   return *(const uint32_t *)&h;
 }
 
-// rows [0, nvalid) of src (row stride S floats, 128 columns) -> f16 rows [row0, row0 + nvalid) of dst; rows
-// [row0 + nvalid, row_end) and [0, row0) of the destination range are zero filled by the caller's ranges.
+// rows [0, nvalid) of src (row stride S floats, 128 columns) -> f16 rows of dst, rows [nvalid, nrows) zero.
+// Eight 16-byte loads are in flight per thread before the first conversion: the fill is latency, not bandwidth.
 __device__ __forceinline__ void fill_rows_f16(__half *dst, const float *__restrict__ src, int S, int nvalid, int nrows) {
-  for (int e = threadIdx.x; e < nrows * 32; e += kAWarps * 32) {
-    const int r = e >> 5, c = (e & 31) * 4;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < nvalid) v = __ldg((const float4 *)(src + (size_t)r * S + c));
-    uint2 o;
-    o.x = pack_h2(v.x, v.y);
-    o.y = pack_h2(v.z, v.w);
-    *(uint2 *)(dst + (size_t)r * kALd + c) = o;
+  constexpr int U = 8, NT = kAWarps * 32;
+  const int total = nrows * 32;
+  for (int base = threadIdx.x; base < total; base += NT * U) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int e = base + u * NT, r = e >> 5, c = (e & 31) * 4;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < total && r < nvalid) v[u] = __ldg((const float4 *)(src + (size_t)r * S + c));
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int e = base + u * NT, r = e >> 5, c = (e & 31) * 4;
+      if (e < total) {
+        uint2 o;
+        o.x = pack_h2(v[u].x, v[u].y);
+        o.y = pack_h2(v[u].z, v[u].w);
+        *(uint2 *)(dst + (size_t)r * kALd + c) = o;
+      }
+    }
   }
 }
 
-// A fragment (16 query rows x 16 head columns at k0) of q + bias, straight from the f32 projection.
-__device__ __forceinline__ void load_q_frag(uint32_t (&a)[4], const float *__restrict__ q0, const float *__restrict__ q1,
-                                            const float *__restrict__ bias, int k0, int t, bool ok0, bool ok1) {
-  const int c = k0 + 2 * t;
-  const float2 b0 = *(const float2 *)(bias + c), b1 = *(const float2 *)(bias + c + 8);
-  float2 x0 = make_float2(0.f, 0.f), x1 = x0, x2 = x0, x3 = x0;
-  if (ok0) {
-    x0 = *(const float2 *)(q0 + c);
-    x2 = *(const float2 *)(q0 + c + 8);
+// The warp's 16 query rows plus a per-head bias vector as an f16 tile [16][kALd] (warp-private): a lane owns four
+// columns, eight rows are in flight at a time, every load instruction reads one 512-byte row.
+__device__ __forceinline__ void q_tile_f16(__half *dst, const float *__restrict__ qrows, const float *__restrict__ bias,
+                                           int S, int nvalid, int lane) {
+  const float4 bb = *(const float4 *)(bias + lane * 4);
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    float4 x[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      x[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (half * 8 + r < nvalid) x[r] = __ldg((const float4 *)(qrows + (size_t)(half * 8 + r) * S) + lane);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      uint2 o;
+      o.x = pack_h2(x[r].x + bb.x, x[r].y + bb.y);
+      o.y = pack_h2(x[r].z + bb.z, x[r].w + bb.w);
+      *(uint2 *)(dst + (size_t)(half * 8 + r) * kALd + lane * 4) = o;
+    }
   }
-  if (ok1) {
-    x1 = *(const float2 *)(q1 + c);
-    x3 = *(const float2 *)(q1 + c + 8);
-  }
-  a[0] = pack_h2(x0.x + b0.x, x0.y + b0.y);
-  a[1] = pack_h2(x1.x + b0.x, x1.y + b0.y);
-  a[2] = pack_h2(x2.x + b1.x, x2.y + b1.y);
-  a[3] = pack_h2(x3.x + b1.x, x3.y + b1.y);
 }
 
 __global__ void __launch_bounds__(kAWarps * 32, 1)
@@ -94,19 +109,26 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int NP = 2 * T - 1;
 
+  const int i0 = warp * 16, r0 = i0 + g, r1 = r0 + 8;
+  const bool ok0 = r0 < T, ok1 = r1 < T;
+  const bool active = i0 < T;  // warps whose 16 rows all lie past T only help with the fills and the barriers
+  const float *qrows = q + ((size_t)w * T + (active ? i0 : 0)) * S + h * kAHD;
+  const int qvalid = active ? min(16, T - i0) : 0;
+  float *st = stage + (size_t)warp * 16 * kAStLd;
+  __half *qu_tile = (__half *)st;                               // the staging tile is idle until the positional scores
+  __half *qv_tile = Ks + (size_t)warp * 16 * kALd;              // the key rows are idle after the content scores
+
   fill_rows_f16(Ks, k + (size_t)w * T * S + h * kAHD, S, T, kAT);
   for (int e = threadIdx.x; e < kAPosPad * 32; e += kAWarps * 32)
     *(uint2 *)(Ps + (size_t)(e >> 5) * kALd + (e & 31) * 4) = make_uint2(0u, 0u);
   fill_rows_f16(Ps + (size_t)kAPosPad * kALd, pos + h * kAHD, S, NP, kAPosRows - kAPosPad);
+  if (active) q_tile_f16(qu_tile, qrows, pbu + h * kAHD, S, qvalid, lane);
   __syncthreads();
 
-  const int i0 = warp * 16, r0 = i0 + g, r1 = r0 + 8;
-  const bool ok0 = r0 < T, ok1 = r1 < T;
-  const bool active = i0 < T;  // warps whose 16 rows all lie past T only help with the fills and the barriers
-  const float *q0 = q + ((size_t)w * T + (ok0 ? r0 : 0)) * S + h * kAHD;
-  const float *q1 = q + ((size_t)w * T + (ok1 ? r1 : 0)) * S + h * kAHD;
-  // ldmatrix row addresses: lane l names row l%8 of matrix l/8; matrices = (n tile 0|1) x (k half 0|1)
+  // ldmatrix row addresses: lane l names row l%8 of matrix l/8.  B operands: matrices = (n tile 0|1) x (k half 0|1);
+  // A operand: matrices = (k half 0|1) x (row half 0|1)
   const int lm_row = (lane & 7) + ((lane >> 4) << 3), lm_col = ((lane >> 3) & 1) << 3;
+  const int la_off = ((lane & 7) + (((lane >> 3) & 1) << 3)) * kALd + ((lane >> 4) << 3);
 
   float s[24][4];
 #pragma unroll
@@ -114,12 +136,10 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
 
   // content scores: S = (q + u) K^T, 16 x 192 per warp
   if (active) {
-    const float *bu = pbu + h * kAHD;
-    uint32_t a[4], an[4];
-    load_q_frag(a, q0, q1, bu, 0, t, ok0, ok1);
-#pragma unroll 1
+#pragma unroll 2
     for (int ks = 0; ks < 8; ks++) {
-      if (ks < 7) load_q_frag(an, q0, q1, bu, (ks + 1) * 16, t, ok0, ok1);
+      uint32_t a[4];
+      ldsm4(a, qu_tile + la_off + ks * 16);
       const __half *kb = Ks + (size_t)lm_row * kALd + ks * 16 + lm_col;
 #pragma unroll
       for (int np = 0; np < 12; np++) {
@@ -128,29 +148,27 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
         mma16816(s[2 * np], a, b[0], b[1]);
         mma16816(s[2 * np + 1], a, b[2], b[3]);
       }
-#pragma unroll
-      for (int x = 0; x < 4; x++) a[x] = an[x];
     }
   }
-  __syncthreads();  // every warp is done with the keys: their rows become V
-  fill_rows_f16(Ks, v + (size_t)w * T * S + h * kAHD, S, T, kAT);
+  __syncthreads();  // every warp is done with the keys: their rows hold the q + v tiles next, V after that
+  if (active) {
+    q_tile_f16(qv_tile, qrows, pbv + h * kAHD, S, qvalid, lane);
+    __syncwarp();
+  }
 
   // positional scores, one 64-key block at a time: the 80 positions p_lo .. p_lo+79 with
   // p_lo = T - 16 - i0 + j0 cover bd[i][T-1-i+j] for the warp's 16 rows and the block's 64 keys
   if (active) {
-    const float *bv = pbv + h * kAHD;
-    float *st = stage + (size_t)warp * 16 * kAStLd;
 #pragma unroll  // (unrolled so that s[] is indexed statically and stays in registers)
     for (int jb = 0; jb < 3; jb++) {
       float c[10][4];
 #pragma unroll
       for (int n = 0; n < 10; n++) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
       const __half *pb = Ps + (size_t)(T - i0 + jb * 64 + lm_row) * kALd + lm_col;  // row (p_lo + 16) + ...
-      uint32_t a[4], an[4];
-      load_q_frag(a, q0, q1, bv, 0, t, ok0, ok1);
-#pragma unroll 1
+#pragma unroll 2
       for (int ks = 0; ks < 8; ks++) {
-        if (ks < 7) load_q_frag(an, q0, q1, bv, (ks + 1) * 16, t, ok0, ok1);
+        uint32_t a[4];
+        ldsm4(a, qv_tile + la_off + ks * 16);
 #pragma unroll
         for (int np = 0; np < 5; np++) {
           uint32_t b[4];
@@ -158,8 +176,6 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
           mma16816(c[2 * np], a, b[0], b[1]);
           mma16816(c[2 * np + 1], a, b[2], b[3]);
         }
-#pragma unroll
-        for (int x = 0; x < 4; x++) a[x] = an[x];
       }
 #pragma unroll
       for (int n = 0; n < 10; n++) {
@@ -219,6 +235,8 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
       pf[kk][3] = pack_h2(s[2 * kk + 1][2] * inv1, s[2 * kk + 1][3] * inv1);
     }
   }
+  __syncthreads();  // every warp is done with its q + v tile
+  fill_rows_f16(Ks, v + (size_t)w * T * S + h * kAHD, S, T, kAT);
   __syncthreads();  // V is in place
   if (!active) return;
 
