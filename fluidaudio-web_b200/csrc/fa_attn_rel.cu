@@ -98,7 +98,7 @@ __device__ __forceinline__ void q_tile_f16(__half *dst, const float *__restrict_
 
 __global__ void __launch_bounds__(kAWarps * 32, 1)
     k_attn_rel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
-               const float *__restrict__ pos, const float *__restrict__ pbu, const float *__restrict__ pbv,
+               const __half *__restrict__ pos16, const float *__restrict__ pbu, const float *__restrict__ pbv,
                float *__restrict__ out, __half *__restrict__ out16, int T, int H, int Mrows) {
   fa_grid_dep_sync();
   extern __shared__ __align__(16) unsigned char attn_smem[];
@@ -118,10 +118,19 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
   __half *qu_tile = (__half *)st;                               // the staging tile is idle until the positional scores
   __half *qv_tile = Ks + (size_t)warp * 16 * kALd;              // the key rows are idle after the content scores
 
+  // the head's positional rows (already f16) go to shared memory as asynchronous 16-byte copies that nobody waits
+  // for until the content scores are done; the zero rows around them are plain stores
+  for (int e = threadIdx.x; e < NP * 16; e += kAWarps * 32) {
+    const int r = e >> 4, ch = e & 15;
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Ps + (size_t)(kAPosPad + r) * kALd + ch * 8);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(pos16 + (size_t)r * S + h * kAHD + ch * 8) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int e = threadIdx.x; e < (kAPosRows - NP) * 16; e += kAWarps * 32) {
+    const int r = e >> 4, ch = e & 15, row = r < kAPosPad ? r : NP + r;
+    *(uint4 *)(Ps + (size_t)row * kALd + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
   fill_rows_f16(Ks, k + (size_t)w * T * S + h * kAHD, S, T, kAT);
-  for (int e = threadIdx.x; e < kAPosPad * 32; e += kAWarps * 32)
-    *(uint2 *)(Ps + (size_t)(e >> 5) * kALd + (e & 31) * 4) = make_uint2(0u, 0u);
-  fill_rows_f16(Ps + (size_t)kAPosPad * kALd, pos + h * kAHD, S, NP, kAPosRows - kAPosPad);
   if (active) q_tile_f16(qu_tile, qrows, pbu + h * kAHD, S, qvalid, lane);
   __syncthreads();
 
@@ -150,7 +159,9 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
       }
     }
   }
-  __syncthreads();  // every warp is done with the keys: their rows hold the q + v tiles next, V after that
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncthreads();  // every warp is done with the keys (their rows hold the q + v tiles next, V after that) and
+                    // everybody's share of the positional rows has landed
   if (active) {
     q_tile_f16(qv_tile, qrows, pbv + h * kAHD, S, qvalid, lane);
     __syncwarp();
@@ -274,6 +285,28 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
   }
 }
 
+struct Block {  // pool block released at scope exit
+  fa_ctx *ctx;
+  void *p = nullptr;
+  size_t bytes = 0;
+  explicit Block(fa_ctx *c) : ctx(c) {}
+  int get(size_t need) { return fa_block_acquire(ctx, need, &p, &bytes); }
+  ~Block() {
+    if (p) fa_block_release(ctx, p);
+  }
+};
+
+__global__ void k_f32_to_f16(const float *__restrict__ x, __half *__restrict__ y, size_t n4) {
+  fa_grid_dep_sync();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = ((const float4 *)x)[i];
+    uint2 o;
+    o.x = pack_h2(v.x, v.y);
+    o.y = pack_h2(v.z, v.w);
+    ((uint2 *)y)[i] = o;
+  }
+}
+
 }  // namespace
 
 bool fa_attn_rel_shape_ok(int T, int H, int HD, int W) {
@@ -281,17 +314,51 @@ bool fa_attn_rel_shape_ok(int T, int H, int HD, int W) {
 }
 
 // out (f32 [W*T, H*HD]) may be NULL when out16 (the packed f16 row operand of the projection that follows) is given.
-int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
-                const float *pbv, float *out, __half *out16, int T, int H, int HD, int W) {
+// pos_cache (may be NULL): the tensor behind `pos`; its f16 copy is kept on it across calls (the projected positional
+// table of a layer is the same every step) unless the call is being recorded.
+int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache,
+                const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W) {
   FA_REQUIRE(ctx, fa_attn_rel_shape_ok(T, H, HD, W) && (out || out16), "attnFused: shape outside the one-kernel form");
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
     FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_attn_rel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kASmem));
     attr_set[ctx->device & 63] = true;
   }
+  const int NP = 2 * T - 1, S = H * HD;
+  const size_t halves = (size_t)NP * S;
+  Block tmp(ctx);
+  const __half *pos16 = nullptr;
+  const bool cacheable = pos_cache && !pos_cache->view;
+  if (cacheable && pos_cache->hk16_valid && pos_cache->hk_kind == 1 && pos_cache->hk_Tb == NP && pos_cache->hk_H == H &&
+      pos_cache->hk_HD == HD) {
+    pos16 = (const __half *)pos_cache->hk16;
+  } else {
+    __half *dst = nullptr;
+    if (cacheable && !ctx->capturing) {  // (a block taken while recording belongs to the recording)
+      if (pos_cache->hk16 && pos_cache->hk16_bytes < halves * 2) {
+        fa_block_release(ctx, pos_cache->hk16);
+        pos_cache->hk16 = nullptr;
+      }
+      if (!pos_cache->hk16) FA_TRY(fa_block_acquire(ctx, halves * 2, &pos_cache->hk16, &pos_cache->hk16_bytes));
+      pos_cache->hk_kind = 1, pos_cache->hk_Tb = NP, pos_cache->hk_H = H, pos_cache->hk_HD = HD;
+      pos_cache->hk16_valid = true;
+      dst = (__half *)pos_cache->hk16;
+    } else {
+      FA_TRY(tmp.get(halves * 2));
+      dst = (__half *)tmp.p;
+    }
+    {
+      LaunchScope ls(ctx, "attn_pos_f16");
+      const size_t n4 = halves / 4;
+      size_t gsz = (n4 + 255) / 256, cap = (size_t)ctx->sm_count * 8;
+      fa_launch_dep(ctx, k_f32_to_f16, dim3((unsigned)(gsz < cap ? gsz : cap)), dim3(256), 0, pos, dst, n4);
+    }
+    FA_LAUNCH_CHECK(ctx, "attn_pos_f16");
+    pos16 = dst;
+  }
   {
     LaunchScope ls(ctx, "attn_rel");
-    fa_launch_dep(ctx, k_attn_rel, dim3((unsigned)(W * H)), dim3(kAWarps * 32), kASmem, q, k, v, pos, pbu, pbv, out, out16, T, H,
+    fa_launch_dep(ctx, k_attn_rel, dim3((unsigned)(W * H)), dim3(kAWarps * 32), kASmem, q, k, v, pos16, pbu, pbv, out, out16, T, H,
                   W * T);
   }
   FA_LAUNCH_CHECK(ctx, "attn_rel");

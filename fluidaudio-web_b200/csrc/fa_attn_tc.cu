@@ -187,7 +187,7 @@ static int pack_keys(fa_ctx *ctx, const float *b, fa_tensor *b_cache, int Tb, in
   const int S = H * HD, nch = ceil_div(HD, 64), tiles_n = ceil_div(Tb, 128);
   const int wb = b_shared ? H : (int)batches;
   const bool cacheable = b_shared && b_cache && !b_cache->view;
-  const bool cached = cacheable && b_cache->hk16_valid && b_cache->hk_Tb == Tb && b_cache->hk_H == H && b_cache->hk_HD == HD;
+  const bool cached = cacheable && b_cache->hk16_valid && b_cache->hk_kind == 0 && b_cache->hk_Tb == Tb && b_cache->hk_H == H && b_cache->hk_HD == HD;
   if (cached) {
     *wpk = (const __half *)b_cache->hk16;
     return FA_OK;
@@ -198,7 +198,7 @@ static int pack_keys(fa_ctx *ctx, const float *b, fa_tensor *b_cache, int Tb, in
       b_cache->hk16 = nullptr;
     }
     if (!b_cache->hk16) FA_TRY(fa_block_acquire(ctx, w_halves * 2, &b_cache->hk16, &b_cache->hk16_bytes));
-    b_cache->hk_Tb = Tb, b_cache->hk_H = H, b_cache->hk_HD = HD;
+    b_cache->hk_kind = 0, b_cache->hk_Tb = Tb, b_cache->hk_H = H, b_cache->hk_HD = HD;
     b_cache->hk16_valid = true;
     *wpk = (const __half *)b_cache->hk16;
   } else {

@@ -1585,7 +1585,7 @@ extern "C" int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k
       y->lazy_sticky = ctx->capturing != nullptr;
     }
     int rc1 = fa_attn_rel(ctx, (const float *)q->dptr, (const float *)k->dptr, (const float *)v->dptr, (const float *)pos->dptr,
-                          (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W);
+                          const_cast<fa_tensor *>(pos), (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W);
     if (rc1 != FA_OK) {
       fa_free_tensor(ctx, y);
       return rc1;

@@ -49,6 +49,7 @@ struct fa_tensor {
   size_t hk16_bytes = 0;
   bool hk16_valid = false;
   int hk_Tb = 0, hk_H = 0, hk_HD = 0;
+  int hk_kind = 0;  // 0: per-head packed keys of the batched GEMM form; 1: plain row-major f16 copy (one-kernel attention)
 };
 
 struct fa_bytes {
@@ -344,8 +345,8 @@ static inline bool fa_operand_only_ok(const fa_ctx *ctx, int rows, int cols) {
   return ctx->lazy_f32 && rows > ctx->f16_hilo_rows && cols >= 64 && (long long)rows * cols * 64 >= (1ll << 21);
 }
 bool fa_attn_rel_shape_ok(int T, int H, int HD, int W);
-int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, const float *pbu,
-                const float *pbv, float *out, __half *out16, int T, int H, int HD, int W);
+int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache,
+                const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W);
 int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache, const float *pbu,
                      const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done);
 // Shadow management (fa_linalg.cu): block for t's packed f16 shadow (nullptr when t cannot carry one),
