@@ -72,6 +72,7 @@ SIGNATURES = {
     "fa_bmm_qk": [P, P, P, P, I, I, I, I, PP],
     "fa_bmm_pv": [P, P, P, I, I, I, PP],
     "fa_attn_fused": [P, P, P, P, P, P, P, I, I, I, PP],
+    "fa_attn_fused_qkv": [P, P, P, P, P, I, I, I, PP],
     "fa_rel_shift_b": [P, P, I, PP],
     "fa_ewise": [P, P, P, I, PP],
     "fa_scale": [P, P, C.c_float, PP],

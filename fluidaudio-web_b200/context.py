@@ -363,6 +363,13 @@ class CudaContext:
         self._check(self._lib.fa_attn_fused(self._h, q.h, k.h, v.h, pos.h, pbu.h, pbv.h, H, HD, W, C.byref(out)))
         return self._wrap(out) if out.value else None
 
+    def attnFusedQKV(self, qkv, pos, pbu, pbv, H: int, HD: int, W: int) -> Optional[Tensor]:
+        """Optional member: attnFused over one fused projection qkv [W*T, 3*H*HD] (q | k | v columns).  Returns
+        None outside the one-kernel form's range (HD == 128, 16 <= T <= 192)."""
+        out = C.c_void_p()
+        self._check(self._lib.fa_attn_fused_qkv(self._h, qkv.h, pos.h, pbu.h, pbv.h, H, HD, W, C.byref(out)))
+        return self._wrap(out) if out.value else None
+
     def relShift(self, x) -> Tensor:
         return self._op(self._lib.fa_rel_shift_b, x.h, 1)
 

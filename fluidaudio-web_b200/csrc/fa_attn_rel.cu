@@ -99,7 +99,7 @@ __device__ __forceinline__ void q_tile_f16(__half *dst, const float *__restrict_
 __global__ void __launch_bounds__(kAWarps * 32, 1)
     k_attn_rel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                const __half *__restrict__ pos16, const float *__restrict__ pbu, const float *__restrict__ pbv,
-               float *__restrict__ out, __half *__restrict__ out16, int T, int H, int Mrows) {
+               float *__restrict__ out, __half *__restrict__ out16, int T, int H, int Mrows, int ldq) {
   fa_grid_dep_sync();
   extern __shared__ __align__(16) unsigned char attn_smem[];
   __half *Ks = (__half *)attn_smem;                              // [192][136]; V after the scores are done
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
   const int i0 = warp * 16, r0 = i0 + g, r1 = r0 + 8;
   const bool ok0 = r0 < T, ok1 = r1 < T;
   const bool active = i0 < T;  // warps whose 16 rows all lie past T only help with the fills and the barriers
-  const float *qrows = q + ((size_t)w * T + (active ? i0 : 0)) * S + h * kAHD;
+  const float *qrows = q + ((size_t)w * T + (active ? i0 : 0)) * ldq + h * kAHD;  // q, k, v rows are ldq floats apart
   const int qvalid = active ? min(16, T - i0) : 0;
   float *st = stage + (size_t)warp * 16 * kAStLd;
   __half *qu_tile = (__half *)st;                               // the staging tile is idle until the positional scores
@@ -130,8 +130,8 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
     const int r = e >> 4, ch = e & 15, row = r < kAPosPad ? r : NP + r;
     *(uint4 *)(Ps + (size_t)row * kALd + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
   }
-  fill_rows_f16(Ks, k + (size_t)w * T * S + h * kAHD, S, T, kAT);
-  if (active) q_tile_f16(qu_tile, qrows, pbu + h * kAHD, S, qvalid, lane);
+  fill_rows_f16(Ks, k + (size_t)w * T * ldq + h * kAHD, ldq, T, kAT);
+  if (active) q_tile_f16(qu_tile, qrows, pbu + h * kAHD, ldq, qvalid, lane);
   __syncthreads();
 
   // ldmatrix row addresses: lane l names row l%8 of matrix l/8.  B operands: matrices = (n tile 0|1) x (k half 0|1);
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
   __syncthreads();  // every warp is done with the keys (their rows hold the q + v tiles next, V after that) and
                     // everybody's share of the positional rows has landed
   if (active) {
-    q_tile_f16(qv_tile, qrows, pbv + h * kAHD, S, qvalid, lane);
+    q_tile_f16(qv_tile, qrows, pbv + h * kAHD, ldq, qvalid, lane);
     __syncwarp();
   }
 
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
     }
   }
   __syncthreads();  // every warp is done with its q + v tile
-  fill_rows_f16(Ks, v + (size_t)w * T * S + h * kAHD, S, T, kAT);
+  fill_rows_f16(Ks, v + (size_t)w * T * ldq + h * kAHD, ldq, T, kAT);
   __syncthreads();  // V is in place
   if (!active) return;
 
@@ -314,11 +314,14 @@ bool fa_attn_rel_shape_ok(int T, int H, int HD, int W) {
 }
 
 // out (f32 [W*T, H*HD]) may be NULL when out16 (the packed f16 row operand of the projection that follows) is given.
+// q, k, v: rows ldq floats apart (H*HD for separate projections, 3*H*HD for the columns of one fused projection).
 // pos_cache (may be NULL): the tensor behind `pos`; its f16 copy is kept on it across calls (the projected positional
 // table of a layer is the same every step) unless the call is being recorded.
 int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache,
-                const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W) {
+                const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, int ldq) {
   FA_REQUIRE(ctx, fa_attn_rel_shape_ok(T, H, HD, W) && (out || out16), "attnFused: shape outside the one-kernel form");
+  FA_REQUIRE(ctx, ldq >= H * HD && (ldq & 3) == 0 && ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v)) & 15) == 0,
+             "attnFused: q/k/v rows must be 16-byte aligned");
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
     FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_attn_rel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kASmem));
@@ -359,7 +362,7 @@ int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, con
   {
     LaunchScope ls(ctx, "attn_rel");
     fa_launch_dep(ctx, k_attn_rel, dim3((unsigned)(W * H)), dim3(kAWarps * 32), kASmem, q, k, v, pos16, pbu, pbv, out, out16, T, H,
-                  W * T);
+                  W * T, ldq);
   }
   FA_LAUNCH_CHECK(ctx, "attn_rel");
   return FA_OK;

@@ -1585,7 +1585,7 @@ extern "C" int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k
       y->lazy_sticky = ctx->capturing != nullptr;
     }
     int rc1 = fa_attn_rel(ctx, (const float *)q->dptr, (const float *)k->dptr, (const float *)v->dptr, (const float *)pos->dptr,
-                          const_cast<fa_tensor *>(pos), (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W);
+                          const_cast<fa_tensor *>(pos), (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W, S);
     if (rc1 != FA_OK) {
       fa_free_tensor(ctx, y);
       return rc1;
@@ -1599,6 +1599,42 @@ extern "C" int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k
                             (const float *)pos->dptr, const_cast<fa_tensor *>(pos), (const float *)pbu->dptr,
                             (const float *)pbv->dptr, (float *)y->dptr, y16, T, H, HD, W, &done);
   if (rc != FA_OK || !done) {  // not this shape: the caller falls back to the separate ops (may return null)
+    fa_free_tensor(ctx, y);
+    return rc;
+  }
+  if (y16) y->a16_valid = true;
+  *out = y;
+  return FA_OK;
+}
+
+// attnFused over the columns of ONE fused projection qkv [W*T, 3*H*HD] (q | k | v side by side): the three
+// projections of the attention block as one product with the weights concatenated at load time.  One-kernel form
+// only; *out stays NULL when the shape is outside its range.
+extern "C" int fa_attn_fused_qkv(fa_ctx *ctx, const fa_tensor *qkv, const fa_tensor *pos, const fa_tensor *pbu,
+                                 const fa_tensor *pbv, int H, int HD, int W, fa_tensor **out) {
+  GLUE_PROLOGUE("attnFusedQKV");
+  *out = nullptr;
+  const fa_tensor *ts[4] = {qkv, pos, pbu, pbv};
+  for (int i = 0; i < 4; i++) FA_TRY(need_f32(ctx, ts[i], "attnFusedQKV"));
+  FA_REQUIRE(ctx, H > 0 && HD > 0 && W > 0 && qkv->rows % W == 0, "attnFusedQKV: bad geometry");
+  const int T = qkv->rows / W, S = H * HD;
+  FA_REQUIRE(ctx, qkv->cols == 3 * S && pos->cols == S && pos->rows == 2 * T - 1 && pbu->rows * pbu->cols >= S &&
+                      pbv->rows * pbv->cols >= S,
+             "attnFusedQKV: operand shapes do not match T=%d H=%d HD=%d W=%d", T, H, HD, W);
+  if (!ctx->attn_one_kernel || !fa_attn_rel_shape_ok(T, H, HD, W)) return FA_OK;  // declined
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, W * T, S, FA_F32, true, &y));
+  __half *y16 = (S & 63) == 0 ? fa_shadow_block(ctx, y) : nullptr;
+  float *yp = (float *)y->dptr;
+  if (y16 && fa_operand_only_ok(ctx, W * T, S)) {
+    yp = nullptr;
+    y->f32_lazy = true;
+    y->lazy_sticky = ctx->capturing != nullptr;
+  }
+  const float *base = (const float *)qkv->dptr;
+  int rc = fa_attn_rel(ctx, base, base + S, base + 2 * S, (const float *)pos->dptr, const_cast<fa_tensor *>(pos),
+                       (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W, 3 * S);
+  if (rc != FA_OK) {
     fa_free_tensor(ctx, y);
     return rc;
   }

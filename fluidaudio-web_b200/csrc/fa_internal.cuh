@@ -346,7 +346,7 @@ static inline bool fa_operand_only_ok(const fa_ctx *ctx, int rows, int cols) {
 }
 bool fa_attn_rel_shape_ok(int T, int H, int HD, int W);
 int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache,
-                const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W);
+                const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, int ldq);
 int fa_tc_attn_fused(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache, const float *pbu,
                      const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, bool *done);
 // Shadow management (fa_linalg.cu): block for t's packed f16 shadow (nullptr when t cannot carry one),

@@ -67,6 +67,24 @@ def load_encoder(ctx, weights: Dict[str, np.ndarray], cfg_override: Optional[dic
             dwb=vec(g("dwb")), pw2T=pwT(g("pw2"), D, D), pw1b=vec_opt(g("pw1b")), pw2b=vec_opt(g("pw2b")),
             lnff2=(vec(g("lnff2_w")), vec(g("lnff2_b"))), ff2w1=mat(g("ff2w1")), ff2w2=mat(g("ff2w2"), 0.5),
             ff2b1=vec_opt(g("ff2b1")), ff2b2=vec_opt(g("ff2b2"), 0.5), lnout=(vec(g("lnout_w")), vec(g("lnout_b")))))
+    if hasattr(ctx, "attnFusedQKV") and HD == 128:
+        # optional member: q | k | v as ONE projection (weights and biases side by side), consumed column-wise
+        for L, lw in enumerate(layers):
+            g = lambda s: f"L{L}_{s}"
+            cat = np.concatenate([weights[g("q")].astype(f32) * f32(INV), weights[g("k")].astype(f32),
+                                  weights[g("v")].astype(f32)], axis=1).astype(f32)
+            lw["qkv"] = ctx.uploadF16(np.ascontiguousarray(cat), cat.shape[0], cat.shape[1])
+            n = cat.shape[1] // 3
+            parts = [(g("qb"), INV), (g("kb"), None), (g("vb"), None)]
+            if any(k in weights for k, _ in parts):
+                b = np.zeros(3 * n, f32)
+                for i, (k, sc) in enumerate(parts):
+                    if k in weights:
+                        v = weights[k].astype(f32).reshape(-1)
+                        b[i * n:(i + 1) * n] = (v * f32(sc)).astype(f32) if sc is not None else v
+                lw["qkvb"] = ctx.upload(b, 1, b.size)
+            else:
+                lw["qkvb"] = None
     return dict(sub=sub, layers=layers, cfg=cfg, _pe={}, _posProj={})
 
 
@@ -184,9 +202,13 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                 w = enc["layers"][L]
                 x = ff(x, w["lnff1"], w["ff1w1"], w["ff1w2"], w["ff1b1"], w["ff1b2"])
                 xln = ln_op(x, w["lnatt"])
-                q = ctx.matmul(xln, w["q"], dict(bias=w["qb"]))
-                k = ctx.matmul(xln, w["k"], dict(bias=w["kb"]))
-                v = ctx.matmul(xln, w["v"], dict(bias=w["vb"]))
+                fused_qkv = use_fast and "qkv" in w and W * Tsub >= 256 and 16 <= Tsub <= 192
+                if fused_qkv:
+                    qkv = ctx.matmul(xln, w["qkv"], dict(bias=w["qkvb"]))
+                else:
+                    q = ctx.matmul(xln, w["q"], dict(bias=w["qb"]))
+                    k = ctx.matmul(xln, w["k"], dict(bias=w["kb"]))
+                    v = ctx.matmul(xln, w["v"], dict(bias=w["vb"]))
                 if W > 1:  # pos projection is constant per (layer, Tsub): cached across groups (:307-317)
                     p = enc["_posProj"].get((L, Tsub))
                     if p is None:
@@ -195,7 +217,12 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                 else:
                     p = ctx.matmul(peT, w["pos"])
                 outc = None
-                if use_fast and getattr(ctx, "attnFused", None):  # optional member, may decline (:333-336)
+                if fused_qkv:
+                    outc = ctx.attnFusedQKV(qkv, p, w["pbuAll"], w["pbvAll"], H, HD, W)
+                    if outc is None:  # declined: cut the columns apart and carry on with the separate members
+                        S = H * HD
+                        q, k, v = (ctx.sliceCols(qkv, i * S, S) for i in range(3))
+                if outc is None and use_fast and getattr(ctx, "attnFused", None):  # optional member, may decline (:333-336)
                     outc = ctx.attnFused(q, k, v, p, w["pbuAll"], w["pbvAll"], H, HD, W)
                 if outc is None:
                     ac = ctx.bmmQK(q, k, w["pbuAll"], H, HD, W)

@@ -202,6 +202,11 @@ int fa_bmm_pv(fa_ctx *ctx, const fa_tensor *p, const fa_tensor *v, int H, int HD
  * positional table, pbu/pbv [1, H*HD].  *out == NULL with status 0 means "not this shape". */
 int fa_attn_fused(fa_ctx *ctx, const fa_tensor *q, const fa_tensor *k, const fa_tensor *v, const fa_tensor *pos,
                   const fa_tensor *pbu, const fa_tensor *pbv, int H, int HD, int W, fa_tensor **out);
+/* Optional member attnFusedQKV: attnFused over the columns of one fused projection qkv [W*T, 3*H*HD] (q | k | v
+ * side by side, the three weight matrices concatenated at load time so that the projections are one product).
+ * *out is NULL (and the call succeeds) when the shape is outside the one-kernel form (HD == 128, 16 <= T <= 192). */
+int fa_attn_fused_qkv(fa_ctx *ctx, const fa_tensor *qkv, const fa_tensor *pos, const fa_tensor *pbu, const fa_tensor *pbv,
+                      int H, int HD, int W, fa_tensor **out);
 int fa_rel_shift_b(fa_ctx *ctx, const fa_tensor *x, int H, fa_tensor **out);              /* relShift/relShiftB :195-197 */
 int fa_ewise(fa_ctx *ctx, const fa_tensor *a, const fa_tensor *b, int op_mul, fa_tensor **out); /* ewise/add/mul :202-204 */
 int fa_scale(fa_ctx *ctx, const fa_tensor *x, float s, fa_tensor **out);                  /* scale :205 */

@@ -299,3 +299,8 @@ def test_attn_fused_matches_the_op_sequence(ctx, W, H, T):
             assert np.abs(y - ref.array() @ wout.astype(np.float16).astype(np.float32)).max() <= 5e-3
         finally:
             ctx.setOption("attn_one_kernel", 1)
+    # the same attention over the columns of one fused projection [q | k | v]: bit-identical to the separate tensors
+    one = ctx.attnFused(q, k, v, pos, pbu, pbv, H, HD, W)
+    cat = np.concatenate([ctx.download(x).reshape(W * T, S) for x in (q, k, v)], axis=1)
+    fused = ctx.attnFusedQKV(ctx.upload(cat, W * T, 3 * S), pos, pbu, pbv, H, HD, W)
+    assert fused is not None and np.array_equal(ctx.download(fused), ctx.download(one))
