@@ -52,8 +52,12 @@ class StagedRead:
     def __init__(self, ctx: "CudaContext", h: int, rows: int, cols: int):
         self._ctx, self._h, self._shape = ctx, h, (rows, cols)
 
-    def read(self) -> np.ndarray:
-        out = np.empty(self._shape[0] * self._shape[1], np.float32)
+    def read(self, out: Optional[np.ndarray] = None) -> np.ndarray:
+        """The snapshot, into `out` (a contiguous f32 array of the right size, e.g. one the caller reuses every
+        step) or a new array."""
+        if out is None:
+            out = np.empty(self._shape[0] * self._shape[1], np.float32)
+        assert out.dtype == np.float32 and out.flags["C_CONTIGUOUS"] and out.size >= self._shape[0] * self._shape[1]
         self._ctx._check(self._ctx._lib.fa_staged_read(self._ctx._h, self._h, out.ctypes.data))
         return out
 

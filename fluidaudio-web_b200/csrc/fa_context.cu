@@ -96,6 +96,7 @@ extern "C" int fa_ctx_destroy(fa_ctx *ctx) {
     if (s->done) cudaEventDestroy(s->done);
     delete s;
   }
+  for (auto &b : ctx->staged_free) cudaFreeHost(b.first);
   for (fa_graph *g : ctx->graphs) {
     if (g->exec) cudaGraphExecDestroy(g->exec);
     if (g->graph) cudaGraphDestroy(g->graph);
@@ -568,10 +569,26 @@ extern "C" int fa_stage_download(fa_ctx *ctx, const fa_tensor *t, fa_staged **ou
   FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
   fa_staged *s = new fa_staged();
   s->count = (size_t)t->rows * t->cols;
-  cudaError_t e = cudaMallocHost((void **)&s->host, s->count ? s->count * 4 : 4);
-  if (e != cudaSuccess) {
-    delete s;
-    return fa_fail(ctx, FA_ERR_OOM, "stageDownload: cudaMallocHost: %s", cudaGetErrorString(e));
+  const size_t need = s->count ? s->count * 4 : 4;
+  for (size_t i = 0; i < ctx->staged_free.size(); i++) {  // smallest free buffer that fits
+    if (ctx->staged_free[i].second >= need && (!s->host || ctx->staged_free[i].second < s->host_bytes)) {
+      s->host = ctx->staged_free[i].first;
+      s->host_bytes = ctx->staged_free[i].second;
+    }
+  }
+  if (s->host) {
+    for (size_t i = 0; i < ctx->staged_free.size(); i++)
+      if (ctx->staged_free[i].first == s->host) {
+        ctx->staged_free.erase(ctx->staged_free.begin() + i);
+        break;
+      }
+  } else {
+    cudaError_t e = cudaMallocHost((void **)&s->host, need);
+    if (e != cudaSuccess) {
+      delete s;
+      return fa_fail(ctx, FA_ERR_OOM, "stageDownload: cudaMallocHost: %s", cudaGetErrorString(e));
+    }
+    s->host_bytes = need;
   }
   ctx->staged.insert(s);
   if (s->count) {
@@ -595,8 +612,15 @@ extern "C" int fa_staged_read(fa_ctx *ctx, fa_staged *s, float *host_out) {
   FA_CHECK_CUDA(ctx, cudaEventSynchronize(s->done));
   if (s->count) memcpy(host_out, s->host, s->count * 4);
   s->consumed = true;
-  cudaFreeHost(s->host);  // staging storage is released on first read (compute.d.ts:39-42)
+  // staging storage is released on first read (compute.d.ts:39-42): back to the context's free list (at most four
+  // buffers are kept), and the event with it
+  if (ctx->staged_free.size() < 4)
+    ctx->staged_free.emplace_back(s->host, s->host_bytes);
+  else
+    cudaFreeHost(s->host);
   s->host = nullptr;
+  cudaEventDestroy(s->done);
+  s->done = nullptr;
   return FA_OK;
 }
 

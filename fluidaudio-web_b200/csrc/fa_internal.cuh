@@ -78,6 +78,7 @@ struct fa_staged {
   float *host = nullptr;     // page-locked snapshot target (f32)
   void *dev_tmp = nullptr;   // device f32 temp when the source is f16 storage
   size_t dev_tmp_bytes = 0;
+  size_t host_bytes = 0;     // capacity of `host` (it may come from the context's free list, larger than needed)
   size_t count = 0;
   cudaEvent_t done = nullptr;
   bool consumed = false;
@@ -124,6 +125,9 @@ struct fa_ctx {
   std::unordered_set<fa_tensor *> tensors;     // every live handle
   std::unordered_set<fa_bytes *> byte_handles;
   std::unordered_set<fa_staged *> staged;
+  // Page-locked staging buffers handed back by consumed reads, for the next stageDownload: allocating and freeing
+  // page-locked memory costs milliseconds and synchronises the device, which a read-back per step cannot afford.
+  std::vector<std::pair<float *, size_t>> staged_free;
   // profiling
   bool profiling = false;
   int profile_cap = 0;

@@ -66,3 +66,43 @@ def test_full_width_layer_teacher_forced(ctx, pkg):
     ctx.popArena(h)
     assert np.abs(got - ref).max() <= 2e-2
     assert np.abs(got_seq - ref).max() <= 2e-2
+
+
+def test_pipelined_encoder_returns_each_batch_in_order(ctx, pkg):
+    """PipelinedEncoder (two recorded forwards on two streams, used alternately) hands back, one call late, exactly
+    the frames encode_batch gives for the windows that were in the host buffers at submit time."""
+    fc, synth = _eng()
+    w = synth.encoder_weights(synth.TINY, seed=3)
+    dev = ctx.device
+    ctx, ctx2 = pkg.CudaContext(dev), pkg.CudaContext(dev)  # contexts of its own: recordings reserve pool blocks
+    try:
+        encs = [fc.load_encoder(ctx, w), fc.load_encoder(ctx2, w)]
+        audio = synth.synth_audio(6, samples=16000 * 2, seed=4)
+        mels = [fc.mel_time_major(synth.log_mel(a, 32).reshape(-1), 32) for a in audio]
+        n = mels[0].size
+        host = [[c.pinnedArray(n) for _ in range(2)] for c in (ctx, ctx2)]  # two windows per batch, per slot
+        for bufs in host:
+            for b, m in zip(bufs, mels[:2]):
+                b[:] = m
+        pipe = fc.PipelinedEncoder([ctx, ctx2], encs, lambda s: host[s], n)
+        want = []
+        got = []
+        for step in range(3):
+            pair = mels[2 * step:2 * step + 2]
+            for b, m in zip(host[step % 2], pair):
+                b[:] = m
+            h = ctx.pushArena()
+            ref, _ = fc.encode_batch(ctx, encs[0], [ctx.upload(m, 1, n) for m in pair])
+            want.append(ctx.download(ref))
+            ctx.popArena(h)
+            r = pipe.submit()
+            if r is not None:
+                got.append(r.copy())
+        got += pipe.flush()
+        pipe.free()
+        assert len(got) == 3
+        for g, r in zip(got, want):
+            assert np.array_equal(g, r)
+    finally:
+        ctx.destroy()
+        ctx2.destroy()
