@@ -324,6 +324,31 @@ __global__ void k_sub_reshape(const float *__restrict__ x, float *__restrict__ y
     y[i] = x[(size_t)c * Tsub * F + (size_t)ho * F + wo];
   }
 }
+// The same move four columns at a time (F % 4 == 0), also emitting the result as the packed f16 row operand
+// Ap[k/64][m][k%64] of the product that follows (m = window*Tsub + frame, k = c*F + f); y may be NULL when only
+// that operand is wanted.  Thread = one float4 of one output row; consecutive threads walk the output row.
+__global__ void __launch_bounds__(256) k_sub_reshape4(const float *__restrict__ x, float *__restrict__ y,
+                                                      __half *__restrict__ y16, int C, int Tsub, int F, size_t xstride,
+                                                      int rows) {
+  fa_grid_dep_sync();
+  const int CF4 = (C * F) >> 2, F4 = F >> 2;
+  const int m = blockIdx.y, wdw = m / Tsub, ho = m - wdw * Tsub;
+  const float *xw = x + (size_t)wdw * xstride + (size_t)ho * F;
+  for (int q = blockIdx.x * 256 + threadIdx.x; q < CF4; q += gridDim.x * 256) {
+    const int c = q / F4, f4 = q - c * F4;
+    const float4 v = __ldg((const float4 *)(xw + (size_t)c * Tsub * F) + f4);
+    if (y) ((float4 *)(y + (size_t)m * C * F))[q] = v;
+    if (y16) {
+      const int k = q * 4;
+      const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+      uint2 o;
+      o.x = *(const uint32_t *)&h0;
+      o.y = *(const uint32_t *)&h1;
+      *(uint2 *)(y16 + ((size_t)(k >> 6) * rows + m) * 64 + (k & 63)) = o;
+    }
+  }
+}
+
 // Batched rel_shift (wasm-context.js:525-538): x[H*t, 2t-1] -> [H*t, t].  With f = t + i*(2t-1) + j the
 // reference reads row f / 2t, column f % 2t - 1; for 0 <= i, j < t that is row i, column t-1-i+j (never
 // the zero column), so every output row is one contiguous run of its input row.
@@ -1376,6 +1401,31 @@ static int sub_reshape_impl(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, in
   fa_tensor *y = nullptr;
   FA_TRY(fa_tensor_new(ctx, windows * Tsub, C * F, FA_F32, true, &y));
   size_t n = (size_t)Tsub * C * F;
+  const int rows = windows * Tsub;
+  if ((F & 3) == 0 && rows <= 65535 && (x->cols & 3) == 0 && ((size_t)Tsub * F & 3) == 0 &&
+      ((((uintptr_t)x->dptr) | ((uintptr_t)y->dptr)) & 15) == 0) {
+    // the result is the row operand of the stem's linear layer: emit it as that (and, when the product is sure to
+    // read only that, as nothing else)
+    __half *y16 = nullptr;
+    float *yp = (float *)y->dptr;
+    if (((C * F) & 63) == 0 && fa_tc_available(ctx) && rows >= 16 && (y16 = fa_shadow_block(ctx, y)) != nullptr) {
+      y->a16_valid = true;
+      if (fa_operand_only_ok(ctx, rows, C * F)) {
+        yp = nullptr;
+        y->f32_lazy = true;
+        y->lazy_sticky = ctx->capturing != nullptr;
+      }
+    }
+    {
+      LaunchScope ls(ctx, "sub_reshape");
+      const int gx = ceil_div((C * F) >> 2, 256);
+      fa_launch_dep(ctx, k_sub_reshape4, dim3(gx < 8 ? gx : 8, rows), dim3(256), 0, (const float *)x->dptr, yp, y16, C, Tsub, F,
+                    windows == 1 ? (size_t)0 : (size_t)x->cols, rows);
+    }
+    FA_LAUNCH_CHECK(ctx, "sub_reshape");
+    *out = y;
+    return FA_OK;
+  }
   {
     LaunchScope ls(ctx, "sub_reshape");
     fa_launch_dep(ctx, k_sub_reshape, dim3(dim3(grid1d(ctx, n, 256), windows)), dim3(256), 0, (const float *)x->dptr, (float *)y->dptr, C,

@@ -246,6 +246,27 @@ def test_sub_reshape_windows(ctx):
         assert np.array_equal(got[i], one)
 
 
+@pytest.mark.parametrize("W,C,Tsub,F", [(3, 8, 21, 16), (2, 256, 47, 16), (1, 16, 10, 4)])
+def test_sub_reshape_vector_form_and_packed_operand(ctx, W, C, Tsub, F):
+    """F % 4 == 0 takes the four-column kernel, which also hands the result over as the packed f16 operand of the
+    linear layer (and, when large enough, as that alone): values against the host statement of the move, and a
+    product of the result against the product of an uploaded copy."""
+    rng = np.random.default_rng(C + Tsub)
+    x = rng.standard_normal((W, C * Tsub * F)).astype(np.float32)
+    want = x.reshape(W, C, Tsub, F).transpose(0, 2, 1, 3).reshape(W * Tsub, C * F)
+    xt = ctx.upload(x, W, x.shape[1]) if W > 1 else ctx.upload(x[0], C, Tsub * F)
+    got = ctx.subReshapeWindows(xt, C, Tsub, F, W) if W > 1 else ctx.subReshape(xt, C, Tsub, F)
+    g = ctx.download(got).reshape(W * Tsub, C * F)
+    lazy = W * Tsub > 64 and (C * F) % 64 == 0 and W * Tsub * C * F >= 32768
+    assert np.array_equal(g, want.astype(np.float16).astype(np.float32) if lazy else want)
+    if (C * F) % 64 == 0:
+        wl = ctx.uploadF16((rng.standard_normal((C * F, 128)) * 0.05).astype(np.float32), C * F, 128)
+        again = ctx.subReshapeWindows(xt, C, Tsub, F, W) if W > 1 else ctx.subReshape(xt, C, Tsub, F)
+        a = ctx.download(ctx.matmul(again, wl))
+        b = ctx.download(ctx.matmul(ctx.upload(want, W * Tsub, C * F), wl))
+        assert np.abs(a - b).max() <= (0 if W * Tsub > 64 else 2e-3)
+
+
 @pytest.mark.parametrize("h,Cc,W,bias", [(70, 64, 3, True), (37, 128, 2, True), (131, 64, 1, False), (7, 256, 2, True)])
 def test_conv_stem_windows_equals_the_three_layer_sequence(ctx, h, Cc, W, bias):
     """convStemWindows (optional member) against the conv2dWindows calls it replaces, bit for bit, over image
