@@ -240,6 +240,9 @@ class CudaContext:
     def matmul(self, a: Tensor, b: Tensor, opts: Optional[dict] = None, *, bias=None, act="none", add=None) -> Tensor:
         if opts:
             bias, act, add = opts.get("bias", bias), opts.get("act", act), opts.get("add", add)
+            if opts.get("operandOnly") and add is None:
+                # optional hint: the result is only read as a packed f16 operand (another matmul, attnFusedQKV)
+                return self._op(self._lib.fa_matmul_operand, a.h, b.h, self._h_of(bias), ACT[act])
         return self._op(self._lib.fa_matmul, a.h, b.h, self._h_of(bias), ACT[act], self._h_of(add))
 
     def matmulV2(self, a, b, opts: Optional[dict] = None, *, bias=None, act="none") -> Tensor:

@@ -96,6 +96,45 @@ __device__ __forceinline__ void q_tile_f16(__half *dst, const float *__restrict_
   }
 }
 
+// The same two moves when the projection arrives as the packed f16 row operand of a product, Xp[col/64][m][col%64]
+// (m = row of the [Mrows, *] projection): a row's 128 head columns are two 128-byte runs, so keys and values go to
+// shared memory as sixteen asynchronous 16-byte copies per row and the query tile needs one 8-byte load per lane.
+__device__ __forceinline__ void fill_rows_packed(__half *dst, const __half *__restrict__ src, int col0, size_t m0, int Mrows,
+                                                 int nvalid, int nrows) {
+  for (int e = threadIdx.x; e < nrows * 16; e += kAWarps * 32) {
+    const int r = e >> 4, ch = e & 15, col = col0 + ch * 8;
+    __half *d = dst + (size_t)r * kALd + ch * 8;
+    if (r < nvalid) {
+      const uint32_t da = (uint32_t)__cvta_generic_to_shared(d);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(da),
+                   "l"(src + ((size_t)(col >> 6) * Mrows + m0 + r) * 64 + (col & 63))
+                   : "memory");
+    } else {
+      *(uint4 *)d = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+__device__ __forceinline__ void q_tile_packed(__half *dst, const __half *__restrict__ src, int col0, size_t m0, int Mrows,
+                                              const float *__restrict__ bias, int nvalid, int lane) {
+  const float4 bb = *(const float4 *)(bias + lane * 4);
+  const int col = col0 + lane * 4;
+  const __half *base = src + ((size_t)(col >> 6) * Mrows + m0) * 64 + (col & 63);
+  uint2 x[16];
+#pragma unroll
+  for (int r = 0; r < 16; r++) x[r] = r < nvalid ? __ldg((const uint2 *)(base + (size_t)r * 64)) : make_uint2(0u, 0u);
+#pragma unroll
+  for (int r = 0; r < 16; r++) {
+    const float2 a = __half22float2(*(const __half2 *)&x[r].x), b = __half22float2(*(const __half2 *)&x[r].y);
+    uint2 o;
+    o.x = r < nvalid ? pack_h2(a.x + bb.x, a.y + bb.y) : 0u;
+    o.y = r < nvalid ? pack_h2(b.x + bb.z, b.y + bb.w) : 0u;
+    *(uint2 *)(dst + (size_t)r * kALd + lane * 4) = o;
+  }
+}
+
+// PACKED: q, k, v are column ranges [0,S), [S,2S), [2S,3S) of ONE projection stored as its packed f16 operand
+// (q points at it, k and v are unused, ldq is ignored); otherwise f32 rows ldq floats apart.
+template <bool PACKED>
 __global__ void __launch_bounds__(kAWarps * 32, 1)
     k_attn_rel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                const __half *__restrict__ pos16, const float *__restrict__ pbu, const float *__restrict__ pbv,
@@ -118,6 +157,12 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
   __half *qu_tile = (__half *)st;                               // the staging tile is idle until the positional scores
   __half *qv_tile = Ks + (size_t)warp * 16 * kALd;              // the key rows are idle after the content scores
 
+  const __half *qkv16 = (const __half *)q;
+  const size_t mw = (size_t)w * T;
+  if (PACKED) {  // the keys first: their copy group is the one the content scores wait for
+    fill_rows_packed(Ks, qkv16, S + h * kAHD, mw, Mrows, T, kAT);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   // the head's positional rows (already f16) go to shared memory as asynchronous 16-byte copies that nobody waits
   // for until the content scores are done; the zero rows around them are plain stores
   for (int e = threadIdx.x; e < NP * 16; e += kAWarps * 32) {
@@ -130,8 +175,13 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
     const int r = e >> 4, ch = e & 15, row = r < kAPosPad ? r : NP + r;
     *(uint4 *)(Ps + (size_t)row * kALd + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
   }
-  fill_rows_f16(Ks, k + (size_t)w * T * ldq + h * kAHD, ldq, T, kAT);
-  if (active) q_tile_f16(qu_tile, qrows, pbu + h * kAHD, ldq, qvalid, lane);
+  if (PACKED) {
+    if (active) q_tile_packed(qu_tile, qkv16, h * kAHD, mw + i0, Mrows, pbu + h * kAHD, qvalid, lane);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // the keys have landed, the positional rows may still fly
+  } else {
+    fill_rows_f16(Ks, k + (size_t)w * T * ldq + h * kAHD, ldq, T, kAT);
+    if (active) q_tile_f16(qu_tile, qrows, pbu + h * kAHD, ldq, qvalid, lane);
+  }
   __syncthreads();
 
   // ldmatrix row addresses: lane l names row l%8 of matrix l/8.  B operands: matrices = (n tile 0|1) x (k half 0|1);
@@ -163,7 +213,10 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
   __syncthreads();  // every warp is done with the keys (their rows hold the q + v tiles next, V after that) and
                     // everybody's share of the positional rows has landed
   if (active) {
-    q_tile_f16(qv_tile, qrows, pbv + h * kAHD, ldq, qvalid, lane);
+    if (PACKED)
+      q_tile_packed(qv_tile, qkv16, h * kAHD, mw + i0, Mrows, pbv + h * kAHD, qvalid, lane);
+    else
+      q_tile_f16(qv_tile, qrows, pbv + h * kAHD, ldq, qvalid, lane);
     __syncwarp();
   }
 
@@ -247,7 +300,13 @@ __global__ void __launch_bounds__(kAWarps * 32, 1)
     }
   }
   __syncthreads();  // every warp is done with its q + v tile
-  fill_rows_f16(Ks, v + (size_t)w * T * ldq + h * kAHD, ldq, T, kAT);
+  if (PACKED) {
+    fill_rows_packed(Ks, qkv16, 2 * S + h * kAHD, mw, Mrows, T, kAT);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else {
+    fill_rows_f16(Ks, v + (size_t)w * T * ldq + h * kAHD, ldq, T, kAT);
+  }
   __syncthreads();  // V is in place
   if (!active) return;
 
@@ -314,17 +373,19 @@ bool fa_attn_rel_shape_ok(int T, int H, int HD, int W) {
 }
 
 // out (f32 [W*T, H*HD]) may be NULL when out16 (the packed f16 row operand of the projection that follows) is given.
-// q, k, v: rows ldq floats apart (H*HD for separate projections, 3*H*HD for the columns of one fused projection).
+// q, k, v: rows ldq floats apart (H*HD for separate projections, 3*H*HD for the columns of one fused projection);
+// ldq == 0: q is the packed f16 row operand Xp[col/64][m][col%64] of the fused [W*T, 3*H*HD] projection (k, v unused).
 // pos_cache (may be NULL): the tensor behind `pos`; its f16 copy is kept on it across calls (the projected positional
 // table of a layer is the same every step) unless the call is being recorded.
 int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, const float *pos, fa_tensor *pos_cache,
                 const float *pbu, const float *pbv, float *out, __half *out16, int T, int H, int HD, int W, int ldq) {
   FA_REQUIRE(ctx, fa_attn_rel_shape_ok(T, H, HD, W) && (out || out16), "attnFused: shape outside the one-kernel form");
-  FA_REQUIRE(ctx, ldq >= H * HD && (ldq & 3) == 0 && ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v)) & 15) == 0,
+  FA_REQUIRE(ctx, ldq == 0 || (ldq >= H * HD && (ldq & 3) == 0 && ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v)) & 15) == 0),
              "attnFused: q/k/v rows must be 16-byte aligned");
   static bool attr_set[64] = {false};
   if (!attr_set[ctx->device & 63]) {
-    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_attn_rel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kASmem));
+    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_attn_rel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kASmem));
+    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_attn_rel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kASmem));
     attr_set[ctx->device & 63] = true;
   }
   const int NP = 2 * T - 1, S = H * HD;
@@ -361,8 +422,12 @@ int fa_attn_rel(fa_ctx *ctx, const float *q, const float *k, const float *v, con
   }
   {
     LaunchScope ls(ctx, "attn_rel");
-    fa_launch_dep(ctx, k_attn_rel, dim3((unsigned)(W * H)), dim3(kAWarps * 32), kASmem, q, k, v, pos16, pbu, pbv, out, out16, T, H,
-                  W * T, ldq);
+    if (ldq == 0)  // q is the packed f16 operand of the fused q|k|v projection
+      fa_launch_dep(ctx, k_attn_rel<true>, dim3((unsigned)(W * H)), dim3(kAWarps * 32), kASmem, q, k, v, pos16, pbu, pbv, out,
+                    out16, T, H, W * T, ldq);
+    else
+      fa_launch_dep(ctx, k_attn_rel<false>, dim3((unsigned)(W * H)), dim3(kAWarps * 32), kASmem, q, k, v, pos16, pbu, pbv, out,
+                    out16, T, H, W * T, ldq);
   }
   FA_LAUNCH_CHECK(ctx, "attn_rel");
   return FA_OK;

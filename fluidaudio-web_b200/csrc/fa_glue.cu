@@ -1664,8 +1664,12 @@ extern "C" int fa_attn_fused_qkv(fa_ctx *ctx, const fa_tensor *qkv, const fa_ten
                                  const fa_tensor *pbv, int H, int HD, int W, fa_tensor **out) {
   GLUE_PROLOGUE("attnFusedQKV");
   *out = nullptr;
-  const fa_tensor *ts[4] = {qkv, pos, pbu, pbv};
-  for (int i = 0; i < 4; i++) FA_TRY(need_f32(ctx, ts[i], "attnFusedQKV"));
+  FA_REQUIRE(ctx, fa_valid(ctx, qkv) && qkv->storage == FA_F32, "attnFusedQKV: qkv must be an f32-storage tensor");
+  // a projection that exists only as its packed f16 operand (matmul with the operand hint) is read as that
+  const bool packed = qkv->f32_lazy && qkv->a16_valid && !qkv->a16_hilo && qkv->a16 && !qkv->view;
+  if (!packed) FA_TRY(need_f32(ctx, qkv, "attnFusedQKV"));
+  const fa_tensor *ts[3] = {pos, pbu, pbv};
+  for (int i = 0; i < 3; i++) FA_TRY(need_f32(ctx, ts[i], "attnFusedQKV"));
   FA_REQUIRE(ctx, H > 0 && HD > 0 && W > 0 && qkv->rows % W == 0, "attnFusedQKV: bad geometry");
   const int T = qkv->rows / W, S = H * HD;
   FA_REQUIRE(ctx, qkv->cols == 3 * S && pos->cols == S && pos->rows == 2 * T - 1 && pbu->rows * pbu->cols >= S &&
@@ -1681,9 +1685,9 @@ extern "C" int fa_attn_fused_qkv(fa_ctx *ctx, const fa_tensor *qkv, const fa_ten
     y->f32_lazy = true;
     y->lazy_sticky = ctx->capturing != nullptr;
   }
-  const float *base = (const float *)qkv->dptr;
+  const float *base = packed ? (const float *)qkv->a16 : (const float *)qkv->dptr;
   int rc = fa_attn_rel(ctx, base, base + S, base + 2 * S, (const float *)pos->dptr, const_cast<fa_tensor *>(pos),
-                       (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W, 3 * S);
+                       (const float *)pbu->dptr, (const float *)pbv->dptr, yp, y16, T, H, HD, W, packed ? 0 : 3 * S);
   if (rc != FA_OK) {
     fa_free_tensor(ctx, y);
     return rc;

@@ -148,8 +148,10 @@ static int row_operand_f16(fa_ctx *ctx, const fa_tensor *a, const float *ap, Scr
   return FA_OK;
 }
 
-extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act,
-                         const fa_tensor *add, fa_tensor **out) {
+// operand_hint: the caller states that the result is only read as a packed f16 operand (by another product or by
+// attnFusedQKV), so it may be written as that alone even without a fused activation.
+static int matmul_impl(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act, const fa_tensor *add,
+                       bool operand_hint, fa_tensor **out) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmul: NULL argument");
   FA_REQUIRE(ctx, fa_valid(ctx, a) && fa_valid(ctx, b), "matmul: unknown tensor handle");
   const int M = a->rows, K = a->cols, N = b->cols;
@@ -191,7 +193,8 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
       ep.act = act;
       // A product with a fused activation is a hidden layer: its result goes straight into the next
       // product, so the epilogue also emits it as that product's packed f16 row operand.
-      if (act != FA_ACT_NONE && (N & 63) == 0 && (ep.out16 = fa_shadow_block(ctx, c)) != nullptr) {
+      const bool hinted = operand_hint && !add && fa_operand_only_ok(ctx, M, N);
+      if ((act != FA_ACT_NONE || hinted) && (N & 63) == 0 && (ep.out16 = fa_shadow_block(ctx, c)) != nullptr) {
         c->a16_valid = true;
         if (ctx->lazy_f32 && !add) {  // ... and only as that: the f32 copy is made if and when something else reads it
           ep.skip_f32 = true;
@@ -212,6 +215,15 @@ extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa
   }
   *out = c;
   return FA_OK;
+}
+
+extern "C" int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act,
+                         const fa_tensor *add, fa_tensor **out) {
+  return matmul_impl(ctx, a, b, bias, act, add, false, out);
+}
+extern "C" int fa_matmul_operand(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act,
+                                 fa_tensor **out) {
+  return matmul_impl(ctx, a, b, bias, act, nullptr, true, out);
 }
 
 // N-sharded product with the all-gather fused into the epilogue: this rank's block of output columns

@@ -204,7 +204,7 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                 xln = ln_op(x, w["lnatt"])
                 fused_qkv = use_fast and "qkv" in w and W * Tsub >= 256 and 16 <= Tsub <= 192
                 if fused_qkv:
-                    qkv = ctx.matmul(xln, w["qkv"], dict(bias=w["qkvb"]))
+                    qkv = ctx.matmul(xln, w["qkv"], dict(bias=w["qkvb"], operandOnly=True))  # read by attnFusedQKV only
                 else:
                     q = ctx.matmul(xln, w["q"], dict(bias=w["qb"]))
                     k = ctx.matmul(xln, w["k"], dict(bias=w["kb"]))

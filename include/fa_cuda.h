@@ -139,6 +139,10 @@ int fa_graph_free(fa_ctx *ctx, fa_graph *g);
  * f16 storage (uploadF16); routing is by shape and storage only. */
 int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act, const fa_tensor *add,
               fa_tensor **out);
+/* Optional member matmul(..., {operandOnly: true}): the caller states that the result is only read as a packed f16
+ * operand - by another matmul or by attnFusedQKV.  A tensor-core sized result is then written as that operand alone
+ * (f32 storage filled from it, f16-rounded, if anything else reads the tensor).  No residual input. */
+int fa_matmul_operand(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act, fa_tensor **out);
 /* matmulInt8 :164.  wq: int8 weights, byte index k*N+n (rust/wasm-kernels/src/lib.rs:141-142);
  * scale [1,N] per output column; y = act(scale[n]*sum_k a[m,k]*q[k,n] + bias[n]).
  * Large shapes run on int8 tensor cores: each activation row is split into `int8_limbs` int8

@@ -325,3 +325,16 @@ def test_attn_fused_matches_the_op_sequence(ctx, W, H, T):
     cat = np.concatenate([ctx.download(x).reshape(W * T, S) for x in (q, k, v)], axis=1)
     fused = ctx.attnFusedQKV(ctx.upload(cat, W * T, 3 * S), pos, pbu, pbv, H, HD, W)
     assert fused is not None and np.array_equal(ctx.download(fused), ctx.download(one))
+    # ... and over a projection that exists only as its packed f16 operand (matmul with the operandOnly hint)
+    if W * T > 64 and W * T * 3 * S * 64 >= (1 << 21):
+        xin = rng.standard_normal((W * T, 256)).astype(np.float32)
+        wcat = (rng.standard_normal((256, 3 * S)) * 0.02).astype(np.float32)  # unit-scale scores, as in the model
+        bcat, _ = up(ctx, rng.standard_normal(3 * S) * 0.1)
+        xt, wt = ctx.upload(xin, W * T, 256), ctx.uploadF16(wcat, 256, 3 * S)
+        plain = ctx.matmul(xt, wt, dict(bias=bcat))
+        hinted = ctx.matmul(xt, wt, dict(bias=bcat, operandOnly=True))
+        a = ctx.download(ctx.attnFusedQKV(plain, pos, pbu, pbv, H, HD, W))
+        b = ctx.download(ctx.attnFusedQKV(hinted, pos, pbu, pbv, H, HD, W))
+        assert np.abs(a - b).max() <= 3e-3 * max(1.0, float(np.abs(a).max()))
+        pl = ctx.download(plain)
+        assert np.array_equal(ctx.download(hinted), pl.astype(np.float16).astype(np.float32))
