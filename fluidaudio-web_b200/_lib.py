@@ -64,6 +64,7 @@ SIGNATURES = {
     "fa_matmul_int8_static": [P, P, P, P, P, I, P, I, I, I],
     "fa_layernorm": [P, P, P, P, C.c_float, PP],
     "fa_layernorm_operand": [P, P, P, P, C.c_float, PP],
+    "fa_layernorm_chain": [P, P, P, P, P, P, C.c_float, PP, PP],
     "fa_softmax": [P, P, PP],
     "fa_conv1d": [P, P, P, P, I, I, I, I, I, I, I, I, PP],
     "fa_conv1d_windows": [P, P, P, P, I, I, I, I, I, I, I, I, PP],

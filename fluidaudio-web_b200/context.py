@@ -283,6 +283,12 @@ class CudaContext:
         f32 storage from that operand (values rounded to f16)."""
         return self._op(self._lib.fa_layernorm_operand, x.h, gamma.h, beta.h, eps)
 
+    def layernormChain(self, x, g1, b1, g2, b2, eps: float = 1e-5):
+        """Optional member: (layernorm(x, g1, b1), layernormOperand(of that, g2, b2)) in one pass over the rows."""
+        y, z = C.c_void_p(), C.c_void_p()
+        self._check(self._lib.fa_layernorm_chain(self._h, x.h, g1.h, b1.h, g2.h, b2.h, eps, C.byref(y), C.byref(z)))
+        return self._wrap(y), self._wrap(z)
+
     def softmax(self, x) -> Tensor:
         return self._op(self._lib.fa_softmax, x.h)
 

@@ -136,9 +136,10 @@ __device__ __forceinline__ void act16(float (&v)[16], int act) {
       break;
     case FA_ACT_SILU:
 #pragma unroll
-      // ex2.approx + rcp.approx (a few ulp): the IEEE division here made the SiLU products epilogue-bound
-      // (84 us against 53 us for the same product without activation)
-      for (int j = 0; j < 16; j++) v[j] = __fdividef(v[j], 1.0f + __expf(-fminf(fmaxf(v[j], -30.0f), 30.0f)));
+      // one tanh.approx per element (fa_silu_fast).  The IEEE-division form made the SiLU products epilogue-bound
+      // (84 us against 53 us for the same product without activation); ex2.approx + rcp.approx still cost 8 us of
+      // special-function time per product.
+      for (int j = 0; j < 16; j++) v[j] = fa_silu_fast(v[j]);
       break;
     default:
 #pragma unroll
@@ -1062,6 +1063,10 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
         p.MT = cand;
       }
     }
+  }
+  if (const char *e = getenv("FA_TC_MT")) {  // measurement switch: force the tile height of multi-tile products
+    const int f = atoi(e);
+    if (M > mt_max && f >= 16 && f <= mt_max && (f & 15) == 0) p.MT = f;
   }
   // CTA pairs (cta_group::2) for large single-limb f16 products: halves the activation bytes each CTA stages.
   static const bool pair_enabled = getenv("FA_TC_PAIR") != nullptr;

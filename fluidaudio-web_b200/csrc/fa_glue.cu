@@ -197,6 +197,64 @@ __global__ void __launch_bounds__(256) k_layernorm_warp(const float *__restrict_
   }
 }
 
+// Two layernorms back to back on the same rows (the last one of a conformer block, then the first of the next
+// block, which only feeds a product): y = LN1(x) leaves as f32, z = LN2(y) as the packed f16 row operand alone.
+// The row never leaves the warp's registers in between, so z is bit-identical to layernorm of the stored y.
+template <int V4>
+__global__ void __launch_bounds__(256) k_layernorm_chain(const float *__restrict__ x, const float *__restrict__ g1,
+                                                         const float *__restrict__ b1, const float *__restrict__ g2,
+                                                         const float *__restrict__ b2, float *__restrict__ y,
+                                                         __half *__restrict__ z16, int R, int C, float eps) {
+  fa_grid_dep_sync();
+  const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5), c4 = C >> 2;
+  if (r >= R) return;
+  const float4 *row = (const float4 *)(x + (size_t)r * C);
+  float4 v[V4];
+#pragma unroll
+  for (int u = 0; u < V4; u++) {
+    const int q = lane + u * 32;
+    v[u] = q < c4 ? row[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int pass = 0; pass < 2; pass++) {
+    const float *g = pass ? g2 : g1, *b = pass ? b2 : b1;
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < V4; u++) s += (v[u].x + v[u].y) + (v[u].z + v[u].w);  // (lanes past the row hold zeros)
+    const float mean = warp_sum(s) / (float)C;
+    float vs = 0.f;
+#pragma unroll
+    for (int u = 0; u < V4; u++) {
+      if (lane + u * 32 < c4) {
+        const float a = v[u].x - mean, bb = v[u].y - mean, c = v[u].z - mean, d = v[u].w - mean;
+        vs += (a * a + bb * bb) + (c * c + d * d);
+      }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(vs) / (float)C + eps);
+#pragma unroll
+    for (int u = 0; u < V4; u++) {
+      const int q = lane + u * 32;
+      if (q < c4) {
+        const float4 gg = ((const float4 *)g)[q], bb = ((const float4 *)b)[q];
+        float4 o;
+        o.x = (v[u].x - mean) * inv * gg.x + bb.x;
+        o.y = (v[u].y - mean) * inv * gg.y + bb.y;
+        o.z = (v[u].z - mean) * inv * gg.z + bb.z;
+        o.w = (v[u].w - mean) * inv * gg.w + bb.w;
+        v[u] = o;
+        if (pass == 0) {
+          ((float4 *)(y + (size_t)r * C))[q] = o;
+        } else {
+          const int j = q * 4;
+          __half2 *d16 = (__half2 *)(z16 + ((size_t)(j >> 6) * R + r) * 64 + (j & 63));
+          d16[0] = __floats2half2_rn(o.x, o.y);
+          d16[1] = __floats2half2_rn(o.z, o.w);
+        }
+      }
+    }
+  }
+}
+
 // One warp per row (wasm-context.js:327-343).
 __global__ void k_softmax(const float *__restrict__ x, float *__restrict__ y, int R, int C) {
   fa_grid_dep_sync();
@@ -892,7 +950,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
 #pragma unroll
   for (int j = 0; j < 16 + K - 1; j++) {
     const int tg = t0 - padl + j;
-    g[j] = (tg >= lo && tg < hi) ? __fdividef(g[j], 1.0f + __expf(-gate[j])) : 0.f;
+    g[j] = (tg >= lo && tg < hi) ? g[j] * fa_sigmoid_fast(gate[j]) : 0.f;
   }
 #pragma unroll
   for (int i = 0; i < 16; i++) {
@@ -900,7 +958,7 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
     float acc = b;
 #pragma unroll
     for (int kk = 0; kk < K; kk++) acc = fmaf(wk[kk], g[i + kk], acc);
-    const float o = act == FA_ACT_SILU ? __fdividef(acc, 1.0f + __expf(-fminf(fmaxf(acc, -30.0f), 30.0f))) : fa_actf(acc, act);
+    const float o = act == FA_ACT_SILU ? fa_silu_fast(acc) : fa_actf(acc, act);
     const int t = t0 + i;
     if (y) y[(size_t)t * D + c] = o;  // y == nullptr: the result exists only as the packed operand
     if (y16) y16[((size_t)(c >> 6) * rows + t) * 64 + (c & 63)] = __float2half_rn(o);
@@ -1135,6 +1193,54 @@ extern "C" int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *ga
 extern "C" int fa_layernorm_operand(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta,
                                     float eps, fa_tensor **out) {
   return layernorm_impl(ctx, x, gamma, beta, eps, true, out);
+}
+
+// y = layernorm(x, g1, b1); z = layernormOperand(y, g2, b2) - in one pass over the rows when z can be kept as the
+// packed operand alone, as the two calls otherwise.
+extern "C" int fa_layernorm_chain(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *g1, const fa_tensor *b1,
+                                  const fa_tensor *g2, const fa_tensor *b2, float eps, fa_tensor **out_y, fa_tensor **out) {
+  GLUE_PROLOGUE("layernormChain");
+  if (!out_y) return fa_fail(ctx, FA_ERR_INVALID, "layernormChain: NULL argument");
+  const fa_tensor *ts[5] = {x, g1, b1, g2, b2};
+  for (int i = 0; i < 5; i++) FA_TRY(need_f32(ctx, ts[i], "layernormChain"));
+  for (int i = 1; i < 5; i++)
+    FA_REQUIRE(ctx, ts[i]->rows * ts[i]->cols >= x->cols, "layernormChain: gamma/beta shorter than %d columns", x->cols);
+  const bool al = ((((uintptr_t)x->dptr) | ((uintptr_t)g1->dptr) | ((uintptr_t)b1->dptr) | ((uintptr_t)g2->dptr) |
+                    ((uintptr_t)b2->dptr)) & 15) == 0;
+  if (!(al && (x->cols & 63) == 0 && x->cols <= 1024 && fa_tc_available(ctx) && fa_operand_only_ok(ctx, x->rows, x->cols))) {
+    FA_TRY(layernorm_impl(ctx, x, g1, b1, eps, false, out_y));
+    int rc = layernorm_impl(ctx, *out_y, g2, b2, eps, true, out);
+    if (rc != FA_OK) fa_free_tensor(ctx, *out_y);
+    return rc;
+  }
+  fa_tensor *y = nullptr, *z = nullptr;
+  FA_TRY(fa_tensor_new(ctx, x->rows, x->cols, FA_F32, true, &y));
+  int rc = fa_tensor_new(ctx, x->rows, x->cols, FA_F32, true, &z);
+  __half *z16 = rc == FA_OK ? fa_shadow_block(ctx, z) : nullptr;
+  if (rc != FA_OK || !z16 || ((((uintptr_t)y->dptr)) & 15)) {
+    if (z) fa_free_tensor(ctx, z);
+    fa_free_tensor(ctx, y);
+    return rc != FA_OK ? rc : fa_fail(ctx, FA_ERR_OOM, "layernormChain: no block for the packed operand");
+  }
+  z->a16_valid = true;
+  z->f32_lazy = true;
+  z->lazy_sticky = ctx->capturing != nullptr;
+  {
+    LaunchScope ls(ctx, "layernorm");
+    const float *xp = (const float *)x->dptr;
+    if (x->cols <= 512)
+      fa_launch_dep(ctx, k_layernorm_chain<4>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, (const float *)g1->dptr,
+                    (const float *)b1->dptr, (const float *)g2->dptr, (const float *)b2->dptr, (float *)y->dptr, z16, x->rows,
+                    x->cols, eps);
+    else
+      fa_launch_dep(ctx, k_layernorm_chain<8>, dim3(ceil_div(x->rows, 8)), dim3(256), 0, xp, (const float *)g1->dptr,
+                    (const float *)b1->dptr, (const float *)g2->dptr, (const float *)b2->dptr, (float *)y->dptr, z16, x->rows,
+                    x->cols, eps);
+  }
+  FA_LAUNCH_CHECK(ctx, "layernorm");
+  *out_y = y;
+  *out = z;
+  return FA_OK;
 }
 
 extern "C" int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out) {

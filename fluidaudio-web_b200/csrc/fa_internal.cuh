@@ -241,6 +241,21 @@ inline cudaError_t fa_launch_dep(fa_ctx *ctx, void (*kernel)(KArgs...), dim3 gri
 // ---- device helpers ----------------------------------------------------------------
 
 // Activation table of src/gpu/kernels/actf.js:5-22 (same clamps), f32.
+// SiLU and the logistic gate through ONE special-function instruction per element: x*sigmoid(x) = h + h*tanh(h)
+// with h = x/2, tanh.approx.f32 (error ~2^-11 of full scale, under the f16 rounding the results get as product
+// operands).  The exp + reciprocal form needs two, and the special-function unit (16 results per clock per SM)
+// is what the epilogue warps of a product with a fused SiLU wait on.
+__device__ __forceinline__ float fa_tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fa_silu_fast(float x) {
+  const float h = 0.5f * x;
+  return fmaf(h, fa_tanh_approx(h), h);
+}
+__device__ __forceinline__ float fa_sigmoid_fast(float x) { return fmaf(0.5f, fa_tanh_approx(0.5f * x), 0.5f); }
+
 __device__ __forceinline__ float fa_actf(float x, int a) {
   switch (a) {
     case FA_ACT_GELU: {

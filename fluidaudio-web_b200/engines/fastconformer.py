@@ -191,16 +191,22 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
     # a layernorm that only feeds products: optional member, keeps the result as the product's operand alone
     ln_op = (lambda x, lp: ctx.layernormOperand(x, lp[0], lp[1])) if use_fast and hasattr(ctx, "layernormOperand") else ln
 
-    def ff(x, lp, w1, w2, b1, b2):
-        return ctx.matmul(ctx.matmul(ln_op(x, lp), w1, dict(bias=b1, act="silu")), w2, dict(bias=b2, add=x))
+    def ff(x, lp, w1, w2, b1, b2, xn=None):
+        xn = ln_op(x, lp) if xn is None else xn
+        return ctx.matmul(ctx.matmul(xn, w1, dict(bias=b1, act="silu")), w2, dict(bias=b2, add=x))
+
+    # optional member: a block's last layernorm and the next block's first one in one pass over the rows
+    chain = use_fast and hasattr(ctx, "layernormChain")
 
     def body():
         nonlocal x
+        xff = None  # layernorm(x, lnff1) of the coming block when the previous block already made it
         for L in range(LAYERS):
             layerArena = ctx.pushArena()
             try:
                 w = enc["layers"][L]
-                x = ff(x, w["lnff1"], w["ff1w1"], w["ff1w2"], w["ff1b1"], w["ff1b2"])
+                x = ff(x, w["lnff1"], w["ff1w1"], w["ff1w2"], w["ff1b1"], w["ff1b2"], xff)
+                xff = None
                 xln = ln_op(x, w["lnatt"])
                 fused_qkv = use_fast and "qkv" in w and W * Tsub >= 256 and 16 <= Tsub <= 192
                 if fused_qkv:
@@ -247,7 +253,12 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                     dwoT = ctx.transpose(dwo)
                 x = ctx.matmul(dwoT, w["pw2T"], dict(bias=w["pw2b"], add=x))
                 x = ff(x, w["lnff2"], w["ff2w1"], w["ff2w2"], w["ff2b1"], w["ff2b2"])
-                x = ln(x, w["lnout"])
+                if chain and L + 1 < LAYERS:
+                    nxt = enc["layers"][L + 1]["lnff1"]
+                    x, xff = ctx.layernormChain(x, w["lnout"][0], w["lnout"][1], nxt[0], nxt[1])
+                    ctx.pin(xff, True)
+                else:
+                    x = ln(x, w["lnout"])
                 ctx.pin(x, True)  # x feeds the next layer: promote to the enclosing arena
                 if layer_hook is not None:
                     layer_hook(L, x)

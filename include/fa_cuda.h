@@ -179,6 +179,10 @@ int fa_layernorm(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const 
  * its f32 storage is filled from that (values rounded to f16) only if something else reads the tensor. */
 int fa_layernorm_operand(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *gamma, const fa_tensor *beta, float eps,
                          fa_tensor **out);
+/* Optional member layernormChain: y = layernorm(x, g1, b1) and z = layernormOperand(y, g2, b2) in one pass over the
+ * rows (the last layernorm of a conformer block and the first of the next); same values as the two calls. */
+int fa_layernorm_chain(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *g1, const fa_tensor *b1, const fa_tensor *g2,
+                       const fa_tensor *b2, float eps, fa_tensor **out_y, fa_tensor **out_z);
 int fa_softmax(fa_ctx *ctx, const fa_tensor *x, fa_tensor **out);                         /* softmax :168 */
 /* conv1d :172 — grouped/depthwise direct form (lib.rs:99-138); w = Cout*(Cin/groups)*K. */
 int fa_conv1d(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w, const fa_tensor *bias, int cout, int k, int stride,

@@ -74,6 +74,21 @@ def test_layernorm_operand_is_the_f16_operand_of_the_same_layernorm(ctx):
     batch.free()
 
 
+def test_layernorm_chain_equals_the_two_calls(ctx):
+    rng = np.random.default_rng(13)
+    for R, C in [(200, 1024), (130, 320), (9, 64), (70, 1500)]:
+        x, _ = up(ctx, rng.standard_normal((R, C)) * 2)
+        g1, _ = up(ctx, rng.standard_normal(C))
+        b1, _ = up(ctx, rng.standard_normal(C))
+        g2, _ = up(ctx, rng.standard_normal(C))
+        b2, _ = up(ctx, rng.standard_normal(C))
+        y, z = ctx.layernormChain(x, g1, b1, g2, b2)
+        y0 = ctx.layernorm(x, g1, b1)
+        z0 = ctx.layernormOperand(y0, g2, b2)
+        assert np.array_equal(ctx.download(y), ctx.download(y0))
+        assert np.array_equal(ctx.download(z), ctx.download(z0))
+
+
 def test_elementwise_and_movement(ctx):
     rng = np.random.default_rng(1)
     a, ao = up(ctx, rng.standard_normal((37, 50)))
