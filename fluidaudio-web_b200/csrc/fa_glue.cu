@@ -939,29 +939,46 @@ __global__ void __launch_bounds__(256) k_glu_dwconv_tm_k(const float *__restrict
   for (int kk = 0; kk < K; kk++) wk[kk] = w[(size_t)c * K + kk];
   const float b = bias ? bias[c] : 0.f;
   float g[16 + K - 1], gate[16 + K - 1];
-  // all loads first (addresses clamped into the window so none is conditional), then the gating math
+  const size_t ld = 2 * (size_t)D;
+  // a chunk whose 16 + K - 1 frames all lie inside the window (all but the first and last chunk of a window) needs
+  // no clamping, no zero taps and no ragged tail: one base address and constant strides
+  const bool interior = t0 - padl >= lo && t0 - padl + 16 + K - 1 <= hi;
+  if (interior) {
+    const float *xr = x + (size_t)(t0 - padl) * ld + c;
 #pragma unroll
-  for (int j = 0; j < 16 + K - 1; j++) {
-    const int tg = t0 - padl + j, tc = min(max(tg, lo), hi - 1);
-    const float *xr = x + (size_t)tc * (2 * D);
-    g[j] = __ldg(xr + c);
-    gate[j] = __ldg(xr + c + D);
-  }
+    for (int j = 0; j < 16 + K - 1; j++) {
+      g[j] = __ldg(xr + j * ld);
+      gate[j] = __ldg(xr + j * ld + D);
+    }
 #pragma unroll
-  for (int j = 0; j < 16 + K - 1; j++) {
-    const int tg = t0 - padl + j;
-    g[j] = (tg >= lo && tg < hi) ? g[j] * fa_sigmoid_fast(gate[j]) : 0.f;
+    for (int j = 0; j < 16 + K - 1; j++) g[j] *= fa_sigmoid_fast(gate[j]);
+  } else {
+    // all loads first (addresses clamped into the window so none is conditional), then the gating math
+#pragma unroll
+    for (int j = 0; j < 16 + K - 1; j++) {
+      const int tg = t0 - padl + j, tc = min(max(tg, lo), hi - 1);
+      const float *xr = x + (size_t)tc * ld;
+      g[j] = __ldg(xr + c);
+      gate[j] = __ldg(xr + c + D);
+    }
+#pragma unroll
+    for (int j = 0; j < 16 + K - 1; j++) {
+      const int tg = t0 - padl + j;
+      g[j] = (tg >= lo && tg < hi) ? g[j] * fa_sigmoid_fast(gate[j]) : 0.f;
+    }
   }
+  float *yr = y ? y + (size_t)t0 * D + c : nullptr;  // y == nullptr: the result exists only as the packed operand
+  __half *y16r = y16 ? y16 + ((size_t)(c >> 6) * rows + t0) * 64 + (c & 63) : nullptr;
+  const bool silu = act == FA_ACT_SILU;
 #pragma unroll
   for (int i = 0; i < 16; i++) {
-    if (i >= nt) break;
+    if (!interior && i >= nt) break;
     float acc = b;
 #pragma unroll
     for (int kk = 0; kk < K; kk++) acc = fmaf(wk[kk], g[i + kk], acc);
-    const float o = act == FA_ACT_SILU ? fa_silu_fast(acc) : fa_actf(acc, act);
-    const int t = t0 + i;
-    if (y) y[(size_t)t * D + c] = o;  // y == nullptr: the result exists only as the packed operand
-    if (y16) y16[((size_t)(c >> 6) * rows + t) * 64 + (c & 63)] = __float2half_rn(o);
+    const float o = silu ? fa_silu_fast(acc) : fa_actf(acc, act);
+    if (yr) yr[(size_t)i * D] = o;
+    if (y16r) y16r[i * 64] = __float2half_rn(o);
   }
 }
 
