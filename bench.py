@@ -496,8 +496,9 @@ class Encoder:
                 "avg_launch_us": round(e["ms"] / e["count"] * 1e3, 2), "peak_source": peaks["source"] + " (sustained bf16)"}
 
     def roofline_live(self, ctx, peaks, timer):
-        """The dominant kernel on its own: the ten weight products of one conformer block at this batch's
-        M (2x FF up, 2x FF down, q/k/v/out/pw2 at D x D, pw1 at D x 2D), recorded back to back and replayed;
+        """The dominant kernel on its own: the weight products of one conformer block at this batch's
+        M (2x FF up, 2x FF down, the fused q|k|v projection at D x 3D, out/pw2 at D x D, pw1 at D x 2D), recorded
+        back to back and replayed;
         achieved = their algorithmic FLOPs / CUDA-event time.  The row operands are already packed, as they
         are inside the forward (producers hand them over as f16)."""
         D, DFF, M = 1024, 4096, self.W * 188
@@ -505,8 +506,9 @@ class Encoder:
         x1 = ctx.upload(rng.standard_normal((M, D)).astype(np.float32), M, D)
         x4 = ctx.upload(rng.standard_normal((M, DFF)).astype(np.float32), M, DFF)
         L0 = self.enc["layers"][0]
-        seq = [(x1, L0["ff1w1"]), (x4, L0["ff1w2"]), (x1, L0["q"]), (x1, L0["k"]), (x1, L0["v"]), (x1, L0["out"]),
-               (x1, L0["pw1T"]), (x1, L0["pw2T"]), (x1, L0["ff2w1"]), (x4, L0["ff2w2"])]
+        qkv = [(x1, L0["qkv"])] if "qkv" in L0 else [(x1, L0["q"]), (x1, L0["k"]), (x1, L0["v"])]
+        seq = [(x1, L0["ff1w1"]), (x4, L0["ff1w2"])] + qkv + [(x1, L0["out"]), (x1, L0["pw1T"]), (x1, L0["pw2T"]),
+                                                             (x1, L0["ff2w1"]), (x4, L0["ff2w2"])]
         flops = sum(2.0 * a.rows * a.cols * b.cols for a, b in seq)
 
         def body():
@@ -530,7 +532,7 @@ class Encoder:
                 "(the rest of the 67 MB f32 result was still in the 126 MB L2 at kernel end); algorithmic 84 MB",
                 "kernel": "k_tc_gemm<f16> (label tc_gemm_f16)", "launches_timed": len(seq) * reps,
                 "avg_launch_us": round(ms * 1e3 / (len(seq) * reps), 2),
-                "what": "the 10 weight products of one conformer block at M=%d, back to back (recorded batch)" % M,
+                "what": "the %d weight products of one conformer block at M=%d, back to back (recorded batch)" % (len(seq), M),
                 "peak_source": peaks["source"] + " (burst bf16: kernel timed alone)"}
 
     def cpu_sample(self, threads=True):
