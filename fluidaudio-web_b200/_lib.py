@@ -44,6 +44,7 @@ SIGNATURES = {
     "fa_host_alloc": [C.c_size_t, PP],
     "fa_host_free": [P],
     "fa_download": [P, P, P],
+    "fa_download_async": [P, P, P],
     "fa_stage_download": [P, P, PP],
     "fa_staged_read": [P, P, P],
     "fa_staged_free": [P, P],

@@ -186,6 +186,12 @@ class CudaContext:
 
     downloadF16 = download
 
+    def downloadAsync(self, t: Tensor, pinned: np.ndarray) -> None:
+        """Enqueue (or record) the device-to-host copy of t into a page-locked array from pinnedArray(); the
+        contents are valid after the next sync()."""
+        assert pinned.dtype == np.float32 and pinned.flags["C_CONTIGUOUS"] and pinned.size >= t.rows * t.cols
+        self._check(self._lib.fa_download_async(self._h, t.h, pinned.ctypes.data))
+
     def stageDownload(self, t: Tensor) -> StagedRead:
         out = C.c_void_p()
         self._check(self._lib.fa_stage_download(self._h, t.h, C.byref(out)))

@@ -563,6 +563,21 @@ extern "C" int fa_download(fa_ctx *ctx, const fa_tensor *t, float *host_out) {
   return fa_sync(ctx);
 }
 
+// The copy only, enqueued on the context's stream (recordable): host_out must be page-locked memory (fa_host_alloc)
+// and is valid after the next fa_sync - or, inside a recorded batch, after a sync that follows each launch.
+extern "C" int fa_download_async(fa_ctx *ctx, const fa_tensor *t, float *host_out) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "downloadAsync: NULL context");
+  FA_REQUIRE(ctx, fa_valid(ctx, t), "downloadAsync: unknown tensor handle");
+  FA_REQUIRE(ctx, t->storage == FA_F32, "downloadAsync: f32-storage tensors only");
+  const size_t n = (size_t)t->rows * t->cols;
+  FA_REQUIRE(ctx, host_out || n == 0, "downloadAsync: host pointer is NULL");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!n) return FA_OK;
+  FA_TRY(fa_touch_f32(ctx, t));
+  FA_CHECK_CUDA(ctx, cudaMemcpyAsync(host_out, t->dptr, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  return FA_OK;
+}
+
 extern "C" int fa_stage_download(fa_ctx *ctx, const fa_tensor *t, fa_staged **out) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "stageDownload: NULL argument");
   FA_REQUIRE(ctx, fa_valid(ctx, t), "stageDownload: unknown tensor handle");

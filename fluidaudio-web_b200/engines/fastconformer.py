@@ -272,10 +272,11 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
 class PipelinedEncoder:
     """encode_batch for a stream of window batches with the host<->device copies hidden: `depth` contexts (one
     CUDA stream each) on one GPU hold a recorded forward each - upload of the batch's windows from page-locked
-    host memory, the forward, a staged read-back of the frames - and take the batches in turn, so the copies of
-    one batch run while another batch computes.  submit() enqueues one batch and hands back the frames of the
-    batch submitted `depth - 1` calls earlier (None until the pipeline is full; the array is reused by that slot's
-    next result); flush() drains it.
+    host memory, the forward, the read-back of the frames into a page-locked result array - and take the batches
+    in turn, so the copies of one batch run while another batch computes and the host never copies a frame.
+    submit() launches one batch and hands back the frames of the batch submitted `depth - 1` calls earlier (None
+    until the pipeline is full) as a view of that slot's result array: valid until the next submit(), which
+    re-launches that slot.  flush() drains the pipeline and returns copies.
 
     ctxs: the contexts; encs: load_encoder(ctx, weights) for each; host_windows(slot): the list of page-locked
     f32 arrays (time-major windows, see mel_time_major) that slot's recording uploads on every launch - the caller
@@ -284,20 +285,23 @@ class PipelinedEncoder:
     def __init__(self, ctxs, encs, host_windows, mel_len: int):
         self.ctxs, self.encs, self.mel_len = list(ctxs), list(encs), mel_len
         self.host = [host_windows(s) for s in range(len(self.ctxs))]
-        self.batches, self.outs, self.pending = [], [], []
-        self.results = [None] * len(self.ctxs)
-        for s, (ctx, enc) in enumerate(zip(self.ctxs, self.encs)):
-            ctx.freeTensor(self._body(s))  # once eagerly: weight repacks and pool growth stay out of the recording
-            b, out = ctx.recordBatch(lambda s=s: self._body(s))
+        self.batches, self.results, self.pending = [], [], []
+        for s, ctx in enumerate(self.ctxs):
+            x = self._body(s, None)  # once eagerly: weight repacks and pool growth stay out of the recording
+            res = ctx.pinnedArray(x.rows * x.cols)
+            ctx.freeTensor(x)
+            b, _ = ctx.recordBatch(lambda s=s, res=res: self._body(s, res))
             self.batches.append(b)
-            self.outs.append(out)
+            self.results.append(res)
         self.next = 0
 
-    def _body(self, s):
+    def _body(self, s, res):
         ctx = self.ctxs[s]
         h = ctx.pushArena()
         mels = [ctx.upload(m, 1, self.mel_len) for m in self.host[s]]
         x, _ = encode_batch(ctx, self.encs[s], mels)
+        if res is not None:
+            ctx.downloadAsync(x, res)
         ctx.pin(x)
         ctx.popArena(h)
         return x
@@ -306,19 +310,17 @@ class PipelinedEncoder:
         s = self.next
         self.next = (s + 1) % len(self.ctxs)
         self.batches[s].launch()
-        self.pending.append((s, self.ctxs[s].stageDownload(self.outs[s])))
+        self.pending.append(s)
         if len(self.pending) >= len(self.ctxs):
-            return self._read(*self.pending.pop(0))
+            return self._read(self.pending.pop(0))
         return None
 
-    def _read(self, s, staged):
-        # one result array per slot, reused: the frames stay valid until that slot's next result is read
-        if self.results[s] is None:
-            self.results[s] = np.empty(self.outs[s].rows * self.outs[s].cols, np.float32)
-        return staged.read(self.results[s])
+    def _read(self, s):
+        self.ctxs[s].sync()
+        return self.results[s]
 
     def flush(self):
-        res = [self._read(s, p).copy() for s, p in self.pending]
+        res = [self._read(s).copy() for s in self.pending]
         self.pending = []
         return res
 

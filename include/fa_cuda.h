@@ -108,6 +108,10 @@ int fa_host_free(void *p);
 
 /* ---- readback (compute.d.ts:135-145) -------------------------------------- */
 int fa_download(fa_ctx *ctx, const fa_tensor *t, float *host_out);          /* download / downloadF16 :137-138 */
+/* The device-to-host copy of an f32 tensor alone, enqueued on the context's stream (and recorded, inside
+ * fa_graph_begin/end): host_out must be page-locked (fa_host_alloc); its contents are valid after the next fa_sync.
+ * Lets a recorded batch end with its own read-back, so a replay needs no per-step staging or host-side copy. */
+int fa_download_async(fa_ctx *ctx, const fa_tensor *t, float *host_out);
 int fa_stage_download(fa_ctx *ctx, const fa_tensor *t, fa_staged **out);    /* stageDownload :141 */
 int fa_staged_read(fa_ctx *ctx, fa_staged *s, float *host_out); /* StagedRead.read :44; 2nd call: FA_ERR_INVALID */
 int fa_staged_free(fa_ctx *ctx, fa_staged *s);

@@ -77,14 +77,16 @@ def test_bad_shapes_and_handles_fail_loudly(ctx, pkg):
 
 
 def test_pool_cap_reports_out_of_memory(ctx, pkg):
-    ctx.trimPool(0)
-    ctx.setOption("pool_cap_bytes", ctx.memStats()["createdBytes"])  # already above any headroom
+    ctx = pkg.CudaContext(ctx.device)  # a context of its own: the cap is set against a pool nothing else has filled
     try:
+        ctx.alloc(64, 64)
+        ctx.trimPool(0)
+        ctx.setOption("pool_cap_bytes", ctx.memStats()["createdBytes"])  # already above any headroom
         with pytest.raises(pkg.CudaError) as ei:
             ctx.alloc(4096, 4096)
         assert ei.value.code == 3
     finally:
-        ctx.setOption("pool_cap_bytes", 0)
+        ctx.destroy()
 
 
 def test_recorded_batch_replays_with_new_inputs(ctx):
