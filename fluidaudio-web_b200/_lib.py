@@ -90,6 +90,7 @@ SIGNATURES = {
     "fa_sub_reshape": [P, P, I, I, I, PP],
     "fa_sub_reshape_windows": [P, P, I, I, I, I, PP],
     "fa_conv_stem_windows": [P, P, P, P, P, P, P, P, I, I, I, I, PP],
+    "fa_conv_dw_pw_windows": [P, P, P, P, P, P, I, I, I, I, PP],
     "fa_argmax_rows": [P, P, I, PP],
     "fa_embed_rows": [P, P, P, P, I, PP],
     "fa_unshard_cols": [P, P, I, PP],

@@ -368,6 +368,17 @@ class CudaContext:
         self._check(self._lib.fa_conv_stem_windows(self._h, x.h, *hs, Cc, h, w, W, C.byref(out)))
         return self._wrap(out) if out.value else None
 
+    def convDwPwWindows(self, x, layers, Cc: int, h: int, w: int, W: int) -> Optional[Tensor]:
+        """Optional member: 3x3 stride-2 depthwise conv then pointwise conv + relu over W feature maps
+        x [W, C*h*w] in one call; `layers` = two dicts {"w", "b"}.  Bit-identical to the two conv2dWindows calls;
+        None outside the fused kernel's range (w == 32, C a multiple of 64)."""
+        out = C.c_void_p()
+        hs = []
+        for l in layers:
+            hs += [l["w"].h, self._h_of(l.get("b"))]
+        self._check(self._lib.fa_conv_dw_pw_windows(self._h, x.h, *hs, Cc, h, w, W, C.byref(out)))
+        return self._wrap(out) if out.value else None
+
     # -- attention (compute.d.ts:189-199) ----------------------------------------------------------
     def bmmQK(self, q, b, qb, H: int, HD: int, W: int = 1, bShared: bool = False) -> Tensor:
         return self._op(self._lib.fa_bmm_qk, q.h, b.h, self._h_of(qb), H, HD, W, 1 if bShared else 0)

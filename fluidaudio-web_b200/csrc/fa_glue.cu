@@ -882,6 +882,60 @@ __global__ void __launch_bounds__(256, 3) k_stem_c1_dw_pack(const float *__restr
   }
 }
 
+// Depthwise 3x3, stride 2, pad 1 over 32-column feature maps [C][H][32] -> [C][H2][16], written straight into the
+// packed f16 layout Wp[n/128][k/64][n%128][k%64] (n = pixel y*16 + x, k = channel) of the pointwise product that
+// follows: the stem's fourth layer without its f32 result and without the separate pack pass.  Same accumulation
+// order as k_dwconv2d_3x3, same rounding as k_pack_w_f16.  CTA = 8 output rows (one 128-pixel block) x 64 channels
+// x one window; a half-warp owns a channel, a lane one output column: it loads its two input columns of each of
+// the 17 rows as one 8-byte word (a half-warp reads one 128-byte row) and gets the left neighbour by one shuffle.
+constexpr int kDwPitch = 72;  // halves per pixel row of the staging tile: 144 B keeps 16-byte alignment, spreads banks
+__global__ void __launch_bounds__(256) k_dw_s2_pack(const float *__restrict__ x, const float *__restrict__ w1,
+                                                    const float *__restrict__ b1, __half *__restrict__ out, int C, int H,
+                                                    int H2, int nblocks, int nch, size_t xstride, size_t slab) {
+  fa_grid_dep_sync();
+  __shared__ __align__(16) __half o_s[128 * kDwPitch];
+  const int y0 = blockIdx.x * 8, cq = blockIdx.y, win = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, x2 = lane & 15;
+  x += (size_t)win * xstride;
+#pragma unroll 1
+  for (int ci = 0; ci < 4; ci++) {
+    const int cl = warp * 8 + ci * 2 + (lane >> 4), c = cq * 64 + cl;
+    const float2 *xc = (const float2 *)(x + (size_t)c * H * 32) + x2;
+    float2 v[17];
+#pragma unroll
+    for (int r = 0; r < 17; r++) {
+      const int row = 2 * y0 - 1 + r;
+      v[r] = (row >= 0 && row < H) ? __ldg(xc + (size_t)row * 16) : make_float2(0.f, 0.f);
+    }
+    float wk[9];
+#pragma unroll
+    for (int t = 0; t < 9; t++) wk[t] = __ldg(w1 + (size_t)c * 9 + t);
+    const float bb = b1 ? __ldg(b1 + c) : 0.f;
+    float lf[17];
+#pragma unroll
+    for (int r = 0; r < 17; r++) {
+      lf[r] = __shfl_up_sync(0xffffffffu, v[r].y, 1);
+      if (x2 == 0) lf[r] = 0.f;  // column -1 is padding (and lane 16 must not see the other channel)
+    }
+#pragma unroll
+    for (int yl = 0; yl < 8; yl++) {
+      float acc = bb;
+#pragma unroll
+      for (int a = 0; a < 3; a++) {
+        acc = fmaf(lf[2 * yl + a], wk[a * 3], acc);
+        acc = fmaf(v[2 * yl + a].x, wk[a * 3 + 1], acc);
+        acc = fmaf(v[2 * yl + a].y, wk[a * 3 + 2], acc);
+      }
+      o_s[(yl * 16 + x2) * kDwPitch + cl] = __float2half_rn(y0 + yl < H2 ? acc : 0.f);
+    }
+  }
+  __syncthreads();
+  if ((int)blockIdx.x < nblocks) {
+    uint4 *dst = (uint4 *)(out + (size_t)win * slab + ((size_t)blockIdx.x * nch + cq) * 128 * 64);
+    for (int e = threadIdx.x; e < 128 * 8; e += 256) dst[e] = *(const uint4 *)(o_s + (e >> 3) * kDwPitch + (e & 7) * 8);
+  }
+}
+
 // The conformer conv module between its two pointwise projections, in the time-major layout the
 // projections use (src/engines/asr-parakeet/raw-encoder.js:340-362 does it as transpose -> glu ->
 // per-window depthwise conv1d(+act) -> transpose): x [W*T, 2D] -> y [W*T, D],
@@ -2032,6 +2086,68 @@ extern "C" int fa_conv_stem_windows(fa_ctx *ctx, const fa_tensor *x, const fa_te
                     ceil_div(P, 128), fa_tc_chunks(C, 2), (size_t)x->cols, slab / sizeof(__half));
     }
     if (cudaGetLastError() != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "stem_c1_dw_pack: launch failed");
+  }
+  if (rc == FA_OK) rc = fa_prep_a_f16(ctx, (const float *)w2->dptr, C, C, (__half *)wa);
+  if (rc == FA_OK) {
+    TcEpilogue ep;
+    ep.rowbias = b2 ? (const float *)b2->dptr : nullptr;
+    ep.act = FA_ACT_RELU;
+    ep.batches = windows;
+    ep.a_shared = true;
+    ep.o_div = 1;
+    ep.o_hi = (long long)C * P;
+    ep.ldc = P;
+    rc = fa_tc_gemm_f16(ctx, (const __half *)wa, (const __half *)xa, (float *)y->dptr, C, P, C, ep);
+  }
+  if (xa) fa_block_release(ctx, xa);
+  if (wa) fa_block_release(ctx, wa);
+  if (rc != FA_OK) {
+    fa_free_tensor(ctx, y);
+    return rc;
+  }
+  *out = y;
+  return FA_OK;
+}
+
+// depthwise(3x3, s2, p1) -> pointwise(C->C, relu) over 32-column feature maps x [windows, C*h*32]: the stem's fourth
+// and fifth layers as one member (k_dw_s2_pack + the tensor-core product of the pointwise layer).  *out stays NULL
+// when the geometry is not the fused kernel's: the caller runs the two members.
+extern "C" int fa_conv_dw_pw_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w1, const fa_tensor *b1,
+                                     const fa_tensor *w2, const fa_tensor *b2, int C, int h, int w_, int windows,
+                                     fa_tensor **out) {
+  GLUE_PROLOGUE("convDwPwWindows");
+  *out = nullptr;
+  FA_TRY(need_f32(ctx, x, "convDwPwWindows"));
+  FA_TRY(need_f32(ctx, w1, "convDwPwWindows"));
+  FA_TRY(need_f32(ctx, w2, "convDwPwWindows"));
+  if (b1) FA_TRY(need_f32(ctx, b1, "convDwPwWindows"));
+  if (b2) FA_TRY(need_f32(ctx, b2, "convDwPwWindows"));
+  FA_REQUIRE(ctx, C > 0 && h > 0 && w_ > 0 && windows >= 1 && windows <= 65535, "convDwPwWindows: bad geometry");
+  FA_REQUIRE(ctx, (long long)x->rows * x->cols >= (long long)windows * C * h * w_ && (windows == 1 || x->rows == windows),
+             "convDwPwWindows: x is [%d,%d], need %d windows of %d*%d*%d", x->rows, x->cols, windows, C, h, w_);
+  FA_REQUIRE(ctx, (long long)w1->rows * w1->cols >= (long long)C * 9 && (long long)w2->rows * w2->cols >= (long long)C * C,
+             "convDwPwWindows: weight tensor too small");
+  FA_REQUIRE(ctx, (!b1 || b1->rows * b1->cols >= C) && (!b2 || b2->rows * b2->cols >= C), "convDwPwWindows: bias shorter than %d", C);
+  const int H2 = (h - 1) / 2 + 1, W2 = 16, P = H2 * W2;
+  // declined unless conv2d would also run the pointwise layer as the tensor-core product (same size rule)
+  if (w_ != 32 || (C & 63) || !fa_tc_available(ctx) || ceil_div(H2, 8) > 65535 || (C >> 6) > 65535 || P < 64 ||
+      (long long)C * C * P < (1ll << 21))
+    return FA_OK;
+  fa_tensor *y = nullptr;
+  FA_TRY(fa_tensor_new(ctx, windows, C * P, FA_F32, true, &y));
+  void *xa = nullptr, *wa = nullptr;
+  size_t xb = 0, wb = 0;
+  const size_t slab = fa_tc_weight_bytes(P, C, 2);
+  int rc = fa_block_acquire(ctx, slab * windows, &xa, &xb);
+  if (rc == FA_OK) rc = fa_block_acquire(ctx, fa_tc_act_bytes(C, C, 2, 1), &wa, &wb);
+  if (rc == FA_OK) {
+    {
+      LaunchScope ls(ctx, "dw_s2_pack");
+      fa_launch_dep(ctx, k_dw_s2_pack, dim3(ceil_div(H2, 8), C >> 6, windows), dim3(256), 0, (const float *)x->dptr,
+                    (const float *)w1->dptr, b1 ? (const float *)b1->dptr : nullptr, (__half *)xa, C, h, H2, ceil_div(P, 128),
+                    fa_tc_chunks(C, 2), windows == 1 ? (size_t)0 : (size_t)x->cols, slab / sizeof(__half));
+    }
+    if (cudaGetLastError() != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "dw_s2_pack: launch failed");
   }
   if (rc == FA_OK) rc = fa_prep_a_f16(ctx, (const float *)w2->dptr, C, C, (__half *)wa);
   if (rc == FA_OK) {

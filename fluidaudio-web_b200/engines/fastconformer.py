@@ -150,6 +150,11 @@ def pre_encode_windows(ctx, enc, mels):
         if head is not None:
             s, first = head, 3
             Hh, Wd = ((Hh - 1) // 2 + 1 - 1) // 2 + 1, ((Wd - 1) // 2 + 1 - 1) // 2 + 1
+    if first == 3 and hasattr(ctx, "convDwPwWindows"):  # optional member: layers 3-4, no f32 depthwise result, no pack pass
+        tail = ctx.convDwPwWindows(s, enc["sub"]["conv"][3:5], Csub, Hh, Wd, W)
+        if tail is not None:
+            s, first = tail, 5
+            Hh, Wd = (Hh - 1) // 2 + 1, (Wd - 1) // 2 + 1
     for i, (cout, cin, k, st, gr, act, s2) in enumerate(conv):
         if i < first:
             continue

@@ -248,6 +248,11 @@ int fa_sub_reshape_windows(fa_ctx *ctx, const fa_tensor *x, int C, int Tsub, int
 int fa_conv_stem_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w0, const fa_tensor *b0, const fa_tensor *w1,
                          const fa_tensor *b1, const fa_tensor *w2, const fa_tensor *b2, int C, int h, int w_, int windows,
                          fa_tensor **out);
+/* Optional member convDwPwWindows: the stem's fourth and fifth layers as one call: depthwise(3x3, stride 2, pad 1)
+ * -> pointwise(C->C, relu) over x [windows, C*h*w]; returns [windows, C*H2*W2], bit-identical to the two
+ * conv2d_windows calls; *out is NULL outside the fused kernel's range (w == 32, C a multiple of 64). */
+int fa_conv_dw_pw_windows(fa_ctx *ctx, const fa_tensor *x, const fa_tensor *w1, const fa_tensor *b1, const fa_tensor *w2,
+                          const fa_tensor *b2, int C, int h, int w_, int windows, fa_tensor **out);
 /* argmax over each row (host picks tokens from it; the reference does this on the host,
  * src/engines/asr-whisper/index.ts:80-97): out [rows,2] = {index, value}.  Only the first `ncols`
  * columns of each row take part (ncols <= 0: all of them) - the tied vocabulary projection is padded

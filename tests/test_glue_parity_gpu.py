@@ -353,3 +353,24 @@ def test_attn_fused_matches_the_op_sequence(ctx, W, H, T):
         assert np.abs(a - b).max() <= 3e-3 * max(1.0, float(np.abs(a).max()))
         pl = ctx.download(plain)
         assert np.array_equal(ctx.download(hinted), pl.astype(np.float16).astype(np.float32))
+
+
+@pytest.mark.parametrize("h,Cc,W,bias", [(75, 64, 3, True), (19, 128, 2, True), (70, 64, 1, False), (8, 256, 2, True)])
+def test_conv_dw_pw_windows_equals_the_two_layer_sequence(ctx, h, Cc, W, bias):
+    """convDwPwWindows (optional member) against the two conv2dWindows calls it replaces, bit for bit."""
+    rng = np.random.default_rng(h * 7 + Cc)
+    w = 32
+    x = ctx.upload(rng.standard_normal((W, Cc * h * w)).astype(np.float32), W, Cc * h * w)
+    mk = lambda n, s: ctx.upload((rng.standard_normal(n) * s).astype(np.float32), 1, n)
+    layers = [dict(w=mk(Cc * 9, 0.3), b=mk(Cc, 0.1) if bias else None), dict(w=mk(Cc * Cc, 0.1), b=mk(Cc, 0.1) if bias else None)]
+    got = ctx.convDwPwWindows(x, layers, Cc, h, w, W)
+    assert got is not None
+    s, Hh, Wd = x, h, w
+    for l, (k, st, gr, act, p) in zip(layers, [(3, 2, Cc, "none", 1), (1, 1, 1, "relu", 0)]):
+        s = ctx.conv2dWindows(s, l["w"], dict(cout=Cc, cin=Cc, h=Hh, w=Wd, kh=k, kw=k, bias=l["b"], strideH=st, strideW=st,
+                                              padTop=p, padBottom=p, padLeft=p, padRight=p, groups=gr, act=act), W)
+        Hh, Wd = (Hh + 2 * p - k) // st + 1, (Wd + 2 * p - k) // st + 1
+    assert (got.rows, got.cols) == (W, Cc * Hh * Wd)
+    assert np.array_equal(ctx.download(got).reshape(-1), ctx.download(s).reshape(-1))
+    x64 = ctx.upload(rng.standard_normal((W, Cc * h * 64)).astype(np.float32), W, Cc * h * 64)
+    assert ctx.convDwPwWindows(x64, layers, Cc, h, 64, W) is None  # not a 32-column map: declined
