@@ -4,7 +4,7 @@
 //   prob[i]  = softmax_j( ac[i][j] + bd[i][T-1-i+j] )          out[i] = sum_j prob[i][j] * v[j]
 // per (window, head), T <= 192 frames, head width 128.  The separate-op form stores ac and bd (36 + 72 MB per
 // block for 32 windows), reads them back for the shifted softmax and packs q, k, v and the probabilities into
-// GEMM operand layouts with four more kernels: seven launches that are all memory traffic around 9 GFLOP.
+// GEMM operand layouts with four more kernels: seven launches that are all memory traffic for 9 GFLOP of arithmetic.
 // Here one CTA owns one (window, head): keys and the head's slice of the positional projection are converted to
 // f16 into shared memory once, each of the 12 warps owns 16 query rows and keeps their whole score row block
 // (16 x 192, f32) in registers, the positional scores of a 64-key block are computed for the 80 positions those
