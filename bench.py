@@ -5,7 +5,8 @@
 One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded
 synthetic input; `value` is whole-job throughput with inputs resident in HBM, `e2e` the same metric
 through the public ComputeContext API with host buffers (uploads and the result download inside the
-timed region).  `roofline` describes the dominant kernel, timed per launch with CUDA events on the
+timed region; the encoder workload feeds its batches through two recorded forwards on two streams, so one
+batch's copies run under the other's compute - every step still uploads its inputs and reads its result).  `roofline` describes the dominant kernel, timed per launch with CUDA events on the
 context's own stream; `cpu_baseline` is the CPU port of the reference's wasm kernels on a bounded
 sample.  `--impl reference` times that CPU port alone with every host thread (rank 0 only).
 
