@@ -70,7 +70,6 @@ extern "C" int fa_ctx_create(int device, fa_ctx **out) {
     delete ctx;
     return fa_fail(nullptr, FA_ERR_CUDA, "fa_ctx_create: status word allocation failed");
   }
-  if (const char *e = getenv("FA_PDL")) ctx->pdl = atoi(e) != 0;  // A/B switch for measurements
   ctx->gemv_ticket_count = 8192;
   if (cudaMalloc(&ctx->gemv_tickets, sizeof(int) * ctx->gemv_ticket_count) != cudaSuccess ||
       cudaMemsetAsync(ctx->gemv_tickets, 0, sizeof(int) * ctx->gemv_ticket_count, ctx->stream) != cudaSuccess) {

@@ -29,8 +29,6 @@
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..9 = epilogue (TMEM lane quadrant = warp_id % 4, two warps per quadrant).
-#include <cstdlib>
-
 #include "fa_tc_common.cuh"
 
 namespace {
@@ -86,18 +84,7 @@ struct TcParams {
   const uint8_t *nb_zp;
   int nblk;
   int *status;
-  unsigned long long *trace;  // debugging aid: per-phase %globaltimer stamps of CTA 0, or nullptr
 };
-
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
-  return t;
-}
-#define TC_TRACE(slot)                                                                                   \
-  do {                                                                                                   \
-    if (p.trace && blockIdx.x == 0 && blockIdx.z == 0 && (slot) < 256) p.trace[slot] = gtime();          \
-  } while (0)
 
 __device__ __forceinline__ void report_timeout(int *status, int code, int detail) {
   if (atomicCAS(status, 0, code) == 0) {
@@ -326,7 +313,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
   fa_grid_dep_sync();  // barriers, TMEM and descriptors were set up while the previous kernel drained
-  if (threadIdx.x == 0) TC_TRACE(0);
 
   auto aborted = [&]() {
     uint32_t v;
@@ -365,7 +351,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             stop = true;
             break;
           }
-          if (it < 64) TC_TRACE(1 + it);
           if (KIND == 2) {
             mbar_expect_tx(fb, q_bytes + kRawTileBytes);
             tma_load_2d(dst + kPTileBytes + q_bytes, &map_w, 0, (tn * p.num_kb + kb) * 16, fb);  // 4 KB nibble tile
@@ -415,7 +400,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             break;
           }
           tc_fence_after();
-          if (it < 64) TC_TRACE(65 + it);
           const uint64_t da = desc0 + (uint64_t)s * st_off, db = da + q_off;
           umma<MK>(d_tmem, da, db, idesc, kb > kb0 ? 1u : 0u);  // 4 x 32 bytes of K per slot
           umma<MK>(d_tmem, da + 2, db + 2, idesc, 1u);
@@ -483,8 +467,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           const int c = cg + 2 * i;
           if (c >= chunks) break;
           const uint32_t it = it_base + (uint32_t)c, slot_i = it % nst, ph = (it / nst) & 1u;
-          const bool tr = dq == 0 && c < 32;
-          if (tr) TC_TRACE(140 + 4 * (c >> 1));
           int okw = 1;
           if (lane == 0 && !mbar_wait(full_bar((int)slot_i), ph)) {
             set_abort(5, c);
@@ -492,7 +474,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           }
           ok = __shfl_sync(0xffffffffu, okw, 0) != 0 && !aborted();
           if (!ok) break;
-          if (tr) TC_TRACE(141 + 4 * (c >> 1));
           const uint32_t slot = smem_base + slot_i * stage_bytes;
 #pragma unroll
           for (int hb = 0; hb < 2; hb++) {
@@ -522,11 +503,9 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                            : "memory");
             }
           }
-          if (tr) TC_TRACE(142 + 4 * (c >> 1));
           fence_proxy_async_smem();  // the tile is read by the tensor core through the async proxy
           __syncwarp();
           if (lane == 0) mbar_arrive(deq_bar((int)slot_i));
-          if (tr) TC_TRACE(143 + 4 * (c >> 1));
         }
 #pragma unroll
         for (int i = 0; i < 2 * G; i++) scg[i] = scn[i];
@@ -559,14 +538,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !aborted();
       if (!ok) break;
       tc_fence_after();
-      if (threadIdx.x == 64) TC_TRACE(129);
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
       epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial);
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty(buf));
-      if (threadIdx.x == 64) TC_TRACE(130);
     }
   }
 
@@ -626,7 +603,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) TC_TRACE(131);
   if (aborted()) {
     // A wait ran out: give copies still in flight time to land before the CTA's shared memory goes away.
     for (int i = 0; i < 1000; i++) __nanosleep(1000);
@@ -634,179 +610,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
-  }
-}
-
-// ---- CTA-pair variant (f16, one limb) --------------------------------------------------------------
-// Two CTAs of a cluster work on one 256 (weights) x MT (activations) tile with tcgen05.mma.cta_group::2:
-// each CTA stages its own 128 weight rows and HALF of the activation rows, so per CTA and K chunk the
-// operand traffic is 16 KB + MT*64 B instead of 16 KB + MT*128 B - the main loop of the single-CTA kernel
-// is bound by exactly that traffic (shared-memory fill rate), not by the tensor pipe.  No TMA multicast:
-// every CTA loads only what it alone needs.  The leader (rank 0) issues the MMAs for the pair; loads of
-// both CTAs count on the leader's "full" barriers, MMA completion is signalled to both CTAs' "empty" and
-// "accumulator full" barriers, and both CTAs' epilogue warps release the accumulator on the leader's barrier.
-template <int KIND>
-__global__ void __launch_bounds__(kThreads, 1)
-k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int half_rows = p.MT / 2;  // activation rows this CTA stages
-  const uint32_t stage_bytes = kPTileBytes + (uint32_t)half_rows * kRowBytes;
-  const uint32_t bars = smem_base + (uint32_t)p.stages * stage_bytes;
-  auto full_bar = [&](int s) { return bars + (uint32_t)s * 8u; };
-  auto empty_bar = [&](int s) { return bars + (uint32_t)(p.stages + s) * 8u; };
-  auto acc_full = [&](int b) { return bars + (uint32_t)(2 * p.stages + b) * 8u; };
-  auto acc_empty = [&](int b) { return bars + (uint32_t)(2 * p.stages + 2 + b) * 8u; };
-  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4) * 8u;
-  const uint32_t abort_flag = tmem_slot + 4u;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_rank();
-  uint32_t acc_stride = 32;
-  while ((int)acc_stride < p.MT) acc_stride <<= 1;
-  const uint32_t tmem_cols = 2 * acc_stride;
-  const int tiles_n2 = (p.tiles_n + 1) / 2;
-  const int num_tiles = tiles_n2 * p.tiles_m;
-  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; s++) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 2; b++) {
-      mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 2 * kEpiWarps);  // both CTAs' epilogue warps arrive on the leader's barrier
-    }
-    asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(0u) : "memory");
-    fence_barrier_init();
-    fence_proxy_async_smem();
-    tma_prefetch_desc(&map_w);
-    tma_prefetch_desc(&map_a);
-  }
-  if (warp == 1) tmem_alloc2(tmem_slot, tmem_cols);
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync();  // the peer's barriers exist before anything signals them
-  tc_fence_after();
-  uint32_t tmem_base;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
-  if (threadIdx.x == 0) TC_TRACE(0);
-
-  auto aborted = [&]() {
-    uint32_t v;
-    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(abort_flag) : "memory");
-    return v != 0;
-  };
-  auto set_abort = [&](int code, int detail) {
-    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(1u) : "memory");
-    report_timeout(p.status, code, detail);
-  };
-
-  if (warp == 0) {
-    // ---- TMA producer (both CTAs), single lane, lean loop ------------------------------------------
-    if (lane == 0) {
-      uint32_t s = 0, ph = 0, it = 0;
-      const uint32_t nst = (uint32_t)p.stages;
-      bool stop = false;
-      for (int tile = pair; tile < num_tiles && !stop; tile += npairs) {
-        const int tn2 = tile % tiles_n2, tm = tile / tiles_n2;
-        const int tn = tn2 * 2 + (int)rank;  // this CTA's 128-row weight tile (may lie past N: reads as zero)
-        int wrow = tn * p.num_kb * 128;
-        const int arow = tm * p.MT + (int)rank * half_rows;
-        for (int kb = 0; kb < p.num_kb; kb++, it++, wrow += 128) {
-          const uint32_t fb = bars + s * 8u, dst = smem_base + s * stage_bytes;
-          if (it >= nst && !mbar_wait(fb + nst * 8u, ph ^ 1u)) {
-            set_abort(11, kb);
-            stop = true;
-            break;
-          }
-          if (it < 64) TC_TRACE(1 + it);
-          if (rank == 0) mbar_expect_tx(fb, 2 * stage_bytes);  // bytes of both CTAs land on this barrier
-          tma_load_2d_pair(dst, &map_w, 0, wrow, fb);
-          tma_load_3d_pair(dst + kPTileBytes, &map_a, 0, arow, kb, fb);
-          if (++s == nst) {
-            s = 0;
-            ph ^= 1u;
-          }
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ---- MMA issuer (leader only), single lane, lean loop ------------------------------------------
-    if (rank == 0 && lane == 0) {
-      const uint32_t idesc = make_idesc(KIND, 256, p.MT);
-      const uint32_t nst = (uint32_t)p.stages;
-      const uint64_t desc0 = smem_desc_sw128(smem_base);
-      const uint64_t q_off = (uint64_t)(kPTileBytes >> 4), st_off = (uint64_t)(stage_bytes >> 4);
-      uint32_t s = 0, ph = 0, it = 0, lt = 0;
-      bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
-        const uint32_t buf = lt & 1, use = lt >> 1;
-        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1)) {
-          set_abort(14, tile);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * acc_stride;
-        for (int kb = 0; kb < p.num_kb; kb++, it++) {
-          const uint32_t fb = bars + s * 8u;
-          if (!mbar_wait(fb, ph)) {
-            set_abort(12, kb);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          if (it < 64) TC_TRACE(65 + it);
-          const uint64_t da = desc0 + (uint64_t)s * st_off, db = da + q_off;
-          umma2_f16(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
-          umma2_f16(d_tmem, da + 2, db + 2, idesc, 1u);
-          umma2_f16(d_tmem, da + 4, db + 4, idesc, 1u);
-          umma2_f16(d_tmem, da + 6, db + 6, idesc, 1u);
-          umma_commit_pair(fb + nst * 8u);
-          if (++s == nst) {
-            s = 0;
-            ph ^= 1u;
-          }
-        }
-        if (ok) umma_commit_pair(acc_full(buf));
-      }
-    }
-    __syncwarp();
-  } else {
-    // ---- epilogue (both CTAs): this CTA's 128 output columns x all MT rows -----------------------------
-    const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
-    uint32_t lt = 0;
-    bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
-      const int tn2 = tile % tiles_n2, tm = tile / tiles_n2;
-      const int n0 = (tn2 * 2 + (int)rank) * 128, m0 = tm * p.MT;
-      const uint32_t buf = lt & 1, use = lt >> 1;
-      ok = mbar_wait(acc_full(buf), use & 1);
-      if (!ok && lane == 0) set_abort(13, tile);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !aborted();
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<KIND>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, 0u);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_remote(acc_empty(buf), 0);
-    }
-  }
-
-  // ---- teardown: neither CTA leaves while the other may still read its shared memory or TMEM -----------
-  __syncwarp();
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync();
-  if (aborted()) {
-    for (int i = 0; i < 1000; i++) __nanosleep(1000);
-  }
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc2(tmem_base, tmem_cols);
   }
 }
 
@@ -1033,7 +836,7 @@ int grid_for(fa_ctx *ctx, size_t n, int block, int per_sm) {
 
 template <int KIND>
 int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs, void *out, bool raw_i32, int M, int N,
-              int K, const TcEpilogue &ep, bool allow_trace = true) {
+              int K, const TcEpilogue &ep) {
   const int elem = KIND == 1 ? 1 : 2;
   TcParams p{};
   p.M = M;
@@ -1058,26 +861,6 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     for (int cand = mt_max; cand >= 64; cand -= 16) {
       const long long tiles = (long long)p.tiles_n * ceil_div(M, cand) * batches;
       const long long cost = ((tiles + ctx->sm_count - 1) / ctx->sm_count) * (128 + cand * limbs);
-      if (best < 0 || cost < best) {
-        best = cost;
-        p.MT = cand;
-      }
-    }
-  }
-  if (const char *e = getenv("FA_TC_MT")) {  // measurement switch: force the tile height of multi-tile products
-    const int f = atoi(e);
-    if (M > mt_max && f >= 16 && f <= mt_max && (f & 15) == 0) p.MT = f;
-  }
-  // CTA pairs (cta_group::2) for large single-limb f16 products: halves the activation bytes each CTA stages.
-  static const bool pair_enabled = getenv("FA_TC_PAIR") != nullptr;
-  const bool use_pair = pair_enabled && KIND == 0 && limbs == 1 && !raw_i32 && ep.batches <= 1 && p.tiles_n >= 2 &&
-                        M >= 256 && (ctx->sm_count & 1) == 0;
-  if (use_pair) {
-    const int npairs = ctx->sm_count / 2, tiles_n2 = (p.tiles_n + 1) / 2;
-    long long best = -1;
-    for (int cand = 256; cand >= 64; cand -= 32) {
-      const long long tiles = (long long)tiles_n2 * ceil_div(M, cand);
-      const long long cost = ((tiles + npairs - 1) / npairs) * (256 + cand);
       if (best < 0 || cost < best) {
         best = cost;
         p.MT = cand;
@@ -1114,70 +897,6 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
       p.splitk = ceil_div(p.num_kb, p.kb_per_split);
     }
   }
-  if (use_pair) {
-    p.splitk = 1;
-    p.kb_per_split = p.num_kb;
-    const size_t stage_b = (size_t)kPTileBytes + (size_t)(p.MT / 2) * kRowBytes;
-    const size_t tail_b = (size_t)(2 * 12 + 4) * 8 + 16 + 1024;
-    const int npairs = ctx->sm_count / 2, ptiles = ((p.tiles_n + 1) / 2) * p.tiles_m;
-    int st = (int)((220 * 1024 - tail_b) / stage_b);
-    if (st > 12) st = 12;
-    const int kb_per_cta = p.num_kb * ceil_div(ptiles, npairs);
-    if (st > kb_per_cta) st = kb_per_cta;
-    p.stages = st < 1 ? 1 : st;
-    p.raw_i32 = 0;
-    p.out = (float *)out;
-    p.rowscale = ep.rowscale;
-    p.colscale = ep.colscale;
-    p.bias = ep.bias;
-    p.add = ep.add;
-    p.rowbias = ep.rowbias;
-    p.act = ep.act;
-    p.status = ctx->dev_status;
-    p.trace = nullptr;
-    static const bool want_trace2 = getenv("FA_TC_TRACE") != nullptr;
-    unsigned long long *trace_dev = nullptr;
-    if (want_trace2 && allow_trace) {
-      cudaMalloc(&trace_dev, 256 * 8);
-      cudaMemsetAsync(trace_dev, 0, 256 * 8, ctx->stream);
-      p.trace = trace_dev;
-    }
-    CUtensorMap map_w, map_a;
-    FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, (uint64_t)p.tiles_n * p.num_kb * 128, 0, 128));
-    FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M, (uint64_t)p.num_kb, (uint32_t)(p.MT / 2)));
-    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm_pair<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    cudaLaunchConfig_t cfg{};
-    cudaLaunchAttribute attr[1];
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = stage_b * p.stages + tail_b;
-    cfg.stream = ctx->stream;
-    cfg.gridDim = dim3(2 * (ptiles < npairs ? ptiles : npairs));
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    {
-      LaunchScope ls(ctx, "tc_gemm_f16_pair");
-      cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm_pair<KIND>, map_w, map_a, p);
-      if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm_pair: %s", cudaGetErrorString(e));
-    }
-    FA_LAUNCH_CHECK(ctx, "tc_gemm_pair");
-    if (trace_dev) {
-      unsigned long long h[256];
-      cudaMemcpyAsync(h, trace_dev, sizeof h, cudaMemcpyDeviceToHost, ctx->stream);
-      cudaStreamSynchronize(ctx->stream);
-      cudaFree(trace_dev);
-      fprintf(stderr, "[tc pair trace] M=%d N=%d K=%d MT=%d stages=%d num_kb=%d grid=%d\n  tma issue :", M, N, K, p.MT, p.stages,
-              p.num_kb, cfg.gridDim.x);
-      for (int i = 0; i < 64 && h[1 + i]; i++) fprintf(stderr, " %lld", (long long)(h[1 + i] - h[0]));
-      fprintf(stderr, "\n  mma ready :");
-      for (int i = 0; i < 64 && h[65 + i]; i++) fprintf(stderr, " %lld", (long long)(h[65 + i] - h[0]));
-      fprintf(stderr, "\n");
-    }
-    return FA_OK;
-  }
   const size_t stage_bytes = (size_t)kPTileBytes + (size_t)p.MT * limbs * kRowBytes + (KIND == 2 ? kRawTileBytes : 0);
   const size_t tail_bytes = (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + 1024;
   int stages = (int)((220 * 1024 - tail_bytes) / stage_bytes);
@@ -1195,13 +914,6 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.rowbias = ep.rowbias;
   p.act = ep.act;
   p.status = ctx->dev_status;
-  static const bool want_trace = getenv("FA_TC_TRACE") != nullptr;
-  unsigned long long *trace_dev = nullptr;
-  if (want_trace && allow_trace) {
-    cudaMalloc(&trace_dev, 256 * 8);
-    cudaMemsetAsync(trace_dev, 0, 256 * 8, ctx->stream);
-    p.trace = trace_dev;
-  }
   const size_t smem = stage_bytes * stages + tail_bytes;
 
   CUtensorMap map_w, map_a;
@@ -1241,27 +953,6 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm: %s", cudaGetErrorString(e));
   }
   FA_LAUNCH_CHECK(ctx, "tc_gemm");
-  if (trace_dev) {  // debugging aid (FA_TC_TRACE=1): timeline of CTA 0 in ns since its start
-    unsigned long long h[256];
-    cudaMemcpyAsync(h, trace_dev, sizeof h, cudaMemcpyDeviceToHost, ctx->stream);
-    cudaStreamSynchronize(ctx->stream);
-    cudaFree(trace_dev);
-    fprintf(stderr, "[tc trace] M=%d N=%d K=%d MT=%d limbs=%d stages=%d num_kb=%d tiles=%dx%d splitk=%d grid=%d\n", M, N, K,
-            p.MT, limbs, stages, p.num_kb, p.tiles_n, p.tiles_m, p.splitk, cfg.gridDim.x);
-    fprintf(stderr, "  tma issue :");
-    for (int i = 0; i < 64 && h[1 + i]; i++) fprintf(stderr, " %lld", (long long)(h[1 + i] - h[0]));
-    fprintf(stderr, "\n  mma ready :");
-    for (int i = 0; i < 64 && h[65 + i]; i++) fprintf(stderr, " %lld", (long long)(h[65 + i] - h[0]));
-    fprintf(stderr, "\n  last acc ready %lld, last epilogue end %lld, all joined %lld\n", (long long)(h[129] - h[0]),
-            (long long)(h[130] - h[0]), (long long)(h[131] - h[0]));
-    if (KIND == 2) {
-      fprintf(stderr, "  unpack warp 0 (loop top / tile landed / stored / arrived):");
-      for (int i = 0; i < 16 && h[140 + 4 * i]; i++)
-        fprintf(stderr, " [%lld %lld %lld %lld]", (long long)(h[140 + 4 * i] - h[0]), (long long)(h[141 + 4 * i] - h[0]),
-                (long long)(h[142 + 4 * i] - h[0]), (long long)(h[143 + 4 * i] - h[0]));
-      fprintf(stderr, "\n");
-    }
-  }
   return FA_OK;
 }
 
@@ -1528,7 +1219,7 @@ extern "C" int fa_matmul_int8_static(fa_ctx *ctx, const float *a_dev, const void
     ep.colscale = scale_dev;
     ep.bias = bias_dev;
     ep.act = act;
-    rc = launch_tc<1>(ctx, w_packed, a_planes, limbs, y_dev, false, M, N, K, ep, /*allow_trace=*/false);
+    rc = launch_tc<1>(ctx, w_packed, a_planes, limbs, y_dev, false, M, N, K, ep);
   }
   ctx->profiling = was_profiling;
   return rc;

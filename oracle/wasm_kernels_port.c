@@ -4,12 +4,15 @@
  * TEST INFRASTRUCTURE ONLY. This file is the checker the CUDA backend is compared
  * against; nothing in the shipped package links, imports or calls it.
  *
- * Pinning status: the reference holds no golden output vectors for this path and
- * cannot be executed here (no Node / wasm runtime / Rust toolchain), so this port is
- * pinned to what the reference's own gates contain - the closed-form expectations of
- * scripts/wasm-verify.mjs and the seeded cases of scripts/backend-conformance.mjs,
- * both restated in tests/test_oracle.py - and NOT to outputs produced by the
- * reference: to that extent, parity unpinned.
+ * Pinning status: PINNED to outputs of the reference itself.  The four kernels restated here ship
+ * compiled as src/gpu/wasm-kernels.wasm; oracle/wasm_exec.py executes that module through the host
+ * calling convention of src/gpu/wasm-context.js, tests/golden/gen_wasm_golden.py stores what it returns
+ * on the reference gate's seeded cases plus ragged / partial-block / grouped-convolution cases, and
+ * tests/test_oracle_pinned.py requires this file to reproduce every stored array bit for bit (and
+ * re-executes the module live where a reference checkout is present).  The JavaScript half (bias,
+ * activation, residual, glue ops) has no compiled form to execute; it stays pinned to the closed-form
+ * expectations of scripts/wasm-verify.mjs and the seeded cases of scripts/backend-conformance.mjs
+ * restated in tests/test_oracle.py.
  *
  * It restates, operation by operation and in the same order, the reference's own
  * CPU implementation of the path:
@@ -29,13 +32,6 @@
  *     acc += x[i]*y[i]` accumulates in f64 and rounds once when stored back into a
  *     Float32Array.  Every glue op below therefore uses `double` exactly where the
  *     JS uses a plain `let`.
- *
- * Pinning status: the reference holds no golden vectors for this path and its
- * wasm binary cannot be executed in the build container (no Node, no wasm
- * runtime, no Rust toolchain).  The oracle is pinned to the only known-answer
- * material the reference has: the in-script reference formulas and tolerances of
- * scripts/wasm-verify.mjs:27-59,167-228 and the seeded cases of
- * scripts/backend-conformance.mjs:46-141 (tests/test_oracle.py).
  */
 #include <math.h>
 #include <stddef.h>
