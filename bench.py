@@ -206,8 +206,8 @@ class Int4Decode:
         ach = sum(self.algorithmic_bytes(M) for M in Ms) * self.nsets * reps / (ms * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(ach / peaks["hbm_gbs"], 4),
-                "traffic": 10.8e6, "traffic_note": "per launch, ncu memory throughput x duration of the M=4 launches "
-                "(profiles/gemv_nbits_int4_decode.md); algorithmic bytes per launch 10.6e6",
+                "traffic": 10.8e6, "traffic_note": "per launch, from an ncu capture of the M=4, K=2048, N=8192 launches "
+                "(memory throughput x duration); algorithmic bytes per launch 10.6e6",
                 "kernel": "k_gemv_nbits (label gemv_nbits), the M = 1 and M = 4 products", "launches_timed": n,
                 "avg_launch_us": round(ms * 1e3 / n, 2), "peak_source": peaks["source"]}
 
@@ -528,9 +528,10 @@ class Encoder:
         ach = flops * reps / (ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"]
         return {"bound": "tensor", "achieved": round(ach, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
-                "traffic": 26.3e6, "traffic_note": "ncu dram read+write of ONE launch at M=4096, K=1024, N=4096 "
-                "(profiles/tc_gemm_f16_M4096_K1024_N4096.md): 16.9 MB read = the two f16 operands once, 9.4 MB written "
-                "(the rest of the 67 MB f32 result was still in the 126 MB L2 at kernel end); algorithmic 84 MB",
+                "traffic": 26.3e6, "traffic_note": "ncu dram read+write of ONE launch of this kernel at M=4096, K=1024, N=4096 "
+                "(a smaller case than the M=%d products timed here): 16.9 MB read = the two f16 operands once, 9.4 MB "
+                "written (the rest of the 67 MB f32 result was still in the 126 MB L2 at kernel end); algorithmic bytes "
+                "of that launch 84 MB" % M,
                 "kernel": "k_tc_gemm<f16> (label tc_gemm_f16)", "launches_timed": len(seq) * reps,
                 "avg_launch_us": round(ms * 1e3 / (len(seq) * reps), 2),
                 "what": "the %d weight products of one conformer block at M=%d, back to back (recorded batch)" % (len(seq), M),
@@ -649,8 +650,8 @@ class Decoder:
         ach = 2 * self.attn_bytes_per_step() / (ms * 1e-3) / 1e9  # per step; the caller scales by `steps`
         return {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
                 "traffic": float(self.S * self.Tenc * self.cfg["D"] * 4),
-                "traffic_note": "per cross-attention launch = its algorithmic bytes: ncu shows 1-2 % L2 hits on these "
-                "launches (profiles/bmm_t1_cross_attention.md), i.e. the cache is streamed from DRAM once",
+                "traffic_note": "per cross-attention launch = its algorithmic bytes: an ncu capture of these launches shows "
+                "1-2 % L2 hits, i.e. the cache is streamed from DRAM once",
                 "kernel": "k_bmm_qk_t1 + k_bmm_pv_t1 (single-query attention over the f32 K/V caches)",
                 "launches": launches, "avg_launch_us": round(ms / launches * 1e3, 2),
                 "share_of_step": None, "peak_source": peaks["source"]}
@@ -782,6 +783,130 @@ DEFAULT_WORKLOAD = "encoder"
 
 
 # --------------------------------------------------------------------------------------------
+# per-shape roofline records of the named GEMM / GEMV shapes
+# --------------------------------------------------------------------------------------------
+
+def shapes_report(ctx, peaks, timer, quick=False):
+    """Every named product shape of the int8, int4 and f16 benchmark configurations, timed on its own:
+    the product over a rotating set of weight matrices larger than L2 is recorded once (one CUDA graph) and
+    replayed between CUDA events on the context's stream; `us` is the time per product.  `frac` = time floor
+    / measured time, the floor being the larger of (algorithmic bytes / measured HBM copy bandwidth) and
+    (operations / tensor peak), `bound` names which of the two it is.  Algorithmic bytes are those of the
+    reference's own storage formats (f32 activations and results, int8 / int4+f32 scales / f16 weights).
+    The int8 tensor peak is taken as 2x the measured bf16 figure (not measured on its own)."""
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    out = []
+    l2x2 = 2 * L2_BYTES
+
+    def time_products(make_body, n_products, reps):
+        body = make_body
+        body()
+        ctx.sync()
+        batch, _ = ctx.recordBatch(body)
+        for _ in range(2):
+            batch.launch()
+        ms = timer(lambda _c: batch.launch(), reps)
+        batch.free()
+        return ms * 1e3 / (n_products * reps)
+
+    def record(cfg, shape, kernel, us, bytes_, ops, ops_peak, extra=None):
+        t_mem, t_ops = bytes_ / hbm, ops / ops_peak
+        floor = max(t_mem, t_ops)
+        r = {"config": cfg, "shape": shape, "kernel": kernel, "us": round(us, 2),
+             "bound": "hbm" if t_mem >= t_ops else "tensor",
+             "achieved": round((bytes_ / (us * 1e-6) / 1e9) if t_mem >= t_ops else (ops / (us * 1e-6) / 1e12), 1),
+             "peak": round(peaks["hbm_gbs"] if t_mem >= t_ops else ops_peak / 1e12, 1),
+             "unit": "GB/s" if t_mem >= t_ops else "TFLOP/s", "frac": round(floor / (us * 1e-6), 4),
+             "algorithmic_bytes": int(bytes_), "ops": int(ops)}
+        if extra:
+            r.update(extra)
+        out.append(r)
+
+    # ---- int8 GEMM 512 x 1024 x 4096 (seed 0) -------------------------------------------------------
+    rng = np.random.default_rng(0)
+    M, K, N = 512, 1024, 4096
+    nsets = 8 if quick else max(2, -(-l2x2 // (K * N)))
+    a = ctx.upload(rng.standard_normal((M, K)).astype(np.float32), M, K)
+    sc = ctx.upload(rng.uniform(1e-3, 1e-2, N).astype(np.float32), 1, N)
+    ws = [ctx.uploadBytes(rng.integers(-127, 128, (K, N), dtype=np.int8)) for _ in range(nsets)]
+
+    def body_i8():
+        h = ctx.pushArena()
+        for w in ws:
+            ctx.matmulInt8(a, w, sc, N, K)
+        ctx.popArena(h)
+
+    us = time_products(body_i8, nsets, 10)
+    ops = 2.0 * M * N * K
+    record("int8_gemm", f"M={M} K={K} N={N}", "k_tc_gemm<i8> (+ activation digit prepass)", us,
+           M * K * 4 + K * N + N * 4 + M * N * 4, ops, 2 * tf,
+           {"tensor_tops": round(ops / (us * 1e-6) / 1e12, 1), "frac_of_int8_tensor_peak_2x_bf16": round(ops / (us * 1e-6) / (2 * tf), 4),
+            "weight_sets": nsets})
+    for w in ws:
+        ctx.freeBytes(w)
+    ctx.freeTensor(a)
+    ctx.freeTensor(sc)
+
+    # ---- int4 decode products K = 2048, N in {2048, 8192}, M in {1, 4, 16} (seed 1) -----------------------
+    rng = np.random.default_rng(1)
+    K = 2048
+    nblk = K // 32
+    for N in (2048, 8192):
+        wbytes = N * K // 2 + N * nblk * 4 + N * (nblk // 2)
+        nsets = 8 if quick else max(2, -(-l2x2 // wbytes))
+        sets = []
+        for _ in range(nsets):
+            bq = rng.integers(0, 256, N * nblk * 16, dtype=np.uint8)
+            scl = rng.uniform(5e-3, 2e-2, N * nblk).astype(np.float16).astype(np.float32)
+            zp = np.full(N * (nblk // 2), 0x88, np.uint8)
+            sets.append((ctx.uploadBytes(bq), ctx.upload(scl, 1, scl.size), ctx.uploadBytes(zp)))
+        for M in (1, 4, 16):
+            act = ctx.upload(rng.standard_normal((M, K)).astype(np.float16).astype(np.float32), M, K)
+
+            def body_i4(act=act):
+                h = ctx.pushArena()
+                for bq, scl, zp in sets:
+                    ctx.matmulNBits(act, bq, scl, zp, N)
+                ctx.popArena(h)
+
+            us = time_products(body_i4, nsets, 10)
+            record("int4_decode", f"M={M} K={K} N={N}", "k_gemv_nbits" if M <= 4 else "k_tc_gemm (int4 weights)", us,
+                   wbytes + 4 * M * K + 4 * M * N, 2.0 * M * N * K, tf, {"weight_sets": nsets})
+            ctx.freeTensor(act)
+        for bq, scl, zp in sets:
+            ctx.freeBytes(bq)
+            ctx.freeTensor(scl)
+            ctx.freeBytes(zp)
+
+    # ---- f16-weight GEMM sweep over the encoder's shapes (seed 2) ------------------------------------
+    rng = np.random.default_rng(2)
+    KNs = ((1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024))
+    Ms = (4096,) if quick else (256, 1024, 4096, 16384)
+    for K, N in KNs:
+        w_host = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+        for M in Ms:
+            abytes, cbytes = M * K * 4, M * N * 4
+            # small products live in L2 unless the weights rotate; large ones stream activations and results anyway
+            nsets = 1 if (abytes + cbytes > l2x2 or quick) else max(2, min(64, -(-l2x2 // (K * N * 2))))
+            ws = [ctx.uploadF16(w_host, K, N) for _ in range(nsets)]
+            act = ctx.upload(rng.standard_normal((M, K)).astype(np.float32), M, K)
+
+            def body_f16(act=act, ws=ws):
+                h = ctx.pushArena()
+                for w in ws:
+                    ctx.matmul(act, w)
+                ctx.popArena(h)
+
+            us = time_products(body_f16, nsets, 10 if M <= 4096 else 4)
+            record("f16_gemm", f"M={M} K={K} N={N}", "k_tc_gemm<f16>", us, abytes + K * N * 2 + cbytes, 2.0 * M * N * K, tf,
+                   {"weight_sets": nsets})
+            ctx.freeTensor(act)
+            for w in ws:
+                ctx.freeTensor(w)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
 # arms
 # --------------------------------------------------------------------------------------------
 
@@ -808,6 +933,7 @@ def run_reference(args):
     value = float(np.mean(vals))
     line = {"impl": "reference", "metric": wl.metric, "value": round(value, 6), "unit": wl.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
+            "ms_per_step_is": "wall time of one bounded CPU sample (see cpu_baseline.sample), not of a full step of the workload",
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU port of the wasm kernels)",
             "data": "synthetic", "config": {"workload": wl.name, "note": "Node/wasm runtime absent on the box: C port of rust/wasm-kernels timed instead"},
             "cpu_baseline": {"value": round(value, 6), "unit": wl.unit, "cores": cores, "kind": "port", "sample": desc},
@@ -924,6 +1050,10 @@ def run_cuda(args):
     e2e_val = wl.value_from(args.steps, e2e_s) * units
     h2d, d2h = wl.e2e_bytes()
 
+    shapes = None
+    if world == 1 and not args.no_shapes:
+        shapes = shapes_report(ctx, peaks, timed, quick=args.quick)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle.wasm_oracle import LIB
@@ -942,7 +1072,7 @@ def run_cuda(args):
                            "roofline_timing": "per-launch CUDA event pairs, repeat pass of the same steps"},
                 "roofline": roof, "cpu_baseline": cpu,
                 "e2e": {"value": round(e2e_val, 3), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-                "gpu_launches": int(launches), "clocks": clocks,
+                "gpu_launches": int(launches), "clocks": clocks, "shapes": shapes,
                 "kernels": [{"label": e["label"], "launches": e["count"], "ms": round(e["ms"], 3)} for e in prof]}
         print(json.dumps(line), flush=True)
     ctx.destroy()
@@ -959,6 +1089,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--quick", action="store_true", help="smaller rotating set (for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape roofline records of the GEMM / GEMV shapes")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

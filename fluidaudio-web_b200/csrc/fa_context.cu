@@ -148,6 +148,16 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->int8_limbs = (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "wait_limit")) {
+    FA_REQUIRE(ctx, value >= 4096 && value <= (1ll << 28), "wait_limit must be in 4096..2^28 polls");
+    ctx->wait_limit = (unsigned)value;
+    return FA_OK;
+  }
+  if (!strcmp(key, "tc_test_withhold_chunk")) {
+    FA_REQUIRE(ctx, value >= -1 && value < 4096, "tc_test_withhold_chunk must be -1 or a K-chunk index");
+    ctx->tc_withhold_chunk = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "pool_cap_bytes")) {
     FA_REQUIRE(ctx, value >= 0, "pool_cap_bytes must be >= 0");
     ctx->pool_cap = (size_t)value;
@@ -279,6 +289,15 @@ bool fa_valid(fa_ctx *ctx, const fa_tensor *t) { return t && ctx->tensors.count(
 int fa_touch_f32(fa_ctx *ctx, const fa_tensor *t) {
   fa_tensor *m = const_cast<fa_tensor *>(t);
   if (!m || !m->f32_lazy) return FA_OK;
+  if (ctx->capturing && !m->lazy_sticky) {
+    // a result from before the open recording: the fill below would only be captured, yet the tensor would look
+    // current to an eager reader before the first replay
+    auto ow = ctx->block_owner.find(m->dptr);
+    if (ow == ctx->block_owner.end() || ow->second != ctx->capturing)
+      return fa_fail(ctx, FA_ERR_INVALID,
+                     "a hidden-layer result made before fa_graph_begin is first read as f32 inside the recording; read it "
+                     "once (or run the sequence once eagerly) before recording");
+  }
   if (!m->lazy_sticky) m->f32_lazy = false;
   return fa_unpack_a_f16(ctx, (const __half *)m->a16, m->rows, m->cols, (float *)m->dptr);
 }
@@ -328,21 +347,34 @@ static int upload_common(fa_ctx *ctx, const float *host, int rows, int cols, int
   fa_tensor *t = nullptr;
   FA_TRY(fa_tensor_new(ctx, rows, cols, storage, /*pooled=*/false, &t));  // uploads are pool-exempt
   size_t n = (size_t)rows * cols;
+  int rc = FA_OK;
   if (n) {
     if (storage == FA_F32) {
-      FA_CHECK_CUDA(ctx, cudaMemcpyAsync(t->dptr, host, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+      cudaError_t e = cudaMemcpyAsync(t->dptr, host, n * 4, cudaMemcpyHostToDevice, ctx->stream);
+      if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "upload: %s", cudaGetErrorString(e));
     } else {
       void *tmp = nullptr;
       size_t blk = 0;
-      FA_TRY(fa_block_acquire(ctx, n * 4, &tmp, &blk));
-      FA_CHECK_CUDA(ctx, cudaMemcpyAsync(tmp, host, n * 4, cudaMemcpyHostToDevice, ctx->stream));
-      {
-        LaunchScope ls(ctx, "cvt_f32_f16");
-        k_f32_to_f16<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)tmp, (__half *)t->dptr, n);
+      rc = fa_block_acquire(ctx, n * 4, &tmp, &blk);
+      if (rc == FA_OK) {
+        cudaError_t e = cudaMemcpyAsync(tmp, host, n * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) {
+          rc = fa_fail(ctx, FA_ERR_CUDA, "uploadF16: %s", cudaGetErrorString(e));
+        } else {
+          {
+            LaunchScope ls(ctx, "cvt_f32_f16");
+            k_f32_to_f16<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>((const float *)tmp, (__half *)t->dptr, n);
+          }
+          e = cudaGetLastError();
+          if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "launch cvt_f32_f16: %s", cudaGetErrorString(e));
+        }
+        fa_block_release(ctx, tmp);  // stream-ordered: the next user is queued after the convert
       }
-      FA_LAUNCH_CHECK(ctx, "cvt_f32_f16");
-      fa_block_release(ctx, tmp);  // stream-ordered: the next user is queued after the convert
     }
+  }
+  if (rc != FA_OK) {  // no half-made handle stays registered
+    fa_free_tensor(ctx, t);
+    return rc;
   }
   *out = t;
   return FA_OK;
@@ -605,16 +637,29 @@ extern "C" int fa_stage_download(fa_ctx *ctx, const fa_tensor *t, fa_staged **ou
     s->host_bytes = need;
   }
   ctx->staged.insert(s);
+  int rc = FA_OK;
   if (s->count) {
     const float *src = nullptr;
     fa_tensor *tmp = nullptr;
-    FA_TRY(fa_as_f32(ctx, t, &src, &tmp));
-    // The copy is ordered now, at stage time: later ops on the stream cannot change what is read.
-    FA_CHECK_CUDA(ctx, cudaMemcpyAsync(s->host, src, s->count * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    rc = fa_as_f32(ctx, t, &src, &tmp);
+    if (rc == FA_OK) {
+      // The copy is ordered now, at stage time: later ops on the stream cannot change what is read.
+      cudaError_t e = cudaMemcpyAsync(s->host, src, s->count * 4, cudaMemcpyDeviceToHost, ctx->stream);
+      if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "stageDownload: %s", cudaGetErrorString(e));
+    }
     if (tmp) fa_free_tensor(ctx, tmp);
   }
-  FA_CHECK_CUDA(ctx, cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming));
-  FA_CHECK_CUDA(ctx, cudaEventRecord(s->done, ctx->stream));
+  if (rc == FA_OK) {
+    cudaError_t e = cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(s->done, ctx->stream);
+    if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "stageDownload: %s", cudaGetErrorString(e));
+  }
+  if (rc != FA_OK) {  // the caller gets no handle: give the staging buffer back and forget the read
+    const std::string msg = ctx->err;
+    fa_staged_free(ctx, s);
+    ctx->err = msg;
+    return rc;
+  }
   *out = s;
   return FA_OK;
 }

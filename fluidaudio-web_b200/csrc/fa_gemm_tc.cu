@@ -84,6 +84,9 @@ struct TcParams {
   const uint8_t *nb_zp;
   int nblk;
   int *status;
+  uint32_t wait_limit;  // polls before a barrier wait gives up (fa_ctx::wait_limit)
+  int withhold_kb;      // >= 0: CTA 0 never loads this K chunk of its first tile, so the waits downstream of it run
+                        // out (the way the bounded-wait path is tested without faulting the GPU); -1 in normal use
 };
 
 __device__ __forceinline__ void report_timeout(int *status, int code, int detail) {
@@ -346,10 +349,17 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const int m0 = tm * p.MT;
         for (int kb = kb0; kb < kb1; kb++, it++, wrow += 128, aslab++) {
           const uint32_t fb = bars + s * 8u, dst = smem_base + s * stage_bytes;
-          if (it >= nst && !mbar_wait(fb + nst * 8u, ph ^ 1u)) {  // empty barrier of slot s, previous use
+          if (it >= nst && !mbar_wait(fb + nst * 8u, ph ^ 1u, p.wait_limit)) {  // empty barrier of slot s, previous use
             set_abort(1, kb);
             stop = true;
             break;
+          }
+          if (p.withhold_kb == kb && tile == 0) {  // test hook: this chunk never arrives
+            if (++s == nst) {
+              s = 0;
+              ph ^= 1u;
+            }
+            continue;
           }
           if (KIND == 2) {
             mbar_expect_tx(fb, q_bytes + kRawTileBytes);
@@ -381,7 +391,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
         const uint32_t buf = lt & 1, use = lt >> 1;
-        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1)) {
+        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit)) {
           set_abort(4, tile);
           break;
         }
@@ -389,12 +399,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const uint32_t d_tmem = tmem_base + buf * acc_stride;
         for (int kb = kb0; kb < kb1; kb++, it++) {
           const uint32_t fb = bars + s * 8u;
-          if (!mbar_wait(fb, ph)) {
+          if (!mbar_wait(fb, ph, p.wait_limit)) {
             set_abort(2, kb);
             ok = false;
             break;
           }
-          if (KIND == 2 && !mbar_wait(fb + (2u * nst + 4u) * 8u, ph)) {  // weights tile unpacked
+          if (KIND == 2 && !mbar_wait(fb + (2u * nst + 4u) * 8u, ph, p.wait_limit)) {  // weights tile unpacked
             set_abort(6, kb);
             ok = false;
             break;
@@ -468,7 +478,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           if (c >= chunks) break;
           const uint32_t it = it_base + (uint32_t)c, slot_i = it % nst, ph = (it / nst) & 1u;
           int okw = 1;
-          if (lane == 0 && !mbar_wait(full_bar((int)slot_i), ph)) {
+          if (lane == 0 && !mbar_wait(full_bar((int)slot_i), ph, p.wait_limit)) {
             set_abort(5, c);
             okw = 0;
           }
@@ -527,12 +537,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       const uint32_t buf = lt & 1, use = lt >> 1;
       if (KIND == 2) {  // leave the issue slots to the unpack warps while the tile is being accumulated
         ok = false;
-        for (uint32_t i = 0; i < (kWaitLimit >> 4) && !ok; i++) {
+        for (uint32_t i = 0; i < (p.wait_limit >> 4) && !ok; i++) {
           ok = mbar_try_wait(acc_full(buf), use & 1) != 0;
           if (!ok) __nanosleep(256);
         }
       } else {
-        ok = mbar_wait(acc_full(buf), use & 1);
+        ok = mbar_wait(acc_full(buf), use & 1, p.wait_limit);
       }
       if (!ok && lane == 0) set_abort(3, tile);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !aborted();
@@ -887,7 +897,9 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   // every SM streams weights.  Each split keeps at least 2 chunks.
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
-  if (!raw_i32 && !ep.out16 && ep.n_peers == 0 && p.batches == 1 && p.tiles_m == 1 && p.MT <= kSplitMaxMT &&
+  // (the split-K finish stores rows at pitch N: a caller-chosen pitch keeps the one-CTA-per-tile form)
+  if (!raw_i32 && !ep.out16 && ep.n_peers == 0 && (ep.ldc == 0 || ep.ldc == N) && p.batches == 1 && p.tiles_m == 1 &&
+      p.MT <= kSplitMaxMT &&
       num_tiles * 2 <= ctx->sm_count) {
     int s = ctx->sm_count / num_tiles;
     if (s > 8) s = 8;
@@ -914,6 +926,9 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.rowbias = ep.rowbias;
   p.act = ep.act;
   p.status = ctx->dev_status;
+  p.wait_limit = ctx->wait_limit;
+  p.withhold_kb = ctx->tc_withhold_chunk;
+  ctx->tc_withhold_chunk = -1;  // one launch only
   const size_t smem = stage_bytes * stages + tail_bytes;
 
   CUtensorMap map_w, map_a;

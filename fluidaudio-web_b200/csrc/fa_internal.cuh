@@ -111,6 +111,8 @@ struct fa_ctx {
   int nbits_fused = 0;     // 1: int4 products on the tensor cores unpack nibbles in shared memory (0: f16 copy, faster today)
   int gemv_rows = 4;       // products with at most this many rows run on the CUDA-core GEMV kernels (0 = never)
   int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
+  unsigned wait_limit = 1u << 24;  // polls before a device-side barrier wait gives up (about a second)
+  int tc_withhold_chunk = -1;      // test hook, one launch: see TcParams::withhold_kb
   size_t pool_cap = 0;
   // exact-size pool (the reference pools by exact byte size, buffer-pool.js:49-84)
   std::unordered_map<size_t, std::vector<void *>> pool;

@@ -35,10 +35,24 @@ int check_vec(fa_ctx *ctx, const fa_tensor *t, int n, const char *what) {
   return fa_touch_f32(ctx, t);
 }
 
+// A handle made before the open recording.  Work that such a handle caches on itself (packed weight copies,
+// operand shadows, the f32 fill of a lazy result) must not be started while recording: the kernels would only be
+// captured, the handle would look ready, and an eager use before the first replay would read unwritten memory.
+bool foreign_to_recording(fa_ctx *ctx, const void *dptr) {
+  if (!ctx->capturing) return false;
+  auto it = ctx->block_owner.find(const_cast<void *>(dptr));
+  return it == ctx->block_owner.end() || it->second != ctx->capturing;
+}
+#define FA_NO_FIRST_USE_IN_RECORDING(ctx, dptr, what)                                                              \
+  FA_REQUIRE(ctx, !foreign_to_recording(ctx, dptr),                                                                \
+             "%s: the packed copy of these weights is built on their first use, which must not happen inside a "   \
+             "recording; run the sequence once eagerly before fa_graph_begin", what)
+
 // Packed f16 copy of a [K][N] weight tensor, built once per handle.
 int ensure_bt_f16(fa_ctx *ctx, fa_tensor *b) {
   if (b->view) return fa_fail(ctx, FA_ERR_INVALID, "matmul: a rowsView cannot be the weight operand of a large product");
   if (b->bt_f16) return FA_OK;
+  FA_NO_FIRST_USE_IN_RECORDING(ctx, b->dptr, "matmul");
   FA_TRY(fa_block_acquire(ctx, fa_tc_weight_bytes(b->cols, b->rows, 2), &b->bt_f16, &b->bt_bytes));
   return fa_pack_w_f16(ctx, b->dptr, b->storage, b->rows, b->cols, (__half *)b->bt_f16);
 }
@@ -46,6 +60,7 @@ int ensure_bt_f16(fa_ctx *ctx, fa_tensor *b) {
 // Packed int8 copy of a [K][N] int8 payload, built once per handle and (N,K).
 int ensure_nk_i8(fa_ctx *ctx, fa_bytes *wq, int N, int K) {
   if (wq->nk_i8 && wq->nk_N == N && wq->nk_K == K) return FA_OK;
+  FA_NO_FIRST_USE_IN_RECORDING(ctx, wq->dptr, "matmulInt8");
   if (wq->nk_i8) fa_block_release(ctx, wq->nk_i8);
   wq->nk_i8 = nullptr;
   FA_TRY(fa_block_acquire(ctx, fa_tc_weight_bytes(N, K, 1), &wq->nk_i8, &wq->nk_bytes));
@@ -133,7 +148,10 @@ static int fa_shadow_hilo_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out) 
 static int row_operand_f16(fa_ctx *ctx, const fa_tensor *a, const float *ap, Scratch &sa, const __half **out,
                            bool *hilo) {
   *hilo = a->rows <= ctx->f16_hilo_rows;
-  const bool can_shadow = a->storage == FA_F32 && !a->view;
+  // (a tensor from before the open recording that has no current shadow of the right kind is packed into per-call
+  // scratch instead: a shadow started here would be marked valid while its kernel is only captured)
+  const bool have = a->a16 && a->a16_valid && a->a16_hilo == *hilo;
+  const bool can_shadow = a->storage == FA_F32 && !a->view && (have || !foreign_to_recording(ctx, a->dptr));
   if (*hilo) {
     if (can_shadow) return fa_shadow_hilo_ensure(ctx, const_cast<fa_tensor *>(a), out);
     FA_TRY(sa.get(fa_tc_act_bytes(a->rows, a->cols, 2, 2)));
@@ -196,7 +214,7 @@ static int matmul_impl(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_t
       const bool hinted = operand_hint && !add && fa_operand_only_ok(ctx, M, N);
       if ((act != FA_ACT_NONE || hinted) && (N & 63) == 0 && (ep.out16 = fa_shadow_block(ctx, c)) != nullptr) {
         c->a16_valid = true;
-        if (ctx->lazy_f32 && !add) {  // ... and only as that: the f32 copy is made if and when something else reads it
+        if (ctx->lazy_f32 && !add && fa_operand_only_ok(ctx, M, N)) {  // ... and only as that: the f32 copy is made if and when something else reads it
           ep.skip_f32 = true;
           c->f32_lazy = true;
           c->lazy_sticky = ctx->capturing != nullptr;
@@ -345,6 +363,7 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
                         bq->side_zp == zp->dptr;
     const size_t tb = fa_nbits_tiles_bytes(N, K), sb = (size_t)N * nblk * 4;
     if (!cached) {  // one-time tensor-core form of this handle: nibble tiles, block-major scales and zero-points
+      FA_NO_FIRST_USE_IN_RECORDING(ctx, bq->dptr, "matmulNBits");
       if (bq->nb_side) fa_block_release(ctx, bq->nb_side);
       bq->nb_side = nullptr;
       rc = fa_block_acquire(ctx, tb + sb + (size_t)N * nblk, &bq->nb_side, &bq->nb_side_bytes);
@@ -370,6 +389,7 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
     const bool cached = bq->nk_f16 && bq->f16_N == N && bq->f16_K == K && bq->f16_scales == scales->dptr &&
                         bq->f16_zp == zp->dptr;
     if (!cached) {
+      FA_NO_FIRST_USE_IN_RECORDING(ctx, bq->dptr, "matmulNBits");
       if (bq->nk_f16) fa_block_release(ctx, bq->nk_f16);
       bq->nk_f16 = nullptr;
       rc = fa_block_acquire(ctx, fa_tc_weight_bytes(N, K, 2), &bq->nk_f16, &bq->nk_f16_bytes);
@@ -416,17 +436,13 @@ extern "C" int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_by
   int rc = FA_OK;
   FA_TRY(ensure_nk_i8(ctx, wq, N, K));
   // stage the caller's int8 activations row-major, then pack them into the chunk-major operand layout
-  void *raw = nullptr;
-  size_t raw_bytes = 0;
-  FA_TRY(fa_block_acquire(ctx, (size_t)M * K, &raw, &raw_bytes));
-  FA_CHECK_CUDA(ctx, cudaMemcpyAsync(raw, aq_host, (size_t)M * K, cudaMemcpyHostToDevice, ctx->stream));
-  Scratch sa(ctx);
+  Scratch raw(ctx), sa(ctx), acc_s(ctx);
+  FA_TRY(raw.get((size_t)M * K));
+  FA_CHECK_CUDA(ctx, cudaMemcpyAsync(raw.p, aq_host, (size_t)M * K, cudaMemcpyHostToDevice, ctx->stream));
   FA_TRY(sa.get(fa_tc_act_bytes(M, K, 1, 1)));
-  FA_TRY(fa_pack_a_i8_raw(ctx, (const int8_t *)raw, M, K, (int8_t *)sa.p));
-  fa_block_release(ctx, raw);
-  void *acc = nullptr;
-  size_t got = 0;
-  FA_TRY(fa_block_acquire(ctx, (size_t)M * N * 4, &acc, &got));
+  FA_TRY(fa_pack_a_i8_raw(ctx, (const int8_t *)raw.p, M, K, (int8_t *)sa.p));
+  FA_TRY(acc_s.get((size_t)M * N * 4));
+  void *acc = acc_s.p;
   TcEpilogue ep;
   rc = fa_tc_gemm_i8(ctx, (const int8_t *)sa.p, 1, (const int8_t *)wq->nk_i8, acc, true, M, N, K, ep);
   if (rc == FA_OK) {
@@ -434,6 +450,5 @@ extern "C" int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_by
     if (e != cudaSuccess) rc = fa_fail(ctx, FA_ERR_CUDA, "int8GemmI32 readback: %s", cudaGetErrorString(e));
   }
   if (rc == FA_OK) rc = fa_sync(ctx);
-  fa_block_release(ctx, acc);
   return rc;
 }

@@ -41,10 +41,11 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// Bounded wait.  Returns false when the limit ran out (about a second of polling).
+// Bounded wait.  Returns false when `limit` polls ran out (the default, kWaitLimit, is about a second; the context
+// option "wait_limit" shortens it).
 constexpr uint32_t kWaitLimit = 1u << 24;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; i++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = kWaitLimit) {
+  for (uint32_t i = 0; i < limit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 4096) __nanosleep(64);
   }

@@ -73,7 +73,12 @@ const char *fa_last_error(fa_ctx *ctx);
  * a tensor-core product with a fused activation is written only as the packed f16 operand of the next product;
  * its f32 storage is filled from that, f16-rounded, the first time anything else reads it; the same holds for
  * the results of layernormOperand, gluDwConvTimeMajor and attnFused), "attn_one_kernel" (0/1, default 1:
- * attnFused runs as one kernel per call when head width is 128 and T <= 192; 0 = the batched-GEMM form). */
+ * attnFused runs as one kernel per call when head width is 128 and T <= 192; 0 = the batched-GEMM form),
+ * "wait_limit" (4096..2^28, default 2^24, about a second: polls after which a device-side barrier wait gives
+ * up; the kernel then records a status word, unwinds and returns, and the next fa_sync fails with
+ * FA_ERR_TIMEOUT while the context stays usable), "tc_test_withhold_chunk" (-1 = off; k >= 0: test hook for that
+ * path - in the NEXT tensor-core product only, one thread block never loads K chunk k of its first tile, so
+ * the waits behind it run out; the product's result is then undefined). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);
@@ -131,7 +136,12 @@ int fa_end_batch(fa_ctx *ctx);   /* endBatch :149 */
  * fa_graph_launch replays them with one submission.  Rules: no download/sync/staged read while recording;
  * uploads inside a recording must come from fa_host_alloc memory (replays re-read that memory);
  * device blocks touched by the recording stay reserved for the graph until fa_graph_free, so tensors made
- * inside it (its outputs) stay valid across replays. */
+ * inside it (its outputs) stay valid across replays.
+ * Run the sequence once eagerly before recording it: handles cache work on their first use (the packed
+ * tensor-core copy of a weight matrix, the f32 fill of a hidden-layer result), and a first use inside a
+ * recording would only be captured while the handle already looked ready.  Such a first use of a handle
+ * made before fa_graph_begin fails with FA_ERR_INVALID; row operands from before the recording that carry
+ * no packed copy yet are packed into per-call scratch on every replay instead. */
 int fa_graph_begin(fa_ctx *ctx);
 int fa_graph_end(fa_ctx *ctx, fa_graph **out);
 int fa_graph_launch(fa_ctx *ctx, fa_graph *g);
@@ -140,7 +150,13 @@ int fa_graph_free(fa_ctx *ctx, fa_graph *g);
 /* ---- linear algebra: the hot path (compute.d.ts:153-168) ------------------- */
 /* matmul :155, and matmulV2/V3/V4/F16 :158-162 (one shape-routed implementation):
  * C = act(A[M,K] @ B[K,N] + bias[1,N]) + add[M,N].  bias/add may be NULL.  B may be f32 or
- * f16 storage (uploadF16); routing is by shape and storage only. */
+ * f16 storage (uploadF16); routing is by shape and storage only.
+ * Precision: f32-storage B and small or ragged shapes are computed in f32.  Against f16-storage B a
+ * tensor-core sized product rounds A to f16 (to f16 value + f16 residue, ~22 bits, for at most
+ * "f16_hilo_rows" rows) and accumulates in f32 - the reference's f16-B route (tolerance 2e-2 in its gate).
+ * With option "lazy_f32" (default) a result with a fused activation and no residual, large enough that every
+ * product consuming it takes the tensor-core route (more than "f16_hilo_rows" rows, rows*cols*64 >= 2^21), is
+ * kept as its packed f16 operand; read any other way it comes back rounded to f16 (relative 5e-4). */
 int fa_matmul(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_tensor *bias, int act, const fa_tensor *add,
               fa_tensor **out);
 /* Optional member matmul(..., {operandOnly: true}): the caller states that the result is only read as a packed f16

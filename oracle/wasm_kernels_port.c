@@ -127,22 +127,29 @@ ORACLE_API void wk_matmul_int8(const float *a, const uint8_t *wq, const float *s
  * accumulator per output) with the loops interchanged to i, k, j so the weight
  * row is read contiguously; bit-identical results, used for larger parity cases
  * and the multithreaded CPU baseline.  Needs `acc` scratch of n floats per row. */
-static void int8_row_kj(const float *arow, const uint8_t *wq, const float *scale, float *yrow, size_t n, size_t k) {
-  for (size_t j = 0; j < n; j++) yrow[j] = 0.0f;
+static void int8_row_kj(const float *arow, const uint8_t *wq, const float *scale, float *yrow, size_t n, size_t k,
+                        size_t j0, size_t j1) {
+  for (size_t j = j0; j < j1; j++) yrow[j] = 0.0f;
   for (size_t kk = 0; kk < k; kk++) {
     const float av = arow[kk];
     const int8_t *wrow = (const int8_t *)(wq + kk * n);
-    for (size_t j = 0; j < n; j++) {
+    for (size_t j = j0; j < j1; j++) {
       float p = av * (float)wrow[j];
       yrow[j] = yrow[j] + p;
     }
   }
-  for (size_t j = 0; j < n; j++) yrow[j] = yrow[j] * scale[j];
+  for (size_t j = j0; j < j1; j++) yrow[j] = yrow[j] * scale[j];
 }
+/* Work items are (row, block of 512 columns): outputs are independent, so few-row products (token-by-token
+ * decoding) spread over the threads as well. */
 ORACLE_API void wk_matmul_int8_kj(const float *a, const uint8_t *wq, const float *scale, float *y, size_t m, size_t n,
                                   size_t k) {
+  const long cb = 512, nb = (long)((n + cb - 1) / cb);
 #pragma omp parallel for schedule(static)
-  for (long i = 0; i < (long)m; i++) int8_row_kj(a + (size_t)i * k, wq, scale, y + (size_t)i * n, n, k);
+  for (long w = 0; w < (long)m * nb; w++) {
+    const size_t i = (size_t)(w / nb), j0 = (size_t)(w % nb) * cb, j1 = j0 + cb < n ? j0 + cb : n;
+    int8_row_kj(a + i * k, wq, scale, y + i * n, n, k, j0, j1);
+  }
 }
 /* The reference loop order itself, rows over OpenMP threads (timed CPU baseline). */
 ORACLE_API void wk_matmul_int8_mt(const float *a, const uint8_t *wq, const float *scale, float *y, size_t m, size_t n,

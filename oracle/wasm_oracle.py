@@ -134,7 +134,10 @@ class WasmOracle:
     def __init__(self, threads: bool = False):
         # threads=True uses the bit-identical multi-threaded forms of the three GEMMs
         # (rows/columns are independent); default follows the reference's serial loops.
+        # For int8 that is the i,k,j loop order: every output still sums its k terms in order, so the
+        # result is bit-identical to the reference's i,j,k order while the weight bytes are read row-wise.
         self._mt = threads
+        self._int8_order = "ikj" if threads else "ijk"
 
     # -- memory / tensors (:53-123) ------------------------------------------------
     def upload(self, data, rows, cols):
@@ -226,7 +229,8 @@ class WasmOracle:
 
     matmulV3 = matmulV4 = matmulF16 = matmulV2
 
-    def matmulInt8(self, a, wq, scale, N, K, bias=None, act="none", loop_order="ijk"):
+    def matmulInt8(self, a, wq, scale, N, K, bias=None, act="none", loop_order=None):
+        loop_order = loop_order or self._int8_order
         M = a.rows
         assert a.cols == K and wq.bytes.size >= K * N
         out = np.empty(M * N, np.float32)

@@ -1,0 +1,82 @@
+"""Error paths that must leave the context usable: a device-side bounded wait that runs out, and first
+uses that a recording must not swallow.  No GPU fault is provoked anywhere: the wait test withholds one
+asynchronous copy, so a barrier is simply never completed and the kernel's own poll limit ends the wait."""
+import numpy as np
+import pytest
+
+from oracle.wasm_oracle import T, WasmOracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _product(ctx, rng, M=256, K=512, N=256):
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    return a, w, ctx.upload(a, M, K), ctx.uploadF16(w, K, N)
+
+
+def test_bounded_wait_runs_out_and_context_survives(pkg):
+    """One thread block of a tensor-core product never gets K chunk 3 of its first tile: the MMA warp's wait on
+    that stage gives up after `wait_limit` polls (a few milliseconds here, not the default second), the kernel
+    records a status word, unwinds, frees its TMEM and returns; fa_sync reports FA_ERR_TIMEOUT; the next product
+    on the same context is correct."""
+    ctx = pkg.CudaContext(0)
+    try:
+        rng = np.random.default_rng(3)
+        a, w, A, Wt = _product(ctx, rng)
+        ref = WasmOracle(threads=True).matmul(T(a, 256, 512), T(w, 512, 256)).array()
+        good = ctx.download(ctx.matmul(A, Wt)).reshape(256, 256)  # also builds the packed weight copy
+        assert np.abs(good - ref).max() <= 2e-2
+        ctx.setOption("wait_limit", 20000)
+        ctx.setOption("tc_test_withhold_chunk", 3)
+        ctx.matmul(A, Wt)
+        with pytest.raises(pkg.CudaError) as ei:
+            ctx.sync()
+        assert ei.value.code == 5 and "bounded wait ran out" in str(ei.value)  # FA_ERR_TIMEOUT
+        ctx.setOption("wait_limit", 1 << 24)
+        again = ctx.download(ctx.matmul(A, Wt)).reshape(256, 256)
+        assert np.array_equal(again, good)
+        ctx.sync()  # status word was cleared: no stale error
+    finally:
+        ctx.destroy()
+
+
+def test_first_use_of_a_weight_inside_a_recording_is_refused(pkg):
+    """The packed tensor-core copy of a weight is built on first use.  Inside a recording that step would only be
+    captured while the handle already looked ready, and an eager product before the first replay would read
+    unwritten memory; the library refuses instead, and after one eager run recording works and eager use between
+    recording and replay is correct."""
+    ctx = pkg.CudaContext(0)
+    try:
+        rng = np.random.default_rng(4)
+        a, w, A, Wt = _product(ctx, rng)
+        ref = WasmOracle(threads=True).matmul(T(a, 256, 512), T(w, 512, 256)).array()
+        with pytest.raises(pkg.CudaError, match="eagerly before"):
+            ctx.recordBatch(lambda: ctx.matmul(A, Wt))
+        ctx.freeTensor(ctx.matmul(A, Wt))  # once eagerly
+        batch, out = ctx.recordBatch(lambda: ctx.matmul(A, Wt))
+        eager = ctx.download(ctx.matmul(A, Wt)).reshape(256, 256)  # before any replay
+        assert np.abs(eager - ref).max() <= 2e-2
+        batch.launch()
+        assert np.array_equal(ctx.download(out).reshape(256, 256), eager)
+        batch.free()
+    finally:
+        ctx.destroy()
+
+
+def test_row_operand_from_before_a_recording_is_repacked_per_replay(pkg):
+    """A row operand uploaded before the recording and first used inside it carries no packed copy: it is packed
+    into per-call scratch on every replay, so a replay sees new contents written into it in between."""
+    ctx = pkg.CudaContext(0)
+    try:
+        rng = np.random.default_rng(5)
+        a, w, A, Wt = _product(ctx, rng)
+        A2 = ctx.upload(a, 256, 512)  # never used eagerly as an operand
+        ctx.freeTensor(ctx.matmul(A, Wt))
+        batch, out = ctx.recordBatch(lambda: ctx.matmul(A2, Wt))
+        want = ctx.download(ctx.matmul(A2, Wt)).reshape(256, 256)  # eager, before the first replay
+        batch.launch()
+        assert np.array_equal(ctx.download(out).reshape(256, 256), want)
+        batch.free()
+    finally:
+        ctx.destroy()

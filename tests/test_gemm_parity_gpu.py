@@ -327,6 +327,21 @@ def test_matmul_scatter_writes_every_result_buffer(ctx, oracle):
         assert np.array_equal(got, first)  # every buffer holds the same bits
 
 
+def test_matmul_scatter_single_buffer_wide_pitch_few_rows(ctx, oracle):
+    """One result buffer whose row pitch is wider than the product, with 65..128 rows and few column tiles: the
+    shape class that would otherwise take the K-split cluster form, whose finish writes rows at pitch N."""
+    rng = np.random.default_rng(13)
+    M, K, Ns, ldc, col0 = 96, 1024, 256, 640, 130  # col0 not a multiple of 4 either
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, Ns)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    ref = oracle.matmul(oracle.upload(a, M, K), oracle.upload(b, K, Ns)).array()
+    buf = ctx.upload(np.full((M, ldc), -7.0, np.float32), M, ldc)
+    ctx.matmulScatter(ctx.upload(a, M, K), ctx.uploadF16(b, K, Ns), [ctx.devicePtr(buf)], ldc, col0)
+    got = ctx.download(buf).reshape(M, ldc)
+    assert np.all(got[:, :col0] == -7.0) and np.all(got[:, col0 + Ns:] == -7.0)
+    assert np.abs(got[:, col0:col0 + Ns] - ref).max() <= 2e-2
+
+
 def test_hidden_layer_result_is_lazy_and_consistent(ctx, oracle):
     """A product with a fused activation writes only the packed f16 operand of the next product; its f32
     storage is filled (f16-rounded) when something else reads it.  The chained product is bit-identical with
