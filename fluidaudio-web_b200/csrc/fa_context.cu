@@ -148,6 +148,16 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->int8_limbs = (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "tc_tile_rows")) {
+    FA_REQUIRE(ctx, value >= 0 && value <= 256, "tc_tile_rows must be 0 (automatic) or 16..256");
+    ctx->tc_tile_rows = (int)value;
+    return FA_OK;
+  }
+  if (!strcmp(key, "tc_split_k")) {
+    FA_REQUIRE(ctx, value >= 0 && value <= 8, "tc_split_k must be 0 (automatic) or 1..8");
+    ctx->tc_split_k = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "wait_limit")) {
     FA_REQUIRE(ctx, value >= 4096 && value <= (1ll << 28), "wait_limit must be in 4096..2^28 polls");
     ctx->wait_limit = (unsigned)value;
@@ -330,6 +340,8 @@ int fa_tensor_new(fa_ctx *ctx, int rows, int cols, int storage, bool pooled, fa_
 static void tensor_drop_storage(fa_ctx *ctx, fa_tensor *t) {
   if (t->view) return;
   if (t->bt_f16) fa_block_release(ctx, t->bt_f16);
+  if (t->bt_tf32) fa_block_release(ctx, t->bt_tf32);
+  t->bt_tf32 = nullptr;
   if (t->a16) fa_block_release(ctx, t->a16);
   if (t->hk16) fa_block_release(ctx, t->hk16);
   t->hk16 = nullptr;

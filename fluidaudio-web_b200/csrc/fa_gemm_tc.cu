@@ -83,7 +83,10 @@ struct TcParams {
   const float *nb_scales;
   const uint8_t *nb_zp;
   int nblk;
+  int w_lo_rows;        // KIND 4: row offset of the weights' residue plane in the weight map
   int *status;
+  int tma_out;          // 1: results leave through shared-memory slabs and TMA stores (see epilogue_tile)
+  uint32_t slab_f16_off;  // byte offset of the f16 slabs behind the f32 slabs (0 when no f32 result is stored)
   uint32_t wait_limit;  // polls before a barrier wait gives up (fa_ctx::wait_limit)
   int withhold_kb;      // >= 0: CTA 0 never loads this K chunk of its first tile, so the waits downstream of it run
                         // out (the way the bounded-wait path is tested without faulting the GPU); -1 in normal use
@@ -139,9 +142,20 @@ __device__ __forceinline__ void act16(float (&v)[16], int act) {
 
 // One tile's epilogue for one warp: TMEM lanes [32*quad, 32*quad+32) = output columns n0 + 32*quad + lane,
 // column chunks c = 16*half, 16*half + 32, ... = output rows m0 + c .. m0 + c + 15.
+//
+// Where results go.  Plain products (one batch, no peer buffers, no K split) stage every 16-row x 32-column block
+// in a slab of shared memory owned by the warp - lane = column, so the 32 lanes of a store instruction fill one
+// 128-byte row and no bank is hit twice - and one lane hands the slab to the copy engine (cp.async.bulk.tensor
+// store: rows and columns past the edge of the tensor are clipped by the engine).  The epilogue warps then never
+// wait on the global store path: with per-lane st.global a 128 x 224 tile spent 1.7 us of its 8.6 us there,
+// next to a 6 us main loop.  Two slabs per warp and per result kind alternate; before a slab is refilled the
+// issuing lane waits until the store that last used it has finished reading it.  The other modes (batched
+// attention products, peer stores, raw int32, ragged row pitches) keep the direct stores.
 template <int KIND, bool PEERS = false>
 __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_addr, int n0, int m0, int quad, int lane,
-                                              int half, float *outb, int r16, int c16, uint32_t partial) {
+                                              int half, float *outb, int r16, int c16, uint32_t partial,
+                                              const CUtensorMap *map_o, const CUtensorMap *map_o16, uint32_t slab_f32,
+                                              uint32_t slab_f16, uint32_t &slab_turn) {
   const int n = n0 + quad * 32 + lane;
   const bool n_ok = n < p.N;
   const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
@@ -204,7 +218,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
     float v[16];
 #pragma unroll
     for (int j = 0; j < 16; j++) {
-      if (KIND == 0) {
+      if (KIND != 1) {
         v[j] = __uint_as_float(v0[j]);
       } else {
         v[j] = (float)(int32_t)v0[j];
@@ -223,6 +237,34 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
 #pragma unroll
     for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs) + rb[j];
     act16(v, p.act);
+    if (!PEERS && p.tma_out) {
+      const uint32_t b = slab_turn & 1u;
+      slab_turn++;
+      if (lane == 0) tma_store_wait_read<1>();  // the group that used slab b two blocks ago has read it
+      __syncwarp();
+      if (p.out16) {
+        const uint32_t dst = slab_f16 + b * 1024u + (uint32_t)lane * 2u;
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst + (uint32_t)j * 64u), "h"(__half_as_ushort(__float2half_rn(v[j] + ad[j])))
+                       : "memory");
+      }
+      if (!p.skip_f32) {
+        const uint32_t dst = slab_f32 + b * 2048u + (uint32_t)lane * 4u;
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + (uint32_t)j * 128u), "f"(v[j] + ad[j]) : "memory");
+      }
+      fence_proxy_async_smem();  // the copy engine reads the slab through the async proxy
+      __syncwarp();
+      if (lane == 0) {
+        const int gn = n0 + quad * 32 + c16;
+        if (p.out16) tma_store_3d(map_o16, slab_f16 + b * 1024u, gn & 63, r16 + m0 + c, gn >> 6);
+        if (!p.skip_f32) tma_store_2d(map_o, slab_f32 + b * 2048u, n0 + quad * 32, m0 + c);
+        tma_store_commit();
+      }
+      continue;
+    }
     if (n_ok) {
       if (p.out16) {  // shadow: Ap[k/64][row][k%64] of the output tensor, 32 lanes = 64 contiguous bytes
         const int gn = n + c16;
@@ -253,6 +295,11 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
   }
 }
 
+// KIND 4: f32 weights AND f32 activations on the tensor cores (kind::tf32), each operand as two planes - the f32 value,
+// of which the MMA reads the top 19 bits, and what that truncation drops, computed by the prepass - with three products
+// per K step (value x value, residue x value, value x residue) accumulated into the same TMEM columns: f32 range,
+// relative error ~2^-20 per term, which is how f32-storage B keeps the reference's f32 arithmetic (1e-3 gate with three
+// orders of magnitude to spare) at tensor-core speed.  A stage holds both weight planes and both activation planes.
 // KIND 0: f16 weights, 1: int8 weights, 2: int4 (MatMulNBits) weights, 3: f16 weights with the epilogue also storing
 // into peer GPUs' result buffers (TcParams::peer_out; a separate instantiation so the common epilogue stays lean -
 // as a run-time loop it cost the plain f16 product 5 %).  KIND 2 is the f16 pipeline with one more
@@ -264,15 +311,17 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
 // extracts); the activation tile is packed in the same order, and a sum over k does not care.
 template <int KIND>
 __global__ void __launch_bounds__(KIND == 2 ? kThreadsNbits : kThreads, 1)
-k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
-  constexpr int MK = KIND >= 2 ? 0 : KIND;  // MMA kind and epilogue arithmetic (KIND 3: f16 with peer stores)
+k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+          const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_o16, const TcParams p) {
+  constexpr int MK = KIND == 4 ? 2 : (KIND >= 2 ? 0 : KIND);  // MMA kind and epilogue arithmetic (KIND 3: f16 with peer stores)
+  constexpr uint32_t kWTiles = KIND == 4 ? 2u : 1u;  // weight tiles per stage (KIND 4: value and residue planes)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B | raw nibble tile 4 KB for KIND 2), barriers,
   // split-K partial tile
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int q_rows = p.MT * p.limbs;
   const uint32_t q_bytes = (uint32_t)q_rows * kRowBytes;
-  const uint32_t stage_bytes = kPTileBytes + q_bytes + (KIND == 2 ? kRawTileBytes : 0);
+  const uint32_t stage_bytes = kWTiles * kPTileBytes + q_bytes + (KIND == 2 ? kRawTileBytes : 0);
   const uint32_t bars = smem_base + (uint32_t)p.stages * stage_bytes;  // 8-byte aligned (stage_bytes % 1024 == 0)
   auto full_bar = [&](int s) { return bars + (uint32_t)s * 8u; };
   auto empty_bar = [&](int s) { return bars + (uint32_t)(p.stages + s) * 8u; };
@@ -283,6 +332,9 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   const uint32_t abort_flag = tmem_slot + 4u;
   const uint32_t partial = (tmem_slot + 16u + 15u) & ~15u;  // [MT][128] f32, split-K mode only; 16-byte aligned for
                                                             // the vector loads of the reduction (3*stages+4 may be odd)
+  // store slabs of the epilogue warps (tma_out mode only, never together with the split-K tile): per warp two
+  // [16][32] f32 slabs, then per warp two [16][32] f16 slabs
+  const uint32_t slabs = (tmem_slot + 16u + 127u) & ~127u;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int acc_cols = p.limb_sum ? p.MT : q_rows;
@@ -308,6 +360,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     fence_proxy_async_smem();
     tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_a);
+    if (p.tma_out) {
+      if (!p.skip_f32) tma_prefetch_desc(&map_o);
+      if (p.out16) tma_prefetch_desc(&map_o16);
+    }
   }
   if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
   tc_fence_before();
@@ -367,10 +423,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           } else {
             mbar_expect_tx(fb, stage_bytes);
             tma_load_2d(dst, &map_w, 0, wrow, fb);
+            if (KIND == 4) tma_load_2d(dst + kPTileBytes, &map_w, 0, wrow + p.w_lo_rows, fb);  // residue plane
           }
-          tma_load_3d(dst + kPTileBytes, &map_a, 0, m0, aslab, fb);
+          tma_load_3d(dst + kWTiles * kPTileBytes, &map_a, 0, m0, aslab, fb);
           for (int l = 1; l < p.limbs; l++)
-            tma_load_3d(dst + kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
+            tma_load_3d(dst + kWTiles * kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
           if (++s == nst) {
             s = 0;
             ph ^= 1u;
@@ -385,7 +442,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       const uint32_t idesc = make_idesc(MK, 128, acc_cols);
       const uint32_t nst = (uint32_t)p.stages;
       const uint64_t desc0 = smem_desc_sw128(smem_base);  // slot 0 weights tile; other tiles are address offsets
-      const uint64_t q_off = (uint64_t)(kPTileBytes >> 4), st_off = (uint64_t)(stage_bytes >> 4);
+      const uint64_t q_off = (uint64_t)((kWTiles * kPTileBytes) >> 4), st_off = (uint64_t)(stage_bytes >> 4);
+      const uint64_t wlo_off = (uint64_t)(kPTileBytes >> 4);  // KIND 4: residue plane of the weights
       const uint64_t lo_off = (uint64_t)((p.MT * kRowBytes) >> 4);  // residue plane of the activations
       uint32_t s = 0, ph = 0, it = 0, lt = 0;
       bool ok = true;
@@ -420,6 +478,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             umma<MK>(d_tmem, da + 2, db + lo_off + 2, idesc, 1u);
             umma<MK>(d_tmem, da + 4, db + lo_off + 4, idesc, 1u);
             umma<MK>(d_tmem, da + 6, db + lo_off + 6, idesc, 1u);
+          }
+          if (KIND == 4) {  // weights' residue x activations' value
+            umma<MK>(d_tmem, da + wlo_off, db, idesc, 1u);
+            umma<MK>(d_tmem, da + wlo_off + 2, db + 2, idesc, 1u);
+            umma<MK>(d_tmem, da + wlo_off + 4, db + 4, idesc, 1u);
+            umma<MK>(d_tmem, da + wlo_off + 6, db + 6, idesc, 1u);
           }
           umma_commit(fb + nst * 8u);  // frees the slot when these MMAs have read it
           if (++s == nst) {
@@ -526,7 +590,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   } else {
     // ---- epilogue: TMEM -> registers -> global (or -> smem partial in split-K mode) -------------
     const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
-    uint32_t lt = 0;
+    uint32_t lt = 0, slab_turn = 0;
+    const uint32_t slab_f32 = slabs + (uint32_t)ew * 4096u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)ew * 2048u;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
       const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
@@ -549,12 +614,15 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       if (!ok) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial);
+      epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial, &map_o, &map_o16,
+                                   slab_f32, slab_f16, slab_turn);
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty(buf));
     }
+    if (p.tma_out && lane == 0) tma_store_wait_all();  // the slabs must outlive the stores that read them
+    __syncwarp();
   }
 
   if (p.splitk > 1) {
@@ -707,6 +775,41 @@ __global__ void k_prep_a_f16_hilo(const float *__restrict__ a, int M, int K, int
   }
 }
 
+// f32 [M][K] -> two f32 planes Ap[2][k/32][m][k%32] for the kind::tf32 product: the value as is (the MMA reads its top
+// 19 bits) and what that truncation drops, a - trunc19(a), exact in f32.
+__global__ void k_prep_a_tf32(const float *__restrict__ a, int M, int K, int nch, float *__restrict__ out) {
+  fa_grid_dep_sync();
+  const size_t total = (size_t)nch * M * 32;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int kk = (int)(i % 32), m = (int)((i / 32) % M), c = (int)(i / ((size_t)32 * M));
+    const int k = c * 32 + kk;
+    const float x = k < K ? a[(size_t)m * K + k] : 0.0f;
+    out[i] = x;
+    out[total + i] = x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+  }
+}
+
+// f32 [K][N] -> Wp[2][n/128][k/32][n%128][k%32] (value plane, residue plane), 32x32 tiles through shared memory;
+// the destination was zero-filled.
+__global__ void k_pack_w_tf32(const float *__restrict__ w, int K, int N, int nch, size_t plane, float *__restrict__ out) {
+  __shared__ float t[32][33];
+  const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    int k = k0 + r, n = n0 + threadIdx.x;
+    t[r][threadIdx.x] = (k < K && n < N) ? w[(size_t)k * N + n] : 0.0f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < K) {
+      const float x = t[threadIdx.x][r];
+      const size_t o = (((size_t)(n >> 7) * nch + (k >> 5)) * 128 + (n & 127)) * 32 + (k & 31);
+      out[o] = x;
+      out[plane + o] = x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    }
+  }
+}
+
 // One CTA per activation row: s = max|a|/127 (1 when the row is all zero), r = a/s,
 // q1 = rint(r), q2 = rint((r-q1)*128), q3 = rint(((r-q1)*128-q2)*128); planes Ap[limb][k/128][m][k%128].
 // With one limb this is the usual symmetric per-row int8 quantiser; each further limb adds 7 bits.
@@ -847,7 +950,7 @@ int grid_for(fa_ctx *ctx, size_t n, int block, int per_sm) {
 template <int KIND>
 int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs, void *out, bool raw_i32, int M, int N,
               int K, const TcEpilogue &ep) {
-  const int elem = KIND == 1 ? 1 : 2;
+  const int elem = KIND == 1 ? 1 : (KIND == 4 ? 4 : 2);
   TcParams p{};
   p.M = M;
   p.N = N;
@@ -892,26 +995,67 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.o16_rows = ep.o16_rows > 0 ? ep.o16_rows : M;
   p.o16_row_hi = ep.o16_row_hi;
   p.o16_col_lo = ep.o16_col_lo;
-  const int num_tiles = p.tiles_n * p.tiles_m * p.batches;
-  // Decode-size products have fewer tiles than SMs: split K across a cluster (<= 8 CTAs) so that
-  // every SM streams weights.  Each split keeps at least 2 chunks.
+  int num_tiles = p.tiles_n * p.tiles_m * p.batches;
+  // Products with less than one wave of tiles (decode sizes, thin encoder shapes): split K across a cluster of up to
+  // 8 CTAs and, if that helps, cut the rows into shorter tiles, so that every SM streams operands.  Tile height and
+  // split are chosen together by a cost in units of "128-byte operand rows staged by the busiest CTA":
+  //   rounds over the SMs x (K chunks per CTA x (128 weight rows + MT x planes activation rows) + a fixed
+  //   prologue/epilogue term) + the cluster reduction of a split tile.
+  // (the split-K finish stores rows at pitch N: a caller-chosen pitch keeps the one-CTA-per-tile form)
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
-  // (the split-K finish stores rows at pitch N: a caller-chosen pitch keeps the one-CTA-per-tile form)
-  if (!raw_i32 && !ep.out16 && ep.n_peers == 0 && (ep.ldc == 0 || ep.ldc == N) && p.batches == 1 && p.tiles_m == 1 &&
-      p.MT <= kSplitMaxMT &&
-      num_tiles * 2 <= ctx->sm_count) {
-    int s = ctx->sm_count / num_tiles;
-    if (s > 8) s = 8;
-    while (s > 1 && p.num_kb / s < 2) s--;
-    if (s > 1) {
-      p.kb_per_split = ceil_div(p.num_kb, s);
-      p.splitk = ceil_div(p.num_kb, p.kb_per_split);
+  const bool split_ok = !raw_i32 && !ep.out16 && ep.n_peers == 0 && (ep.ldc == 0 || ep.ldc == N) && p.batches == 1;
+  if (split_ok && num_tiles * 2 <= ctx->sm_count) {
+    constexpr long long kFixed = 6 * 256, kReduce = 16;
+    long long best = -1;
+    int best_mt = p.MT, best_s = 1;
+    const int mt_hi = p.MT;
+    for (int cand = mt_hi; cand >= 16; cand -= 16) {
+      const int tm = ceil_div(M, cand);
+      if (cand > 16 && ceil_div(M, cand - 16) == tm) continue;  // a shorter tile gives the same row tiling
+      for (int sp = 1; sp <= 8; sp++) {
+        if (sp > 1 && (cand > kSplitMaxMT || p.num_kb / sp < 2)) break;
+        const int kb = ceil_div(p.num_kb, sp), real_s = ceil_div(p.num_kb, kb);
+        if (real_s != sp) continue;
+        const long long ctas = (long long)p.tiles_n * tm * sp;
+        const long long rounds = (ctas + ctx->sm_count - 1) / ctx->sm_count;
+        const long long cost = rounds * ((long long)kb * (128 + cand * limbs) + kFixed) + (sp > 1 ? kReduce * sp * (cand / 16) : 0);
+        if (best < 0 || cost < best) {
+          best = cost;
+          best_mt = cand;
+          best_s = sp;
+        }
+      }
     }
+    if (ctx->tc_tile_rows > 0 || ctx->tc_split_k > 0) {  // tuning overrides (options "tc_tile_rows", "tc_split_k")
+      if (ctx->tc_tile_rows > 0) best_mt = ((ctx->tc_tile_rows + 15) / 16) * 16 < mt_hi ? ((ctx->tc_tile_rows + 15) / 16) * 16 : mt_hi;
+      best_s = ctx->tc_split_k > 0 ? ctx->tc_split_k : 1;
+      if (best_mt > kSplitMaxMT) best_s = 1;
+      while (best_s > 1 && p.num_kb / best_s < 2) best_s--;
+      if (best_s > 1) best_s = ceil_div(p.num_kb, ceil_div(p.num_kb, best_s));
+    }
+    p.MT = best_mt;
+    p.tiles_m = ceil_div(M, p.MT);
+    if (best_s > 1) {
+      p.kb_per_split = ceil_div(p.num_kb, best_s);
+      p.splitk = best_s;
+    }
+    num_tiles = p.tiles_n * p.tiles_m * p.batches;
   }
-  const size_t stage_bytes = (size_t)kPTileBytes + (size_t)p.MT * limbs * kRowBytes + (KIND == 2 ? kRawTileBytes : 0);
-  const size_t tail_bytes = (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + 1024;
-  int stages = (int)((220 * 1024 - tail_bytes) / stage_bytes);
+  const size_t stage_bytes =
+      (size_t)(KIND == 4 ? 2 : 1) * kPTileBytes + (size_t)p.MT * limbs * kRowBytes + (KIND == 2 ? kRawTileBytes : 0);
+  p.w_lo_rows = KIND == 4 ? p.tiles_n * p.num_kb * 128 : 0;
+  // Results through shared-memory slabs and TMA stores: plain products only (see epilogue_tile), and only where the
+  // copy engine's alignment rules hold (16-byte row pitch and base address).
+  p.tma_out = ((KIND <= 1 || KIND == 4) && !raw_i32 && p.splitk == 1 && p.batches == 1 && ep.n_peers == 0 && (p.ldc & 3) == 0 &&
+               ((uintptr_t)out & 15) == 0 && (!ep.out16 || ((uintptr_t)ep.out16 & 127) == 0) && M >= 16)
+                  ? 1
+                  : 0;
+  p.slab_f16_off = p.skip_f32 ? 0u : (uint32_t)kEpiWarps * 4096u;
+  const size_t slab_bytes = p.tma_out ? (size_t)p.slab_f16_off + (p.out16 ? (size_t)kEpiWarps * 2048 : 0) + 128 : 0;
+  const size_t tail_bytes =
+      (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + slab_bytes + 1024;
+  int stages = (int)((227 * 1024 - tail_bytes) / stage_bytes);
   if (stages > 12) stages = 12;
   const int kb_per_cta = p.kb_per_split * ceil_div(num_tiles, p.splitk > 1 ? num_tiles : ctx->sm_count);
   if (stages > kb_per_cta) stages = kb_per_cta;
@@ -938,10 +1082,15 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
                   // engine as 16 rows of 256 bytes (as 128 rows of 32 bytes it cost the engine ~0.5 us per tile)
     FA_TRY(tc::make_tmap_bytes2d(ctx, &map_w, w_packed, 256, (uint64_t)p.tiles_n * p.num_kb * 16, 256, 16));
   else
-    FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, w_batches * p.tiles_n * p.num_kb * 128, 0, 128));
+    FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, (KIND == 4 ? 2 : 1) * w_batches * p.tiles_n * p.num_kb * 128, 0, 128));
   // activations: [limbs * num_kb] slabs of M rows of 128 bytes, boxes of MT rows (rows >= M read as zero)
   FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M,
                                (uint64_t)(p.a_shared ? 1 : p.batches) * limbs * p.num_kb, (uint32_t)p.MT));
+  CUtensorMap map_o = map_w, map_o16 = map_w;  // placeholders when unused (never dereferenced then)
+  if (p.tma_out) {
+    if (!p.skip_f32) FA_TRY(tc::make_tmap_out_f32(ctx, &map_o, (const float *)out, (uint64_t)M, (uint64_t)N, (uint64_t)p.ldc));
+    if (p.out16) FA_TRY(tc::make_tmap_out_f16_packed(ctx, &map_o16, p.out16, (uint64_t)p.o16_rows, (uint64_t)(N >> 6)));
+  }
   FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[2];
@@ -963,8 +1112,8 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     cfg.gridDim = dim3(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);  // persistent: one CTA per SM
   }
   {
-    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : (KIND == 2 ? "tc_gemm_nbits" : "tc_gemm_f16_scatter")));
-    cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, p);
+    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : (KIND == 2 ? "tc_gemm_nbits" : (KIND == 4 ? "tc_gemm_tf32x3" : "tc_gemm_f16_scatter"))));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, map_o, map_o16, p);
     if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm: %s", cudaGetErrorString(e));
   }
   FA_LAUNCH_CHECK(ctx, "tc_gemm");
@@ -986,7 +1135,7 @@ int tc::make_tmap_rows128(fa_ctx *ctx, CUtensorMap *out, const void *base, int e
   cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, rows * (cuuint64_t)kRowBytes};
   cuuint32_t box[3] = {inner, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, rank,
+  CUresult r = enc(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8), rank,
                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -1009,6 +1158,34 @@ int tc::make_tmap_bytes2d(fa_ctx *ctx, CUtensorMap *out, const void *base, uint6
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled (bytes) failed with CUresult %d", (int)r);
+  return FA_OK;
+}
+
+int tc::make_tmap_out_f32(fa_ctx *ctx, CUtensorMap *out, const float *base, uint64_t rows, uint64_t cols, uint64_t ld) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable in this driver");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {32, 16};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled (f32 result) failed with CUresult %d", (int)r);
+  return FA_OK;
+}
+
+int tc::make_tmap_out_f16_packed(fa_ctx *ctx, CUtensorMap *out, const __half *base, uint64_t rows, uint64_t chunks) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable in this driver");
+  cuuint64_t dims[3] = {64, rows, chunks};
+  cuuint64_t strides[2] = {128, rows * 128};
+  cuuint32_t box[3] = {32, 16, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half *>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fa_fail(ctx, FA_ERR_CUDA, "cuTensorMapEncodeTiled (f16 operand result) failed with CUresult %d", (int)r);
   return FA_OK;
 }
 
@@ -1066,6 +1243,33 @@ int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, 
 int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *w_packed, void *c, bool raw_i32, int M,
                   int N, int K, const TcEpilogue &ep) {
   return launch_tc<1>(ctx, w_packed, a_packed, limbs, c, raw_i32, M, N, K, ep);
+}
+
+// f32 x f32 on the tensor cores (kind::tf32, value + residue planes on both sides; see KIND 4).
+size_t fa_tc_tf32_weight_bytes(int N, int K) { return 2 * fa_tc_weight_bytes(N, K, 4); }
+size_t fa_tc_tf32_act_bytes(int M, int K) { return fa_tc_act_bytes(M, K, 4, 2); }
+int fa_pack_w_tf32(fa_ctx *ctx, const float *w_kn, int K, int N, float *out) {
+  FA_CHECK_CUDA(ctx, cudaMemsetAsync(out, 0, fa_tc_tf32_weight_bytes(N, K), ctx->stream));
+  dim3 grid(ceil_div(K, 32), ceil_div(N, 32)), block(32, 8);
+  {
+    LaunchScope ls(ctx, "pack_w_tf32");
+    k_pack_w_tf32<<<grid, block, 0, ctx->stream>>>(w_kn, K, N, fa_tc_chunks(K, 4), fa_tc_weight_bytes(N, K, 4) / 4, out);
+  }
+  FA_LAUNCH_CHECK(ctx, "pack_w_tf32");
+  return FA_OK;
+}
+int fa_prep_a_tf32(fa_ctx *ctx, const float *a, int M, int K, float *out) {
+  if (M == 0) return FA_OK;
+  const int nch = fa_tc_chunks(K, 4);
+  {
+    LaunchScope ls(ctx, "prep_a_tf32");
+    fa_launch_dep(ctx, k_prep_a_tf32, dim3(grid_for(ctx, (size_t)nch * M * 32, 256, 8)), dim3(256), 0, a, M, K, nch, out);
+  }
+  FA_LAUNCH_CHECK(ctx, "prep_a_tf32");
+  return FA_OK;
+}
+int fa_tc_gemm_tf32(fa_ctx *ctx, const float *a_planes, const float *w_planes, float *c, int M, int N, int K, const TcEpilogue &ep) {
+  return launch_tc<4>(ctx, w_planes, a_planes, 2, c, false, M, N, K, ep);
 }
 
 int fa_prep_a_f16(fa_ctx *ctx, const float *a, int M, int K, __half *out) {

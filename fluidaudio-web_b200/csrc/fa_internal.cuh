@@ -30,6 +30,10 @@ struct fa_tensor {
   // Lazily built packed f16 copy used when this tensor is the weight side of a tensor-core GEMM.
   void *bt_f16 = nullptr;
   size_t bt_bytes = 0;
+  // Lazily built value + residue f32 planes used when this f32-storage tensor is the weight side of a large product.
+  void *bt_tf32 = nullptr;
+  size_t bt_tf32_bytes = 0;
+  bool bt_stale = false;  // the tensor was written in place after a packed weight copy was made: repack on next use
   // Packed f16 shadow Ap[k/64][row][k%64] used when this tensor is the row (activation) side of a
   // tensor-core GEMM.  Written by the producing kernel (layernorm, GEMM epilogue) or on first use;
   // dropped whenever the tensor is written in place.  Storage stays opaque to callers (compute.d.ts:10-15).
@@ -113,6 +117,7 @@ struct fa_ctx {
   int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
   unsigned wait_limit = 1u << 24;  // polls before a device-side barrier wait gives up (about a second)
   int tc_withhold_chunk = -1;      // test hook, one launch: see TcParams::withhold_kb
+  int tc_tile_rows = 0, tc_split_k = 0;  // tuning overrides for sub-wave tensor-core products (0 = chosen by the cost model)
   size_t pool_cap = 0;
   // exact-size pool (the reference pools by exact byte size, buffer-pool.js:49-84)
   std::unordered_map<size_t, std::vector<void *>> pool;
@@ -352,6 +357,12 @@ int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, 
 int fa_pack_w_f16_batched(fa_ctx *ctx, const void *w_kn, int K, int N, int batch, size_t src_stride, __half *out);
 int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk,
                         int zpb, __half *out);
+size_t fa_tc_tf32_weight_bytes(int N, int K);
+size_t fa_tc_tf32_act_bytes(int M, int K);
+int fa_pack_w_tf32(fa_ctx *ctx, const float *w_kn, int K, int N, float *out);
+int fa_prep_a_tf32(fa_ctx *ctx, const float *a, int M, int K, float *out);
+int fa_tc_gemm_tf32(fa_ctx *ctx, const float *a_planes, const float *w_planes, float *c, int M, int N, int K,
+                    const TcEpilogue &ep);
 bool fa_tc_available(fa_ctx *ctx);
 // Batched attention products on the tensor cores (fa_attn_tc.cu); return FA_OK and *done=false when the
 // shape does not fit the packed layouts (the caller then uses the any-shape kernels).
@@ -378,6 +389,7 @@ int fa_shadow_ensure(fa_ctx *ctx, fa_tensor *t, const __half **out);
 // Called by in-place writers AFTER they made the f32 storage current (need_f32): from here on the f32 storage
 // is the truth again.
 static inline void fa_shadow_drop(fa_tensor *t) {
+  t->bt_stale = t->bt_f16 != nullptr || t->bt_tf32 != nullptr;
   t->a16_valid = false;
   t->hk16_valid = false;
   t->f32_lazy = false;

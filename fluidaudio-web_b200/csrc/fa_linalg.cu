@@ -51,11 +51,35 @@ bool foreign_to_recording(fa_ctx *ctx, const void *dptr) {
 // Packed f16 copy of a [K][N] weight tensor, built once per handle.
 int ensure_bt_f16(fa_ctx *ctx, fa_tensor *b) {
   if (b->view) return fa_fail(ctx, FA_ERR_INVALID, "matmul: a rowsView cannot be the weight operand of a large product");
-  if (b->bt_f16) return FA_OK;
+  if (b->bt_f16 && !b->bt_stale) return FA_OK;
   FA_NO_FIRST_USE_IN_RECORDING(ctx, b->dptr, "matmul");
-  FA_TRY(fa_block_acquire(ctx, fa_tc_weight_bytes(b->cols, b->rows, 2), &b->bt_f16, &b->bt_bytes));
+  if (b->bt_stale && b->bt_tf32) {  // both copies are out of date: drop the one not being rebuilt
+    fa_block_release(ctx, b->bt_tf32);
+    b->bt_tf32 = nullptr;
+  }
+  b->bt_stale = false;
+  if (!b->bt_f16) FA_TRY(fa_block_acquire(ctx, fa_tc_weight_bytes(b->cols, b->rows, 2), &b->bt_f16, &b->bt_bytes));
   return fa_pack_w_f16(ctx, b->dptr, b->storage, b->rows, b->cols, (__half *)b->bt_f16);
 }
+
+// Value + residue f32 planes of a [K][N] f32 weight tensor (kind::tf32 route), built once per handle.
+int ensure_bt_tf32(fa_ctx *ctx, fa_tensor *b) {
+  if (b->bt_tf32 && !b->bt_stale) return FA_OK;
+  FA_NO_FIRST_USE_IN_RECORDING(ctx, b->dptr, "matmul");
+  FA_TRY(fa_touch_f32(ctx, b));
+  if (b->bt_stale && b->bt_f16) {
+    fa_block_release(ctx, b->bt_f16);
+    b->bt_f16 = nullptr;
+  }
+  b->bt_stale = false;
+  if (!b->bt_tf32) FA_TRY(fa_block_acquire(ctx, fa_tc_tf32_weight_bytes(b->cols, b->rows), &b->bt_tf32, &b->bt_tf32_bytes));
+  return fa_pack_w_tf32(ctx, (const float *)b->dptr, b->rows, b->cols, (float *)b->bt_tf32);
+}
+
+// f32-storage B at the sizes the reference hands to its fastest f32 kernel (M, N, K >= 256, src/gpu/compute.js:426)
+// runs on the tensor cores in f32-grade arithmetic (kind::tf32 with value + residue planes); smaller or ragged
+// products stay on the any-shape CUDA-core kernel.
+bool tf32_shape_ok(fa_ctx *ctx, int M, int N, int K) { return fa_tc_available(ctx) && M >= 256 && N >= 256 && K >= 256; }
 
 // Packed int8 copy of a [K][N] int8 payload, built once per handle and (N,K).
 int ensure_nk_i8(fa_ctx *ctx, fa_bytes *wq, int N, int K) {
@@ -221,6 +245,18 @@ static int matmul_impl(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_t
         }
       }
       rc = fa_tc_gemm_f16(ctx, a16, (const __half *)b->bt_f16, (float *)c->dptr, M, N, K, ep);
+    }
+  } else if (b->storage == FA_F32 && !b->view && tf32_shape_ok(ctx, M, N, K)) {
+    Scratch sa(ctx);
+    rc = ensure_bt_tf32(ctx, b);
+    if (rc == FA_OK) rc = sa.get(fa_tc_tf32_act_bytes(M, K));
+    if (rc == FA_OK) rc = fa_prep_a_tf32(ctx, ap, M, K, (float *)sa.p);
+    if (rc == FA_OK) {
+      TcEpilogue ep;
+      ep.bias = biasp;
+      ep.add = addp;
+      ep.act = act;
+      rc = fa_tc_gemm_tf32(ctx, (const float *)sa.p, (const float *)b->bt_tf32, (float *)c->dptr, M, N, K, ep);
     }
   } else {
     rc = fa_simt_gemm(ctx, ap, b->dptr, b->storage == FA_F16 ? 1 : 0, nullptr, biasp, act, addp, (float *)c->dptr, M,

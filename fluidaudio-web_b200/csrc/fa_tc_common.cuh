@@ -66,6 +66,26 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
       "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Stores of a shared-memory tile into this GPU's global memory (bulk async group; never a multicast form).
+// Rows or columns of the box that fall outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x),
+               "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src),
+               "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until all but the newest `N` store groups of this thread have finished READING shared memory.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until every store group of this thread is complete (its global writes performed).
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -85,9 +105,15 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues it for the CTA.
-template <int KIND /*0 f16, 1 i8*/>
+template <int KIND /*0 f16, 1 i8, 2 tf32*/>
 __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  if (KIND == 0) {
+  if (KIND == 2) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if (KIND == 0) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
@@ -123,10 +149,11 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
          ((uint64_t)2 << 61);
 }
-// Instruction descriptor: dense, D format (1 f32, 2 s32), A/B formats (f16: 0, s8: 1), both K-major,
-// N>>3 at bit 17, M>>4 at bit 24.
+// Instruction descriptor: dense, D format (1 f32, 2 s32), A/B formats (kind::f16: 0 = f16; kind::i8: 1 = s8;
+// kind::tf32: 2 = tf32), both K-major, N>>3 at bit 17, M>>4 at bit 24.
 __host__ __device__ constexpr uint32_t make_idesc(int kind, int M, int N) {
-  return (kind == 0 ? ((1u << 4) | (0u << 7) | (0u << 10)) : ((2u << 4) | (1u << 7) | (1u << 10))) |
+  return (kind == 0 ? ((1u << 4) | (0u << 7) | (0u << 10))
+                    : (kind == 1 ? ((2u << 4) | (1u << 7) | (1u << 10)) : ((1u << 4) | (2u << 7) | (2u << 10)))) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
@@ -139,5 +166,9 @@ int make_tmap_rows128(fa_ctx *ctx, CUtensorMap *out, const void *base, int elem_
                       uint32_t box_rows);
 int make_tmap_bytes2d(fa_ctx *ctx, CUtensorMap *out, const void *base, uint64_t row_bytes, uint64_t rows,
                       uint32_t box_bytes, uint32_t box_rows);
+// Result tensors as the epilogue's store targets: f32 [rows][cols] with a row pitch of ld elements, boxes of
+// 16 rows x 32 columns; and a packed f16 operand Ap[cols/64][rows][64], boxes of 16 rows x 32 columns of one chunk.
+int make_tmap_out_f32(fa_ctx *ctx, CUtensorMap *out, const float *base, uint64_t rows, uint64_t cols, uint64_t ld);
+int make_tmap_out_f16_packed(fa_ctx *ctx, CUtensorMap *out, const __half *base, uint64_t rows, uint64_t chunks);
 
 }  // namespace tc

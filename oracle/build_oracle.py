@@ -2,7 +2,7 @@
 
     python oracle/build_oracle.py
 
-Compiles oracle/wasm_kernels_port.c and oracle/parakeet_decoder_port.c into oracle/liboracle.so.  -ffp-contract=off keeps
+Compiles oracle/wasm_kernels_port.c, oracle/parakeet_decoder_port.c and oracle/nemo_mel_port.c into oracle/liboracle.so.  -ffp-contract=off keeps
 every multiply and add separately rounded, as wasm32 simd128 does; -O3 changes no
 floating-point result without -ffast-math.  OpenMP (used only by the *_mt / *_kj
 entry points and conv2d, all bit-identical to their serial forms) is enabled when the
@@ -16,7 +16,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SRCS = [os.path.join(HERE, "wasm_kernels_port.c"), os.path.join(HERE, "parakeet_decoder_port.c")]
+SRCS = [os.path.join(HERE, "wasm_kernels_port.c"), os.path.join(HERE, "parakeet_decoder_port.c"),
+        os.path.join(HERE, "nemo_mel_port.c")]
 OUT = os.path.join(HERE, "liboracle.so")
 BASE = ["-O3", "-march=x86-64-v3", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-fvisibility=hidden",
         "-Wall", "-Wextra", "-shared"]

@@ -382,3 +382,41 @@ def test_hidden_layer_result_is_lazy_and_consistent(ctx, oracle):
     h = ctx.matmul(A, W1, dict(bias=B, act="silu"))
     s2 = ctx.download(ctx.scale(h, 2.0)).reshape(M, N)
     assert np.array_equal(s2, h1 * 2.0)
+
+
+# ---- f32-storage B: tensor-core route (value + residue planes on kind::tf32) -------------------------------
+
+@pytest.mark.parametrize("M,K,N,opts", [(512, 1024, 4096, {}), (256, 256, 256, dict(bias=True, act="gelu_erf")),
+                                        (300, 520, 264, dict(bias=True, act="silu", add=True)), (1024, 4096, 1024, dict(add=True))])
+def test_f32_weight_gemm_on_tensor_cores_vs_oracle(ctx, M, K, N, opts):
+    """f32 x f32 at the sizes the reference routes to its fastest f32 kernel (M, N, K >= 256,
+    src/gpu/compute.js:426; its own check of that kernel is scripts/gemm-verify-v4.mjs:22-50 at 2e-4).  The
+    gate's 1e-3 holds with orders of magnitude to spare because both operands keep ~20 bits."""
+    rng = np.random.default_rng(31)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32) if opts.get("bias") else None
+    add = rng.standard_normal((M, N)).astype(np.float32) if opts.get("add") else None
+    act = opts.get("act", "none")
+    ctx.startProfile(16)
+    got = ctx.download(ctx.matmul(ctx.upload(a, M, K), ctx.upload(b, K, N), bias=ctx.upload(bias, 1, N) if bias is not None else None,
+                                  act=act, add=ctx.upload(add, M, N) if add is not None else None)).reshape(M, N)
+    labels = {e["label"] for e in ctx.endProfile()}
+    assert "tc_gemm_tf32x3" in labels, labels  # the tensor-core route ran, not the CUDA-core kernel
+    rows = np.unique(np.concatenate([[0, M - 1], rng.integers(0, M, 48)]))
+    ora = WasmOracle(threads=True)
+    ref = ora.matmul(T(a[rows], len(rows), K), T(b, K, N), bias=T(bias, 1, N) if bias is not None else None, act=act,
+                     add=T(add[rows], len(rows), N) if add is not None else None).array()
+    assert np.abs(got[rows] - ref).max() <= 2e-4
+    assert rel_err(got[rows], ref) <= 1e-3
+
+
+def test_f32_weight_small_shapes_stay_exact_f32(ctx):
+    """300 x 64 x 300 (K below the threshold): the any-shape f32 kernel, as before."""
+    rng = np.random.default_rng(32)
+    M, K, N = 300, 64, 300
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal((K, N)).astype(np.float32)
+    got = ctx.download(ctx.matmul(ctx.upload(a, M, K), ctx.upload(b, K, N))).reshape(M, N)
+    ora = WasmOracle(threads=True)
+    assert np.abs(got - ora.matmul(T(a, M, K), T(b, K, N)).array()).max() <= 1e-4

@@ -351,8 +351,12 @@ def test_attn_fused_matches_the_op_sequence(ctx, W, H, T):
         a = ctx.download(ctx.attnFusedQKV(plain, pos, pbu, pbv, H, HD, W))
         b = ctx.download(ctx.attnFusedQKV(hinted, pos, pbu, pbv, H, HD, W))
         assert np.abs(a - b).max() <= 3e-3 * max(1.0, float(np.abs(a).max()))
-        pl = ctx.download(plain)
-        assert np.array_equal(ctx.download(hinted), pl.astype(np.float16).astype(np.float32))
+        # the operand-only result is the plain result rounded to f16; the two launches may sum K in a different
+        # order (a thin product splits K over a cluster), so allow the rounding to land on the neighbouring f16
+        pl16 = ctx.download(plain).astype(np.float16).astype(np.float32)
+        hd = ctx.download(hinted)
+        assert np.abs(hd - pl16).max() <= 2.0 ** -10 * max(1.0, float(np.abs(pl16).max()))
+        assert (hd != pl16).mean() < 0.01
 
 
 @pytest.mark.parametrize("h,Cc,W,bias", [(75, 64, 3, True), (19, 128, 2, True), (70, 64, 1, False), (8, 256, 2, True)])
