@@ -93,6 +93,10 @@ SIGNATURES = {
     "fa_conv_dw_pw_windows": [P, P, P, P, P, P, I, I, I, I, PP],
     "fa_argmax_rows": [P, P, I, PP],
     "fa_embed_rows": [P, P, P, P, I, PP],
+    "fa_log_mel_windows": [P, P, I, C.c_double, I, PP],
+    "fa_tdt_create": [P] + [P] * 13 + [PP],
+    "fa_tdt_decode_proj": [P, P, P, I, I, I, P, P, P, IP],
+    "fa_tdt_free": [P, P],
     "fa_unshard_cols": [P, P, I, PP],
     "fa_ipc_export": [P, P, P],
     "fa_ipc_open": [P, P, PP],

@@ -482,6 +482,13 @@ class CudaContext:
         arr = (C.c_void_p * len(out_ptrs))(*[C.c_void_p(int(p)) for p in out_ptrs])
         self._check(self._lib.fa_matmul_scatter(self._h, a.h, b_shard.h, self._h_of(bias), ACT[act], arr, len(out_ptrs), ldc, col0))
 
+    def logMelWindows(self, audio: Tensor, nMels: int = 128, logGuard: float = 2.0 ** -24, normalize: bool = True) -> Tensor:
+        """Optional member: the reference's host-side log-mel front end (ParakeetMel / JsPreprocessor,
+        src/engines/asr-parakeet/parakeet-mel.js, src/engines/asr-nemotron/nemotron-mel.js) for a batch of windows
+        on the device.  audio [W, N] f32 at 16 kHz -> [W, T*nMels], time-major per window, T = floor(N/160)
+        (normalize=True, Parakeet) or N/160 + 1 (normalize=False with logGuard=1e-10, Nemotron)."""
+        return self._op(self._lib.fa_log_mel_windows, audio.h, int(nMels), float(logGuard), 1 if normalize else 0)
+
     def embedRows(self, table: Tensor, pos: Tensor, idx: Tensor, n: int) -> Tensor:
         """[S, D] = table[id_s] + pos[n], ids read from column 0 of `idx` on the device (so a greedy
         decode needs no host round trip between tokens)."""

@@ -148,6 +148,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->int8_limbs = (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "gemv_ctas_per_sm")) {
+    FA_REQUIRE(ctx, value >= 1 && value <= 4, "gemv_ctas_per_sm must be 1..4");
+    ctx->gemv_ctas_per_sm = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "tc_tile_rows")) {
     FA_REQUIRE(ctx, value >= 0 && value <= 256, "tc_tile_rows must be 0 (automatic) or 16..256");
     ctx->tc_tile_rows = (int)value;

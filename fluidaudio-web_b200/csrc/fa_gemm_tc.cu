@@ -61,6 +61,7 @@ struct TcParams {
   int tiles_n, tiles_m;
   int splitk;         // > 1: cluster of `splitk` CTAs along z shares one tile, each taking kb_per_split chunks
   int kb_per_split;
+  int split_rb;       // split-K: 16-row blocks of a tile each CTA of the cluster owns, ceil(MT / 16 / splitk)
   int raw_i32;        // 1: store the limb-0 int32 accumulators instead of the float epilogue
   // batched mode (attention products): `batches` independent [M][N] problems share one launch.  Batch b
   // reads weight slab (w_batch_mod ? b % w_batch_mod : b) and activation slabs of batch b, and writes at
@@ -102,21 +103,8 @@ __device__ __forceinline__ void report_timeout(int *status, int code, int detail
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
-  uint32_t ra;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
-  uint32_t ra;
-  float4 v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra) : "memory");
-  return v;
-}
+__device__ __forceinline__ void cluster_arrive_all() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_all() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // Activation applied to 16 values at once with the selector outside the loop, so the 16 chains stay
 // independent (one warp per scheduler has no other work to hide a per-element branch behind).
@@ -155,7 +143,7 @@ template <int KIND, bool PEERS = false>
 __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_addr, int n0, int m0, int quad, int lane,
                                               int half, float *outb, int r16, int c16, uint32_t partial,
                                               const CUtensorMap *map_o, const CUtensorMap *map_o16, uint32_t slab_f32,
-                                              uint32_t slab_f16, uint32_t &slab_turn) {
+                                              uint32_t slab_f16, uint32_t &slab_turn, uint32_t cl_rank) {
   const int n = n0 + quad * 32 + lane;
   const bool n_ok = n < p.N;
   const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
@@ -227,11 +215,16 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
       }
     }
     if (p.splitk > 1) {
-      // partial[m_local][n_local]: lanes write consecutive addresses
+      // K split over a cluster: 16-row blocks of the tile are dealt to the CTAs of the cluster in turn; this CTA's
+      // partial sums of a block go straight into the OWNER's shared memory (remote stores, nothing waits on them),
+      // slot [source rank][owned block][row][column]: lanes write consecutive addresses.
+      const uint32_t blk = (uint32_t)c >> 4, owner = blk % (uint32_t)p.splitk, ob = blk / (uint32_t)p.splitk;
+      const uint32_t local = partial + ((((cl_rank * (uint32_t)p.split_rb + ob) * 16u) * 128u + (uint32_t)(quad * 32 + lane)) * 4u);
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
 #pragma unroll
       for (int j = 0; j < 16; j++)
-        asm volatile("st.shared.f32 [%0], %1;" ::"r"(partial + (uint32_t)(((c + j) * 128 + quad * 32 + lane) * 4)), "f"(v[j])
-                     : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(j * 128 * 4)), "f"(v[j]) : "memory");
       continue;
     }
 #pragma unroll
@@ -371,6 +364,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+  // K split over a cluster: a CTA's shared memory may be written by its peers only once it is known to be running.
+  // Everyone arrives here; the epilogue warps complete the barrier before their first remote store, the other
+  // warps after their role.
+  if (p.splitk > 1) cluster_arrive_all();
   fa_grid_dep_sync();  // barriers, TMEM and descriptors were set up while the previous kernel drained
 
   auto aborted = [&]() {
@@ -590,7 +587,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   } else {
     // ---- epilogue: TMEM -> registers -> global (or -> smem partial in split-K mode) -------------
     const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
-    uint32_t lt = 0, slab_turn = 0;
+    uint32_t lt = 0, slab_turn = 0, cl_rank = 0;
+    if (p.splitk > 1) {
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cl_rank));
+      cluster_wait_all();
+    }
     const uint32_t slab_f32 = slabs + (uint32_t)ew * 4096u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)ew * 2048u;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
@@ -615,7 +616,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
       epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial, &map_o, &map_o16,
-                                   slab_f32, slab_f16, slab_turn);
+                                   slab_f32, slab_f16, slab_turn, cl_rank);
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -625,10 +626,14 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     __syncwarp();
   }
 
+  if (p.splitk > 1 && !(warp >= 2 && warp < 2 + kEpiWarps)) {
+    __syncwarp();
+    cluster_wait_all();
+  }
   if (p.splitk > 1) {
-    // ---- split-K: the cluster's CTAs hold partial tiles in shared memory; each CTA sums its share of
-    // the tile over distributed shared memory in rank order (deterministic), applies the epilogue and
-    // stores. ----
+    // ---- split-K finish: after the cluster barrier every CTA holds, for the 16-row blocks it owns, one partial
+    // block from each CTA of the cluster in its OWN shared memory; it adds them in rank order (deterministic),
+    // applies the epilogue and stores.  No remote access happens after the barrier. ----
     __syncwarp();
     cluster_sync_all();
     uint32_t rank;
@@ -638,22 +643,21 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       const int n0 = tn * 128, m0 = tm * p.MT;
       const int t = threadIdx.x - 64;  // the epilogue threads, each owns groups of 4 consecutive columns
       const bool vec_ok = (p.N & 3) == 0;
-      // every CTA of the cluster finishes an interleaved share of the tile (remote reads are the cost)
       constexpr int ET = 32 * kEpiWarps;
-      for (int g = t + ET * (int)rank; g < p.MT * 32; g += ET * p.splitk) {
-        const int ml = g >> 5, nl = (g & 31) * 4, m = m0 + ml, n = n0 + nl;
-        if (m >= p.M || n >= p.N) continue;
-        // all remote reads first (independent), then the rank-ordered sum
-        float4 part[8];
-#pragma unroll
-        for (int r = 0; r < 8; r++)
-          if (r < p.splitk) part[r] = ld_dsmem_f32x4(partial + (uint32_t)((ml * 128 + nl) * 4), (uint32_t)r);
+      for (int g = t; g < p.split_rb * 16 * 32; g += ET) {
+        const int lrow = g >> 5, nl = (g & 31) * 4;         // row within this CTA's owned blocks, first column
+        const int ml = ((lrow >> 4) * p.splitk + (int)rank) * 16 + (lrow & 15);  // row within the tile
+        const int m = m0 + ml, n = n0 + nl;
+        if (ml >= p.MT || m >= p.M || n >= p.N) continue;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int r = 0; r < 8; r++)
-          if (r < p.splitk) {
-            acc[0] += part[r].x; acc[1] += part[r].y; acc[2] += part[r].z; acc[3] += part[r].w;
-          }
+        for (int r = 0; r < p.splitk; r++) {
+          float4 v;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                       : "r"(partial + (uint32_t)((((r * p.split_rb * 16) + lrow) * 128 + nl) * 4))
+                       : "memory");
+          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        }
         const float rs = p.rowscale ? p.rowscale[m] : 1.0f;
         float o[4];
 #pragma unroll
@@ -674,7 +678,6 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       }
     }
     __syncwarp();
-    cluster_sync_all();  // every CTA keeps its shared memory alive until its peers have read it
   }
 
   // ---- teardown --------------------------------------------------------------------------------
@@ -1005,7 +1008,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
   const bool split_ok = !raw_i32 && !ep.out16 && ep.n_peers == 0 && (ep.ldc == 0 || ep.ldc == N) && p.batches == 1;
-  if (split_ok && num_tiles * 2 <= ctx->sm_count) {
+  if (split_ok && num_tiles <= ctx->sm_count) {
     constexpr long long kFixed = 6 * 256, kReduce = 16;
     long long best = -1;
     int best_mt = p.MT, best_s = 1;
@@ -1013,7 +1016,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     for (int cand = mt_hi; cand >= 16; cand -= 16) {
       const int tm = ceil_div(M, cand);
       if (cand > 16 && ceil_div(M, cand - 16) == tm) continue;  // a shorter tile gives the same row tiling
-      for (int sp = 1; sp <= 8; sp++) {
+      for (int sp = 1; sp <= 8; sp *= 2) {  // (clusters of 3, 5, 6, 7 CTAs place badly on the GPCs: measured 2x slower)
         if (sp > 1 && (cand > kSplitMaxMT || p.num_kb / sp < 2)) break;
         const int kb = ceil_div(p.num_kb, sp), real_s = ceil_div(p.num_kb, kb);
         if (real_s != sp) continue;
@@ -1047,6 +1050,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.w_lo_rows = KIND == 4 ? p.tiles_n * p.num_kb * 128 : 0;
   // Results through shared-memory slabs and TMA stores: plain products only (see epilogue_tile), and only where the
   // copy engine's alignment rules hold (16-byte row pitch and base address).
+  p.split_rb = p.splitk > 1 ? ceil_div(ceil_div(p.MT, 16), p.splitk) : 0;
   p.tma_out = ((KIND <= 1 || KIND == 4) && !raw_i32 && p.splitk == 1 && p.batches == 1 && ep.n_peers == 0 && (p.ldc & 3) == 0 &&
                ((uintptr_t)out & 15) == 0 && (!ep.out16 || ((uintptr_t)ep.out16 & 127) == 0) && M >= 16)
                   ? 1
@@ -1054,7 +1058,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.slab_f16_off = p.skip_f32 ? 0u : (uint32_t)kEpiWarps * 4096u;
   const size_t slab_bytes = p.tma_out ? (size_t)p.slab_f16_off + (p.out16 ? (size_t)kEpiWarps * 2048 : 0) + 128 : 0;
   const size_t tail_bytes =
-      (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.MT * 128 * 4 : 0) + slab_bytes + 1024;
+      (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.splitk * p.split_rb * 16 * 128 * 4 : 0) + slab_bytes + 1024;
   int stages = (int)((227 * 1024 - tail_bytes) / stage_bytes);
   if (stages > 12) stages = 12;
   const int kb_per_cta = p.kb_per_split * ceil_div(num_tiles, p.splitk > 1 ? num_tiles : ctx->sm_count);

@@ -72,17 +72,21 @@ __device__ __forceinline__ void nbits_block(const uint4 (&wv)[R], const float (&
 }
 
 // The kernel is one pass: a warp's first (for the benchmark shapes: only) group of R weight rows is requested
-// from HBM BEFORE the activation digits are made, so the stream over the weights - the whole cost of the product -
-// runs under the prologue instead of after it (measured before the change: ~4 us of a 5.5 us launch were prologue
-// and ramp with no weight byte in flight, against 1.6 us of streaming).  PRE blocks per lane are requested early
-// (64 blocks per row at K = 2048 = 2 per lane); longer rows load the rest in the loop.  The activation row is read
-// from global memory once: each thread keeps its KR elements per row in registers between the maximum and the
-// quantisation (K <= 256 * KR; longer rows re-read).
+// from HBM BEFORE the activation digits are made - before the kernel even waits for its predecessor in the stream:
+// the packed weights of a PackedBytes handle are only ever written by an upload, never by a kernel, so reading them
+// early is safe, while scales, zero-points and activations (tensors a kernel may have produced) are read after the
+// wait.  The stream over the weights - the whole cost of the product - thus runs under the predecessor's tail and
+// the prologue instead of after them (measured before the change: ~4 us of a 5.5 us launch had no weight byte in
+// flight, against 1.6 us of streaming).  PRE blocks per lane are requested early (64 blocks per row at K = 2048 =
+// 2 per lane); longer rows load the rest in the loop.
+// Prologue: a thread owns 8 consecutive k of every row (256 threads x 8 = 2048 per sweep), which is exactly one
+// 32-bit word of the even-k digit plane and one of the odd-k plane, so digits go to shared memory as whole words and
+// the per-block digit sums are two shuffles; for K <= 2048 the activations are read from global memory once.
 template <int M, int R>
 __global__ void __launch_bounds__(kThreads, 2) k_gemv_nbits(const float *__restrict__ a, const uint8_t *__restrict__ bq,
-                                                         const float *__restrict__ scales, const uint8_t *__restrict__ zp,
-                                                         float *__restrict__ y, int N, int K, int nblk, int zpb) {
-  constexpr int PRE = 2, KR = 8;
+                                                            const float *__restrict__ scales, const uint8_t *__restrict__ zp,
+                                                            float *__restrict__ y, int N, int K, int nblk, int zpb) {
+  constexpr int PRE = 2, SWEEP = kThreads * 8;
   extern __shared__ __align__(16) unsigned char smem[];
   int8_t *dig = (int8_t *)smem;                     // [M][2] planes of K bytes: even-k words of every block (16 B
                                                     // each, so 8 lanes read 128 consecutive bytes), then odd-k words
@@ -91,10 +95,20 @@ __global__ void __launch_bounds__(kThreads, 2) k_gemv_nbits(const float *__restr
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint4 *bq4 = (const uint4 *)bq;
   const int n_first = (blockIdx.x * 8 + warp) * R, n_stride = gridDim.x * 8 * R;
-  fa_grid_dep_sync();
 
-  // ---- early requests: the first group's weights, scales and zero-points -------------------------------------
+  // ---- early requests: the first group's weights --------------------------------------------------------------
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   uint4 pw[PRE][R];
+#pragma unroll
+  for (int i = 0; i < PRE; i++) {
+    const int b = lane + 32 * i;
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int n = n_first + r < N ? n_first + r : N - 1;
+      pw[i][r] = (b < nblk && n_first < N) ? __ldcs(bq4 + (size_t)n * nblk + b) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   float psc[PRE][R];
   unsigned pzb[PRE][R];
 #pragma unroll
@@ -103,40 +117,26 @@ __global__ void __launch_bounds__(kThreads, 2) k_gemv_nbits(const float *__restr
 #pragma unroll
     for (int r = 0; r < R; r++) {
       const int n = n_first + r < N ? n_first + r : N - 1;
-      if (b < nblk && n_first < N) {
-        pw[i][r] = __ldcs(bq4 + (size_t)n * nblk + b);
-        psc[i][r] = __ldg(scales + (size_t)n * nblk + b);
-        pzb[i][r] = __ldg(zp + (size_t)n * zpb + (b >> 1));
-      } else {
-        pw[i][r] = make_uint4(0u, 0u, 0u, 0u);
-        psc[i][r] = 0.f;
-        pzb[i][r] = 0u;
-      }
+      const bool ok = b < nblk && n_first < N;
+      psc[i][r] = ok ? __ldg(scales + (size_t)n * nblk + b) : 0.f;
+      pzb[i][r] = ok ? (unsigned)__ldg(zp + (size_t)n * zpb + (b >> 1)) : 0u;
     }
   }
 
-  // ---- activation digits, all M rows at once: row maxima, then q1 = rint(a/s), q2 = rint((a/s - q1) * 128) with
-  // s = max/127, stored in the order the nibbles unpack to -------------------------------------------------------
-  const bool in_regs = M <= 2 && K <= kThreads * KR;  // (3 and 4 rows: the registers are needed for the weights)
-  float av[M <= 2 ? M : 1][KR];
+  // ---- activation digits: q1 = rint(a/s), q2 = rint((a/s - q1) * 128) with s = max|row| / 127 --------------------
+  const bool one_sweep = K <= SWEEP;
+  float av[M][8];
   float mx[M];
 #pragma unroll
   for (int m = 0; m < M; m++) mx[m] = 0.f;
-  if (in_regs) {
+  for (int k0 = tid * 8; k0 < K; k0 += SWEEP) {
 #pragma unroll
-    for (int i = 0; i < KR; i++) {
-      const int k = tid + i * kThreads;
+    for (int m = 0; m < M; m++) {
+      const float4 x0 = __ldg((const float4 *)(a + (size_t)m * K + k0)), x1 = __ldg((const float4 *)(a + (size_t)m * K + k0 + 4));
+      av[m][0] = x0.x, av[m][1] = x0.y, av[m][2] = x0.z, av[m][3] = x0.w;
+      av[m][4] = x1.x, av[m][5] = x1.y, av[m][6] = x1.z, av[m][7] = x1.w;
 #pragma unroll
-      for (int m = 0; m < M; m++) {
-        av[M <= 2 ? m : 0][i] = k < K ? __ldg(a + (size_t)m * K + k) : 0.f;
-        mx[m] = fmaxf(mx[m], fabsf(av[M <= 2 ? m : 0][i]));
-      }
-    }
-  } else {
-#pragma unroll 4
-    for (int k = tid; k < K; k += kThreads) {
-#pragma unroll
-      for (int m = 0; m < M; m++) mx[m] = fmaxf(mx[m], fabsf(a[(size_t)m * K + k]));
+      for (int i = 0; i < 8; i++) mx[m] = fmaxf(mx[m], fabsf(av[m][i]));
     }
   }
 #pragma unroll
@@ -154,40 +154,44 @@ __global__ void __launch_bounds__(kThreads, 2) k_gemv_nbits(const float *__restr
     rs[m] = t > 0.f ? t / 127.0f : 1.0f;
     inv[m] = 1.0f / rs[m];
   }
-  auto put = [&](int k, int m, float x) {
-    const int b = k >> 5, j = k & 31;
-    const int off = (j & 1) * (K >> 1) + b * 16 + (j >> 3) * 4 + ((j & 7) >> 1);
-    const float t = x * inv[m];
-    const float q1 = rintf(t);
-    dig[(size_t)(m * 2 + 0) * K + off] = (int8_t)q1;
-    dig[(size_t)(m * 2 + 1) * K + off] = (int8_t)rintf((t - q1) * 128.0f);
-  };
-  if (in_regs) {
+  for (int k0 = tid * 8; k0 < ((K + SWEEP - 1) / SWEEP) * SWEEP; k0 += SWEEP) {  // whole warps stay together for the shuffles
+    const bool in = k0 < K;
+    const int b = k0 >> 5, wi = (k0 & 31) >> 3;
 #pragma unroll
-    for (int i = 0; i < KR; i++) {
-      const int k = tid + i * kThreads;
-      if (k < K) {
+    for (int m = 0; m < M; m++) {
+      if (!one_sweep && in) {
+        const float4 x0 = __ldg((const float4 *)(a + (size_t)m * K + k0)), x1 = __ldg((const float4 *)(a + (size_t)m * K + k0 + 4));
+        av[m][0] = x0.x, av[m][1] = x0.y, av[m][2] = x0.z, av[m][3] = x0.w;
+        av[m][4] = x1.x, av[m][5] = x1.y, av[m][6] = x1.z, av[m][7] = x1.w;
+      }
+      int q1[8], q2[8], s1 = 0, s2 = 0;
 #pragma unroll
-        for (int m = 0; m < M; m++) put(k, m, av[M <= 2 ? m : 0][i]);
+      for (int i = 0; i < 8; i++) {
+        const float t = in ? av[m][i] * inv[m] : 0.f;
+        const float f1 = rintf(t);
+        q1[i] = (int)f1;
+        q2[i] = (int)rintf((t - f1) * 128.0f);
+        s1 += q1[i];
+        s2 += q2[i];
+      }
+      // digit words: bytes = k 0,2,4,6 (even plane) and 1,3,5,7 (odd plane) of this thread's 8
+      auto pack = [](int b0, int b1, int b2, int b3) {
+        return (unsigned)(b0 & 0xFF) | ((unsigned)(b1 & 0xFF) << 8) | ((unsigned)(b2 & 0xFF) << 16) | ((unsigned)(b3 & 0xFF) << 24);
+      };
+      if (in) {
+        *(unsigned *)(dig + (size_t)(m * 2 + 0) * K + b * 16 + wi * 4) = pack(q1[0], q1[2], q1[4], q1[6]);
+        *(unsigned *)(dig + (size_t)(m * 2 + 0) * K + (K >> 1) + b * 16 + wi * 4) = pack(q1[1], q1[3], q1[5], q1[7]);
+        *(unsigned *)(dig + (size_t)(m * 2 + 1) * K + b * 16 + wi * 4) = pack(q2[0], q2[2], q2[4], q2[6]);
+        *(unsigned *)(dig + (size_t)(m * 2 + 1) * K + (K >> 1) + b * 16 + wi * 4) = pack(q2[1], q2[3], q2[5], q2[7]);
+      }
+      // the 4 lanes of a 32-weight block
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 1), s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, 1), s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+      if (in && (lane & 3) == 0) {
+        SA[(m * 2 + 0) * nblk + b] = s1;
+        SA[(m * 2 + 1) * nblk + b] = s2;
       }
     }
-  } else {
-#pragma unroll 4
-    for (int k = tid; k < K; k += kThreads) {
-#pragma unroll
-      for (int m = 0; m < M; m++) put(k, m, a[(size_t)m * K + k]);
-    }
-  }
-  __syncthreads();
-  for (int idx = tid; idx < M * 2 * nblk; idx += kThreads) {
-    const int p = idx / nblk, b = idx - p * nblk;
-    const int4 w0 = *(const int4 *)(dig + (size_t)p * K + b * 16);
-    const int4 w1 = *(const int4 *)(dig + (size_t)p * K + (K >> 1) + b * 16);
-    int s = __dp4a(w0.x, 0x01010101, 0);
-    s = __dp4a(w0.y, 0x01010101, s), s = __dp4a(w0.z, 0x01010101, s), s = __dp4a(w0.w, 0x01010101, s);
-    s = __dp4a(w1.x, 0x01010101, s), s = __dp4a(w1.y, 0x01010101, s);
-    s = __dp4a(w1.z, 0x01010101, s), s = __dp4a(w1.w, 0x01010101, s);
-    SA[idx] = s;
   }
   __syncthreads();
 
@@ -416,7 +420,7 @@ int launch_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *sc
   int per_sm = 0;
   FA_CHECK_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem));
   if (per_sm < 1) per_sm = 1;
-  if (per_sm > 4) per_sm = 4;
+  if (per_sm > ctx->gemv_ctas_per_sm) per_sm = ctx->gemv_ctas_per_sm;
   int grid = ceil_div(N, 8 * R);
   if (grid > ctx->sm_count * per_sm) grid = ctx->sm_count * per_sm;
   {

@@ -114,6 +114,7 @@ struct fa_ctx {
   int pdl = 1;             // programmatic dependent launch between the library's kernels (see fa_launch_dep)
   int nbits_fused = 0;     // 1: int4 products on the tensor cores unpack nibbles in shared memory (0: f16 copy, faster today)
   int gemv_rows = 4;       // products with at most this many rows run on the CUDA-core GEMV kernels (0 = never)
+  int gemv_ctas_per_sm = 2;  // resident CTAs per SM the int4 GEMV sizes its grid for
   int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
   unsigned wait_limit = 1u << 24;  // polls before a device-side barrier wait gives up (about a second)
   int tc_withhold_chunk = -1;      // test hook, one launch: see TcParams::withhold_kb
@@ -139,6 +140,8 @@ struct fa_ctx {
   bool profiling = false;
   int profile_cap = 0;
   std::vector<ProfileRec> prof;
+  // log-mel front end: device tables (filterbank, window, twiddles) per mel count, built on first use
+  std::unordered_map<int, void *> mel_tables;
   // device-side status word written by kernels whose bounded waits ran out
   int *dev_status = nullptr;
   int *gemv_tickets = nullptr;  // zeroed arrival counters of the split-K GEMV (self-resetting)

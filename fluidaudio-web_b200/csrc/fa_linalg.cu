@@ -77,9 +77,13 @@ int ensure_bt_tf32(fa_ctx *ctx, fa_tensor *b) {
 }
 
 // f32-storage B at the sizes the reference hands to its fastest f32 kernel (M, N, K >= 256, src/gpu/compute.js:426)
-// runs on the tensor cores in f32-grade arithmetic (kind::tf32 with value + residue planes); smaller or ragged
-// products stay on the any-shape CUDA-core kernel.
-bool tf32_shape_ok(fa_ctx *ctx, int M, int N, int K) { return fa_tc_available(ctx) && M >= 256 && N >= 256 && K >= 256; }
+// runs on the tensor cores in f32-grade arithmetic (kind::tf32 with value + residue planes), and so do products
+// with fewer rows against a weight matrix of that size when there is enough work to pay for packing the row operand
+// (the lock-step LSTM and joint products of the batched TDT decoder); smaller or ragged products stay on the
+// any-shape CUDA-core kernel.
+bool tf32_shape_ok(fa_ctx *ctx, int M, int N, int K) {
+  return fa_tc_available(ctx) && N >= 256 && K >= 256 && (M >= 256 || (M >= 8 && (long long)M * N * K >= kTcMinMacs));
+}
 
 // Packed int8 copy of a [K][N] int8 payload, built once per handle and (N,K).
 int ensure_nk_i8(fa_ctx *ctx, fa_bytes *wq, int N, int K) {

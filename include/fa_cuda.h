@@ -74,7 +74,10 @@ const char *fa_last_error(fa_ctx *ctx);
  * its f32 storage is filled from that, f16-rounded, the first time anything else reads it; the same holds for
  * the results of layernormOperand, gluDwConvTimeMajor and attnFused), "attn_one_kernel" (0/1, default 1:
  * attnFused runs as one kernel per call when head width is 128 and T <= 192; 0 = the batched-GEMM form),
- * "wait_limit" (4096..2^28, default 2^24, about a second: polls after which a device-side barrier wait gives
+ * "tc_tile_rows" / "tc_split_k" (0 = automatic, the default; otherwise rows per tile and CTAs per K-split cluster
+ * of tensor-core products with less than one wave of tiles) and "gemv_ctas_per_sm" (1..4, default 2: resident
+ * thread blocks per SM the int4 GEMV sizes its grid for) are tuning overrides of choices the library makes by
+ * shape, "wait_limit" (4096..2^28, default 2^24, about a second: polls after which a device-side barrier wait gives
  * up; the kernel then records a status word, unwinds and returns, and the next fa_sync fails with
  * FA_ERR_TIMEOUT while the context stays usable), "tc_test_withhold_chunk" (-1 = off; k >= 0: test hook for that
  * path - in the NEXT tensor-core product only, one thread block never loads K chunk k of its first tile, so
@@ -298,6 +301,37 @@ int fa_matmul_scatter(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b_shard, const
  * the next fa_sync fail with FA_ERR_INVALID. */
 int fa_embed_rows(fa_ctx *ctx, const fa_tensor *table, const fa_tensor *pos, const fa_tensor *idx, int n,
                   fa_tensor **out);
+
+/* ---- callers either side of the path ------------------------------------------ */
+/* Optional member logMelWindows.  The reference computes log-mel features on the host, one window per worker
+ * thread: ParakeetMel.process (src/engines/asr-parakeet/parakeet-mel.js:16-21) = JsPreprocessor.computeRawMel +
+ * normalizeFeatures (src/engines/asr-nemotron/nemotron-mel.js:451-573, 586-620).  Here: audio [W, N] f32, W windows
+ * of N samples at 16 kHz -> [W, T * n_mels], window b in row b, TIME-major (frame t at columns [t*n_mels,
+ * (t+1)*n_mels)), which is the image the encoder's subsampling front end reads.  Pipeline and arithmetic types as in
+ * the reference: pre-emphasis 0.97, 512-point frames every 160 samples under a Hann(400) window, FFT in doubles,
+ * power as f32, slaney filterbank, log(mel + log_guard).  normalize = 1: per-feature mean / variance normalisation
+ * over T = floor(N/160) frames (Parakeet, log_guard 2^-24); normalize = 0: raw log-mel over T = N/160 + 1 frames
+ * (Nemotron, log_guard 1e-10). */
+int fa_log_mel_windows(fa_ctx *ctx, const fa_tensor *audio, int n_mels, double log_guard, int normalize, fa_tensor **out);
+
+/* Batched greedy TDT decoding: the prediction network + joint of rust/parakeet-decoder/src/lib.rs (set_weights :99-110,
+ * set_out_q :93-96, decode_proj :288-319; JS host src/engines/asr-parakeet/raw-decoder-wasm.js:12-70; the reference's
+ * own GPU form is src/engines/asr-parakeet/gpu-decoder.js) for W independent windows in lock-step.
+ * fa_tdt_create takes HOST pointers in the reference manifest's shapes: embed [8193,640], lNw / lNr [2560,640]
+ * (ONNX iofc gate order), lNb [5120], pred_w [640,640], pred_b [640], out_b [8198], and the joint's out matrix either
+ * as int8 rows + per-row scales (out_q [640,8198], out_scale [640]; the reference's default, quantised by its loader)
+ * or as f32 out_w [640,8198] (pass NULL for the form not used).
+ * fa_tdt_decode_proj: proj [W*T, 640] = pre-projected encoder frames (projection bias included), window w in rows
+ * [w*T, (w+1)*T).  Writes, per window, counts[w] token ids and their emission frames into ids / frames at offset
+ * w*cap (cap >= 10*T holds the worst case, as the reference sizes its buffers); rounds_out (may be NULL) receives the
+ * number of lock-step rounds run.  Blocks until the results are on the host. */
+typedef struct fa_tdt fa_tdt;
+int fa_tdt_create(fa_ctx *ctx, const float *embed, const float *l0w, const float *l0r, const float *l0b, const float *l1w,
+                  const float *l1r, const float *l1b, const float *pred_w, const float *pred_b, const float *out_w,
+                  const float *out_b, const int8_t *out_q, const float *out_scale, fa_tdt **out);
+int fa_tdt_decode_proj(fa_ctx *ctx, fa_tdt *dec, const fa_tensor *proj, int W, int T, int cap, int32_t *ids_host,
+                       int32_t *frames_host, int32_t *counts_host, int *rounds_out);
+int fa_tdt_free(fa_ctx *ctx, fa_tdt *dec);
 
 /* ---- profiling (compute.d.ts:250-251; scheduler.js:139-180) ----------------- */
 typedef struct fa_profile_entry {

@@ -1,0 +1,61 @@
+"""Batched TDT decoding on the device against the C restatement of rust/parakeet-decoder (itself pinned bit for bit
+to the shipped parakeet-decoder.wasm): token ids and emission frames must be identical per window.  The reference's
+own gate for its GPU decoder is the same one - token identity against wasmDecodeProj per window
+(src/engines/asr-parakeet/gpu-decoder.js:7-8, scripts/gpu-decoder-check.mjs)."""
+import numpy as np
+import pytest
+
+from oracle.tdt_oracle import TdtOracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _frames(W, T, seed):
+    return np.random.default_rng(seed).standard_normal((W, T, 640)).astype(np.float32)
+
+
+@pytest.mark.parametrize("int8", [True, False])
+@pytest.mark.parametrize("W,T", [(4, 24), (32, 188)])
+def test_tokens_and_frames_identical_to_oracle(ctx, pkg, W, T, int8):
+    from fluidaudio_web_b200.engines import tdt_decoder as td
+
+    if not int8 and W > 4:
+        pytest.skip("the f32 out-matrix variant is covered at the small size")
+    w = td.synth_tdt_weights(5)
+    proj = _frames(W, T, seed=W * 100 + T)
+    ora = TdtOracle(w, int8=int8, threads=8)
+    want = ora.decode_proj_batch(proj, W, T)
+    dec = td.TdtDecoder(ctx, w, int8=int8)
+    try:
+        got = dec.decode_proj(ctx.upload(proj.reshape(W * T, 640), W * T, 640), W, T)
+    finally:
+        dec.free()
+    emitted = 0
+    for wi in range(W):
+        assert got[wi][0].tolist() == want[wi][0].tolist(), f"window {wi}: token ids differ"
+        assert got[wi][1].tolist() == want[wi][1].tolist(), f"window {wi}: emission frames differ"
+        emitted += len(want[wi][0])
+    assert emitted >= W  # the case exercises emission, commit and the prediction network
+    assert dec.rounds >= T // 4
+
+
+def test_projection_then_decode_from_encoder_frames(ctx, pkg):
+    """frames [W*T, 1024] -> the joint's projection on the device (f16 weights, as the encoder's other products) ->
+    decode; the oracle gets the device's projected frames, so the comparison isolates the decoder."""
+    from fluidaudio_web_b200.engines import tdt_decoder as td
+
+    W, T = 3, 40
+    w = td.synth_tdt_weights(5)
+    frames = np.random.default_rng(8).standard_normal((W * T, 1024)).astype(np.float32)
+    dec = td.TdtDecoder(ctx, w)
+    try:
+        proj = dec.project(ctx.upload(frames, W * T, 1024))
+        proj_host = ctx.download(proj).reshape(W, T, 640)
+        ref = (frames @ w["encW"].astype(np.float16).astype(np.float32) + w["encB"]).reshape(W, T, 640)
+        assert np.abs(proj_host - ref).max() <= 2e-2
+        got = dec.decode_proj(proj, W, T)
+    finally:
+        dec.free()
+    want = TdtOracle(w, int8=True, threads=4).decode_proj_batch(proj_host, W, T)
+    for wi in range(W):
+        assert got[wi][0].tolist() == want[wi][0].tolist() and got[wi][1].tolist() == want[wi][1].tolist()
