@@ -419,10 +419,21 @@ class Encoder:
     dtype = "f16 weights x f16 activations, f32 accumulate"
     nsets = 1
 
+    weights_mode = "int8"  # "int8": the artifact's int8 matrices stay int8 in HBM; "f16": dequantised at load (f16 storage)
+
     def __init__(self, quick=False):
         self.W = 4 if quick else 32
         self.layers = 4 if quick else 24
         self.window_s = 15.0
+
+    def _load(self, ctx):
+        """The encoder from the int8 artifact (blob + manifest, the reference's shipping format)."""
+        from fluidaudio_web_b200.engines import blob
+
+        if not hasattr(self, "_artifact"):
+            self._artifact = blob.write_int8_blob(self._weights)
+        data, man = self._artifact
+        return self.fc.load_encoder_blob(ctx, data, man, int8_resident=self.weights_mode == "int8")
 
     def setup(self, ctx):
         import __graft_entry__ as ge
@@ -432,7 +443,10 @@ class Encoder:
 
         self.fc = fastconformer
         cfg = dict(synth.PARAKEET_06B, layers=self.layers)
-        self.enc = fastconformer.load_encoder(ctx, synth.encoder_weights(cfg, seed=3))
+        self._weights = synth.encoder_weights(cfg, seed=3)
+        self.enc = self._load(ctx)
+        self.dtype = ("int8 weights (resident, widened to f16 in shared memory) x f16 activations, f32 accumulate"
+                      if self.weights_mode == "int8" else "f16 weights x f16 activations, f32 accumulate")
         audio = synth.synth_audio(4, seed=3)  # 4 distinct windows, cycled to fill the batch
         base = [fastconformer.mel_time_major(synth.log_mel(a, 128).reshape(-1), 128) for a in audio]
         self.mel_len = base[0].size
@@ -467,8 +481,7 @@ class Encoder:
             from fluidaudio_web_b200.engines import synth
 
             ctx2 = ge.load_package().CudaContext(ctx.device)
-            cfg = dict(synth.PARAKEET_06B, layers=self.layers)
-            enc2 = self.fc.load_encoder(ctx2, synth.encoder_weights(cfg, seed=3))
+            enc2 = self._load(ctx2)
             self.e2e_batch = self.fc.PipelinedEncoder([ctx, ctx2], [self.enc, enc2], lambda s: self.host_mels, self.mel_len)
         return self.e2e_batch.submit()
 
@@ -487,10 +500,10 @@ class Encoder:
         return per_frame_layer * self.layers * T * self.W + 2 * 4096 * D * T * self.W
 
     def roofline(self, prof, peaks):
-        ent = [e for e in prof if e["label"] == "tc_gemm_f16"]
+        ent = [e for e in prof if e["label"] in ("tc_gemm_f16", "tc_gemm_i8w_f16a")]
         if not ent:
             return None
-        e = ent[0]
+        e = max(ent, key=lambda x: x["ms"])
         ach = self.gemm_flops_per_step() / (e["ms"] * 1e-3) / 1e12  # prof covers `steps` steps; caller scales
         return {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": None, "traffic": None, "kernel": "tc_gemm_f16", "launches": e["count"],
@@ -515,7 +528,7 @@ class Encoder:
         def body():
             h = ctx.pushArena()
             for a, b in seq:
-                ctx.matmul(a, b)
+                self.fc.mm(ctx, a, b)
             ctx.popArena(h)
 
         body()
@@ -532,7 +545,8 @@ class Encoder:
                 "(a smaller case than the M=%d products timed here): 16.9 MB read = the two f16 operands once, 9.4 MB "
                 "written (the rest of the 67 MB f32 result was still in the 126 MB L2 at kernel end); algorithmic bytes "
                 "of that launch 84 MB" % M,
-                "kernel": "k_tc_gemm<f16> (label tc_gemm_f16)", "launches_timed": len(seq) * reps,
+                "kernel": ("k_tc_gemm<int8 weights, f16 activations> (label tc_gemm_i8w_f16a)" if self.weights_mode == "int8"
+                           else "k_tc_gemm<f16> (label tc_gemm_f16)"), "launches_timed": len(seq) * reps,
                 "avg_launch_us": round(ms * 1e3 / (len(seq) * reps), 2),
                 "what": "the %d weight products of one conformer block at M=%d, back to back (recorded batch)" % (len(seq), M),
                 "peak_source": peaks["source"] + " (burst bf16: kernel timed alone)"}
@@ -957,6 +971,8 @@ def run_cuda(args):
     torch.cuda.set_device(local_rank)
     stream = torch.cuda.ExternalStream(ctx.stream(), device=local_rank)
     wl = WORKLOADS[args.workload](quick=args.quick)
+    if isinstance(wl, Encoder):
+        wl.weights_mode = args.encoder_weights
     wl.setup(ctx)
     ctx.sync()
 
@@ -1090,6 +1106,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="smaller rotating set (for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape roofline records of the GEMM / GEMV shapes")
+    ap.add_argument("--encoder-weights", default="int8", choices=["int8", "f16"],
+                    help="encoder workload: keep the artifact's int8 matrices int8 in HBM (default) or dequantise them to f16 at load")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

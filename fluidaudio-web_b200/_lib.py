@@ -60,6 +60,7 @@ SIGNATURES = {
     "fa_matmul": [P, P, P, P, I, P, PP],
     "fa_matmul_operand": [P, P, P, P, I, PP],
     "fa_matmul_int8": [P, P, P, P, I, I, P, I, PP],
+    "fa_matmul_int8_operand": [P, P, P, P, I, I, P, I, P, I, PP],
     "fa_matmul_nbits": [P, P, P, P, P, I, I, PP],
     "fa_int8_gemm_i32": [P, P, I, P, I, I, P],
     "fa_matmul_int8_static": [P, P, P, P, P, I, P, I, I, I],

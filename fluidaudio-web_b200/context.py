@@ -262,6 +262,17 @@ class CudaContext:
             bias, act = opts.get("bias", bias), opts.get("act", act)
         return self._op(self._lib.fa_matmul_int8, a.h, wq.h, scale.h, N, K, self._h_of(bias), ACT[act])
 
+    def matmulInt8Operand(self, a: Tensor, wq: PackedBytes, scale: Tensor, N: int, K: int, opts: Optional[dict] = None, *,
+                          bias=None, act="none", add=None, operandOnly=False) -> Tensor:
+        """Optional member: matmulInt8 with the weights kept int8 on the device and widened to f16 inside the
+        tensor-core kernel; activations rounded to f16 as on matmul's f16-B route; takes a residual `add` and the
+        operandOnly hint like matmul."""
+        if opts:
+            bias, act, add = opts.get("bias", bias), opts.get("act", act), opts.get("add", add)
+            operandOnly = opts.get("operandOnly", operandOnly)
+        return self._op(self._lib.fa_matmul_int8_operand, a.h, wq.h, scale.h, N, K, self._h_of(bias), ACT[act],
+                        self._h_of(add), 1 if operandOnly else 0)
+
     def matmulNBits(self, a: Tensor, bq: PackedBytes, scales: Tensor, zp: PackedBytes, N: int, blockSize: int = 32) -> Tensor:
         return self._op(self._lib.fa_matmul_nbits, a.h, bq.h, scales.h, zp.h, N, blockSize)
 

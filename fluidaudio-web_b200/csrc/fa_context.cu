@@ -453,6 +453,7 @@ extern "C" int fa_free_bytes(fa_ctx *ctx, fa_bytes *b) {
   if (!b) return FA_OK;
   FA_REQUIRE(ctx, fa_valid_bytes(ctx, b), "freeBytes: unknown or already freed handle");
   if (b->nk_i8) fa_block_release(ctx, b->nk_i8);
+  if (b->nk_i8w) fa_block_release(ctx, b->nk_i8w);
   if (b->nk_f16) fa_block_release(ctx, b->nk_f16);
   if (b->nb_side) fa_block_release(ctx, b->nb_side);
   fa_block_release(ctx, b->dptr);

@@ -48,6 +48,14 @@ constexpr int kPTileBytes = 128 * kRowBytes;   // weights tile: 128 rows
 constexpr int kDeqWarps = 8;
 constexpr int kThreadsNbits = 32 * (2 + kEpiWarps + 2 * kDeqWarps - 2);
 constexpr int kRawTileBytes = 128 * 32;        // int4 variant: 128 rows x 64 nibbles of one K chunk, as uploaded
+// int8-weight variant with f16 activations (KIND 5): 128 rows x 64 int8 of one K chunk; two groups of four warps (the
+// warp ids of the int4 variant's unpack warps) take alternate chunks and turn them into the f16 weights tile
+constexpr int kRaw8TileBytes = 128 * 64;
+constexpr int kThreadsI8W = kThreadsNbits;
+template <int KIND>
+__host__ __device__ constexpr int tc_threads() { return KIND == 2 ? kThreadsNbits : (KIND == 5 ? kThreadsI8W : kThreads); }
+template <int KIND>
+__host__ __device__ constexpr int tc_raw_bytes() { return KIND == 2 ? kRawTileBytes : 0; }  // (KIND 5 lands its raw tile inside the weights tile)
 constexpr int kSplitMaxMT = 128;               // split-K mode keeps a [MT][128] f32 partial tile in smem
 
 struct TcParams {
@@ -303,10 +311,11 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
 // Within every group of 8 weights the unpack leaves k in the order 0,4,1,5,2,6,3,7 (the pairs one mask
 // extracts); the activation tile is packed in the same order, and a sum over k does not care.
 template <int KIND>
-__global__ void __launch_bounds__(KIND == 2 ? kThreadsNbits : kThreads, 1)
+__global__ void __launch_bounds__(tc_threads<KIND>(), 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
           const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_o16, const TcParams p) {
   constexpr int MK = KIND == 4 ? 2 : (KIND >= 2 ? 0 : KIND);  // MMA kind and epilogue arithmetic (KIND 3: f16 with peer stores)
+  constexpr bool kDeq = KIND == 2 || KIND == 5;               // a weights tile is made in shared memory from a raw tile
   constexpr uint32_t kWTiles = KIND == 4 ? 2u : 1u;  // weight tiles per stage (KIND 4: value and residue planes)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B | raw nibble tile 4 KB for KIND 2), barriers,
@@ -314,14 +323,14 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int q_rows = p.MT * p.limbs;
   const uint32_t q_bytes = (uint32_t)q_rows * kRowBytes;
-  const uint32_t stage_bytes = kWTiles * kPTileBytes + q_bytes + (KIND == 2 ? kRawTileBytes : 0);
+  const uint32_t stage_bytes = kWTiles * kPTileBytes + q_bytes + (uint32_t)tc_raw_bytes<KIND>();
   const uint32_t bars = smem_base + (uint32_t)p.stages * stage_bytes;  // 8-byte aligned (stage_bytes % 1024 == 0)
   auto full_bar = [&](int s) { return bars + (uint32_t)s * 8u; };
   auto empty_bar = [&](int s) { return bars + (uint32_t)(p.stages + s) * 8u; };
   auto acc_full = [&](int b) { return bars + (uint32_t)(2 * p.stages + b) * 8u; };
   auto acc_empty = [&](int b) { return bars + (uint32_t)(2 * p.stages + 2 + b) * 8u; };
   auto deq_bar = [&](int s) { return bars + (uint32_t)(2 * p.stages + 4 + s) * 8u; };  // KIND 2 only
-  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4 + (KIND == 2 ? p.stages : 0)) * 8u;
+  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4 + (kDeq ? p.stages : 0)) * 8u;
   const uint32_t abort_flag = tmem_slot + 4u;
   const uint32_t partial = (tmem_slot + 16u + 15u) & ~15u;  // [MT][128] f32, split-K mode only; 16-byte aligned for
                                                             // the vector loads of the reduction (3*stages+4 may be odd)
@@ -342,7 +351,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     for (int s = 0; s < p.stages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      if (KIND == 2) mbar_init(deq_bar(s), kDeqWarps / 2);  // the four warps of the group that owns the chunk
+      if (kDeq) mbar_init(deq_bar(s), 4);  // KIND 2: the four warps of the group that owns the chunk; KIND 5: its four warps
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(acc_full(b), 1);
@@ -414,7 +423,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             }
             continue;
           }
-          if (KIND == 2) {
+          if (KIND == 5) {
+            mbar_expect_tx(fb, q_bytes + kRaw8TileBytes);
+            tma_load_2d(dst + kPTileBytes - kRaw8TileBytes, &map_w, 0, (tn * p.num_kb + kb) * 32, fb);  // 8 KB int8 tile, in
+                                                                                                      // the upper half of the f16 tile
+          } else if (KIND == 2) {
             mbar_expect_tx(fb, q_bytes + kRawTileBytes);
             tma_load_2d(dst + kPTileBytes + q_bytes, &map_w, 0, (tn * p.num_kb + kb) * 16, fb);  // 4 KB nibble tile
           } else {
@@ -459,7 +472,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             ok = false;
             break;
           }
-          if (KIND == 2 && !mbar_wait(fb + (2u * nst + 4u) * 8u, ph, p.wait_limit)) {  // weights tile unpacked
+          if (kDeq && !mbar_wait(fb + (2u * nst + 4u) * 8u, ph, p.wait_limit)) {  // weights tile unpacked
             set_abort(6, kb);
             ok = false;
             break;
@@ -489,6 +502,66 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
           }
         }
         if (ok) umma_commit(acc_full(buf));  // this tile's accumulators are complete
+      }
+    }
+    __syncwarp();
+  } else if (KIND == 5 && warp >= 2 + kEpiWarps && (warp & 2) == 0) {
+    // spare warp ids (see kDeqWarps): no role
+  } else if (KIND == 5 && warp >= 2 + kEpiWarps) {
+    // ---- int8 weights -> f16 weights tile: two groups of four warps take alternate K chunks; thread r of a group
+    // owns weight row r of the tile.  A byte q becomes the f16 value q exactly: (q ^ 0x80) placed under the exponent
+    // byte 0x64 is the f16 number 1024 + q + 128, minus 1152.  The per-column scale of the weights is applied to the
+    // f32 accumulator in the epilogue. ----
+    const int dw = ((warp - (2 + kEpiWarps)) >> 2) * 2 + (warp & 1);
+    const int dq = dw * 32 + lane, r = dq & 127, grp = dq >> 7;
+    const uint32_t nst = (uint32_t)p.stages;
+    const int chunks = kb1 - kb0;
+    const __half2 off = __float2half2_rn(1152.0f);
+    uint32_t it = 0;  // ring index of the next chunk (all chunks, both groups)
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int c = 0; c < chunks && ok; c++, it++) {
+        if ((int)(it & 1u) != grp) continue;
+        const uint32_t slot_i = it % nst, ph = (it / nst) & 1u;
+        int okw = 1;
+        if (lane == 0 && !mbar_wait(full_bar((int)slot_i), ph, p.wait_limit)) {
+          set_abort(5, c);
+          okw = 0;
+        }
+        ok = __shfl_sync(0xffffffffu, okw, 0) != 0 && !aborted();
+        if (!ok) break;
+        const uint32_t slot = smem_base + slot_i * stage_bytes;
+        // The int8 tile sits in the upper half of the f16 tile it becomes (no shared memory of its own, so the ring is
+        // as deep as the f16 kernel's): every thread of the group first takes its 64 bytes into registers, the group
+        // meets at its own named barrier, and only then are the f16 rows written over them.
+        const uint32_t src = slot + (uint32_t)(kPTileBytes - kRaw8TileBytes) + (uint32_t)(r * 64);
+        uint32_t wd[16];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(wd[4 * j]), "=r"(wd[4 * j + 1]), "=r"(wd[4 * j + 2]), "=r"(wd[4 * j + 3]) : "r"(src + (uint32_t)(j * 16)) : "memory");
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+#pragma unroll
+        for (int j = 0; j < 4; j++) {  // 16 weights per step -> two 16-byte pieces of the 128-byte f16 row
+          uint32_t h[8];
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const uint32_t x = wd[4 * j + q] ^ 0x80808080u;
+            uint32_t a0 = __byte_perm(x, 0x64646464u, 0x5140), a1 = __byte_perm(x, 0x64646464u, 0x5342);
+            __half2 h0 = __hsub2(*(__half2 *)&a0, off), h1 = __hsub2(*(__half2 *)&a1, off);
+            h[2 * q] = *(uint32_t *)&h0;
+            h[2 * q + 1] = *(uint32_t *)&h1;
+          }
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const uint32_t cc = (uint32_t)(2 * j + e);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(slot + (uint32_t)(r * 128) + ((cc ^ (uint32_t)(r & 7)) << 4)),
+                         "r"(h[4 * e]), "r"(h[4 * e + 1]), "r"(h[4 * e + 2]), "r"(h[4 * e + 3])
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();  // the tile is read by the tensor core through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(deq_bar((int)slot_i));
       }
     }
     __syncwarp();
@@ -601,7 +674,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       float *const outb = p.out + (size_t)(batch / p.o_div) * p.o_hi + (size_t)(batch % p.o_div) * p.o_lo;
       const int r16 = (batch / p.o_div) * p.o16_row_hi, c16 = (batch % p.o_div) * p.o16_col_lo;
       const uint32_t buf = lt & 1, use = lt >> 1;
-      if (KIND == 2) {  // leave the issue slots to the unpack warps while the tile is being accumulated
+      if (kDeq) {  // leave the issue slots to the unpack warps while the tile is being accumulated
         ok = false;
         for (uint32_t i = 0; i < (p.wait_limit >> 4) && !ok; i++) {
           ok = mbar_try_wait(acc_full(buf), use & 1) != 0;
@@ -874,6 +947,22 @@ __global__ void k_pack_w_i8(const int8_t *__restrict__ w, int K, int N, int nch,
   }
 }
 
+// int8 [K][N] (reference byte order k*N+n) -> Wp8[n/128][k/64][n%128][k%64] for the f16-activation route (KIND 5): the K
+// chunks of the f16 kernels, one byte per weight.  The destination was zero-filled.
+__global__ void k_pack_w_i8_k64(const int8_t *__restrict__ w, int K, int N, int nch, int8_t *__restrict__ out) {
+  __shared__ int8_t t[32][33];
+  const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    int k = k0 + r, n = n0 + threadIdx.x;
+    t[r][threadIdx.x] = (k < K && n < N) ? w[(size_t)k * N + n] : (int8_t)0;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < K) out[(((size_t)(n >> 7) * nch + (k >> 6)) * 128 + (n & 127)) * 64 + (k & 63)] = t[threadIdx.x][r];
+  }
+}
+
 // f32 or f16 [K][N] -> f16 Wp[n/128][k/64][n%128][k%64].
 template <typename SRC>
 __global__ void k_pack_w_f16(const SRC *__restrict__ w, int K, int N, int nch, __half *__restrict__ out,
@@ -999,35 +1088,32 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   p.o16_row_hi = ep.o16_row_hi;
   p.o16_col_lo = ep.o16_col_lo;
   int num_tiles = p.tiles_n * p.tiles_m * p.batches;
-  // Products with less than one wave of tiles (decode sizes, thin encoder shapes): split K across a cluster of up to
-  // 8 CTAs and, if that helps, cut the rows into shorter tiles, so that every SM streams operands.  Tile height and
-  // split are chosen together by a cost in units of "128-byte operand rows staged by the busiest CTA":
-  //   rounds over the SMs x (K chunks per CTA x (128 weight rows + MT x planes activation rows) + a fixed
-  //   prologue/epilogue term) + the cluster reduction of a split tile.
+  // Products whose tiles fit one wave of the SMs (decode sizes, thin encoder shapes) are bound by what ONE thread
+  // block can pull from L2 / HBM (measured ~120 GB/s per SM) on top of a fixed launch-and-ramp cost, so the aim is
+  // as many busy SMs as possible without a second wave: first shorter row tiles (no reduction needed), then K split
+  // over a cluster of 2, 4 or 8 CTAs whose partial tiles meet in shared memory.  Measured on 24 thin shapes: a
+  // second wave costs more than any split saves; clusters of 3, 5, 6, 7 place badly on the GPCs (2x slower);
+  // fewer than 4 K chunks per CTA no longer pays for the reduction.
   // (the split-K finish stores rows at pitch N: a caller-chosen pitch keeps the one-CTA-per-tile form)
   p.splitk = 1;
   p.kb_per_split = p.num_kb;
   const bool split_ok = !raw_i32 && !ep.out16 && ep.n_peers == 0 && (ep.ldc == 0 || ep.ldc == N) && p.batches == 1;
   if (split_ok && num_tiles <= ctx->sm_count) {
-    constexpr long long kFixed = 6 * 256, kReduce = 16;
-    long long best = -1;
-    int best_mt = p.MT, best_s = 1;
     const int mt_hi = p.MT;
-    for (int cand = mt_hi; cand >= 16; cand -= 16) {
-      const int tm = ceil_div(M, cand);
-      if (cand > 16 && ceil_div(M, cand - 16) == tm) continue;  // a shorter tile gives the same row tiling
-      for (int sp = 1; sp <= 8; sp *= 2) {  // (clusters of 3, 5, 6, 7 CTAs place badly on the GPCs: measured 2x slower)
-        if (sp > 1 && (cand > kSplitMaxMT || p.num_kb / sp < 2)) break;
-        const int kb = ceil_div(p.num_kb, sp), real_s = ceil_div(p.num_kb, kb);
-        if (real_s != sp) continue;
-        const long long ctas = (long long)p.tiles_n * tm * sp;
-        const long long rounds = (ctas + ctx->sm_count - 1) / ctx->sm_count;
-        const long long cost = rounds * ((long long)kb * (128 + cand * limbs) + kFixed) + (sp > 1 ? kReduce * sp * (cand / 16) : 0);
-        if (best < 0 || cost < best) {
-          best = cost;
-          best_mt = cand;
-          best_s = sp;
-        }
+    int best_mt = p.MT, best_s = 1;
+    // shortest row tile of at least 64 rows (or the whole of a shorter M) whose tiles still fit one wave
+    for (int cand = mt_hi; cand >= (mt_hi < 64 ? mt_hi : 64); cand -= 16) {
+      if ((long long)p.tiles_n * ceil_div(M, cand) > ctx->sm_count) break;
+      best_mt = cand;
+    }
+    while (best_mt > 16 && ceil_div(M, best_mt - 16) == ceil_div(M, best_mt)) best_mt -= 16;  // same tiling, less padding
+    // K split (tiles of at most 64 rows: the reduction of taller tiles costs more than the split saves): the widest
+    // power-of-two cluster that keeps one wave and at least 4 K chunks per CTA
+    if (best_mt <= 64) {
+      const long long tiles = (long long)p.tiles_n * ceil_div(M, best_mt);
+      for (int sp = 2; sp <= 8; sp *= 2) {
+        if (tiles * sp > ctx->sm_count || p.num_kb / sp < 4) break;
+        best_s = sp;
       }
     }
     if (ctx->tc_tile_rows > 0 || ctx->tc_split_k > 0) {  // tuning overrides (options "tc_tile_rows", "tc_split_k")
@@ -1046,12 +1132,12 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     num_tiles = p.tiles_n * p.tiles_m * p.batches;
   }
   const size_t stage_bytes =
-      (size_t)(KIND == 4 ? 2 : 1) * kPTileBytes + (size_t)p.MT * limbs * kRowBytes + (KIND == 2 ? kRawTileBytes : 0);
+      (size_t)(KIND == 4 ? 2 : 1) * kPTileBytes + (size_t)p.MT * limbs * kRowBytes + (size_t)tc_raw_bytes<KIND>();
   p.w_lo_rows = KIND == 4 ? p.tiles_n * p.num_kb * 128 : 0;
   // Results through shared-memory slabs and TMA stores: plain products only (see epilogue_tile), and only where the
   // copy engine's alignment rules hold (16-byte row pitch and base address).
   p.split_rb = p.splitk > 1 ? ceil_div(ceil_div(p.MT, 16), p.splitk) : 0;
-  p.tma_out = ((KIND <= 1 || KIND == 4) && !raw_i32 && p.splitk == 1 && p.batches == 1 && ep.n_peers == 0 && (p.ldc & 3) == 0 &&
+  p.tma_out = ((KIND <= 1 || KIND == 4 || KIND == 5) && !raw_i32 && p.splitk == 1 && p.batches == 1 && ep.n_peers == 0 && (p.ldc & 3) == 0 &&
                ((uintptr_t)out & 15) == 0 && (!ep.out16 || ((uintptr_t)ep.out16 & 127) == 0) && M >= 16)
                   ? 1
                   : 0;
@@ -1082,7 +1168,9 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   CUtensorMap map_w, map_a;
   // weights: rows of 128 bytes, (tiles_n * num_kb * 128) of them, boxes of 128 rows
   const uint64_t w_batches = p.w_batch_mod ? p.w_batch_mod : p.batches;
-  if (KIND == 2)  // nibble tiles [n/128][k/64][n%128][32 B]: a tile is one contiguous 4 KB run, described to the copy
+  if (KIND == 5)  // int8 tiles [n/128][k/64][n%128][64 B]: one contiguous 8 KB run each, as 32 rows of 256 bytes
+    FA_TRY(tc::make_tmap_bytes2d(ctx, &map_w, w_packed, 256, (uint64_t)p.tiles_n * p.num_kb * 32, 256, 32));
+  else if (KIND == 2)  // nibble tiles [n/128][k/64][n%128][32 B]: a tile is one contiguous 4 KB run, described to the copy
                   // engine as 16 rows of 256 bytes (as 128 rows of 32 bytes it cost the engine ~0.5 us per tile)
     FA_TRY(tc::make_tmap_bytes2d(ctx, &map_w, w_packed, 256, (uint64_t)p.tiles_n * p.num_kb * 16, 256, 16));
   else
@@ -1098,7 +1186,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[2];
-  cfg.blockDim = dim3(KIND == 2 ? kThreadsNbits : kThreads);
+  cfg.blockDim = dim3(tc_threads<KIND>());
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see fa_launch_dep
@@ -1116,7 +1204,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     cfg.gridDim = dim3(num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count);  // persistent: one CTA per SM
   }
   {
-    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : (KIND == 2 ? "tc_gemm_nbits" : (KIND == 4 ? "tc_gemm_tf32x3" : "tc_gemm_f16_scatter"))));
+    LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : (KIND == 2 ? "tc_gemm_nbits" : (KIND == 4 ? "tc_gemm_tf32x3" : (KIND == 5 ? "tc_gemm_i8w_f16a" : "tc_gemm_f16_scatter")))));
     cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, map_o, map_o16, p);
     if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm: %s", cudaGetErrorString(e));
   }
@@ -1247,6 +1335,23 @@ int fa_tc_gemm_f16(fa_ctx *ctx, const __half *a_packed, const __half *w_packed, 
 int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *w_packed, void *c, bool raw_i32, int M,
                   int N, int K, const TcEpilogue &ep) {
   return launch_tc<1>(ctx, w_packed, a_packed, limbs, c, raw_i32, M, N, K, ep);
+}
+
+// int8 weights x f16 activations (KIND 5): weights stay int8 in HBM, are widened to f16 in shared memory.
+size_t fa_tc_i8w_weight_bytes(int N, int K) { return (size_t)ceil_div(N, 128) * fa_tc_chunks(K, 2) * kRaw8TileBytes; }
+int fa_pack_w_i8_k64(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out) {
+  FA_CHECK_CUDA(ctx, cudaMemsetAsync(out, 0, fa_tc_i8w_weight_bytes(N, K), ctx->stream));
+  dim3 grid(ceil_div(K, 32), ceil_div(N, 32)), block(32, 8);
+  {
+    LaunchScope ls(ctx, "pack_w_i8_k64");
+    k_pack_w_i8_k64<<<grid, block, 0, ctx->stream>>>(w_kn, K, N, fa_tc_chunks(K, 2), out);
+  }
+  FA_LAUNCH_CHECK(ctx, "pack_w_i8_k64");
+  return FA_OK;
+}
+int fa_tc_gemm_i8w_f16a(fa_ctx *ctx, const __half *a_packed, const int8_t *w_packed, float *c, int M, int N, int K,
+                        const TcEpilogue &ep) {
+  return launch_tc<5>(ctx, w_packed, a_packed, ep.a_hilo ? 2 : 1, c, false, M, N, K, ep);
 }
 
 // f32 x f32 on the tensor cores (kind::tf32, value + residue planes on both sides; see KIND 4).

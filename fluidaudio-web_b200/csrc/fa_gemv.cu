@@ -79,14 +79,13 @@ __device__ __forceinline__ void nbits_block(const uint4 (&wv)[R], const float (&
 // the prologue instead of after them (measured before the change: ~4 us of a 5.5 us launch had no weight byte in
 // flight, against 1.6 us of streaming).  PRE blocks per lane are requested early (64 blocks per row at K = 2048 =
 // 2 per lane); longer rows load the rest in the loop.
-// Prologue: a thread owns 8 consecutive k of every row (256 threads x 8 = 2048 per sweep), which is exactly one
-// 32-bit word of the even-k digit plane and one of the odd-k plane, so digits go to shared memory as whole words and
-// the per-block digit sums are two shuffles; for K <= 2048 the activations are read from global memory once.
+// Prologue: a thread owns 8 consecutive k of one row, which is exactly one 32-bit word of the even-k digit plane and
+// one of the odd-k plane, so digits go to shared memory as whole words and the per-block digit sums are two shuffles.
 template <int M, int R>
 __global__ void __launch_bounds__(kThreads, 2) k_gemv_nbits(const float *__restrict__ a, const uint8_t *__restrict__ bq,
                                                             const float *__restrict__ scales, const uint8_t *__restrict__ zp,
                                                             float *__restrict__ y, int N, int K, int nblk, int zpb) {
-  constexpr int PRE = 2, SWEEP = kThreads * 8;
+  constexpr int PRE = 2;
   extern __shared__ __align__(16) unsigned char smem[];
   int8_t *dig = (int8_t *)smem;                     // [M][2] planes of K bytes: even-k words of every block (16 B
                                                     // each, so 8 lanes read 128 consecutive bytes), then odd-k words
@@ -124,50 +123,51 @@ __global__ void __launch_bounds__(kThreads, 2) k_gemv_nbits(const float *__restr
   }
 
   // ---- activation digits: q1 = rint(a/s), q2 = rint((a/s - q1) * 128) with s = max|row| / 127 --------------------
-  const bool one_sweep = K <= SWEEP;
-  float av[M][8];
-  float mx[M];
-#pragma unroll
-  for (int m = 0; m < M; m++) mx[m] = 0.f;
-  for (int k0 = tid * 8; k0 < K; k0 += SWEEP) {
-#pragma unroll
-    for (int m = 0; m < M; m++) {
-      const float4 x0 = __ldg((const float4 *)(a + (size_t)m * K + k0)), x1 = __ldg((const float4 *)(a + (size_t)m * K + k0 + 4));
-      av[m][0] = x0.x, av[m][1] = x0.y, av[m][2] = x0.z, av[m][3] = x0.w;
-      av[m][4] = x1.x, av[m][5] = x1.y, av[m][6] = x1.z, av[m][7] = x1.w;
-#pragma unroll
-      for (int i = 0; i < 8; i++) mx[m] = fmaxf(mx[m], fabsf(av[m][i]));
+  // The warps split the rows between them (8 / M warps per row), so the code below handles ONE row per thread and
+  // its register need does not grow with M; the second sweep re-reads the row (a few KB, L1-resident).
+  constexpr int WPR = 8 / M;                       // warps per row (M = 3: two warps idle here)
+  const int row = warp % M, wr = warp / M;
+  const bool prow = wr < WPR;
+  const float *arow = a + (size_t)row * K;
+  float mx = 0.f;
+  if (prow)
+    for (int k0 = (wr * 32 + lane) * 8; k0 < K; k0 += WPR * 256) {
+      const float4 x0 = __ldg((const float4 *)(arow + k0)), x1 = __ldg((const float4 *)(arow + k0 + 4));
+      mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x0.x), fabsf(x0.y)), fmaxf(fabsf(x0.z), fabsf(x0.w))));
+      mx = fmaxf(mx, fmaxf(fmaxf(fabsf(x1.x), fabsf(x1.y)), fmaxf(fabsf(x1.z), fabsf(x1.w))));
     }
-  }
-#pragma unroll
-  for (int m = 0; m < M; m++) {
-    mx[m] = warp_max_f(mx[m]);
-    if (lane == 0) red[warp * M + m] = mx[m];
-  }
+  mx = warp_max_f(mx);
+  if (lane == 0) red[warp] = mx;
   __syncthreads();
-  float rs[M], inv[M];
+  float rs[M];
 #pragma unroll
   for (int m = 0; m < M; m++) {
-    float t = red[m];
+    float t = 0.f;
 #pragma unroll
-    for (int w = 1; w < 8; w++) t = fmaxf(t, red[w * M + m]);
+    for (int w = 0; w < WPR; w++) t = fmaxf(t, red[w * M + m]);
     rs[m] = t > 0.f ? t / 127.0f : 1.0f;
-    inv[m] = 1.0f / rs[m];
   }
-  for (int k0 = tid * 8; k0 < ((K + SWEEP - 1) / SWEEP) * SWEEP; k0 += SWEEP) {  // whole warps stay together for the shuffles
-    const bool in = k0 < K;
-    const int b = k0 >> 5, wi = (k0 & 31) >> 3;
+  if (prow) {
+    float inv = 1.0f;
 #pragma unroll
-    for (int m = 0; m < M; m++) {
-      if (!one_sweep && in) {
-        const float4 x0 = __ldg((const float4 *)(a + (size_t)m * K + k0)), x1 = __ldg((const float4 *)(a + (size_t)m * K + k0 + 4));
-        av[m][0] = x0.x, av[m][1] = x0.y, av[m][2] = x0.z, av[m][3] = x0.w;
-        av[m][4] = x1.x, av[m][5] = x1.y, av[m][6] = x1.z, av[m][7] = x1.w;
+    for (int m = 0; m < M; m++)
+      if (m == row) inv = 1.0f / rs[m];
+    const int kend = ((K + WPR * 256 - 1) / (WPR * 256)) * (WPR * 256);  // whole warps stay together for the shuffles
+    for (int k0 = (wr * 32 + lane) * 8; k0 < kend; k0 += WPR * 256) {
+      const bool in = k0 < K;
+      const int b = k0 >> 5, wi = (k0 & 31) >> 3;
+      float x[8];
+      if (in) {
+        const float4 x0 = __ldg((const float4 *)(arow + k0)), x1 = __ldg((const float4 *)(arow + k0 + 4));
+        x[0] = x0.x, x[1] = x0.y, x[2] = x0.z, x[3] = x0.w, x[4] = x1.x, x[5] = x1.y, x[6] = x1.z, x[7] = x1.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] = 0.f;
       }
       int q1[8], q2[8], s1 = 0, s2 = 0;
 #pragma unroll
       for (int i = 0; i < 8; i++) {
-        const float t = in ? av[m][i] * inv[m] : 0.f;
+        const float t = x[i] * inv;
         const float f1 = rintf(t);
         q1[i] = (int)f1;
         q2[i] = (int)rintf((t - f1) * 128.0f);
@@ -179,17 +179,17 @@ __global__ void __launch_bounds__(kThreads, 2) k_gemv_nbits(const float *__restr
         return (unsigned)(b0 & 0xFF) | ((unsigned)(b1 & 0xFF) << 8) | ((unsigned)(b2 & 0xFF) << 16) | ((unsigned)(b3 & 0xFF) << 24);
       };
       if (in) {
-        *(unsigned *)(dig + (size_t)(m * 2 + 0) * K + b * 16 + wi * 4) = pack(q1[0], q1[2], q1[4], q1[6]);
-        *(unsigned *)(dig + (size_t)(m * 2 + 0) * K + (K >> 1) + b * 16 + wi * 4) = pack(q1[1], q1[3], q1[5], q1[7]);
-        *(unsigned *)(dig + (size_t)(m * 2 + 1) * K + b * 16 + wi * 4) = pack(q2[0], q2[2], q2[4], q2[6]);
-        *(unsigned *)(dig + (size_t)(m * 2 + 1) * K + (K >> 1) + b * 16 + wi * 4) = pack(q2[1], q2[3], q2[5], q2[7]);
+        *(unsigned *)(dig + (size_t)(row * 2 + 0) * K + b * 16 + wi * 4) = pack(q1[0], q1[2], q1[4], q1[6]);
+        *(unsigned *)(dig + (size_t)(row * 2 + 0) * K + (K >> 1) + b * 16 + wi * 4) = pack(q1[1], q1[3], q1[5], q1[7]);
+        *(unsigned *)(dig + (size_t)(row * 2 + 1) * K + b * 16 + wi * 4) = pack(q2[0], q2[2], q2[4], q2[6]);
+        *(unsigned *)(dig + (size_t)(row * 2 + 1) * K + (K >> 1) + b * 16 + wi * 4) = pack(q2[1], q2[3], q2[5], q2[7]);
       }
       // the 4 lanes of a 32-weight block
       s1 += __shfl_xor_sync(0xffffffffu, s1, 1), s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
       s2 += __shfl_xor_sync(0xffffffffu, s2, 1), s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
       if (in && (lane & 3) == 0) {
-        SA[(m * 2 + 0) * nblk + b] = s1;
-        SA[(m * 2 + 1) * nblk + b] = s2;
+        SA[(row * 2 + 0) * nblk + b] = s1;
+        SA[(row * 2 + 1) * nblk + b] = s2;
       }
     }
   }
@@ -412,8 +412,10 @@ template <int M>
 int launch_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y, int N,
                  int K, int nblk, int zpb) {
   const size_t smem = (size_t)M * 2 * K + (size_t)M * 2 * nblk * 4 + 8 * M * 4;
-  constexpr int R = 4;  // output columns per warp pass: shares each digit load between R rows of weights, and with two
-                        // resident CTAs per SM (register cap 128) one wave covers 148 * 2 * 8 * 4 = 9472 columns
+  // output columns per warp pass (each digit load is shared between R rows of weights): 4 for one activation row -
+  // with two resident CTAs per SM (register cap 128) one wave then covers 148 * 2 * 8 * 4 = 9472 columns - and 2 for
+  // more rows, where 4 would not fit the registers next to the early-requested weights
+  constexpr int R = M == 1 ? 4 : 2;
   auto kern = k_gemv_nbits<M, R>;
   if (smem > 48 * 1024) FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   // one resident wave: every CTA pays the digit prologue once and a second wave would pay it twice

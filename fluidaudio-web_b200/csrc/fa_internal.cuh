@@ -64,6 +64,11 @@ struct fa_bytes {
   void *nk_i8 = nullptr;
   size_t nk_bytes = 0;
   int nk_N = 0, nk_K = 0;
+  // Lazily built tile-contiguous int8 copy Wp8[n/128][k/64][n%128][64] for the f16-activation route (still one
+  // byte per weight).
+  void *nk_i8w = nullptr;
+  size_t nk_i8w_bytes = 0;
+  int i8w_N = 0, i8w_K = 0;
   // Lazily built packed f16 dequantised copy of an int4 payload (with the scales/zp it was built from).
   void *nk_f16 = nullptr;
   size_t nk_f16_bytes = 0;
@@ -360,6 +365,10 @@ int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, 
 int fa_pack_w_f16_batched(fa_ctx *ctx, const void *w_kn, int K, int N, int batch, size_t src_stride, __half *out);
 int fa_pack_w_nbits_f16(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk,
                         int zpb, __half *out);
+size_t fa_tc_i8w_weight_bytes(int N, int K);
+int fa_pack_w_i8_k64(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out);
+int fa_tc_gemm_i8w_f16a(fa_ctx *ctx, const __half *a_packed, const int8_t *w_packed, float *c, int M, int N, int K,
+                        const TcEpilogue &ep);
 size_t fa_tc_tf32_weight_bytes(int N, int K);
 size_t fa_tc_tf32_act_bytes(int M, int K);
 int fa_pack_w_tf32(fa_ctx *ctx, const float *w_kn, int K, int N, float *out);

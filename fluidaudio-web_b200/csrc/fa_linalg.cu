@@ -97,6 +97,18 @@ int ensure_nk_i8(fa_ctx *ctx, fa_bytes *wq, int N, int K) {
   return fa_pack_w_i8(ctx, (const int8_t *)wq->dptr, K, N, (int8_t *)wq->nk_i8);
 }
 
+// Tile-contiguous int8 copy of a [K][N] int8 payload for the f16-activation route, built once per handle and (N,K).
+int ensure_nk_i8w(fa_ctx *ctx, fa_bytes *wq, int N, int K) {
+  if (wq->nk_i8w && wq->i8w_N == N && wq->i8w_K == K) return FA_OK;
+  FA_NO_FIRST_USE_IN_RECORDING(ctx, wq->dptr, "matmulInt8Operand");
+  if (wq->nk_i8w) fa_block_release(ctx, wq->nk_i8w);
+  wq->nk_i8w = nullptr;
+  FA_TRY(fa_block_acquire(ctx, fa_tc_i8w_weight_bytes(N, K), &wq->nk_i8w, &wq->nk_i8w_bytes));
+  wq->i8w_N = N;
+  wq->i8w_K = K;
+  return fa_pack_w_i8_k64(ctx, (const int8_t *)wq->dptr, K, N, (int8_t *)wq->nk_i8w);
+}
+
 // Per-call scratch: a pool block that goes back to the pool as soon as the consuming kernel is
 // enqueued (reuse is stream-ordered).
 struct Scratch {
@@ -491,4 +503,76 @@ extern "C" int fa_int8_gemm_i32(fa_ctx *ctx, const int8_t *aq_host, int M, fa_by
   }
   if (rc == FA_OK) rc = fa_sync(ctx);
   return rc;
+}
+
+
+// Optional member matmulInt8Operand: y = act(scale[n] * sum_k f16(a[m,k]) * q[k,n] + bias[n]) + add[m,n] with the
+// activations rounded to f16, as on the f16-B route of matmul (the reference's tolerance for that route is 2e-2), while
+// the weights STAY int8 in device memory: the tensor-core kernel widens each int8 tile to f16 in shared memory and
+// applies the per-column scale to the f32 accumulator.  This is what lets an encoder whose artifact stores int8 per
+// output channel keep half the weight bytes resident, with the same producers (layernorm, attention, GLU + depthwise,
+// a previous product) handing over packed f16 operands.  Shapes outside the tensor-core route go through matmulInt8.
+extern "C" int fa_matmul_int8_operand(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, const fa_tensor *scale, int N, int K,
+                                      const fa_tensor *bias, int act, const fa_tensor *add, int operand_only, fa_tensor **out) {
+  if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmulInt8Operand: NULL argument");
+  FA_REQUIRE(ctx, fa_valid(ctx, a) && fa_valid_bytes(ctx, wq), "matmulInt8Operand: unknown handle");
+  FA_REQUIRE(ctx, N > 0 && K > 0, "matmulInt8Operand: N=%d K=%d", N, K);
+  const int M = a->rows;
+  FA_REQUIRE(ctx, a->cols == K, "matmulInt8Operand: A is [%d,%d] but K=%d", M, a->cols, K);
+  FA_REQUIRE(ctx, wq->nbytes >= (size_t)N * K, "matmulInt8Operand: packed weights hold %zu bytes, need %zu", wq->nbytes, (size_t)N * K);
+  FA_REQUIRE(ctx, act >= 0 && act <= 5, "matmulInt8Operand: unknown activation code %d", act);
+  FA_TRY(check_vec(ctx, scale, N, "matmulInt8Operand: scale"));
+  if (bias) FA_TRY(check_vec(ctx, bias, N, "matmulInt8Operand: bias"));
+  if (add) {
+    FA_TRY(check_vec(ctx, add, M * N, "matmulInt8Operand: add"));
+    FA_REQUIRE(ctx, add->rows == M && add->cols == N, "matmulInt8Operand: add is [%d,%d], expected [%d,%d]", add->rows, add->cols, M, N);
+  }
+  if (!(tc_shape_ok(ctx, M, N, K) && M > ctx->f16_hilo_rows)) {  // decode sizes and tiny shapes: exact-activation routes
+    fa_tensor *y = nullptr;
+    FA_TRY(fa_matmul_int8(ctx, a, wq, scale, N, K, bias, act, &y));
+    if (!add) {
+      *out = y;
+      return FA_OK;
+    }
+    const int rc = fa_ewise(ctx, y, add, 0, out);
+    fa_free_tensor(ctx, y);
+    return rc;
+  }
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  const float *ap = nullptr;
+  fa_tensor *atmp = nullptr;
+  const bool shadow_only = a->storage == FA_F32 && !a->view && a->a16_valid && !a->a16_hilo;
+  if (!shadow_only) FA_TRY(fa_as_f32(ctx, a, &ap, &atmp));
+  fa_tensor *c = nullptr;
+  FA_TRY(fa_tensor_new(ctx, M, N, FA_F32, true, &c));
+  Scratch sa(ctx);
+  const __half *a16 = nullptr;
+  bool hilo = false;
+  int rc = ensure_nk_i8w(ctx, wq, N, K);
+  if (rc == FA_OK) rc = row_operand_f16(ctx, a, ap, sa, &a16, &hilo);
+  if (rc == FA_OK) {
+    TcEpilogue ep;
+    ep.a_hilo = hilo;
+    ep.colscale = (const float *)scale->dptr;
+    ep.bias = bias ? (const float *)bias->dptr : nullptr;
+    ep.add = add ? (const float *)add->dptr : nullptr;
+    ep.act = act;
+    const bool hinted = operand_only && !add && fa_operand_only_ok(ctx, M, N);
+    if ((act != FA_ACT_NONE || hinted) && (N & 63) == 0 && (ep.out16 = fa_shadow_block(ctx, c)) != nullptr) {
+      c->a16_valid = true;
+      if (ctx->lazy_f32 && !add && fa_operand_only_ok(ctx, M, N)) {
+        ep.skip_f32 = true;
+        c->f32_lazy = true;
+        c->lazy_sticky = ctx->capturing != nullptr;
+      }
+    }
+    rc = fa_tc_gemm_i8w_f16a(ctx, a16, (const int8_t *)wq->nk_i8w, (float *)c->dptr, M, N, K, ep);
+  }
+  if (atmp) fa_free_tensor(ctx, atmp);
+  if (rc != FA_OK) {
+    fa_free_tensor(ctx, c);
+    return rc;
+  }
+  *out = c;
+  return FA_OK;
 }

@@ -25,7 +25,42 @@ def infer_config(man: Dict[str, np.ndarray]) -> dict:
                 melBins=Fsub * 8)
 
 
-def load_encoder(ctx, weights: Dict[str, np.ndarray], cfg_override: Optional[dict] = None) -> dict:
+class Int8Weight:
+    """A weight matrix [K, N] kept int8 on the device with its per-output-column f32 scales (optional backend member
+    matmulInt8Operand); `rows` / `cols` mirror a tensor's so that shape inference keeps working."""
+
+    __slots__ = ("q", "scale", "rows", "cols")
+
+    def __init__(self, ctx, q_kn: np.ndarray, scale: np.ndarray):
+        self.rows, self.cols = q_kn.shape
+        self.q = ctx.uploadBytes(np.ascontiguousarray(q_kn, np.int8))
+        self.scale = ctx.upload(np.ascontiguousarray(scale, np.float32), 1, scale.size)
+
+
+def mm(ctx, x, w, opts: Optional[dict] = None):
+    """matmul against a weight that is either a backend tensor (f16 storage) or an Int8Weight."""
+    if isinstance(w, Int8Weight):
+        return ctx.matmulInt8Operand(x, w.q, w.scale, w.cols, w.rows, opts)
+    return ctx.matmul(x, w, opts)
+
+
+def load_encoder_blob(ctx, blob: bytes, man: dict, int8_resident: bool = True, cfg_override: Optional[dict] = None) -> dict:
+    """loadParakeetEncoder for the int8 artifact (raw-encoder.js:39-161; format: engines/blob.py).  With
+    int8_resident the matrices the artifact stores int8 per output column (and the two pointwise convolutions, stored
+    per output channel = per column of their transposed form) stay int8 on the device - half the bytes of the f16
+    storage the reference uploads - and run through the backend's optional member matmulInt8Operand; the folds of the
+    loader (q * 1/sqrt(HD), FF output projections * 0.5) go into the column scales, exactly.  Without it (or on a
+    backend without that member) every tensor is dequantised on the host as the reference does."""
+    from . import blob as blobfmt
+
+    b = blobfmt.Blob(blob, man)
+    weights = b.as_f32_dict()
+    if not (int8_resident and hasattr(ctx, "matmulInt8Operand")):
+        return load_encoder(ctx, weights, cfg_override)
+    return load_encoder(ctx, weights, cfg_override, _i8=b)
+
+
+def load_encoder(ctx, weights: Dict[str, np.ndarray], cfg_override: Optional[dict] = None, _i8=None) -> dict:
     """Upload all encoder weights once (raw-encoder.js:39-161).  `weights` holds f32 arrays (already
     dequantised when the artifact stores int8, :55-76).  Matrices go up as f16 storage (:92-95)."""
     cfg = {**infer_config(weights), **(cfg_override or {})}
@@ -34,6 +69,9 @@ def load_encoder(ctx, weights: Dict[str, np.ndarray], cfg_override: Optional[dic
     f32 = np.float32
 
     def mat(k, s=None):
+        if _i8 is not None and _i8.is_i8(k) and _i8.man[k]["quant"] == "col":
+            q, sc, _ = _i8.tensor_i8(k)  # stays int8; a fold multiplies the column scales
+            return Int8Weight(ctx, q, sc if s is None else (sc * f32(s)).astype(f32))
         a = weights[k].astype(f32)
         if s is not None:
             a = (a * f32(s)).astype(f32)
@@ -50,6 +88,9 @@ def load_encoder(ctx, weights: Dict[str, np.ndarray], cfg_override: Optional[dic
 
     def pwT(k, cout, cin):
         # pointwise conv weight [cout, cin, 1] as a transposed matrix [cin, cout] (:112-118)
+        if _i8 is not None and _i8.is_i8(k):
+            q, sc, _ = _i8.tensor_i8(k)  # per-output-channel scales = per column of the transposed matrix
+            return Int8Weight(ctx, np.ascontiguousarray(q.reshape(cout, cin).T), sc)
         w = weights[k].astype(f32).reshape(cout, cin)
         return ctx.uploadF16(np.ascontiguousarray(w.T), cin, cout)
 
@@ -71,9 +112,15 @@ def load_encoder(ctx, weights: Dict[str, np.ndarray], cfg_override: Optional[dic
         # optional member: q | k | v as ONE projection (weights and biases side by side), consumed column-wise
         for L, lw in enumerate(layers):
             g = lambda s: f"L{L}_{s}"
-            cat = np.concatenate([weights[g("q")].astype(f32) * f32(INV), weights[g("k")].astype(f32),
-                                  weights[g("v")].astype(f32)], axis=1).astype(f32)
-            lw["qkv"] = ctx.uploadF16(np.ascontiguousarray(cat), cat.shape[0], cat.shape[1])
+            if _i8 is not None and all(_i8.is_i8(g(n)) for n in "qkv"):
+                qs = [_i8.tensor_i8(g(n)) for n in "qkv"]
+                lw["qkv"] = Int8Weight(ctx, np.concatenate([t[0] for t in qs], axis=1),
+                                       np.concatenate([(qs[0][1] * f32(INV)).astype(f32), qs[1][1], qs[2][1]]))
+                cat = np.zeros((1, 3 * weights[g("q")].shape[1]), f32)
+            else:
+                cat = np.concatenate([weights[g("q")].astype(f32) * f32(INV), weights[g("k")].astype(f32),
+                                      weights[g("v")].astype(f32)], axis=1).astype(f32)
+                lw["qkv"] = ctx.uploadF16(np.ascontiguousarray(cat), cat.shape[0], cat.shape[1])
             n = cat.shape[1] // 3
             parts = [(g("qb"), INV), (g("kb"), None), (g("vb"), None)]
             if any(k in weights for k, _ in parts):
@@ -127,7 +174,7 @@ def pre_encode(ctx, enc, mel):
         Hh = (Hh + 2 * p - k) // st + 1
         Wd = (Wd + 2 * p - k) // st + 1
     flat = ctx.subReshape(s, Csub, Hh, Wd)
-    return ctx.matmul(flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
+    return mm(ctx, flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
 
 
 def pre_encode_windows(ctx, enc, mels):
@@ -166,7 +213,7 @@ def pre_encode_windows(ctx, enc, mels):
         Hh = (Hh + 2 * p - k) // st + 1
         Wd = (Wd + 2 * p - k) // st + 1
     flat = ctx.subReshapeWindows(s, Csub, Hh, Wd, W)
-    return ctx.matmul(flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
+    return mm(ctx, flat, enc["sub"]["linw"], dict(bias=enc["sub"]["linb"])), Hh
 
 
 def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bool = True):
@@ -198,7 +245,7 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
 
     def ff(x, lp, w1, w2, b1, b2, xn=None):
         xn = ln_op(x, lp) if xn is None else xn
-        return ctx.matmul(ctx.matmul(xn, w1, dict(bias=b1, act="silu")), w2, dict(bias=b2, add=x))
+        return mm(ctx, mm(ctx, xn, w1, dict(bias=b1, act="silu")), w2, dict(bias=b2, add=x))
 
     # optional member: a block's last layernorm and the next block's first one in one pass over the rows
     chain = use_fast and hasattr(ctx, "layernormChain")
@@ -215,18 +262,18 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                 xln = ln_op(x, w["lnatt"])
                 fused_qkv = use_fast and "qkv" in w and W * Tsub >= 256 and 16 <= Tsub <= 192
                 if fused_qkv:
-                    qkv = ctx.matmul(xln, w["qkv"], dict(bias=w["qkvb"], operandOnly=True))  # read by attnFusedQKV only
+                    qkv = mm(ctx, xln, w["qkv"], dict(bias=w["qkvb"], operandOnly=True))  # read by attnFusedQKV only
                 else:
-                    q = ctx.matmul(xln, w["q"], dict(bias=w["qb"]))
-                    k = ctx.matmul(xln, w["k"], dict(bias=w["kb"]))
-                    v = ctx.matmul(xln, w["v"], dict(bias=w["vb"]))
+                    q = mm(ctx, xln, w["q"], dict(bias=w["qb"]))
+                    k = mm(ctx, xln, w["k"], dict(bias=w["kb"]))
+                    v = mm(ctx, xln, w["v"], dict(bias=w["vb"]))
                 if W > 1:  # pos projection is constant per (layer, Tsub): cached across groups (:307-317)
                     p = enc["_posProj"].get((L, Tsub))
                     if p is None:
-                        p = ctx.pin(ctx.matmul(peT, w["pos"]))
+                        p = ctx.pin(mm(ctx, peT, w["pos"]))
                         enc["_posProj"][(L, Tsub)] = p
                 else:
-                    p = ctx.matmul(peT, w["pos"])
+                    p = mm(ctx, peT, w["pos"])
                 outc = None
                 if fused_qkv:
                     outc = ctx.attnFusedQKV(qkv, p, w["pbuAll"], w["pbvAll"], H, HD, W)
@@ -240,8 +287,8 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                     bd = ctx.relShiftB(ctx.bmmQK(q, p, w["pbvAll"], H, HD, W, True), W * H)
                     probs = ctx.softmax(ctx.add(ac, bd))
                     outc = ctx.bmmPV(probs, v, H, HD, W)
-                x = ctx.matmul(outc, w["out"], dict(bias=w["outb"], add=x))
-                pre1 = ctx.matmul(ln_op(x, w["lnconv"]), w["pw1T"], dict(bias=w["pw1b"]))  # [W*T, 2D]
+                x = mm(ctx, outc, w["out"], dict(bias=w["outb"], add=x))
+                pre1 = mm(ctx, ln_op(x, w["lnconv"]), w["pw1T"], dict(bias=w["pw1b"]))  # [W*T, 2D]
                 opts = dict(cout=D, k=dwK, groups=D, padLeft=dwPadL, padRight=dwPadR, bias=w["dwb"], act="silu")
                 if use_fast and hasattr(ctx, "gluDwConvTimeMajor"):  # optional member: the module's middle in one launch
                     dwoT = ctx.gluDwConvTimeMajor(pre1, w["dw"], opts, W)  # [W*T, D]
@@ -256,7 +303,7 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
                         for wi in range(W):
                             ctx.setCols(dwo, ctx.conv1d(ctx.sliceCols(glu, wi * Tsub, Tsub), w["dw"], opts), wi * Tsub)
                     dwoT = ctx.transpose(dwo)
-                x = ctx.matmul(dwoT, w["pw2T"], dict(bias=w["pw2b"], add=x))
+                x = mm(ctx, dwoT, w["pw2T"], dict(bias=w["pw2b"], add=x))
                 x = ff(x, w["lnff2"], w["ff2w1"], w["ff2w2"], w["ff2b1"], w["ff2b2"])
                 if chain and L + 1 < LAYERS:
                     nxt = enc["layers"][L + 1]["lnff1"]

@@ -173,6 +173,16 @@ int fa_matmul_operand(fa_ctx *ctx, const fa_tensor *a, fa_tensor *b, const fa_te
  * digit products are exact int32 sums, recombined in the epilogue. */
 int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, const fa_tensor *scale, int N, int K,
                    const fa_tensor *bias, int act, fa_tensor **out);
+/* Optional member matmulInt8Operand (no counterpart in compute.d.ts; the reference dequantises an int8 artifact to
+ * f32 / f16 on the host when it loads it, src/engines/asr-parakeet/raw-encoder.js:55-76,92-95):
+ * y = act(scale[n] * sum_k a[m,k] * q[k,n] + bias[n]) + add[m,n], wq and scale as for matmulInt8.  The int8 weights
+ * STAY int8 in device memory (tile-contiguous, one byte per weight) and are widened to f16 inside the tensor-core
+ * kernel, the per-column scale multiplies the f32 accumulator; the activations are rounded to f16 as on matmul's
+ * f16-B route (tolerance 2e-2 in the reference's gate), so the producers that hand over packed f16 operands feed it
+ * directly.  operand_only != 0: the caller states the result is only read as a packed f16 operand (see
+ * fa_matmul_operand).  Shapes outside the tensor-core route (few rows, tiny products) go through fa_matmul_int8. */
+int fa_matmul_int8_operand(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, const fa_tensor *scale, int N, int K,
+                           const fa_tensor *bias, int act, const fa_tensor *add, int operand_only, fa_tensor **out);
 /* matmulNBits :166 (ONNX MatMulNBits, bits=4).  bq [N][nblk][16] bytes, low nibble = even k;
  * scales f32 [N*nblk]; zp packed nibbles [N][ceil(nblk/2)] (lib.rs:164-203).  block_size must be 32. */
 int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, const fa_tensor *scales, fa_bytes *zp, int N,

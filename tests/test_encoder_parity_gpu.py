@@ -106,3 +106,50 @@ def test_pipelined_encoder_returns_each_batch_in_order(ctx, pkg):
     finally:
         ctx.destroy()
         ctx2.destroy()
+
+
+def test_int8_artifact_loader_resident_weights(ctx, pkg):
+    """The encoder loaded from the int8 artifact (blob + manifest written by the restated quantiser) with the
+    matrices kept int8 on the device: one full-width block, teacher-forced, against the oracle running the
+    host-dequantised model (2e-2, the per-layer gate), and the tiny stack end to end against the f16-storage loader."""
+    from fluidaudio_web_b200.engines import blob
+
+    fc, synth = _eng()
+    # tiny stack: int8-resident vs host-dequantised on the same backend
+    w = synth.encoder_weights(synth.TINY, seed=3)
+    data, man = blob.write_int8_blob(w)
+    mels = [synth.log_mel(a, 32).reshape(-1) for a in synth.synth_audio(3, samples=16000 * 2, seed=3)]
+    h = ctx.pushArena()
+    a, _ = fc.encode_batch(ctx, fc.load_encoder_blob(ctx, data, man, int8_resident=True), mels)
+    b, _ = fc.encode_batch(ctx, fc.load_encoder_blob(ctx, data, man, int8_resident=False), mels)
+    assert np.abs(ctx.download(a) - ctx.download(b)).max() <= 2e-2
+    ctx.popArena(h)
+    # one real-size block
+    cfg = dict(synth.PARAKEET_06B, layers=1)
+    w = synth.encoder_weights(cfg, seed=3)
+    data, man = blob.write_int8_blob(w)
+    rng = np.random.default_rng(3)
+    Wn, Tsub, D = 2, 188, 1024
+    x0 = rng.standard_normal((Wn * Tsub, D)).astype(np.float32)
+
+    def run_layer(c, enc):
+        orig, orig_w = fc.pre_encode, fc.pre_encode_windows
+        fc.pre_encode = lambda c_, e_, m_: (c_.upload(m_, Tsub, D), Tsub)
+        fc.pre_encode_windows = lambda c_, e_, ms: (c_.upload(np.concatenate(ms), len(ms) * Tsub, D), Tsub)
+        try:
+            out, _ = fc.encode_batch(c, enc, [x0[i * Tsub:(i + 1) * Tsub] for i in range(Wn)])
+        finally:
+            fc.pre_encode, fc.pre_encode_windows = orig, orig_w
+        return out
+
+    ora = WasmOracle(threads=True)
+    ref = run_layer(ora, fc.load_encoder_blob(ora, data, man)).array()  # the oracle has no resident-int8 member
+    h = ctx.pushArena()
+    enc = fc.load_encoder_blob(ctx, data, man, int8_resident=True)
+    assert isinstance(enc["layers"][0]["ff1w1"], fc.Int8Weight) and isinstance(enc["layers"][0]["pw2T"], fc.Int8Weight)
+    ctx.startProfile(512)
+    got = ctx.download(run_layer(ctx, enc)).reshape(ref.shape)
+    labels = {e["label"] for e in ctx.endProfile()}
+    ctx.popArena(h)
+    assert "tc_gemm_i8w_f16a" in labels and "tc_gemm_f16" not in labels  # every weight product ran on int8 weights
+    assert np.abs(got - ref).max() <= 2e-2

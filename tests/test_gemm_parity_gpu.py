@@ -420,3 +420,41 @@ def test_f32_weight_small_shapes_stay_exact_f32(ctx):
     got = ctx.download(ctx.matmul(ctx.upload(a, M, K), ctx.upload(b, K, N))).reshape(M, N)
     ora = WasmOracle(threads=True)
     assert np.abs(got - ora.matmul(T(a, M, K), T(b, K, N)).array()).max() <= 1e-4
+
+
+# ---- int8 weights resident on the device, f16 activations (matmulInt8Operand) ----------------------------
+
+@pytest.mark.parametrize("M,K,N,opts", [(300, 520, 264, dict(bias=True, act="silu")), (512, 1024, 4096, {}),
+                                        (1024, 4096, 1024, dict(bias=True, add=True)), (200, 256, 192, dict(operandOnly=True)),
+                                        (6016, 1024, 3072, dict(bias=True, operandOnly=True)), (16, 1024, 512, dict(bias=True, add=True))])
+def test_int8_resident_weights_f16_activations_vs_oracle(ctx, M, K, N, opts):
+    """Against the oracle's matmulInt8 (f32 activations): the f16 rounding of the activations is the only difference,
+    so the f16-B route's tolerance applies (2e-2 on unit-scale outputs)."""
+    rng = np.random.default_rng(41)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    wq = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    sc = (rng.uniform(0.5, 1.5, N) / (73.0 * np.sqrt(K))).astype(np.float32)  # unit-scale outputs
+    bias = rng.standard_normal(N).astype(np.float32) if opts.get("bias") else None
+    add = rng.standard_normal((M, N)).astype(np.float32) if opts.get("add") else None
+    act = opts.get("act", "none")
+    o = dict(act=act, operandOnly=bool(opts.get("operandOnly")))
+    if bias is not None:
+        o["bias"] = ctx.upload(bias, 1, N)
+    if add is not None:
+        o["add"] = ctx.upload(add, M, N)
+    h = ctx.pushArena()
+    try:
+        ctx.startProfile(16)
+        got = ctx.download(ctx.matmulInt8Operand(ctx.upload(a, M, K), ctx.uploadBytes(wq), ctx.upload(sc, 1, N), N, K, o)).reshape(M, N)
+        labels = {e["label"] for e in ctx.endProfile()}
+    finally:
+        ctx.popArena(h)
+    if M > 64:
+        assert "tc_gemm_i8w_f16a" in labels, labels
+    rows = np.unique(np.concatenate([[0, M - 1], rng.integers(0, M, 48)]))
+    ora = WasmOracle(threads=True)
+    ref = ora.matmulInt8(T(a[rows], len(rows), K), ora.uploadBytes(wq), T(sc, 1, N), N, K, bias=T(bias, 1, N) if bias is not None else None,
+                         act=act).array()
+    if add is not None:
+        ref = ref + add[rows]
+    assert np.abs(got[rows] - ref).max() <= 2e-2
