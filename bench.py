@@ -419,7 +419,8 @@ class Encoder:
     dtype = "f16 weights x f16 activations, f32 accumulate"
     nsets = 1
 
-    weights_mode = "int8"  # "int8": the artifact's int8 matrices stay int8 in HBM; "f16": dequantised at load (f16 storage)
+    weights_mode = "f16"  # "f16": the int8 artifact is dequantised at load to f16 storage, as the reference's loader does
+                          # (the faster of the two today); "int8": its matrices stay int8 in HBM (matmulInt8Operand)
 
     def __init__(self, quick=False):
         self.W = 4 if quick else 32
@@ -447,49 +448,49 @@ class Encoder:
         self.enc = self._load(ctx)
         self.dtype = ("int8 weights (resident, widened to f16 in shared memory) x f16 activations, f32 accumulate"
                       if self.weights_mode == "int8" else "f16 weights x f16 activations, f32 accumulate")
-        audio = synth.synth_audio(4, seed=3)  # 4 distinct windows, cycled to fill the batch
-        base = [fastconformer.mel_time_major(synth.log_mel(a, 128).reshape(-1), 128) for a in audio]
-        self.mel_len = base[0].size
-        self.host_mels, self.dev_mels = [], []
-        for i in range(self.W):
-            buf = ctx.pinnedArray(self.mel_len)  # page-locked, time-major image of one window
-            buf[:] = base[i % len(base)]
-            self.host_mels.append(buf)
-            self.dev_mels.append(ctx.upload(buf, 1, self.mel_len))
+        audio = synth.synth_audio(self.W, seed=3)  # one distinct 15 s window per batch slot
+        self.n_samples = audio.shape[1]
+        # device-resident leg: the windows' log-mel features, computed once by the device front end
+        # (time-major, floor(N/160) = 1500 frames per window as the reference's ParakeetMel returns)
+        pcm = ctx.upload(audio, self.W, self.n_samples)
+        self.dev_mels = ctx.logMelWindows(pcm, 128)
+        ctx.freeTensor(pcm)
+        self.mel_len = self.dev_mels.cols
+        # end-to-end leg: page-locked PCM, one array per pipeline slot (filled by _pcm_slot)
+        self._audio = audio
         self.units_per_step = self.W
         self.e2e_batch = None
+
+    def _pcm_slot(self, ctx):
+        buf = ctx.pinnedArray(self.W * self.n_samples)
+        buf[:] = self._audio.reshape(-1)
+        return buf
 
     def step_device(self, ctx):
         h = ctx.pushArena()
         self.fc.encode_batch(ctx, self.enc, self.dev_mels)  # windows resident in HBM
         ctx.popArena(h)
 
-    def _e2e_body(self, ctx):
-        h = ctx.pushArena()
-        mels = [ctx.upload(m, 1, self.mel_len) for m in self.host_mels]  # H2D from page-locked memory
-        x, _ = self.fc.encode_batch(ctx, self.enc, mels)
-        ctx.pin(x)
-        ctx.popArena(h)
-        return x
-
     def step_e2e(self, ctx):
-        # public API, host buffers in, host frames out: PipelinedEncoder keeps two recorded forwards (uploads from
-        # page-locked memory and the staged read-back included) on two streams of this GPU and alternates, so one
-        # batch's copies run under the other's compute; every step uploads its windows and reads its frames back
+        # public API, host PCM in, host frames out: PipelinedEncoder keeps two recorded forwards (upload of the windows'
+        # 16 kHz samples from page-locked memory, log-mel front end on the device, encoder, read-back of the frames) on
+        # two streams of this GPU and alternates, so one batch's copies run under the other's compute; every step
+        # uploads its windows and reads its frames back
         if self.e2e_batch is None:
             import __graft_entry__ as ge
             from fluidaudio_web_b200.engines import synth
 
             ctx2 = ge.load_package().CudaContext(ctx.device)
             enc2 = self._load(ctx2)
-            self.e2e_batch = self.fc.PipelinedEncoder([ctx, ctx2], [self.enc, enc2], lambda s: self.host_mels, self.mel_len)
+            slots = [self._pcm_slot(ctx), self._pcm_slot(ctx2)]
+            self.e2e_batch = self.fc.PipelinedEncoder([ctx, ctx2], [self.enc, enc2], lambda s: slots[s], self.n_samples, from_pcm=True)
         return self.e2e_batch.submit()
 
     def e2e_drain(self):
         return self.e2e_batch.flush() if self.e2e_batch is not None else []
 
     def e2e_bytes(self):
-        return self.W * self.mel_len * 4, self.W * 188 * 1024 * 4
+        return self.W * self.n_samples * 4, self.W * 188 * 1024 * 4
 
     def value_from(self, steps, seconds):
         return self.W * self.window_s * steps / seconds
@@ -699,6 +700,81 @@ class DecoderInt8(Decoder):
     quant = "int8"
 
 
+class TdtDecode:
+    """The stage after the encoder: greedy TDT decoding (prediction network + joint, int8 out-matrix) of the 32
+    windows of one encoder batch, 188 pre-projected frames each, random-init weights with a bias on the blank logit so
+    that most frames emit nothing (as with a trained model), frames ~ N(0,1).  One step = the whole decode of the
+    batch, token ids and emission frames landed on the host.  Seed 5."""
+
+    name = "parakeet_tdt_decode_32_windows_188_frames"
+    metric = "tdt_decode_audio_seconds_per_second"
+    unit = "audio-s/s"
+    dtype = "int8 out-matrix x 3 int8 activation digits (joint), f32 value+residue planes on kind::tf32 (LSTM)"
+    nsets = 1
+    graph = False  # the decode reads a device counter back every few rounds: eager steps
+
+    def __init__(self, quick=False):
+        self.W = 8 if quick else 32
+        self.T = 188
+
+    def setup(self, ctx):
+        import __graft_entry__ as ge
+
+        ge.load_package()
+        from fluidaudio_web_b200.engines import tdt_decoder
+
+        self.td = tdt_decoder
+        self.weights = tdt_decoder.synth_tdt_weights(5)
+        self.dec = tdt_decoder.TdtDecoder(ctx, self.weights, int8=True)
+        self.host_proj = ctx.pinnedArray(self.W * self.T * 640)
+        self.host_proj[:] = np.random.default_rng(6).standard_normal(self.W * self.T * 640).astype(np.float32)
+        self.proj = ctx.upload(self.host_proj, self.W * self.T, 640)
+        self.units_per_step = self.W
+        self.tokens = 0
+
+    def step_device(self, ctx):
+        out = self.dec.decode_proj(self.proj, self.W, self.T)
+        self.tokens = sum(len(i) for i, _ in out)
+
+    def step_e2e(self, ctx):
+        p = ctx.upload(self.host_proj, self.W * self.T, 640)
+        out = self.dec.decode_proj(p, self.W, self.T)
+        ctx.freeTensor(p)
+        return out
+
+    def e2e_bytes(self):
+        return self.W * self.T * 640 * 4, 2 * 4 * max(1, self.tokens) + 4 * self.W
+
+    def value_from(self, steps, seconds):
+        return self.W * 15.0 * steps / seconds
+
+    def roofline(self, prof, peaks):
+        ent = [e for e in prof if e["label"] == "tc_gemm_i8"]
+        if not ent:
+            return None
+        e = ent[0]
+        per_launch = e["ms"] / e["count"]
+        alg = 640 * 8198 + self.W * 640 * 4 + self.W * 8198 * 4 + 8198 * 4  # int8 out-matrix + J + logits + bias
+        ach = alg / (per_launch * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4),
+                "traffic": None, "kernel": "k_tc_gemm<i8> (the joint's 640 -> 8198 product, one per lock-step round)",
+                "launches": e["count"], "avg_launch_us": round(per_launch * 1e3, 2), "rounds": self.dec.rounds,
+                "note": "per-launch event pairs in an eager decode; the 5.2 MB out-matrix stays in L2 between rounds, so the "
+                        "HBM figure says how far a round is from streaming its operands once; rounds are bound by launch and ramp",
+                "peak_source": peaks["source"]}
+
+    def cpu_sample(self, threads=True):
+        from oracle.tdt_oracle import TdtOracle, synth_tdt_weights
+
+        n = 8 if threads else 2
+        ora = TdtOracle(getattr(self, "weights", None) or synth_tdt_weights(5), int8=True, threads=(os.cpu_count() or 1) if threads else 1)
+        proj = np.random.default_rng(6).standard_normal((n, self.T, 640)).astype(np.float32)
+        t0 = time.perf_counter()
+        ora.decode_proj_batch(proj, n, self.T)
+        dt = time.perf_counter() - t0
+        return n * 15.0 / dt, f"{n} windows x {self.T} frames on the C restatement of rust/parakeet-decoder ({dt:.2f} s)"
+
+
 class F16GemmNSharded:
     """Benchmark configuration 3, its multi-GPU leg: the M = 16384 row of the f16 GEMM sweep with the output columns
     sharded over the ranks (each GPU holds N/world columns of every weight matrix) and an NCCL all-gather of
@@ -791,8 +867,81 @@ class F16GemmNSharded:
     cpu_sample = F16Gemm.cpu_sample
 
 
+def config4_sharded(ctx, wl, world, rank, local_rank):
+    """The encoder configuration as BASELINE states it: 256 independent 15 s windows, batches of 32, sharded over the
+    ranks in contiguous blocks (sharding.shard_range), frames gathered to rank 0 in window order and landed on the
+    host.  The clock (wall, max over ranks) covers upload of this rank's PCM, log-mel, the encoder batches, the
+    gather (NCCL, device to device) and rank 0's copy to host memory.  Rank 0 then re-encodes the last batch of the
+    last rank's shard itself and requires the gathered frames to be identical."""
+    import torch
+    from fluidaudio_web_b200 import sharding
+    from fluidaudio_web_b200.engines import synth
+
+    n_win, B, D, T = 256, wl.W, 1024, 188
+    lo, hi = sharding.shard_range(n_win, world, rank)
+    base = wl._audio  # the batch's 32 distinct windows; window i of the job = base[i % 32] scaled by a per-window gain
+    gain = (0.5 + 0.5 * np.random.default_rng(11).random(n_win)).astype(np.float32)
+    mine = np.stack([base[i % B] * gain[i] for i in range(lo, hi)]) if hi > lo else np.zeros((0, wl.n_samples), np.float32)
+    host = ctx.pinnedArray(max(1, mine.size))
+    host[:mine.size] = mine.reshape(-1)
+    out_host = ctx.pinnedArray(n_win * T * D) if rank == 0 else None
+    stream = torch.cuda.ExternalStream(ctx.stream(), device=local_rank)
+
+    def run():
+        frames = []
+        for i in range(0, hi - lo, B):
+            nb = min(B, hi - lo - i)
+            pcm = ctx.upload(host[i * wl.n_samples:(i + nb) * wl.n_samples], nb, wl.n_samples)
+            x, _ = wl.fc.encode_batch(ctx, wl.enc, ctx.logMelWindows(pcm, 128))
+            frames.append(x)
+        local = ctx.concatRows(frames) if len(frames) > 1 else frames[0]
+        if world == 1:
+            ctx.downloadAsync(local, out_host)
+            ctx.sync()
+            return
+        lt = sharding.as_torch(ctx, local)
+        with torch.cuda.stream(stream):
+            if rank == 0:
+                parts = [torch.empty_like(lt) for _ in range(world)]
+                torch.distributed.gather(lt, parts, dst=0)
+                full = torch.cat(parts, 0)
+                torch.from_numpy(out_host).view(n_win * T, D).copy_(full, non_blocking=True)
+            else:
+                torch.distributed.gather(lt, None, dst=0)
+        ctx.sync()
+        torch.cuda.synchronize()
+
+    if n_win % (world * B):
+        return {"skipped": f"256 windows do not split into batches of {B} over {world} ranks"}
+    h = ctx.pushArena()
+    run()  # warm-up (pool growth, NCCL set-up)
+    ctx.popArena(h)
+    if world > 1:
+        torch.distributed.barrier()
+    h = ctx.pushArena()
+    t0 = time.perf_counter()
+    run()
+    dt = time.perf_counter() - t0
+    ctx.popArena(h)
+    if world > 1:
+        t = torch.tensor([dt], device=f"cuda:{local_rank}")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        dt = float(t.item())
+    checked = None
+    if rank == 0:
+        h = ctx.pushArena()
+        last = np.stack([base[i % B] * gain[i] for i in range(n_win - B, n_win)])
+        x, _ = wl.fc.encode_batch(ctx, wl.enc, ctx.logMelWindows(ctx.upload(last, B, wl.n_samples), 128))
+        want = ctx.download(x)
+        ctx.popArena(h)
+        checked = bool(np.array_equal(want.reshape(-1), out_host[(n_win - B) * T * D:]))
+    return {"windows": n_win, "batch": B, "ms": round(dt * 1e3, 2), "audio_s_per_s": round(n_win * wl.window_s / dt, 1),
+            "timing": "wall clock around upload of PCM, log-mel, encoder batches, gather to rank 0 and copy to host; max over ranks",
+            "gathered_frames_identical_to_rank0_recompute": checked}
+
+
 WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "f16_gemm": F16Gemm, "encoder": Encoder,
-             "decoder": Decoder, "decoder_int8": DecoderInt8, "f16_gemm_nsharded": F16GemmNSharded}
+             "decoder": Decoder, "decoder_int8": DecoderInt8, "f16_gemm_nsharded": F16GemmNSharded, "tdt_decode": TdtDecode}
 DEFAULT_WORKLOAD = "encoder"
 
 
@@ -1066,6 +1215,10 @@ def run_cuda(args):
     e2e_val = wl.value_from(args.steps, e2e_s) * units
     h2d, d2h = wl.e2e_bytes()
 
+    cfg4 = None
+    if isinstance(wl, Encoder) and not args.quick:
+        cfg4 = config4_sharded(ctx, wl, world, rank, local_rank)
+
     shapes = None
     if world == 1 and not args.no_shapes:
         shapes = shapes_report(ctx, peaks, timed, quick=args.quick)
@@ -1088,7 +1241,7 @@ def run_cuda(args):
                            "roofline_timing": "per-launch CUDA event pairs, repeat pass of the same steps"},
                 "roofline": roof, "cpu_baseline": cpu,
                 "e2e": {"value": round(e2e_val, 3), "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-                "gpu_launches": int(launches), "clocks": clocks, "shapes": shapes,
+                "gpu_launches": int(launches), "clocks": clocks, "config4_256_windows_sharded": cfg4, "shapes": shapes,
                 "kernels": [{"label": e["label"], "launches": e["count"], "ms": round(e["ms"], 3)} for e in prof]}
         print(json.dumps(line), flush=True)
     ctx.destroy()
@@ -1106,8 +1259,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="smaller rotating set (for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape roofline records of the GEMM / GEMV shapes")
-    ap.add_argument("--encoder-weights", default="int8", choices=["int8", "f16"],
-                    help="encoder workload: keep the artifact's int8 matrices int8 in HBM (default) or dequantise them to f16 at load")
+    ap.add_argument("--encoder-weights", default="f16", choices=["int8", "f16"],
+                    help="encoder workload: dequantise the int8 artifact to f16 storage at load (default) or keep its matrices int8 in HBM")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -182,11 +182,14 @@ def pre_encode_windows(ctx, enc, mels):
     conv2dWindows / subReshapeWindows): same per-window arithmetic, x [W*Tsub, D] directly."""
     cfg = enc["cfg"]
     Csub, melBins = cfg["Csub"], cfg["melBins"]
-    W = len(mels)
-    if isinstance(mels[0], np.ndarray):
+    if not isinstance(mels, (list, tuple)):  # one backend tensor [W, T*melBins], a time-major window per row
+        s, W = mels, mels.rows               # (what the optional member logMelWindows returns)
+    elif isinstance(mels[0], np.ndarray):
+        W = len(mels)
         stacked = np.stack([mel_time_major(m, melBins) for m in mels])
         s = ctx.upload(stacked, W, stacked.shape[1])
     else:
+        W = len(mels)
         s = ctx.concatRows(list(mels))  # [W, T*melBins]
     Hh, Wd = s.cols // melBins, melBins
     conv = [(Csub, 1, 3, 2, 1, "relu", True), (Csub, Csub, 3, 2, Csub, "none", True), (Csub, Csub, 1, 1, 1, "relu", False),
@@ -224,8 +227,11 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
     cfg = enc["cfg"]
     D, H, HD, LAYERS, dwK = cfg["D"], cfg["H"], cfg["HD"], cfg["layers"], cfg["dwK"]
     ln = lambda x, lp: ctx.layernorm(x, lp[0], lp[1])
-    W = len(mels)
-    sizes = {(m.size if isinstance(m, np.ndarray) else m.rows * m.cols) for m in mels}
+    if not isinstance(mels, (list, tuple)):  # stacked windows on the device (see pre_encode_windows)
+        if not (hasattr(ctx, "conv2dWindows") and hasattr(ctx, "subReshapeWindows") and mels.rows > 1):
+            mels = [ctx.sliceRows(mels, i, 1) for i in range(mels.rows)]
+    W = mels.rows if not isinstance(mels, (list, tuple)) else len(mels)
+    sizes = {0} if not isinstance(mels, (list, tuple)) else {(m.size if isinstance(m, np.ndarray) else m.rows * m.cols) for m in mels}
     if use_fast and W > 1 and len(sizes) == 1 and hasattr(ctx, "conv2dWindows") and hasattr(ctx, "subReshapeWindows"):
         x, Tsub = pre_encode_windows(ctx, enc, mels)  # optional members: the whole front end in 7 launches
     else:
@@ -334,8 +340,13 @@ class PipelinedEncoder:
     f32 arrays (time-major windows, see mel_time_major) that slot's recording uploads on every launch - the caller
     fills them before submit()."""
 
-    def __init__(self, ctxs, encs, host_windows, mel_len: int):
+    def __init__(self, ctxs, encs, host_windows, mel_len: int, from_pcm: bool = False, post=None):
+        """from_pcm: the host windows hold 16 kHz PCM (mel_len = samples per window) and the recording starts with the
+        log-mel front end on the device (optional member logMelWindows; the reference runs it in host workers,
+        src/engines/asr-parakeet/mel-scheduler.js).  post(slot, frames) -> tensor: an op riding the batch whose result
+        is read back instead of the frames (the joint's encoder projection, src/engines/asr-parakeet/pipeline.js:57-61)."""
         self.ctxs, self.encs, self.mel_len = list(ctxs), list(encs), mel_len
+        self.from_pcm, self.post = from_pcm, post
         self.host = [host_windows(s) for s in range(len(self.ctxs))]
         self.batches, self.results, self.pending = [], [], []
         for s, ctx in enumerate(self.ctxs):
@@ -350,8 +361,17 @@ class PipelinedEncoder:
     def _body(self, s, res):
         ctx = self.ctxs[s]
         h = ctx.pushArena()
-        mels = [ctx.upload(m, 1, self.mel_len) for m in self.host[s]]
+        if isinstance(self.host[s], np.ndarray):  # one page-locked array holding all windows of the slot back to back
+            mels = ctx.upload(self.host[s], self.host[s].size // self.mel_len, self.mel_len)
+        else:
+            mels = [ctx.upload(m, 1, self.mel_len) for m in self.host[s]]
+        if self.from_pcm:
+            if isinstance(mels, list):
+                mels = ctx.concatRows(mels) if len(mels) > 1 else mels[0]
+            mels = ctx.logMelWindows(mels, self.encs[s]["cfg"]["melBins"])
         x, _ = encode_batch(ctx, self.encs[s], mels)
+        if self.post is not None:
+            x = self.post(s, x)
         if res is not None:
             ctx.downloadAsync(x, res)
         ctx.pin(x)
