@@ -296,6 +296,119 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
   }
 }
 
+// The same epilogue for the common case (float accumulators, one output per accumulator, no row scale / row bias, no
+// K split), software-pipelined: the TMEM read and the residual loads of a warp's NEXT 16-row block are issued before
+// the current block is finished, so their latencies (a few hundred cycles for the TMEM read, an L2 round trip for the
+// residual) overlap the arithmetic and stores of the current block instead of adding up block after block.  With
+// K = 1024 a tile's epilogue (28 blocks of 16 x 32 values per warp pair) was longer than its main loop: the warps
+// spent most of it waiting on one load at a time.
+template <bool PEERS>
+__device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t lane_addr, int n0, int m0, int quad, int lane,
+                                                   int half, float *outb, int r16, int c16, const CUtensorMap *map_o,
+                                                   const CUtensorMap *map_o16, uint32_t slab_f32, uint32_t slab_f16,
+                                                   uint32_t &slab_turn) {
+  const int n = n0 + quad * 32 + lane;
+  const bool n_ok = n < p.N;
+  const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
+  const float bs = (p.bias && n_ok) ? p.bias[n] : 0.0f;
+  const bool has_add = p.add != nullptr && n_ok;
+  int c = half * 16;
+  if (c >= p.MT || m0 + c >= p.M) return;
+
+  auto issue = [&](int cc, uint32_t (&v)[16], float (&ad)[16]) {
+    tmem_ld16(lane_addr + (uint32_t)cc, v);
+    if (has_add) {
+      const float *arow = p.add + (size_t)(m0 + cc) * p.N + n;
+      if (m0 + cc + 16 <= p.M) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) ad[j] = __ldg(arow + (size_t)j * p.N);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) ad[j] = m0 + cc + j < p.M ? __ldg(arow + (size_t)j * p.N) : 0.0f;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j++) ad[j] = 0.0f;
+    }
+  };
+  auto finish = [&](int cc, const uint32_t (&vr)[16], const float (&ad)[16]) {
+    const bool full_rows = m0 + cc + 16 <= p.M;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = fmaf(__uint_as_float(vr[j]), cs, bs);
+    act16(v, p.act);
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] += ad[j];
+    if (!PEERS && p.tma_out) {
+      const uint32_t b = slab_turn & 1u;
+      slab_turn++;
+      if (lane == 0) tma_store_wait_read<1>();  // the group that used slab b two blocks ago has read it
+      __syncwarp();
+      if (p.out16) {
+        const uint32_t dst = slab_f16 + b * 1024u + (uint32_t)lane * 2u;
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst + (uint32_t)j * 64u), "h"(__half_as_ushort(__float2half_rn(v[j]))) : "memory");
+      }
+      if (!p.skip_f32) {
+        const uint32_t dst = slab_f32 + b * 2048u + (uint32_t)lane * 4u;
+#pragma unroll
+        for (int j = 0; j < 16; j++) asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + (uint32_t)j * 128u), "f"(v[j]) : "memory");
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int gn = n0 + quad * 32 + c16;
+        if (p.out16) tma_store_3d(map_o16, slab_f16 + b * 1024u, gn & 63, r16 + m0 + cc, gn >> 6);
+        if (!p.skip_f32) tma_store_2d(map_o, slab_f32 + b * 2048u, n0 + quad * 32, m0 + cc);
+        tma_store_commit();
+      }
+      return;
+    }
+    if (!n_ok) return;
+    if (p.out16) {
+      const int gn = n + c16;
+      __half *h16 = p.out16 + ((size_t)(gn >> 6) * p.o16_rows + (r16 + m0 + cc)) * 64 + (gn & 63);
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        if (full_rows || m0 + cc + j < p.M) h16[(size_t)j * 64] = __float2half_rn(v[j]);
+    }
+    if (!p.skip_f32) {
+      float *orow = outb + (size_t)(m0 + cc) * p.ldc + n;
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        if (full_rows || m0 + cc + j < p.M) orow[(size_t)j * p.ldc] = v[j];
+    }
+    if (PEERS)
+      for (int pi = 0; pi < p.n_peers; pi++) {
+        float *prow = p.peer_out[pi] + (size_t)(m0 + cc) * p.ldc + n;
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if (full_rows || m0 + cc + j < p.M) prow[(size_t)j * p.ldc] = v[j];
+      }
+  };
+
+  uint32_t va[16], vb[16];
+  float aa[16], ab[16];
+  issue(c, va, aa);
+  for (;;) {
+    tmem_ld_wait();
+    int cn = c + 4 * kEpiWarps;
+    bool more = cn < p.MT && m0 + cn < p.M;
+    if (more) issue(cn, vb, ab);
+    finish(c, va, aa);
+    if (!more) break;
+    c = cn;
+    tmem_ld_wait();
+    cn = c + 4 * kEpiWarps;
+    more = cn < p.MT && m0 + cn < p.M;
+    if (more) issue(cn, va, aa);
+    finish(c, vb, ab);
+    if (!more) break;
+    c = cn;
+  }
+}
+
 // KIND 4: f32 weights AND f32 activations on the tensor cores (kind::tf32), each operand as two planes - the f32 value,
 // of which the MMA reads the top 19 bits, and what that truncation drops, computed by the prepass - with three products
 // per K step (value x value, residue x value, value x residue) accumulated into the same TMEM columns: f32 range,
@@ -688,8 +801,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       if (!ok) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial, &map_o, &map_o16,
-                                   slab_f32, slab_f16, slab_turn, cl_rank);
+      if (!kDeq && MK != 1 && p.splitk == 1 && !p.rowscale && !p.rowbias)
+        epilogue_tile_fast<KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, &map_o, &map_o16, slab_f32,
+                                      slab_f16, slab_turn);
+      else
+        epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial, &map_o, &map_o16,
+                                     slab_f32, slab_f16, slab_turn, cl_rank);
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
