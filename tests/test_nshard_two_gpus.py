@@ -58,6 +58,9 @@ def test_two_gpu_forms_agree(tmp_path):
     r0, r1 = np.load(tmp_path / "r0.npy"), np.load(tmp_path / "r1.npy")
     for r in (r0, r1):
         gathered, fused, whole = r
-        assert np.array_equal(gathered, whole)  # same kernel, same per-column arithmetic
-        assert np.array_equal(fused, whole)
+        # the same f16 operands and f32 accumulation everywhere; a thin column block may split K over a cluster, which
+        # changes the order of the f32 sums, so the forms agree to f32 rounding, not bit for bit
+        tol = 2e-6 * float(np.abs(whole).max()) * np.sqrt(512)
+        assert np.abs(gathered - whole).max() <= tol
+        assert np.abs(fused - whole).max() <= tol
     assert np.array_equal(r0, r1)  # both ranks end with the same full product
