@@ -1254,7 +1254,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   // Results through shared-memory slabs and TMA stores: plain products only (see epilogue_tile), and only where the
   // copy engine's alignment rules hold (16-byte row pitch and base address).
   p.split_rb = p.splitk > 1 ? ceil_div(ceil_div(p.MT, 16), p.splitk) : 0;
-  p.tma_out = ((KIND <= 1 || KIND == 4 || KIND == 5) && !raw_i32 && p.splitk == 1 && p.batches == 1 && ep.n_peers == 0 && (p.ldc & 3) == 0 &&
+  p.tma_out = (ctx->tc_tma_store && (KIND <= 1 || KIND == 4 || KIND == 5) && !raw_i32 && p.splitk == 1 && p.batches == 1 && ep.n_peers == 0 && (p.ldc & 3) == 0 &&
                ((uintptr_t)out & 15) == 0 && (!ep.out16 || ((uintptr_t)ep.out16 & 127) == 0) && M >= 16)
                   ? 1
                   : 0;
