@@ -153,6 +153,10 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->gemv_ctas_per_sm = (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "tc_pair")) {
+    ctx->tc_pair = value != 0;
+    return FA_OK;
+  }
   if (!strcmp(key, "tc_tma_store")) {
     ctx->tc_tma_store = value != 0;
     return FA_OK;

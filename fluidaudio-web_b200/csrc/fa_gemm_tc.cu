@@ -29,6 +29,8 @@
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..9 = epilogue (TMEM lane quadrant = warp_id % 4, two warps per quadrant).
+#include <type_traits>
+
 #include "fa_tc_common.cuh"
 
 namespace {
@@ -38,7 +40,12 @@ using namespace tc;
 constexpr int kEpiWarps = 8;                   // two per TMEM lane quadrant (one per quadrant leaves the MMA and
                                                // producer warps more issue slots - later tiles ran ~15 % faster - but
                                                // doubles the epilogue's own time, and the encoder step got 20 % slower)
-constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
+constexpr int kThreads = 96 + 32 * kEpiWarps;  // warp 0 weights producer, warp 1 MMA, warps 2..9 epilogue, warp 10
+                                               // activations producer.  ONE thread sustains a tile load only every
+                                               // ~300-400 clocks whatever the tile's size (measured: 407 clocks per
+                                               // load per issuing thread for 4 KB..16 KB tiles, four threads four times
+                                               // the loads), so a K chunk's two loads from one thread paced the whole
+                                               // pipeline at ~650 clocks per chunk against 448-512 for its MMAs
 constexpr int kRowBytes = 128;                 // one swizzle atom of K per stage
 constexpr int kPTileBytes = 128 * kRowBytes;   // weights tile: 128 rows
 // int4 variant: 8 more warps unpack nibbles into the f16 weights tile.  They sit on the warp ids above the epilogue
@@ -430,6 +437,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   constexpr int MK = KIND == 4 ? 2 : (KIND >= 2 ? 0 : KIND);  // MMA kind and epilogue arithmetic (KIND 3: f16 with peer stores)
   constexpr bool kDeq = KIND == 2 || KIND == 5;               // a weights tile is made in shared memory from a raw tile
   constexpr uint32_t kWTiles = KIND == 4 ? 2u : 1u;  // weight tiles per stage (KIND 4: value and residue planes)
+  constexpr bool kTwoProd = !kDeq;  // a second producer thread (warp 2 + kEpiWarps) loads the activation tiles
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: [stages] x (P tile 16 KB | Q tile limbs*MT*128 B | raw nibble tile 4 KB for KIND 2), barriers,
   // split-K partial tile
@@ -511,9 +519,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   // also reconverges the warp before the block-wide barriers (aligned barriers need converged warps).
   if (warp == 0) {
     // ---- TMA producer: runs ahead across tiles, bounded only by the ring ----------------------
+    // Ring position as running values (barrier address, slot address, parity) advanced without a branch; the wait on
+    // a slot's empty barrier uses the opposite parity of its full barrier, which a freshly initialised barrier
+    // passes at once, so the first trip round the ring needs no special case.
     if (lane == 0) {
-      uint32_t s = 0, ph = 0, it = 0;  // ring slot, parity of the slot's current use, chunks issued
-      const uint32_t nst = (uint32_t)p.stages;
+      const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
+      uint32_t fb = bars, dst = smem_base, ph = 0;
       bool stop = false;
       for (int tile = blockIdx.x; tile < num_tiles && !stop; tile += gridDim.x) {
         const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
@@ -522,100 +533,149 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         int wrow = ((wb * p.tiles_n + tn) * p.num_kb + kb0) * 128;
         int aslab = (p.a_shared ? 0 : batch) * p.limbs * p.num_kb + kb0;
         const int m0 = tm * p.MT;
-        for (int kb = kb0; kb < kb1; kb++, it++, wrow += 128, aslab++) {
-          const uint32_t fb = bars + s * 8u, dst = smem_base + s * stage_bytes;
-          if (it >= nst && !mbar_wait(fb + nst * 8u, ph ^ 1u, p.wait_limit)) {  // empty barrier of slot s, previous use
+        const int wh = tile == 0 ? p.withhold_kb : -1;  // test hook: this chunk never arrives
+        for (int kb = kb0; kb < kb1; kb++, wrow += 128, aslab++) {
+          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {  // empty barrier of the slot, previous use
             set_abort(1, kb);
             stop = true;
             break;
           }
-          if (p.withhold_kb == kb && tile == 0) {  // test hook: this chunk never arrives
-            if (++s == nst) {
-              s = 0;
-              ph ^= 1u;
+          if (kb != wh) {
+            if (KIND == 5) {
+              mbar_expect_tx(fb, q_bytes + kRaw8TileBytes);
+              tma_load_2d(dst + kPTileBytes - kRaw8TileBytes, &map_w, 0, (tn * p.num_kb + kb) * 32, fb);  // 8 KB int8 tile, in
+                                                                                                        // the upper half of the f16 tile
+            } else if (KIND == 2) {
+              mbar_expect_tx(fb, q_bytes + kRawTileBytes);
+              tma_load_2d(dst + kPTileBytes + q_bytes, &map_w, 0, (tn * p.num_kb + kb) * 16, fb);  // 4 KB nibble tile
+            } else {
+              mbar_expect_tx(fb, stage_bytes);
+              tma_load_2d(dst, &map_w, 0, wrow, fb);
+              if (KIND == 4) tma_load_2d(dst + kPTileBytes, &map_w, 0, wrow + p.w_lo_rows, fb);  // residue plane
             }
-            continue;
+            if (!kTwoProd) {
+              tma_load_3d(dst + kWTiles * kPTileBytes, &map_a, 0, m0, aslab, fb);
+              for (int l = 1; l < p.limbs; l++)
+                tma_load_3d(dst + kWTiles * kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
+            }
           }
-          if (KIND == 5) {
-            mbar_expect_tx(fb, q_bytes + kRaw8TileBytes);
-            tma_load_2d(dst + kPTileBytes - kRaw8TileBytes, &map_w, 0, (tn * p.num_kb + kb) * 32, fb);  // 8 KB int8 tile, in
-                                                                                                      // the upper half of the f16 tile
-          } else if (KIND == 2) {
-            mbar_expect_tx(fb, q_bytes + kRawTileBytes);
-            tma_load_2d(dst + kPTileBytes + q_bytes, &map_w, 0, (tn * p.num_kb + kb) * 16, fb);  // 4 KB nibble tile
-          } else {
-            mbar_expect_tx(fb, stage_bytes);
-            tma_load_2d(dst, &map_w, 0, wrow, fb);
-            if (KIND == 4) tma_load_2d(dst + kPTileBytes, &map_w, 0, wrow + p.w_lo_rows, fb);  // residue plane
+          fb += 8u;
+          dst += stage_bytes;
+          const bool wrap = fb == fb_end;
+          fb = wrap ? bars : fb;
+          dst = wrap ? smem_base : dst;
+          ph ^= wrap ? 1u : 0u;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (kTwoProd && warp == 2 + kEpiWarps) {
+    // ---- second producer: the activation tiles of every chunk.  It walks the ring exactly like warp 0 and lands its
+    // bytes on the same full barrier; warp 0's expect_tx announces the whole stage, and bytes that arrive before that
+    // announcement are simply counted early (the phase cannot complete before warp 0's arrival). ----
+    if (lane == 0) {
+      const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
+      uint32_t fb = bars, dst = smem_base + kWTiles * kPTileBytes, ph = 0;
+      const uint32_t dst0 = dst;
+      bool stop = false;
+      for (int tile = blockIdx.x; tile < num_tiles && !stop; tile += gridDim.x) {
+        const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
+        const int tm = tin / p.tiles_n;
+        int aslab = (p.a_shared ? 0 : batch) * p.limbs * p.num_kb + kb0;
+        const int m0 = tm * p.MT;
+        const int wh = tile == 0 ? p.withhold_kb : -1;
+        for (int kb = kb0; kb < kb1; kb++, aslab++) {
+          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {
+            set_abort(7, kb);
+            stop = true;
+            break;
           }
-          tma_load_3d(dst + kWTiles * kPTileBytes, &map_a, 0, m0, aslab, fb);
-          for (int l = 1; l < p.limbs; l++)
-            tma_load_3d(dst + kWTiles * kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
-          if (++s == nst) {
-            s = 0;
-            ph ^= 1u;
+          if (kb != wh) {
+            tma_load_3d(dst, &map_a, 0, m0, aslab, fb);
+            for (int l = 1; l < p.limbs; l++)
+              tma_load_3d(dst + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
           }
+          fb += 8u;
+          dst += stage_bytes;
+          const bool wrap = fb == fb_end;
+          fb = wrap ? bars : fb;
+          dst = wrap ? dst0 : dst;
+          ph ^= wrap ? 1u : 0u;
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---- MMA issuer: alternates between the two TMEM accumulator buffers -----------------------
+    // Per K chunk: one poll of the slot's full barrier, four MMAs (eight with a second plane), one commit, and a
+    // branch-free step round the ring.  The loop exists twice (with and without the residue plane of the
+    // activations) so that choice is not a branch per chunk.
     if (lane == 0) {
       const uint32_t idesc = make_idesc(MK, 128, acc_cols);
-      const uint32_t nst = (uint32_t)p.stages;
       const uint64_t desc0 = smem_desc_sw128(smem_base);  // slot 0 weights tile; other tiles are address offsets
-      const uint64_t q_off = (uint64_t)((kWTiles * kPTileBytes) >> 4), st_off = (uint64_t)(stage_bytes >> 4);
-      const uint64_t wlo_off = (uint64_t)(kPTileBytes >> 4);  // KIND 4: residue plane of the weights
-      const uint64_t lo_off = (uint64_t)((p.MT * kRowBytes) >> 4);  // residue plane of the activations
-      uint32_t s = 0, ph = 0, it = 0, lt = 0;
+      const uint32_t d_hi = (uint32_t)(desc0 >> 32), da0 = (uint32_t)desc0;
+      const uint32_t q_off = (kWTiles * kPTileBytes) >> 4, st_off = stage_bytes >> 4;
+      const uint32_t wlo_off = kPTileBytes >> 4;                    // KIND 4: residue plane of the weights
+      const uint32_t lo_off = (uint32_t)(p.MT * kRowBytes) >> 4;    // residue plane of the activations
+      const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
+      const uint32_t doff = (2u * (uint32_t)p.stages + 4u) * 8u;    // full barrier -> unpack barrier of the slot
+      uint32_t fb = bars, da = da0, ph = 0, lt = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
-        const uint32_t buf = lt & 1, use = lt >> 1;
-        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit)) {
-          set_abort(4, tile);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * acc_stride;
-        for (int kb = kb0; kb < kb1; kb++, it++) {
-          const uint32_t fb = bars + s * 8u;
-          if (!mbar_wait(fb, ph, p.wait_limit)) {
-            set_abort(2, kb);
-            ok = false;
-            break;
-          }
-          if (kDeq && !mbar_wait(fb + (2u * nst + 4u) * 8u, ph, p.wait_limit)) {  // weights tile unpacked
-            set_abort(6, kb);
-            ok = false;
+      auto run = [&](auto ls_tag) {
+        constexpr bool kLimbSum = decltype(ls_tag)::value;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
+          const uint32_t buf = lt & 1, use = lt >> 1;
+          if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit)) {
+            set_abort(4, tile);
             break;
           }
           tc_fence_after();
-          const uint64_t da = desc0 + (uint64_t)s * st_off, db = da + q_off;
-          umma<MK>(d_tmem, da, db, idesc, kb > kb0 ? 1u : 0u);  // 4 x 32 bytes of K per slot
-          umma<MK>(d_tmem, da + 2, db + 2, idesc, 1u);
-          umma<MK>(d_tmem, da + 4, db + 4, idesc, 1u);
-          umma<MK>(d_tmem, da + 6, db + 6, idesc, 1u);
-          if (p.limb_sum) {
-            umma<MK>(d_tmem, da, db + lo_off, idesc, 1u);
-            umma<MK>(d_tmem, da + 2, db + lo_off + 2, idesc, 1u);
-            umma<MK>(d_tmem, da + 4, db + lo_off + 4, idesc, 1u);
-            umma<MK>(d_tmem, da + 6, db + lo_off + 6, idesc, 1u);
+          const uint32_t d_tmem = tmem_base + buf * acc_stride;
+          uint32_t acc = 0;
+          for (int kb = kb0; kb < kb1; kb++) {
+            if (!mbar_wait(fb, ph, p.wait_limit)) {
+              set_abort(2, kb);
+              ok = false;
+              break;
+            }
+            if (kDeq) {
+              if (!mbar_wait(fb + doff, ph, p.wait_limit)) {  // weights tile unpacked
+                set_abort(6, kb);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            const uint32_t db = da + q_off;
+            umma_lo<MK>(d_tmem, da, db, d_hi, idesc, acc);  // 4 x 32 bytes of K per slot
+            acc = 1u;
+            umma_lo<MK>(d_tmem, da + 2, db + 2, d_hi, idesc, 1u);
+            umma_lo<MK>(d_tmem, da + 4, db + 4, d_hi, idesc, 1u);
+            umma_lo<MK>(d_tmem, da + 6, db + 6, d_hi, idesc, 1u);
+            if (kLimbSum) {
+              umma_lo<MK>(d_tmem, da, db + lo_off, d_hi, idesc, 1u);
+              umma_lo<MK>(d_tmem, da + 2, db + lo_off + 2, d_hi, idesc, 1u);
+              umma_lo<MK>(d_tmem, da + 4, db + lo_off + 4, d_hi, idesc, 1u);
+              umma_lo<MK>(d_tmem, da + 6, db + lo_off + 6, d_hi, idesc, 1u);
+            }
+            if (KIND == 4) {  // weights' residue x activations' value
+              umma_lo<MK>(d_tmem, da + wlo_off, db, d_hi, idesc, 1u);
+              umma_lo<MK>(d_tmem, da + wlo_off + 2, db + 2, d_hi, idesc, 1u);
+              umma_lo<MK>(d_tmem, da + wlo_off + 4, db + 4, d_hi, idesc, 1u);
+              umma_lo<MK>(d_tmem, da + wlo_off + 6, db + 6, d_hi, idesc, 1u);
+            }
+            umma_commit(fb + eoff);  // frees the slot when these MMAs have read it
+            fb += 8u;
+            da += st_off;
+            const bool wrap = fb == fb_end;
+            fb = wrap ? bars : fb;
+            da = wrap ? da0 : da;
+            ph ^= wrap ? 1u : 0u;
           }
-          if (KIND == 4) {  // weights' residue x activations' value
-            umma<MK>(d_tmem, da + wlo_off, db, idesc, 1u);
-            umma<MK>(d_tmem, da + wlo_off + 2, db + 2, idesc, 1u);
-            umma<MK>(d_tmem, da + wlo_off + 4, db + 4, idesc, 1u);
-            umma<MK>(d_tmem, da + wlo_off + 6, db + 6, idesc, 1u);
-          }
-          umma_commit(fb + nst * 8u);  // frees the slot when these MMAs have read it
-          if (++s == nst) {
-            s = 0;
-            ph ^= 1u;
-          }
+          if (ok) umma_commit(acc_full(buf));  // this tile's accumulators are complete
         }
-        if (ok) umma_commit(acc_full(buf));  // this tile's accumulators are complete
-      }
+      };
+      if (p.limb_sum) run(std::true_type{}); else run(std::false_type{});
     }
     __syncwarp();
   } else if (KIND == 5 && warp >= 2 + kEpiWarps && (warp & 2) == 0) {
@@ -881,6 +941,220 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ---- CTA pairs: the f16 product for shapes with many tiles -----------------------------------------------------
+// What bounds the one-CTA kernel above at large M is the SM's shared-memory bandwidth: every operand byte is written
+// once by the copy engine and read once by the tensor core, and a 128 x 256 tile moves 2 x 48 KB per K chunk
+// through a ~128 B/clk port while its four MMAs need 512 clocks (measured: 650 clocks per chunk with nothing else
+// running, 770-840 with the epilogue's slab traffic beside it, the same on 16 busy SMs as on 148).  Here two CTAs of a
+// cluster share one 256-lane MMA (cta_group::2): the pair's tile is 256 output columns x MT rows, each CTA loads its
+// own 128 weight rows and HALF of the activation rows (2 x 32 KB per chunk), the hardware feeds both tensor cores
+// from the two halves, and each CTA finds its 128 columns x all MT rows in its own TMEM - so its epilogue is the
+// one-CTA epilogue unchanged.  Barriers: `full` lives in the leader (even) CTA and counts the bytes of both CTAs'
+// loads; `empty` and `acc_full` exist in both CTAs and are signalled together by the leader's tcgen05.commit;
+// `acc_empty` lives in the leader and collects the epilogue warps of both CTAs.  No load is delivered to more than
+// one CTA.
+__global__ void __launch_bounds__(kThreads, 1)
+k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+               const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_o16, const TcParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int half_rows = p.MT / 2;  // activation rows this CTA stages
+  const uint32_t stage_bytes = kPTileBytes + (uint32_t)half_rows * kRowBytes;
+  const uint32_t bars = smem_base + (uint32_t)p.stages * stage_bytes;
+  auto acc_full = [&](int b) { return bars + (uint32_t)(2 * p.stages + b) * 8u; };
+  auto acc_empty = [&](int b) { return bars + (uint32_t)(2 * p.stages + 2 + b) * 8u; };
+  const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4) * 8u;
+  const uint32_t abort_flag = tmem_slot + 4u;
+  const uint32_t slabs = (tmem_slot + 16u + 127u) & ~127u;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  uint32_t acc_stride = 32;
+  while ((int)acc_stride < p.MT) acc_stride <<= 1;
+  const uint32_t tmem_cols = 2 * acc_stride;
+  const int tiles_n2 = p.tiles_n / 2;  // tiles_n is even in this mode
+  const int num_tiles = tiles_n2 * p.tiles_m;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; s++) {
+      mbar_init(bars + (uint32_t)s * 8u, 1);               // full (used in the leader)
+      mbar_init(bars + (uint32_t)(p.stages + s) * 8u, 1);  // empty
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 2 * kEpiWarps);  // both CTAs' epilogue warps arrive on the leader's barrier
+    }
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(0u) : "memory");
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_a);
+    if (p.tma_out) {
+      if (!p.skip_f32) tma_prefetch_desc(&map_o);
+      if (p.out16) tma_prefetch_desc(&map_o16);
+    }
+  }
+  if (warp == 1) tmem_alloc2(tmem_slot, tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+  fa_grid_dep_sync();
+
+  auto aborted = [&]() {
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(abort_flag) : "memory");
+    return v != 0;
+  };
+  auto set_abort = [&](int code, int detail) {
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(1u) : "memory");
+    report_timeout(p.status, code, detail);
+  };
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs): own weights tile; the leader announces the bytes of the whole pair ----
+    if (lane == 0) {
+      const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
+      uint32_t fb = bars, dst = smem_base, ph = 0;
+      bool stop = false;
+      for (int tile = pair; tile < num_tiles && !stop; tile += npairs) {
+        const int tn2 = tile % tiles_n2;
+        int wrow = (tn2 * 2 + (int)rank) * p.num_kb * 128;
+        for (int kb = 0; kb < p.num_kb; kb++, wrow += 128) {
+          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {
+            set_abort(11, kb);
+            stop = true;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(fb, 2 * stage_bytes);  // the bytes of both CTAs land on this barrier
+          tma_load_2d_pair(dst, &map_w, 0, wrow, fb);
+          fb += 8u;
+          dst += stage_bytes;
+          const bool wrap = fb == fb_end;
+          fb = wrap ? bars : fb;
+          dst = wrap ? smem_base : dst;
+          ph ^= wrap ? 1u : 0u;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2 + kEpiWarps) {
+    // ---- second producer (both CTAs): own half of the activation rows (one thread sustains only one tile load per
+    // ~300-400 clocks, see kThreads) ----
+    if (lane == 0) {
+      const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
+      uint32_t fb = bars, dst = smem_base + kPTileBytes, ph = 0;
+      bool stop = false;
+      for (int tile = pair; tile < num_tiles && !stop; tile += npairs) {
+        const int tm = tile / tiles_n2;
+        const int arow = tm * p.MT + (int)rank * half_rows;
+        for (int kb = 0; kb < p.num_kb; kb++) {
+          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {
+            set_abort(15, kb);
+            stop = true;
+            break;
+          }
+          tma_load_3d_pair(dst, &map_a, 0, arow, kb, fb);
+          fb += 8u;
+          dst += stage_bytes;
+          const bool wrap = fb == fb_end;
+          fb = wrap ? bars : fb;
+          dst = wrap ? smem_base + kPTileBytes : dst;
+          ph ^= wrap ? 1u : 0u;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---- MMA issuer (leader only) ----
+    if (rank == 0 && lane == 0) {
+      const uint32_t idesc = make_idesc(0, 256, p.MT);
+      const uint64_t desc0 = smem_desc_sw128(smem_base);
+      const uint32_t d_hi = (uint32_t)(desc0 >> 32), da0 = (uint32_t)desc0;
+      const uint32_t q_off = kPTileBytes >> 4, st_off = stage_bytes >> 4;
+      const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
+      uint32_t fb = bars, da = da0, ph = 0, lt = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
+        const uint32_t buf = lt & 1, use = lt >> 1;
+        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit)) {
+          set_abort(14, tile);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * acc_stride;
+        uint32_t acc = 0;
+        for (int kb = 0; kb < p.num_kb; kb++) {
+          if (!mbar_wait(fb, ph, p.wait_limit)) {
+            set_abort(12, kb);
+            ok = false;
+            break;
+          }
+          const uint32_t db = da + q_off;
+          umma2_f16_lo(d_tmem, da, db, d_hi, idesc, acc);
+          acc = 1u;
+          umma2_f16_lo(d_tmem, da + 2, db + 2, d_hi, idesc, 1u);
+          umma2_f16_lo(d_tmem, da + 4, db + 4, d_hi, idesc, 1u);
+          umma2_f16_lo(d_tmem, da + 6, db + 6, d_hi, idesc, 1u);
+          umma_commit_pair(fb + eoff);
+          fb += 8u;
+          da += st_off;
+          const bool wrap = fb == fb_end;
+          fb = wrap ? bars : fb;
+          da = wrap ? da0 : da;
+          ph ^= wrap ? 1u : 0u;
+        }
+        if (ok) umma_commit_pair(acc_full(buf));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---- epilogue (both CTAs): this CTA's 128 output columns x all MT rows of the pair's tile ----
+    const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
+    uint32_t lt = 0, slab_turn = 0;
+    const uint32_t slab_f32 = slabs + (uint32_t)ew * 4096u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)ew * 2048u;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
+      const int tn2 = tile % tiles_n2, tm = tile / tiles_n2;
+      const int n0 = (tn2 * 2 + (int)rank) * 128, m0 = tm * p.MT;
+      const uint32_t buf = lt & 1, use = lt >> 1;
+      ok = mbar_wait(acc_full(buf), use & 1, p.wait_limit);
+      if (!ok && lane == 0) set_abort(13, tile);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !aborted();
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
+      if (!p.rowscale && !p.rowbias)
+        epilogue_tile_fast<false>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, &map_o, &map_o16, slab_f32, slab_f16,
+                                  slab_turn);
+      else
+        epilogue_tile<0, false>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, 0u, &map_o, &map_o16, slab_f32,
+                                slab_f16, slab_turn, 0u);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(acc_empty(buf), 0);
+    }
+    if (p.tma_out && lane == 0) tma_store_wait_all();
+    __syncwarp();
+  }
+
+  // ---- teardown: neither CTA leaves while the other may still read its shared memory or TMEM ----
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (aborted()) {
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, tmem_cols);
   }
 }
 
@@ -1248,7 +1522,27 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     }
     num_tiles = p.tiles_n * p.tiles_m * p.batches;
   }
-  const size_t stage_bytes =
+  // Many tiles: CTA pairs (see k_tc_gemm_pair).  Row tile by the same rule as above over half as many workers,
+  // with a per-tile constant for the ramp of a tile's first loads.
+  bool pair = false;
+  if (KIND == 0 && ctx->tc_pair && limbs == 1 && p.batches == 1 && p.splitk == 1 && ep.n_peers == 0 && !raw_i32 && (N & 255) == 0 &&
+      M >= 512 && num_tiles > ctx->sm_count && ctx->sm_count >= 2) {
+    pair = true;
+    const int npairs = ctx->sm_count / 2;
+    long long best = -1;
+    for (int cand = 256; cand >= 128; cand -= 16) {
+      const long long tiles = (long long)(p.tiles_n / 2) * ceil_div(M, cand);
+      const long long cost = ((tiles + npairs - 1) / npairs) * (cand + 24);
+      if (best < 0 || cost < best) {
+        best = cost;
+        p.MT = cand;
+      }
+    }
+    if (ctx->tc_tile_rows >= 128 && ctx->tc_tile_rows <= 256) p.MT = ctx->tc_tile_rows / 16 * 16;
+    p.tiles_m = ceil_div(M, p.MT);
+    num_tiles = (p.tiles_n / 2) * p.tiles_m;  // pair tiles
+  }
+  const size_t stage_bytes = pair ? (size_t)kPTileBytes + (size_t)(p.MT / 2) * kRowBytes :
       (size_t)(KIND == 4 ? 2 : 1) * kPTileBytes + (size_t)p.MT * limbs * kRowBytes + (size_t)tc_raw_bytes<KIND>();
   p.w_lo_rows = KIND == 4 ? p.tiles_n * p.num_kb * 128 : 0;
   // Results through shared-memory slabs and TMA stores: plain products only (see epilogue_tile), and only where the
@@ -1264,7 +1558,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
       (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.splitk * p.split_rb * 16 * 128 * 4 : 0) + slab_bytes + 1024;
   int stages = (int)((227 * 1024 - tail_bytes) / stage_bytes);
   if (stages > 12) stages = 12;
-  const int kb_per_cta = p.kb_per_split * ceil_div(num_tiles, p.splitk > 1 ? num_tiles : ctx->sm_count);
+  const int kb_per_cta = p.kb_per_split * ceil_div(num_tiles, p.splitk > 1 ? num_tiles : (pair ? ctx->sm_count / 2 : ctx->sm_count));
   if (stages > kb_per_cta) stages = kb_per_cta;
   if (stages < 1) stages = 1;
   p.stages = stages;
@@ -1294,13 +1588,12 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     FA_TRY(tc::make_tmap_rows128(ctx, &map_w, w_packed, elem, (KIND == 4 ? 2 : 1) * w_batches * p.tiles_n * p.num_kb * 128, 0, 128));
   // activations: [limbs * num_kb] slabs of M rows of 128 bytes, boxes of MT rows (rows >= M read as zero)
   FA_TRY(tc::make_tmap_rows128(ctx, &map_a, a_packed, elem, (uint64_t)M,
-                               (uint64_t)(p.a_shared ? 1 : p.batches) * limbs * p.num_kb, (uint32_t)p.MT));
+                               (uint64_t)(p.a_shared ? 1 : p.batches) * limbs * p.num_kb, (uint32_t)(pair ? p.MT / 2 : p.MT)));
   CUtensorMap map_o = map_w, map_o16 = map_w;  // placeholders when unused (never dereferenced then)
   if (p.tma_out) {
     if (!p.skip_f32) FA_TRY(tc::make_tmap_out_f32(ctx, &map_o, (const float *)out, (uint64_t)M, (uint64_t)N, (uint64_t)p.ldc));
     if (p.out16) FA_TRY(tc::make_tmap_out_f16_packed(ctx, &map_o16, p.out16, (uint64_t)p.o16_rows, (uint64_t)(N >> 6)));
   }
-  FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[2];
   cfg.blockDim = dim3(tc_threads<KIND>());
@@ -1310,6 +1603,24 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (pair) {
+    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    const int npairs = ctx->sm_count / 2;
+    cfg.gridDim = dim3(2 * (num_tiles < npairs ? num_tiles : npairs));
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    {
+      LaunchScope ls(ctx, "tc_gemm_f16_pair");
+      cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm_pair, map_w, map_a, map_o, map_o16, p);
+      if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm_pair: %s", cudaGetErrorString(e));
+    }
+    FA_LAUNCH_CHECK(ctx, "tc_gemm_pair");
+    return FA_OK;
+  }
+  FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tc_gemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   if (p.splitk > 1) {
     cfg.gridDim = dim3(num_tiles, 1, p.splitk);
     attr[1].id = cudaLaunchAttributeClusterDimension;
