@@ -248,7 +248,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
     if (!PEERS && p.tma_out) {
       const uint32_t b = slab_turn & 1u;
       slab_turn++;
-      if (lane == 0) tma_store_wait_read<1>();  // the group that used slab b two blocks ago has read it
+      tma_store_wait_read<1>();  // lane 0: the group that used slab b two blocks ago has read it (the other lanes own no groups)
       __syncwarp();
       if (p.out16) {
         const uint32_t dst = slab_f16 + b * 1024u + (uint32_t)lane * 2u;
@@ -265,10 +265,11 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
       }
       fence_proxy_async_smem();  // the copy engine reads the slab through the async proxy
       __syncwarp();
-      if (lane == 0) {
+      {
+        const uint32_t lead = lane == 0 ? 1u : 0u;
         const int gn = n0 + quad * 32 + c16;
-        if (p.out16) tma_store_3d(map_o16, slab_f16 + b * 1024u, gn & 63, r16 + m0 + c, gn >> 6);
-        if (!p.skip_f32) tma_store_2d(map_o, slab_f32 + b * 2048u, n0 + quad * 32, m0 + c);
+        if (p.out16) tma_store_3d_w(lead, map_o16, slab_f16 + b * 1024u, gn & 63, r16 + m0 + c, gn >> 6);
+        if (!p.skip_f32) tma_store_2d_w(lead, map_o, slab_f32 + b * 2048u, n0 + quad * 32, m0 + c);
         tma_store_commit();
       }
       continue;
@@ -349,7 +350,7 @@ __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t l
     if (!PEERS && p.tma_out) {
       const uint32_t b = slab_turn & 1u;
       slab_turn++;
-      if (lane == 0) tma_store_wait_read<1>();  // the group that used slab b two blocks ago has read it
+      tma_store_wait_read<1>();  // lane 0: the group that used slab b two blocks ago has read it (the other lanes own no groups)
       __syncwarp();
       if (p.out16) {
         const uint32_t dst = slab_f16 + b * 1024u + (uint32_t)lane * 2u;
@@ -364,10 +365,11 @@ __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t l
       }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
+      {
+        const uint32_t lead = lane == 0 ? 1u : 0u;
         const int gn = n0 + quad * 32 + c16;
-        if (p.out16) tma_store_3d(map_o16, slab_f16 + b * 1024u, gn & 63, r16 + m0 + cc, gn >> 6);
-        if (!p.skip_f32) tma_store_2d(map_o, slab_f32 + b * 2048u, n0 + quad * 32, m0 + cc);
+        if (p.out16) tma_store_3d_w(lead, map_o16, slab_f16 + b * 1024u, gn & 63, r16 + m0 + cc, gn >> 6);
+        if (!p.skip_f32) tma_store_2d_w(lead, map_o, slab_f32 + b * 2048u, n0 + quad * 32, m0 + cc);
         tma_store_commit();
       }
       return;
@@ -522,7 +524,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     // Ring position as running values (barrier address, slot address, parity) advanced without a branch; the wait on
     // a slot's empty barrier uses the opposite parity of its full barrier, which a freshly initialised barrier
     // passes at once, so the first trip round the ring needs no special case.
-    if (lane == 0) {
+    {
+      const uint32_t lead = elect_lead();
       const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
       uint32_t fb = bars, dst = smem_base, ph = 0;
       bool stop = false;
@@ -535,28 +538,28 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const int m0 = tm * p.MT;
         const int wh = tile == 0 ? p.withhold_kb : -1;  // test hook: this chunk never arrives
         for (int kb = kb0; kb < kb1; kb++, wrow += 128, aslab++) {
-          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {  // empty barrier of the slot, previous use
-            set_abort(1, kb);
+          if (!__all_sync(0xffffffffu, mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit))) {  // empty barrier of the slot, previous use
+            if (lane == 0) set_abort(1, kb);
             stop = true;
             break;
           }
           if (kb != wh) {
             if (KIND == 5) {
-              mbar_expect_tx(fb, q_bytes + kRaw8TileBytes);
-              tma_load_2d(dst + kPTileBytes - kRaw8TileBytes, &map_w, 0, (tn * p.num_kb + kb) * 32, fb);  // 8 KB int8 tile, in
+              mbar_expect_tx_w(lead, fb, q_bytes + kRaw8TileBytes);
+              tma_load_2d_w(lead, dst + kPTileBytes - kRaw8TileBytes, &map_w, 0, (tn * p.num_kb + kb) * 32, fb);  // 8 KB int8 tile, in
                                                                                                         // the upper half of the f16 tile
             } else if (KIND == 2) {
-              mbar_expect_tx(fb, q_bytes + kRawTileBytes);
-              tma_load_2d(dst + kPTileBytes + q_bytes, &map_w, 0, (tn * p.num_kb + kb) * 16, fb);  // 4 KB nibble tile
+              mbar_expect_tx_w(lead, fb, q_bytes + kRawTileBytes);
+              tma_load_2d_w(lead, dst + kPTileBytes + q_bytes, &map_w, 0, (tn * p.num_kb + kb) * 16, fb);  // 4 KB nibble tile
             } else {
-              mbar_expect_tx(fb, stage_bytes);
-              tma_load_2d(dst, &map_w, 0, wrow, fb);
-              if (KIND == 4) tma_load_2d(dst + kPTileBytes, &map_w, 0, wrow + p.w_lo_rows, fb);  // residue plane
+              mbar_expect_tx_w(lead, fb, stage_bytes);
+              tma_load_2d_w(lead, dst, &map_w, 0, wrow, fb);
+              if (KIND == 4) tma_load_2d_w(lead, dst + kPTileBytes, &map_w, 0, wrow + p.w_lo_rows, fb);  // residue plane
             }
             if (!kTwoProd) {
-              tma_load_3d(dst + kWTiles * kPTileBytes, &map_a, 0, m0, aslab, fb);
+              tma_load_3d_w(lead, dst + kWTiles * kPTileBytes, &map_a, 0, m0, aslab, fb);
               for (int l = 1; l < p.limbs; l++)
-                tma_load_3d(dst + kWTiles * kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
+                tma_load_3d_w(lead, dst + kWTiles * kPTileBytes + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
             }
           }
           fb += 8u;
@@ -573,7 +576,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     // ---- second producer: the activation tiles of every chunk.  It walks the ring exactly like warp 0 and lands its
     // bytes on the same full barrier; warp 0's expect_tx announces the whole stage, and bytes that arrive before that
     // announcement are simply counted early (the phase cannot complete before warp 0's arrival). ----
-    if (lane == 0) {
+    {
+      const uint32_t lead = elect_lead();
       const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
       uint32_t fb = bars, dst = smem_base + kWTiles * kPTileBytes, ph = 0;
       const uint32_t dst0 = dst;
@@ -585,15 +589,15 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const int m0 = tm * p.MT;
         const int wh = tile == 0 ? p.withhold_kb : -1;
         for (int kb = kb0; kb < kb1; kb++, aslab++) {
-          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {
-            set_abort(7, kb);
+          if (!__all_sync(0xffffffffu, mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit))) {
+            if (lane == 0) set_abort(7, kb);
             stop = true;
             break;
           }
           if (kb != wh) {
-            tma_load_3d(dst, &map_a, 0, m0, aslab, fb);
+            tma_load_3d_w(lead, dst, &map_a, 0, m0, aslab, fb);
             for (int l = 1; l < p.limbs; l++)
-              tma_load_3d(dst + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
+              tma_load_3d_w(lead, dst + (uint32_t)(l * p.MT) * kRowBytes, &map_a, 0, m0, aslab + l * p.num_kb, fb);
           }
           fb += 8u;
           dst += stage_bytes;
@@ -610,7 +614,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     // Per K chunk: one poll of the slot's full barrier, four MMAs (eight with a second plane), one commit, and a
     // branch-free step round the ring.  The loop exists twice (with and without the residue plane of the
     // activations) so that choice is not a branch per chunk.
-    if (lane == 0) {
+    {
+      const uint32_t lead = elect_lead();
       const uint32_t idesc = make_idesc(MK, 128, acc_cols);
       const uint64_t desc0 = smem_desc_sw128(smem_base);  // slot 0 weights tile; other tiles are address offsets
       const uint32_t d_hi = (uint32_t)(desc0 >> 32), da0 = (uint32_t)desc0;
@@ -625,46 +630,46 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         constexpr bool kLimbSum = decltype(ls_tag)::value;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
           const uint32_t buf = lt & 1, use = lt >> 1;
-          if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit)) {
-            set_abort(4, tile);
+          if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit))) {
+            if (lane == 0) set_abort(4, tile);
             break;
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * acc_stride;
           uint32_t acc = 0;
           for (int kb = kb0; kb < kb1; kb++) {
-            if (!mbar_wait(fb, ph, p.wait_limit)) {
-              set_abort(2, kb);
+            if (!__all_sync(0xffffffffu, mbar_wait(fb, ph, p.wait_limit))) {
+              if (lane == 0) set_abort(2, kb);
               ok = false;
               break;
             }
             if (kDeq) {
-              if (!mbar_wait(fb + doff, ph, p.wait_limit)) {  // weights tile unpacked
-                set_abort(6, kb);
+              if (!__all_sync(0xffffffffu, mbar_wait(fb + doff, ph, p.wait_limit))) {  // weights tile unpacked
+                if (lane == 0) set_abort(6, kb);
                 ok = false;
                 break;
               }
               tc_fence_after();
             }
             const uint32_t db = da + q_off;
-            umma_lo<MK>(d_tmem, da, db, d_hi, idesc, acc);  // 4 x 32 bytes of K per slot
+            umma_lo_w<MK>(lead, d_tmem, da, db, d_hi, idesc, acc);  // 4 x 32 bytes of K per slot
             acc = 1u;
-            umma_lo<MK>(d_tmem, da + 2, db + 2, d_hi, idesc, 1u);
-            umma_lo<MK>(d_tmem, da + 4, db + 4, d_hi, idesc, 1u);
-            umma_lo<MK>(d_tmem, da + 6, db + 6, d_hi, idesc, 1u);
+            umma_lo_w<MK>(lead, d_tmem, da + 2, db + 2, d_hi, idesc, 1u);
+            umma_lo_w<MK>(lead, d_tmem, da + 4, db + 4, d_hi, idesc, 1u);
+            umma_lo_w<MK>(lead, d_tmem, da + 6, db + 6, d_hi, idesc, 1u);
             if (kLimbSum) {
-              umma_lo<MK>(d_tmem, da, db + lo_off, d_hi, idesc, 1u);
-              umma_lo<MK>(d_tmem, da + 2, db + lo_off + 2, d_hi, idesc, 1u);
-              umma_lo<MK>(d_tmem, da + 4, db + lo_off + 4, d_hi, idesc, 1u);
-              umma_lo<MK>(d_tmem, da + 6, db + lo_off + 6, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da, db + lo_off, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da + 2, db + lo_off + 2, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da + 4, db + lo_off + 4, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da + 6, db + lo_off + 6, d_hi, idesc, 1u);
             }
             if (KIND == 4) {  // weights' residue x activations' value
-              umma_lo<MK>(d_tmem, da + wlo_off, db, d_hi, idesc, 1u);
-              umma_lo<MK>(d_tmem, da + wlo_off + 2, db + 2, d_hi, idesc, 1u);
-              umma_lo<MK>(d_tmem, da + wlo_off + 4, db + 4, d_hi, idesc, 1u);
-              umma_lo<MK>(d_tmem, da + wlo_off + 6, db + 6, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da + wlo_off, db, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da + wlo_off + 2, db + 2, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da + wlo_off + 4, db + 4, d_hi, idesc, 1u);
+              umma_lo_w<MK>(lead, d_tmem, da + wlo_off + 6, db + 6, d_hi, idesc, 1u);
             }
-            umma_commit(fb + eoff);  // frees the slot when these MMAs have read it
+            umma_commit_w(lead, fb + eoff);  // frees the slot when these MMAs have read it
             fb += 8u;
             da += st_off;
             const bool wrap = fb == fb_end;
@@ -672,7 +677,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             da = wrap ? da0 : da;
             ph ^= wrap ? 1u : 0u;
           }
-          if (ok) umma_commit(acc_full(buf));  // this tile's accumulators are complete
+          if (ok) umma_commit_w(lead, acc_full(buf));  // this tile's accumulators are complete
         }
       };
       if (p.limb_sum) run(std::true_type{}); else run(std::false_type{});
@@ -1019,7 +1024,8 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == 0) {
     // ---- TMA producer (both CTAs): own weights tile; the leader announces the bytes of the whole pair ----
-    if (lane == 0) {
+    {
+      const uint32_t lead = elect_lead();
       const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
       uint32_t fb = bars, dst = smem_base, ph = 0;
       bool stop = false;
@@ -1027,13 +1033,13 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int tn2 = tile % tiles_n2;
         int wrow = (tn2 * 2 + (int)rank) * p.num_kb * 128;
         for (int kb = 0; kb < p.num_kb; kb++, wrow += 128) {
-          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {
-            set_abort(11, kb);
+          if (!__all_sync(0xffffffffu, mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit))) {
+            if (lane == 0) set_abort(11, kb);
             stop = true;
             break;
           }
-          if (rank == 0) mbar_expect_tx(fb, 2 * stage_bytes);  // the bytes of both CTAs land on this barrier
-          tma_load_2d_pair(dst, &map_w, 0, wrow, fb);
+          mbar_expect_tx_w(rank == 0 ? lead : 0u, fb, 2 * stage_bytes);  // the bytes of both CTAs land on this barrier
+          tma_load_2d_pair_w(lead, dst, &map_w, 0, wrow, fb);
           fb += 8u;
           dst += stage_bytes;
           const bool wrap = fb == fb_end;
@@ -1047,7 +1053,8 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else if (warp == 2 + kEpiWarps) {
     // ---- second producer (both CTAs): own half of the activation rows (one thread sustains only one tile load per
     // ~300-400 clocks, see kThreads) ----
-    if (lane == 0) {
+    {
+      const uint32_t lead = elect_lead();
       const uint32_t fb_end = bars + (uint32_t)p.stages * 8u, eoff = (uint32_t)p.stages * 8u;
       uint32_t fb = bars, dst = smem_base + kPTileBytes, ph = 0;
       bool stop = false;
@@ -1055,12 +1062,12 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int tm = tile / tiles_n2;
         const int arow = tm * p.MT + (int)rank * half_rows;
         for (int kb = 0; kb < p.num_kb; kb++) {
-          if (!mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit)) {
-            set_abort(15, kb);
+          if (!__all_sync(0xffffffffu, mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit))) {
+            if (lane == 0) set_abort(15, kb);
             stop = true;
             break;
           }
-          tma_load_3d_pair(dst, &map_a, 0, arow, kb, fb);
+          tma_load_3d_pair_w(lead, dst, &map_a, 0, arow, kb, fb);
           fb += 8u;
           dst += stage_bytes;
           const bool wrap = fb == fb_end;
@@ -1072,8 +1079,9 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ---- MMA issuer (leader only) ----
-    if (rank == 0 && lane == 0) {
+    // ---- MMA issuer (leader CTA only): the whole warp walks the ring, one elected lane issues ----
+    if (rank == 0) {
+      const uint32_t lead = elect_lead();
       const uint32_t idesc = make_idesc(0, 256, p.MT);
       const uint64_t desc0 = smem_desc_sw128(smem_base);
       const uint32_t d_hi = (uint32_t)(desc0 >> 32), da0 = (uint32_t)desc0;
@@ -1083,26 +1091,26 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
         const uint32_t buf = lt & 1, use = lt >> 1;
-        if (use > 0 && !mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit)) {
-          set_abort(14, tile);
+        if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(acc_empty(buf), (use - 1) & 1, p.wait_limit))) {
+          if (lane == 0) set_abort(14, tile);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * acc_stride;
         uint32_t acc = 0;
         for (int kb = 0; kb < p.num_kb; kb++) {
-          if (!mbar_wait(fb, ph, p.wait_limit)) {
-            set_abort(12, kb);
+          if (!__all_sync(0xffffffffu, mbar_wait(fb, ph, p.wait_limit))) {
+            if (lane == 0) set_abort(12, kb);
             ok = false;
             break;
           }
           const uint32_t db = da + q_off;
-          umma2_f16_lo(d_tmem, da, db, d_hi, idesc, acc);
+          umma2_f16_lo_w(lead, d_tmem, da, db, d_hi, idesc, acc);
           acc = 1u;
-          umma2_f16_lo(d_tmem, da + 2, db + 2, d_hi, idesc, 1u);
-          umma2_f16_lo(d_tmem, da + 4, db + 4, d_hi, idesc, 1u);
-          umma2_f16_lo(d_tmem, da + 6, db + 6, d_hi, idesc, 1u);
-          umma_commit_pair(fb + eoff);
+          umma2_f16_lo_w(lead, d_tmem, da + 2, db + 2, d_hi, idesc, 1u);
+          umma2_f16_lo_w(lead, d_tmem, da + 4, db + 4, d_hi, idesc, 1u);
+          umma2_f16_lo_w(lead, d_tmem, da + 6, db + 6, d_hi, idesc, 1u);
+          umma_commit_pair_w(lead, fb + eoff);
           fb += 8u;
           da += st_off;
           const bool wrap = fb == fb_end;
@@ -1110,7 +1118,7 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           da = wrap ? da0 : da;
           ph ^= wrap ? 1u : 0u;
         }
-        if (ok) umma_commit_pair(acc_full(buf));
+        if (ok) umma_commit_pair_w(lead, acc_full(buf));
       }
     }
     __syncwarp();

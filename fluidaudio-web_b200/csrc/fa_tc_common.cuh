@@ -85,6 +85,17 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t sr
                "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+// Whole-warp forms of the stores (see elect_lead): every lane executes the call, the lane with `lead` != 0 issues.
+__device__ __forceinline__ void tma_store_2d_w(uint32_t lead, const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t@q cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n\t}" ::"l"(map),
+               "r"(src), "r"(x), "r"(y), "r"(lead)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d_w(uint32_t lead, const CUtensorMap *map, uint32_t src, int x, int y, int z) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t@q cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];\n\t}" ::"l"(map),
+               "r"(src), "r"(x), "r"(y), "r"(z), "r"(lead)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until all but the newest `N` store groups of this thread have finished READING shared memory.
 template <int N>
@@ -202,6 +213,92 @@ __device__ __forceinline__ void umma2_f16_lo(uint32_t d_tmem, uint32_t a_lo, uin
       "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
       "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Whole-warp forms: every lane executes the call with the same (warp-uniform) operands and `lead` is non-zero in
+// exactly one lane, which alone issues the instruction.  With the loop around them free of divergent branches the
+// compiler can keep descriptors, barrier addresses and coordinates in the uniform datapath these instructions take
+// their operands from, instead of moving them there from one lane's registers before every issue.
+__device__ __forceinline__ uint32_t elect_lead() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void mbar_expect_tx_w(uint32_t lead, uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes),
+               "r"(lead)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_w(uint32_t lead, uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(x), "r"(y), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_w(uint32_t lead, uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n\t}" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_w(uint32_t lead, uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}" ::"r"(dst),
+      "l"(map), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_w(uint32_t lead, uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n\t}" ::"r"(dst),
+      "l"(map), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "r"(z), "r"(lead)
+      : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void umma_lo_w(uint32_t lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if (KIND == 2) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, %6, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(lead)
+        : "memory");
+  } else if (KIND == 0) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, %6, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(lead)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, %6, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(lead)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void umma_commit_w(uint32_t lead, uint32_t bar) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar),
+               "r"(lead)
+               : "memory");
+}
+__device__ __forceinline__ void umma2_f16_lo_w(uint32_t lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, %6, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair_w(uint32_t lead, uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}" ::"r"(bar),
+      "h"(mask), "r"(lead)
       : "memory");
 }
 // Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far have
