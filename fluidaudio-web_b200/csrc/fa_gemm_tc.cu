@@ -345,8 +345,10 @@ __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t l
 #pragma unroll
     for (int j = 0; j < 16; j++) v[j] = fmaf(__uint_as_float(vr[j]), cs, bs);
     act16(v, p.act);
+    if (has_add) {
 #pragma unroll
-    for (int j = 0; j < 16; j++) v[j] += ad[j];
+      for (int j = 0; j < 16; j++) v[j] += ad[j];
+    }
     if (!PEERS && p.tma_out) {
       const uint32_t b = slab_turn & 1u;
       slab_turn++;
