@@ -1066,6 +1066,32 @@ def shapes_report(ctx, peaks, timer, quick=False):
             ctx.freeTensor(act)
             for w in ws:
                 ctx.freeTensor(w)
+
+    # ---- layernorm on the encoder's residual stream (32 windows x 188 frames x 1024, seed 3) ------------------------
+    # HBM-bound glue between the products: f32 rows in, the packed f16 operand of the next product out (and the f32
+    # rows as well for the block-final form).  Inputs rotate through more than L2, which is the harsher case: inside
+    # the encoder step the input was written by the kernel before and is still in L2.
+    if not quick:
+        rng = np.random.default_rng(3)
+        M, D = 32 * 188, 1024
+        nx = max(2, -(-l2x2 // (M * D * 4)))
+        xs = [ctx.upload(rng.standard_normal((M, D)).astype(np.float32), M, D) for _ in range(nx)]
+        g = ctx.upload(rng.standard_normal(D).astype(np.float32), 1, D)
+        b = ctx.upload(rng.standard_normal(D).astype(np.float32), 1, D)
+        for label, fn, nbytes in (("layernorm (f32 rows + packed f16 operand out)", ctx.layernorm, M * D * (4 + 4 + 2)),
+                                  ("layernormOperand (packed f16 operand out only)", ctx.layernormOperand, M * D * (4 + 2))):
+            def body_ln(fn=fn):
+                h = ctx.pushArena()
+                for x in xs:
+                    fn(x, g, b, 1e-5)
+                ctx.popArena(h)
+
+            us = time_products(body_ln, nx, 10)
+            record("encoder_glue", f"rows={M} cols={D}", "k_layernorm_warp: " + label, us, nbytes, 8.0 * M * D, tf, {"input_sets": nx})
+        for x in xs:
+            ctx.freeTensor(x)
+        ctx.freeTensor(g)
+        ctx.freeTensor(b)
     return out
 
 
