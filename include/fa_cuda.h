@@ -74,10 +74,14 @@ const char *fa_last_error(fa_ctx *ctx);
  * its f32 storage is filled from that, f16-rounded, the first time anything else reads it; the same holds for
  * the results of layernormOperand, gluDwConvTimeMajor and attnFused), "attn_one_kernel" (0/1, default 1:
  * attnFused runs as one kernel per call when head width is 128 and T <= 192; 0 = the batched-GEMM form),
- * "tc_tile_rows" / "tc_split_k" (0 = automatic, the default; otherwise rows per tile and CTAs per K-split cluster
- * of tensor-core products with less than one wave of tiles) and "gemv_ctas_per_sm" (1..4, default 2: resident
- * thread blocks per SM the int4 GEMV sizes its grid for) are tuning overrides of choices the library makes by
- * shape, "wait_limit" (4096..2^28, default 2^24, about a second: polls after which a device-side barrier wait gives
+ * "tc_pair" (0/1, default 1: f16-weight products with more tiles than SMs run on pairs of thread blocks that
+ * share one 256-lane tcgen05 MMA, each loading half of the activation rows of the pair's tile; results are
+ * bit-identical to the one-block kernel, 0 selects that kernel), "tc_tma_store" (0/1, default 1: results of plain
+ * tensor-core products leave through shared-memory slabs and copy-engine stores; 0 = per-lane stores, same values),
+ * "tc_tile_rows" / "tc_split_k" (0 = automatic, the default; otherwise rows per tile - 128..256 for a pair's tile -
+ * and CTAs per K-split cluster of tensor-core products with less than one wave of tiles) and "gemv_ctas_per_sm"
+ * (1..4, default 2: resident thread blocks per SM the int4 GEMV sizes its grid for) are tuning overrides of choices
+ * the library makes by shape, "wait_limit" (4096..2^28, default 2^24, about a second: polls after which a device-side barrier wait gives
  * up; the kernel then records a status word, unwinds and returns, and the next fa_sync fails with
  * FA_ERR_TIMEOUT while the context stays usable), "tc_test_withhold_chunk" (-1 = off; k >= 0: test hook for that
  * path - in the NEXT tensor-core product only, one thread block never loads K chunk k of its first tile, so
