@@ -458,3 +458,51 @@ def test_int8_resident_weights_f16_activations_vs_oracle(ctx, M, K, N, opts):
     if add is not None:
         ref = ref + add[rows]
     assert np.abs(got[rows] - ref).max() <= 2e-2
+
+
+# ---- CTA pairs (tcgen05 cta_group::2) ---------------------------------------------------------------
+
+PAIR_CASES = [
+    (1200, 256, 512, dict()),                                    # 8 x 5 tiles: barely more tiles than SMs
+    (2500, 320, 1024, dict(bias=True)),                          # ragged M (last tile 196 of 224 rows), ragged K chunk
+    (3000, 1024, 768, dict(bias=True, act="silu", operand_only=True)),  # f16 operand out only
+    (2111, 512, 1280, dict(bias=True, add=True)),                # residual read, odd row count
+]
+
+
+@pytest.mark.parametrize("M,K,N,kw", PAIR_CASES, ids=[f"{c[0]}x{c[1]}x{c[2]}" for c in PAIR_CASES])
+def test_pair_kernel_matches_one_cta_kernel_and_oracle(ctx, M, K, N, kw):
+    """Products with more tiles than SMs run on pairs of thread blocks sharing one 256-lane MMA (option "tc_pair",
+    default on).  The pair kernel accumulates the same K chunks in the same order into the same accumulators as the
+    one-block kernel, so the two must agree bit for bit; a sample of rows is also checked against the oracle."""
+    rng = np.random.default_rng(M + N)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32) if kw.get("bias") else None
+    r = rng.standard_normal((M, N)).astype(np.float32) if kw.get("add") else None
+    outs = []
+    try:
+        for pair in (1, 0):
+            ctx.setOption("tc_pair", pair)
+            h = ctx.pushArena()
+            try:
+                opts = dict(act=kw.get("act", "none"))
+                if b is not None:
+                    opts["bias"] = ctx.upload(b, 1, N)
+                if r is not None:
+                    opts["add"] = ctx.upload(r, M, N)
+                if kw.get("operand_only"):
+                    opts["operandOnly"] = True
+                wt = ctx.uploadF16(w, K, N)
+                outs.append(ctx.download(ctx.matmul(ctx.upload(a, M, K), wt, opts)).reshape(M, N).copy())
+                ctx.freeTensor(wt)
+            finally:
+                ctx.popArena(h)
+    finally:
+        ctx.setOption("tc_pair", 1)
+    assert np.array_equal(outs[0], outs[1])
+    rows = np.unique(np.concatenate([[0, 1, M - 2, M - 1], rng.integers(0, M, 28)]))
+    ora = WasmOracle(threads=True)
+    ref = ora.matmul(T(a[rows], len(rows), K), T(w, K, N), bias=T(b, 1, N) if b is not None else None, act=kw.get("act", "none"),
+                     add=T(r[rows], len(rows), N) if r is not None else None).array()
+    assert float(np.abs(outs[0][rows] - ref).max()) <= 2e-2
