@@ -1034,14 +1034,17 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int tile = pair; tile < num_tiles && !stop; tile += npairs) {
         const int tn2 = tile % tiles_n2;
         int wrow = (tn2 * 2 + (int)rank) * p.num_kb * 128;
+        const int wh = (tile == pair && blockIdx.x == 0) ? p.withhold_kb : -1;  // test hook: the leader of pair 0 never
+                                                                                // announces this chunk of its first tile
         for (int kb = 0; kb < p.num_kb; kb++, wrow += 128) {
           if (!__all_sync(0xffffffffu, mbar_wait(fb + eoff, ph ^ 1u, p.wait_limit))) {
             if (lane == 0) set_abort(11, kb);
             stop = true;
             break;
           }
-          mbar_expect_tx_w(rank == 0 ? lead : 0u, fb, 2 * stage_bytes);  // the bytes of both CTAs land on this barrier
-          tma_load_2d_pair_w(lead, dst, &map_w, 0, wrow, fb);
+          const uint32_t go = kb != wh ? lead : 0u;
+          mbar_expect_tx_w(rank == 0 ? go : 0u, fb, 2 * stage_bytes);  // the bytes of both CTAs land on this barrier
+          tma_load_2d_pair_w(go, dst, &map_w, 0, wrow, fb);
           fb += 8u;
           dst += stage_bytes;
           const bool wrap = fb == fb_end;

@@ -41,6 +41,35 @@ def test_bounded_wait_runs_out_and_context_survives(pkg):
         ctx.destroy()
 
 
+def test_bounded_wait_runs_out_in_the_pair_kernel(pkg):
+    """The same for a product large enough to run on pairs of thread blocks (two CTAs of a cluster sharing one MMA):
+    the leader of pair 0 never announces K chunk 2 of its first tile, every role of both CTAs gives up on its own
+    bounded wait, both leave through the cluster barrier, and the context keeps working."""
+    ctx = pkg.CudaContext(0)
+    try:
+        rng = np.random.default_rng(6)
+        M, K, N = 6016, 256, 1024
+        a = rng.standard_normal((M, K)).astype(np.float32)
+        w = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
+        A, Wt = ctx.upload(a, M, K), ctx.uploadF16(w, K, N)
+        good = ctx.download(ctx.matmul(A, Wt)).reshape(M, N)
+        rows = np.arange(0, M, 97)
+        ref = WasmOracle(threads=True).matmul(T(a[rows], len(rows), K), T(w, K, N)).array()
+        assert np.abs(good[rows] - ref).max() <= 2e-2
+        ctx.setOption("wait_limit", 20000)
+        ctx.setOption("tc_test_withhold_chunk", 2)
+        ctx.matmul(A, Wt)
+        with pytest.raises(pkg.CudaError) as ei:
+            ctx.sync()
+        assert ei.value.code == 5 and "bounded wait ran out" in str(ei.value)  # FA_ERR_TIMEOUT
+        ctx.setOption("wait_limit", 1 << 24)
+        again = ctx.download(ctx.matmul(A, Wt)).reshape(M, N)
+        assert np.array_equal(again, good)
+        ctx.sync()
+    finally:
+        ctx.destroy()
+
+
 def test_first_use_of_a_weight_inside_a_recording_is_refused(pkg):
     """The packed tensor-core copy of a weight is built on first use.  Inside a recording that step would only be
     captured while the handle already looked ready, and an eager product before the first replay would read
