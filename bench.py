@@ -775,6 +775,65 @@ class TdtDecode:
         return n * 15.0 / dt, f"{n} windows x {self.T} frames on the C restatement of rust/parakeet-decoder ({dt:.2f} s)"
 
 
+class AsrPipeline(Encoder):
+    """The reference's transcription pipeline for one batch of windows (src/engines/asr-parakeet/pipeline.js:32-61):
+    16 kHz samples -> log-mel front end -> FastConformer encoder -> the joint's encoder projection riding the same
+    submission (1024 -> 640) -> greedy TDT decoding of the 32 windows in lock step -> token ids and emission frames on
+    the host.  Everything between the upload of the samples and the read-back of the ids stays on the device.  Weights
+    random-init (encoder seed 3, decoder seed 5 with a bias on the blank logit so that most frames emit nothing)."""
+
+    name = "parakeet_asr_pipeline_pcm_to_token_ids_batch32"
+    metric = "asr_pipeline_audio_seconds_per_second"
+    graph = False  # the decode reads a device counter back every few rounds: eager steps
+
+    def setup(self, ctx):
+        super().setup(ctx)
+        from fluidaudio_web_b200.engines import tdt_decoder
+
+        self.tdt_weights = tdt_decoder.synth_tdt_weights(5)
+        self.dec = tdt_decoder.TdtDecoder(ctx, self.tdt_weights, int8=True)
+        self.dtype = "encoder: f16 x f16 -> f32; joint: int8 out-matrix x 3 int8 activation digits"
+        self.pcm_host = self._pcm_slot(ctx)
+        self.tokens = 0
+
+    def _decode(self, ctx, mels):
+        x, tsub = self.fc.encode_batch(ctx, self.enc, mels)
+        out = self.dec.decode_proj(self.dec.project(x), self.W, tsub)
+        self.tokens = sum(len(i) for i, _ in out)
+        return out
+
+    def step_device(self, ctx):
+        h = ctx.pushArena()
+        self._decode(ctx, self.dev_mels)
+        ctx.popArena(h)
+
+    def step_e2e(self, ctx):
+        h = ctx.pushArena()
+        pcm = ctx.upload(self.pcm_host, self.W, self.n_samples)
+        out = self._decode(ctx, ctx.logMelWindows(pcm, 128))
+        ctx.popArena(h)
+        return out
+
+    def e2e_drain(self):
+        return []
+
+    def e2e_bytes(self):
+        return self.W * self.n_samples * 4, 2 * 4 * max(1, self.tokens) + 4 * self.W
+
+    def cpu_sample(self, threads=True):
+        from oracle.tdt_oracle import TdtOracle, synth_tdt_weights
+
+        v_enc, d_enc = super().cpu_sample(threads=threads)
+        n = 8 if threads else 2
+        ora = TdtOracle(getattr(self, "tdt_weights", None) or synth_tdt_weights(5), int8=True,
+                        threads=(os.cpu_count() or 1) if threads else 1)
+        proj = np.random.default_rng(6).standard_normal((n, 188, 640)).astype(np.float32)
+        t0 = time.perf_counter()
+        ora.decode_proj_batch(proj, n, 188)
+        v_dec = n * 15.0 / (time.perf_counter() - t0)
+        return 1.0 / (1.0 / v_enc + 1.0 / v_dec), f"encoder: {d_enc}; decoder: {n} windows x 188 frames on the C restatement of rust/parakeet-decoder"
+
+
 class F16GemmNSharded:
     """Benchmark configuration 3, its multi-GPU leg: the M = 16384 row of the f16 GEMM sweep with the output columns
     sharded over the ranks (each GPU holds N/world columns of every weight matrix) and an NCCL all-gather of
@@ -941,7 +1000,7 @@ def config4_sharded(ctx, wl, world, rank, local_rank):
 
 
 WORKLOADS = {"int4_decode": Int4Decode, "int8_gemm": Int8Gemm, "f16_gemm": F16Gemm, "encoder": Encoder,
-             "decoder": Decoder, "decoder_int8": DecoderInt8, "f16_gemm_nsharded": F16GemmNSharded, "tdt_decode": TdtDecode}
+             "decoder": Decoder, "decoder_int8": DecoderInt8, "f16_gemm_nsharded": F16GemmNSharded, "tdt_decode": TdtDecode, "asr_pipeline": AsrPipeline}
 DEFAULT_WORKLOAD = "encoder"
 
 
@@ -1242,7 +1301,7 @@ def run_cuda(args):
     h2d, d2h = wl.e2e_bytes()
 
     cfg4 = None
-    if isinstance(wl, Encoder) and not args.quick:
+    if type(wl) is Encoder and not args.quick:
         cfg4 = config4_sharded(ctx, wl, world, rank, local_rank)
 
     shapes = None

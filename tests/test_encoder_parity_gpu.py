@@ -108,6 +108,54 @@ def test_pipelined_encoder_returns_each_batch_in_order(ctx, pkg):
         ctx2.destroy()
 
 
+def test_pipelined_encoder_post_op_rides_the_batch(ctx, pkg):
+    """The `post` hook of PipelinedEncoder (the joint's encoder projection that the reference appends to the encoder's
+    submission, src/engines/asr-parakeet/pipeline.js:57-61): what is read back is post(frames), identical to applying
+    the same product to encode_batch's frames, and only its bytes cross to the host."""
+    fc, synth = _eng()
+    w = synth.encoder_weights(synth.TINY, seed=3)
+    dev = ctx.device
+    ctx, ctx2 = pkg.CudaContext(dev), pkg.CudaContext(dev)
+    try:
+        encs = [fc.load_encoder(ctx, w), fc.load_encoder(ctx2, w)]
+        audio = synth.synth_audio(4, samples=16000 * 2, seed=5)
+        mels = [fc.mel_time_major(synth.log_mel(a, 32).reshape(-1), 32) for a in audio]
+        n = mels[0].size
+        D = synth.TINY["D"]
+        rng = np.random.default_rng(9)
+        pw = (rng.standard_normal((D, 24)) / np.sqrt(D)).astype(np.float32)
+        pb = rng.standard_normal(24).astype(np.float32)
+        proj = [(c.uploadF16(pw, D, 24), c.upload(pb, 1, 24)) for c in (ctx, ctx2)]
+        host = [[c.pinnedArray(n) for _ in range(2)] for c in (ctx, ctx2)]
+        for bufs in host:
+            for b, m in zip(bufs, mels[:2]):
+                b[:] = m
+        cs = (ctx, ctx2)
+        pipe = fc.PipelinedEncoder([ctx, ctx2], encs, lambda s: host[s], n,
+                                   post=lambda s, x: cs[s].matmul(x, proj[s][0], dict(bias=proj[s][1])))
+        want, got = [], []
+        for step in range(2):
+            pair = mels[2 * step:2 * step + 2]
+            for b, m in zip(host[step % 2], pair):
+                b[:] = m
+            h = ctx.pushArena()
+            ref, _ = fc.encode_batch(ctx, encs[0], [ctx.upload(m, 1, n) for m in pair])
+            want.append(ctx.download(ctx.matmul(ref, proj[0][0], dict(bias=proj[0][1]))))
+            ctx.popArena(h)
+            r = pipe.submit()
+            if r is not None:
+                got.append(r.copy())
+        got += pipe.flush()
+        pipe.free()
+        assert len(got) == 2
+        for g, r in zip(got, want):
+            assert g.size == r.size and g.size % 24 == 0
+            assert np.array_equal(g, r)
+    finally:
+        ctx.destroy()
+        ctx2.destroy()
+
+
 def test_int8_artifact_loader_resident_weights(ctx, pkg):
     """The encoder loaded from the int8 artifact (blob + manifest written by the restated quantiser) with the
     matrices kept int8 on the device: one full-width block, teacher-forced, against the oracle running the
