@@ -29,8 +29,10 @@ DECODER_WASM = "src/engines/asr-parakeet/parakeet-decoder.wasm"
 
 
 def reference_root():
-    """Directory of the reference checkout, or None when this machine has none."""
-    for cand in (os.environ.get("FA_REFERENCE_ROOT"), "/root/reference"):
+    """Directory of the reference checkout - $FA_REFERENCE_ROOT, else a `reference` directory beside this repository -
+    or None when this machine has none."""
+    beside = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+    for cand in (os.environ.get("FA_REFERENCE_ROOT"), beside):
         if cand and os.path.exists(os.path.join(cand, KERNELS_WASM)):
             return cand
     return None
