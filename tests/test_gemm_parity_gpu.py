@@ -467,6 +467,8 @@ PAIR_CASES = [
     (2500, 320, 1024, dict(bias=True)),                          # ragged M (last tile 196 of 224 rows), ragged K chunk
     (3000, 1024, 768, dict(bias=True, act="silu", operand_only=True)),  # f16 operand out only
     (2111, 512, 1280, dict(bias=True, add=True)),                # residual read, odd row count
+    (19001, 64, 256, dict(bias=True)),                           # one K chunk per tile, one column pair, ragged last tile
+    (4097, 96, 512, dict(act="relu")),                           # K not a multiple of the 64-element chunk
 ]
 
 
