@@ -153,6 +153,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->gemv_ctas_per_sm = (int)value;
     return FA_OK;
   }
+  if (!strcmp(key, "nbits_mma_rows")) {
+    if (value < 0 || value > 17) return fa_fail(ctx, FA_ERR_INVALID, "option nbits_mma_rows: %lld (0..16, 17 = up to 16 rows whatever N)", value);
+    ctx->nbits_mma_rows = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "tc_pair")) {
     ctx->tc_pair = value != 0;
     return FA_OK;

@@ -450,6 +450,206 @@ int fa_gemv_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *s
   }
 }
 
+// ---- int4, 5..16 activation rows: weights streamed once as uploaded, dequantised in registers, mma.sync -------------
+// The tensor-core GEMM serves these shapes from a dequantised f16 copy of the weights (4x the bytes of the 4-bit
+// matrix) and pays cluster set-up, a packing prepass and a split-K hand-off for ~0.5 GFLOP of work.  Here a CTA owns
+// groups of 8 output columns; its 16 warps split the K blocks of a group between them (a warp takes 4 consecutive
+// 32-weight blocks, one per lane of a column's 4-lane group, as ONE 16-byte load per lane, so the 4 lanes of a column
+// read 64 consecutive bytes), widens its nibbles to f16 with (q - zp) * scale, and multiplies them as the B fragment
+// of mma.sync.m16n8k16 against all (up to 16) activation rows at once; partial sums of the 16 warps meet in shared
+// memory.  Which K index sits in which of the instruction's 16 k-slots does not matter for a sum, so a lane uses the
+// nibbles in the order one mask extracts them (k, k+4 of every group of 8), and the activation rows are stored in
+// shared memory in that same order (f16 value plane and, optionally, the rounding-residue plane that keeps f32-grade
+// activations) with a row pitch and block pitch that make the A-fragment loads conflict-free.
+constexpr int kMmaWarps = 16;
+constexpr int kMmaBatch = 4;   // column groups whose partial tiles are reduced together (one pair of block barriers)
+constexpr int kMmaSeg = 80;    // bytes per 32-k block of an activation row in shared memory (64 + 16: the 4 lanes of a
+                               // column group read blocks b..b+3 of a row at 16-byte bank groups 0, 5, 2, 7)
+__host__ __device__ constexpr int mma_row_pitch(int nblk) { return nblk * kMmaSeg + (((nblk * kMmaSeg / 16) % 8) == 4 ? 0 : ((4 - (nblk * kMmaSeg / 16) % 8 + 8) % 8) * 16); }
+
+__device__ __forceinline__ void mma16816_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool HILO>
+__global__ void __launch_bounds__(kMmaWarps * 32, 1) k_nbits_mma(const float *__restrict__ a, const uint8_t *__restrict__ bq,
+                                                                  const float *__restrict__ scales, const uint8_t *__restrict__ zp,
+                                                                  float *__restrict__ y, int M, int N, int K, int nblk, int zpb) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int pitch = mma_row_pitch(nblk);
+  unsigned char *planes = smem;                                         // [HILO ? 2 : 1][16][pitch]
+  float *red = (float *)(smem + (size_t)(HILO ? 2 : 1) * 16 * pitch);   // [kMmaBatch][kMmaWarps][32][4]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int groups = N >> 3, quads = (nblk + 3) >> 2;
+  const uint4 *bq4 = (const uint4 *)bq;
+  constexpr int D = kMmaBatch;  // column groups whose weights are requested ahead: slot gi of the registers below always
+                                // serves the gi-th group of a batch, so a value still in flight is never moved
+
+  // requests of this warp's first quad of the first D column groups (weights do not depend on earlier kernels)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  uint4 pw[D];
+  float psc[D];
+  unsigned pzb[D];
+#pragma unroll
+  for (int d = 0; d < D; d++) {
+    const int cg = blockIdx.x + d * gridDim.x, b = 4 * warp + t;
+    const bool ok = cg < groups && b < nblk;
+    const size_t n = (size_t)(cg * 8 + g);
+    pw[d] = ok ? __ldcs(bq4 + n * nblk + b) : make_uint4(0u, 0u, 0u, 0u);
+    psc[d] = ok ? __ldg(scales + n * nblk + b) : 0.f;
+    pzb[d] = ok ? (unsigned)__ldg(zp + n * zpb + (b >> 1)) : 0u;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- activation rows -> f16 planes, 8 consecutive k per thread, stored k0,k4,k1,k5,k2,k6,k3,k7 ----
+  const int words = nblk * 4;
+  unsigned any_residue = 0u;
+  const bool avec = (K & 7) == 0 && ((uintptr_t)a & 15) == 0;  // rows start 16-byte aligned: two float4 per word
+  for (int e = tid; e < 16 * words; e += kMmaWarps * 32) {
+    const int m = e / words, w = e - m * words, k0 = w * 8;
+    float x[8];
+    if (avec && m < M && k0 + 8 <= K) {
+      const float4 x0 = __ldg((const float4 *)(a + (size_t)m * K + k0)), x1 = __ldg((const float4 *)(a + (size_t)m * K + k0 + 4));
+      x[0] = x0.x, x[1] = x0.y, x[2] = x0.z, x[3] = x0.w, x[4] = x1.x, x[5] = x1.y, x[6] = x1.z, x[7] = x1.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) x[i] = (m < M && k0 + i < K) ? __ldg(a + (size_t)m * K + k0 + i) : 0.f;
+    }
+    __half2 h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      h[i] = __floats2half2_rn(x[i], x[i + 4]);
+      const float2 f = __half22float2(h[i]);
+      l[i] = __floats2half2_rn(x[i] - f.x, x[i + 4] - f.y);
+    }
+    unsigned char *dst = planes + (size_t)m * pitch + (w >> 2) * kMmaSeg + (w & 3) * 16;
+    *(uint4 *)dst = make_uint4(*(uint32_t *)&h[0], *(uint32_t *)&h[1], *(uint32_t *)&h[2], *(uint32_t *)&h[3]);
+    if (HILO) {
+      const uint4 lv = make_uint4(*(uint32_t *)&l[0], *(uint32_t *)&l[1], *(uint32_t *)&l[2], *(uint32_t *)&l[3]);
+      *(uint4 *)(dst + (size_t)16 * pitch) = lv;
+      any_residue |= (lv.x | lv.y | lv.z | lv.w) & 0x7FFF7FFFu;
+    }
+  }
+  // rows that are exactly representable in f16 (activations that arrive as f16 values) have an all-zero residue
+  // plane: its products are skipped for the whole launch
+  const bool use_residue = HILO && __syncthreads_or(any_residue != 0u);
+  if (!HILO) __syncthreads();
+
+  for (int cg0 = blockIdx.x; cg0 < groups; cg0 += kMmaBatch * gridDim.x) {
+    float c[kMmaBatch][4];
+#pragma unroll
+    for (int gi = 0; gi < kMmaBatch; gi++) {
+      c[gi][0] = c[gi][1] = c[gi][2] = c[gi][3] = 0.f;
+      const int cg = cg0 + gi * gridDim.x;
+      if (cg >= groups) continue;  // (block-uniform)
+      const int n = cg * 8 + g;
+      for (int q = warp; q < quads; q += kMmaWarps) {
+        const int b = 4 * q + t;
+        const bool in = b < nblk;
+        uint4 wv;
+        float sc;
+        unsigned zb;
+        if (q == warp) {
+          wv = pw[gi], sc = psc[gi], zb = pzb[gi];
+        } else {
+          wv = in ? __ldcs(bq4 + (size_t)n * nblk + b) : make_uint4(0u, 0u, 0u, 0u);
+          sc = in ? __ldg(scales + (size_t)n * nblk + b) : 0.f;
+          zb = in ? (unsigned)__ldg(zp + (size_t)n * zpb + (b >> 1)) : 0u;
+        }
+        const int z = (b & 1) ? (int)(zb >> 4) : (int)(zb & 15u);
+        const __half2 s2 = __float2half2_rn(sc), zsub = __half2half2(__int2half_rn(1024 + z));
+        const unsigned char *arow = planes + (size_t)g * pitch + (size_t)(in ? b : 0) * kMmaSeg;
+        const uint32_t wd[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; wi++) {
+          // word wi = k 8wi..8wi+7 of the block: pairs (k0,k4) (k1,k5) (k2,k6) (k3,k7)
+          uint32_t bp[4];
+#pragma unroll
+          for (int pi = 0; pi < 4; pi++) {
+            uint32_t hx = ((wd[wi] >> (4 * pi)) & 0x000F000Fu) | 0x64006400u;  // 1024 + q in both halves
+            const __half2 wq = __hmul2(__hsub2(*(__half2 *)&hx, zsub), s2);
+            bp[pi] = *(const uint32_t *)&wq;
+          }
+          const uint4 a_lo8 = *(const uint4 *)(arow + wi * 16);                        // row g:     (k0,k4)(k1,k5)(k2,k6)(k3,k7)
+          const uint4 a_hi8 = *(const uint4 *)(arow + (size_t)8 * pitch + wi * 16);    // row g + 8
+          mma16816_f16(c[gi], a_lo8.x, a_hi8.x, a_lo8.y, a_hi8.y, bp[0], bp[1]);
+          mma16816_f16(c[gi], a_lo8.z, a_hi8.z, a_lo8.w, a_hi8.w, bp[2], bp[3]);
+          if (use_residue) {
+            const uint4 r_lo8 = *(const uint4 *)(arow + (size_t)16 * pitch + wi * 16);
+            const uint4 r_hi8 = *(const uint4 *)(arow + (size_t)24 * pitch + wi * 16);
+            mma16816_f16(c[gi], r_lo8.x, r_hi8.x, r_lo8.y, r_hi8.y, bp[0], bp[1]);
+            mma16816_f16(c[gi], r_lo8.z, r_hi8.z, r_lo8.w, r_hi8.w, bp[2], bp[3]);
+          }
+        }
+      }
+      // request this warp's first quad of the same slot's group in the next batch
+      {
+        const int cgn = cg + D * gridDim.x, b = 4 * warp + t;
+        const bool ok = cgn < groups && b < nblk;
+        const size_t nn = (size_t)(cgn * 8 + g);
+        pw[gi] = ok ? __ldcs(bq4 + nn * nblk + b) : make_uint4(0u, 0u, 0u, 0u);
+        psc[gi] = ok ? __ldg(scales + nn * nblk + b) : 0.f;
+        pzb[gi] = ok ? (unsigned)__ldg(zp + nn * zpb + (b >> 1)) : 0u;
+      }
+    }
+    // the 16 warps' partial tiles of the batch meet in shared memory; every thread adds one (group, element) in warp
+    // order and stores it
+#pragma unroll
+    for (int gi = 0; gi < kMmaBatch; gi++)
+      *(float4 *)(red + (((size_t)gi * kMmaWarps + warp) * 32 + lane) * 4) = make_float4(c[gi][0], c[gi][1], c[gi][2], c[gi][3]);
+    __syncthreads();
+    {
+      const int gi = tid >> 7, ln = (tid >> 2) & 31, ci = tid & 3;  // 512 threads = 4 groups x 32 lanes x 4 elements
+      const int cg = cg0 + gi * gridDim.x;
+      if (cg < groups) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; w++) sum += red[(((size_t)gi * kMmaWarps + w) * 32 + ln) * 4 + ci];
+        const int gg = ln >> 2, tt = ln & 3;
+        const int m = gg + ((ci & 2) ? 8 : 0), col = cg * 8 + 2 * tt + (ci & 1);
+        if (m < M) y[(size_t)m * N + col] = sum;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// int4 products with up to 16 activation rows on k_nbits_mma.  hilo: the rows enter as value + residue f16 planes.
+bool fa_nbits_mma_ok(int M, int N, int K, int block_size, bool hilo) {
+  if (!(M >= 1 && M <= 16 && block_size == 32 && K >= 32 && N >= 8 && (N & 7) == 0)) return false;
+  const int nblk = (K + 31) / 32;
+  const size_t smem = (size_t)(hilo ? 2 : 1) * 16 * mma_row_pitch(nblk) + (size_t)kMmaBatch * kMmaWarps * 32 * 16;
+  return smem <= 224 * 1024;
+}
+
+// Measured at K = 2048 (recorded replays): 3.8 us + 1.15 us (1.37 with the residue plane) per column group a thread block
+// walks, against 10.5-13 us for the tensor-core GEMM on the dequantised copy whatever N is - this kernel is the faster
+// one while a block has at most five groups.
+bool fa_nbits_mma_worth(fa_ctx *ctx, int N) { return (long long)(N / 8) <= 5ll * ctx->sm_count; }
+
+int fa_nbits_mma(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y, int M, int N,
+                 int K, int nblk, int zpb, bool hilo) {
+  const size_t smem = (size_t)(hilo ? 2 : 1) * 16 * mma_row_pitch(nblk) + (size_t)kMmaBatch * kMmaWarps * 32 * 16;
+  const int groups = N / 8;
+  const dim3 grid((unsigned)(groups < ctx->sm_count ? groups : ctx->sm_count)), block(kMmaWarps * 32);
+  cudaError_t e;
+  {
+    LaunchScope ls(ctx, "nbits_mma");
+    if (hilo) {
+      FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_nbits_mma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      e = fa_launch_dep(ctx, k_nbits_mma<true>, grid, block, smem, a, bq, scales, zp, y, M, N, K, nblk, zpb);
+    } else {
+      FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_nbits_mma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      e = fa_launch_dep(ctx, k_nbits_mma<false>, grid, block, smem, a, bq, scales, zp, y, M, N, K, nblk, zpb);
+    }
+  }
+  if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch nbits_mma: %s", cudaGetErrorString(e));
+  FA_LAUNCH_CHECK(ctx, "nbits_mma");
+  return FA_OK;
+}
+
 // N-contiguous weights: one activation row only.  From two rows on, the tensor-core kernel (which shares each
 // weight tile between all rows for free) is at least as fast as this one; measured on 1280 x 1280 f16 at
 // M = 4: 10.6 us here against 7.3 us there.

@@ -117,6 +117,8 @@ struct fa_ctx {
   int attn_one_kernel = 1; // attnFused as the single mma kernel (fa_attn_rel.cu) when the shape allows, else the GEMM form
   int lazy_f32 = 1;        // hidden-layer products leave their f32 result unwritten until it is asked for
   int pdl = 1;             // programmatic dependent launch between the library's kernels (see fa_launch_dep)
+  int nbits_mma_rows = 16; // int4 products with more rows than the GEMV takes and at most this many stream the 4-bit
+                           // weights once and multiply with mma.sync (0 = off: tensor-core GEMM on the f16 copy)
   int nbits_fused = 0;     // 1: int4 products on the tensor cores unpack nibbles in shared memory (0: f16 copy, faster today)
   int gemv_rows = 4;       // products with at most this many rows run on the CUDA-core GEMV kernels (0 = never)
   int gemv_ctas_per_sm = 2;  // resident CTAs per SM the int4 GEMV sizes its grid for
@@ -347,6 +349,10 @@ int fa_tc_gemm_i8(fa_ctx *ctx, const int8_t *a_packed, int limbs, const int8_t *
 // CUDA-core products for M <= kGemvMaxRows activation rows, on the weights as uploaded (fa_gemv.cu)
 constexpr int kGemvMaxRows = 4;
 bool fa_gemv_nbits_ok(int M, int N, int K, int block_size);
+bool fa_nbits_mma_ok(int M, int N, int K, int block_size, bool hilo);
+bool fa_nbits_mma_worth(fa_ctx *ctx, int N);
+int fa_nbits_mma(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y, int M, int N,
+                 int K, int nblk, int zpb, bool hilo);
 int fa_gemv_nbits(fa_ctx *ctx, const float *a, const uint8_t *bq, const float *scales, const uint8_t *zp, float *y, int M,
                   int N, int K, int nblk, int zpb);
 bool fa_gemv_kn_ok(int M, int N, int K, bool i8);

@@ -437,6 +437,10 @@ extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, co
       rc = fa_tc_gemm_nbits(ctx, (const __half *)sa.p, side, (const float *)(side + tb), side + tb + sb, (float *)c->dptr, M,
                             N, K, nblk);
     }
+  } else if (tc_shape_ok(ctx, M, N, K) && M <= ctx->nbits_mma_rows && fa_nbits_mma_ok(M, N, K, block_size, M <= ctx->f16_hilo_rows) &&
+             (fa_nbits_mma_worth(ctx, N) || ctx->nbits_mma_rows > 16)) {
+    rc = fa_nbits_mma(ctx, ap, (const uint8_t *)bq->dptr, (const float *)scales->dptr, (const uint8_t *)zp->dptr, (float *)c->dptr,
+                      M, N, K, nblk, zpb, M <= ctx->f16_hilo_rows);
   } else if (tc_shape_ok(ctx, M, N, K)) {
     const bool cached = bq->nk_f16 && bq->f16_N == N && bq->f16_K == K && bq->f16_scales == scales->dptr &&
                         bq->f16_zp == zp->dptr;

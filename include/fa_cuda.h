@@ -74,7 +74,10 @@ const char *fa_last_error(fa_ctx *ctx);
  * its f32 storage is filled from that, f16-rounded, the first time anything else reads it; the same holds for
  * the results of layernormOperand, gluDwConvTimeMajor and attnFused), "attn_one_kernel" (0/1, default 1:
  * attnFused runs as one kernel per call when head width is 128 and T <= 192; 0 = the batched-GEMM form),
- * "tc_pair" (0/1, default 1: f16-weight products with more tiles than SMs run on pairs of thread blocks that
+ * "nbits_mma_rows" (0..17, default 16: int4 products with more activation rows than the GEMV takes and at most this
+ * many - at most 16 - stream the 4-bit weights once as uploaded, widen them to f16 in registers and multiply with
+ * mma.sync, when the matrix is narrow enough for that to beat the tensor-core GEMM on the dequantised copy; 17 = for
+ * every width; 0 = never), "tc_pair" (0/1, default 1: f16-weight products with more tiles than SMs run on pairs of thread blocks that
  * share one 256-lane tcgen05 MMA, each loading half of the activation rows of the pair's tile; results are
  * bit-identical to the one-block kernel, 0 selects that kernel), "tc_tma_store" (0/1, default 1: results of plain
  * tensor-core products leave through shared-memory slabs and copy-engine stores; 0 = per-lane stores, same values),

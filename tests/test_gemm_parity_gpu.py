@@ -185,6 +185,40 @@ def test_int4_partial_block_and_random_zero_points(ctx):
         assert np.abs(y - ref).max() <= 2e-2, (M, K, N)
 
 
+MMA_CASES = [(5, 2048, 2048, 64), (8, 100, 64, 64), (16, 2048, 8192, 64), (13, 1000, 328, 64), (16, 4352, 1024, 0),
+             (2, 2048, 2048, 64), (16, 64, 8, 64)]
+
+
+@pytest.mark.parametrize("M,K,N,hilo_rows", MMA_CASES, ids=[f"{c[0]}x{c[1]}x{c[2]}-{c[3]}" for c in MMA_CASES])
+def test_int4_few_rows_streamed_nibbles_mma(ctx, M, K, N, hilo_rows):
+    """int4 products with up to 16 activation rows stream the 4-bit weights once and multiply with mma.sync
+    (option "nbits_mma_rows"): partial last block, unsigned random zero-points, more than 64 blocks per row (a warp
+    then walks two quads), with and without the residue plane of the activations - against the oracle, and against
+    the tensor-core GEMM on the dequantised copy (option off)."""
+    rng = np.random.default_rng(M * 7 + N)
+    a, bq, scales, zp = _int4_case(rng, M, K, N, signed_zp=False)
+    a = (a + rng.standard_normal(a.shape).astype(np.float32) * 1e-3).astype(np.float32)  # not f16-representable
+    ora = WasmOracle(threads=True)
+    ref = ora.matmulNBits(T(a, M, K), ora.uploadBytes(bq), T(scales, 1, scales.size), ora.uploadBytes(zp), N).array()
+    ctx.setOption("f16_hilo_rows", hilo_rows)
+    outs = []
+    try:
+        for rows in (17, 0):  # 17: this kernel whatever N is (by default only while a thread block walks few column groups)
+            ctx.setOption("nbits_mma_rows", rows)
+            ctx.setOption("gemv_rows", 0 if M <= 4 else 4)  # route the few-row cases here, not to the dp4a GEMV
+            h = ctx.pushArena()
+            y = ctx.download(ctx.matmulNBits(ctx.upload(a, M, K), ctx.uploadBytes(bq), ctx.upload(scales, 1, scales.size),
+                                             ctx.uploadBytes(zp), N)).reshape(M, N)
+            ctx.popArena(h)
+            outs.append(y)
+    finally:
+        ctx.setOption("nbits_mma_rows", 16)
+        ctx.setOption("gemv_rows", 4)
+        ctx.setOption("f16_hilo_rows", 64)
+    assert np.abs(outs[0] - ref).max() <= 2e-2, float(np.abs(outs[0] - ref).max())
+    assert np.abs(outs[0] - outs[1]).max() <= 2e-2
+
+
 # ---- size-independent properties at full size ------------------------------------------------------
 
 def test_int8_full_size_linearity_and_exactness(ctx):
