@@ -16,6 +16,8 @@
 //                 waiting) adds them in slice order, so the result does not depend on scheduling.
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "fa_internal.cuh"
 
 namespace {
@@ -537,6 +539,10 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) k_nbits_mma(const float *__
   const bool use_residue = HILO && __syncthreads_or(any_residue != 0u);
   if (!HILO) __syncthreads();
 
+  // (the walk over the column groups exists twice, with and without the residue products: as a test inside the loop
+  // the compiler predicates the instructions instead of branching around them, and they keep their issue slots)
+  auto walk = [&](auto res_tag) {
+  constexpr bool kRes = decltype(res_tag)::value;
   for (int cg0 = blockIdx.x; cg0 < groups; cg0 += kMmaBatch * gridDim.x) {
     float c[kMmaBatch][4];
 #pragma unroll
@@ -559,7 +565,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) k_nbits_mma(const float *__
           zb = in ? (unsigned)__ldg(zp + (size_t)n * zpb + (b >> 1)) : 0u;
         }
         const int z = (b & 1) ? (int)(zb >> 4) : (int)(zb & 15u);
-        const __half2 s2 = __float2half2_rn(sc), zsub = __half2half2(__int2half_rn(1024 + z));
+        const __half2 s2 = __float2half2_rn(sc);
+        const uint32_t s2_u = *(const uint32_t *)&s2, zsub_u = 0x64006400u + (uint32_t)z * 0x00010001u;  // 1024 + zp, both halves
         const unsigned char *arow = planes + (size_t)g * pitch + (size_t)(in ? b : 0) * kMmaSeg;
         const uint32_t wd[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
@@ -568,15 +575,16 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) k_nbits_mma(const float *__
           uint32_t bp[4];
 #pragma unroll
           for (int pi = 0; pi < 4; pi++) {
-            uint32_t hx = ((wd[wi] >> (4 * pi)) & 0x000F000Fu) | 0x64006400u;  // 1024 + q in both halves
-            const __half2 wq = __hmul2(__hsub2(*(__half2 *)&hx, zsub), s2);
-            bp[pi] = *(const uint32_t *)&wq;
+            const uint32_t hx = ((wd[wi] >> (4 * pi)) & 0x000F000Fu) | 0x64006400u;  // 1024 + q in both halves
+            uint32_t d;
+            asm("{\n\t.reg .b32 t;\n\tsub.f16x2 t, %1, %2;\n\tmul.f16x2 %0, t, %3;\n\t}" : "=r"(d) : "r"(hx), "r"(zsub_u), "r"(s2_u));
+            bp[pi] = d;
           }
           const uint4 a_lo8 = *(const uint4 *)(arow + wi * 16);                        // row g:     (k0,k4)(k1,k5)(k2,k6)(k3,k7)
           const uint4 a_hi8 = *(const uint4 *)(arow + (size_t)8 * pitch + wi * 16);    // row g + 8
           mma16816_f16(c[gi], a_lo8.x, a_hi8.x, a_lo8.y, a_hi8.y, bp[0], bp[1]);
           mma16816_f16(c[gi], a_lo8.z, a_hi8.z, a_lo8.w, a_hi8.w, bp[2], bp[3]);
-          if (use_residue) {
+          if (kRes) {
             const uint4 r_lo8 = *(const uint4 *)(arow + (size_t)16 * pitch + wi * 16);
             const uint4 r_hi8 = *(const uint4 *)(arow + (size_t)24 * pitch + wi * 16);
             mma16816_f16(c[gi], r_lo8.x, r_hi8.x, r_lo8.y, r_hi8.y, bp[0], bp[1]);
@@ -614,6 +622,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1) k_nbits_mma(const float *__
     }
     __syncthreads();
   }
+  };
+  if (use_residue) walk(std::true_type{}); else walk(std::false_type{});
 }
 
 // int4 products with up to 16 activation rows on k_nbits_mma.  hilo: the rows enter as value + residue f16 planes.
