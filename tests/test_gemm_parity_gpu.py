@@ -518,8 +518,9 @@ def test_pair_kernel_matches_one_cta_kernel_and_oracle(ctx, M, K, N, kw):
     r = rng.standard_normal((M, N)).astype(np.float32) if kw.get("add") else None
     outs = []
     try:
-        for pair in (1, 0):
+        for pair, tma_store in ((1, 1), (0, 1), (1, 0)):  # pairs, one-block kernel, pairs with per-lane stores
             ctx.setOption("tc_pair", pair)
+            ctx.setOption("tc_tma_store", tma_store)
             h = ctx.pushArena()
             try:
                 opts = dict(act=kw.get("act", "none"))
@@ -536,7 +537,9 @@ def test_pair_kernel_matches_one_cta_kernel_and_oracle(ctx, M, K, N, kw):
                 ctx.popArena(h)
     finally:
         ctx.setOption("tc_pair", 1)
+        ctx.setOption("tc_tma_store", 1)
     assert np.array_equal(outs[0], outs[1])
+    assert np.array_equal(outs[0], outs[2])
     rows = np.unique(np.concatenate([[0, 1, M - 2, M - 1], rng.integers(0, M, 28)]))
     ora = WasmOracle(threads=True)
     ref = ora.matmul(T(a[rows], len(rows), K), T(w, K, N), bias=T(b, 1, N) if b is not None else None, act=kw.get("act", "none"),
