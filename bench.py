@@ -1092,7 +1092,10 @@ def shapes_report(ctx, peaks, timer, quick=False):
                 ctx.popArena(h)
 
             us = time_products(body_i4, nsets, 10)
-            record("int4_decode", f"M={M} K={K} N={N}", "k_gemv_nbits" if M <= 4 else "k_tc_gemm (int4 weights)", us,
+            kern = ("k_gemv_nbits (dp4a on the raw nibbles)" if M <= 4 else
+                    "k_nbits_mma (4-bit weights streamed once, mma.sync)" if N // 8 <= 5 * 148 else
+                    "k_tc_gemm<f16> on the dequantised copy of the weights")
+            record("int4_decode", f"M={M} K={K} N={N}", kern, us,
                    wbytes + 4 * M * K + 4 * M * N, 2.0 * M * N * K, tf, {"weight_sets": nsets})
             ctx.freeTensor(act)
         for bq, scl, zp in sets:
