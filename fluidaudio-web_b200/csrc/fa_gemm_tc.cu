@@ -27,8 +27,10 @@
 // f16 activations of few-row products arrive as two planes, value and rounding residue, accumulated
 // into the SAME TMEM columns (f32-grade activations where the weight stream is the cost anyway).
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..9 = epilogue (TMEM lane quadrant = warp_id % 4, two warps per quadrant).
+// Warp roles (352 threads): warp 0 = TMA producer of the weight tiles, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (TMEM lane quadrant = warp_id % 4, two warps per quadrant), warp 10 = TMA producer of the
+// activation tiles.  Shapes with more tiles than SMs run as k_tc_gemm_pair: two CTAs of a cluster share one
+// 256-lane MMA (cta_group::2) and each loads half of the activation rows of the pair's tile.
 #include <type_traits>
 
 #include "fa_tc_common.cuh"
@@ -514,13 +516,13 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     report_timeout(p.status, code, detail);
   };
 
-  // Role loops are executed by whole warps (lane 0 does the work, the shuffle keeps the other lanes in
-  // step) so that every warp reaches the block-wide barriers converged, as aligned barriers require.
-  // The two single-lane role loops below are latency-critical: one thread issues every TMA load / every
-  // MMA of the CTA, and with no other warp on its scheduler to hide behind, each extra instruction costs its
-  // full dependent-issue latency per K chunk.  So: no division, no per-chunk warp shuffle, ring position and
-  // barrier addresses kept as running values.  Lanes 1..31 wait at the __syncwarp that closes the role, which
-  // also reconverges the warp before the block-wide barriers (aligned barriers need converged warps).
+  // The role loops below are latency-critical: one warp issues every weight load, one every activation load, one
+  // every MMA of the CTA, and with little else on its scheduler to hide behind, each extra instruction or taken
+  // branch costs its full latency per K chunk (measured: the loops, not bandwidth or the tensor pipe, set the pace
+  // of the ring).  So: whole warps execute them with warp-uniform operands and ONE elected lane issues the
+  // tcgen05 / TMA instructions (the operands then stay in the uniform datapath those instructions read); no
+  // division, ring position and barrier addresses kept as running values that wrap by select, one inline poll
+  // per barrier.  The __syncwarp that closes a role reconverges the warp before the block-wide barriers.
   if (warp == 0) {
     // ---- TMA producer: runs ahead across tiles, bounded only by the ring ----------------------
     // Ring position as running values (barrier address, slot address, parity) advanced without a branch; the wait on
