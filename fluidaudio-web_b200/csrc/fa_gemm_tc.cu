@@ -312,7 +312,11 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
 // residual) overlap the arithmetic and stores of the current block instead of adding up block after block.  With
 // K = 1024 a tile's epilogue (28 blocks of 16 x 32 values per warp pair) was longer than its main loop: the warps
 // spent most of it waiting on one load at a time.
-template <bool PEERS>
+// ADD: the launch has a residual operand.  The epilogue is paced by its own instruction count (two warps per
+// scheduler, dependent chains), so the variant without a residual carries no registers, loads or adds for one:
+// +2..5 % on the products without residual.  (Fixing the result kinds and the activation at compile time as well
+// made the register allocator of the whole kernel spill and cost more than it saved.)
+template <bool PEERS, bool ADD>
 __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t lane_addr, int n0, int m0, int quad, int lane,
                                                    int half, float *outb, int r16, int c16, const CUtensorMap *map_o,
                                                    const CUtensorMap *map_o16, uint32_t slab_f32, uint32_t slab_f16,
@@ -321,35 +325,36 @@ __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t l
   const bool n_ok = n < p.N;
   const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
   const float bs = (p.bias && n_ok) ? p.bias[n] : 0.0f;
-  const bool has_add = p.add != nullptr && n_ok;
+  const bool has_add = ADD && n_ok;
   int c = half * 16;
   if (c >= p.MT || m0 + c >= p.M) return;
 
-  auto issue = [&](int cc, uint32_t (&v)[16], float (&ad)[16]) {
+  auto issue = [&](int cc, uint32_t (&v)[16], float (&ad)[ADD ? 16 : 1]) {
     tmem_ld16(lane_addr + (uint32_t)cc, v);
+    if (!ADD) return;
     if (has_add) {
       const float *arow = p.add + (size_t)(m0 + cc) * p.N + n;
       if (m0 + cc + 16 <= p.M) {
 #pragma unroll
-        for (int j = 0; j < 16; j++) ad[j] = __ldg(arow + (size_t)j * p.N);
+        for (int j = 0; j < (ADD ? 16 : 1); j++) ad[j] = __ldg(arow + (size_t)j * p.N);
       } else {
 #pragma unroll
-        for (int j = 0; j < 16; j++) ad[j] = m0 + cc + j < p.M ? __ldg(arow + (size_t)j * p.N) : 0.0f;
+        for (int j = 0; j < (ADD ? 16 : 1); j++) ad[j] = m0 + cc + j < p.M ? __ldg(arow + (size_t)j * p.N) : 0.0f;
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 16; j++) ad[j] = 0.0f;
+      for (int j = 0; j < (ADD ? 16 : 1); j++) ad[j] = 0.0f;
     }
   };
-  auto finish = [&](int cc, const uint32_t (&vr)[16], const float (&ad)[16]) {
+  auto finish = [&](int cc, const uint32_t (&vr)[16], const float (&ad)[ADD ? 16 : 1]) {
     const bool full_rows = m0 + cc + 16 <= p.M;
     float v[16];
 #pragma unroll
     for (int j = 0; j < 16; j++) v[j] = fmaf(__uint_as_float(vr[j]), cs, bs);
     act16(v, p.act);
-    if (has_add) {
+    if (ADD) {
 #pragma unroll
-      for (int j = 0; j < 16; j++) v[j] += ad[j];
+      for (int j = 0; j < 16; j++) v[j] += ad[ADD ? j : 0];
     }
     if (!PEERS && p.tma_out) {
       const uint32_t b = slab_turn & 1u;
@@ -402,7 +407,7 @@ __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t l
   };
 
   uint32_t va[16], vb[16];
-  float aa[16], ab[16];
+  float aa[ADD ? 16 : 1], ab[ADD ? 16 : 1];
   issue(c, va, aa);
   for (;;) {
     tmem_ld_wait();
@@ -871,8 +876,14 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
       if (!kDeq && MK != 1 && p.splitk == 1 && !p.rowscale && !p.rowbias)
-        epilogue_tile_fast<KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, &map_o, &map_o16, slab_f32,
-                                      slab_f16, slab_turn);
+      {
+        if (p.add)
+          epilogue_tile_fast<KIND == 3, true>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, &map_o, &map_o16, slab_f32,
+                                              slab_f16, slab_turn);
+        else
+          epilogue_tile_fast<KIND == 3, false>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, &map_o, &map_o16, slab_f32,
+                                               slab_f16, slab_turn);
+      }
       else
         epilogue_tile<MK, KIND == 3>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, partial, &map_o, &map_o16,
                                      slab_f32, slab_f16, slab_turn, cl_rank);
@@ -1145,9 +1156,12 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      if (!p.rowscale && !p.rowbias)
-        epilogue_tile_fast<false>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, &map_o, &map_o16, slab_f32, slab_f16,
-                                  slab_turn);
+      if (!p.rowscale && !p.rowbias && p.add)
+        epilogue_tile_fast<false, true>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, &map_o, &map_o16, slab_f32, slab_f16,
+                                        slab_turn);
+      else if (!p.rowscale && !p.rowbias)
+        epilogue_tile_fast<false, false>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, &map_o, &map_o16, slab_f32, slab_f16,
+                                         slab_turn);
       else
         epilogue_tile<0, false>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, 0u, &map_o, &map_o16, slab_f32,
                                 slab_f16, slab_turn, 0u);
