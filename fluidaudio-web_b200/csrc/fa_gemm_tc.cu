@@ -65,6 +65,10 @@ template <int KIND>
 __host__ __device__ constexpr int tc_threads() { return KIND == 2 ? kThreadsNbits : (KIND == 5 ? kThreadsI8W : kThreads); }
 template <int KIND>
 __host__ __device__ constexpr int tc_raw_bytes() { return KIND == 2 ? kRawTileBytes : 0; }  // (KIND 5 lands its raw tile inside the weights tile)
+constexpr int kSlabsMax = 4;                    // store slabs per epilogue warp and result kind (TcParams::nslab = 2 or 4): a
+                                                // slab is refilled only when the copy engine has read it, and the engine takes
+                                                // the stores in turn with the tile loads queued ahead of them; four are used
+                                                // when they do not cost the ring a stage (+1-2 %)
 constexpr int kSplitMaxMT = 128;               // split-K mode keeps a [MT][128] f32 partial tile in smem
 
 struct TcParams {
@@ -105,6 +109,7 @@ struct TcParams {
   int *status;
   int tma_out;          // 1: results leave through shared-memory slabs and TMA stores (see epilogue_tile)
   uint32_t slab_f16_off;  // byte offset of the f16 slabs behind the f32 slabs (0 when no f32 result is stored)
+  int nslab;              // store slabs per epilogue warp and result kind: 2 or 4
   uint32_t wait_limit;  // polls before a barrier wait gives up (fa_ctx::wait_limit)
   int withhold_kb;      // >= 0: CTA 0 never loads this K chunk of its first tile, so the waits downstream of it run
                         // out (the way the bounded-wait path is tested without faulting the GPU); -1 in normal use
@@ -248,9 +253,9 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
     for (int j = 0; j < 16; j++) v[j] = fmaf(v[j] * rs[j], cs, bs) + rb[j];
     act16(v, p.act);
     if (!PEERS && p.tma_out) {
-      const uint32_t b = slab_turn & 1u;
+      const uint32_t b = slab_turn & (uint32_t)(p.nslab - 1);
       slab_turn++;
-      tma_store_wait_read<1>();  // lane 0: the group that used slab b two blocks ago has read it (the other lanes own no groups)
+      if (p.nslab == 4) tma_store_wait_read<3>(); else tma_store_wait_read<1>();  // lane 0: the group that last used slab b has read it (the other lanes own no groups)
       __syncwarp();
       if (p.out16) {
         const uint32_t dst = slab_f16 + b * 1024u + (uint32_t)lane * 2u;
@@ -357,9 +362,9 @@ __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t l
       for (int j = 0; j < 16; j++) v[j] += ad[ADD ? j : 0];
     }
     if (!PEERS && p.tma_out) {
-      const uint32_t b = slab_turn & 1u;
+      const uint32_t b = slab_turn & (uint32_t)(p.nslab - 1);
       slab_turn++;
-      tma_store_wait_read<1>();  // lane 0: the group that used slab b two blocks ago has read it (the other lanes own no groups)
+      if (p.nslab == 4) tma_store_wait_read<3>(); else tma_store_wait_read<1>();  // lane 0: the group that last used slab b has read it (the other lanes own no groups)
       __syncwarp();
       if (p.out16) {
         const uint32_t dst = slab_f16 + b * 1024u + (uint32_t)lane * 2u;
@@ -852,7 +857,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cl_rank));
       cluster_wait_all();
     }
-    const uint32_t slab_f32 = slabs + (uint32_t)ew * 4096u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)ew * 2048u;
+    const uint32_t slab_f32 = slabs + (uint32_t)(ew * p.nslab) * 2048u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)(ew * p.nslab) * 1024u;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, lt++) {
       const int tpb = p.tiles_n * p.tiles_m, batch = tile / tpb, tin = tile - batch * tpb;
@@ -1144,7 +1149,7 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---- epilogue (both CTAs): this CTA's 128 output columns x all MT rows of the pair's tile ----
     const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
     uint32_t lt = 0, slab_turn = 0;
-    const uint32_t slab_f32 = slabs + (uint32_t)ew * 4096u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)ew * 2048u;
+    const uint32_t slab_f32 = slabs + (uint32_t)(ew * p.nslab) * 2048u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)(ew * p.nslab) * 1024u;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
       const int tn2 = tile % tiles_n2, tm = tile / tiles_n2;
@@ -1581,10 +1586,17 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
                ((uintptr_t)out & 15) == 0 && (!ep.out16 || ((uintptr_t)ep.out16 & 127) == 0) && M >= 16)
                   ? 1
                   : 0;
-  p.slab_f16_off = p.skip_f32 ? 0u : (uint32_t)kEpiWarps * 4096u;
-  const size_t slab_bytes = p.tma_out ? (size_t)p.slab_f16_off + (p.out16 ? (size_t)kEpiWarps * 2048 : 0) + 128 : 0;
-  const size_t tail_bytes =
-      (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.splitk * p.split_rb * 16 * 128 * 4 : 0) + slab_bytes + 1024;
+  // two store slabs per warp and result kind, four when that leaves the ring as deep
+  auto slab_bytes_for = [&](int nslab) {
+    const size_t f16_off = p.skip_f32 ? 0 : (size_t)kEpiWarps * nslab * 2048;
+    return p.tma_out ? f16_off + (p.out16 ? (size_t)kEpiWarps * nslab * 1024 : 0) + 128 : (size_t)0;
+  };
+  const size_t tail_fixed = (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.splitk * p.split_rb * 16 * 128 * 4 : 0) + 1024;
+  const int st2 = (int)((227 * 1024 - tail_fixed - slab_bytes_for(2)) / stage_bytes), st4 = (int)((227 * 1024 - tail_fixed - slab_bytes_for(kSlabsMax)) / stage_bytes);
+  p.nslab = (p.tma_out && (st4 == st2 || st4 >= 12)) ? kSlabsMax : 2;
+  p.slab_f16_off = p.skip_f32 ? 0u : (uint32_t)(kEpiWarps * p.nslab) * 2048u;
+  const size_t slab_bytes = slab_bytes_for(p.nslab);
+  const size_t tail_bytes = tail_fixed + slab_bytes;
   int stages = (int)((227 * 1024 - tail_bytes) / stage_bytes);
   if (stages > 12) stages = 12;
   const int kb_per_cta = p.kb_per_split * ceil_div(num_tiles, p.splitk > 1 ? num_tiles : (pair ? ctx->sm_count / 2 : ctx->sm_count));
