@@ -367,6 +367,10 @@ size_t fa_nbits_tiles_bytes(int N, int K);
 int fa_nbits_side(fa_ctx *ctx, const uint8_t *bq, const float *scales, const uint8_t *zp, int N, int K, int nblk, int zpb,
                   uint8_t *tiles, float *scales_t, uint8_t *zp_t);
 int fa_prep_a_i8(fa_ctx *ctx, const float *a, int M, int K, int limbs, int8_t *out, float *rowscale);
+// fa_matmul_int8 on digit planes and row scales written by the caller in fa_prep_a_i8's layout (fa_linalg.cu)
+bool fa_matmul_int8_planes_ok(fa_ctx *ctx, int M, int N, int K);
+int fa_matmul_int8_planes(fa_ctx *ctx, const int8_t *a_planes, const float *rowscale, int limbs, int M, fa_bytes *wq,
+                          const float *colscale, int N, int K, const float *bias, float *c);
 int fa_pack_a_i8_raw(fa_ctx *ctx, const int8_t *aq, int M, int K, int8_t *out);
 int fa_pack_w_i8(fa_ctx *ctx, const int8_t *w_kn, int K, int N, int8_t *out);
 int fa_pack_w_f16(fa_ctx *ctx, const void *w_kn, int src_storage, int K, int N, __half *out);

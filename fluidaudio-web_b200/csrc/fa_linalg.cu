@@ -386,6 +386,23 @@ extern "C" int fa_matmul_int8(fa_ctx *ctx, const fa_tensor *a, fa_bytes *wq, con
   return FA_OK;
 }
 
+// fa_matmul_int8's tensor-core route for a caller that has written the activation digit planes and the row scales
+// itself (the batched TDT joint): same product, same epilogue, no pass over the activations.
+bool fa_matmul_int8_planes_ok(fa_ctx *ctx, int M, int N, int K) {
+  return !(gemv_shape_ok(ctx, M, N, K) && fa_gemv_kn_ok(M, N, K, true)) && tc_shape_ok(ctx, M, N, K);
+}
+int fa_matmul_int8_planes(fa_ctx *ctx, const int8_t *a_planes, const float *rowscale, int limbs, int M, fa_bytes *wq,
+                          const float *colscale, int N, int K, const float *bias, float *c) {
+  FA_REQUIRE(ctx, fa_valid_bytes(ctx, wq) && wq->nbytes >= (size_t)N * K, "matmulInt8: bad weight handle");
+  FA_TRY(ensure_nk_i8(ctx, wq, N, K));
+  TcEpilogue ep;
+  ep.rowscale = rowscale;
+  ep.colscale = colscale;
+  ep.bias = bias;
+  ep.act = FA_ACT_NONE;
+  return fa_tc_gemm_i8(ctx, a_planes, limbs, (const int8_t *)wq->nk_i8, c, false, M, N, K, ep);
+}
+
 extern "C" int fa_matmul_nbits(fa_ctx *ctx, const fa_tensor *a, fa_bytes *bq, const fa_tensor *scales, fa_bytes *zp,
                                int N, int block_size, fa_tensor **out) {
   if (!ctx || !out) return fa_fail(ctx, FA_ERR_INVALID, "matmulNBits: NULL argument");

@@ -47,7 +47,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // a dependent instruction only every several clocks and pays a refetch for every taken branch), so the common
 // "already complete" case must cost one instruction and one untaken branch.
 constexpr uint32_t kWaitLimit = 1u << 24;
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t limit) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t limit) {
   for (uint32_t i = 1; i < limit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 4096) __nanosleep(64);

@@ -20,6 +20,7 @@
 // Gate nonlinearities are the crate's own exp / tanh approximations (lib.rs:49-68), evaluated with separate
 // multiplies and adds, so that the only difference from the reference is the summation order inside the products.
 #include "fa_internal.cuh"
+#include "fa_tc_common.cuh"
 
 namespace {
 
@@ -54,6 +55,11 @@ __device__ __forceinline__ float t_tanhf(float x) {
   return __fdiv_rn(__fsub_rn(e, 1.0f), __fadd_rn(e, 1.0f));
 }
 
+// State vectors of the prediction network live in "chunk-transposed" form: windows in chunks of 32, element n of
+// window w at ((w / 32) * HID + n) * 32 + w % 32, so that the 32 windows' values of one n are one 128-byte line (what
+// k_tdt_rows streams).  Rows past W in the last chunk stay zero.
+__device__ __forceinline__ size_t t_idx(int w, int n) { return ((size_t)(w >> 5) * HID + n) * 32 + (w & 31); }
+
 // J[w][n] = relu(proj[w*T + t_w][n] + predproj[w][n]) * scale[n]; finished windows produce zeros.
 __global__ void __launch_bounds__(256) k_tdt_joint_in(const float *__restrict__ proj, const int *__restrict__ t, int T,
                                                       const float *__restrict__ predproj, const float *__restrict__ scale,
@@ -70,12 +76,63 @@ __global__ void __launch_bounds__(256) k_tdt_joint_in(const float *__restrict__ 
   }
 }
 
+// The same joint input, written directly as the int8 product's row operand: per window the row scale max|J|/127 and
+// `limbs` int8 digit planes Ap[limb][k/128][w][k%128], with fa_prep_a_i8's arithmetic digit for digit (that kernel
+// documents the split), so that the lock-step round needs no separate pass over J.
+__global__ void __launch_bounds__(256) k_tdt_joint_digits(const float *__restrict__ proj, const int *__restrict__ t, int T,
+                                                          const float *__restrict__ predproj, const float *__restrict__ scale,
+                                                          int W, int limbs, int8_t *__restrict__ out, float *__restrict__ rowscale) {
+  static_assert(HID % 128 == 0 && HID <= 3 * 256, "three values per thread, whole 128-wide K chunks");
+  __shared__ float red[8];
+  const int w = blockIdx.x, tw = t[w];
+  float v[3];
+  float mx = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 3; i++) {
+    const int n = threadIdx.x + i * 256;
+    float x = 0.0f;
+    if (n < HID && tw < T) {
+      x = __fadd_rn(proj[((size_t)w * T + tw) * HID + n], predproj[(size_t)w * HID + n]);
+      x = x > 0.0f ? x : 0.0f;
+      if (scale) x = __fmul_rn(x, scale[n]);
+    }
+    v[i] = x;
+    mx = fmaxf(mx, fabsf(x));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int k = 1; k < 8; k++) mx = fmaxf(mx, red[k]);
+  const float s = mx > 0.0f ? mx / 127.0f : 1.0f;
+  if (threadIdx.x == 0) rowscale[w] = s;
+  const size_t plane = (size_t)(HID / 128) * W * 128;
+#pragma unroll
+  for (int i = 0; i < 3; i++) {
+    const int k = threadIdx.x + i * 256;
+    if (k >= HID) break;
+    const size_t o = ((size_t)(k >> 7) * W + w) * 128 + (k & 127);
+    const float r = v[i] / s;
+    const float q1 = fminf(fmaxf(rintf(r), -127.0f), 127.0f);
+    out[o] = (int8_t)q1;
+    if (limbs > 1) {
+      const float r1 = (r - q1) * 128.0f;
+      const float q2 = rintf(r1);
+      out[plane + o] = (int8_t)q2;
+      if (limbs > 2) out[2 * plane + o] = (int8_t)rintf((r1 - q2) * 128.0f);
+    }
+  }
+}
+
 // One block per window: first-maximum over tokens and durations (the reference scans upwards with a strict >),
 // then the TDT bookkeeping of decode_proj (lib.rs:300-316) and, on an emission, the commit of the candidate state.
 __global__ void __launch_bounds__(256) k_tdt_pick(const float *__restrict__ logits, int ld, int T, int cap, int *__restrict__ t,
                                                   int *__restrict__ emitted, int *__restrict__ last_tok, int *__restrict__ counts,
-                                                  int *__restrict__ ids, int *__restrict__ frames, float *__restrict__ xh0,
-                                                  float *__restrict__ xh1, const float *__restrict__ nh1, float *__restrict__ c0,
+                                                  int *__restrict__ ids, int *__restrict__ frames, const float *__restrict__ embed,
+                                                  float *__restrict__ xt, float *__restrict__ h0t, const float *__restrict__ nh0t,
+                                                  float *__restrict__ h1t, const float *__restrict__ nh1t, float *__restrict__ c0,
                                                   float *__restrict__ c1, const float *__restrict__ nc0, const float *__restrict__ nc1,
                                                   int *__restrict__ done_count) {
   __shared__ float sv[8];
@@ -122,36 +179,178 @@ __global__ void __launch_bounds__(256) k_tdt_pick(const float *__restrict__ logi
     s_tok = tok;
   }
   __syncthreads();
-  if (s_tok != BLANK) {  // commit_state: H = NH, C = NC (H0 / H1 live in the right halves of the two LSTM inputs)
+  if (s_tok != BLANK) {  // commit_state: H = NH, C = NC; the new last token's embedding is layer 0's next input
+    const float *e = embed + (size_t)s_tok * HID;
     for (int n = threadIdx.x; n < HID; n += blockDim.x) {
-      xh0[(size_t)w * 2 * HID + HID + n] = xh1[(size_t)w * 2 * HID + n];  // NH0 is the left half of layer 1's input
-      xh1[(size_t)w * 2 * HID + HID + n] = nh1[(size_t)w * HID + n];
+      const size_t i = t_idx(w, n);
+      h0t[i] = nh0t[i];
+      h1t[i] = nh1t[i];
+      xt[i] = e[n];
       c0[(size_t)w * HID + n] = nc0[(size_t)w * HID + n];
       c1[(size_t)w * HID + n] = nc1[(size_t)w * HID + n];
     }
   }
 }
 
-// xh0[w][0:640] = embed[last_tok[w]]
+// XT[:, w] = embed[last_tok[w]]
 __global__ void __launch_bounds__(256) k_tdt_embed(const float *__restrict__ embed, const int *__restrict__ last_tok,
-                                                   float *__restrict__ xh0) {
+                                                   float *__restrict__ xt) {
   const int w = blockIdx.x;
   const float *e = embed + (size_t)last_tok[w] * HID;
-  for (int n = threadIdx.x; n < HID; n += blockDim.x) xh0[(size_t)w * 2 * HID + n] = e[n];
+  for (int n = threadIdx.x; n < HID; n += blockDim.x) xt[t_idx(w, n)] = e[n];
 }
 
-// ONNX iofc gates G [W][2560] (bias already added) and the committed cell state -> candidate cell and hidden state.
-// nh goes out with row pitch nh_ld (layer 0 writes the left half of layer 1's input).
-__global__ void __launch_bounds__(256) k_tdt_cell(const float *__restrict__ G, const float *__restrict__ c, float *__restrict__ nc,
-                                                  float *__restrict__ nh, int nh_ld, int W) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= W * HID) return;
-  const int w = i / HID, g = i - w * HID;
-  const float *gr = G + (size_t)w * 4 * HID;
-  const float zi = gr[g], zo = gr[HID + g], zf = gr[2 * HID + g], zc = gr[3 * HID + g];
-  const float cc = __fadd_rn(__fmul_rn(t_sigmoid(zf), c[i]), __fmul_rn(t_sigmoid(zi), t_tanhf(zc)));
-  nc[i] = cc;
-  nh[(size_t)w * nh_ld + g] = __fmul_rn(t_sigmoid(zo), t_tanhf(cc));
+// ---- k_tdt_rows: the prediction network's products, exact f32 ------------------------------------------------
+//
+// out[w][n] = sum_k x[w][k] * Wt[k][n] (+ bias) for up to a few hundred windows and f32 weights, K = 1280 (an LSTM
+// layer: [input | committed hidden state] against [W;R]^T, followed in the same kernel by the cell) or K = 640 (the
+// prediction projection).  With 32 rows a tensor-core tile is mostly padding and the f32 weights would need the
+// three-product tf32 scheme; plain FFMA does the 105 MFLOP of a layer in a few microseconds and is exact f32.
+//
+// One block owns 20 output columns (for an LSTM layer: the 4 gates of 5 hidden units, so that the cell can follow
+// without a grid-wide step) and one chunk of 32 windows.  Its 16 warps split K; a warp streams its slice of the
+// activations (chunk-transposed: 128 bytes per k) and of the block's weights (packed [block][k][20] at upload: 80
+// bytes per k) through a private ring of shared-memory stages filled by bulk copies (cp.async.bulk, one elected
+// lane, one mbarrier per stage), so that no thread waits on a global load.  A lane holds a 4-row x 5-column
+// accumulator tile: per k one 16-byte read of activations, one 16-byte and one 4-byte read of weights (all
+// broadcast within the warp) and 20 FFMA.  Partial sums of the 16 warps meet in shared memory in a fixed order.
+constexpr int kRowsWarps = 16, kRowsThreads = kRowsWarps * 32, kRowsCols = 20, kRowsKS = 8, kRowsNS = 5;
+constexpr int kRowsStageBytes = kRowsKS * (128 + kRowsCols * 4);                       // 1664
+constexpr int kRowsRingBytes = kRowsWarps * kRowsNS * kRowsStageBytes;                 // 133120
+constexpr int kRowsRedBytes = kRowsWarps * 32 * kRowsCols * 4;                         // 40960
+constexpr int kRowsSmem = kRowsRingBytes + kRowsRedBytes + 32 * kRowsCols * 4 + kRowsWarps * kRowsNS * 8;
+
+struct RowsParams {
+  const float *xa, *xb;  // activations for k < 640 and k >= 640, chunk-transposed
+  const float *wt;       // [blocks][K][20]: per k the columns (g, u < 4) as g*4+u, then (g, u = 4) as 16+g
+  const float *bias;     // LSTM: [4*HID] in gate order i, o, f, c; projection: [HID]
+  const float *c;        // LSTM: committed cell state [W][HID]
+  float *nc, *nht;       // LSTM: candidate cell state [W][HID] and hidden state (chunk-transposed)
+  float *out;            // projection: [W][HID]
+  int W;
+  int *status;
+  uint32_t wait_limit;
+  int withhold;          // >= 0: warp 0 of block 0 never loads this stage (test hook for the bounded wait)
+};
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <bool LSTM>
+__global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p) {
+  constexpr int K = LSTM ? 2 * HID : HID, KPER = K / kRowsWarps, NLOAD = KPER / kRowsKS;
+  static_assert(KPER % kRowsKS == 0 && HID % KPER == 0, "a warp's K slice is whole stages inside one operand");
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t *ring = smem;
+  float *red = reinterpret_cast<float *>(smem + kRowsRingBytes);
+  float *z = reinterpret_cast<float *>(smem + kRowsRingBytes + kRowsRedBytes);
+  const uint32_t bars = tc::smem_u32(smem + kRowsRingBytes + kRowsRedBytes + 32 * kRowsCols * 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, blk = blockIdx.x, chunk = blockIdx.y;
+  const int rq = lane >> 2, g = lane & 3;
+  const int k0 = warp * KPER;
+  const float *xsrc = (k0 < HID ? p.xa + ((size_t)chunk * HID + k0) * 32 : p.xb + ((size_t)chunk * HID + (k0 - HID)) * 32);
+  const float *wsrc = p.wt + ((size_t)blk * K + k0) * kRowsCols;
+  uint8_t *my = ring + (size_t)warp * kRowsNS * kRowsStageBytes;
+  const uint32_t my_u = tc::smem_u32(my), my_bar = bars + warp * kRowsNS * 8;
+  const int wh = (blk == 0 && chunk == 0 && warp == 0) ? p.withhold : -1;
+
+  // one lane; what = 1: weights, 2: activations, 3: both.  The barrier expects the whole stage with the weights.
+  auto load_stage = [&](int it, int what) {
+    const int s = it % kRowsNS;
+    const uint32_t bar = my_bar + s * 8, dst = my_u + s * kRowsStageBytes;
+    if (what & 1) tc::mbar_expect_tx(bar, kRowsStageBytes);
+    if (it == wh) return;
+    if (what & 1) bulk_g2s(dst + kRowsKS * 128, wsrc + (size_t)it * kRowsKS * kRowsCols, kRowsKS * kRowsCols * 4, bar);
+    if (what & 2) bulk_g2s(dst, xsrc + (size_t)it * kRowsKS * 32, kRowsKS * 128, bar);
+  };
+  constexpr int kFirst = NLOAD < kRowsNS ? NLOAD : kRowsNS;
+  if (lane == 0) {
+    for (int s = 0; s < kRowsNS; s++) tc::mbar_init(my_bar + s * 8, 1);
+    tc::fence_barrier_init();
+    tc::fence_proxy_async_smem();
+    for (int it = 0; it < kFirst; it++) load_stage(it, 1);  // the weights do not depend on the launch before
+  }
+  fa_grid_dep_sync();  // the activations do
+  if (lane == 0)
+    for (int it = 0; it < kFirst; it++) load_stage(it, 2);
+  __syncwarp();
+
+  float acc[4][5];
+#pragma unroll
+  for (int r = 0; r < 4; r++)
+#pragma unroll
+    for (int u = 0; u < 5; u++) acc[r][u] = 0.0f;
+  bool ok = true;
+#pragma unroll
+  for (int it = 0; it < NLOAD; it++) {
+    const int s = it % kRowsNS;
+    if (!__all_sync(0xffffffffu, tc::mbar_wait(my_bar + s * 8, (it / kRowsNS) & 1, p.wait_limit))) {
+      ok = false;
+      break;
+    }
+    const float4 *xs = reinterpret_cast<const float4 *>(my + s * kRowsStageBytes) + rq;
+    const float *ws = reinterpret_cast<const float *>(my + s * kRowsStageBytes + kRowsKS * 128);
+#pragma unroll
+    for (int kk = 0; kk < kRowsKS; kk++) {
+      const float4 xv = xs[kk * 8];
+      const float4 wv = *reinterpret_cast<const float4 *>(ws + kk * kRowsCols + g * 4);
+      const float w4 = ws[kk * kRowsCols + 16 + g];
+      const float xr[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+      for (int r = 0; r < 4; r++) {
+        acc[r][0] = fmaf(xr[r], wv.x, acc[r][0]);
+        acc[r][1] = fmaf(xr[r], wv.y, acc[r][1]);
+        acc[r][2] = fmaf(xr[r], wv.z, acc[r][2]);
+        acc[r][3] = fmaf(xr[r], wv.w, acc[r][3]);
+        acc[r][4] = fmaf(xr[r], w4, acc[r][4]);
+      }
+    }
+    if (it + kRowsNS < NLOAD) {
+      __syncwarp();  // every lane has read the stage before it is refilled
+      if (lane == 0) load_stage(it + kRowsNS, 3);
+    }
+  }
+  if (!ok && lane == 0 && atomicCAS(p.status, 0, 7) == 0) {
+    p.status[1] = (int)blockIdx.x;
+    p.status[2] = warp;
+  }
+  // partial sums: red[warp][r*5+u][lane]
+#pragma unroll
+  for (int r = 0; r < 4; r++)
+#pragma unroll
+    for (int u = 0; u < 5; u++) red[(warp * 20 + r * 5 + u) * 32 + lane] = acc[r][u];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * kRowsCols; i += kRowsThreads) {
+    float sum = red[i];
+#pragma unroll
+    for (int w = 1; w < kRowsWarps; w++) sum = __fadd_rn(sum, red[w * 32 * kRowsCols + i]);
+    const int j = i >> 5, l = i & 31;  // j = r*5+u, l = rq*4+g
+    const int row = (l >> 2) * 4 + j / 5, col = (l & 3) * 5 + j % 5;
+    z[row * kRowsCols + col] = sum;
+  }
+  __syncthreads();
+  if (LSTM) {
+    if (threadIdx.x < 32 * 5) {
+      const int row = threadIdx.x & 31, u = threadIdx.x >> 5, unit = blk * 5 + u, w = chunk * 32 + row;
+      if (w < p.W) {
+        const float *zr = z + row * kRowsCols;
+        const float zi = __fadd_rn(zr[u], p.bias[unit]), zo = __fadd_rn(zr[5 + u], p.bias[HID + unit]);
+        const float zf = __fadd_rn(zr[10 + u], p.bias[2 * HID + unit]), zc = __fadd_rn(zr[15 + u], p.bias[3 * HID + unit]);
+        const size_t i = (size_t)w * HID + unit;
+        const float cc = __fadd_rn(__fmul_rn(t_sigmoid(zf), p.c[i]), __fmul_rn(t_sigmoid(zi), t_tanhf(zc)));
+        p.nc[i] = cc;
+        p.nht[t_idx(w, unit)] = __fmul_rn(t_sigmoid(zo), t_tanhf(cc));
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < 32 * kRowsCols; i += kRowsThreads) {
+      const int row = i / kRowsCols, col = i - row * kRowsCols, w = chunk * 32 + row, n = blk * kRowsCols + col;
+      if (w < p.W) p.out[(size_t)w * HID + n] = __fadd_rn(z[i], p.bias[n]);
+    }
+  }
 }
 
 __global__ void k_fill_int(int *p, int n, int v) {
@@ -183,21 +382,32 @@ extern "C" int fa_tdt_create(fa_ctx *ctx, const float *embed, const float *l0w, 
   FA_REQUIRE(ctx, (out_q && out_scale) || out_w, "tdtCreate: needs the out matrix as int8 rows + scales or as f32");
   fa_tdt *d = new fa_tdt();
   int rc = fa_upload_f32(ctx, embed, VOCAB, HID, &d->embed);
-  // LSTM weights [4*HID][HID] (row = gate output) as one [2*HID][4*HID] right-hand matrix per layer: rows 0..639
-  // multiply the layer input, rows 640..1279 the committed hidden state
+  // k_tdt_rows' weight packing: block b owns hidden units 5b..5b+4 (their four gates, ONNX order i, o, f, c) over
+  // K = 1280: rows 0..639 multiply the layer input, rows 640..1279 the committed hidden state
+  auto pos = [](int g, int u) { return u < 4 ? g * 4 + u : 16 + g; };
   const float *lw[2] = {l0w, l1w}, *lr[2] = {l0r, l1r}, *lb[2] = {l0b, l1b};
   std::vector<float> tmp((size_t)2 * HID * 4 * HID), bs(4 * HID);
   for (int l = 0; l < 2 && rc == FA_OK; l++) {
-    for (int g = 0; g < 4 * HID; g++)
-      for (int k = 0; k < HID; k++) {
-        tmp[(size_t)k * 4 * HID + g] = lw[l][(size_t)g * HID + k];
-        tmp[(size_t)(HID + k) * 4 * HID + g] = lr[l][(size_t)g * HID + k];
+    for (int blk = 0; blk < HID / 5; blk++)
+      for (int k = 0; k < 2 * HID; k++) {
+        float *dst = &tmp[((size_t)blk * 2 * HID + k) * kRowsCols];
+        for (int g = 0; g < 4; g++)
+          for (int u = 0; u < 5; u++) {
+            const size_t row = (size_t)g * HID + blk * 5 + u;
+            dst[pos(g, u)] = k < HID ? lw[l][row * HID + k] : lr[l][row * HID + (k - HID)];
+          }
       }
     for (int g = 0; g < 4 * HID; g++) bs[g] = lb[l][g] + lb[l][4 * HID + g];  // lib.rs:139: b[g] + b[4*HID + g] first
-    rc = fa_upload_f32(ctx, tmp.data(), 2 * HID, 4 * HID, &d->wr[l]);
+    rc = fa_upload_f32(ctx, tmp.data(), (HID / 5) * 2 * HID, kRowsCols, &d->wr[l]);
     if (rc == FA_OK) rc = fa_upload_f32(ctx, bs.data(), 1, 4 * HID, &d->bsum[l]);
   }
-  if (rc == FA_OK) rc = fa_upload_f32(ctx, pred_w, HID, HID, &d->pred_w);
+  if (rc == FA_OK) {  // the projection [k][n]: block b owns columns 20b..20b+19
+    for (int blk = 0; blk < HID / kRowsCols; blk++)
+      for (int k = 0; k < HID; k++)
+        for (int g = 0; g < 4; g++)
+          for (int u = 0; u < 5; u++) tmp[((size_t)blk * HID + k) * kRowsCols + pos(g, u)] = pred_w[(size_t)k * HID + blk * kRowsCols + g * 5 + u];
+    rc = fa_upload_f32(ctx, tmp.data(), (HID / kRowsCols) * HID, kRowsCols, &d->pred_w);
+  }
   if (rc == FA_OK) rc = fa_upload_f32(ctx, pred_b, 1, HID, &d->pred_b);
   if (rc == FA_OK) rc = fa_upload_f32(ctx, out_b, 1, LOGITS, &d->out_b);
   if (rc == FA_OK && out_q) {
@@ -227,37 +437,48 @@ extern "C" int fa_tdt_free(fa_ctx *ctx, fa_tdt *d) {
 namespace {
 
 struct TdtState {
-  fa_tensor *xh0 = nullptr, *xh1 = nullptr, *c0 = nullptr, *c1 = nullptr, *nc0 = nullptr, *nc1 = nullptr, *nh1 = nullptr,
-            *predproj = nullptr, *J = nullptr;
+  // chunk-transposed [ceil(W/32)][HID][32]: embedding of the last token, committed and candidate hidden states
+  fa_tensor *xt = nullptr, *h0t = nullptr, *nh0t = nullptr, *h1t = nullptr, *nh1t = nullptr;
+  fa_tensor *c0 = nullptr, *c1 = nullptr, *nc0 = nullptr, *nc1 = nullptr, *predproj = nullptr, *J = nullptr;  // [W][HID]
+  fa_tensor *logits = nullptr;                   // [W][LOGITS] when the joint's digit planes are written here
+  void *planes = nullptr, *rowscale = nullptr;   // the int8 product's row operand (see k_tdt_joint_digits)
+  size_t planes_bytes = 0, rowscale_bytes = 0;
   void *ints = nullptr;  // t, emitted, last_tok, counts [W each], done_count, then ids and frames [W*cap each]
   size_t ints_bytes = 0;
 };
 
-// predict(last_tok) + compute_predproj for every window, from the committed state
-int tdt_predict(fa_ctx *ctx, fa_tdt *d, TdtState &s, int W, const int *last_tok) {
-  {
-    LaunchScope ls(ctx, "tdt_embed");
-    k_tdt_embed<<<W, 256, 0, ctx->stream>>>((const float *)d->embed->dptr, last_tok, (float *)s.xh0->dptr);
+template <bool LSTM>
+int tdt_rows(fa_ctx *ctx, const RowsParams &p, int blocks, int W, int withhold) {
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[LSTM]) {
+    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tdt_rows<LSTM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowsSmem));
+    attr_set[LSTM] = true;
   }
-  fa_tensor *g = nullptr;
-  FA_TRY(fa_matmul(ctx, s.xh0, d->wr[0], d->bsum[0], FA_ACT_NONE, nullptr, &g));
-  {
-    LaunchScope ls(ctx, "tdt_cell");
-    k_tdt_cell<<<ceil_div(W * HID, 256), 256, 0, ctx->stream>>>((const float *)g->dptr, (const float *)s.c0->dptr,
-                                                                 (float *)s.nc0->dptr, (float *)s.xh1->dptr, 2 * HID, W);
-  }
-  FA_TRY(fa_free_tensor(ctx, g));
-  FA_TRY(fa_matmul(ctx, s.xh1, d->wr[1], d->bsum[1], FA_ACT_NONE, nullptr, &g));
-  {
-    LaunchScope ls(ctx, "tdt_cell");
-    k_tdt_cell<<<ceil_div(W * HID, 256), 256, 0, ctx->stream>>>((const float *)g->dptr, (const float *)s.c1->dptr,
-                                                                 (float *)s.nc1->dptr, (float *)s.nh1->dptr, HID, W);
-  }
-  FA_TRY(fa_free_tensor(ctx, g));
-  fa_tensor *pp = nullptr;
-  FA_TRY(fa_matmul(ctx, s.nh1, d->pred_w, d->pred_b, FA_ACT_NONE, nullptr, &pp));
-  FA_CHECK_CUDA(ctx, cudaMemcpyAsync(s.predproj->dptr, pp->dptr, (size_t)W * HID * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-  FA_TRY(fa_free_tensor(ctx, pp));
+  RowsParams q = p;
+  q.W = W;
+  q.status = ctx->dev_status;
+  q.wait_limit = ctx->wait_limit;
+  q.withhold = withhold;
+  LaunchScope ls(ctx, LSTM ? "tdt_lstm" : "tdt_pred");
+  FA_CHECK_CUDA(ctx, fa_launch_dep(ctx, k_tdt_rows<LSTM>, dim3(blocks, ceil_div(W, 32)), dim3(kRowsThreads), kRowsSmem, q));
+  return FA_OK;
+}
+
+// predict + compute_predproj for every window, from the committed state and the last token's embedding
+int tdt_predict(fa_ctx *ctx, fa_tdt *d, TdtState &s, int W) {
+  const int withhold = ctx->tc_withhold_chunk;
+  ctx->tc_withhold_chunk = -1;  // one launch only
+  RowsParams p{};
+  p.xa = (const float *)s.xt->dptr, p.xb = (const float *)s.h0t->dptr, p.wt = (const float *)d->wr[0]->dptr;
+  p.bias = (const float *)d->bsum[0]->dptr, p.c = (const float *)s.c0->dptr, p.nc = (float *)s.nc0->dptr, p.nht = (float *)s.nh0t->dptr;
+  FA_TRY(tdt_rows<true>(ctx, p, HID / 5, W, withhold));
+  p.xa = (const float *)s.nh0t->dptr, p.xb = (const float *)s.h1t->dptr, p.wt = (const float *)d->wr[1]->dptr;
+  p.bias = (const float *)d->bsum[1]->dptr, p.c = (const float *)s.c1->dptr, p.nc = (float *)s.nc1->dptr, p.nht = (float *)s.nh1t->dptr;
+  FA_TRY(tdt_rows<true>(ctx, p, HID / 5, W, -1));
+  RowsParams q{};
+  q.xa = (const float *)s.nh1t->dptr, q.xb = q.xa, q.wt = (const float *)d->pred_w->dptr, q.bias = (const float *)d->pred_b->dptr;
+  q.out = (float *)s.predproj->dptr;
+  FA_TRY(tdt_rows<false>(ctx, q, HID / kRowsCols, W, -1));
   FA_LAUNCH_CHECK(ctx, "tdt_predict");
   return FA_OK;
 }
@@ -265,26 +486,39 @@ int tdt_predict(fa_ctx *ctx, fa_tdt *d, TdtState &s, int W, const int *last_tok)
 int tdt_round(fa_ctx *ctx, fa_tdt *d, TdtState &s, const fa_tensor *proj, int W, int T, int cap) {
   int *t = (int *)s.ints, *emitted = t + W, *last_tok = t + 2 * W, *counts = t + 3 * W, *done = t + 4 * W;
   int *ids = done + 4, *frames = ids + (size_t)W * cap;
-  {
-    LaunchScope ls(ctx, "tdt_joint_in");
-    k_tdt_joint_in<<<W, 256, 0, ctx->stream>>>((const float *)proj->dptr, t, T, (const float *)s.predproj->dptr,
-                                               d->out_scale ? (const float *)d->out_scale->dptr : nullptr, (float *)s.J->dptr);
-  }
   fa_tensor *logits = nullptr;
-  if (d->out_q)
-    FA_TRY(fa_matmul_int8(ctx, s.J, d->out_q, d->ones, LOGITS, HID, d->out_b, FA_ACT_NONE, &logits));
-  else
-    FA_TRY(fa_matmul(ctx, s.J, d->out_w, d->out_b, FA_ACT_NONE, nullptr, &logits));
+  if (s.planes) {
+    {
+      LaunchScope ls(ctx, "tdt_joint_digits");
+      k_tdt_joint_digits<<<W, 256, 0, ctx->stream>>>((const float *)proj->dptr, t, T, (const float *)s.predproj->dptr,
+                                                   (const float *)d->out_scale->dptr, W, ctx->int8_limbs, (int8_t *)s.planes,
+                                                   (float *)s.rowscale);
+    }
+    FA_TRY(fa_matmul_int8_planes(ctx, (const int8_t *)s.planes, (const float *)s.rowscale, ctx->int8_limbs, W, d->out_q,
+                                 (const float *)d->ones->dptr, LOGITS, HID, (const float *)d->out_b->dptr, (float *)s.logits->dptr));
+  } else {
+    {
+      LaunchScope ls(ctx, "tdt_joint_in");
+      k_tdt_joint_in<<<W, 256, 0, ctx->stream>>>((const float *)proj->dptr, t, T, (const float *)s.predproj->dptr,
+                                                 d->out_scale ? (const float *)d->out_scale->dptr : nullptr, (float *)s.J->dptr);
+    }
+    if (d->out_q)
+      FA_TRY(fa_matmul_int8(ctx, s.J, d->out_q, d->ones, LOGITS, HID, d->out_b, FA_ACT_NONE, &logits));
+    else
+      FA_TRY(fa_matmul(ctx, s.J, d->out_w, d->out_b, FA_ACT_NONE, nullptr, &logits));
+  }
+  const float *lg = (const float *)(logits ? logits->dptr : s.logits->dptr);
   {
     LaunchScope ls(ctx, "tdt_pick");
-    k_tdt_pick<<<W, 256, 0, ctx->stream>>>((const float *)logits->dptr, LOGITS, T, cap, t, emitted, last_tok, counts, ids, frames,
-                                           (float *)s.xh0->dptr, (float *)s.xh1->dptr, (const float *)s.nh1->dptr,
+    k_tdt_pick<<<W, 256, 0, ctx->stream>>>(lg, LOGITS, T, cap, t, emitted, last_tok, counts, ids, frames,
+                                           (const float *)d->embed->dptr, (float *)s.xt->dptr, (float *)s.h0t->dptr,
+                                           (const float *)s.nh0t->dptr, (float *)s.h1t->dptr, (const float *)s.nh1t->dptr,
                                            (float *)s.c0->dptr, (float *)s.c1->dptr, (const float *)s.nc0->dptr,
                                            (const float *)s.nc1->dptr, done);
   }
-  FA_TRY(fa_free_tensor(ctx, logits));
+  if (logits) FA_TRY(fa_free_tensor(ctx, logits));
   FA_LAUNCH_CHECK(ctx, "tdt_round");
-  return tdt_predict(ctx, d, s, W, last_tok);
+  return tdt_predict(ctx, d, s, W);
 }
 
 }  // namespace
@@ -307,18 +541,26 @@ extern "C" int fa_tdt_decode_proj(fa_ctx *ctx, fa_tdt *d, const fa_tensor *proj,
   fa_graph *graph = nullptr;
   int rc = FA_OK, rounds = 0;
   auto alloc = [&](int r, int c, fa_tensor **t) { return rc == FA_OK ? (rc = fa_alloc(ctx, r, c, t)) : rc; };
-  alloc(W, 2 * HID, &s.xh0), alloc(W, 2 * HID, &s.xh1), alloc(W, HID, &s.c0), alloc(W, HID, &s.c1), alloc(W, HID, &s.nc0),
-      alloc(W, HID, &s.nc1), alloc(W, HID, &s.nh1), alloc(W, HID, &s.predproj), alloc(W, HID, &s.J);
+  const int wpad = ceil_div(W, 32) * 32;
+  alloc(wpad, HID, &s.xt), alloc(wpad, HID, &s.h0t), alloc(wpad, HID, &s.nh0t), alloc(wpad, HID, &s.h1t), alloc(wpad, HID, &s.nh1t),
+      alloc(W, HID, &s.c0), alloc(W, HID, &s.c1), alloc(W, HID, &s.nc0), alloc(W, HID, &s.nc1), alloc(W, HID, &s.predproj),
+      alloc(W, HID, &s.J);
   const size_t n_int = (size_t)4 * W + 4 + (size_t)2 * W * cap;
   if (rc == FA_OK) rc = fa_block_acquire(ctx, n_int * 4, &s.ints, &s.ints_bytes);
+  if (rc == FA_OK && d->out_q && fa_matmul_int8_planes_ok(ctx, W, LOGITS, HID)) {
+    alloc(W, LOGITS, &s.logits);
+    if (rc == FA_OK) rc = fa_block_acquire(ctx, fa_tc_act_bytes(W, HID, 1, ctx->int8_limbs), &s.planes, &s.planes_bytes);
+    if (rc == FA_OK) rc = fa_block_acquire(ctx, (size_t)W * 4, &s.rowscale, &s.rowscale_bytes);
+  }
   int *t = (int *)s.ints, *last_tok = t + 2 * W, *done = t + 4 * W;
   if (rc == FA_OK) {
     // decode_proj :290-294: zero state, last token = blank, predict + predproj once
-    fa_tensor *z[] = {s.xh0, s.xh1, s.c0, s.c1, s.nc0, s.nc1, s.nh1};
+    fa_tensor *z[] = {s.xt, s.h0t, s.nh0t, s.h1t, s.nh1t, s.c0, s.c1, s.nc0, s.nc1};
     for (fa_tensor *x : z) cudaMemsetAsync(x->dptr, 0, (size_t)x->rows * x->cols * 4, ctx->stream);
     cudaMemsetAsync(s.ints, 0, n_int * 4, ctx->stream);
     k_fill_int<<<ceil_div(W, 256), 256, 0, ctx->stream>>>(last_tok, W, BLANK);
-    rc = tdt_predict(ctx, d, s, W, last_tok);
+    k_tdt_embed<<<W, 256, 0, ctx->stream>>>((const float *)d->embed->dptr, last_tok, (float *)s.xt->dptr);
+    rc = tdt_predict(ctx, d, s, W);
   }
   // one round eagerly (first-use caches of the weights), then the round as a recorded batch, replayed
   if (rc == FA_OK) rc = tdt_round(ctx, d, s, proj, W, T, cap);
@@ -353,6 +595,8 @@ extern "C" int fa_tdt_decode_proj(fa_ctx *ctx, fa_tdt *d, const fa_tensor *proj,
   const std::string msg = ctx->err;
   if (graph) fa_graph_free(ctx, graph);
   if (s.ints) fa_block_release(ctx, s.ints);
+  if (s.planes) fa_block_release(ctx, s.planes);
+  if (s.rowscale) fa_block_release(ctx, s.rowscale);
   ctx->int8_limbs = saved_limbs;
   fa_pop_arena(ctx, arena);
   if (rc != FA_OK) ctx->err = msg;

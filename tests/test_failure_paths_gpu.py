@@ -70,6 +70,35 @@ def test_bounded_wait_runs_out_in_the_pair_kernel(pkg):
         ctx.destroy()
 
 
+def test_bounded_wait_runs_out_in_the_prediction_network_kernel(pkg):
+    """The TDT decoder's exact-f32 products stream their operands through per-warp rings of bulk copies: warp 0 of
+    block 0 never issues stage 2 of the first LSTM layer's first evaluation, its bounded wait runs out, the decode
+    returns FA_ERR_TIMEOUT and the next decode on the same context gives the reference's tokens."""
+    from fluidaudio_web_b200.engines import tdt_decoder as td
+    from oracle.tdt_oracle import TdtOracle
+
+    ctx = pkg.CudaContext(0)
+    try:
+        W, Tn = 4, 24
+        w = td.synth_tdt_weights(5)
+        proj = np.random.default_rng(424).standard_normal((W, Tn, 640)).astype(np.float32)
+        want = TdtOracle(w, int8=True, threads=4).decode_proj_batch(proj, W, Tn)
+        dec = td.TdtDecoder(ctx, w, int8=True)
+        P = ctx.upload(proj.reshape(W * Tn, 640), W * Tn, 640)
+        ctx.setOption("wait_limit", 20000)
+        ctx.setOption("tc_test_withhold_chunk", 2)
+        with pytest.raises(pkg.CudaError) as ei:
+            dec.decode_proj(P, W, Tn)
+        assert ei.value.code == 5 and "bounded wait ran out" in str(ei.value)  # FA_ERR_TIMEOUT
+        ctx.setOption("wait_limit", 1 << 24)
+        got = dec.decode_proj(P, W, Tn)
+        for wi in range(W):
+            assert got[wi][0].tolist() == want[wi][0].tolist() and got[wi][1].tolist() == want[wi][1].tolist()
+        dec.free()
+    finally:
+        ctx.destroy()
+
+
 def test_first_use_of_a_weight_inside_a_recording_is_refused(pkg):
     """The packed tensor-core copy of a weight is built on first use.  Inside a recording that step would only be
     captured while the handle already looked ready, and an eager product before the first replay would read

@@ -15,7 +15,7 @@ def _frames(W, T, seed):
 
 
 @pytest.mark.parametrize("int8", [True, False])
-@pytest.mark.parametrize("W,T", [(4, 24), (32, 188)])
+@pytest.mark.parametrize("W,T", [(4, 24), (40, 24), (32, 188)])  # 40: two chunks of windows, the second ragged
 def test_tokens_and_frames_identical_to_oracle(ctx, pkg, W, T, int8):
     from fluidaudio_web_b200.engines import tdt_decoder as td
 
