@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(256) k_tdt_joint_digits(const float *__restric
                                                           int W, int limbs, int8_t *__restrict__ out, float *__restrict__ rowscale) {
   static_assert(HID % 128 == 0 && HID <= 3 * 256, "three values per thread, whole 128-wide K chunks");
   __shared__ float red[8];
+  fa_grid_dep_sync();
   const int w = blockIdx.x, tw = t[w];
   float v[3];
   float mx = 0.0f;
@@ -128,42 +129,73 @@ __global__ void __launch_bounds__(256) k_tdt_joint_digits(const float *__restric
 
 // One block per window: first-maximum over tokens and durations (the reference scans upwards with a strict >),
 // then the TDT bookkeeping of decode_proj (lib.rs:300-316) and, on an emission, the commit of the candidate state.
-__global__ void __launch_bounds__(256) k_tdt_pick(const float *__restrict__ logits, int ld, int T, int cap, int *__restrict__ t,
-                                                  int *__restrict__ emitted, int *__restrict__ last_tok, int *__restrict__ counts,
-                                                  int *__restrict__ ids, int *__restrict__ frames, const float *__restrict__ embed,
-                                                  float *__restrict__ xt, float *__restrict__ h0t, const float *__restrict__ nh0t,
-                                                  float *__restrict__ h1t, const float *__restrict__ nh1t, float *__restrict__ c0,
-                                                  float *__restrict__ c1, const float *__restrict__ nc0, const float *__restrict__ nc1,
-                                                  int *__restrict__ done_count) {
-  __shared__ float sv[8];
-  __shared__ int si[8];
+// Every global read whose address does not depend on the picked token is issued before the first comparison (a
+// thread's eight logits, the durations, the bookkeeping words, the candidate state), so that the block pays one
+// memory latency for them, not one per loop trip.
+constexpr int kPickThreads = 1024;
+__global__ void __launch_bounds__(kPickThreads) k_tdt_pick(const float *__restrict__ logits, int ld, int T, int cap, int *__restrict__ t,
+                                                           int *__restrict__ emitted, int *__restrict__ last_tok, int *__restrict__ counts,
+                                                           int *__restrict__ ids, int *__restrict__ frames, const float *__restrict__ embed,
+                                                           float *__restrict__ xt, float *__restrict__ h0t, const float *__restrict__ nh0t,
+                                                           float *__restrict__ h1t, const float *__restrict__ nh1t, float *__restrict__ c0,
+                                                           float *__restrict__ c1, const float *__restrict__ nc0, const float *__restrict__ nc1,
+                                                           int *__restrict__ done_count) {
+  static_assert(VOCAB == 8 * kPickThreads + 1 && HID <= kPickThreads, "eight logits per thread and one more for thread 0");
+  __shared__ float sv[32];
+  __shared__ int si[32];
   __shared__ int s_tok;
-  const int w = blockIdx.x, tw = t[w];
+  fa_grid_dep_sync();
+  const int w = blockIdx.x, tid = threadIdx.x, tw = t[w];
   if (tw >= T) return;  // this window finished in an earlier round (block-uniform)
   const float *row = logits + (size_t)w * ld;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) v[j] = row[tid + j * kPickThreads];
+  float last = -INFINITY, dur[LOGITS - VOCAB];
+  int em = 0, n_out = 0;
+  if (tid == 0) {
+    last = row[VOCAB - 1];
+#pragma unroll
+    for (int i = 0; i < LOGITS - VOCAB; i++) dur[i] = row[VOCAB + i];
+    em = emitted[w];
+    n_out = counts[w];
+  }
+  float p_h0 = 0.0f, p_h1 = 0.0f, p_c0 = 0.0f, p_c1 = 0.0f;
+  if (tid < HID) {
+    p_h0 = nh0t[t_idx(w, tid)], p_h1 = nh1t[t_idx(w, tid)];
+    p_c0 = nc0[(size_t)w * HID + tid], p_c1 = nc1[(size_t)w * HID + tid];
+  }
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < VOCAB; i += blockDim.x) {
-    const float v = row[i];
-    if (v > bv) { bv = v; bi = i; }  // ascending i per thread: keeps the first maximum
-  }
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+    if (v[j] > bv) { bv = v[j]; bi = tid + j * kPickThreads; }  // ascending index per thread: keeps the first maximum
+  if (tid == 0 && last > bv) { bv = last; bi = VOCAB - 1; }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
   }
-  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  if ((tid & 31) == 0) { sv[tid >> 5] = bv; si[tid >> 5] = bi; }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int k = 1; k < 8; k++)
-      if (sv[k] > bv || (sv[k] == bv && si[k] < bi)) { bv = sv[k]; bi = si[k]; }
+  if (tid < 32) {
+    bv = sv[tid], bi = si[tid];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+  }
+  if (tid == 0) {
     const int tok = bi == 0x7fffffff ? 0 : bi;  // every logit NaN or -inf: the reference's scan leaves index 0
     int step = 0;
     float dv = -INFINITY;
-    for (int i = VOCAB; i < LOGITS; i++)
-      if (row[i] > dv) { dv = row[i]; step = i - VOCAB; }
-    int em = emitted[w], n_out = counts[w], tn = tw;
+#pragma unroll
+    for (int i = 0; i < LOGITS - VOCAB; i++)
+      if (dur[i] > dv) { dv = dur[i]; step = i; }
+    int tn = tw;
     if (tok != BLANK) {
       if (n_out < cap) { ids[(size_t)w * cap + n_out] = tok; frames[(size_t)w * cap + n_out] = tw; }
       n_out++;
@@ -179,16 +211,13 @@ __global__ void __launch_bounds__(256) k_tdt_pick(const float *__restrict__ logi
     s_tok = tok;
   }
   __syncthreads();
-  if (s_tok != BLANK) {  // commit_state: H = NH, C = NC; the new last token's embedding is layer 0's next input
-    const float *e = embed + (size_t)s_tok * HID;
-    for (int n = threadIdx.x; n < HID; n += blockDim.x) {
-      const size_t i = t_idx(w, n);
-      h0t[i] = nh0t[i];
-      h1t[i] = nh1t[i];
-      xt[i] = e[n];
-      c0[(size_t)w * HID + n] = nc0[(size_t)w * HID + n];
-      c1[(size_t)w * HID + n] = nc1[(size_t)w * HID + n];
-    }
+  if (s_tok != BLANK && tid < HID) {  // commit_state: H = NH, C = NC; the new token's embedding is layer 0's next input
+    const size_t i = t_idx(w, tid);
+    xt[i] = embed[(size_t)s_tok * HID + tid];
+    h0t[i] = p_h0;
+    h1t[i] = p_h1;
+    c0[(size_t)w * HID + tid] = p_c0;
+    c1[(size_t)w * HID + tid] = p_c1;
   }
 }
 
@@ -218,7 +247,8 @@ constexpr int kRowsWarps = 16, kRowsThreads = kRowsWarps * 32, kRowsCols = 20, k
 constexpr int kRowsStageBytes = kRowsKS * (128 + kRowsCols * 4);                       // 1664
 constexpr int kRowsRingBytes = kRowsWarps * kRowsNS * kRowsStageBytes;                 // 133120
 constexpr int kRowsRedBytes = kRowsWarps * 32 * kRowsCols * 4;                         // 40960
-constexpr int kRowsSmem = kRowsRingBytes + kRowsRedBytes + 32 * kRowsCols * 4 + kRowsWarps * kRowsNS * 8;
+constexpr int kRowsZBytes = (32 + 1) * kRowsCols * 4;  // the block's sums, then one row for the projection's bias
+constexpr int kRowsSmem = kRowsRingBytes + kRowsRedBytes + kRowsZBytes + kRowsWarps * kRowsNS * 8;
 
 struct RowsParams {
   const float *xa, *xb;  // activations for k < 640 and k >= 640, chunk-transposed
@@ -247,7 +277,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
   uint8_t *ring = smem;
   float *red = reinterpret_cast<float *>(smem + kRowsRingBytes);
   float *z = reinterpret_cast<float *>(smem + kRowsRingBytes + kRowsRedBytes);
-  const uint32_t bars = tc::smem_u32(smem + kRowsRingBytes + kRowsRedBytes + 32 * kRowsCols * 4);
+  const uint32_t bars = tc::smem_u32(smem + kRowsRingBytes + kRowsRedBytes + kRowsZBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, blk = blockIdx.x, chunk = blockIdx.y;
   const int rq = lane >> 2, g = lane & 3;
   const int k0 = warp * KPER;
@@ -278,6 +308,18 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
     for (int it = 0; it < kFirst; it++) load_stage(it, 2);
   __syncwarp();
 
+  // what the epilogue needs from global memory, fetched under the K loop
+  float e_c = 0.0f, e_b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (LSTM) {
+    if (threadIdx.x < 32 * 5) {
+      const int unit = blk * 5 + (threadIdx.x >> 5), w = chunk * 32 + (threadIdx.x & 31);
+      if (w < p.W) e_c = p.c[(size_t)w * HID + unit];
+#pragma unroll
+      for (int q = 0; q < 4; q++) e_b[q] = p.bias[q * HID + unit];
+    }
+  } else if (threadIdx.x < kRowsCols) {
+    e_b[0] = p.bias[blk * kRowsCols + threadIdx.x];
+  }
   float acc[4][5];
 #pragma unroll
   for (int r = 0; r < 4; r++)
@@ -337,18 +379,20 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
       const int row = threadIdx.x & 31, u = threadIdx.x >> 5, unit = blk * 5 + u, w = chunk * 32 + row;
       if (w < p.W) {
         const float *zr = z + row * kRowsCols;
-        const float zi = __fadd_rn(zr[u], p.bias[unit]), zo = __fadd_rn(zr[5 + u], p.bias[HID + unit]);
-        const float zf = __fadd_rn(zr[10 + u], p.bias[2 * HID + unit]), zc = __fadd_rn(zr[15 + u], p.bias[3 * HID + unit]);
+        const float zi = __fadd_rn(zr[u], e_b[0]), zo = __fadd_rn(zr[5 + u], e_b[1]);
+        const float zf = __fadd_rn(zr[10 + u], e_b[2]), zc = __fadd_rn(zr[15 + u], e_b[3]);
         const size_t i = (size_t)w * HID + unit;
-        const float cc = __fadd_rn(__fmul_rn(t_sigmoid(zf), p.c[i]), __fmul_rn(t_sigmoid(zi), t_tanhf(zc)));
+        const float cc = __fadd_rn(__fmul_rn(t_sigmoid(zf), e_c), __fmul_rn(t_sigmoid(zi), t_tanhf(zc)));
         p.nc[i] = cc;
         p.nht[t_idx(w, unit)] = __fmul_rn(t_sigmoid(zo), t_tanhf(cc));
       }
     }
   } else {
+    if (threadIdx.x < kRowsCols) z[32 * kRowsCols + threadIdx.x] = e_b[0];
+    __syncthreads();
     for (int i = threadIdx.x; i < 32 * kRowsCols; i += kRowsThreads) {
       const int row = i / kRowsCols, col = i - row * kRowsCols, w = chunk * 32 + row, n = blk * kRowsCols + col;
-      if (w < p.W) p.out[(size_t)w * HID + n] = __fadd_rn(z[i], p.bias[n]);
+      if (w < p.W) p.out[(size_t)w * HID + n] = __fadd_rn(z[i], z[32 * kRowsCols + col]);
     }
   }
 }
@@ -490,9 +534,9 @@ int tdt_round(fa_ctx *ctx, fa_tdt *d, TdtState &s, const fa_tensor *proj, int W,
   if (s.planes) {
     {
       LaunchScope ls(ctx, "tdt_joint_digits");
-      k_tdt_joint_digits<<<W, 256, 0, ctx->stream>>>((const float *)proj->dptr, t, T, (const float *)s.predproj->dptr,
-                                                   (const float *)d->out_scale->dptr, W, ctx->int8_limbs, (int8_t *)s.planes,
-                                                   (float *)s.rowscale);
+      FA_CHECK_CUDA(ctx, fa_launch_dep(ctx, k_tdt_joint_digits, dim3(W), dim3(256), 0, (const float *)proj->dptr, (const int *)t, T,
+                                       (const float *)s.predproj->dptr, (const float *)d->out_scale->dptr, W, ctx->int8_limbs,
+                                       (int8_t *)s.planes, (float *)s.rowscale));
     }
     FA_TRY(fa_matmul_int8_planes(ctx, (const int8_t *)s.planes, (const float *)s.rowscale, ctx->int8_limbs, W, d->out_q,
                                  (const float *)d->ones->dptr, LOGITS, HID, (const float *)d->out_b->dptr, (float *)s.logits->dptr));
@@ -510,11 +554,11 @@ int tdt_round(fa_ctx *ctx, fa_tdt *d, TdtState &s, const fa_tensor *proj, int W,
   const float *lg = (const float *)(logits ? logits->dptr : s.logits->dptr);
   {
     LaunchScope ls(ctx, "tdt_pick");
-    k_tdt_pick<<<W, 256, 0, ctx->stream>>>(lg, LOGITS, T, cap, t, emitted, last_tok, counts, ids, frames,
-                                           (const float *)d->embed->dptr, (float *)s.xt->dptr, (float *)s.h0t->dptr,
-                                           (const float *)s.nh0t->dptr, (float *)s.h1t->dptr, (const float *)s.nh1t->dptr,
-                                           (float *)s.c0->dptr, (float *)s.c1->dptr, (const float *)s.nc0->dptr,
-                                           (const float *)s.nc1->dptr, done);
+    FA_CHECK_CUDA(ctx, fa_launch_dep(ctx, k_tdt_pick, dim3(W), dim3(kPickThreads), 0, lg, LOGITS, T, cap, t, emitted, last_tok, counts,
+                                     ids, frames, (const float *)d->embed->dptr, (float *)s.xt->dptr, (float *)s.h0t->dptr,
+                                     (const float *)s.nh0t->dptr, (float *)s.h1t->dptr, (const float *)s.nh1t->dptr,
+                                     (float *)s.c0->dptr, (float *)s.c1->dptr, (const float *)s.nc0->dptr,
+                                     (const float *)s.nc1->dptr, done));
   }
   if (logits) FA_TRY(fa_free_tensor(ctx, logits));
   FA_LAUNCH_CHECK(ctx, "tdt_round");
