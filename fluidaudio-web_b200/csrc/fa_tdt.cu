@@ -240,12 +240,12 @@ __global__ void __launch_bounds__(256) k_tdt_embed(const float *__restrict__ emb
 // without a grid-wide step) and one chunk of 32 windows.  Its 16 warps split K; a warp streams its slice of the
 // activations (chunk-transposed: 128 bytes per k) and of the block's weights (packed [block][k][20] at upload: 80
 // bytes per k) through a private ring of shared-memory stages filled by bulk copies (cp.async.bulk, one elected
-// lane, one mbarrier per stage), so that no thread waits on a global load.  A lane holds a 4-row x 5-column
-// accumulator tile: per k one 16-byte read of activations, one 16-byte and one 4-byte read of weights (all
-// broadcast within the warp) and 20 FFMA.  Partial sums of the 16 warps meet in shared memory in a fixed order.
-constexpr int kRowsWarps = 16, kRowsThreads = kRowsWarps * 32, kRowsCols = 20, kRowsKS = 8, kRowsNS = 5;
+// lane, one mbarrier per stage), so that no thread waits on a global load.  A lane holds an 8-row x 10-column
+// accumulator tile for every fourth k of the slice (see the loop); the four k-quarters of a warp meet by shuffles
+// and the 16 warps in shared memory, both in a fixed order.
+constexpr int kRowsWarps = 16, kRowsThreads = kRowsWarps * 32, kRowsCols = 20, kRowsKS = 8, kRowsNS = 3, kRowsAhead = 2;
 constexpr int kRowsStageBytes = kRowsKS * (128 + kRowsCols * 4);                       // 1664
-constexpr int kRowsRingBytes = kRowsWarps * kRowsNS * kRowsStageBytes;                 // 133120
+constexpr int kRowsRingBytes = kRowsWarps * kRowsNS * kRowsStageBytes;                 // 79872
 constexpr int kRowsRedBytes = kRowsWarps * 32 * kRowsCols * 4;                         // 40960
 constexpr int kRowsZBytes = (32 + 1) * kRowsCols * 4;  // the block's sums, then one row for the projection's bias
 constexpr int kRowsSmem = kRowsRingBytes + kRowsRedBytes + kRowsZBytes + kRowsWarps * kRowsNS * 8;
@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
   float *z = reinterpret_cast<float *>(smem + kRowsRingBytes + kRowsRedBytes);
   const uint32_t bars = tc::smem_u32(smem + kRowsRingBytes + kRowsRedBytes + kRowsZBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, blk = blockIdx.x, chunk = blockIdx.y;
-  const int rq = lane >> 2, g = lane & 3;
+  const int ch = lane & 1, rq = (lane >> 1) & 3, kq = lane >> 3;  // gate pair, row octet, k quarter
   const int k0 = warp * KPER;
   const float *xsrc = (k0 < HID ? p.xa + ((size_t)chunk * HID + k0) * 32 : p.xb + ((size_t)chunk * HID + (k0 - HID)) * 32);
   const float *wsrc = p.wt + ((size_t)blk * K + k0) * kRowsCols;
@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
     if (what & 1) bulk_g2s(dst + kRowsKS * 128, wsrc + (size_t)it * kRowsKS * kRowsCols, kRowsKS * kRowsCols * 4, bar);
     if (what & 2) bulk_g2s(dst, xsrc + (size_t)it * kRowsKS * 32, kRowsKS * 128, bar);
   };
-  constexpr int kFirst = NLOAD < kRowsNS ? NLOAD : kRowsNS;
+  constexpr int kFirst = NLOAD < kRowsAhead ? NLOAD : kRowsAhead;
   if (lane == 0) {
     for (int s = 0; s < kRowsNS; s++) tc::mbar_init(my_bar + s * 8, 1);
     tc::fence_barrier_init();
@@ -320,57 +320,80 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
   } else if (threadIdx.x < kRowsCols) {
     e_b[0] = p.bias[blk * kRowsCols + threadIdx.x];
   }
-  float acc[4][5];
+  // A lane's accumulators: 8 rows x 10 columns (two gates x 5 units) over every fourth k of the warp's slice.
+  // Shared memory hands a warp 128 bytes per clock whether or not lanes share an address, so the operand bytes per
+  // FFMA decide the pace: this tile reads 18 values for 80 FFMA (4.5 clocks of shared-memory time per k and warp,
+  // under the 5 clocks the FFMA pipe needs), where a 4 x 5 tile on every k read 9 for 20 (9 clocks).
+  float acc[8][10];
 #pragma unroll
-  for (int r = 0; r < 4; r++)
+  for (int r = 0; r < 8; r++)
 #pragma unroll
-    for (int u = 0; u < 5; u++) acc[r][u] = 0.0f;
+    for (int c = 0; c < 10; c++) acc[r][c] = 0.0f;
   bool ok = true;
 #pragma unroll
   for (int it = 0; it < NLOAD; it++) {
     const int s = it % kRowsNS;
+    if (it + kRowsAhead < NLOAD) {  // the stage read in the iteration before this one takes the load two ahead
+      __syncwarp();
+      if (lane == 0) load_stage(it + kRowsAhead, 3);
+    }
     if (!__all_sync(0xffffffffu, tc::mbar_wait(my_bar + s * 8, (it / kRowsNS) & 1, p.wait_limit))) {
       ok = false;
       break;
     }
-    const float4 *xs = reinterpret_cast<const float4 *>(my + s * kRowsStageBytes) + rq;
+    const float4 *xs = reinterpret_cast<const float4 *>(my + s * kRowsStageBytes) + rq * 2;
     const float *ws = reinterpret_cast<const float *>(my + s * kRowsStageBytes + kRowsKS * 128);
 #pragma unroll
-    for (int kk = 0; kk < kRowsKS; kk++) {
-      const float4 xv = xs[kk * 8];
-      const float4 wv = *reinterpret_cast<const float4 *>(ws + kk * kRowsCols + g * 4);
-      const float w4 = ws[kk * kRowsCols + 16 + g];
-      const float xr[4] = {xv.x, xv.y, xv.z, xv.w};
+    for (int j = 0; j < kRowsKS / 4; j++) {
+      const int kk = kq + 4 * j;
+      const float4 xa = xs[kk * 8], xb = xs[kk * 8 + 1];
+      const float4 wa = *reinterpret_cast<const float4 *>(ws + kk * kRowsCols + ch * 8);
+      const float4 wb = *reinterpret_cast<const float4 *>(ws + kk * kRowsCols + ch * 8 + 4);
+      const float2 wc = *reinterpret_cast<const float2 *>(ws + kk * kRowsCols + 16 + ch * 2);
+      const float xr[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+      const float wr[10] = {wa.x, wa.y, wa.z, wa.w, wc.x, wb.x, wb.y, wb.z, wb.w, wc.y};
 #pragma unroll
-      for (int r = 0; r < 4; r++) {
-        acc[r][0] = fmaf(xr[r], wv.x, acc[r][0]);
-        acc[r][1] = fmaf(xr[r], wv.y, acc[r][1]);
-        acc[r][2] = fmaf(xr[r], wv.z, acc[r][2]);
-        acc[r][3] = fmaf(xr[r], wv.w, acc[r][3]);
-        acc[r][4] = fmaf(xr[r], w4, acc[r][4]);
-      }
-    }
-    if (it + kRowsNS < NLOAD) {
-      __syncwarp();  // every lane has read the stage before it is refilled
-      if (lane == 0) load_stage(it + kRowsNS, 3);
+      for (int r = 0; r < 8; r++)
+#pragma unroll
+        for (int c = 0; c < 10; c++) acc[r][c] = fmaf(xr[r], wr[c], acc[r][c]);
     }
   }
   if (!ok && lane == 0 && atomicCAS(p.status, 0, 7) == 0) {
     p.status[1] = (int)blockIdx.x;
     p.status[2] = warp;
   }
+  // The four k-quarters of a warp meet by two exchange steps that halve what a lane holds: lanes 16 apart split the
+  // rows (the lower lane keeps rows 0..3 of its eight), lanes 8 apart split the two gates.  A lane ends with 4 rows x
+  // 5 units of one gate, summed over the warp's whole K slice.
+  const bool b4 = (lane & 16) != 0, b3 = (lane & 8) != 0;
+  float a1[4][10];
+#pragma unroll
+  for (int r = 0; r < 4; r++)
+#pragma unroll
+    for (int c = 0; c < 10; c++) {
+      const float lo = acc[r][c], hi = acc[r + 4][c];
+      a1[r][c] = __fadd_rn(b4 ? hi : lo, __shfl_xor_sync(0xffffffffu, b4 ? lo : hi, 16));
+    }
+  float a2[4][5];
+#pragma unroll
+  for (int r = 0; r < 4; r++)
+#pragma unroll
+    for (int u = 0; u < 5; u++) {
+      const float lo = a1[r][u], hi = a1[r][u + 5];
+      a2[r][u] = __fadd_rn(b3 ? hi : lo, __shfl_xor_sync(0xffffffffu, b3 ? lo : hi, 8));
+    }
   // partial sums: red[warp][r*5+u][lane]
 #pragma unroll
   for (int r = 0; r < 4; r++)
 #pragma unroll
-    for (int u = 0; u < 5; u++) red[(warp * 20 + r * 5 + u) * 32 + lane] = acc[r][u];
+    for (int u = 0; u < 5; u++) red[(warp * 20 + r * 5 + u) * 32 + lane] = a2[r][u];
   __syncthreads();
   for (int i = threadIdx.x; i < 32 * kRowsCols; i += kRowsThreads) {
     float sum = red[i];
 #pragma unroll
     for (int w = 1; w < kRowsWarps; w++) sum = __fadd_rn(sum, red[w * 32 * kRowsCols + i]);
-    const int j = i >> 5, l = i & 31;  // j = r*5+u, l = rq*4+g
-    const int row = (l >> 2) * 4 + j / 5, col = (l & 3) * 5 + j % 5;
+    const int j = i >> 5, l = i & 31;  // j = r*5+u; l = lane: bit 0 gate pair, bits 1-2 row octet, bit 3 gate, bit 4 row half
+    const int row = ((l >> 1) & 3) * 8 + (l >> 4) * 4 + j / 5, col = ((l & 1) * 2 + ((l >> 3) & 1)) * 5 + j % 5;
     z[row * kRowsCols + col] = sum;
   }
   __syncthreads();
