@@ -269,6 +269,22 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                : "memory");
 }
 
+// Packed pair of f32 multiply-adds (sm_100): d.lo = a.lo * b.lo + c.lo, d.hi = a.hi * b.hi + c.hi, each fused and
+// rounded to nearest like fmaf.
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t dup_f32x2(float x) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(d) : "f"(x));
+  return d;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
 template <bool LSTM>
 __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p) {
   constexpr int K = LSTM ? 2 * HID : HID, KPER = K / kRowsWarps, NLOAD = KPER / kRowsKS;
@@ -322,22 +338,27 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
   }
   // A lane's accumulators: 8 rows x 10 columns (two gates x 5 units) over every fourth k of the warp's slice.
   // Shared memory hands a warp 128 bytes per clock whether or not lanes share an address, so the operand bytes per
-  // FFMA decide the pace: this tile reads 18 values for 80 FFMA (4.5 clocks of shared-memory time per k and warp,
-  // under the 5 clocks the FFMA pipe needs), where a 4 x 5 tile on every k read 9 for 20 (9 clocks).
-  float acc[8][10];
+  // FFMA decide the pace: this tile reads 18 values for 80 multiply-adds (4.5 clocks of shared-memory time per k and
+  // warp, under the 5 clocks the FFMA pipe needs), where a 4 x 5 tile on every k read 9 for 20 (9 clocks).
+  // The multiply-adds are packed pairs (fma.rn.f32x2) over two adjacent columns: the weight pairs are the 64-bit
+  // halves of the loads as they come, an activation is duplicated into both halves by one move; half the issue
+  // slots for the same arithmetic, each lane of a pair rounded exactly like a scalar FFMA.
+  // Column pairs: (A0,A1) (A2,A3) (B0,B1) (B2,B3) (A4,B4) for the lane's two gates A, B and units 0..4.
+  uint64_t acc2[8][5];
 #pragma unroll
   for (int r = 0; r < 8; r++)
 #pragma unroll
-    for (int c = 0; c < 10; c++) acc[r][c] = 0.0f;
+    for (int c = 0; c < 5; c++) acc2[r][c] = 0ull;
   bool ok = true;
-#pragma unroll
+  int s = 0;
+  uint32_t ph = 0;
+#pragma unroll 1
   for (int it = 0; it < NLOAD; it++) {
-    const int s = it % kRowsNS;
     if (it + kRowsAhead < NLOAD) {  // the stage read in the iteration before this one takes the load two ahead
       __syncwarp();
       if (lane == 0) load_stage(it + kRowsAhead, 3);
     }
-    if (!__all_sync(0xffffffffu, tc::mbar_wait(my_bar + s * 8, (it / kRowsNS) & 1, p.wait_limit))) {
+    if (!__all_sync(0xffffffffu, tc::mbar_wait(my_bar + s * 8, ph, p.wait_limit))) {
       ok = false;
       break;
     }
@@ -347,16 +368,28 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
     for (int j = 0; j < kRowsKS / 4; j++) {
       const int kk = kq + 4 * j;
       const float4 xa = xs[kk * 8], xb = xs[kk * 8 + 1];
-      const float4 wa = *reinterpret_cast<const float4 *>(ws + kk * kRowsCols + ch * 8);
-      const float4 wb = *reinterpret_cast<const float4 *>(ws + kk * kRowsCols + ch * 8 + 4);
-      const float2 wc = *reinterpret_cast<const float2 *>(ws + kk * kRowsCols + 16 + ch * 2);
+      const ulonglong2 wa = *reinterpret_cast<const ulonglong2 *>(ws + kk * kRowsCols + ch * 8);
+      const ulonglong2 wb = *reinterpret_cast<const ulonglong2 *>(ws + kk * kRowsCols + ch * 8 + 4);
+      const uint64_t wc = *reinterpret_cast<const uint64_t *>(ws + kk * kRowsCols + 16 + ch * 2);
       const float xr[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-      const float wr[10] = {wa.x, wa.y, wa.z, wa.w, wc.x, wb.x, wb.y, wb.z, wb.w, wc.y};
+      const uint64_t wp[5] = {wa.x, wa.y, wb.x, wb.y, wc};
 #pragma unroll
-      for (int r = 0; r < 8; r++)
+      for (int r = 0; r < 8; r++) {
+        const uint64_t xx = dup_f32x2(xr[r]);
 #pragma unroll
-        for (int c = 0; c < 10; c++) acc[r][c] = fmaf(xr[r], wr[c], acc[r][c]);
+        for (int c = 0; c < 5; c++) acc2[r][c] = ffma2(xx, wp[c], acc2[r][c]);
+      }
     }
+    if (++s == kRowsNS) { s = 0; ph ^= 1u; }
+  }
+  float acc[8][10];
+#pragma unroll
+  for (int r = 0; r < 8; r++) {
+    unpack_f32x2(acc2[r][0], acc[r][0], acc[r][1]);
+    unpack_f32x2(acc2[r][1], acc[r][2], acc[r][3]);
+    unpack_f32x2(acc2[r][2], acc[r][5], acc[r][6]);
+    unpack_f32x2(acc2[r][3], acc[r][7], acc[r][8]);
+    unpack_f32x2(acc2[r][4], acc[r][4], acc[r][9]);
   }
   if (!ok && lane == 0 && atomicCAS(p.status, 0, 7) == 0) {
     p.status[1] = (int)blockIdx.x;
