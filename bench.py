@@ -709,7 +709,7 @@ class TdtDecode:
     name = "parakeet_tdt_decode_32_windows_188_frames"
     metric = "tdt_decode_audio_seconds_per_second"
     unit = "audio-s/s"
-    dtype = "int8 out-matrix x 3 int8 activation digits (joint), f32 value+residue planes on kind::tf32 (LSTM)"
+    dtype = "int8 out-matrix x 3 int8 activation digits (joint), f32 multiply-adds (LSTM layers, projection)"
     nsets = 1
     graph = False  # the decode reads a device counter back every few rounds: eager steps
 

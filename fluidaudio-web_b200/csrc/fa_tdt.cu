@@ -7,13 +7,16 @@
 // (src/engines/asr-parakeet/gpu-decoder.js).  Windows are independent, so here they advance in LOCK-STEP, one joint
 // evaluation per window per round, and every product of a round is a matrix product over all windows:
 //
-//   joint in   J[w]   = relu(proj[w, t_w] + predproj[w]) * out_scale      (gather at each window's own frame t_w)
+//   joint in   J[w]   = relu(proj[w, t_w] + predproj[w]) * out_scale      (gather at each window's own frame t_w),
+//                                              written directly as the int8 product's digit planes and row scales
 //   logits     OUT    = J @ out_q + out_b      int8 out-matrix [640][8198], three int8 digits per activation row on
 //                                              kind::i8 (exact integer sums, f32-grade result)
 //   pick       argmax over the 8193 tokens and the 5 durations; emit / commit the candidate state / advance t_w
 //   predict    G0 = [embed[tok] | H0] @ [W0;R0]^T + b  -> cell -> (NH0, NC0);  G1 = [NH0 | H1] @ [W1;R1]^T + b -> cell
-//   predproj   = NH1 @ pred_w + pred_b         f32 weights on kind::tf32 with value + residue planes (f32-grade)
+//   predproj   = NH1 @ pred_w + pred_b         f32 weights, exact f32 multiply-adds (k_tdt_rows: one launch per LSTM
+//                                              layer with the cell in its epilogue, one for the projection)
 //
+// Six launches per round, each scheduled under its predecessor's tail (programmatic dependent launch).
 // The prediction network is evaluated for every window in every round: for a window that did not emit, its inputs
 // (committed state, last token) are unchanged, so the result is the same as the cached one the reference keeps.
 // A round is recorded once and replayed; the host looks at a device counter of finished windows every few rounds.

@@ -88,7 +88,8 @@ const char *fa_last_error(fa_ctx *ctx);
  * up; the kernel then records a status word, unwinds and returns, and the next fa_sync fails with
  * FA_ERR_TIMEOUT while the context stays usable), "tc_test_withhold_chunk" (-1 = off; k >= 0: test hook for that
  * path - in the NEXT tensor-core product only, one thread block never loads K chunk k of its first tile, so
- * the waits behind it run out; the product's result is then undefined). */
+ * the waits behind it run out; the product's result is then undefined.  fa_tdt_decode_proj consumes it the same
+ * way: one warp of its first prediction-network launch never loads stage k of its operand ring). */
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);
