@@ -13,6 +13,7 @@
 //                                              kind::i8 (exact integer sums, f32-grade result)
 //   pick       argmax over the 8193 tokens and the 5 durations; emit / commit the candidate state / advance t_w
 //   predict    G0 = [embed[tok] | H0] @ [W0;R0]^T + b  -> cell -> (NH0, NC0);  G1 = [NH0 | H1] @ [W1;R1]^T + b -> cell
+//              (embed[tok] @ W0^T + b is a table over the vocabulary made at creation: layer 0 sums over H0 only)
 //   predproj   = NH1 @ pred_w + pred_b         f32 weights, exact f32 multiply-adds (k_tdt_rows: one launch per LSTM
 //                                              layer with the cell in its epilogue, one for the projection)
 //
@@ -138,8 +139,8 @@ __global__ void __launch_bounds__(256) k_tdt_joint_digits(const float *__restric
 constexpr int kPickThreads = 1024;
 __global__ void __launch_bounds__(kPickThreads) k_tdt_pick(const float *__restrict__ logits, int ld, int T, int cap, int *__restrict__ t,
                                                            int *__restrict__ emitted, int *__restrict__ last_tok, int *__restrict__ counts,
-                                                           int *__restrict__ ids, int *__restrict__ frames, const float *__restrict__ embed,
-                                                           float *__restrict__ xt, float *__restrict__ h0t, const float *__restrict__ nh0t,
+                                                           int *__restrict__ ids, int *__restrict__ frames,
+                                                           float *__restrict__ h0t, const float *__restrict__ nh0t,
                                                            float *__restrict__ h1t, const float *__restrict__ nh1t, float *__restrict__ c0,
                                                            float *__restrict__ c1, const float *__restrict__ nc0, const float *__restrict__ nc1,
                                                            int *__restrict__ done_count) {
@@ -214,22 +215,13 @@ __global__ void __launch_bounds__(kPickThreads) k_tdt_pick(const float *__restri
     s_tok = tok;
   }
   __syncthreads();
-  if (s_tok != BLANK && tid < HID) {  // commit_state: H = NH, C = NC; the new token's embedding is layer 0's next input
+  if (s_tok != BLANK && tid < HID) {  // commit_state: H = NH, C = NC (layer 0 finds the new token through last_tok)
     const size_t i = t_idx(w, tid);
-    xt[i] = embed[(size_t)s_tok * HID + tid];
     h0t[i] = p_h0;
     h1t[i] = p_h1;
     c0[(size_t)w * HID + tid] = p_c0;
     c1[(size_t)w * HID + tid] = p_c1;
   }
-}
-
-// XT[:, w] = embed[last_tok[w]]
-__global__ void __launch_bounds__(256) k_tdt_embed(const float *__restrict__ embed, const int *__restrict__ last_tok,
-                                                   float *__restrict__ xt) {
-  const int w = blockIdx.x;
-  const float *e = embed + (size_t)last_tok[w] * HID;
-  for (int n = threadIdx.x; n < HID; n += blockDim.x) xt[t_idx(w, n)] = e[n];
 }
 
 // ---- k_tdt_rows: the prediction network's products, exact f32 ------------------------------------------------
@@ -257,6 +249,8 @@ struct RowsParams {
   const float *xa, *xb;  // activations for k < 640 and k >= 640, chunk-transposed
   const float *wt;       // [blocks][K][20]: per k the columns (g, u < 4) as g*4+u, then (g, u = 4) as 16+g
   const float *bias;     // LSTM: [4*HID] in gate order i, o, f, c; projection: [HID]
+  const float *tab;      // MODE 2: [VOCAB][4*HID], W0 . embed[token] + bias in gate order
+  const int *last_tok;   // MODE 2: [W]
   const float *c;        // LSTM: committed cell state [W][HID]
   float *nc, *nht;       // LSTM: candidate cell state [W][HID] and hidden state (chunk-transposed)
   float *out;            // projection: [W][HID]
@@ -288,9 +282,13 @@ __device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 
-template <bool LSTM>
+// MODE 0: the projection (K = 640, bias, row-major result).  MODE 1: an LSTM layer over [input | hidden] (K = 1280).
+// MODE 2: an LSTM layer whose input is an embedding row: K = 640 over the hidden state only, the input half of the
+// gates (and the bias) comes from a table indexed by each window's last token.
+template <int MODE>
 __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p) {
-  constexpr int K = LSTM ? 2 * HID : HID, KPER = K / kRowsWarps, NLOAD = KPER / kRowsKS;
+  constexpr bool LSTM = MODE != 0;
+  constexpr int K = MODE == 1 ? 2 * HID : HID, KPER = K / kRowsWarps, NLOAD = KPER / kRowsKS;
   static_assert(KPER % kRowsKS == 0 && HID % KPER == 0, "a warp's K slice is whole stages inside one operand");
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t *ring = smem;
@@ -333,8 +331,16 @@ __global__ void __launch_bounds__(kRowsThreads, 1) k_tdt_rows(const RowsParams p
     if (threadIdx.x < 32 * 5) {
       const int unit = blk * 5 + (threadIdx.x >> 5), w = chunk * 32 + (threadIdx.x & 31);
       if (w < p.W) e_c = p.c[(size_t)w * HID + unit];
+      if (MODE == 2) {
+        if (w < p.W) {
+          const float *row = p.tab + (size_t)p.last_tok[w] * 4 * HID;
 #pragma unroll
-      for (int q = 0; q < 4; q++) e_b[q] = p.bias[q * HID + unit];
+          for (int q = 0; q < 4; q++) e_b[q] = row[q * HID + unit];
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; q++) e_b[q] = p.bias[q * HID + unit];
+      }
     }
   } else if (threadIdx.x < kRowsCols) {
     e_b[0] = p.bias[blk * kRowsCols + threadIdx.x];
@@ -464,13 +470,13 @@ __global__ void k_fill_int(int *p, int n, int v) {
 }  // namespace
 
 struct fa_tdt {
-  fa_tensor *embed = nullptr, *wr[2] = {nullptr, nullptr}, *bsum[2] = {nullptr, nullptr}, *pred_w = nullptr, *pred_b = nullptr;
+  fa_tensor *gate_tab = nullptr, *wr[2] = {nullptr, nullptr}, *bsum1 = nullptr, *pred_w = nullptr, *pred_b = nullptr;
   fa_tensor *out_b = nullptr, *out_scale = nullptr, *ones = nullptr, *out_w = nullptr;
   fa_bytes *out_q = nullptr;
 };
 
 static void tdt_release(fa_ctx *ctx, fa_tdt *d) {
-  fa_tensor *ts[] = {d->embed, d->wr[0], d->wr[1], d->bsum[0], d->bsum[1], d->pred_w, d->pred_b, d->out_b, d->out_scale, d->ones, d->out_w};
+  fa_tensor *ts[] = {d->gate_tab, d->wr[0], d->wr[1], d->bsum1, d->pred_w, d->pred_b, d->out_b, d->out_scale, d->ones, d->out_w};
   for (fa_tensor *t : ts)
     if (t) fa_free_tensor(ctx, t);
   if (d->out_q) fa_free_bytes(ctx, d->out_q);
@@ -484,25 +490,48 @@ extern "C" int fa_tdt_create(fa_ctx *ctx, const float *embed, const float *l0w, 
   FA_REQUIRE(ctx, embed && l0w && l0r && l0b && l1w && l1r && l1b && pred_w && pred_b && out_b, "tdtCreate: NULL weight pointer");
   FA_REQUIRE(ctx, (out_q && out_scale) || out_w, "tdtCreate: needs the out matrix as int8 rows + scales or as f32");
   fa_tdt *d = new fa_tdt();
-  int rc = fa_upload_f32(ctx, embed, VOCAB, HID, &d->embed);
-  // k_tdt_rows' weight packing: block b owns hidden units 5b..5b+4 (their four gates, ONNX order i, o, f, c) over
-  // K = 1280: rows 0..639 multiply the layer input, rows 640..1279 the committed hidden state
+  // k_tdt_rows' weight packing: block b owns hidden units 5b..5b+4 (their four gates, ONNX order i, o, f, c).
+  // Layer 1 runs over K = 1280: rows 0..639 multiply the layer input, rows 640..1279 the committed hidden state.
+  // Layer 0's input is an embedding row, so the input half of its gates is a table over the vocabulary, made here
+  // once: gate_tab[token] = embed[token] . W0^T + (b[g] + b[4*HID + g]) (lib.rs:139 adds the two biases first), on the
+  // CUDA-core f32 kernel; the layer itself then runs over the hidden state only (K = 640).
   auto pos = [](int g, int u) { return u < 4 ? g * 4 + u : 16 + g; };
   const float *lw[2] = {l0w, l1w}, *lr[2] = {l0r, l1r}, *lb[2] = {l0b, l1b};
   std::vector<float> tmp((size_t)2 * HID * 4 * HID), bs(4 * HID);
+  int rc = FA_OK;
   for (int l = 0; l < 2 && rc == FA_OK; l++) {
+    const int K = l == 0 ? HID : 2 * HID;
     for (int blk = 0; blk < HID / 5; blk++)
-      for (int k = 0; k < 2 * HID; k++) {
-        float *dst = &tmp[((size_t)blk * 2 * HID + k) * kRowsCols];
+      for (int k = 0; k < K; k++) {
+        float *dst = &tmp[((size_t)blk * K + k) * kRowsCols];
         for (int g = 0; g < 4; g++)
           for (int u = 0; u < 5; u++) {
             const size_t row = (size_t)g * HID + blk * 5 + u;
-            dst[pos(g, u)] = k < HID ? lw[l][row * HID + k] : lr[l][row * HID + (k - HID)];
+            dst[pos(g, u)] = l == 0 ? lr[l][row * HID + k] : (k < HID ? lw[l][row * HID + k] : lr[l][row * HID + (k - HID)]);
           }
       }
-    for (int g = 0; g < 4 * HID; g++) bs[g] = lb[l][g] + lb[l][4 * HID + g];  // lib.rs:139: b[g] + b[4*HID + g] first
-    rc = fa_upload_f32(ctx, tmp.data(), (HID / 5) * 2 * HID, kRowsCols, &d->wr[l]);
-    if (rc == FA_OK) rc = fa_upload_f32(ctx, bs.data(), 1, 4 * HID, &d->bsum[l]);
+    rc = fa_upload_f32(ctx, tmp.data(), (HID / 5) * K, kRowsCols, &d->wr[l]);
+  }
+  for (int g = 0; g < 4 * HID; g++) bs[g] = lb[1][g] + lb[1][4 * HID + g];
+  if (rc == FA_OK) rc = fa_upload_f32(ctx, bs.data(), 1, 4 * HID, &d->bsum1);
+  if (rc == FA_OK) {
+    fa_tensor *emb = nullptr, *w0t = nullptr, *b0 = nullptr;
+    for (int g = 0; g < 4 * HID; g++) {
+      bs[g] = lb[0][g] + lb[0][4 * HID + g];
+      for (int k = 0; k < HID; k++) tmp[(size_t)k * 4 * HID + g] = l0w[(size_t)g * HID + k];
+    }
+    rc = fa_upload_f32(ctx, embed, VOCAB, HID, &emb);
+    if (rc == FA_OK) rc = fa_upload_f32(ctx, tmp.data(), HID, 4 * HID, &w0t);
+    if (rc == FA_OK) rc = fa_upload_f32(ctx, bs.data(), 1, 4 * HID, &b0);
+    if (rc == FA_OK) rc = fa_alloc(ctx, VOCAB, 4 * HID, &d->gate_tab);
+    if (rc == FA_OK)
+      rc = fa_simt_gemm(ctx, (const float *)emb->dptr, w0t->dptr, 0, nullptr, (const float *)b0->dptr, FA_ACT_NONE, nullptr,
+                        (float *)d->gate_tab->dptr, VOCAB, 4 * HID, HID);
+    const std::string msg = ctx->err;
+    fa_tensor *ts[] = {emb, w0t, b0};
+    for (fa_tensor *t : ts)
+      if (t) fa_free_tensor(ctx, t);
+    if (rc != FA_OK) ctx->err = msg;
   }
   if (rc == FA_OK) {  // the projection [k][n]: block b owns columns 20b..20b+19
     for (int blk = 0; blk < HID / kRowsCols; blk++)
@@ -540,8 +569,8 @@ extern "C" int fa_tdt_free(fa_ctx *ctx, fa_tdt *d) {
 namespace {
 
 struct TdtState {
-  // chunk-transposed [ceil(W/32)][HID][32]: embedding of the last token, committed and candidate hidden states
-  fa_tensor *xt = nullptr, *h0t = nullptr, *nh0t = nullptr, *h1t = nullptr, *nh1t = nullptr;
+  // chunk-transposed [ceil(W/32)][HID][32]: committed and candidate hidden states
+  fa_tensor *h0t = nullptr, *nh0t = nullptr, *h1t = nullptr, *nh1t = nullptr;
   fa_tensor *c0 = nullptr, *c1 = nullptr, *nc0 = nullptr, *nc1 = nullptr, *predproj = nullptr, *J = nullptr;  // [W][HID]
   fa_tensor *logits = nullptr;                   // [W][LOGITS] when the joint's digit planes are written here
   void *planes = nullptr, *rowscale = nullptr;   // the int8 product's row operand (see k_tdt_joint_digits)
@@ -550,38 +579,39 @@ struct TdtState {
   size_t ints_bytes = 0;
 };
 
-template <bool LSTM>
+template <int MODE>
 int tdt_rows(fa_ctx *ctx, const RowsParams &p, int blocks, int W, int withhold) {
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[LSTM]) {
-    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tdt_rows<LSTM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowsSmem));
-    attr_set[LSTM] = true;
+  static bool attr_set[3] = {false, false, false};
+  if (!attr_set[MODE]) {
+    FA_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_tdt_rows<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowsSmem));
+    attr_set[MODE] = true;
   }
   RowsParams q = p;
   q.W = W;
   q.status = ctx->dev_status;
   q.wait_limit = ctx->wait_limit;
   q.withhold = withhold;
-  LaunchScope ls(ctx, LSTM ? "tdt_lstm" : "tdt_pred");
-  FA_CHECK_CUDA(ctx, fa_launch_dep(ctx, k_tdt_rows<LSTM>, dim3(blocks, ceil_div(W, 32)), dim3(kRowsThreads), kRowsSmem, q));
+  LaunchScope ls(ctx, MODE ? "tdt_lstm" : "tdt_pred");
+  FA_CHECK_CUDA(ctx, fa_launch_dep(ctx, k_tdt_rows<MODE>, dim3(blocks, ceil_div(W, 32)), dim3(kRowsThreads), kRowsSmem, q));
   return FA_OK;
 }
 
 // predict + compute_predproj for every window, from the committed state and the last token's embedding
-int tdt_predict(fa_ctx *ctx, fa_tdt *d, TdtState &s, int W) {
+int tdt_predict(fa_ctx *ctx, fa_tdt *d, TdtState &s, int W, const int *last_tok) {
   const int withhold = ctx->tc_withhold_chunk;
   ctx->tc_withhold_chunk = -1;  // one launch only
   RowsParams p{};
-  p.xa = (const float *)s.xt->dptr, p.xb = (const float *)s.h0t->dptr, p.wt = (const float *)d->wr[0]->dptr;
-  p.bias = (const float *)d->bsum[0]->dptr, p.c = (const float *)s.c0->dptr, p.nc = (float *)s.nc0->dptr, p.nht = (float *)s.nh0t->dptr;
-  FA_TRY(tdt_rows<true>(ctx, p, HID / 5, W, withhold));
+  p.xa = (const float *)s.h0t->dptr, p.xb = p.xa, p.wt = (const float *)d->wr[0]->dptr;
+  p.tab = (const float *)d->gate_tab->dptr, p.last_tok = last_tok;
+  p.c = (const float *)s.c0->dptr, p.nc = (float *)s.nc0->dptr, p.nht = (float *)s.nh0t->dptr;
+  FA_TRY(tdt_rows<2>(ctx, p, HID / 5, W, withhold));
   p.xa = (const float *)s.nh0t->dptr, p.xb = (const float *)s.h1t->dptr, p.wt = (const float *)d->wr[1]->dptr;
-  p.bias = (const float *)d->bsum[1]->dptr, p.c = (const float *)s.c1->dptr, p.nc = (float *)s.nc1->dptr, p.nht = (float *)s.nh1t->dptr;
-  FA_TRY(tdt_rows<true>(ctx, p, HID / 5, W, -1));
+  p.bias = (const float *)d->bsum1->dptr, p.c = (const float *)s.c1->dptr, p.nc = (float *)s.nc1->dptr, p.nht = (float *)s.nh1t->dptr;
+  FA_TRY(tdt_rows<1>(ctx, p, HID / 5, W, -1));
   RowsParams q{};
   q.xa = (const float *)s.nh1t->dptr, q.xb = q.xa, q.wt = (const float *)d->pred_w->dptr, q.bias = (const float *)d->pred_b->dptr;
   q.out = (float *)s.predproj->dptr;
-  FA_TRY(tdt_rows<false>(ctx, q, HID / kRowsCols, W, -1));
+  FA_TRY(tdt_rows<0>(ctx, q, HID / kRowsCols, W, -1));
   FA_LAUNCH_CHECK(ctx, "tdt_predict");
   return FA_OK;
 }
@@ -614,14 +644,14 @@ int tdt_round(fa_ctx *ctx, fa_tdt *d, TdtState &s, const fa_tensor *proj, int W,
   {
     LaunchScope ls(ctx, "tdt_pick");
     FA_CHECK_CUDA(ctx, fa_launch_dep(ctx, k_tdt_pick, dim3(W), dim3(kPickThreads), 0, lg, LOGITS, T, cap, t, emitted, last_tok, counts,
-                                     ids, frames, (const float *)d->embed->dptr, (float *)s.xt->dptr, (float *)s.h0t->dptr,
+                                     ids, frames, (float *)s.h0t->dptr,
                                      (const float *)s.nh0t->dptr, (float *)s.h1t->dptr, (const float *)s.nh1t->dptr,
                                      (float *)s.c0->dptr, (float *)s.c1->dptr, (const float *)s.nc0->dptr,
                                      (const float *)s.nc1->dptr, done));
   }
   if (logits) FA_TRY(fa_free_tensor(ctx, logits));
   FA_LAUNCH_CHECK(ctx, "tdt_round");
-  return tdt_predict(ctx, d, s, W);
+  return tdt_predict(ctx, d, s, W, last_tok);
 }
 
 }  // namespace
@@ -645,7 +675,7 @@ extern "C" int fa_tdt_decode_proj(fa_ctx *ctx, fa_tdt *d, const fa_tensor *proj,
   int rc = FA_OK, rounds = 0;
   auto alloc = [&](int r, int c, fa_tensor **t) { return rc == FA_OK ? (rc = fa_alloc(ctx, r, c, t)) : rc; };
   const int wpad = ceil_div(W, 32) * 32;
-  alloc(wpad, HID, &s.xt), alloc(wpad, HID, &s.h0t), alloc(wpad, HID, &s.nh0t), alloc(wpad, HID, &s.h1t), alloc(wpad, HID, &s.nh1t),
+  alloc(wpad, HID, &s.h0t), alloc(wpad, HID, &s.nh0t), alloc(wpad, HID, &s.h1t), alloc(wpad, HID, &s.nh1t),
       alloc(W, HID, &s.c0), alloc(W, HID, &s.c1), alloc(W, HID, &s.nc0), alloc(W, HID, &s.nc1), alloc(W, HID, &s.predproj),
       alloc(W, HID, &s.J);
   const size_t n_int = (size_t)4 * W + 4 + (size_t)2 * W * cap;
@@ -658,12 +688,11 @@ extern "C" int fa_tdt_decode_proj(fa_ctx *ctx, fa_tdt *d, const fa_tensor *proj,
   int *t = (int *)s.ints, *last_tok = t + 2 * W, *done = t + 4 * W;
   if (rc == FA_OK) {
     // decode_proj :290-294: zero state, last token = blank, predict + predproj once
-    fa_tensor *z[] = {s.xt, s.h0t, s.nh0t, s.h1t, s.nh1t, s.c0, s.c1, s.nc0, s.nc1};
+    fa_tensor *z[] = {s.h0t, s.nh0t, s.h1t, s.nh1t, s.c0, s.c1, s.nc0, s.nc1};
     for (fa_tensor *x : z) cudaMemsetAsync(x->dptr, 0, (size_t)x->rows * x->cols * 4, ctx->stream);
     cudaMemsetAsync(s.ints, 0, n_int * 4, ctx->stream);
     k_fill_int<<<ceil_div(W, 256), 256, 0, ctx->stream>>>(last_tok, W, BLANK);
-    k_tdt_embed<<<W, 256, 0, ctx->stream>>>((const float *)d->embed->dptr, last_tok, (float *)s.xt->dptr);
-    rc = tdt_predict(ctx, d, s, W);
+    rc = tdt_predict(ctx, d, s, W, last_tok);
   }
   // one round eagerly (first-use caches of the weights), then the round as a recorded batch, replayed
   if (rc == FA_OK) rc = tdt_round(ctx, d, s, proj, W, T, cap);
