@@ -26,6 +26,8 @@ SIGNATURES = {
     "fa_ctx_destroy": [P],
     "fa_ctx_set_option": [P, C.c_char_p, C.c_longlong],
     "fa_ctx_stream": [P, PP],
+    "fa_ctx_mark": [P],
+    "fa_ctx_wait_mark": [P, P],
     "fa_sync": [P],
     "fa_launch_count": [P, ULLP],
     "fa_upload_f32": [P, P, I, I, PP],

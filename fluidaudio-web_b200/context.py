@@ -525,6 +525,14 @@ class CudaContext:
         return {"bytes": self.memStats()["poolBytes"]}
 
     # -- extras for harnesses ------------------------------------------------------------------
+    def mark(self) -> None:
+        """Record a point in this context's stream (all that was enqueued so far) that other contexts can wait for."""
+        self._check(self._lib.fa_ctx_mark(self._h))
+
+    def waitMark(self, other: "CudaContext") -> None:
+        """What this context enqueues from now on waits, on the device, for the point `other` marked last."""
+        self._check(self._lib.fa_ctx_wait_mark(self._h, other._h))
+
     def sync(self) -> None:
         self._check(self._lib.fa_sync(self._h))
 

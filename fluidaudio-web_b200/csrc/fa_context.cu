@@ -106,6 +106,7 @@ extern "C" int fa_ctx_destroy(fa_ctx *ctx) {
   for (auto &kv : ctx->blocks) cudaFree(kv.first);
   cudaFree(ctx->dev_status);
   cudaFree(ctx->gemv_tickets);
+  if (ctx->mark) cudaEventDestroy(ctx->mark);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return FA_OK;
@@ -197,6 +198,29 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
 extern "C" int fa_ctx_stream(fa_ctx *ctx, void **stream_out) {
   if (!ctx || !stream_out) return fa_fail(ctx, FA_ERR_INVALID, "fa_ctx_stream: NULL argument");
   *stream_out = (void *)ctx->stream;
+  return FA_OK;
+}
+
+// A context is one stream; two contexts on one GPU run concurrently.  fa_ctx_mark records a point in ctx's stream
+// (everything enqueued so far), fa_ctx_wait_mark makes everything ctx enqueues from now on wait, on the device, for
+// the point `other` marked last (no host wait; a context that never marked is not waited for).  This is how a pipeline
+// of contexts keeps its copies concurrent while its forwards run one after the other (engines/fastconformer.py).
+extern "C" int fa_ctx_mark(fa_ctx *ctx) {
+  if (!ctx) return fa_fail(ctx, FA_ERR_INVALID, "fa_ctx_mark: NULL context");
+  FA_REQUIRE(ctx, !ctx->capturing, "fa_ctx_mark: not allowed while a graph is being recorded");
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!ctx->mark) FA_CHECK_CUDA(ctx, cudaEventCreateWithFlags(&ctx->mark, cudaEventDisableTiming));
+  FA_CHECK_CUDA(ctx, cudaEventRecord(ctx->mark, ctx->stream));
+  return FA_OK;
+}
+
+extern "C" int fa_ctx_wait_mark(fa_ctx *ctx, fa_ctx *other) {
+  if (!ctx || !other) return fa_fail(ctx, FA_ERR_INVALID, "fa_ctx_wait_mark: NULL context");
+  FA_REQUIRE(ctx, !ctx->capturing, "fa_ctx_wait_mark: not allowed while a graph is being recorded");
+  FA_REQUIRE(ctx, ctx->device == other->device, "fa_ctx_wait_mark: contexts on different devices (%d, %d)", ctx->device, other->device);
+  if (!other->mark || other == ctx) return FA_OK;
+  FA_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
+  FA_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, other->mark, 0));
   return FA_OK;
 }
 

@@ -109,6 +109,7 @@ struct fa_ctx {
   int device = 0;
   int sm_count = 0;
   cudaStream_t stream = nullptr;
+  cudaEvent_t mark = nullptr;      // fa_ctx_mark / fa_ctx_wait_mark: a point in this context's stream other contexts can wait for
   std::string err;
   bool in_batch = false;
   unsigned long long launches = 0;

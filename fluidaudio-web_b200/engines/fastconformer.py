@@ -329,9 +329,12 @@ def encode_batch(ctx, enc, mels: List[np.ndarray], layer_hook=None, use_fast: bo
 
 class PipelinedEncoder:
     """encode_batch for a stream of window batches with the host<->device copies hidden: `depth` contexts (one
-    CUDA stream each) on one GPU hold a recorded forward each - upload of the batch's windows from page-locked
-    host memory, the forward, the read-back of the frames into a page-locked result array - and take the batches
-    in turn, so the copies of one batch run while another batch computes and the host never copies a frame.
+    CUDA stream each) on one GPU take the batches in turn.  A slot holds two recordings - the upload of the batch's
+    windows from page-locked host memory (with the log-mel front end when the windows are PCM), and the forward - and
+    reads the frames back into a page-locked result array behind them.  The forwards of different slots are ordered on the device (each waits for the point the slot
+    before it marked behind its forward), so that one forward has the whole GPU at a time, while the copies of a
+    batch run under the forward of another and the host never copies a frame.  (Two whole forwards left to run side
+    by side take each other's SMs kernel by kernel: every persistent product then runs on what the other leaves.)
     submit() launches one batch and hands back the frames of the batch submitted `depth - 1` calls earlier (None
     until the pipeline is full) as a view of that slot's result array: valid until the next submit(), which
     re-launches that slot.  flush() drains the pipeline and returns copies.
@@ -348,17 +351,26 @@ class PipelinedEncoder:
         self.ctxs, self.encs, self.mel_len = list(ctxs), list(encs), mel_len
         self.from_pcm, self.post = from_pcm, post
         self.host = [host_windows(s) for s in range(len(self.ctxs))]
-        self.batches, self.results, self.pending = [], [], []
+        self.uploads, self.batches, self.outs, self.results, self.pending = [], [], [], [], []
         for s, ctx in enumerate(self.ctxs):
-            x = self._body(s, None)  # once eagerly: weight repacks and pool growth stay out of the recording
+            m0 = self._upload(s)
+            x = self._forward(s, m0)  # once eagerly: weight repacks and pool growth stay out of the recordings
             res = ctx.pinnedArray(x.rows * x.cols)
             ctx.freeTensor(x)
-            b, _ = ctx.recordBatch(lambda s=s, res=res: self._body(s, res))
+            for m in (m0 if isinstance(m0, list) else [m0]):
+                ctx.freeTensor(m)
+            u, mels = ctx.recordBatch(lambda s=s: self._upload(s))
+            b, x = ctx.recordBatch(lambda s=s, mels=mels: self._forward(s, mels))
+            self.uploads.append(u)
             self.batches.append(b)
+            self.outs.append(x)
             self.results.append(res)
         self.next = 0
+        self.last = None  # the slot whose forward was enqueued last
 
-    def _body(self, s, res):
+    def _upload(self, s):
+        """The slot's copies and, from PCM, the log-mel front end: small thread blocks that are not ordered against the
+        other slot's forward and fill the SMs its launches leave idle."""
         ctx = self.ctxs[s]
         h = ctx.pushArena()
         if isinstance(self.host[s], np.ndarray):  # one page-locked array holding all windows of the slot back to back
@@ -369,19 +381,32 @@ class PipelinedEncoder:
             if isinstance(mels, list):
                 mels = ctx.concatRows(mels) if len(mels) > 1 else mels[0]
             mels = ctx.logMelWindows(mels, self.encs[s]["cfg"]["melBins"])
+        for m in (mels if isinstance(mels, list) else [mels]):
+            ctx.pin(m)
+        ctx.popArena(h)
+        return mels
+
+    def _forward(self, s, mels):
+        ctx = self.ctxs[s]
+        h = ctx.pushArena()
         x, _ = encode_batch(ctx, self.encs[s], mels)
         if self.post is not None:
             x = self.post(s, x)
-        if res is not None:
-            ctx.downloadAsync(x, res)
         ctx.pin(x)
         ctx.popArena(h)
         return x
 
     def submit(self):
         s = self.next
+        ctx = self.ctxs[s]
         self.next = (s + 1) % len(self.ctxs)
+        self.uploads[s].launch()
+        if self.last is not None and self.last != s:
+            ctx.waitMark(self.ctxs[self.last])  # this forward starts when the one before it has finished
         self.batches[s].launch()
+        ctx.mark()
+        self.last = s
+        ctx.downloadAsync(self.outs[s], self.results[s])
         self.pending.append(s)
         if len(self.pending) >= len(self.ctxs):
             return self._read(self.pending.pop(0))
@@ -397,5 +422,5 @@ class PipelinedEncoder:
         return res
 
     def free(self):
-        for b in self.batches:
+        for b in self.batches + self.uploads:
             b.free()

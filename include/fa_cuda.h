@@ -93,6 +93,13 @@ const char *fa_last_error(fa_ctx *ctx);
 int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value);
 /* cudaStream_t of the context, for callers that order their own work after it. */
 int fa_ctx_stream(fa_ctx *ctx, void **stream_out);
+/* Ordering between two contexts (streams) of one GPU, on the device, with no host wait: fa_ctx_mark records a point
+ * in ctx's stream (all that was enqueued so far); fa_ctx_wait_mark makes what ctx enqueues from now on wait for the
+ * point `other` marked last (a no-op when other never marked).  Not part of the reference interface, whose one
+ * queue orders everything (src/gpu/scheduler.js:17-60); here it lets a pipeline of contexts overlap the copies of
+ * one batch with the forward of another while the forwards themselves run one after the other. */
+int fa_ctx_mark(fa_ctx *ctx);
+int fa_ctx_wait_mark(fa_ctx *ctx, fa_ctx *other);
 /* Block until every enqueued op has finished; surfaces asynchronous kernel errors. */
 int fa_sync(fa_ctx *ctx);
 /* Number of kernels this library has launched on ctx since creation. */

@@ -138,3 +138,35 @@ def test_row_operand_from_before_a_recording_is_repacked_per_replay(pkg):
         batch.free()
     finally:
         ctx.destroy()
+
+
+def test_mark_and_wait_mark_between_contexts(pkg):
+    """Ordering between two contexts of one GPU: waiting for a context that never marked is a no-op, a marked point
+    can be waited for, and neither call is accepted while a recording is open (it would not be part of it)."""
+    a, b = pkg.CudaContext(0), pkg.CudaContext(0)
+    try:
+        rng = np.random.default_rng(9)
+        x, w, X, Wt = _product(a, rng)
+        b.waitMark(a)  # nothing marked yet
+        y = a.matmul(X, Wt)
+        a.mark()
+        b.waitMark(a)
+        x2, w2, X2, Wt2 = _product(b, rng)
+        y2 = b.matmul(X2, Wt2)
+        assert np.abs(b.download(y2).reshape(x2.shape[0], -1) - x2 @ w2).max() <= 2e-2
+        assert np.abs(a.download(y).reshape(x.shape[0], -1) - x @ w).max() <= 2e-2
+
+        def body():
+            with pytest.raises(pkg.CudaError):
+                a.mark()
+            with pytest.raises(pkg.CudaError):
+                a.waitMark(b)
+            return a.matmul(X, Wt)
+
+        batch, _ = a.recordBatch(body)
+        batch.launch()
+        a.sync()
+        batch.free()
+    finally:
+        a.destroy()
+        b.destroy()
