@@ -152,6 +152,7 @@ struct fa_ctx {
   std::vector<ProfileRec> prof;
   // log-mel front end: device tables (filterbank, window, twiddles) per mel count, built on first use
   std::unordered_map<int, void *> mel_tables;
+  std::unordered_map<int, int> mel_spans;  // widest filter of each mel count's filterbank, in bins
   // device-side status word written by kernels whose bounded waits ran out
   int *dev_status = nullptr;
   int *gemv_tickets = nullptr;  // zeroed arrival counters of the split-K GEMV (self-resetting)
