@@ -8,12 +8,14 @@
 //   even/odd samples + real-spectrum reconstruction | power stored as f32 | slaney filterbank (f32 weights) summed in
 //   a double over each filter's non-zero span | log(. + guard) stored as f32 | per mel row over floor(N/160) frames:
 //   mean, variance with N-1, (x - mean) / (sqrt(var) + 1e-5), sums in doubles.
-// Doubles cost nothing that matters here (48k frames of 256-point FFTs are ~0.5 GFLOP per 32-window batch), and they
-// keep the result within rounding of the reference's.  Multiplies and adds are kept separate (no fused multiply-add)
+// Doubles are affordable here (48k frames of 256-point FFTs are ~1 GFLOP per 32-window batch; the kernel is paced by
+// shared-memory traffic and instruction issue, not by the FP64 pipe) and they keep the result within rounding of the
+// reference's.  Multiplies and adds are kept separate (no fused multiply-add)
 // where the JavaScript has them separate.
 //
-// One warp transforms one frame in shared memory; the filterbank, window and twiddle tables are built on the host
-// in doubles with the reference's formulas, once per context and mel count.
+// One warp transforms one frame (three stages in registers, five in shared memory: see k_mel_raw); the filterbank,
+// window and twiddle tables are built on the host in doubles with the reference's formulas, once per context and
+// mel count.
 #include <cmath>
 
 #include "fa_internal.cuh"
