@@ -779,7 +779,10 @@ class AsrPipeline(Encoder):
     """The reference's transcription pipeline for one batch of windows (src/engines/asr-parakeet/pipeline.js:32-61):
     16 kHz samples -> log-mel front end -> FastConformer encoder -> the joint's encoder projection riding the same
     submission (1024 -> 640) -> greedy TDT decoding of the 32 windows in lock step -> token ids and emission frames on
-    the host.  Everything between the upload of the samples and the read-back of the ids stays on the device.  Weights
+    the host.  Everything between the upload of the samples and the read-back of the ids stays on the device.  Batches
+    alternate between two slots (contexts) of the GPU, the decode of one batch running under the encoder forward of the
+    next, as the reference overlaps its decode workers with the next group's encode (pipeline.js `pipelined`); a step
+    enqueues one batch and lands the token ids of the batch before it.  Weights
     random-init (encoder seed 3, decoder seed 5 with a bias on the blank logit so that most frames emit nothing)."""
 
     name = "parakeet_asr_pipeline_pcm_to_token_ids_batch32"
@@ -790,32 +793,50 @@ class AsrPipeline(Encoder):
         super().setup(ctx)
         from fluidaudio_web_b200.engines import tdt_decoder
 
+        import __graft_entry__ as ge
+        from fluidaudio_web_b200.engines import asr_pipeline
+
         self.tdt_weights = tdt_decoder.synth_tdt_weights(5)
         self.dec = tdt_decoder.TdtDecoder(ctx, self.tdt_weights, int8=True)
-        self.dtype = "encoder: f16 x f16 -> f32; joint: int8 out-matrix x 3 int8 activation digits"
-        self.pcm_host = self._pcm_slot(ctx)
+        self.dtype = "encoder: f16 x f16 -> f32; joint: int8 out-matrix x 3 int8 activation digits; prediction network f32"
         self.tokens = 0
+        # one batch, stage after stage on one stream: the kernels a step launches
+        l0 = ctx.launchCount()
+        h = ctx.pushArena()
+        x, tsub = self.fc.encode_batch(ctx, self.enc, self.dev_mels)
+        self._count(self.dec.decode_proj(self.dec.project(x), self.W, tsub))
+        ctx.popArena(h)
+        self.launches_per_step = ctx.launchCount() - l0
+        # the pipelined form the steps run: two slots (contexts), the decode of one batch under the forward of the next
+        ctx2 = ge.load_package().CudaContext(ctx.device)
+        enc2 = self._load(ctx2)
+        dec2 = tdt_decoder.TdtDecoder(ctx2, self.tdt_weights, int8=True)
+        pcm2 = ctx2.upload(self._audio, self.W, self.n_samples)
+        mels2 = ctx2.logMelWindows(pcm2, 128)
+        ctx2.freeTensor(pcm2)
+        slots = [self._pcm_slot(ctx), self._pcm_slot(ctx2)]
+        args = ([ctx, ctx2], [self.enc, enc2], [self.dec, dec2])
+        self.pipe_dev = asr_pipeline.PipelinedAsr(*args, None, self.mel_len, self.W, from_pcm=False, resident=[self.dev_mels, mels2])
+        self.pipe_e2e = asr_pipeline.PipelinedAsr(*args, lambda s: slots[s], self.n_samples, self.W, from_pcm=True)
 
-    def _decode(self, ctx, mels):
-        x, tsub = self.fc.encode_batch(ctx, self.enc, mels)
-        out = self.dec.decode_proj(self.dec.project(x), self.W, tsub)
-        self.tokens = sum(len(i) for i, _ in out)
-        return out
+    def _count(self, out):
+        if out is not None:
+            self.tokens = sum(len(i) for i, _ in out)
 
     def step_device(self, ctx):
-        h = ctx.pushArena()
-        self._decode(ctx, self.dev_mels)
-        ctx.popArena(h)
+        self._count(self.pipe_dev.submit())  # windows' features resident in HBM; token ids of the batch before land on the host
+
+    def device_drain(self):
+        for out in self.pipe_dev.flush():
+            self._count(out)
 
     def step_e2e(self, ctx):
-        h = ctx.pushArena()
-        pcm = ctx.upload(self.pcm_host, self.W, self.n_samples)
-        out = self._decode(ctx, ctx.logMelWindows(pcm, 128))
-        ctx.popArena(h)
+        out = self.pipe_e2e.submit()
+        self._count(out)
         return out
 
     def e2e_drain(self):
-        return []
+        return self.pipe_e2e.flush()
 
     def e2e_bytes(self):
         return self.W * self.n_samples * 4, 2 * 4 * max(1, self.tokens) + 4 * self.W
@@ -1219,13 +1240,15 @@ def run_cuda(args):
         if world > 1:
             torch.distributed.barrier()
 
-    def timed(step_fn, steps):
+    def timed(step_fn, steps, drain=None):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         with torch.cuda.stream(stream):
             e0.record(stream)
             for _ in range(steps):
                 step_fn(ctx)
+            if drain is not None:
+                drain()  # a pipelined workload still owes its last batch (a host call that returns when it is done)
             e1.record(stream)
         ctx.sync()
         torch.cuda.synchronize()
@@ -1248,14 +1271,17 @@ def run_cuda(args):
     else:
         wl.step_device(ctx)
         batch = None
-    launches_per_step = ctx.launchCount() - l0
+    launches_per_step = getattr(wl, "launches_per_step", ctx.launchCount() - l0)
     for _ in range(3):
         batch.launch() if use_graph else wl.step_device(ctx)
+    drain = getattr(wl, "device_drain", None)
+    if drain is not None:
+        drain()
     ctx.sync()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = timed((lambda _ctx: batch.launch()) if use_graph else wl.step_device, args.steps)
+    ms = timed((lambda _ctx: batch.launch()) if use_graph else wl.step_device, args.steps, drain)
     launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     if use_graph:
@@ -1269,6 +1295,8 @@ def run_cuda(args):
     ctx.startProfile(200000)
     for _ in range(psteps):
         wl.step_device(ctx)
+    if drain is not None:
+        drain()
     prof = ctx.endProfile()
     peaks = measured_peaks()
     roof = wl.roofline(prof, peaks)

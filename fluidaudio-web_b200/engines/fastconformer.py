@@ -343,23 +343,31 @@ class PipelinedEncoder:
     f32 arrays (time-major windows, see mel_time_major) that slot's recording uploads on every launch - the caller
     fills them before submit()."""
 
-    def __init__(self, ctxs, encs, host_windows, mel_len: int, from_pcm: bool = False, post=None):
+    def __init__(self, ctxs, encs, host_windows, mel_len: int, from_pcm: bool = False, post=None, resident=None, read_back: bool = True):
         """from_pcm: the host windows hold 16 kHz PCM (mel_len = samples per window) and the recording starts with the
         log-mel front end on the device (optional member logMelWindows; the reference runs it in host workers,
         src/engines/asr-parakeet/mel-scheduler.js).  post(slot, frames) -> tensor: an op riding the batch whose result
-        is read back instead of the frames (the joint's encoder projection, src/engines/asr-parakeet/pipeline.js:57-61)."""
+        is read back instead of the frames (the joint's encoder projection, src/engines/asr-parakeet/pipeline.js:57-61).
+        resident: one device tensor of features per slot, in place of host windows (nothing is uploaded).
+        read_back=False: the result stays on the device (self.outs[slot]) for a consumer on the slot's stream."""
         self.ctxs, self.encs, self.mel_len = list(ctxs), list(encs), mel_len
-        self.from_pcm, self.post = from_pcm, post
-        self.host = [host_windows(s) for s in range(len(self.ctxs))]
+        self.from_pcm, self.post, self.resident, self.read_back = from_pcm, post, resident, read_back
+        self.host = [host_windows(s) for s in range(len(self.ctxs))] if resident is None else None
         self.uploads, self.batches, self.outs, self.results, self.pending = [], [], [], [], []
         for s, ctx in enumerate(self.ctxs):
-            m0 = self._upload(s)
-            x = self._forward(s, m0)  # once eagerly: weight repacks and pool growth stay out of the recordings
-            res = ctx.pinnedArray(x.rows * x.cols)
-            ctx.freeTensor(x)
-            for m in (m0 if isinstance(m0, list) else [m0]):
-                ctx.freeTensor(m)
-            u, mels = ctx.recordBatch(lambda s=s: self._upload(s))
+            if resident is not None:
+                x = self._forward(s, resident[s])
+                res = ctx.pinnedArray(x.rows * x.cols) if read_back else None
+                ctx.freeTensor(x)
+                u, mels = None, resident[s]
+            else:
+                m0 = self._upload(s)
+                x = self._forward(s, m0)  # once eagerly: weight repacks and pool growth stay out of the recordings
+                res = ctx.pinnedArray(x.rows * x.cols) if read_back else None
+                ctx.freeTensor(x)
+                for m in (m0 if isinstance(m0, list) else [m0]):
+                    ctx.freeTensor(m)
+                u, mels = ctx.recordBatch(lambda s=s: self._upload(s))
             b, x = ctx.recordBatch(lambda s=s, mels=mels: self._forward(s, mels))
             self.uploads.append(u)
             self.batches.append(b)
@@ -396,17 +404,23 @@ class PipelinedEncoder:
         ctx.popArena(h)
         return x
 
-    def submit(self):
-        s = self.next
+    def _launch(self, s):
+        """Enqueue slot s: its copies, then its forward behind the forward enqueued last, then the read-back."""
         ctx = self.ctxs[s]
-        self.next = (s + 1) % len(self.ctxs)
-        self.uploads[s].launch()
+        if self.uploads[s] is not None:
+            self.uploads[s].launch()
         if self.last is not None and self.last != s:
             ctx.waitMark(self.ctxs[self.last])  # this forward starts when the one before it has finished
         self.batches[s].launch()
         ctx.mark()
         self.last = s
-        ctx.downloadAsync(self.outs[s], self.results[s])
+        if self.read_back:
+            ctx.downloadAsync(self.outs[s], self.results[s])
+
+    def submit(self):
+        s = self.next
+        self.next = (s + 1) % len(self.ctxs)
+        self._launch(s)
         self.pending.append(s)
         if len(self.pending) >= len(self.ctxs):
             return self._read(self.pending.pop(0))
@@ -423,4 +437,5 @@ class PipelinedEncoder:
 
     def free(self):
         for b in self.batches + self.uploads:
-            b.free()
+            if b is not None:
+                b.free()

@@ -59,3 +59,44 @@ def test_projection_then_decode_from_encoder_frames(ctx, pkg):
     want = TdtOracle(w, int8=True, threads=4).decode_proj_batch(proj_host, W, T)
     for wi in range(W):
         assert got[wi][0].tolist() == want[wi][0].tolist() and got[wi][1].tolist() == want[wi][1].tolist()
+
+
+def test_pipelined_asr_decodes_under_the_next_forward(pkg):
+    """PipelinedAsr (two slots: the decode of one batch runs under the encoder forward of the next) hands back, one
+    call late, the tokens the stages give when run one after the other on one stream."""
+    from fluidaudio_web_b200.engines import asr_pipeline, fastconformer as fc, synth, tdt_decoder as td
+
+    cfg = dict(synth.PARAKEET_06B, layers=1)
+    ew = synth.encoder_weights(cfg, seed=3)
+    dw = td.synth_tdt_weights(5)
+    W, n = 2, 16000 * 4
+    ctx, ctx2 = pkg.CudaContext(0), pkg.CudaContext(0)
+    try:
+        cs = (ctx, ctx2)
+        encs = [fc.load_encoder(c, ew) for c in cs]
+        decs = [td.TdtDecoder(c, dw, int8=True) for c in cs]
+        batches = [synth.synth_audio(W, samples=n, seed=20 + b) for b in range(3)]
+        host = [c.pinnedArray(W * n) for c in cs]
+        want = []
+        for a in batches:
+            h = ctx.pushArena()
+            x, tsub = fc.encode_batch(ctx, encs[0], ctx.logMelWindows(ctx.upload(a, W, n), cfg["melBins"]))
+            want.append(decs[0].decode_proj(decs[0].project(x), W, tsub))
+            ctx.popArena(h)
+        pipe = asr_pipeline.PipelinedAsr(cs, encs, decs, lambda s: host[s], n, W, from_pcm=True)
+        got = []
+        for b, a in enumerate(batches):
+            host[b % 2][:] = a.reshape(-1)
+            out = pipe.submit()
+            if out is not None:
+                got.append(out)
+        got += pipe.flush()
+        pipe.free()
+        assert len(got) == 3
+        for g, r in zip(got, want):
+            for wi in range(W):
+                assert g[wi][0].tolist() == r[wi][0].tolist() and g[wi][1].tolist() == r[wi][1].tolist()
+        assert sum(len(i) for o in want for i, _ in o) > 0
+    finally:
+        ctx.destroy()
+        ctx2.destroy()
