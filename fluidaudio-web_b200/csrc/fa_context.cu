@@ -182,6 +182,11 @@ extern "C" int fa_ctx_set_option(fa_ctx *ctx, const char *key, long long value) 
     ctx->wait_limit = (unsigned)value;
     return FA_OK;
   }
+  if (!strcmp(key, "tc_tma_add")) {
+    FA_REQUIRE(ctx, value == 0 || value == 1, "tc_tma_add must be 0 or 1");
+    ctx->tc_tma_add = (int)value;
+    return FA_OK;
+  }
   if (!strcmp(key, "tc_test_withhold_chunk")) {
     FA_REQUIRE(ctx, value >= -1 && value < 4096, "tc_test_withhold_chunk must be -1 or a K-chunk index");
     ctx->tc_withhold_chunk = (int)value;

@@ -110,6 +110,9 @@ struct TcParams {
   int tma_out;          // 1: results leave through shared-memory slabs and TMA stores (see epilogue_tile)
   uint32_t slab_f16_off;  // byte offset of the f16 slabs behind the f32 slabs (0 when no f32 result is stored)
   int nslab;              // store slabs per epilogue warp and result kind: 2 or 4
+  int tma_add;            // 1: the residual operand comes in through the copy engine, block by block, into residual slabs
+                          // behind the store slabs (see epilogue_tile_resadd); needs tma_out and an f32 result
+  uint32_t slab_res_off;  // byte offset of the residual slabs from the first store slab
   uint32_t wait_limit;  // polls before a barrier wait gives up (fa_ctx::wait_limit)
   int withhold_kb;      // >= 0: CTA 0 never loads this K chunk of its first tile, so the waits downstream of it run
                         // out (the way the bounded-wait path is tested without faulting the GPU); -1 in normal use
@@ -311,6 +314,111 @@ __device__ __forceinline__ void epilogue_tile(const TcParams &p, uint32_t lane_a
   }
 }
 
+// The fast epilogue below for a launch with a residual operand, with the residual brought in by the copy engine: the
+// [16][32] f32 block a warp is going to add is loaded (TMA, one mbarrier per slab) two blocks ahead into one of three
+// residual slabs of the warp, and read from shared memory when its turn comes.  As plain loads the residual cost a
+// product with K = 1024 four microseconds of nineteen: sixteen global loads of dependent latency per block in warps
+// that are paced by their own instruction count, where a block now costs sixteen shared-memory reads (19.1 -> 17.4 us
+// at M = 6016, N = K = 1024; 60.4 -> 57.0 at N = 4096).  The loads share the copy engine's ingest with the operand
+// tiles, which is what paces the main loop: a residual tile is 20 % of a tile's operand bytes at K = 1024 and 5 % at
+// K = 4096, where the exchange no longer pays (43.9 -> 44.2 us) - the launch uses this path up to K = 2048.  One block
+// of look-ahead (two slabs) gave 18.4 us: the look-ahead is latency cover, not the ring's depth.
+constexpr int kResSlabs = 3;
+__device__ __forceinline__ void epilogue_tile_resadd(const TcParams &p, uint32_t lane_addr, int n0, int m0, int quad, int lane,
+                                                     int half, int r16, int c16, const CUtensorMap *map_o,
+                                                     const CUtensorMap *map_o16, const CUtensorMap *map_add, uint32_t slab_f32,
+                                                     uint32_t slab_f16, uint32_t slab_res, uint32_t res_bar0, uint32_t &slab_turn,
+                                                     uint32_t &res_turn) {
+  const int n = n0 + quad * 32 + lane;
+  const bool n_ok = n < p.N;
+  const float cs = (p.colscale && n_ok) ? p.colscale[n] : 1.0f;
+  const float bs = (p.bias && n_ok) ? p.bias[n] : 0.0f;
+  constexpr int kStep = 4 * kEpiWarps;  // rows between a warp's consecutive blocks
+  int c = half * 16;
+  if (c >= p.MT || m0 + c >= p.M) return;
+  auto has = [&](int cc) { return cc < p.MT && m0 + cc < p.M; };
+
+  // residual rows m0+cc .. +15 of this warp's 32 columns into the residual slab of turn t (its last reader was turn
+  // t - 3, whose reads ended before that turn's stores were issued)
+  auto res_issue = [&](int cc, uint32_t t) {
+    if (lane == 0) {
+      const uint32_t b = t % kResSlabs, bar = res_bar0 + b * 8u;
+      mbar_expect_tx(bar, 2048u);
+      tma_load_2d(slab_res + b * 2048u, map_add, n0 + quad * 32, m0 + cc, bar);
+    }
+  };
+  auto finish = [&](int cc, const uint32_t (&vr)[16], uint32_t t) {
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = fmaf(__uint_as_float(vr[j]), cs, bs);
+    act16(v, p.act);
+    const uint32_t rb = t % kResSlabs;
+    if (!mbar_wait(res_bar0 + rb * 8u, (t / kResSlabs) & 1u, p.wait_limit) && lane == 0) report_timeout(p.status, 9, cc);
+    {
+      const uint32_t src = slab_res + rb * 2048u + (uint32_t)lane * 4u;
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        float r;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(r) : "r"(src + (uint32_t)j * 128u) : "memory");
+        v[j] += r;
+      }
+    }
+    const uint32_t b = slab_turn & (uint32_t)(p.nslab - 1);
+    slab_turn++;
+    if (p.nslab == 4) tma_store_wait_read<3>(); else tma_store_wait_read<1>();  // lane 0 owns the groups
+    __syncwarp();
+    if (p.out16) {
+      const uint32_t d16 = slab_f16 + b * 1024u + (uint32_t)lane * 2u;
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        asm volatile("st.shared.b16 [%0], %1;" ::"r"(d16 + (uint32_t)j * 64u), "h"(__half_as_ushort(__float2half_rn(v[j]))) : "memory");
+    }
+    {
+      const uint32_t dst = slab_f32 + b * 2048u + (uint32_t)lane * 4u;
+#pragma unroll
+      for (int j = 0; j < 16; j++) asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + (uint32_t)j * 128u), "f"(v[j]) : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    {
+      const uint32_t lead = lane == 0 ? 1u : 0u;
+      const int gn = n0 + quad * 32 + c16;
+      if (p.out16) tma_store_3d_w(lead, map_o16, slab_f16 + b * 1024u, gn & 63, r16 + m0 + cc, gn >> 6);
+      tma_store_2d_w(lead, map_o, slab_f32 + b * 2048u, n0 + quad * 32, m0 + cc);
+      tma_store_commit();
+    }
+  };
+
+  uint32_t va[16], vb[16];
+  uint32_t turn = res_turn;
+  constexpr int kAhead = kResSlabs - 1;  // blocks a residual load is issued ahead of its use
+#pragma unroll
+  for (int i = 0; i < kAhead; i++)
+    if (has(c + i * kStep)) res_issue(c + i * kStep, turn + (uint32_t)i);
+  tmem_ld16(lane_addr + (uint32_t)c, va);
+  for (;;) {
+    tmem_ld_wait();
+    int cn = c + kStep;
+    bool more = has(cn);
+    if (more) tmem_ld16(lane_addr + (uint32_t)cn, vb);
+    if (has(c + kAhead * kStep)) res_issue(c + kAhead * kStep, turn + kAhead);
+    finish(c, va, turn);
+    turn++;
+    if (!more) break;
+    c = cn;
+    tmem_ld_wait();
+    cn = c + kStep;
+    more = has(cn);
+    if (more) tmem_ld16(lane_addr + (uint32_t)cn, va);
+    if (has(c + kAhead * kStep)) res_issue(c + kAhead * kStep, turn + kAhead);
+    finish(c, vb, turn);
+    turn++;
+    if (!more) break;
+    c = cn;
+  }
+  res_turn = turn;
+}
+
 // The same epilogue for the common case (float accumulators, one output per accumulator, no row scale / row bias, no
 // K split), software-pipelined: the TMEM read and the residual loads of a warp's NEXT 16-row block are issued before
 // the current block is finished, so their latencies (a few hundred cycles for the TMEM read, an L2 round trip for the
@@ -449,7 +557,8 @@ __device__ __forceinline__ void epilogue_tile_fast(const TcParams &p, uint32_t l
 template <int KIND>
 __global__ void __launch_bounds__(tc_threads<KIND>(), 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-          const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_o16, const TcParams p) {
+          const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_o16,
+          const __grid_constant__ CUtensorMap map_add, const TcParams p) {
   constexpr int MK = KIND == 4 ? 2 : (KIND >= 2 ? 0 : KIND);  // MMA kind and epilogue arithmetic (KIND 3: f16 with peer stores)
   constexpr bool kDeq = KIND == 2 || KIND == 5;               // a weights tile is made in shared memory from a raw tile
   constexpr uint32_t kWTiles = KIND == 4 ? 2u : 1u;  // weight tiles per stage (KIND 4: value and residue planes)
@@ -473,7 +582,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                                                             // the vector loads of the reduction (3*stages+4 may be odd)
   // store slabs of the epilogue warps (tma_out mode only, never together with the split-K tile): per warp two
   // [16][32] f32 slabs, then per warp two [16][32] f16 slabs
-  const uint32_t slabs = (tmem_slot + 16u + 127u) & ~127u;
+  const uint32_t res_bars = (tmem_slot + 16u + 7u) & ~7u;  // tma_add: one barrier per epilogue warp and residual slab
+  const uint32_t slabs = (tmem_slot + 16u + (p.tma_add ? (uint32_t)(kEpiWarps * kResSlabs) * 8u : 0u) + 127u) & ~127u;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int acc_cols = p.limb_sum ? p.MT : q_rows;
@@ -494,6 +604,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       mbar_init(acc_full(b), 1);
       mbar_init(acc_empty(b), kEpiWarps);
     }
+    if (p.tma_add)
+      for (int i = 0; i < kEpiWarps * kResSlabs; i++) mbar_init(res_bars + (uint32_t)i * 8u, 1);
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(0u) : "memory");
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -503,6 +615,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       if (!p.skip_f32) tma_prefetch_desc(&map_o);
       if (p.out16) tma_prefetch_desc(&map_o16);
     }
+    if (p.tma_add) tma_prefetch_desc(&map_add);
   }
   if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
   tc_fence_before();
@@ -852,7 +965,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
   } else {
     // ---- epilogue: TMEM -> registers -> global (or -> smem partial in split-K mode) -------------
     const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
-    uint32_t lt = 0, slab_turn = 0, cl_rank = 0;
+    uint32_t lt = 0, slab_turn = 0, cl_rank = 0, res_turn = 0;
     if (p.splitk > 1) {
       asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cl_rank));
       cluster_wait_all();
@@ -882,7 +995,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
       if (!kDeq && MK != 1 && p.splitk == 1 && !p.rowscale && !p.rowbias)
       {
-        if (p.add)
+        if (KIND == 0 && p.tma_add)
+          epilogue_tile_resadd(p, lane_addr, n0, m0, quad, lane, half, r16, c16, &map_o, &map_o16, &map_add, slab_f32, slab_f16,
+                               slabs + p.slab_res_off + (uint32_t)(ew * kResSlabs) * 2048u, res_bars + (uint32_t)(ew * kResSlabs) * 8u,
+                               slab_turn, res_turn);
+        else if (p.add)
           epilogue_tile_fast<KIND == 3, true>(p, lane_addr, n0, m0, quad, lane, half, outb, r16, c16, &map_o, &map_o16, slab_f32,
                                               slab_f16, slab_turn);
         else
@@ -983,7 +1100,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 // one CTA.
 __global__ void __launch_bounds__(kThreads, 1)
 k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-               const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_o16, const TcParams p) {
+               const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_o16,
+               const __grid_constant__ CUtensorMap map_add, const TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int half_rows = p.MT / 2;  // activation rows this CTA stages
@@ -993,7 +1111,8 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   auto acc_empty = [&](int b) { return bars + (uint32_t)(2 * p.stages + 2 + b) * 8u; };
   const uint32_t tmem_slot = bars + (uint32_t)(2 * p.stages + 4) * 8u;
   const uint32_t abort_flag = tmem_slot + 4u;
-  const uint32_t slabs = (tmem_slot + 16u + 127u) & ~127u;
+  const uint32_t res_bars = (tmem_slot + 16u + 7u) & ~7u;  // tma_add: one barrier per epilogue warp and residual slab
+  const uint32_t slabs = (tmem_slot + 16u + (p.tma_add ? (uint32_t)(kEpiWarps * kResSlabs) * 8u : 0u) + 127u) & ~127u;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
@@ -1013,6 +1132,8 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(acc_full(b), 1);
       mbar_init(acc_empty(b), 2 * kEpiWarps);  // both CTAs' epilogue warps arrive on the leader's barrier
     }
+    if (p.tma_add)
+      for (int i = 0; i < kEpiWarps * kResSlabs; i++) mbar_init(res_bars + (uint32_t)i * 8u, 1);
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(abort_flag), "r"(0u) : "memory");
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -1022,6 +1143,7 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!p.skip_f32) tma_prefetch_desc(&map_o);
       if (p.out16) tma_prefetch_desc(&map_o16);
     }
+    if (p.tma_add) tma_prefetch_desc(&map_add);
   }
   if (warp == 1) tmem_alloc2(tmem_slot, tmem_cols);
   tc_fence_before();
@@ -1148,7 +1270,7 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ---- epilogue (both CTAs): this CTA's 128 output columns x all MT rows of the pair's tile ----
     const int ew = warp - 2, quad = warp & 3, half = ew >> 2;
-    uint32_t lt = 0, slab_turn = 0;
+    uint32_t lt = 0, slab_turn = 0, res_turn = 0;
     const uint32_t slab_f32 = slabs + (uint32_t)(ew * p.nslab) * 2048u, slab_f16 = slabs + p.slab_f16_off + (uint32_t)(ew * p.nslab) * 1024u;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += npairs, lt++) {
@@ -1161,7 +1283,11 @@ k_tc_gemm_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * acc_stride + ((uint32_t)(quad * 32) << 16);
-      if (!p.rowscale && !p.rowbias && p.add)
+      if (p.tma_add)
+        epilogue_tile_resadd(p, lane_addr, n0, m0, quad, lane, half, 0, 0, &map_o, &map_o16, &map_add, slab_f32, slab_f16,
+                             slabs + p.slab_res_off + (uint32_t)(ew * kResSlabs) * 2048u, res_bars + (uint32_t)(ew * kResSlabs) * 8u,
+                             slab_turn, res_turn);
+      else if (!p.rowscale && !p.rowbias && p.add)
         epilogue_tile_fast<false, true>(p, lane_addr, n0, m0, quad, lane, half, p.out, 0, 0, &map_o, &map_o16, slab_f32, slab_f16,
                                         slab_turn);
       else if (!p.rowscale && !p.rowbias)
@@ -1586,14 +1712,21 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
                ((uintptr_t)out & 15) == 0 && (!ep.out16 || ((uintptr_t)ep.out16 & 127) == 0) && M >= 16)
                   ? 1
                   : 0;
+  // the residual through the copy engine (epilogue_tile_resadd): the plain f16 product with an f32 result and TMA stores
+  const bool want_add = KIND == 0 && p.tma_out && ep.add && !p.skip_f32 && !ep.rowscale && !ep.rowbias && (N & 3) == 0 && K <= 2048 &&
+                        ((uintptr_t)ep.add & 15) == 0 && ctx->tc_tma_add;
   // two store slabs per warp and result kind, four when that leaves the ring as deep
   auto slab_bytes_for = [&](int nslab) {
     const size_t f16_off = p.skip_f32 ? 0 : (size_t)kEpiWarps * nslab * 2048;
     return p.tma_out ? f16_off + (p.out16 ? (size_t)kEpiWarps * nslab * 1024 : 0) + 128 : (size_t)0;
   };
-  const size_t tail_fixed = (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.splitk * p.split_rb * 16 * 128 * 4 : 0) + 1024;
+  const size_t res_bytes = want_add ? (size_t)kEpiWarps * kResSlabs * 2048 : 0;
+  const size_t tail_fixed = (size_t)(3 * 12 + 4) * 8 + 16 + (p.splitk > 1 ? (size_t)p.splitk * p.split_rb * 16 * 128 * 4 : 0) + 1024 +
+                            (want_add ? (size_t)kEpiWarps * kResSlabs * 8 : 0) + res_bytes;
   const int st2 = (int)((227 * 1024 - tail_fixed - slab_bytes_for(2)) / stage_bytes), st4 = (int)((227 * 1024 - tail_fixed - slab_bytes_for(kSlabsMax)) / stage_bytes);
   p.nslab = (p.tma_out && (st4 == st2 || st4 >= 12)) ? kSlabsMax : 2;
+  p.tma_add = want_add ? 1 : 0;
+  p.slab_res_off = (uint32_t)(slab_bytes_for(p.nslab) - 128);
   p.slab_f16_off = p.skip_f32 ? 0u : (uint32_t)(kEpiWarps * p.nslab) * 2048u;
   const size_t slab_bytes = slab_bytes_for(p.nslab);
   const size_t tail_bytes = tail_fixed + slab_bytes;
@@ -1635,6 +1768,8 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     if (!p.skip_f32) FA_TRY(tc::make_tmap_out_f32(ctx, &map_o, (const float *)out, (uint64_t)M, (uint64_t)N, (uint64_t)p.ldc));
     if (p.out16) FA_TRY(tc::make_tmap_out_f16_packed(ctx, &map_o16, p.out16, (uint64_t)p.o16_rows, (uint64_t)(N >> 6)));
   }
+  CUtensorMap map_add = map_w;
+  if (p.tma_add) FA_TRY(tc::make_tmap_out_f32(ctx, &map_add, ep.add, (uint64_t)M, (uint64_t)N, (uint64_t)N));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[2];
   cfg.blockDim = dim3(tc_threads<KIND>());
@@ -1655,7 +1790,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
     cfg.numAttrs = 2;
     {
       LaunchScope ls(ctx, "tc_gemm_f16_pair");
-      cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm_pair, map_w, map_a, map_o, map_o16, p);
+      cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm_pair, map_w, map_a, map_o, map_o16, map_add, p);
       if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm_pair: %s", cudaGetErrorString(e));
     }
     FA_LAUNCH_CHECK(ctx, "tc_gemm_pair");
@@ -1674,7 +1809,7 @@ int launch_tc(fa_ctx *ctx, const void *w_packed, const void *a_packed, int limbs
   }
   {
     LaunchScope ls(ctx, KIND == 0 ? "tc_gemm_f16" : (KIND == 1 ? "tc_gemm_i8" : (KIND == 2 ? "tc_gemm_nbits" : (KIND == 4 ? "tc_gemm_tf32x3" : (KIND == 5 ? "tc_gemm_i8w_f16a" : "tc_gemm_f16_scatter")))));
-    cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, map_o, map_o16, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_tc_gemm<KIND>, map_w, map_a, map_o, map_o16, map_add, p);
     if (e != cudaSuccess) return fa_fail(ctx, FA_ERR_CUDA, "launch tc_gemm: %s", cudaGetErrorString(e));
   }
   FA_LAUNCH_CHECK(ctx, "tc_gemm");

@@ -126,6 +126,7 @@ struct fa_ctx {
   int f16_hilo_rows = 64;  // f16-weight products with at most this many rows use value+residue row planes
   unsigned wait_limit = 1u << 24;  // polls before a device-side barrier wait gives up (about a second)
   int tc_withhold_chunk = -1;      // test hook, one launch: see TcParams::withhold_kb
+  int tc_tma_add = 1;              // residual operand of the large f16 products through the copy engine (TcParams::tma_add)
   int tc_pair = 1;       // f16 products with more tiles than SMs run on CTA pairs sharing one 256-lane MMA
   int tc_tma_store = 1;  // results of plain tensor-core products leave through shared-memory slabs and TMA stores (0: per-lane stores)
   int tc_tile_rows = 0, tc_split_k = 0;  // tuning overrides for sub-wave tensor-core products (0 = chosen by the cost model)

@@ -81,6 +81,8 @@ const char *fa_last_error(fa_ctx *ctx);
  * share one 256-lane tcgen05 MMA, each loading half of the activation rows of the pair's tile; results are
  * bit-identical to the one-block kernel, 0 selects that kernel), "tc_tma_store" (0/1, default 1: results of plain
  * tensor-core products leave through shared-memory slabs and copy-engine stores; 0 = per-lane stores, same values),
+ * "tc_tma_add" (0/1, default 1: the residual operand of an f16-weight product with K <= 2048 and an f32 result reaches
+ * the epilogue through copy-engine loads into shared memory, two blocks ahead; 0 = plain loads, same values),
  * "tc_tile_rows" / "tc_split_k" (0 = automatic, the default; otherwise rows per tile - 128..256 for a pair's tile -
  * and CTAs per K-split cluster of tensor-core products with less than one wave of tiles) and "gemv_ctas_per_sm"
  * (1..4, default 2: resident thread blocks per SM the int4 GEMV sizes its grid for) are tuning overrides of choices

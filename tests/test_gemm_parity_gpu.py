@@ -501,6 +501,8 @@ PAIR_CASES = [
     (2500, 320, 1024, dict(bias=True)),                          # ragged M (last tile 196 of 224 rows), ragged K chunk
     (3000, 1024, 768, dict(bias=True, act="silu", operand_only=True)),  # f16 operand out only
     (2111, 512, 1280, dict(bias=True, add=True)),                # residual read, odd row count
+    (6016, 1024, 1024, dict(add=True)),                          # the encoder's residual products at their real size
+    (2050, 192, 768, dict(bias=True, add=True, act="silu")),     # residual behind an activation, two rows in the last block
     (19001, 64, 256, dict(bias=True)),                           # one K chunk per tile, one column pair, ragged last tile
     (4097, 96, 512, dict(act="relu")),                           # K not a multiple of the 64-element chunk
 ]
@@ -510,7 +512,9 @@ PAIR_CASES = [
 def test_pair_kernel_matches_one_cta_kernel_and_oracle(ctx, M, K, N, kw):
     """Products with more tiles than SMs run on pairs of thread blocks sharing one 256-lane MMA (option "tc_pair",
     default on).  The pair kernel accumulates the same K chunks in the same order into the same accumulators as the
-    one-block kernel, so the two must agree bit for bit; a sample of rows is also checked against the oracle."""
+    one-block kernel, so the two must agree bit for bit; a sample of rows is also checked against the oracle.  A
+    residual operand reaches the epilogue through the copy engine (option "tc_tma_add", default on) or by plain loads:
+    the same additions in the same order, bit for bit as well."""
     rng = np.random.default_rng(M + N)
     a = rng.standard_normal((M, K)).astype(np.float32)
     w = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float16).astype(np.float32)
@@ -518,9 +522,11 @@ def test_pair_kernel_matches_one_cta_kernel_and_oracle(ctx, M, K, N, kw):
     r = rng.standard_normal((M, N)).astype(np.float32) if kw.get("add") else None
     outs = []
     try:
-        for pair, tma_store in ((1, 1), (0, 1), (1, 0)):  # pairs, one-block kernel, pairs with per-lane stores
+        # pairs, one-block kernel, pairs with per-lane stores, pairs with the residual read by plain loads
+        for pair, tma_store, tma_add in ((1, 1, 1), (0, 1, 1), (1, 0, 1), (1, 1, 0)):
             ctx.setOption("tc_pair", pair)
             ctx.setOption("tc_tma_store", tma_store)
+            ctx.setOption("tc_tma_add", tma_add)
             h = ctx.pushArena()
             try:
                 opts = dict(act=kw.get("act", "none"))
@@ -538,8 +544,10 @@ def test_pair_kernel_matches_one_cta_kernel_and_oracle(ctx, M, K, N, kw):
     finally:
         ctx.setOption("tc_pair", 1)
         ctx.setOption("tc_tma_store", 1)
+        ctx.setOption("tc_tma_add", 1)
     assert np.array_equal(outs[0], outs[1])
     assert np.array_equal(outs[0], outs[2])
+    assert np.array_equal(outs[0], outs[3])
     rows = np.unique(np.concatenate([[0, 1, M - 2, M - 1], rng.integers(0, M, 28)]))
     ora = WasmOracle(threads=True)
     ref = ora.matmul(T(a[rows], len(rows), K), T(w, K, N), bias=T(b, 1, N) if b is not None else None, act=kw.get("act", "none"),
