@@ -226,10 +226,11 @@ __global__ void __launch_bounds__(kPickThreads) k_tdt_pick(const float *__restri
 
 // ---- k_tdt_rows: the prediction network's products, exact f32 ------------------------------------------------
 //
-// out[w][n] = sum_k x[w][k] * Wt[k][n] (+ bias) for up to a few hundred windows and f32 weights, K = 1280 (an LSTM
-// layer: [input | committed hidden state] against [W;R]^T, followed in the same kernel by the cell) or K = 640 (the
-// prediction projection).  With 32 rows a tensor-core tile is mostly padding and the f32 weights would need the
-// three-product tf32 scheme; plain FFMA does the 105 MFLOP of a layer in a few microseconds and is exact f32.
+// out[w][n] = sum_k x[w][k] * Wt[k][n] (+ bias) for up to a few hundred windows and f32 weights, K = 1280 (LSTM layer 1:
+// [input | committed hidden state] against [W;R]^T, followed in the same kernel by the cell) or K = 640 (layer 0,
+// whose input half is a table row per token, and the prediction projection).  With 32 rows a tensor-core tile is
+// mostly padding and the f32 weights would need the three-product tf32 scheme; plain FFMA does the 105 MFLOP of a
+// layer in a few microseconds and is exact f32.
 //
 // One block owns 20 output columns (for an LSTM layer: the 4 gates of 5 hidden units, so that the cell can follow
 // without a grid-wide step) and one chunk of 32 windows.  Its 16 warps split K; a warp streams its slice of the
